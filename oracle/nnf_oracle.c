@@ -1,0 +1,552 @@
+/*
+ * CPU restatement of nnForge's plain (CPU) backend for the batch-norm / activation / add /
+ * softmax / max-subsampling path, in plain C.
+ *
+ * TEST INFRASTRUCTURE ONLY. This file is the parity checker and the timed CPU baseline; the product
+ * library never links, loads or calls it. Every function names the reference lines it follows
+ * (paths relative to the reference project root). Expression order, accumulator seeds and scan
+ * order are kept exactly as in those lines because the parity bar is bit-exactness for ReLU and
+ * max-pool results. Build with -O2 -ffp-contract=off and without -ffast-math (oracle/build_oracle.py).
+ *
+ * Pinning: each function below that has a reference counterpart is compared bit-for-bit against the
+ * reference's own sources compiled in place (oracle/build_ref.py -> oracle/_ref) by
+ * tests/test_oracle_vs_reference.py wherever a reference checkout is present, and against the
+ * golden vectors under tests/golden/ (generated from that reference build) everywhere else.
+ * Training-mode batch norm (orc_bn_train_*) has NO reference CPU implementation - the reference
+ * calls cuDNN there - so its parity is UNPINNED by reference code; it restates the documented
+ * spatial batch-norm formulas and is cross-checked against a double-precision twin and against
+ * PyTorch's CPU batch_norm in the tests.
+ *
+ * Layout everywhere: planar fp32, offset = ((n*C + c)*H + y)*W + x.
+ * With -fopenmp the outer loops run in parallel exactly where the reference has its
+ * "#pragma omp parallel for"; results do not depend on the thread count except where stated.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#define ORC_PAR _Pragma("omp parallel for schedule(guided)")
+#else
+#define ORC_PAR
+#endif
+
+typedef int64_t i64;
+
+int orc_max_threads(void)
+{
+#ifdef _OPENMP
+	return omp_get_max_threads();
+#else
+	return 1;
+#endif
+}
+
+/* ---- batch norm, inference: nnforge/plain/batch_norm_layer_tester_plain.cpp:30-75 ------------
+ * mult = gamma*invsigma; add = beta - mult*mean (both rounded to fp32, per (entry, channel));
+ * y = x*mult + add with a separately rounded product (no fused multiply-add). */
+void orc_bn_infer(float * y, const float * x, const float * gamma, const float * beta, const float * mean,
+	const float * invsigma, i64 n, i64 c, i64 hw)
+{
+	const i64 total = n * c;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const i64 ch = w % c;
+		const float mult = gamma[ch] * invsigma[ch];
+		const float add = beta[ch] - mult * mean[ch];
+		const float * in = x + w * hw;
+		float * out = y + w * hw;
+		i64 i;
+		for (i = 0; i < hw; ++i)
+			out[i] = in[i] * mult + add;
+	}
+}
+
+/* ---- ReLU: nnforge/plain/rectified_linear_layer_tester_plain.cpp:50-55 -------------------------
+ * Negative inputs are multiplied by the slope, so slope 0 produces -0.0f. */
+void orc_relu_fwd(float * y, const float * x, float slope, i64 count)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float v = x[i];
+		y[i] = v >= 0.0F ? v : v * slope;
+	}
+}
+
+/* nnforge/plain/rectified_linear_layer_updater_plain.cpp:62-107: gate on the INPUT value. */
+void orc_relu_bwd(float * dx, const float * dy, const float * x, float slope, i64 count, int add_to_destination)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float g = (x[i] >= 0.0F) ? dy[i] : dy[i] * slope;
+		if (add_to_destination)
+			dx[i] += g;
+		else
+			dx[i] = g;
+	}
+}
+
+/* ---- PReLU: nnforge/plain/parametric_rectified_linear_layer_tester_plain.cpp:51-70 ------------- */
+void orc_prelu_fwd(float * y, const float * x, const float * slope, i64 n, i64 c, i64 hw)
+{
+	const i64 total = n * c;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const float a = slope[w % c];
+		const float * in = x + w * hw;
+		float * out = y + w * hw;
+		i64 i;
+		for (i = 0; i < hw; ++i)
+			out[i] = in[i] * (in[i] >= 0.0F ? 1.0F : a);
+	}
+}
+
+/* nnforge/plain/parametric_rectified_linear_layer_updater_plain.cpp:74-135 */
+void orc_prelu_bwd_data(float * dx, const float * dy, const float * x, const float * slope, i64 n, i64 c, i64 hw,
+	int add_to_destination)
+{
+	const i64 total = n * c;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const float a = slope[w % c];
+		i64 i;
+		for (i = 0; i < hw; ++i)
+		{
+			const i64 k = w * hw + i;
+			const float g = dy[k] * (x[k] >= 0.0F ? 1.0F : a);
+			if (add_to_destination)
+				dx[k] += g;
+			else
+				dx[k] = g;
+		}
+	}
+}
+
+/* nnforge/plain/parametric_rectified_linear_layer_updater_plain.cpp:137-190: per channel, an fp32
+ * sum over the pixels of one entry, then an fp32 sum of those over entries, ADDED to the gradient. */
+void orc_prelu_bwd_weights(float * dslope, const float * dy, const float * x, i64 n, i64 c, i64 hw)
+{
+	i64 ch;
+	ORC_PAR
+	for (ch = 0; ch < c; ++ch)
+	{
+		float sum = 0.0F;
+		i64 e;
+		for (e = 0; e < n; ++e)
+		{
+			const i64 base = (e * c + ch) * hw;
+			float local_sum = 0.0F;
+			i64 i;
+			for (i = 0; i < hw; ++i)
+				local_sum += dy[base + i] * (x[base + i] >= 0.0F ? 0.0F : x[base + i]);
+			sum += local_sum;
+		}
+		dslope[ch] += sum;
+	}
+}
+
+/* ---- ELU (alpha fixed at 1): nnforge/plain/exponential_linear_layer_tester_plain.cpp:48-53 ----- */
+void orc_elu_fwd(float * y, const float * x, i64 count)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+		y[i] = x[i] >= 0.0F ? x[i] : (expf(x[i]) - 1.0F);
+}
+
+/* nnforge/plain/exponential_linear_layer_updater_plain.cpp:59-103: derivative from the OUTPUT. */
+void orc_elu_bwd(float * dx, const float * dy, const float * y, i64 count, int add_to_destination)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float der = (y[i] >= 0) ? 1.0F : (y[i] + 1.0F);
+		if (add_to_destination)
+			dx[i] += dy[i] * der;
+		else
+			dx[i] = dy[i] * der;
+	}
+}
+
+/* ---- TanH: nnforge/plain/hyperbolic_tangent_layer_tester_plain.cpp:47-58 ---------------------- */
+void orc_tanh_fwd(float * y, const float * x, float scale, float steepness, i64 count)
+{
+	const float steepness2 = steepness * 2.0F;
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float e = expf(x[i] * steepness2);
+		y[i] = (e - 1.0F) / (e + 1.0F) * scale;
+	}
+}
+
+/* nnforge/plain/hyperbolic_tangent_layer_updater_plain.cpp:62-112 */
+void orc_tanh_bwd(float * dx, const float * dy, const float * y, float scale, float steepness, i64 count, int add_to_destination)
+{
+	const float scale_reverse = 1.0F / scale;
+	const float steepness3 = steepness * scale;
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float nv = y[i] * scale_reverse;
+		const float der = steepness3 * (1.0F - (nv * nv));
+		if (add_to_destination)
+			dx[i] += dy[i] * der;
+		else
+			dx[i] = dy[i] * der;
+	}
+}
+
+/* ---- Sigmoid: nnforge/plain/sigmoid_layer_tester_plain.cpp:47-53 ------------------------------ */
+void orc_sigmoid_fwd(float * y, const float * x, i64 count)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+		y[i] = 1.0F / (expf(-x[i]) + 1.0F);
+}
+
+/* nnforge/plain/sigmoid_layer_updater_plain.cpp:59-103 */
+void orc_sigmoid_bwd(float * dx, const float * dy, const float * y, i64 count, int add_to_destination)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		const float der = y[i] * (1.0F - y[i]);
+		if (add_to_destination)
+			dx[i] += dy[i] * der;
+		else
+			dx[i] = dy[i] * der;
+	}
+}
+
+/* ---- Add: nnforge/plain/add_layer_tester_plain.cpp:53-61 ---------------------------------------
+ * The accumulator starts at +0.0f and the scale is applied to the finished sum. */
+void orc_add_fwd(float * y, const float * const * inputs, int input_count, float alpha, i64 count)
+{
+	i64 i;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		float sum = 0.0F;
+		int j;
+		for (j = 0; j < input_count; ++j)
+			sum += inputs[j][i];
+		y[i] = sum * alpha;
+	}
+}
+
+/* nnforge/plain/add_layer_updater_plain.cpp:66-109 (in place with alpha == 1 is a no-op there). */
+void orc_add_bwd(float * dx, const float * dy, float alpha, i64 count, int add_to_destination)
+{
+	i64 i;
+	if (!add_to_destination && dx == dy && alpha == 1.0F)
+		return;
+	ORC_PAR
+	for (i = 0; i < count; ++i)
+	{
+		if (add_to_destination)
+			dx[i] += dy[i] * alpha;
+		else
+			dx[i] = dy[i] * alpha;
+	}
+}
+
+/* ---- Softmax over channels: nnforge/plain/softmax_layer_tester_plain.cpp:65-88 -----------------
+ * max seeded with -1.0e37f, ascending-c fp32 sum, multiply by the rounded reciprocal. */
+void orc_softmax_fwd(float * y, const float * x, i64 n, i64 c, i64 hw)
+{
+	const i64 total = n * hw;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const i64 e = w / hw;
+		const i64 p = w - e * hw;
+		const float * in = x + e * c * hw + p;
+		float * out = y + e * c * hw + p;
+		float max_val = -1.0e+37F;
+		float sum = 0.0F;
+		float mult;
+		i64 f;
+		for (f = 0; f < c; ++f)
+		{
+			const float v = in[f * hw];
+			max_val = (max_val < v) ? v : max_val; /* std::max(max_val, v) */
+		}
+		for (f = 0; f < c; ++f)
+		{
+			const float v = expf(in[f * hw] - max_val);
+			sum += v;
+			out[f * hw] = v;
+		}
+		mult = 1.0F / sum;
+		for (f = 0; f < c; ++f)
+			out[f * hw] *= mult;
+	}
+}
+
+/* nnforge/plain/softmax_layer_updater_plain.cpp:100-166 */
+void orc_softmax_bwd(float * dx, const float * dy, const float * y, i64 n, i64 c, i64 hw, int add_to_destination)
+{
+	const i64 total = n * hw;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const i64 e = w / hw;
+		const i64 p = w - e * hw;
+		const i64 base = e * c * hw + p;
+		float sum = 0.0F;
+		i64 f;
+		for (f = 0; f < c; ++f)
+			sum += dy[base + f * hw] * y[base + f * hw];
+		for (f = 0; f < c; ++f)
+		{
+			const float g = y[base + f * hw] * (dy[base + f * hw] - sum);
+			if (add_to_destination)
+				dx[base + f * hw] += g;
+			else
+				dx[base + f * hw] = g;
+		}
+	}
+}
+
+/* ---- Max subsampling ---------------------------------------------------------------------------
+ * Output extent: nnforge/max_subsampling_layer.cpp:125-133. */
+i64 orc_maxpool_out_size(i64 in_size, i64 window, i64 stride, int round_up)
+{
+	return (in_size + stride - window + (round_up ? window - 1 : 0)) / stride;
+}
+
+/* Forward with argmax: nnforge/plain/max_subsampling_layer_updater_plain.cpp:118-168.
+ * The window is scanned x-fastest (offset table of :99-115), the first element always seeds the
+ * result and a later one replaces it only on a strict ">" ("<" for is_min). argmax holds the
+ * ABSOLUTE input element offset as unsigned int, or may be NULL (tester variant,
+ * nnforge/plain/max_subsampling_layer_tester_plain.cpp:170-288).
+ * round_up is refused by the plain backend (:60-62); here it clips the window to the input, which
+ * is what the reference CUDA kernel does (nnforge/cuda/max_subsampling_layer_updater_cuda.cuh:108-150). */
+void orc_maxpool_fwd(float * y, uint32_t * argmax, const float * x, i64 n, i64 c, i64 h, i64 w,
+	i64 win_w, i64 win_h, i64 stride_w, i64 stride_h, int round_up_w, int round_up_h, int is_min)
+{
+	const i64 ow = orc_maxpool_out_size(w, win_w, stride_w, round_up_w);
+	const i64 oh = orc_maxpool_out_size(h, win_h, stride_h, round_up_h);
+	const i64 planes = n * c;
+	i64 pl;
+	ORC_PAR
+	for (pl = 0; pl < planes; ++pl)
+	{
+		const float * in = x + pl * h * w;
+		i64 oy, ox;
+		for (oy = 0; oy < oh; ++oy)
+			for (ox = 0; ox < ow; ++ox)
+			{
+				float best = is_min ? 1.0e37F : -1.0e37F;
+				i64 best_index = 0;
+				int first = 1;
+				i64 ky, kx;
+				for (ky = 0; ky < win_h; ++ky)
+				{
+					const i64 iy = oy * stride_h + ky;
+					if (iy >= h)
+						break;
+					for (kx = 0; kx < win_w; ++kx)
+					{
+						const i64 ix = ox * stride_w + kx;
+						float v;
+						if (ix >= w)
+							break;
+						v = in[iy * w + ix];
+						if (first || ((v > best) && !is_min) || ((v < best) && is_min))
+						{
+							best = v;
+							best_index = pl * h * w + iy * w + ix;
+							first = 0;
+						}
+					}
+				}
+				y[(pl * oh + oy) * ow + ox] = best;
+				if (argmax)
+					argmax[(pl * oh + oy) * ow + ox] = (uint32_t)best_index;
+			}
+	}
+}
+
+/* Backward: nnforge/plain/max_subsampling_layer_updater_plain.cpp:173-231, in the only form that is
+ * well defined for overlapping windows: destination zero-filled unless accumulating, then
+ * "dx[argmax[o]] += dy[o]" serially in ascending output index o. (The reference's non-accumulating
+ * branch assigns instead of adding and both branches run under an OpenMP loop, which loses or races
+ * contributions when windows overlap; its CUDA twin zero-fills and adds atomically.) Always serial. */
+void orc_maxpool_bwd(float * dx, const float * dy, const uint32_t * argmax, i64 in_count, i64 out_count, int add_to_destination)
+{
+	i64 o;
+	if (!add_to_destination)
+		memset(dx, 0, (size_t)in_count * sizeof(float));
+	for (o = 0; o < out_count; ++o)
+		dx[argmax[o]] += dy[o];
+}
+
+/* ---- Batch norm, training mode (NO reference CPU code; parity unpinned) ------------------------
+ * Replaces the two cuDNN calls at nnforge/cuda/batch_norm_layer_updater_cuda.cu:89-106 and :145-164.
+ * Documented spatial batch norm: mean = sum(x)/m, biased var = sum((x-mean)^2)/m,
+ * invstd = 1/sqrt(var+eps). The normalisation is then applied in the inference form of
+ * nnforge/plain/batch_norm_layer_tester_plain.cpp:60-72 (mult = gamma*invstd, add = beta - mult*mean,
+ * y = x*mult + add) so that the sign of y - which gates the following PReLU/ELU - is decided by one
+ * expression in forward and backward.
+ *
+ * Statistics are accumulated in double here (the "exact" twin); orc_bn_train_stats_f32 is the fp32
+ * form using the only per-channel reduction order the reference owns (per-entry inner sum, then
+ * across entries: nnforge/plain/parametric_rectified_linear_layer_updater_plain.cpp:166-188).
+ * count_total lets a caller pass statistics summed over several shards (synchronised batch norm). */
+void orc_bn_train_sums(double * sum, double * sumsq, const float * x, i64 n, i64 c, i64 hw)
+{
+	i64 ch;
+	ORC_PAR
+	for (ch = 0; ch < c; ++ch)
+	{
+		double s = 0.0, q = 0.0;
+		i64 e, i;
+		for (e = 0; e < n; ++e)
+		{
+			const float * in = x + (e * c + ch) * hw;
+			for (i = 0; i < hw; ++i)
+			{
+				s += in[i];
+				q += (double)in[i] * in[i];
+			}
+		}
+		sum[ch] = s;
+		sumsq[ch] = q;
+	}
+}
+
+void orc_bn_train_sums_f32(float * sum, float * sumsq, const float * x, i64 n, i64 c, i64 hw)
+{
+	i64 ch;
+	ORC_PAR
+	for (ch = 0; ch < c; ++ch)
+	{
+		float s = 0.0F, q = 0.0F;
+		i64 e, i;
+		for (e = 0; e < n; ++e)
+		{
+			const float * in = x + (e * c + ch) * hw;
+			float ls = 0.0F, lq = 0.0F;
+			for (i = 0; i < hw; ++i)
+			{
+				ls += in[i];
+				lq += in[i] * in[i];
+			}
+			s += ls;
+			q += lq;
+		}
+		sum[ch] = s;
+		sumsq[ch] = q;
+	}
+}
+
+/* mean/invstd from (already global) sums over count_total elements per channel; written as
+ * saved[0:c] = mean, saved[c:2c] = invstd, the layout of the reference's temporary_fixed_buffer
+ * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:105-106). */
+void orc_bn_train_finalize(float * saved, const double * sum, const double * sumsq, i64 c, double count_total, float eps)
+{
+	i64 ch;
+	for (ch = 0; ch < c; ++ch)
+	{
+		const double mean = sum[ch] / count_total;
+		double var = sumsq[ch] / count_total - mean * mean;
+		if (var < 0.0)
+			var = 0.0;
+		saved[ch] = (float)mean;
+		saved[c + ch] = (float)(1.0 / sqrt(var + (double)eps));
+	}
+}
+
+/* y = x*mult + add with the saved statistics. */
+void orc_bn_train_apply(float * y, const float * x, const float * gamma, const float * beta, const float * saved, i64 n, i64 c, i64 hw)
+{
+	orc_bn_infer(y, x, gamma, beta, saved, saved + c, n, c, hw);
+}
+
+/* Per-channel backward sums in double: dbeta = sum(du), dgamma = sum(du * xhat),
+ * xhat = (x - mean)*invstd evaluated in fp32. */
+void orc_bn_train_bwd_sums(double * dbeta, double * dgamma, const float * du, const float * x, const float * saved, i64 n, i64 c, i64 hw)
+{
+	i64 ch;
+	ORC_PAR
+	for (ch = 0; ch < c; ++ch)
+	{
+		const float mean = saved[ch], invstd = saved[c + ch];
+		double sb = 0.0, sg = 0.0;
+		i64 e, i;
+		for (e = 0; e < n; ++e)
+		{
+			const i64 base = (e * c + ch) * hw;
+			for (i = 0; i < hw; ++i)
+			{
+				const float xhat = (x[base + i] - mean) * invstd;
+				sb += du[base + i];
+				sg += (double)du[base + i] * xhat;
+			}
+		}
+		dbeta[ch] = sb;
+		dgamma[ch] = sg;
+	}
+}
+
+/* dx = gamma*invstd/m * (m*du - dbeta - xhat*dgamma), evaluated in double and rounded once;
+ * accumulates when add_to_destination (cuDNN beta_data = 1 at :135). dbeta/dgamma are the global sums. */
+void orc_bn_train_bwd_apply(float * dx, const float * du, const float * x, const float * gamma, const float * saved,
+	const double * dbeta, const double * dgamma, i64 n, i64 c, i64 hw, double count_total, int add_to_destination)
+{
+	const i64 total = n * c;
+	i64 w;
+	ORC_PAR
+	for (w = 0; w < total; ++w)
+	{
+		const i64 ch = w % c;
+		const float mean = saved[ch], invstd = saved[c + ch];
+		const double k = (double)gamma[ch] * invstd / count_total;
+		i64 i;
+		for (i = 0; i < hw; ++i)
+		{
+			const i64 idx = w * hw + i;
+			const float xhat = (x[idx] - mean) * invstd;
+			const float g = (float)(k * (count_total * du[idx] - dbeta[ch] - (double)xhat * dgamma[ch]));
+			if (add_to_destination)
+				dx[idx] += g;
+			else
+				dx[idx] = g;
+		}
+	}
+}
+
+/* Running-statistics pseudo-gradients: nnforge/cuda/batch_norm_layer_updater_cuda.cu:28-44,167-182.
+ * grad_mean += entry_count*(batch_mean - mean), same for the inverse standard deviation. */
+void orc_bn_train_running_grad(float * grad_mean, float * grad_invsigma, const float * saved, const float * mean, const float * invsigma,
+	i64 c, float entry_count)
+{
+	i64 ch;
+	for (ch = 0; ch < c; ++ch)
+	{
+		grad_mean[ch] += entry_count * (saved[ch] - mean[ch]);
+		grad_invsigma[ch] += entry_count * (saved[c + ch] - invsigma[ch]);
+	}
+}

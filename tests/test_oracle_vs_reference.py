@@ -1,0 +1,74 @@
+"""The C restatement against nnForge's own plain sources compiled in place (oracle/_ref), on
+seeded random tensors including ragged sizes. Skipped where no reference build exists (the golden
+fixture test covers those machines)."""
+import numpy as np
+import pytest
+
+import synth
+from util import assert_bits_equal
+
+SHAPES = [(1, 1, 1, 1), (2, 3, 5, 7), (3, 4, 8, 8), (2, 21, 1, 1), (5, 2, 7, 7), (1, 7, 13, 3)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_elementwise(oracle, reference, shape):
+    g = synth.rng(50, salt=sum(shape))
+    x = synth.with_edges(g, synth.normal(g, shape, 0.0, 1.5))
+    xs = synth.normal(g, shape)
+    dy = synth.normal(g, shape)
+    dx0 = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta, mean, invsigma = synth.bn_params(g, c)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    assert_bits_equal(oracle.bn_infer(x, gamma, beta, mean, invsigma), reference.bn_infer(x, gamma, beta, mean, invsigma)[0], "bn")
+    for s in (0.0, 0.25, -0.5):
+        assert_bits_equal(oracle.relu_fwd(x, s), reference.relu_fwd(x, s)[0], "relu")
+        assert_bits_equal(oracle.relu_bwd(dy, x, s), reference.relu_bwd(dy, x, s)[0], "relu bwd")
+        assert_bits_equal(oracle.relu_bwd(dy, x, s, dx=dx0), reference.relu_bwd(dy, x, s, dx=dx0)[0], "relu bwd add")
+    assert_bits_equal(oracle.prelu_fwd(x, slope), reference.prelu_fwd(x, slope)[0], "prelu")
+    assert_bits_equal(oracle.prelu_bwd_data(dy, x, slope), reference.prelu_bwd_data(dy, x, slope)[0], "prelu bwd")
+    assert_bits_equal(oracle.prelu_bwd_data(dy, x, slope, dx=dx0), reference.prelu_bwd_data(dy, x, slope, dx=dx0)[0], "prelu bwd add")
+    assert_bits_equal(oracle.prelu_bwd_weights(dy, xs, dslope=slope), reference.prelu_bwd_weights(dy, xs, dslope=slope)[0], "dslope")
+    y = oracle.elu_fwd(x)
+    assert_bits_equal(y, reference.elu_fwd(x)[0], "elu")
+    assert_bits_equal(oracle.elu_bwd(dy, y), reference.elu_bwd(dy, y)[0], "elu bwd")
+    assert_bits_equal(oracle.elu_bwd(dy, y, dx=dx0), reference.elu_bwd(dy, y, dx=dx0)[0], "elu bwd add")
+    y = oracle.tanh_fwd(xs, 1.7159, 0.6666)
+    assert_bits_equal(y, reference.tanh_fwd(xs, 1.7159, 0.6666)[0], "tanh")
+    assert_bits_equal(oracle.tanh_bwd(dy, y, 1.7159, 0.6666), reference.tanh_bwd(dy, y, 1.7159, 0.6666)[0], "tanh bwd")
+    y = oracle.sigmoid_fwd(x)
+    assert_bits_equal(y, reference.sigmoid_fwd(x)[0], "sigmoid")
+    assert_bits_equal(oracle.sigmoid_bwd(dy, y), reference.sigmoid_bwd(dy, y)[0], "sigmoid bwd")
+    for k, alpha in ((1, 1.0), (2, 1.0), (3, 0.3)):
+        ins = [x, xs, dy][:k]
+        assert_bits_equal(oracle.add_fwd(ins, alpha), reference.add_fwd(ins, alpha)[0], "add")
+    assert_bits_equal(oracle.add_bwd(dy, 0.3), reference.add_bwd(dy, 0.3)[0], "add bwd")
+    assert_bits_equal(oracle.add_bwd(dy, 1.0, dx=dx0), reference.add_bwd(dy, 1.0, dx=dx0)[0], "add bwd add")
+
+
+@pytest.mark.parametrize("shape", [(2, 1, 1, 1), (3, 21, 4, 5), (4, 1000, 1, 1), (2, 5, 1, 9), (1, 33, 3, 3)])
+def test_softmax(oracle, reference, shape):
+    g = synth.rng(51, salt=sum(shape))
+    x = synth.normal(g, shape, 0.0, 3.0)
+    dy = synth.normal(g, shape)
+    y = oracle.softmax_fwd(x)
+    assert_bits_equal(y, reference.softmax_fwd(x)[0], "softmax tester")
+    assert_bits_equal(y, reference.softmax_fwd(x, updater=True)[0], "softmax updater")
+    assert_bits_equal(oracle.softmax_bwd(dy, y), reference.softmax_bwd(dy, y)[0], "softmax bwd")
+    assert_bits_equal(oracle.softmax_bwd(dy, y, dx=x), reference.softmax_bwd(dy, y, dx=x)[0], "softmax bwd add")
+
+
+@pytest.mark.parametrize("hw", [(7, 7), (9, 11), (14, 14), (5, 8)])
+@pytest.mark.parametrize("win,stride", [((3, 3), (2, 2)), ((2, 2), (2, 2)), ((3, 3), (1, 1)), ((2, 3), (2, 1)), ((1, 1), (1, 1)), ((5, 5), (3, 3))])
+def test_maxpool(oracle, reference, hw, win, stride):
+    g = synth.rng(52, salt=hw[0] * 31 + win[0] * 7 + stride[1])
+    x = oracle.relu_fwd(synth.normal(g, (2, 3) + hw), 0.0)  # many exact ties and -0/+0 mixes
+    for is_min in (False, True):
+        y, idx = oracle.maxpool_fwd(x, win, stride, is_min=is_min)
+        ry, ridx, _ = reference.maxpool_fwd(x, win, stride, is_min=is_min)
+        assert_bits_equal(y, ry, "pool values")
+        assert_bits_equal(idx, ridx, "pool argmax")
+        assert_bits_equal(y, reference.maxpool_tester_fwd(x, win, stride, is_min=is_min)[0], "pool tester values")
+    y, idx = oracle.maxpool_fwd(x, win, stride)
+    dy = synth.normal(g, y.shape)
+    assert_bits_equal(oracle.maxpool_bwd(dy, idx, x.shape), reference.maxpool_bwd(dy, idx, x.shape)[0], "pool bwd")
