@@ -1,0 +1,343 @@
+"""Benchmark of the fused batch-norm + activation path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (one "step"): training-mode batch norm fused with PReLU then ELU, forward and backward, on
+x[256, 256, 28, 28] fp32 PER GPU (weak scaling: the global batch is 256*N entries, sharded on the
+batch axis; training batch norm all-reduces 2*C floats forward and 2*C floats backward over NCCL).
+Inputs are seeded synthetic tensors (x ~ N(0.5, 2), dy ~ N(0, 1), gamma ~ U(0.5, 1.5),
+beta ~ N(0, 0.1), slope ~ U(0, 0.3)); each tensor is 205 MB, larger than the 126 MB L2, so timed
+iterations stream from HBM without an explicit flush.
+
+Metric: achieved HBM GB/s over all GPUs, counting ALGORITHMIC bytes only: forward 8 B/element (read
+x, write y) + backward 12 B/element (read x, dy, write dx) = 20 B/element/step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_PER_GPU, C, H, W = 256, 256, 28, 28
+EPS = 1e-5
+BYTES_PER_ELEM_FWD = 8
+BYTES_PER_ELEM_BWD = 12
+METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
+WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        for line in self.lines:
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        # under load = the upper half of the samples (idle samples before/after the region read low or max)
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def elements_per_gpu():
+    return N_PER_GPU * C * H * W
+
+
+def cpu_step_seconds(n_sample, threads_hint=None, reps=2):
+    """One unfused, layer-by-layer training step of the same chain on the host cores, the way the
+    reference schedules its plain backend: BN(batch stats) -> PReLU -> ELU, then ELU', PReLU' (data and
+    weights), BN'. PReLU and ELU run nnForge's own plain sources when the reference-backed library was
+    built; training batch norm has no CPU implementation in the reference, so that layer always runs
+    our C restatement. Returns (seconds per step, threads, description)."""
+    import numpy as np
+    from oracle import Oracle, Reference
+    orc = Oracle(parallel=True)
+    ref = Reference(parallel=True)
+    g = np.random.Generator(np.random.PCG64(1002))
+    shape = (n_sample, C, H, W)
+    x = (g.standard_normal(shape, dtype=np.float32) * 2 + np.float32(0.5)).astype(np.float32)
+    dy = g.standard_normal(shape, dtype=np.float32)
+    gamma = (g.random(C, dtype=np.float32) + np.float32(0.5)).astype(np.float32)
+    beta = (g.standard_normal(C, dtype=np.float32) * np.float32(0.1)).astype(np.float32)
+    slope = (g.random(C, dtype=np.float32) * np.float32(0.3)).astype(np.float32)
+    m = n_sample * H * W
+    best = None
+    for _ in range(reps):
+        t = 0.0
+        t0 = time.perf_counter()
+        s, q = orc.bn_train_sums(x, f32=True)
+        saved = orc.bn_train_finalize(s, q, m, EPS)
+        u = orc.bn_train_apply(x, gamma, beta, saved)
+        t += time.perf_counter() - t0
+        if ref.available:
+            v, dt1 = ref.prelu_fwd(u, slope)
+            y, dt2 = ref.elu_fwd(v)
+            dv, dt3 = ref.elu_bwd(dy, y)
+            du, dt4 = ref.prelu_bwd_data(dv, u, slope)
+            _, dt5 = ref.prelu_bwd_weights(dv, u)
+            t += dt1 + dt2 + dt3 + dt4 + dt5
+        else:
+            t0 = time.perf_counter()
+            v = orc.prelu_fwd(u, slope)
+            y = orc.elu_fwd(v)
+            dv = orc.elu_bwd(dy, y)
+            du = orc.prelu_bwd_data(dv, u, slope)
+            orc.prelu_bwd_weights(dv, u)
+            t += time.perf_counter() - t0
+        t0 = time.perf_counter()
+        db, dg = orc.bn_train_bwd_sums(du, x, saved)
+        orc.bn_train_bwd_apply(du, x, gamma, saved, db, dg, m)
+        t += time.perf_counter() - t0
+        best = t if best is None else min(best, t)
+    kind = "port"  # the dominant layer (training batch norm) has no reference CPU code; see the description
+    desc = ("%d of %d entries of the workload, unfused layer by layer (BN-train fwd/bwd: C restatement, no reference CPU code exists; "
+            "PReLU/ELU fwd/bwd: %s), OpenMP on all host threads, best of %d"
+            % (n_sample, N_PER_GPU, "nnForge plain sources" if ref.available else "C restatement", reps))
+    return best, orc.threads, kind, desc
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU path for the same workload, timed on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_sample = 32
+    # steps are bounded samples; warm-up steps are run too (page faults, thread pool spin-up)
+    for _ in range(min(args.warmup, 2)):
+        cpu_step_seconds(n_sample, reps=1)
+    times = []
+    for _ in range(max(1, min(args.steps, 5))):
+        sec, threads, kind, desc = cpu_step_seconds(n_sample, reps=1)
+        times.append(sec)
+    sec = sum(times) / len(times)
+    elems = n_sample * C * H * W
+    gbs = elems * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD) / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 2),
+        "ms_per_step": sec * 1e3 * (N_PER_GPU / n_sample), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2", "note": "CPU path; ms_per_step extrapolated from the sample to the full per-GPU batch"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind, "sample": desc},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import nnforge_b200.capi as capi  # raises if the CUDA library is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1002 + rank)
+    shape = (N_PER_GPU, C, H, W)
+    x = torch.randn(shape, device="cuda", generator=gen) * 2 + 0.5
+    dy = torch.randn(shape, device="cuda", generator=gen)
+    pgen = torch.Generator(device="cuda")
+    pgen.manual_seed(1002)
+    gamma = torch.rand(C, device="cuda", generator=pgen) + 0.5
+    beta = torch.randn(C, device="cuda", generator=pgen) * 0.1
+    slope = torch.rand(C, device="cuda", generator=pgen) * 0.3
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    hw = H * W
+    m_total = float(N_PER_GPU * world * hw)
+    ws = torch.empty(capi.bn_train_workspace_bytes(N_PER_GPU, C, hw), dtype=torch.uint8, device="cuda")
+    sums, saved = torch.empty(2 * C, device="cuda"), torch.empty(2 * C, device="cuda")
+    bsums, gsums = torch.empty(3 * C, device="cuda"), torch.empty(2 * C, device="cuda")
+    grads = [torch.zeros(C, device="cuda") for _ in range(3)]
+    acts = [capi.prelu(slope), capi.elu()]
+    launches_per_step = 6
+    phases = ("stats", "apply", "bwd_stats", "bwd_apply")
+
+    def step(ev=None):
+        def mark(i):
+            if ev is not None:
+                ev[i].record()
+        mark(0)
+        capi.bn_train_stats(sums, x, ws)
+        mark(1)
+        if dist is not None:
+            dist.all_reduce(sums)
+        mark(2)
+        capi.bn_train_apply_act(y, saved, x, gamma, beta, sums, m_total, EPS, acts)
+        mark(3)
+        capi.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, ws, gsums=gsums if dist is not None else None)
+        mark(4)
+        if dist is not None:
+            dist.all_reduce(gsums)
+        mark(5)
+        capi.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums if dist is not None else bsums, bsums, m_total, acts,
+                                grad_gamma=grads[0], grad_beta=grads[1], grad_slope=grads[2], entry_count=float(N_PER_GPU))
+        mark(6)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(args.steps)]
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    if rank == 0:
+        time.sleep(0.2)
+        clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    elems = elements_per_gpu()
+    bytes_step_all = elems * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD) * world
+    value = bytes_step_all / (ms_step * 1e-3) / 1e9
+
+    # per-kernel durations from the events recorded inside the timed region (this rank)
+    idx = {"stats": (0, 1), "apply": (2, 3), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
+    kernel_ms = {name: sum(e[a].elapsed_time(e[b]) for e in evs) / len(evs) for name, (a, b) in idx.items()}
+    alg_bytes = {"stats": 4 * elems, "apply": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
+    peak, peak_kind = measured_peaks()
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    achieved = alg_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": peak_kind + " copy bandwidth", "traffic": None,
+                "kernels": {k: {"ms": kernel_ms[k], "algorithmic_GBps": alg_bytes[k] / (kernel_ms[k] * 1e-3) / 1e9} for k in phases},
+                "step_frac_of_peak": (value / world) / peak}
+
+    # end to end through the C ABI with host buffers: H2D of x and dy, the same step, D2H of y and dx
+    xh, dyh = x.cpu().pin_memory(), dy.cpu().pin_memory()
+    yh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
+
+    def e2e_step():
+        x.copy_(xh, non_blocking=True)
+        dy.copy_(dyh, non_blocking=True)
+        step()
+        yh.copy_(y, non_blocking=True)
+        dxh.copy_(dx, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    tensor_bytes = elems * 4
+    e2e = {"value": bytes_step_all / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": 2 * tensor_bytes, "d2h_bytes_per_step": 2 * tensor_bytes}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, threads, kind, desc = cpu_step_seconds(32, reps=2)
+        cpu = {"value": 32 * C * H * W * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD) / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": kind, "sample": desc}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": N_PER_GPU * world, "parallelism": "dp%d" % world,
+                       "collective": "2 x all-reduce of 2*C floats per step (NCCL)" if world > 1 else "none",
+                       "l2": "inputs larger than L2 (205 MB per tensor vs 126 MB), no flush needed",
+                       "bytes_per_element": {"forward": BYTES_PER_ELEM_FWD, "backward": BYTES_PER_ELEM_BWD}},
+            "gelem_per_s": elems * world / (ms_step * 1e-3) / 1e9,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

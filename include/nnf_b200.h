@@ -1,0 +1,235 @@
+/*
+ * nnf_b200 - C ABI of the B200 (sm_100a) kernels that replace nnForge's CUDA batch-norm /
+ * activation / add / softmax / max-subsampling layer kernels.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer to planar fp32 data, offset = ((n*C + c)*H + y)*W + x
+ *    (the layout nnforge/cuda/cudnn_util.cpp:27-55 describes to cuDNN), unless stated otherwise.
+ *  - Every call only ENQUEUES work on `stream` (a cudaStream_t); nothing synchronises the device,
+ *    allocates device memory or touches another device. This is the contract of
+ *    layer_tester_cuda::enqueue_forward_propagation (nnforge/cuda/layer_tester_cuda.h:47-57) and of
+ *    the layer_updater_cuda::enqueue_* members (nnforge/cuda/layer_updater_cuda.h:50-112).
+ *  - Return value: NNF_OK (0) or a negative nnf_status; the text of the last failure of the calling
+ *    thread is available from nnf_last_error_string(). Nothing throws. The C++ adapter classes turn
+ *    a non-zero status into the neural_network_exception the reference's callers expect.
+ *  - `hw` is H*W (1 for a fully-connected shaped tensor). Element counts may exceed 2^32; the
+ *    library splits launches internally, the reference's 32-bit indexing limit does not apply.
+ *  - Output buffers may alias the first input where the reference layer answers
+ *    get_input_index_layer_can_write() == 0; this is stated per function.
+ *  - Arithmetic is fp32 with separately rounded multiplies and adds (no FMA contraction), expf and
+ *    division at full precision, so results follow nnForge's plain (CPU) backend: bit-exact for
+ *    batch-norm-inference, ReLU, PReLU, add and max-subsampling (values and argmax), within
+ *    1e-5 relative / 1e-6 absolute elsewhere.
+ */
+#ifndef NNF_B200_H
+#define NNF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NNF_API __attribute__((visibility("default")))
+#else
+#define NNF_API
+#endif
+
+typedef void * nnf_stream_t; /* cudaStream_t */
+
+typedef enum nnf_status
+{
+	NNF_OK = 0,
+	NNF_ERR_INVALID_ARGUMENT = -1, /* null pointer, zero/negative extent, misaligned buffer, unknown enum */
+	NNF_ERR_UNSUPPORTED = -2,      /* valid nnForge configuration this library does not implement */
+	NNF_ERR_WORKSPACE = -3,        /* workspace missing or smaller than nnf_*_workspace_bytes() */
+	NNF_ERR_CUDA = -4              /* a CUDA runtime call or launch failed; text has cudaGetErrorString */
+} nnf_status;
+
+/* Activation kinds, by nnForge layer type name. */
+typedef enum nnf_act_kind
+{
+	NNF_ACT_NONE = 0,
+	NNF_ACT_RELU = 1,    /* "ReLU"    nnforge/rectified_linear_layer.h: p0 = negative_slope */
+	NNF_ACT_PRELU = 2,   /* "PReLU"   nnforge/parametric_rectified_linear_layer.h: slope = device float[C] */
+	NNF_ACT_ELU = 3,     /* "ELU"     nnforge/exponential_linear_layer.h: alpha fixed at 1 */
+	NNF_ACT_TANH = 4,    /* "TanH"    nnforge/hyperbolic_tangent_layer.h: p0 = scale, p1 = steepness */
+	NNF_ACT_SIGMOID = 5  /* "Sigmoid" nnforge/sigmoid_layer.h */
+} nnf_act_kind;
+
+typedef struct nnf_act
+{
+	int32_t kind;        /* nnf_act_kind */
+	float p0;
+	float p1;
+	const float * slope; /* PReLU only */
+} nnf_act;
+
+#define NNF_MAX_ACTS 2   /* a fused chain applies at most this many activations in sequence */
+#define NNF_MAX_ADD_INPUTS 8
+
+NNF_API const char * nnf_last_error_string(void);
+NNF_API int nnf_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Inference batch norm (+ residual add) (+ activation chain), one HBM pass.
+ *   t = x*mult + add,  mult = gamma*invsigma,  add = beta - mult*mean        (gamma != NULL)
+ *   t = x                                                                     (gamma == NULL)
+ *   t = ((0 + t) + residual) * add_alpha                                      (residual != NULL)
+ *   y = act[n_acts-1](...act[0](t))
+ * Replaces batch_norm_layer_tester_cuda::enqueue_forward_propagation
+ * (nnforge/cuda/batch_norm_layer_tester_cuda.cu:62-90; weights = gamma, beta, mean, inverse sigma:
+ * nnforge/batch_norm_layer.h:26) followed by add_layer_tester_cuda (nnforge/cuda/add_layer_tester_cuda.cu:47-83)
+ * and the activation testers (nnforge/cuda/rectified_linear_layer_tester_cuda.cu:52-75,
+ * parametric_rectified_linear_layer_tester_cuda.cu:50-75, exponential_linear_layer_tester_cuda.cu:50-70,
+ * hyperbolic_tangent_layer_tester_cuda.cu:58-84, sigmoid via activation_layer_cudnn_tester_cuda.cpp:40-72).
+ * Arithmetic follows nnforge/plain/batch_norm_layer_tester_plain.cpp:60-72 and
+ * nnforge/plain/add_layer_tester_plain.cpp:53-61. y may alias x. */
+NNF_API int nnf_bn_infer_act(nnf_stream_t stream, float * y, const float * x,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	const float * residual, float add_alpha,
+	const nnf_act * acts, int n_acts,
+	int64_t n, int64_t c, int64_t hw);
+
+/* Stand-alone activation forward: y = act(x); the updater-side forward of the same layers
+ * (nnforge/cuda/*_layer_updater_cuda.cu enqueue_forward_propagation). y may alias x. */
+NNF_API int nnf_act_fwd(nnf_stream_t stream, float * y, const float * x, const nnf_act * act, int64_t n, int64_t c, int64_t hw);
+
+/* Activation backward: dx (+)= dy * act'(.), replacing enqueue_backward_data_propagation of
+ * rectified_linear (nnforge/cuda/rectified_linear_layer_updater_cuda.cu:133-167), parametric_rectified_linear
+ * (:165-213), exponential_linear (:117-143), hyperbolic_tangent (:130-160) and the cuDNN sigmoid
+ * (nnforge/cuda/activation_layer_cudnn_updater_cuda.cpp:77-117).
+ * `neurons` is the layer INPUT for ReLU and PReLU and the layer OUTPUT for ELU, TanH and Sigmoid, the
+ * dependency the plain backend declares (nnforge/plain/rectified_linear_layer_updater_plain.cpp:62-107,
+ * exponential_linear_layer_updater_plain.cpp:59-103, ...). dx may alias dy. */
+NNF_API int nnf_act_bwd(nnf_stream_t stream, float * dx, const float * dy, const float * neurons, const nnf_act * act,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
+/* PReLU slope gradient: dslope[c] += sum_{n,hw} dy * (x >= 0 ? 0 : x), replacing
+ * enqueue_backward_weights_propagation (nnforge/cuda/parametric_rectified_linear_layer_updater_cuda.cu:215-233;
+ * plain: parametric_rectified_linear_layer_updater_plain.cpp:137-190). Deterministic (fixed reduction
+ * tree, no atomics). workspace: nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) bytes. */
+NNF_API size_t nnf_prelu_bwd_weights_workspace_bytes(int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const float * dy, const float * x,
+	int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
+
+/* Add layer: y = ((0 + in[0]) + in[1] + ...) * alpha in one pass for any input count <= NNF_MAX_ADD_INPUTS
+ * (the reference launches one kernel per extra input: nnforge/cuda/add_layer_tester_cuda.cu:59-82;
+ * arithmetic: nnforge/plain/add_layer_tester_plain.cpp:53-61). `inputs` is a HOST array of device pointers.
+ * y may alias inputs[0]. */
+NNF_API int nnf_add_fwd(nnf_stream_t stream, float * y, const float * const * inputs, int input_count, float alpha, int64_t count);
+
+/* Add layer backward: dx (+)= dy*alpha (nnforge/cuda/add_layer_updater_cuda.cu:84-116); a no-op when
+ * dx == dy, alpha == 1 and not accumulating, as in the reference. */
+NNF_API int nnf_add_bwd(nnf_stream_t stream, float * dx, const float * dy, float alpha, int64_t count, int add_to_destination);
+
+/* ---------------------------------------------------------------------------------------------
+ * Channel softmax over C at every (n, pixel), replacing the cuDNN calls of
+ * softmax_layer_tester_cuda (nnforge/cuda/softmax_layer_tester_cuda.cpp:58-67) and softmax_layer_updater_cuda
+ * (nnforge/cuda/softmax_layer_updater_cuda.cpp:61-70, 100-111); arithmetic of
+ * nnforge/plain/softmax_layer_tester_plain.cpp:65-88 and softmax_layer_updater_plain.cpp:100-166.
+ * y may alias x; dx may alias dy. */
+NNF_API int nnf_softmax_fwd(nnf_stream_t stream, float * y, const float * x, int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_softmax_bwd(nnf_stream_t stream, float * dx, const float * dy, const float * y, int64_t n, int64_t c, int64_t hw,
+	int add_to_destination);
+
+/* ---------------------------------------------------------------------------------------------
+ * 2-D max subsampling (H = 1 gives 1-D). Extents and flags are in the reference's dimension order
+ * (x = width first). Output extent per dimension: (in + stride - win + (round_up ? win-1 : 0)) / stride
+ * (nnforge/max_subsampling_layer.cpp:125-133). */
+typedef struct nnf_pool
+{
+	int32_t win_w, win_h;
+	int32_t stride_w, stride_h;
+	int32_t round_up_w, round_up_h; /* clip the last window to the input instead of dropping it */
+	int32_t is_min;
+} nnf_pool;
+
+NNF_API int64_t nnf_pool_out_size(int64_t in_size, int32_t window, int32_t stride, int32_t round_up);
+
+/* Forward, replacing max_subsampling_layer_tester_cuda / max_subsampling_layer_updater_cuda forward
+ * (nnforge/cuda/max_subsampling_layer_tester_cuda.cuh:182-217, max_subsampling_layer_updater_cuda.cuh:527-820).
+ * Tie-break and argmax format are the PLAIN backend's (nnforge/plain/max_subsampling_layer_updater_plain.cpp:139-159):
+ * window scanned x-fastest, first strict maximum wins, argmax = absolute input element offset as
+ * uint32 (so n*c*h*w must be < 2^32 when argmax is requested). argmax may be NULL. */
+NNF_API int nnf_maxpool_fwd(nnf_stream_t stream, float * y, uint32_t * argmax, const float * x,
+	int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool);
+
+/* Backward as a deterministic gather: every input element sums dy of the (few) windows whose stored
+ * argmax points at it, in ascending output index, which equals the plain backend's scatter
+ * (nnforge/plain/max_subsampling_layer_updater_plain.cpp:173-231) run serially with accumulation onto a
+ * zeroed buffer. No zero-fill pass, no atomics (reference: nnforge/cuda/max_subsampling_layer_updater_cuda.cuh:822-977). */
+NNF_API int nnf_maxpool_bwd(nnf_stream_t stream, float * dx, const float * dy, const uint32_t * argmax,
+	int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool, int add_to_destination);
+
+/* ResNet block tail in one pass: z = relu(((0 + bn(x)) + residual) * 1, slope), pooled = maxpool(z).
+ * z is written because later layers and the backward pass need it. gamma == NULL skips the batch norm. */
+NNF_API int nnf_bn_add_relu_maxpool_fwd(nnf_stream_t stream, float * z, float * pooled, uint32_t * argmax,
+	const float * x, const float * residual,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	float relu_slope, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool);
+
+/* Backward of the same chain with frozen batch-norm statistics:
+ *   dz = maxpool_bwd(dpooled), ds = (z sign bit clear) ? dz : dz*slope, dresidual = ds,
+ *   dx = ds * (gamma*invsigma).   Requires relu_slope >= 0 (the gate is read from the sign of z).
+ * dresidual and/or dx may be NULL. */
+NNF_API int nnf_bn_add_relu_maxpool_bwd(nnf_stream_t stream, float * dx, float * dresidual,
+	const float * dpooled, const uint32_t * argmax, const float * z,
+	const float * gamma, const float * invsigma,
+	float relu_slope, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool);
+
+/* ---------------------------------------------------------------------------------------------
+ * Training-mode batch norm fused with the following activation chain, replacing the cuDNN calls
+ * cudnnBatchNormalizationForwardTraining / cudnnBatchNormalizationBackward of batch_norm_layer_updater_cuda
+ * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:60-107, 109-183) plus the activation updaters that follow.
+ * The work is split so that a batch-sharded multi-GPU caller can all-reduce 2*C floats between the steps:
+ *
+ *   forward : nnf_bn_train_stats      -> sums[2C] = {sum x, sum x^2} of THIS shard
+ *             (all-reduce sums over shards; skip with one GPU)
+ *             nnf_bn_train_apply_act  -> saved[2C] = {mean, invstd}, y = acts(x*mult + add)
+ *   backward: nnf_bn_train_bwd_stats  -> bsums[3C] = {sum du, sum du*xhat, sum dv*(u>=0?0:u)} of this shard,
+ *                                        and, when gsums != NULL, a copy of its first 2C floats in gsums[2C]
+ *             (all-reduce gsums in place over shards; with one GPU pass bsums itself as gsums below)
+ *             nnf_bn_train_bwd_apply  -> dx, and the per-channel gradients accumulated from bsums
+ *
+ * u = bn output, v = act[0](u), du/dv = gradient reaching u/v through the chain, xhat = (x-mean)*invstd.
+ * count_total = number of elements per channel over ALL shards (N_global * hw).
+ * saved has the layout of the reference's temporary_fixed_buffer (mean then inverse std-dev,
+ * nnforge/cuda/batch_norm_layer_updater_cuda.cu:105-106, 209-212).
+ * workspace: nnf_bn_train_workspace_bytes(n, c, hw) bytes, used by the two *_stats calls. */
+NNF_API size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw);
+
+NNF_API int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes);
+
+NNF_API int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved, const float * x,
+	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);
+
+NNF_API int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes);
+
+/* dx (+)= gamma*invstd/m * (m*du - gsums[c] - xhat*gsums[C+c]).
+ * Per-channel gradients (each may be NULL) are ACCUMULATED from the LOCAL sums, as the reference
+ * accumulates (beta_weights = 1, nnforge/cuda/batch_norm_layer_updater_cuda.cu:138-139) and leaves the
+ * cross-device sum to the weight all-reduce: grad_gamma += bsums[C+c], grad_beta += bsums[c],
+ * grad_slope += bsums[2C+c], and the running-statistics pseudo-gradients
+ * grad_mean += entry_count*(saved_mean - mean), grad_invsigma += entry_count*(saved_invstd - invsigma)
+ * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:28-44, 167-182). dx may alias dy. */
+NNF_API int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const float * gsums, const float * bsums, double count_total,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NNF_B200_H */

@@ -1,0 +1,61 @@
+"""Compiles the CUDA sources under nnforge_b200/csrc into nnforge_b200/libnnf_b200.so (sm_100a only).
+
+    python -m nnforge_b200.build
+
+-fmad=false: the kernels must round products and sums separately so that results follow nnForge's
+plain (CPU) backend bit for bit where the parity bar is bit-exactness; the kernels are HBM-bound, so
+the lost FMA contraction costs nothing measurable.
+"""
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
+LIB = os.path.join(HERE, "libnnf_b200.so")
+SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_maxpool.cu", "nnf_bn_train.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", "nvcc"):
+        if cand and (os.path.sep not in cand or os.path.exists(cand)):
+            return cand
+    return "nvcc"
+
+
+def _deps_mtime():
+    newest = 0.0
+    for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+        for name in os.listdir(root):
+            if name.endswith((".cuh", ".h")):
+                newest = max(newest, os.path.getmtime(os.path.join(root, name)))
+    return newest
+
+
+def _compile(job):
+    src, obj, hdr_mtime, verbose = job
+    if os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_mtime):
+        return
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    subprocess.check_call(cmd)
+
+
+def build(verbose=False):
+    os.makedirs(OBJ, exist_ok=True)
+    hdr = _deps_mtime()
+    sources = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+    jobs = [(os.path.join(CSRC, s), os.path.join(OBJ, s[:-3] + ".o"), hdr, verbose) for s in sources]
+    with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+        list(pool.map(_compile, jobs))
+    objs = [j[1] for j in jobs]
+    if not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
+        subprocess.check_call([_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv))

@@ -1,0 +1,242 @@
+"""ctypes binding of include/nnf_b200.h (the C ABI of libnnf_b200.so).
+
+Tensors are passed as torch CUDA tensors (or ``None``); the binding hands their ``data_ptr()`` to the
+library and enqueues on torch's current stream unless ``stream=`` is given. A non-zero status raises
+``NnfError`` carrying ``nnf_last_error_string()``. There is no fallback path: if the shared library
+has not been built (``python -m nnforge_b200.build``) the import raises.
+"""
+import ctypes as ct
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnnf_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError("libnnf_b200.so is missing: build it with `python -m nnforge_b200.build` (needs nvcc); "
+                      "this package has no CPU or PyTorch fallback")
+
+lib = ct.CDLL(LIB_PATH)
+
+ACT_NONE, ACT_RELU, ACT_PRELU, ACT_ELU, ACT_TANH, ACT_SIGMOID = range(6)
+MAX_ACTS = 2
+MAX_ADD_INPUTS = 8
+
+
+class NnfError(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__("nnf_b200 status %d: %s" % (status, text))
+        self.status = status
+
+
+class Act(ct.Structure):
+    _fields_ = [("kind", ct.c_int32), ("p0", ct.c_float), ("p1", ct.c_float), ("slope", ct.c_void_p)]
+
+
+class Pool(ct.Structure):
+    _fields_ = [("win_w", ct.c_int32), ("win_h", ct.c_int32), ("stride_w", ct.c_int32), ("stride_h", ct.c_int32),
+                ("round_up_w", ct.c_int32), ("round_up_h", ct.c_int32), ("is_min", ct.c_int32)]
+
+
+_P, _I64, _F, _I, _D, _SZ = ct.c_void_p, ct.c_int64, ct.c_float, ct.c_int, ct.c_double, ct.c_size_t
+_ACTP, _POOLP = ct.POINTER(Act), ct.POINTER(Pool)
+
+_SIGNATURES = {
+    "nnf_last_error_string": (ct.c_char_p, []),
+    "nnf_version": (_I, []),
+    "nnf_bn_infer_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64]),
+    "nnf_act_fwd": (_I, [_P, _P, _P, _ACTP, _I64, _I64, _I64]),
+    "nnf_act_bwd": (_I, [_P, _P, _P, _P, _ACTP, _I64, _I64, _I64, _I]),
+    "nnf_prelu_bwd_weights_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
+    "nnf_prelu_bwd_weights": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_add_fwd": (_I, [_P, _P, ct.POINTER(_P), _I, _F, _I64]),
+    "nnf_add_bwd": (_I, [_P, _P, _P, _F, _I64, _I]),
+    "nnf_softmax_fwd": (_I, [_P, _P, _P, _I64, _I64, _I64]),
+    "nnf_softmax_bwd": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _I]),
+    "nnf_pool_out_size": (_I64, [_I64, ct.c_int32, ct.c_int32, ct.c_int32]),
+    "nnf_maxpool_fwd": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _POOLP]),
+    "nnf_maxpool_bwd": (_I, [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _POOLP, _I]),
+    "nnf_bn_add_relu_maxpool_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _POOLP]),
+    "nnf_bn_add_relu_maxpool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _POOLP]),
+    "nnf_bn_train_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
+    "nnf_bn_train_stats": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_bn_train_apply_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _D, _F, _ACTP, _I, _I64, _I64, _I64]),
+    "nnf_bn_train_bwd_stats": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_bn_train_bwd_apply": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
+                                    _I64, _I64, _I64, _I]),
+}
+
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+EXPORTS = sorted(_SIGNATURES)
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda and t.is_contiguous(), "tensors must be contiguous CUDA tensors"
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _check(status):
+    if status != 0:
+        raise NnfError(status, lib.nnf_last_error_string().decode())
+
+
+def last_error():
+    return lib.nnf_last_error_string().decode()
+
+
+def relu(slope=0.0):
+    return Act(ACT_RELU, slope, 0.0, None)
+
+
+def prelu(slope_tensor):
+    return Act(ACT_PRELU, 0.0, 0.0, _ptr(slope_tensor))
+
+
+def elu():
+    return Act(ACT_ELU, 0.0, 0.0, None)
+
+
+def tanh(scale=1.0, steepness=1.0):
+    return Act(ACT_TANH, scale, steepness, None)
+
+
+def sigmoid():
+    return Act(ACT_SIGMOID, 0.0, 0.0, None)
+
+
+def _acts(acts):
+    acts = list(acts or [])
+    arr = (Act * max(len(acts), 1))(*acts)
+    return arr, len(acts)
+
+
+def _nchw(t):
+    n, c = t.shape[0], t.shape[1]
+    hw = 1
+    for d in t.shape[2:]:
+        hw *= d
+    return n, c, hw
+
+
+def bn_infer_act(y, x, bn=None, residual=None, add_alpha=1.0, acts=(), stream=None):
+    """bn = (gamma, beta, mean, invsigma) device tensors or None."""
+    n, c, hw = _nchw(x)
+    g, b, m, i = bn if bn is not None else (None, None, None, None)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_infer_act(_stream(stream), _ptr(y), _ptr(x), _ptr(g), _ptr(b), _ptr(m), _ptr(i), _ptr(residual), add_alpha, arr, k, n, c, hw))
+
+
+def act_fwd(y, x, act, stream=None):
+    n, c, hw = _nchw(x)
+    _check(lib.nnf_act_fwd(_stream(stream), _ptr(y), _ptr(x), ct.byref(act), n, c, hw))
+
+
+def act_bwd(dx, dy, neurons, act, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(dy)
+    _check(lib.nnf_act_bwd(_stream(stream), _ptr(dx), _ptr(dy), _ptr(neurons), ct.byref(act), n, c, hw, int(add_to_destination)))
+
+
+def prelu_bwd_weights(dslope, dy, x, workspace=None, stream=None):
+    n, c, hw = _nchw(x)
+    need = lib.nnf_prelu_bwd_weights_workspace_bytes(n, c, hw)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    _check(lib.nnf_prelu_bwd_weights(_stream(stream), _ptr(dslope), _ptr(dy), _ptr(x), n, c, hw, _ptr(workspace), workspace.numel()))
+
+
+def add_fwd(y, inputs, alpha=1.0, stream=None):
+    arr = (_P * len(inputs))(*[_ptr(t) for t in inputs])
+    _check(lib.nnf_add_fwd(_stream(stream), _ptr(y), arr, len(inputs), alpha, y.numel()))
+
+
+def add_bwd(dx, dy, alpha=1.0, add_to_destination=False, stream=None):
+    _check(lib.nnf_add_bwd(_stream(stream), _ptr(dx), _ptr(dy), alpha, dy.numel(), int(add_to_destination)))
+
+
+def softmax_fwd(y, x, stream=None):
+    n, c, hw = _nchw(x)
+    _check(lib.nnf_softmax_fwd(_stream(stream), _ptr(y), _ptr(x), n, c, hw))
+
+
+def softmax_bwd(dx, dy, y, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(y)
+    _check(lib.nnf_softmax_bwd(_stream(stream), _ptr(dx), _ptr(dy), _ptr(y), n, c, hw, int(add_to_destination)))
+
+
+def pool(win, stride, round_up=(False, False), is_min=False):
+    """win/stride/round_up are (w, h) pairs, the reference's dimension order."""
+    return Pool(win[0], win[1], stride[0], stride[1], int(round_up[0]), int(round_up[1]), int(is_min))
+
+
+def pool_out_shape(h, w, p):
+    return (int(lib.nnf_pool_out_size(h, p.win_h, p.stride_h, p.round_up_h)), int(lib.nnf_pool_out_size(w, p.win_w, p.stride_w, p.round_up_w)))
+
+
+def maxpool_fwd(y, argmax, x, p, stream=None):
+    n, c, h, w = x.shape
+    _check(lib.nnf_maxpool_fwd(_stream(stream), _ptr(y), _ptr(argmax), _ptr(x), n, c, h, w, ct.byref(p)))
+
+
+def maxpool_bwd(dx, dy, argmax, p, add_to_destination=False, stream=None):
+    n, c, h, w = dx.shape
+    _check(lib.nnf_maxpool_bwd(_stream(stream), _ptr(dx), _ptr(dy), _ptr(argmax), n, c, h, w, ct.byref(p), int(add_to_destination)))
+
+
+def bn_add_relu_maxpool_fwd(z, pooled, argmax, x, residual, bn, relu_slope, p, stream=None):
+    n, c, h, w = x.shape
+    g, b, m, i = bn if bn is not None else (None, None, None, None)
+    _check(lib.nnf_bn_add_relu_maxpool_fwd(_stream(stream), _ptr(z), _ptr(pooled), _ptr(argmax), _ptr(x), _ptr(residual), _ptr(g), _ptr(b),
+                                           _ptr(m), _ptr(i), relu_slope, n, c, h, w, ct.byref(p)))
+
+
+def bn_add_relu_maxpool_bwd(dx, dresidual, dpooled, argmax, z, gamma, invsigma, relu_slope, p, stream=None):
+    n, c, h, w = z.shape
+    _check(lib.nnf_bn_add_relu_maxpool_bwd(_stream(stream), _ptr(dx), _ptr(dresidual), _ptr(dpooled), _ptr(argmax), _ptr(z), _ptr(gamma),
+                                           _ptr(invsigma), relu_slope, n, c, h, w, ct.byref(p)))
+
+
+def bn_train_workspace_bytes(n, c, hw):
+    return int(lib.nnf_bn_train_workspace_bytes(n, c, hw))
+
+
+def bn_train_stats(sums, x, workspace, stream=None):
+    n, c, hw = _nchw(x)
+    _check(lib.nnf_bn_train_stats(_stream(stream), _ptr(sums), _ptr(x), n, c, hw, _ptr(workspace), workspace.numel() * workspace.element_size()))
+
+
+def bn_train_apply_act(y, saved, x, gamma, beta, sums, count_total, eps, acts=(), stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_apply_act(_stream(stream), _ptr(y), _ptr(saved), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(sums), float(count_total), eps,
+                                      arr, k, n, c, hw))
+
+
+def bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, workspace, gsums=None, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_bwd_stats(_stream(stream), _ptr(bsums), _ptr(gsums), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), arr, k, n, c, hw,
+                                      _ptr(workspace), workspace.numel() * workspace.element_size()))
+
+
+def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total, acts=(), grad_gamma=None, grad_beta=None, grad_mean=None,
+                       grad_invsigma=None, grad_slope=None, mean=None, invsigma=None, entry_count=0.0, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
+                                      float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
+                                      _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))

@@ -1,0 +1,556 @@
+// Training-mode batch norm fused with the activation chain that follows it.
+//
+// Forward : stats kernel (read x once) -> [2C-float all-reduce between GPUs] -> apply kernel (the
+//           streaming kernel of nnf_elementwise.cu with mean/invstd derived from the sums in its
+//           prologue; read x, write y).
+// Backward: bwd-stats kernel (read x, dy; recompute the chain; per-channel sums) -> [2C-float
+//           all-reduce] -> bwd-apply kernel (read x, dy; write dx).
+// HBM-bound. Algorithmic bytes per element: forward 8 (x in, y out), backward 12 (x, dy in, dx out);
+// this two-kernel form moves 12 and 20 because x (and dy) are read twice.
+//
+// Per-channel reductions: each CTA owns (channel, slice of entries); threads accumulate fp32
+// partials over ~100 elements each, the cross-thread and cross-CTA combination is done in double in
+// a fixed order (warp shuffles, shared memory, then a second tiny kernel over the per-CTA partials in
+// the workspace), so results are deterministic and independent of the grid.
+#include "nnf_common.cuh"
+
+namespace nnf
+{
+	namespace
+	{
+		constexpr int kThreads = 256;
+		constexpr int kMaxSplit = 64;   // CTAs per channel (upper bound, sizes the workspace)
+		constexpr int kSums = 3;        // partial sums per channel and CTA
+
+		__device__ __forceinline__ double warp_sum_d(double v)
+		{
+			#pragma unroll
+			for (int o = 16; o > 0; o >>= 1)
+				v += __shfl_xor_sync(0xffffffffu, v, o);
+			return v;
+		}
+
+		// Block-wide sum of up to kSums doubles; result valid in thread 0.
+		template <int K>
+		__device__ __forceinline__ void block_sum_d(double (&v)[K], double * s_red)
+		{
+			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+			#pragma unroll
+			for (int k = 0; k < K; ++k)
+				v[k] = warp_sum_d(v[k]);
+			if (lane == 0)
+			{
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					s_red[w * K + k] = v[k];
+			}
+			__syncthreads();
+			if (threadIdx.x == 0)
+			{
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+				{
+					double t = 0.0;
+					for (int i = 0; i < kThreads / 32; ++i)
+						t += s_red[i * K + k];
+					v[k] = t;
+				}
+			}
+		}
+
+		struct chan_geom
+		{
+			uint32_t n, c, hw;
+			uint32_t split;          // CTAs per channel
+			uint32_t entries_per_cta;
+			fastdiv d_vpp;           // vectors (or elements) per plane
+			int vec;                 // 128-bit loads possible (hw % 4 == 0 and aligned base)
+		};
+
+		// workspace layout: double partial[c][split][kSums]
+		__global__ void __launch_bounds__(kThreads) bn_stats_kernel(double * partial, const float * x, chan_geom g)
+		{
+			__shared__ double s_red[(kThreads / 32) * 2];
+			const uint32_t ch = blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x - ch * g.split;
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			float s = 0.0F, q = 0.0F;
+			if (e0 < e1)
+			{
+				const uint32_t per_plane = g.vec ? (g.hw >> 2) : g.hw;
+				const uint32_t total = (e1 - e0) * per_plane;
+				const size_t entry_stride = size_t(g.c) * g.hw;
+				const float * base = x + (size_t(e0) * g.c + ch) * g.hw;
+				for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+				{
+					const uint32_t lp = g.d_vpp.div(i);
+					const uint32_t v = i - lp * per_plane;
+					const float * plane = base + lp * entry_stride;
+					if (g.vec)
+					{
+						const float4 a = __ldg(reinterpret_cast<const float4 *>(plane) + v);
+						s += (a.x + a.y) + (a.z + a.w);
+						q += (a.x * a.x + a.y * a.y) + (a.z * a.z + a.w * a.w);
+					}
+					else
+					{
+						const float a = __ldg(plane + v);
+						s += a;
+						q += a * a;
+					}
+				}
+			}
+			double acc[2] = {double(s), double(q)};
+			block_sum_d<2>(acc, s_red);
+			if (threadIdx.x == 0)
+			{
+				double * out = partial + (size_t(ch) * g.split + sp) * kSums;
+				out[0] = acc[0];
+				out[1] = acc[1];
+			}
+		}
+
+		// sums[k*c + ch] (+)= float(sum over splits of partial[ch][split][k]), k < count
+		// copy (may be null) receives the first copy_count sums too: the buffer a caller all-reduces
+		__global__ void bn_reduce_partials_kernel(float * sums, const double * partial, uint32_t c, uint32_t split, int count, int accumulate,
+			float * copy = nullptr, int copy_count = 0)
+		{
+			const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
+			if (ch >= c)
+				return;
+			for (int k = 0; k < count; ++k)
+			{
+				double t = 0.0;
+				for (uint32_t sp = 0; sp < split; ++sp)
+					t += partial[(size_t(ch) * split + sp) * kSums + k];
+				float * out = sums + size_t(k) * c + ch;
+				*out = accumulate ? *out + float(t) : float(t);
+				if (copy && k < copy_count)
+					copy[size_t(k) * c + ch] = float(t);
+			}
+		}
+
+		// PReLU slope gradient partials: sum dy * (x >= 0 ? 0 : x) per (channel, slice of entries)
+		__global__ void __launch_bounds__(kThreads) prelu_dslope_kernel(double * partial, const float * dy, const float * x, chan_geom g)
+		{
+			__shared__ double s_red[kThreads / 32];
+			const uint32_t ch = blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x - ch * g.split;
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			float s = 0.0F;
+			if (e0 < e1)
+			{
+				const uint32_t per_plane = g.vec ? (g.hw >> 2) : g.hw;
+				const uint32_t total = (e1 - e0) * per_plane;
+				const size_t entry_stride = size_t(g.c) * g.hw;
+				const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
+				for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+				{
+					const uint32_t lp = g.d_vpp.div(i);
+					const uint32_t v = i - lp * per_plane;
+					const size_t off = off0 + lp * entry_stride;
+					if (g.vec)
+					{
+						const float4 a = ld_stream(reinterpret_cast<const float4 *>(x + off) + v);
+						const float4 d = ld_stream(reinterpret_cast<const float4 *>(dy + off) + v);
+						s += d.x * (a.x >= 0.0F ? 0.0F : a.x);
+						s += d.y * (a.y >= 0.0F ? 0.0F : a.y);
+						s += d.z * (a.z >= 0.0F ? 0.0F : a.z);
+						s += d.w * (a.w >= 0.0F ? 0.0F : a.w);
+					}
+					else
+					{
+						const float a = x[off + v];
+						s += dy[off + v] * (a >= 0.0F ? 0.0F : a);
+					}
+				}
+			}
+			double acc[1] = {double(s)};
+			block_sum_d<1>(acc, s_red);
+			if (threadIdx.x == 0)
+				partial[(size_t(ch) * g.split + sp) * kSums] = acc[0];
+		}
+
+		struct bwd_params
+		{
+			const float * dy;
+			const float * x;
+			const float * gamma;
+			const float * beta;
+			const float * saved;   // {mean, invstd}
+			act_chain chain;
+			// bwd-apply only
+			float * dx;
+			const float * gsums;   // global {sum du, sum du*xhat}
+			const float * bsums;   // local  {sum du, sum du*xhat, sum dslope}
+			double count_total;
+			float * grad_gamma, * grad_beta, * grad_mean, * grad_invsigma, * grad_slope;
+			const float * mean, * invsigma;
+			float entry_count;
+			int add;
+		};
+
+		// Recomputes u = x*mult + add and the activation chain, then carries dy back to du.
+		// dslope_term receives d(out of PReLU) * (in >= 0 ? 0 : in) for the PReLU in the chain (else 0).
+		__device__ __forceinline__ float chain_backward(const act_chain& ch, float u, float dy, float slope, float& dslope_term)
+		{
+			float t[NNF_MAX_ACTS + 1];
+			t[0] = u;
+			#pragma unroll
+			for (int i = 0; i < NNF_MAX_ACTS; ++i)
+				t[i + 1] = (i < ch.n) ? act_fwd_dyn(ch.a[i].kind, t[i], ch.a[i].p0, ch.a[i].p1, slope) : t[i];
+			float g = dy;
+			dslope_term = 0.0F;
+			#pragma unroll
+			for (int i = NNF_MAX_ACTS - 1; i >= 0; --i)
+			{
+				if (i < ch.n)
+				{
+					switch (ch.a[i].kind)
+					{
+					case NNF_ACT_RELU: g = act_bwd<NNF_ACT_RELU>(g, t[i], ch.a[i].p0, 0.0F, 0.0F); break;
+					case NNF_ACT_PRELU:
+						// parametric_rectified_linear_layer_updater_plain.cpp:177-180
+						dslope_term = __fmul_rn(g, (t[i] >= 0.0F ? 0.0F : t[i]));
+						g = act_bwd<NNF_ACT_PRELU>(g, t[i], 0.0F, 0.0F, slope);
+						break;
+					case NNF_ACT_ELU: g = act_bwd<NNF_ACT_ELU>(g, t[i + 1], 0.0F, 0.0F, 0.0F); break;
+					case NNF_ACT_TANH: g = act_bwd<NNF_ACT_TANH>(g, t[i + 1], ch.a[i].p0b, ch.a[i].p1b, 0.0F); break;
+					case NNF_ACT_SIGMOID: g = act_bwd<NNF_ACT_SIGMOID>(g, t[i + 1], 0.0F, 0.0F, 0.0F); break;
+					default: break;
+					}
+				}
+			}
+			return g;
+		}
+
+		__device__ __forceinline__ float chain_slope(const act_chain& ch, uint32_t channel)
+		{
+			float a = 0.0F;
+			#pragma unroll
+			for (int i = 0; i < NNF_MAX_ACTS; ++i)
+				if (i < ch.n && ch.a[i].kind == NNF_ACT_PRELU)
+					a = __ldg(ch.a[i].slope + channel);
+			return a;
+		}
+
+		__global__ void __launch_bounds__(kThreads) bn_bwd_stats_kernel(double * partial, const bwd_params p, chan_geom g)
+		{
+			__shared__ double s_red[(kThreads / 32) * 3];
+			const uint32_t ch = blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x - ch * g.split;
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + g.c + ch);
+			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			const float slope = chain_slope(p.chain, ch);
+			float sb = 0.0F, sg = 0.0F, ss = 0.0F;
+			auto element = [&](float x, float dy)
+			{
+				const float u = __fadd_rn(__fmul_rn(x, mult), add);
+				float term;
+				const float du = chain_backward(p.chain, u, dy, slope, term);
+				const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
+				sb += du;
+				sg += du * xhat;
+				ss += term;
+			};
+			if (e0 < e1)
+			{
+				const uint32_t per_plane = g.vec ? (g.hw >> 2) : g.hw;
+				const uint32_t total = (e1 - e0) * per_plane;
+				const size_t entry_stride = size_t(g.c) * g.hw;
+				const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
+				for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+				{
+					const uint32_t lp = g.d_vpp.div(i);
+					const uint32_t v = i - lp * per_plane;
+					const size_t off = off0 + lp * entry_stride;
+					if (g.vec)
+					{
+						const float4 a = __ldg(reinterpret_cast<const float4 *>(p.x + off) + v);
+						const float4 d = __ldg(reinterpret_cast<const float4 *>(p.dy + off) + v);
+						element(a.x, d.x); element(a.y, d.y); element(a.z, d.z); element(a.w, d.w);
+					}
+					else
+						element(__ldg(p.x + off + v), __ldg(p.dy + off + v));
+				}
+			}
+			double acc[3] = {double(sb), double(sg), double(ss)};
+			block_sum_d<3>(acc, s_red);
+			if (threadIdx.x == 0)
+			{
+				double * out = partial + (size_t(ch) * g.split + sp) * kSums;
+				out[0] = acc[0];
+				out[1] = acc[1];
+				out[2] = acc[2];
+			}
+		}
+
+		// dx (+)= mult * (du - dbeta/m - xhat*dgamma/m); one CTA per (channel, slice of entries).
+		__global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const bwd_params p, chan_geom g)
+		{
+			const uint32_t ch = blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x - ch * g.split;
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + g.c + ch);
+			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			const float slope = chain_slope(p.chain, ch);
+			const float c2 = float(double(__ldg(p.gsums + ch)) / p.count_total);
+			const float c3 = float(double(__ldg(p.gsums + g.c + ch)) / p.count_total);
+
+			if (sp == 0 && threadIdx.x == 0)
+			{
+				// per-channel gradients accumulate the LOCAL sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+				if (p.grad_beta) p.grad_beta[ch] += p.bsums[ch];
+				if (p.grad_gamma) p.grad_gamma[ch] += p.bsums[g.c + ch];
+				if (p.grad_slope) p.grad_slope[ch] += p.bsums[2 * g.c + ch];
+				if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+				if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+			}
+
+			auto element = [&](float x, float dy, float old) -> float
+			{
+				const float u = __fadd_rn(__fmul_rn(x, mult), add);
+				float term;
+				const float du = chain_backward(p.chain, u, dy, slope, term);
+				const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
+				const float r = mult * ((du - c2) - xhat * c3);
+				return p.add ? old + r : r;
+			};
+			if (e0 >= e1)
+				return;
+			const uint32_t per_plane = g.vec ? (g.hw >> 2) : g.hw;
+			const uint32_t total = (e1 - e0) * per_plane;
+			const size_t entry_stride = size_t(g.c) * g.hw;
+			const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
+			for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+			{
+				const uint32_t lp = g.d_vpp.div(i);
+				const uint32_t v = i - lp * per_plane;
+				const size_t off = off0 + lp * entry_stride;
+				if (g.vec)
+				{
+					const float4 a = ld_stream(reinterpret_cast<const float4 *>(p.x + off) + v);
+					const float4 d = ld_stream(reinterpret_cast<const float4 *>(p.dy + off) + v);
+					float4 o = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (p.add)
+						o = ld_stream(reinterpret_cast<const float4 *>(p.dx + off) + v);
+					o = make_float4(element(a.x, d.x, o.x), element(a.y, d.y, o.y), element(a.z, d.z, o.z), element(a.w, d.w, o.w));
+					st_stream(reinterpret_cast<float4 *>(p.dx + off) + v, o);
+				}
+				else
+				{
+					const float old = p.add ? p.dx[off + v] : 0.0F;
+					p.dx[off + v] = element(p.x[off + v], p.dy[off + v], old);
+				}
+			}
+		}
+
+		int make_chan_geom(chan_geom& g, const char * who, int64_t n, int64_t c, int64_t hw, bool vec_ok)
+		{
+			if (n > 0x7fffffff || c > 0x7fffffff || hw > 0x7fffffff || n * hw > kMaxElemsPerLaunch)
+				return set_error(NNF_ERR_UNSUPPORTED, "%s: n*hw must stay below 2^31 per channel", who);
+			g.n = (uint32_t)n; g.c = (uint32_t)c; g.hw = (uint32_t)hw;
+			g.vec = (vec_ok && (hw % 4 == 0)) ? 1 : 0;
+			// enough CTAs to fill the machine several times over, but at least ~8K elements per CTA
+			int64_t split = div_up(int64_t(kSmCount) * 8, c);
+			const int64_t max_by_work = (n * hw) / 8192 > 0 ? (n * hw) / 8192 : 1;
+			if (split > max_by_work) split = max_by_work;
+			if (split > n) split = n;
+			if (split > kMaxSplit) split = kMaxSplit;
+			if (split < 1) split = 1;
+			g.entries_per_cta = (uint32_t)div_up(n, split);
+			g.split = (uint32_t)div_up(n, g.entries_per_cta);
+			g.d_vpp = fastdiv(g.vec ? g.hw / 4 : g.hw);
+			return NNF_OK;
+		}
+
+		int check_train_args(const char * who, int64_t n, int64_t c, int64_t hw)
+		{
+			if (n <= 0 || c <= 0 || hw <= 0)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: bad extents n=%lld c=%lld hw=%lld (training batch norm needs at least one entry)", who, (long long)n, (long long)c, (long long)hw);
+			return NNF_OK;
+		}
+	}
+}
+
+using namespace nnf;
+
+extern "C" size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw)
+{
+	(void)n; (void)hw;
+	if (c <= 0)
+		return 0;
+	return size_t(c) * kMaxSplit * kSums * sizeof(double);
+}
+
+extern "C" int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes)
+{
+	int st = check_train_args("nnf_bn_train_stats", n, c, hw);
+	if (st != NNF_OK)
+		return st;
+	if (!sums || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_stats: null pointer");
+	if (!workspace || workspace_bytes < nnf_bn_train_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
+		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_stats: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
+	chan_geom g;
+	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x));
+	if (st != NNF_OK)
+		return st;
+	cudaStream_t s = (cudaStream_t)stream;
+	bn_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), x, g);
+	st = check_launch("bn_stats_kernel");
+	if (st != NNF_OK)
+		return st;
+	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(sums, static_cast<const double *>(workspace), g.c, g.split, 2, 0);
+	return check_launch("bn_reduce_partials_kernel");
+}
+
+extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved, const float * x,
+	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw)
+{
+	int st = check_train_args("nnf_bn_train_apply_act", n, c, hw);
+	if (st != NNF_OK)
+		return st;
+	if (!y || !x || !gamma || !beta || !sums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_apply_act: null pointer");
+	if (!(count_total >= 1.0))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_apply_act: count_total = %g", count_total);
+	act_chain chain;
+	st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	bn_source bn = {};
+	bn.gamma = gamma; bn.beta = beta; bn.sums = sums; bn.saved = saved; bn.count_total = count_total; bn.eps = eps;
+	return run_elementwise((cudaStream_t)stream, y, x, nullptr, 1.0F, bn, chain, n, c, hw);
+}
+
+namespace
+{
+	int fill_bwd(bwd_params& p, const char * who, const float * dy, const float * x, const float * gamma, const float * beta, const float * saved,
+		const nnf_act * acts, int n_acts)
+	{
+		if (!dy || !x || !gamma || !beta || !saved)
+			return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+		int st = make_chain(p.chain, acts, n_acts, true);
+		if (st != NNF_OK)
+			return st;
+		int prelus = 0;
+		for (int i = 0; i < p.chain.n; ++i)
+		{
+			prelus += p.chain.a[i].kind == NNF_ACT_PRELU;
+			if (p.chain.a[i].kind == NNF_ACT_TANH)
+			{
+				// backward constants (hyperbolic_tangent_layer_updater_plain.cpp:87-88); p1 holds steepness*2
+				const float steepness = acts[i].p1;
+				p.chain.a[i].p0b = 1.0F / acts[i].p0;
+				p.chain.a[i].p1b = steepness * acts[i].p0;
+			}
+		}
+		if (prelus > 1)
+			return set_error(NNF_ERR_UNSUPPORTED, "%s: at most one PReLU per fused chain", who);
+		p.dy = dy; p.x = x; p.gamma = gamma; p.beta = beta; p.saved = saved;
+		return NNF_OK;
+	}
+}
+
+extern "C" int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes)
+{
+	int st = check_train_args("nnf_bn_train_bwd_stats", n, c, hw);
+	if (st != NNF_OK)
+		return st;
+	if (!bsums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_stats: null pointer");
+	if (!workspace || workspace_bytes < nnf_bn_train_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
+		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_bwd_stats: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
+	bwd_params p = {};
+	st = fill_bwd(p, "nnf_bn_train_bwd_stats", dy, x, gamma, beta, saved, acts, n_acts);
+	if (st != NNF_OK)
+		return st;
+	chan_geom g;
+	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy));
+	if (st != NNF_OK)
+		return st;
+	cudaStream_t s = (cudaStream_t)stream;
+	bn_bwd_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g);
+	st = check_launch("bn_bwd_stats_kernel");
+	if (st != NNF_OK)
+		return st;
+	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(bsums, static_cast<const double *>(workspace), g.c, g.split, 3, 0, gsums, 2);
+	return check_launch("bn_reduce_partials_kernel");
+}
+
+extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const float * gsums, const float * bsums, double count_total,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination)
+{
+	int st = check_train_args("nnf_bn_train_bwd_apply", n, c, hw);
+	if (st != NNF_OK)
+		return st;
+	if (!dx || !gsums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: null pointer");
+	if ((grad_gamma || grad_beta || grad_slope) && !bsums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: per-channel gradients requested without the local sums");
+	if ((grad_mean && !mean) || (grad_invsigma && !invsigma))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: running-statistics gradients requested without the running statistics");
+	if (!(count_total >= 1.0))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: count_total = %g", count_total);
+	bwd_params p = {};
+	st = fill_bwd(p, "nnf_bn_train_bwd_apply", dy, x, gamma, beta, saved, acts, n_acts);
+	if (st != NNF_OK)
+		return st;
+	p.dx = dx; p.gsums = gsums; p.bsums = bsums; p.count_total = count_total;
+	p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
+	p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
+	p.add = add_to_destination ? 1 : 0;
+	chan_geom g;
+	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx));
+	if (st != NNF_OK)
+		return st;
+	bn_bwd_apply_kernel<<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g);
+	return check_launch("bn_bwd_apply_kernel");
+}
+
+extern "C" size_t nnf_prelu_bwd_weights_workspace_bytes(int64_t n, int64_t c, int64_t hw)
+{
+	return nnf_bn_train_workspace_bytes(n, c, hw);
+}
+
+extern "C" int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const float * dy, const float * x,
+	int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
+{
+	if (n < 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_prelu_bwd_weights: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (n == 0)
+		return NNF_OK;
+	if (!dslope || !dy || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_prelu_bwd_weights: null pointer");
+	if (!workspace || workspace_bytes < nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
+		return set_error(NNF_ERR_WORKSPACE, "nnf_prelu_bwd_weights: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_prelu_bwd_weights_workspace_bytes(n, c, hw), workspace_bytes);
+	chan_geom g;
+	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy));
+	if (st != NNF_OK)
+		return st;
+	cudaStream_t s = (cudaStream_t)stream;
+	prelu_dslope_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), dy, x, g);
+	st = check_launch("prelu_dslope_kernel");
+	if (st != NNF_OK)
+		return st;
+	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(dslope, static_cast<const double *>(workspace), g.c, g.split, 1, 1);
+	return check_launch("bn_reduce_partials_kernel");
+}

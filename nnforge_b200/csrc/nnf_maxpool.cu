@@ -1,0 +1,611 @@
+// 2-D max subsampling forward/backward, stand-alone and fused behind batch norm -> residual add ->
+// ReLU (the tail of a ResNet block). HBM-bound.
+//
+// Data movement: a CTA owns a group of whole consecutive (n, c) planes, which are contiguous in the
+// planar layout. Forward: the group is read once with coalesced 128-bit loads, the fused
+// per-element result z is written straight back (it is needed by later layers and by backward) and
+// also kept in shared memory; the overlapping windows are then evaluated from shared memory and the
+// pooled values + argmax are written with coalesced stores. Every HBM byte is touched once:
+//   forward  bytes per input element = 4*(inputs) + 4 (z, fused only) + 8*rho   (rho = out/in pixels)
+// Backward is a gather: the group's pooled gradients and argmax are staged in shared memory and
+// every input element sums the few windows that cover it and whose argmax points at it, in ascending
+// output index - the order in which nnForge's plain backend scatters them serially
+// (nnforge/plain/max_subsampling_layer_updater_plain.cpp:201-229) - so the result is deterministic and
+// bit-identical to that order, with no zero-fill pass and no atomics.
+//
+// Tie-break and argmax format are the plain backend's: window scanned x-fastest, the first element
+// seeds, a later one wins only on a strict compare; argmax = absolute input element offset (uint32)
+// (nnforge/plain/max_subsampling_layer_updater_plain.cpp:139-159). round_up clips the last window.
+// Planes too large for shared memory fall back to direct global-memory kernels.
+#include "nnf_common.cuh"
+
+namespace nnf
+{
+	namespace
+	{
+		constexpr int kThreads = 256;
+		constexpr int64_t kGroupFloats = 8192;       // target staged floats per CTA iteration (32 KB)
+		constexpr size_t kMaxDynSmem = 200 * 1024;
+
+		struct pool_geom
+		{
+			uint32_t c, h, w, hw, oh, ow, ohw;
+			int win_w, win_h, sw, sh;
+			int is_min;
+			fastdiv d_w, d_hw, d_ow, d_ohw, d_sw, d_sh, d_c;
+		};
+
+		struct pool_fwd_params
+		{
+			pool_geom g;
+			float * z;             // fused only: per-element result written back
+			float * pooled;
+			uint32_t * argmax;     // may be null
+			const float * x;
+			const float * res;     // fused only
+			const float * gamma;   // null -> no batch norm
+			const float * beta;
+			const float * mean;
+			const float * invsigma;
+			float slope;
+			int64_t planes;
+			int group;             // planes per CTA iteration
+			int vec_ok;
+		};
+
+		__device__ __forceinline__ float fused_element(const pool_fwd_params& p, float x, float r, uint32_t channel)
+		{
+			float t = x;
+			if (p.gamma)
+			{
+				const float mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+				const float add = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(mult, __ldg(p.mean + channel)));
+				t = __fadd_rn(__fmul_rn(x, mult), add);
+			}
+			if (p.res)
+				t = __fadd_rn(__fadd_rn(0.0F, t), r); // add layer, alpha = 1: (0 + bn) + residual
+			return t >= 0.0F ? t : __fmul_rn(t, p.slope);
+		}
+
+		// Scans one window of plane `src` (row pitch g.w). Returns the winner and its offset within the plane.
+		__device__ __forceinline__ void scan_window(const pool_geom& g, const float * src, uint32_t oy, uint32_t ox, float& best, uint32_t& best_off)
+		{
+			const uint32_t iy0 = oy * g.sh, ix0 = ox * g.sw;
+			best = g.is_min ? 1.0e37F : -1.0e37F;
+			best_off = iy0 * g.w + ix0;
+			bool first = true;
+			for (int ky = 0; ky < g.win_h; ++ky)
+			{
+				const uint32_t iy = iy0 + ky;
+				if (iy >= g.h)
+					break;
+				for (int kx = 0; kx < g.win_w; ++kx)
+				{
+					const uint32_t ix = ix0 + kx;
+					if (ix >= g.w)
+						break;
+					const float v = src[iy * g.w + ix];
+					const bool better = g.is_min ? (v < best) : (v > best);
+					if (first || better)
+					{
+						best = v;
+						best_off = iy * g.w + ix;
+						first = false;
+					}
+				}
+			}
+		}
+
+		template <bool FUSED>
+		__global__ void __launch_bounds__(kThreads) pool_fwd_staged_kernel(const pool_fwd_params p)
+		{
+			extern __shared__ float s_z[];
+			const pool_geom& g = p.g;
+			const int64_t ngroups = (p.planes + p.group - 1) / p.group;
+			for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
+			{
+				const int64_t plane0 = grp * p.group;
+				const uint32_t np = (uint32_t)((p.planes - plane0 < p.group) ? (p.planes - plane0) : p.group);
+				const uint32_t count = np * g.hw;
+				const int64_t base = plane0 * g.hw;
+				const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
+				const float * x = p.x + base;
+
+				// phase 1: stream the group in, apply the fused per-element chain, keep it in shared memory
+				if (p.vec_ok)
+				{
+					const uint32_t nvec = count >> 2;
+					const float4 * x4 = reinterpret_cast<const float4 *>(x);
+					const float4 * r4 = FUSED && p.res ? reinterpret_cast<const float4 *>(p.res + base) : nullptr;
+					float4 * z4 = FUSED ? reinterpret_cast<float4 *>(p.z + base) : nullptr;
+					float4 * s4 = reinterpret_cast<float4 *>(s_z);
+					for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
+					{
+						float4 a = ld_stream(x4 + v);
+						if (FUSED)
+						{
+							float4 r = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (r4)
+								r = ld_stream(r4 + v);
+							float in[4] = {a.x, a.y, a.z, a.w};
+							const float rr[4] = {r.x, r.y, r.z, r.w};
+							#pragma unroll
+							for (int k = 0; k < 4; ++k)
+							{
+								uint32_t channel = ch0 + g.d_hw.div((v << 2) + k);
+								channel -= g.d_c.div(channel) * g.c;
+								in[k] = fused_element(p, in[k], rr[k], channel);
+							}
+							a = make_float4(in[0], in[1], in[2], in[3]);
+							st_stream(z4 + v, a);
+						}
+						s4[v] = a;
+					}
+					for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kThreads)
+					{
+						float a = x[e];
+						if (FUSED)
+						{
+							uint32_t channel = ch0 + g.d_hw.div(e);
+							channel -= g.d_c.div(channel) * g.c;
+							a = fused_element(p, a, p.res ? p.res[base + e] : 0.0F, channel);
+							p.z[base + e] = a;
+						}
+						s_z[e] = a;
+					}
+				}
+				else
+				{
+					for (uint32_t e = threadIdx.x; e < count; e += kThreads)
+					{
+						float a = ld_stream(x + e);
+						if (FUSED)
+						{
+							uint32_t channel = ch0 + g.d_hw.div(e);
+							channel -= g.d_c.div(channel) * g.c;
+							a = fused_element(p, a, p.res ? ld_stream(p.res + base + e) : 0.0F, channel);
+							st_stream(p.z + base + e, a);
+						}
+						s_z[e] = a;
+					}
+				}
+				__syncthreads();
+
+				// phase 2: windows from shared memory
+				const uint32_t nout = np * g.ohw;
+				const int64_t obase = plane0 * g.ohw;
+				for (uint32_t o = threadIdx.x; o < nout; o += kThreads)
+				{
+					const uint32_t lp = g.d_ohw.div(o);
+					const uint32_t rem = o - lp * g.ohw;
+					const uint32_t oy = g.d_ow.div(rem);
+					const uint32_t ox = rem - oy * g.ow;
+					float best;
+					uint32_t off;
+					scan_window(g, s_z + lp * g.hw, oy, ox, best, off);
+					st_stream(p.pooled + obase + o, best);
+					if (p.argmax)
+						p.argmax[obase + o] = (uint32_t)(base + int64_t(lp) * g.hw + off);
+				}
+				__syncthreads();
+			}
+		}
+
+		// Fallback for planes that do not fit shared memory: one thread per output element, from global.
+		__global__ void __launch_bounds__(kThreads) pool_fwd_direct_kernel(float * pooled, uint32_t * argmax, const float * x, pool_geom g, int64_t planes)
+		{
+			const int64_t total = planes * g.ohw;
+			const int64_t stride = int64_t(gridDim.x) * kThreads;
+			for (int64_t o = int64_t(blockIdx.x) * kThreads + threadIdx.x; o < total; o += stride)
+			{
+				const int64_t plane = o / g.ohw;
+				const uint32_t rem = (uint32_t)(o - plane * g.ohw);
+				const uint32_t oy = g.d_ow.div(rem);
+				const uint32_t ox = rem - oy * g.ow;
+				float best;
+				uint32_t off;
+				scan_window(g, x + plane * g.hw, oy, ox, best, off);
+				pooled[o] = best;
+				if (argmax)
+					argmax[o] = (uint32_t)(plane * g.hw + off);
+			}
+		}
+
+		struct pool_bwd_params
+		{
+			pool_geom g;
+			float * dx;            // may be null (fused)
+			float * dres;          // fused only, may be null
+			const float * dpooled;
+			const uint32_t * argmax;
+			const float * z;       // fused only
+			const float * gamma;   // fused: null -> dx = ds
+			const float * invsigma;
+			float slope;
+			int64_t planes;
+			int group;
+			int vec_ok;
+			int add;               // stand-alone only
+		};
+
+		// Gradient reaching input element (iy, ix) of a plane whose pooled gradients / argmax start at
+		// dyp / idx; abs_off is the element's absolute offset as the argmax stores it.
+		__device__ __forceinline__ float gather_element(const pool_geom& g, const float * dyp, const uint32_t * idx, uint32_t iy, uint32_t ix, uint32_t abs_off, float seed)
+		{
+			const uint32_t oy_lo = iy < (uint32_t)g.win_h ? 0u : g.d_sh.div(iy - g.win_h) + 1u;
+			uint32_t oy_hi = g.d_sh.div(iy);
+			if (oy_hi > g.oh - 1)
+				oy_hi = g.oh - 1;
+			const uint32_t ox_lo = ix < (uint32_t)g.win_w ? 0u : g.d_sw.div(ix - g.win_w) + 1u;
+			uint32_t ox_hi = g.d_sw.div(ix);
+			if (ox_hi > g.ow - 1)
+				ox_hi = g.ow - 1;
+			float sum = seed;
+			for (uint32_t oy = oy_lo; oy <= oy_hi; ++oy)
+				for (uint32_t ox = ox_lo; ox <= ox_hi; ++ox)
+				{
+					const uint32_t o = oy * g.ow + ox;
+					if (idx[o] == abs_off)
+						sum = __fadd_rn(sum, dyp[o]);
+				}
+			return sum;
+		}
+
+		template <bool FUSED>
+		__global__ void __launch_bounds__(kThreads) pool_bwd_staged_kernel(const pool_bwd_params p)
+		{
+			extern __shared__ float s_raw[];
+			const pool_geom& g = p.g;
+			const int64_t ngroups = (p.planes + p.group - 1) / p.group;
+			float * s_dy = s_raw;
+			uint32_t * s_idx = reinterpret_cast<uint32_t *>(s_raw + size_t(p.group) * g.ohw);
+			for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
+			{
+				const int64_t plane0 = grp * p.group;
+				const uint32_t np = (uint32_t)((p.planes - plane0 < p.group) ? (p.planes - plane0) : p.group);
+				const uint32_t nout = np * g.ohw;
+				const int64_t obase = plane0 * g.ohw;
+				for (uint32_t o = threadIdx.x; o < nout; o += kThreads)
+				{
+					s_dy[o] = ld_stream(p.dpooled + obase + o);
+					s_idx[o] = __ldcs(p.argmax + obase + o);
+				}
+				__syncthreads();
+
+				const uint32_t count = np * g.hw;
+				const int64_t base = plane0 * g.hw;
+				const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
+				auto element = [&](uint32_t e, float zval, float seed, float& out_dx, float& out_dres)
+				{
+					const uint32_t lp = g.d_hw.div(e);
+					const uint32_t rem = e - lp * g.hw;
+					const uint32_t iy = g.d_w.div(rem);
+					const uint32_t ix = rem - iy * g.w;
+					const float dz = gather_element(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix, (uint32_t)(base + e), seed);
+					if (FUSED)
+					{
+						// ReLU gate from the sign bit of z (negative pre-activations were multiplied by a
+						// slope >= 0, so their sign bit is set, -0.0 included); add layer backward with
+						// alpha 1 is the identity; frozen batch norm scales by gamma*invsigma.
+						const float ds = (__float_as_uint(zval) >> 31) ? __fmul_rn(dz, p.slope) : dz;
+						out_dres = ds;
+						if (p.gamma)
+						{
+							uint32_t channel = ch0 + lp;
+							channel -= g.d_c.div(channel) * g.c;
+							out_dx = __fmul_rn(ds, __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel)));
+						}
+						else
+							out_dx = ds;
+					}
+					else
+						out_dx = dz;
+				};
+
+				if (p.vec_ok)
+				{
+					const uint32_t nvec = count >> 2;
+					for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
+					{
+						float zv[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+						float seed[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+						if (FUSED)
+						{
+							const float4 z4 = ld_stream(reinterpret_cast<const float4 *>(p.z + base) + v);
+							zv[0] = z4.x; zv[1] = z4.y; zv[2] = z4.z; zv[3] = z4.w;
+						}
+						else if (p.add)
+						{
+							const float4 d4 = ld_stream(reinterpret_cast<const float4 *>(p.dx + base) + v);
+							seed[0] = d4.x; seed[1] = d4.y; seed[2] = d4.z; seed[3] = d4.w;
+						}
+						float odx[4], ores[4];
+						#pragma unroll
+						for (int k = 0; k < 4; ++k)
+							element((v << 2) + k, zv[k], seed[k], odx[k], ores[k]);
+						if (p.dx)
+							st_stream(reinterpret_cast<float4 *>(p.dx + base) + v, make_float4(odx[0], odx[1], odx[2], odx[3]));
+						if (FUSED && p.dres)
+							st_stream(reinterpret_cast<float4 *>(p.dres + base) + v, make_float4(ores[0], ores[1], ores[2], ores[3]));
+					}
+					for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kThreads)
+					{
+						float odx, ores;
+						element(e, FUSED ? p.z[base + e] : 0.0F, (!FUSED && p.add) ? p.dx[base + e] : 0.0F, odx, ores);
+						if (p.dx)
+							p.dx[base + e] = odx;
+						if (FUSED && p.dres)
+							p.dres[base + e] = ores;
+					}
+				}
+				else
+				{
+					for (uint32_t e = threadIdx.x; e < count; e += kThreads)
+					{
+						float odx, ores;
+						element(e, FUSED ? p.z[base + e] : 0.0F, (!FUSED && p.add) ? p.dx[base + e] : 0.0F, odx, ores);
+						if (p.dx)
+							p.dx[base + e] = odx;
+						if (FUSED && p.dres)
+							p.dres[base + e] = ores;
+					}
+				}
+				__syncthreads();
+			}
+		}
+
+		// Fallback gather from global memory, one thread per input element.
+		template <bool FUSED>
+		__global__ void __launch_bounds__(kThreads) pool_bwd_direct_kernel(const pool_bwd_params p)
+		{
+			const pool_geom& g = p.g;
+			const int64_t total = p.planes * g.hw;
+			const int64_t stride = int64_t(gridDim.x) * kThreads;
+			for (int64_t e = int64_t(blockIdx.x) * kThreads + threadIdx.x; e < total; e += stride)
+			{
+				const int64_t plane = e / g.hw;
+				const uint32_t rem = (uint32_t)(e - plane * g.hw);
+				const uint32_t iy = g.d_w.div(rem);
+				const uint32_t ix = rem - iy * g.w;
+				const float seed = (!FUSED && p.add) ? p.dx[e] : 0.0F;
+				const float dz = gather_element(g, p.dpooled + plane * g.ohw, p.argmax + plane * g.ohw, iy, ix, (uint32_t)e, seed);
+				if (FUSED)
+				{
+					const float ds = (__float_as_uint(p.z[e]) >> 31) ? __fmul_rn(dz, p.slope) : dz;
+					if (p.dres)
+						p.dres[e] = ds;
+					if (p.dx)
+					{
+						const uint32_t channel = (uint32_t)(plane % g.c);
+						p.dx[e] = p.gamma ? __fmul_rn(ds, __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel))) : ds;
+					}
+				}
+				else
+					p.dx[e] = dz;
+			}
+		}
+
+		int make_geom(pool_geom& g, const char * who, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
+		{
+			if (!pool)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: pool descriptor is null", who);
+			if (n < 0 || c <= 0 || h <= 0 || w <= 0)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: bad extents n=%lld c=%lld h=%lld w=%lld", who, (long long)n, (long long)c, (long long)h, (long long)w);
+			if (pool->win_w < 1 || pool->win_h < 1 || pool->stride_w < 1 || pool->stride_h < 1)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: window and stride must be >= 1", who);
+			if (h * w > kMaxElemsPerLaunch || c > 0x7fffffff)
+				return set_error(NNF_ERR_UNSUPPORTED, "%s: plane too large", who);
+			const int64_t ow = nnf_pool_out_size(w, pool->win_w, pool->stride_w, pool->round_up_w);
+			const int64_t oh = nnf_pool_out_size(h, pool->win_h, pool->stride_h, pool->round_up_h);
+			if (ow <= 0 || oh <= 0)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: input %lldx%lld produces an empty output", who, (long long)w, (long long)h); // max_subsampling_layer.cpp:129-130
+			g.c = (uint32_t)c; g.h = (uint32_t)h; g.w = (uint32_t)w; g.hw = (uint32_t)(h * w);
+			g.oh = (uint32_t)oh; g.ow = (uint32_t)ow; g.ohw = (uint32_t)(oh * ow);
+			g.win_w = pool->win_w; g.win_h = pool->win_h; g.sw = pool->stride_w; g.sh = pool->stride_h;
+			g.is_min = pool->is_min ? 1 : 0;
+			g.d_w = fastdiv(g.w); g.d_hw = fastdiv(g.hw); g.d_ow = fastdiv(g.ow); g.d_ohw = fastdiv(g.ohw);
+			g.d_sw = fastdiv((uint32_t)g.sw); g.d_sh = fastdiv((uint32_t)g.sh); g.d_c = fastdiv(g.c);
+			return NNF_OK;
+		}
+
+		// planes per CTA iteration; 0 -> does not fit shared memory
+		int choose_group(const pool_geom& g, int64_t planes, bool& vec_ok)
+		{
+			int64_t grp = kGroupFloats / g.hw;
+			if (grp < 1)
+				grp = 1;
+			if (size_t(grp) * g.hw * sizeof(float) > kMaxDynSmem)
+				return 0;
+			if (grp >= 4 && (g.hw % 4) != 0)
+				grp &= ~int64_t(3);
+			// keep at least ~4 groups per SM so that the grid stays balanced
+			while (grp > 4 && div_up(planes, grp) < int64_t(kSmCount) * 4)
+				grp = (grp / 2) & ~int64_t(3);
+			if (grp < 1)
+				grp = 1;
+			if (planes < 0x7fffffff && grp > planes)
+				grp = planes;
+			vec_ok = vec_ok && ((grp * g.hw) % 4 == 0);
+			return (int)grp;
+		}
+
+		int run_pool_fwd(cudaStream_t s, bool fused, pool_fwd_params& p, int64_t n)
+		{
+			p.planes = n * p.g.c;
+			if (p.planes == 0)
+				return NNF_OK;
+			if (p.planes > 0x7fffffff)
+				return set_error(NNF_ERR_UNSUPPORTED, "max subsampling: more than 2^31 planes");
+			if (p.argmax && p.planes * p.g.hw > int64_t(0xffffffffll))
+				return set_error(NNF_ERR_UNSUPPORTED, "max subsampling: argmax offsets need n*c*h*w < 2^32");
+			bool vec_ok = aligned16(p.x) && (!fused || (aligned16(p.z) && (!p.res || aligned16(p.res))));
+			const int grp = choose_group(p.g, p.planes, vec_ok);
+			if (grp == 0)
+			{
+				if (fused)
+					return set_error(NNF_ERR_UNSUPPORTED, "fused max subsampling: a %ux%u plane does not fit shared memory", p.g.w, p.g.h);
+				const int64_t blocks = div_up(p.planes * p.g.ohw, kThreads);
+				const int grid = (int)(blocks < int64_t(kSmCount) * 8 ? blocks : int64_t(kSmCount) * 8);
+				pool_fwd_direct_kernel<<<grid, kThreads, 0, s>>>(p.pooled, p.argmax, p.x, p.g, p.planes);
+				return check_launch("pool_fwd_direct_kernel");
+			}
+			p.group = grp;
+			p.vec_ok = vec_ok ? 1 : 0;
+			const size_t smem = size_t(grp) * p.g.hw * sizeof(float);
+			const int64_t ngroups = div_up(p.planes, grp);
+			int per_sm = (int)((220 * 1024) / (smem + 1024));
+			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+			const int grid = (int)(ngroups < int64_t(kSmCount) * per_sm ? ngroups : int64_t(kSmCount) * per_sm);
+			cudaError_t e;
+			if (fused)
+			{
+				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+				if (e == cudaSuccess)
+					pool_fwd_staged_kernel<true><<<grid, kThreads, smem, s>>>(p);
+			}
+			else
+			{
+				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+				if (e == cudaSuccess)
+					pool_fwd_staged_kernel<false><<<grid, kThreads, smem, s>>>(p);
+			}
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+			return check_launch("pool_fwd_staged_kernel");
+		}
+
+		int run_pool_bwd(cudaStream_t s, bool fused, pool_bwd_params& p, int64_t n)
+		{
+			p.planes = n * p.g.c;
+			if (p.planes == 0)
+				return NNF_OK;
+			if (p.planes > 0x7fffffff)
+				return set_error(NNF_ERR_UNSUPPORTED, "max subsampling: more than 2^31 planes");
+			if (p.planes * p.g.hw > int64_t(0xffffffffll))
+				return set_error(NNF_ERR_UNSUPPORTED, "max subsampling: argmax offsets need n*c*h*w < 2^32");
+			bool vec_ok = (!p.dx || aligned16(p.dx)) && (!fused || (aligned16(p.z) && (!p.dres || aligned16(p.dres))));
+			const int grp = choose_group(p.g, p.planes, vec_ok);
+			const size_t smem = size_t(grp) * p.g.ohw * 2 * sizeof(float);
+			if (grp == 0 || smem > kMaxDynSmem)
+			{
+				const int64_t blocks = div_up(p.planes * p.g.hw, kThreads);
+				const int grid = (int)(blocks < int64_t(kSmCount) * 8 ? blocks : int64_t(kSmCount) * 8);
+				if (fused)
+					pool_bwd_direct_kernel<true><<<grid, kThreads, 0, s>>>(p);
+				else
+					pool_bwd_direct_kernel<false><<<grid, kThreads, 0, s>>>(p);
+				return check_launch("pool_bwd_direct_kernel");
+			}
+			p.group = grp;
+			p.vec_ok = vec_ok ? 1 : 0;
+			const int64_t ngroups = div_up(p.planes, grp);
+			int per_sm = (int)((220 * 1024) / (smem + 1024));
+			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+			const int grid = (int)(ngroups < int64_t(kSmCount) * per_sm ? ngroups : int64_t(kSmCount) * per_sm);
+			cudaError_t e;
+			if (fused)
+			{
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+				if (e == cudaSuccess)
+					pool_bwd_staged_kernel<true><<<grid, kThreads, smem, s>>>(p);
+			}
+			else
+			{
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+				if (e == cudaSuccess)
+					pool_bwd_staged_kernel<false><<<grid, kThreads, smem, s>>>(p);
+			}
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+			return check_launch("pool_bwd_staged_kernel");
+		}
+	}
+}
+
+using namespace nnf;
+
+extern "C" int64_t nnf_pool_out_size(int64_t in_size, int32_t window, int32_t stride, int32_t round_up)
+{
+	if (stride < 1)
+		return 0;
+	// max_subsampling_layer.cpp:127
+	return (in_size + stride - window + (round_up ? window - 1 : 0)) / stride;
+}
+
+extern "C" int nnf_maxpool_fwd(nnf_stream_t stream, float * y, uint32_t * argmax, const float * x,
+	int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
+{
+	pool_fwd_params p = {};
+	int st = make_geom(p.g, "nnf_maxpool_fwd", n, c, h, w, pool);
+	if (st != NNF_OK)
+		return st;
+	if (n == 0)
+		return NNF_OK;
+	if (!y || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_maxpool_fwd: null pointer");
+	p.pooled = y;
+	p.argmax = argmax;
+	p.x = x;
+	return run_pool_fwd((cudaStream_t)stream, false, p, n);
+}
+
+extern "C" int nnf_maxpool_bwd(nnf_stream_t stream, float * dx, const float * dy, const uint32_t * argmax,
+	int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool, int add_to_destination)
+{
+	pool_bwd_params p = {};
+	int st = make_geom(p.g, "nnf_maxpool_bwd", n, c, h, w, pool);
+	if (st != NNF_OK)
+		return st;
+	if (n == 0)
+		return NNF_OK;
+	if (!dx || !dy || !argmax)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_maxpool_bwd: null pointer");
+	p.dx = dx;
+	p.dpooled = dy;
+	p.argmax = argmax;
+	p.add = add_to_destination ? 1 : 0;
+	return run_pool_bwd((cudaStream_t)stream, false, p, n);
+}
+
+extern "C" int nnf_bn_add_relu_maxpool_fwd(nnf_stream_t stream, float * z, float * pooled, uint32_t * argmax,
+	const float * x, const float * residual,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	float relu_slope, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
+{
+	pool_fwd_params p = {};
+	int st = make_geom(p.g, "nnf_bn_add_relu_maxpool_fwd", n, c, h, w, pool);
+	if (st != NNF_OK)
+		return st;
+	if (n == 0)
+		return NNF_OK;
+	if (!z || !pooled || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_add_relu_maxpool_fwd: null pointer");
+	if (gamma && (!beta || !mean || !invsigma))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_add_relu_maxpool_fwd: gamma given but beta/mean/invsigma missing");
+	p.z = z; p.pooled = pooled; p.argmax = argmax; p.x = x; p.res = residual;
+	p.gamma = gamma; p.beta = beta; p.mean = mean; p.invsigma = invsigma;
+	p.slope = relu_slope;
+	return run_pool_fwd((cudaStream_t)stream, true, p, n);
+}
+
+extern "C" int nnf_bn_add_relu_maxpool_bwd(nnf_stream_t stream, float * dx, float * dresidual,
+	const float * dpooled, const uint32_t * argmax, const float * z,
+	const float * gamma, const float * invsigma,
+	float relu_slope, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
+{
+	pool_bwd_params p = {};
+	int st = make_geom(p.g, "nnf_bn_add_relu_maxpool_bwd", n, c, h, w, pool);
+	if (st != NNF_OK)
+		return st;
+	if (n == 0)
+		return NNF_OK;
+	if (!dpooled || !argmax || !z)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_add_relu_maxpool_bwd: null pointer");
+	if (!(relu_slope >= 0.0F))
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_add_relu_maxpool_bwd: the ReLU gate is read from the sign of z, which needs slope >= 0 (got %g)", (double)relu_slope);
+	if (gamma && !invsigma)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_add_relu_maxpool_bwd: gamma given but invsigma missing");
+	p.dx = dx; p.dres = dresidual; p.dpooled = dpooled; p.argmax = argmax; p.z = z;
+	p.gamma = gamma; p.invsigma = invsigma; p.slope = relu_slope;
+	return run_pool_bwd((cudaStream_t)stream, true, p, n);
+}

@@ -1,0 +1,456 @@
+// Channel softmax forward/backward. HBM-bound single pass wherever one (n, pixel) column fits in
+// registers or shared memory: algorithmic bytes = 8 per element forward, 12 backward.
+//
+// Layout cases
+//   hw == 1 : the C logits of an entry are contiguous  -> one warp per row, row kept in registers
+//             (C <= 1024), else one CTA per row with the row staged in shared memory.
+//   hw  > 1 : logits of one pixel are hw floats apart   -> one thread per pixel, consecutive lanes on
+//             consecutive pixels (coalesced 128-byte rows per channel), column kept in registers
+//             (C <= 32), else a shared-memory tile [C][32 pixels] per CTA.
+// Arithmetic follows nnforge/plain/softmax_layer_tester_plain.cpp:65-88 (max seeded with -1e37,
+// expf(x - max), multiply by the rounded reciprocal of the sum) and
+// nnforge/plain/softmax_layer_updater_plain.cpp:139-160; only the order of the sum over C differs
+// (tree instead of ascending), which stays inside the 1e-5 relative tolerance.
+#include "nnf_common.cuh"
+
+namespace nnf
+{
+	namespace
+	{
+		constexpr float kMaxSeed = -1.0e+37F;
+
+		__device__ __forceinline__ float warp_max(float v)
+		{
+			#pragma unroll
+			for (int o = 16; o > 0; o >>= 1)
+				v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+			return v;
+		}
+
+		__device__ __forceinline__ float warp_sum(float v)
+		{
+			#pragma unroll
+			for (int o = 16; o > 0; o >>= 1)
+				v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+			return v;
+		}
+
+		// std::max(a, b) as the plain backend calls it: keeps `a` unless a < b (NaN logits never win).
+		__device__ __forceinline__ float ref_max(float a, float b) { return (a < b) ? b : a; }
+
+		// ---- hw == 1, warp per row ---------------------------------------------------------------
+		template <int PER_LANE, bool BACKWARD>
+		__global__ void __launch_bounds__(256) softmax_rows_warp_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
+		{
+			const int lane = threadIdx.x & 31;
+			const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+			const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+			for (int64_t row = warp; row < rows; row += nwarps)
+			{
+				const float * a = in0 + row * c;
+				float * o = out + row * c;
+				float v[PER_LANE];
+				if (!BACKWARD)
+				{
+					float m = kMaxSeed;
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+					{
+						const int idx = j * 32 + lane;
+						v[j] = idx < c ? ld_stream(a + idx) : kMaxSeed;
+						m = ref_max(m, v[j]);
+					}
+					m = warp_max(m);
+					float s = 0.0F;
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+					{
+						const int idx = j * 32 + lane;
+						v[j] = idx < c ? expf(__fsub_rn(v[j], m)) : 0.0F;
+						s = __fadd_rn(s, v[j]);
+					}
+					s = warp_sum(s);
+					const float mult = __fdiv_rn(1.0F, s);
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+					{
+						const int idx = j * 32 + lane;
+						if (idx < c)
+							st_stream(o + idx, __fmul_rn(v[j], mult));
+					}
+				}
+				else
+				{
+					// in0 = dy, in1 = y
+					const float * y = in1 + row * c;
+					float g[PER_LANE];
+					float s = 0.0F;
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+					{
+						const int idx = j * 32 + lane;
+						g[j] = idx < c ? ld_stream(a + idx) : 0.0F;
+						v[j] = idx < c ? ld_stream(y + idx) : 0.0F;
+						s = __fadd_rn(s, __fmul_rn(g[j], v[j]));
+					}
+					s = warp_sum(s);
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+					{
+						const int idx = j * 32 + lane;
+						if (idx < c)
+						{
+							const float r = __fmul_rn(v[j], __fsub_rn(g[j], s));
+							o[idx] = add ? __fadd_rn(o[idx], r) : r;
+						}
+					}
+				}
+			}
+		}
+
+		__device__ __forceinline__ float block_reduce(float v, float * s_red, bool is_max)
+		{
+			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+			v = is_max ? warp_max(v) : warp_sum(v);
+			__syncthreads();
+			if (lane == 0)
+				s_red[w] = v;
+			__syncthreads();
+			float r = is_max ? kMaxSeed : 0.0F;
+			for (int i = 0; i < nw; ++i)
+				r = is_max ? fmaxf(r, s_red[i]) : __fadd_rn(r, s_red[i]);
+			return r;
+		}
+
+		// ---- hw == 1, CTA per row; the row lives in shared memory when it fits, else it is re-read ----
+		template <bool BACKWARD, bool IN_SMEM>
+		__global__ void __launch_bounds__(256) softmax_rows_block_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
+		{
+			extern __shared__ float s_row[];
+			__shared__ float s_red[8];
+			for (int64_t row = blockIdx.x; row < rows; row += gridDim.x)
+			{
+				const float * a = in0 + row * c;
+				float * o = out + row * c;
+				if (!BACKWARD)
+				{
+					float m = kMaxSeed;
+					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					{
+						const float v = a[i];
+						if (IN_SMEM)
+							s_row[i] = v;
+						m = ref_max(m, v);
+					}
+					m = block_reduce(m, s_red, true);
+					float s = 0.0F;
+					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					{
+						const float e = expf(__fsub_rn(IN_SMEM ? s_row[i] : a[i], m));
+						if (IN_SMEM)
+							s_row[i] = e;
+						s = __fadd_rn(s, e);
+					}
+					s = block_reduce(s, s_red, false);
+					const float mult = __fdiv_rn(1.0F, s);
+					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					{
+						const float e = IN_SMEM ? s_row[i] : expf(__fsub_rn(a[i], m));
+						o[i] = __fmul_rn(e, mult);
+					}
+				}
+				else
+				{
+					const float * y = in1 + row * c;
+					float s = 0.0F;
+					for (int i = threadIdx.x; i < c; i += blockDim.x)
+						s = __fadd_rn(s, __fmul_rn(a[i], y[i]));
+					s = block_reduce(s, s_red, false);
+					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					{
+						const float r = __fmul_rn(y[i], __fsub_rn(a[i], s));
+						o[i] = add ? __fadd_rn(o[i], r) : r;
+					}
+				}
+				__syncthreads();
+			}
+		}
+
+		// ---- hw > 1, thread per pixel, column in registers ------------------------------------------
+		template <int CMAX, bool BACKWARD>
+		__global__ void __launch_bounds__(256) softmax_pixels_reg_kernel(float * out, const float * in0, const float * in1, int64_t pixels, uint32_t hw, fastdiv hwdiv, int c, int add)
+		{
+			const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+			for (int64_t p = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; p < pixels; p += stride)
+			{
+				// pixels < 2^31 per launch: entry = p / hw
+				const uint32_t entry = hwdiv.div((uint32_t)p);
+				const uint32_t pix = (uint32_t)p - entry * hw;
+				const int64_t base = int64_t(entry) * c * hw + pix;
+				float v[CMAX];
+				if (!BACKWARD)
+				{
+					float m = kMaxSeed;
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+					{
+						if (f < c)
+						{
+							v[f] = ld_stream(in0 + base + int64_t(f) * hw);
+							m = ref_max(m, v[f]);
+						}
+					}
+					float s = 0.0F;
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+					{
+						if (f < c)
+						{
+							v[f] = expf(__fsub_rn(v[f], m));
+							s = __fadd_rn(s, v[f]); // ascending c: same order as the plain backend
+						}
+					}
+					const float mult = __fdiv_rn(1.0F, s);
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+						if (f < c)
+							st_stream(out + base + int64_t(f) * hw, __fmul_rn(v[f], mult));
+				}
+				else
+				{
+					float g[CMAX];
+					float s = 0.0F;
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+					{
+						if (f < c)
+						{
+							g[f] = ld_stream(in0 + base + int64_t(f) * hw);
+							v[f] = ld_stream(in1 + base + int64_t(f) * hw);
+						}
+					}
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+						if (f < c)
+							s = __fadd_rn(s, __fmul_rn(g[f], v[f]));
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+					{
+						if (f < c)
+						{
+							const float r = __fmul_rn(v[f], __fsub_rn(g[f], s));
+							float * o = out + base + int64_t(f) * hw;
+							*o = add ? __fadd_rn(*o, r) : r;
+						}
+					}
+				}
+			}
+		}
+
+		// ---- hw > 1, any C: CTA = 32 pixels x 8 channel groups, column tile staged in shared memory
+		// when it fits (single HBM pass), else re-read from global/L2 --------------------------------
+		template <bool BACKWARD, bool IN_SMEM>
+		__global__ void __launch_bounds__(256) softmax_pixels_tile_kernel(float * out, const float * in0, const float * in1, int64_t pixels, uint32_t hw, fastdiv hwdiv, int c, int add)
+		{
+			extern __shared__ float s_tile[]; // [c][32] when IN_SMEM (second [c][32] for backward)
+			__shared__ float s_red[8][32];
+			const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+			const int64_t ntiles = (pixels + 31) / 32;
+			for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x)
+			{
+				const int64_t p = t * 32 + lane;
+				const bool valid = p < pixels;
+				const uint32_t entry = valid ? hwdiv.div((uint32_t)p) : 0;
+				const uint32_t pix = valid ? (uint32_t)p - entry * hw : 0;
+				const int64_t base = int64_t(entry) * c * hw + pix;
+				if (!BACKWARD)
+				{
+					float m = kMaxSeed;
+					for (int f = grp; f < c; f += 8)
+					{
+						const float v = valid ? in0[base + int64_t(f) * hw] : 0.0F;
+						if (IN_SMEM)
+							s_tile[f * 32 + lane] = v;
+						m = ref_max(m, v);
+					}
+					s_red[grp][lane] = m;
+					__syncthreads();
+					m = kMaxSeed;
+					#pragma unroll
+					for (int i = 0; i < 8; ++i)
+						m = fmaxf(m, s_red[i][lane]);
+					__syncthreads();
+					float s = 0.0F;
+					for (int f = grp; f < c; f += 8)
+					{
+						const float x = IN_SMEM ? s_tile[f * 32 + lane] : (valid ? in0[base + int64_t(f) * hw] : 0.0F);
+						const float e = expf(__fsub_rn(x, m));
+						if (IN_SMEM)
+							s_tile[f * 32 + lane] = e;
+						s = __fadd_rn(s, e);
+					}
+					s_red[grp][lane] = s;
+					__syncthreads();
+					s = 0.0F;
+					#pragma unroll
+					for (int i = 0; i < 8; ++i)
+						s = __fadd_rn(s, s_red[i][lane]);
+					const float mult = __fdiv_rn(1.0F, s);
+					if (valid)
+						for (int f = grp; f < c; f += 8)
+						{
+							const float e = IN_SMEM ? s_tile[f * 32 + lane] : expf(__fsub_rn(in0[base + int64_t(f) * hw], m));
+							out[base + int64_t(f) * hw] = __fmul_rn(e, mult);
+						}
+					__syncthreads();
+				}
+				else
+				{
+					float * s_dy = s_tile;
+					float * s_y = s_tile + size_t(c) * 32;
+					float s = 0.0F;
+					for (int f = grp; f < c; f += 8)
+					{
+						const float g = valid ? in0[base + int64_t(f) * hw] : 0.0F;
+						const float y = valid ? in1[base + int64_t(f) * hw] : 0.0F;
+						if (IN_SMEM)
+						{
+							s_dy[f * 32 + lane] = g;
+							s_y[f * 32 + lane] = y;
+						}
+						s = __fadd_rn(s, __fmul_rn(g, y));
+					}
+					s_red[grp][lane] = s;
+					__syncthreads();
+					s = 0.0F;
+					#pragma unroll
+					for (int i = 0; i < 8; ++i)
+						s = __fadd_rn(s, s_red[i][lane]);
+					if (valid)
+						for (int f = grp; f < c; f += 8)
+						{
+							const float g = IN_SMEM ? s_dy[f * 32 + lane] : in0[base + int64_t(f) * hw];
+							const float y = IN_SMEM ? s_y[f * 32 + lane] : in1[base + int64_t(f) * hw];
+							const float r = __fmul_rn(y, __fsub_rn(g, s));
+							float * o = out + base + int64_t(f) * hw;
+							*o = add ? __fadd_rn(*o, r) : r;
+						}
+					__syncthreads();
+				}
+			}
+		}
+
+		constexpr size_t kMaxDynSmem = 200 * 1024;
+
+		template <bool BACKWARD>
+		int run_softmax(cudaStream_t s, float * out, const float * in0, const float * in1, int64_t n, int64_t c, int64_t hw, int add)
+		{
+			if (hw == 1)
+			{
+				const int64_t rows = n;
+				if (c <= 1024)
+				{
+					const int64_t blocks_needed = div_up(rows, 8);
+					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 8 ? blocks_needed : int64_t(kSmCount) * 8);
+#define NNF_ROWS(PL) softmax_rows_warp_kernel<PL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
+					if (c <= 32) NNF_ROWS(1);
+					else if (c <= 64) NNF_ROWS(2);
+					else if (c <= 128) NNF_ROWS(4);
+					else if (c <= 256) NNF_ROWS(8);
+					else if (c <= 512) NNF_ROWS(16);
+					else NNF_ROWS(32);
+#undef NNF_ROWS
+					return check_launch("softmax_rows_warp_kernel");
+				}
+				const int grid = (int)(rows < int64_t(kSmCount) * 4 ? rows : int64_t(kSmCount) * 4);
+				const size_t smem = size_t(c) * sizeof(float);
+				if (!BACKWARD && smem <= kMaxDynSmem)
+				{
+					cudaError_t e = cudaFuncSetAttribute(softmax_rows_block_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+					if (e != cudaSuccess)
+						return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+					softmax_rows_block_kernel<BACKWARD, true><<<grid, 256, smem, s>>>(out, in0, in1, rows, (int)c, add);
+				}
+				else
+					softmax_rows_block_kernel<BACKWARD, false><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add);
+				return check_launch("softmax_rows_block_kernel");
+			}
+
+			// hw > 1: split launches so that the pixel index fits 31 bits
+			if (hw > 0x7fffffff || c > 0x7fffffff)
+				return set_error(NNF_ERR_UNSUPPORTED, "softmax: extent too large");
+			const int64_t entries_per_launch = kMaxElemsPerLaunch / hw;
+			if (entries_per_launch < 1)
+				return set_error(NNF_ERR_UNSUPPORTED, "softmax: hw too large");
+			for (int64_t e0 = 0; e0 < n; e0 += entries_per_launch)
+			{
+				const int64_t ne = (n - e0 < entries_per_launch) ? (n - e0) : entries_per_launch;
+				const int64_t pixels = ne * hw;
+				const int64_t off = e0 * c * hw;
+				float * o = out + off;
+				const float * a = in0 + off;
+				const float * b = in1 ? in1 + off : nullptr;
+				if (c <= 32)
+				{
+					const int64_t blocks_needed = div_up(pixels, 256);
+					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 16 ? blocks_needed : int64_t(kSmCount) * 16);
+					if (c <= 8)
+						softmax_pixels_reg_kernel<8, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					else if (c <= 16)
+						softmax_pixels_reg_kernel<16, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					else
+						softmax_pixels_reg_kernel<32, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					int st = check_launch("softmax_pixels_reg_kernel");
+					if (st != NNF_OK)
+						return st;
+				}
+				else
+				{
+					const int64_t ntiles = div_up(pixels, 32);
+					const size_t smem = size_t(c) * 32 * sizeof(float) * (BACKWARD ? 2 : 1);
+					const bool in_smem = smem <= kMaxDynSmem;
+					const int per_sm = in_smem ? (int)(kMaxDynSmem / (smem < 1024 ? 1024 : smem)) : 8;
+					const int64_t cap = int64_t(kSmCount) * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+					const int grid = (int)(ntiles < cap ? ntiles : cap);
+					if (in_smem)
+					{
+						cudaError_t e = cudaFuncSetAttribute(softmax_pixels_tile_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+						if (e != cudaSuccess)
+							return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+						softmax_pixels_tile_kernel<BACKWARD, true><<<grid, 256, smem, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					}
+					else
+						softmax_pixels_tile_kernel<BACKWARD, false><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					int st = check_launch("softmax_pixels_tile_kernel");
+					if (st != NNF_OK)
+						return st;
+				}
+			}
+			return NNF_OK;
+		}
+	}
+}
+
+using namespace nnf;
+
+extern "C" int nnf_softmax_fwd(nnf_stream_t stream, float * y, const float * x, int64_t n, int64_t c, int64_t hw)
+{
+	if (n < 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_softmax_fwd: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (n == 0)
+		return NNF_OK;
+	if (!y || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_softmax_fwd: null pointer");
+	return run_softmax<false>((cudaStream_t)stream, y, x, nullptr, n, c, hw, 0);
+}
+
+extern "C" int nnf_softmax_bwd(nnf_stream_t stream, float * dx, const float * dy, const float * y, int64_t n, int64_t c, int64_t hw, int add_to_destination)
+{
+	if (n < 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_softmax_bwd: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (n == 0)
+		return NNF_OK;
+	if (!dx || !dy || !y)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_softmax_bwd: null pointer");
+	return run_softmax<true>((cudaStream_t)stream, dx, dy, y, n, c, hw, add_to_destination ? 1 : 0);
+}

@@ -1,0 +1,425 @@
+"""GPU parity: every C-ABI entry point against the CPU oracle on identical seeded inputs.
+
+Bar: bit-exact for batch-norm inference, ReLU, PReLU, add and max-subsampling (values, argmax,
+gradients); |got-want| <= 1e-6 + 1e-5*|want| for everything that goes through expf, a division or a
+long reduction. All calls go through the C ABI (nnforge_b200.capi -> libnnf_b200.so).
+"""
+import numpy as np
+import pytest
+
+import synth
+from util import assert_bits_equal, assert_close
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def capi():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import nnforge_b200.capi as capi
+    return capi
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def make_acts(capi, names, slope_dev):
+    out = []
+    for n in names:
+        if n == "relu0":
+            out.append(capi.relu(0.0))
+        elif n == "relu01":
+            out.append(capi.relu(0.1))
+        elif n == "prelu":
+            out.append(capi.prelu(slope_dev))
+        elif n == "elu":
+            out.append(capi.elu())
+        elif n == "tanh":
+            out.append(capi.tanh(1.7159, 0.6666))
+        elif n == "sigmoid":
+            out.append(capi.sigmoid())
+    return out
+
+
+def oracle_acts(oracle, names, v, slope):
+    for n in names:
+        if n == "relu0":
+            v = oracle.relu_fwd(v, 0.0)
+        elif n == "relu01":
+            v = oracle.relu_fwd(v, 0.1)
+        elif n == "prelu":
+            v = oracle.prelu_fwd(v, slope)
+        elif n == "elu":
+            v = oracle.elu_fwd(v)
+        elif n == "tanh":
+            v = oracle.tanh_fwd(v, 1.7159, 0.6666)
+        elif n == "sigmoid":
+            v = oracle.sigmoid_fwd(v)
+    return v
+
+
+EXACT = {"relu0", "relu01", "prelu"}
+SHAPES = [(64, 64, 32, 32), (3, 5, 7, 7), (2, 3, 1, 1), (1, 1, 1, 1), (5, 4, 3, 2), (2, 130, 9, 5), (7, 2, 16, 4)]
+CHAINS = [(), ("relu0",), ("relu01",), ("prelu",), ("elu",), ("tanh",), ("sigmoid",), ("prelu", "elu"), ("relu01", "tanh")]
+
+
+def compare(got, want, chain, what):
+    if all(n in EXACT for n in chain):
+        assert_bits_equal(got, want, what)
+    else:
+        assert_close(got, want, what)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("chain", CHAINS)
+def test_bn_infer_act(capi, oracle, shape, chain):
+    g = synth.rng(0, salt=sum(shape) + len(chain))
+    sat = "tanh" in chain  # (e-1)/(e+1) is NaN on both sides once e overflows; keep inputs finite there
+    x = synth.normal(g, shape, 0.0, 1.0) if sat else synth.with_edges(g, synth.normal(g, shape, 0.0, 1.0))
+    c = shape[1]
+    bn = synth.bn_params(g, c, 1e-5)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    want = oracle_acts(oracle, chain, oracle.bn_infer(x, *bn), slope)
+    xd, y = dev(x), torch.empty(shape, device="cuda")
+    sd = dev(slope)
+    capi.bn_infer_act(y, xd, bn=[dev(p) for p in bn], acts=make_acts(capi, chain, sd))
+    compare(host(y), want, chain, "bn+%s %s" % (chain, shape))
+    # in place
+    capi.bn_infer_act(xd, xd, bn=[dev(p) for p in bn], acts=make_acts(capi, chain, sd))
+    compare(host(xd), want, chain, "in-place bn+%s %s" % (chain, shape))
+
+
+@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 1, 1)])
+def test_bn_add_act_and_plain_activation(capi, oracle, shape):
+    g = synth.rng(3, salt=sum(shape))
+    x = synth.with_edges(g, synth.normal(g, shape))
+    r = synth.with_edges(g, synth.normal(g, shape))
+    c = shape[1]
+    bn = synth.bn_params(g, c)
+    bnd = [dev(p) for p in bn]
+    y = torch.empty(shape, device="cuda")
+    capi.bn_infer_act(y, dev(x), bn=bnd, residual=dev(r), acts=[capi.relu(0.0)])
+    want = oracle.relu_fwd(oracle.add_fwd([oracle.bn_infer(x, *bn), r], 1.0), 0.0)
+    assert_bits_equal(host(y), want, "bn+add+relu")
+    capi.bn_infer_act(y, dev(x), bn=bnd, residual=dev(r), add_alpha=0.5, acts=[])
+    assert_bits_equal(host(y), oracle.add_fwd([oracle.bn_infer(x, *bn), r], 0.5), "bn+add alpha")
+    # no batch norm: stand-alone activations
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    sd = dev(slope)
+    for name in ("relu0", "prelu", "elu", "sigmoid"):
+        capi.act_fwd(y, dev(x), make_acts(capi, [name], sd)[0])
+        compare(host(y), oracle_acts(oracle, [name], x, slope), (name,), name)
+
+
+def test_unaligned_buffers_take_the_scalar_path(capi, oracle):
+    g = synth.rng(4)
+    shape = (3, 4, 5, 5)
+    n = int(np.prod(shape))
+    x = synth.normal(g, shape)
+    bn = synth.bn_params(g, shape[1])
+    buf_in = torch.zeros(n + 3, device="cuda")
+    buf_out = torch.full((n + 3,), 7.0, device="cuda")
+    buf_in[1:n + 1] = dev(x).reshape(-1)
+    xin = buf_in[1:n + 1].view(shape)
+    yout = buf_out[1:n + 1].view(shape)
+    capi.bn_infer_act(yout, xin, bn=[dev(p) for p in bn], acts=[capi.relu(0.0)])
+    assert_bits_equal(host(yout), oracle.relu_fwd(oracle.bn_infer(x, *bn), 0.0), "unaligned")
+    assert host(buf_out)[0] == 7.0 and (host(buf_out)[n + 1:] == 7.0).all(), "wrote outside the tensor"
+
+
+@pytest.mark.parametrize("shape", [(6, 8, 12, 12), (3, 5, 7, 7), (2, 3, 1, 1), (1, 2, 1, 3)])
+@pytest.mark.parametrize("add", [False, True])
+def test_act_bwd(capi, oracle, shape, add):
+    g = synth.rng(5, salt=sum(shape))
+    x = synth.with_edges(g, synth.normal(g, shape))
+    dy = synth.normal(g, shape)
+    dx0 = synth.normal(g, shape)
+    c = shape[1]
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    sd = dev(slope)
+    seed = dx0 if add else None
+    cases = [
+        ("relu", capi.relu(0.1), x, oracle.relu_bwd(dy, x, 0.1, dx=seed), True),
+        ("relu0", capi.relu(0.0), x, oracle.relu_bwd(dy, x, 0.0, dx=seed), True),
+        ("prelu", capi.prelu(sd), x, oracle.prelu_bwd_data(dy, x, slope, dx=seed), True),
+    ]
+    y = oracle.elu_fwd(x)
+    cases.append(("elu", capi.elu(), y, oracle.elu_bwd(dy, y, dx=seed), True))
+    xs = synth.normal(g, shape)
+    y = oracle.tanh_fwd(xs, 1.7159, 0.6666)
+    cases.append(("tanh", capi.tanh(1.7159, 0.6666), y, oracle.tanh_bwd(dy, y, 1.7159, 0.6666, dx=seed), True))
+    y = oracle.sigmoid_fwd(x)
+    cases.append(("sigmoid", capi.sigmoid(), y, oracle.sigmoid_bwd(dy, y, dx=seed), True))
+    for name, act, neurons, want, exact in cases:
+        dx = dev(dx0.copy())
+        capi.act_bwd(dx, dev(dy), dev(neurons), act, add_to_destination=add)
+        # derivative formulas use only multiplies/adds of stored values: bit-exact on both sides
+        assert_bits_equal(host(dx), want, "%s bwd add=%s" % (name, add))
+
+
+@pytest.mark.parametrize("shape", [(256, 16, 28, 28), (5, 7, 3, 3), (3, 2, 1, 1), (9, 4, 7, 7)])
+def test_prelu_bwd_weights(capi, oracle, shape):
+    g = synth.rng(6, salt=sum(shape))
+    x = synth.normal(g, shape, 0.5, 2.0)
+    dy = synth.normal(g, shape)
+    d0 = synth.normal(g, shape[1])
+    ds = dev(d0.copy())
+    capi.prelu_bwd_weights(ds, dev(dy), dev(x))
+    exact = d0.astype(np.float64) + (dy.astype(np.float64) * np.where(x >= 0, 0.0, x)).sum(axis=(0, 2, 3))
+    m = shape[0] * shape[2] * shape[3]
+    scale = np.sqrt(m) * 2.0  # typical magnitude of a sum of m unit-variance terms
+    # long fp32 sums: the plain backend's own sequential sum differs from the exact value by more than
+    # the GPU's tree does; both must sit within sqrt(m)-scaled rounding of the exact sum
+    assert np.abs(host(ds) - exact).max() <= 1e-6 * scale + 1e-5 * np.abs(exact).max()
+    assert np.abs(oracle.prelu_bwd_weights(dy, x, dslope=d0) - exact).max() <= 1e-5 * scale + 1e-5 * np.abs(exact).max()
+
+
+@pytest.mark.parametrize("count", [1, 3, 4, 1000, 4099])
+def test_add(capi, oracle, count):
+    g = synth.rng(7, salt=count)
+    ins = [synth.with_edges(g, synth.normal(g, (count,))) for _ in range(4)]
+    for k, alpha in ((1, 1.0), (2, 1.0), (3, 0.25), (4, 2.0)):
+        y = torch.empty(count, device="cuda")
+        capi.add_fwd(y, [dev(a) for a in ins[:k]], alpha)
+        assert_bits_equal(host(y), oracle.add_fwd(ins[:k], alpha), "add k=%d" % k)
+    dy, dx0 = ins[0], ins[1]
+    dx = dev(dx0.copy())
+    capi.add_bwd(dx, dev(dy), 0.5)
+    assert_bits_equal(host(dx), oracle.add_bwd(dy, 0.5), "add bwd")
+    dx = dev(dx0.copy())
+    capi.add_bwd(dx, dev(dy), 1.0, add_to_destination=True)
+    assert_bits_equal(host(dx), oracle.add_bwd(dy, 1.0, dx=dx0), "add bwd accumulate")
+
+
+SOFTMAX_SHAPES = [(256, 1000, 1, 1), (32, 21, 128, 128), (4, 21, 32, 32), (3, 1, 1, 1), (5, 33, 3, 3), (2, 2000, 1, 1), (2, 5000, 1, 3),
+                  (7, 8, 5, 1), (3, 100, 2, 2), (6, 1500, 1, 1), (2, 3, 1, 1), (1, 1700, 2, 2)]
+
+
+@pytest.mark.parametrize("shape", SOFTMAX_SHAPES)
+def test_softmax(capi, oracle, shape):
+    g = synth.rng(1, salt=sum(shape))
+    x = synth.normal(g, shape, 0.0, 3.0)
+    dy = synth.normal(g, shape)
+    dx0 = synth.normal(g, shape)
+    want = oracle.softmax_fwd(x)
+    y = torch.empty(shape, device="cuda")
+    capi.softmax_fwd(y, dev(x))
+    assert_close(host(y), want, "softmax fwd %s" % (shape,))
+    np.testing.assert_allclose(host(y).astype(np.float64).sum(axis=1), 1.0, atol=2e-6)
+    xd = dev(x)
+    capi.softmax_fwd(xd, xd)
+    assert_close(host(xd), want, "softmax fwd in place")
+    yd = dev(want)
+    dx = torch.empty(shape, device="cuda")
+    capi.softmax_bwd(dx, dev(dy), yd)
+    # dx = y*(dy - s): cancellation in (dy - s) leaves an absolute error ~ eps*|dy|*y
+    assert_close(host(dx), oracle.softmax_bwd(dy, want), "softmax bwd", atol=2e-6)
+    dx = dev(dx0.copy())
+    capi.softmax_bwd(dx, dev(dy), yd, add_to_destination=True)
+    assert_close(host(dx), oracle.softmax_bwd(dy, want, dx=dx0), "softmax bwd accumulate", atol=2e-6)
+
+
+POOLS = [((3, 3), (2, 2), (False, False)), ((3, 3), (2, 2), (True, True)), ((2, 2), (2, 2), (False, False)), ((2, 2), (2, 2), (True, False)),
+         ((3, 3), (1, 1), (False, False)), ((2, 3), (2, 1), (False, True)), ((1, 1), (1, 1), (False, False)), ((5, 5), (3, 3), (True, True)),
+         ((3, 2), (3, 3), (False, False)), ((4, 4), (4, 4), (True, True)), ((7, 7), (7, 7), (False, False))]
+POOL_SHAPES = [(2, 3, 7, 7), (3, 5, 9, 11), (2, 4, 14, 14), (1, 2, 8, 5), (4, 64, 56, 56), (2, 1, 130, 130), (1, 1, 250, 240)]
+
+
+@pytest.mark.parametrize("shape", POOL_SHAPES)
+@pytest.mark.parametrize("win,stride,round_up", POOLS)
+def test_maxpool(capi, oracle, shape, win, stride, round_up):
+    if any(oracle.maxpool_out_size(s, w, st, r) <= 0 for s, w, st, r in zip((shape[3], shape[2]), win, stride, round_up)):
+        pytest.skip("empty output")
+    g = synth.rng(3, salt=sum(shape) * 13 + win[0] * 5 + stride[1] + round_up[0])
+    x = oracle.relu_fwd(synth.normal(g, shape), 0.0)  # ReLU output: many ties, +0/-0 mixes
+    for is_min in (False, True):
+        want_y, want_idx = oracle.maxpool_fwd(x, win, stride, round_up, is_min)
+        p = capi.pool(win, stride, round_up, is_min)
+        y = torch.empty(want_y.shape, device="cuda")
+        idx = torch.zeros(want_y.shape, device="cuda", dtype=torch.int32)
+        capi.maxpool_fwd(y, idx, dev(x), p)
+        assert_bits_equal(host(y), want_y, "pool values")
+        assert_bits_equal(host(idx).view(np.uint32), want_idx, "pool argmax")
+        capi.maxpool_fwd(y, None, dev(x), p)
+        assert_bits_equal(host(y), want_y, "pool values without argmax")
+    p = capi.pool(win, stride, round_up, False)
+    want_y, want_idx = oracle.maxpool_fwd(x, win, stride, round_up, False)
+    dy = synth.normal(g, want_y.shape)
+    dx = torch.full(shape, 3.0, device="cuda")
+    capi.maxpool_bwd(dx, dev(dy), dev(want_idx.view(np.int32)), p)
+    assert_bits_equal(host(dx), oracle.maxpool_bwd(dy, want_idx, shape), "pool bwd")
+    dx0 = synth.normal(g, shape)
+    dx = dev(dx0.copy())
+    capi.maxpool_bwd(dx, dev(dy), dev(want_idx.view(np.int32)), p, add_to_destination=True)
+    assert_bits_equal(host(dx), oracle.maxpool_bwd(dy, want_idx, shape, dx=dx0), "pool bwd accumulate")
+
+
+@pytest.mark.parametrize("c,hw", [(64, 56), (128, 28), (256, 14), (512, 7), (3, 9)])
+@pytest.mark.parametrize("round_up", [False, True])
+def test_bn_add_relu_maxpool(capi, oracle, c, hw, round_up):
+    """The ResNet-style chain at its four stage shapes (reduced batch) and one ragged shape."""
+    n = 6
+    shape = (n, c, hw, hw)
+    g = synth.rng(3, salt=c + hw)
+    x, r = synth.normal(g, shape), synth.normal(g, shape)
+    bn = synth.bn_params(g, c)
+    win, stride, ru = (3, 3), (2, 2), (round_up, round_up)
+    z_want = oracle.relu_fwd(oracle.add_fwd([oracle.bn_infer(x, *bn), r], 1.0), 0.0)
+    y_want, idx_want = oracle.maxpool_fwd(z_want, win, stride, ru)
+    p = capi.pool(win, stride, ru)
+    z = torch.empty(shape, device="cuda")
+    y = torch.empty(y_want.shape, device="cuda")
+    idx = torch.zeros(y_want.shape, device="cuda", dtype=torch.int32)
+    bnd = [dev(a) for a in bn]
+    capi.bn_add_relu_maxpool_fwd(z, y, idx, dev(x), dev(r), bnd, 0.0, p)
+    assert_bits_equal(host(z), z_want, "fused z")
+    assert_bits_equal(host(y), y_want, "fused pooled")
+    assert_bits_equal(host(idx).view(np.uint32), idx_want, "fused argmax")
+    # backward: pool gather -> ReLU gate -> add identity -> frozen batch norm scale
+    dyp = synth.normal(g, y_want.shape)
+    dz = oracle.maxpool_bwd(dyp, idx_want, shape)
+    s_in = oracle.add_fwd([oracle.bn_infer(x, *bn), r], 1.0)
+    ds = oracle.relu_bwd(dz, s_in, 0.0)
+    mult = (bn[0] * bn[3]).astype(np.float32)
+    dx_want = (ds * mult[None, :, None, None]).astype(np.float32)
+    dx = torch.empty(shape, device="cuda")
+    dr = torch.empty(shape, device="cuda")
+    capi.bn_add_relu_maxpool_bwd(dx, dr, dev(dyp), idx, z, bnd[0], bnd[3], 0.0, p)
+    assert_bits_equal(host(dr), ds, "fused dresidual")
+    assert_bits_equal(host(dx), dx_want, "fused dx")
+
+
+TRAIN_SHAPES = [(16, 32, 28, 28), (5, 3, 7, 7), (4, 6, 1, 1), (3, 2, 5, 3), (64, 8, 14, 14)]
+TRAIN_CHAINS = [("prelu", "elu"), (), ("relu0",), ("tanh",), ("sigmoid",), ("elu",), ("relu01", "prelu")]
+
+
+def train_oracle(oracle, x, dy, gamma, beta, slope, chain, eps, shards=1):
+    """Layer-by-layer training step on the CPU: BN (batch statistics) then each activation layer, and
+    the same backwards, the way the reference schedules unfused layers."""
+    n, c = x.shape[0], x.shape[1]
+    m = x.size // c
+    s, q = oracle.bn_train_sums(x)
+    saved = oracle.bn_train_finalize(s, q, m, eps)
+    u = oracle.bn_train_apply(x, gamma, beta, saved)
+    acts_in, v = [], u
+    for name in chain:
+        acts_in.append(v)
+        v = oracle_acts(oracle, [name], v, slope)
+    y = v
+    g = dy
+    dslope = np.zeros(c, np.float32)
+    outs = acts_in[1:] + [y]
+    for name, a_in, a_out in reversed(list(zip(chain, acts_in, outs))):
+        if name == "relu0":
+            g = oracle.relu_bwd(g, a_in, 0.0)
+        elif name == "relu01":
+            g = oracle.relu_bwd(g, a_in, 0.1)
+        elif name == "prelu":
+            dslope = oracle.prelu_bwd_weights(g, a_in)
+            g = oracle.prelu_bwd_data(g, a_in, slope)
+        elif name == "elu":
+            g = oracle.elu_bwd(g, a_out)
+        elif name == "tanh":
+            g = oracle.tanh_bwd(g, a_out, 1.7159, 0.6666)
+        elif name == "sigmoid":
+            g = oracle.sigmoid_bwd(g, a_out)
+    db, dg = oracle.bn_train_bwd_sums(g, x, saved)
+    dx = oracle.bn_train_bwd_apply(g, x, gamma, saved, db, dg, m)
+    return y, saved, dx, db, dg, dslope
+
+
+def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1):
+    """Same step through the C ABI; with shards > 1 the batch is split and the 2C-float sums are
+    added across shards on the host, standing in for the all-reduce."""
+    n, c = x.shape[0], x.shape[1]
+    hw = x.size // (n * c)
+    m = n * hw
+    sd = dev(slope)
+    acts = make_acts(capi, chain, sd)
+    gd, bd = dev(gamma), dev(beta)
+    bounds = [n * k // shards for k in range(shards + 1)]
+    xs = [dev(x[bounds[k]:bounds[k + 1]]) for k in range(shards)]
+    dys = [dev(dy[bounds[k]:bounds[k + 1]]) for k in range(shards)]
+    ws = torch.empty(capi.bn_train_workspace_bytes(n, c, hw), dtype=torch.uint8, device="cuda")
+    sums = []
+    for xk in xs:
+        t = torch.empty(2 * c, device="cuda")
+        capi.bn_train_stats(t, xk, ws)
+        sums.append(t)
+    total = torch.stack(sums).sum(0)
+    ys, saved = [], None
+    for xk in xs:
+        yk = torch.empty_like(xk)
+        saved = torch.empty(2 * c, device="cuda")
+        capi.bn_train_apply_act(yk, saved, xk, gd, bd, total, m, eps, acts)
+        ys.append(yk)
+    bs = []
+    for xk, dk in zip(xs, dys):
+        t = torch.empty(3 * c, device="cuda")
+        capi.bn_train_bwd_stats(t, dk, xk, gd, bd, saved, acts, ws)
+        bs.append(t)
+    gsum = torch.stack(bs).sum(0)[:2 * c].contiguous()
+    grads = {k: torch.zeros(c, device="cuda") for k in ("gamma", "beta", "slope", "mean", "invsigma")}
+    run_mean, run_inv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    dxs = []
+    for xk, dk, bk in zip(xs, dys, bs):
+        dxk = torch.empty_like(xk)
+        capi.bn_train_bwd_apply(dxk, dk, xk, gd, bd, saved, gsum, bk, m, acts, grad_gamma=grads["gamma"], grad_beta=grads["beta"],
+                                grad_mean=grads["mean"], grad_invsigma=grads["invsigma"], grad_slope=grads["slope"] if "prelu" in chain else None,
+                                mean=run_mean, invsigma=run_inv, entry_count=float(xk.shape[0]))
+        dxs.append(dxk)
+    return (np.concatenate([host(t) for t in ys]), host(saved), np.concatenate([host(t) for t in dxs]),
+            {k: host(v) for k, v in grads.items()})
+
+
+@pytest.mark.parametrize("shape", TRAIN_SHAPES)
+@pytest.mark.parametrize("chain", TRAIN_CHAINS)
+@pytest.mark.parametrize("shards", [1, 2])
+def test_bn_train(capi, oracle, shape, chain, shards):
+    if shards > shape[0]:
+        pytest.skip("fewer entries than shards")
+    g = synth.rng(2, salt=sum(shape) + len(chain))
+    x = synth.normal(g, shape, 0.5, 2.0)
+    dy = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    eps = 1e-5
+    y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, eps)
+    y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards)
+    assert_close(saved, saved_w, "saved mean/invstd")
+    assert_close(y, y_w, "train fwd %s" % (chain,), atol=2e-6)
+    m = x.size // c
+    scale = np.sqrt(m)
+    assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
+    assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
+    if "prelu" in chain:
+        assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
+    # dx = k*(m*du - dbeta - xhat*dgamma)/m: the subtraction leaves an absolute error of a few ulp of |du|*k
+    assert_close(dx, dx_w, "train bwd %s" % (chain,), atol=5e-6)
+    # running-statistics pseudo-gradients: entry_count*(batch - running), running = (0, 1)
+    assert_close(grads["mean"], shape[0] * saved_w[:c], "grad mean", atol=1e-5)
+    assert_close(grads["invsigma"], shape[0] * (saved_w[c:] - 1.0), "grad invsigma", atol=1e-5)
+
+
+def test_errors_are_reported_not_thrown(capi):
+    x = torch.zeros((2, 3, 4, 4), device="cuda")
+    with pytest.raises(capi.NnfError) as e:
+        capi.bn_infer_act(x, x, bn=[x, None, None, None], acts=[])
+    assert "beta" in str(e.value)
+    with pytest.raises(capi.NnfError):
+        capi.maxpool_fwd(x, None, x, capi.pool((9, 9), (1, 1)))
+    with pytest.raises(capi.NnfError):
+        capi.bn_train_stats(x, x, torch.empty(8, dtype=torch.uint8, device="cuda"))
+    empty = torch.zeros((0, 3, 4, 4), device="cuda")
+    capi.bn_infer_act(empty, empty, acts=[capi.relu(0.0)])  # empty batch is a no-op
+    capi.softmax_fwd(empty, empty)
