@@ -82,9 +82,9 @@ NNF_API int nnf_version(void);
  * Replaces batch_norm_layer_tester_cuda::enqueue_forward_propagation
  * (nnforge/cuda/batch_norm_layer_tester_cuda.cu:62-90; weights = gamma, beta, mean, inverse sigma:
  * nnforge/batch_norm_layer.h:26) followed by add_layer_tester_cuda (nnforge/cuda/add_layer_tester_cuda.cu:47-83)
- * and the activation testers (nnforge/cuda/rectified_linear_layer_tester_cuda.cu:52-75,
- * parametric_rectified_linear_layer_tester_cuda.cu:50-75, exponential_linear_layer_tester_cuda.cu:50-70,
- * hyperbolic_tangent_layer_tester_cuda.cu:58-84, sigmoid via activation_layer_cudnn_tester_cuda.cpp:40-72).
+ * and the activation testers (nnforge/cuda/rectified_linear_layer_tester_cuda.cu:52-73,
+ * parametric_rectified_linear_layer_tester_cuda.cu:50-74, exponential_linear_layer_tester_cuda.cu:50-70,
+ * hyperbolic_tangent_layer_tester_cuda.cu:58-80, sigmoid via activation_layer_cudnn_tester_cuda.cpp:42-72).
  * Arithmetic follows nnforge/plain/batch_norm_layer_tester_plain.cpp:60-72 and
  * nnforge/plain/add_layer_tester_plain.cpp:53-61. y may alias x. */
 NNF_API int nnf_bn_infer_act(nnf_stream_t stream, float * y, const float * x,
@@ -98,8 +98,9 @@ NNF_API int nnf_bn_infer_act(nnf_stream_t stream, float * y, const float * x,
 NNF_API int nnf_act_fwd(nnf_stream_t stream, float * y, const float * x, const nnf_act * act, int64_t n, int64_t c, int64_t hw);
 
 /* Activation backward: dx (+)= dy * act'(.), replacing enqueue_backward_data_propagation of
- * rectified_linear (nnforge/cuda/rectified_linear_layer_updater_cuda.cu:133-167), parametric_rectified_linear
- * (:165-213), exponential_linear (:117-143), hyperbolic_tangent (:130-160) and the cuDNN sigmoid
+ * rectified_linear (nnforge/cuda/rectified_linear_layer_updater_cuda.cu:135-167), parametric_rectified_linear
+ * (parametric_rectified_linear_layer_updater_cuda.cu:158-199), exponential_linear (exponential_linear_layer_updater_cuda.cu:117-145),
+ * hyperbolic_tangent (hyperbolic_tangent_layer_updater_cuda.cu:132-162) and the cuDNN sigmoid
  * (nnforge/cuda/activation_layer_cudnn_updater_cuda.cpp:77-117).
  * `neurons` is the layer INPUT for ReLU and PReLU and the layer OUTPUT for ELU, TanH and Sigmoid, the
  * dependency the plain backend declares (nnforge/plain/rectified_linear_layer_updater_plain.cpp:62-107,
@@ -108,7 +109,7 @@ NNF_API int nnf_act_bwd(nnf_stream_t stream, float * dx, const float * dy, const
 	int64_t n, int64_t c, int64_t hw, int add_to_destination);
 
 /* PReLU slope gradient: dslope[c] += sum_{n,hw} dy * (x >= 0 ? 0 : x), replacing
- * enqueue_backward_weights_propagation (nnforge/cuda/parametric_rectified_linear_layer_updater_cuda.cu:215-233;
+ * enqueue_backward_weights_propagation (nnforge/cuda/parametric_rectified_linear_layer_updater_cuda.cu:201-234;
  * plain: parametric_rectified_linear_layer_updater_plain.cpp:137-190). Deterministic (fixed reduction
  * tree, no atomics). workspace: nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) bytes. */
 NNF_API size_t nnf_prelu_bwd_weights_workspace_bytes(int64_t n, int64_t c, int64_t hw);
@@ -121,14 +122,14 @@ NNF_API int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const flo
  * y may alias inputs[0]. */
 NNF_API int nnf_add_fwd(nnf_stream_t stream, float * y, const float * const * inputs, int input_count, float alpha, int64_t count);
 
-/* Add layer backward: dx (+)= dy*alpha (nnforge/cuda/add_layer_updater_cuda.cu:84-116); a no-op when
+/* Add layer backward: dx (+)= dy*alpha (nnforge/cuda/add_layer_updater_cuda.cu:88-116); a no-op when
  * dx == dy, alpha == 1 and not accumulating, as in the reference. */
 NNF_API int nnf_add_bwd(nnf_stream_t stream, float * dx, const float * dy, float alpha, int64_t count, int add_to_destination);
 
 /* ---------------------------------------------------------------------------------------------
  * Channel softmax over C at every (n, pixel), replacing the cuDNN calls of
- * softmax_layer_tester_cuda (nnforge/cuda/softmax_layer_tester_cuda.cpp:58-67) and softmax_layer_updater_cuda
- * (nnforge/cuda/softmax_layer_updater_cuda.cpp:61-70, 100-111); arithmetic of
+ * softmax_layer_tester_cuda (nnforge/cuda/softmax_layer_tester_cuda.cpp:37-68) and softmax_layer_updater_cuda
+ * (nnforge/cuda/softmax_layer_updater_cuda.cpp:38-71, 73-112); arithmetic of
  * nnforge/plain/softmax_layer_tester_plain.cpp:65-88 and softmax_layer_updater_plain.cpp:100-166.
  * y may alias x; dx may alias dy. */
 NNF_API int nnf_softmax_fwd(nnf_stream_t stream, float * y, const float * x, int64_t n, int64_t c, int64_t hw);
@@ -150,7 +151,7 @@ typedef struct nnf_pool
 NNF_API int64_t nnf_pool_out_size(int64_t in_size, int32_t window, int32_t stride, int32_t round_up);
 
 /* Forward, replacing max_subsampling_layer_tester_cuda / max_subsampling_layer_updater_cuda forward
- * (nnforge/cuda/max_subsampling_layer_tester_cuda.cuh:182-217, max_subsampling_layer_updater_cuda.cuh:527-820).
+ * (nnforge/cuda/max_subsampling_layer_tester_cuda.cuh:194-217, max_subsampling_layer_updater_cuda.cuh:539-818).
  * Tie-break and argmax format are the PLAIN backend's (nnforge/plain/max_subsampling_layer_updater_plain.cpp:139-159):
  * window scanned x-fastest, first strict maximum wins, argmax = absolute input element offset as
  * uint32 (so n*c*h*w must be < 2^32 when argmax is requested). argmax may be NULL. */
@@ -160,7 +161,7 @@ NNF_API int nnf_maxpool_fwd(nnf_stream_t stream, float * y, uint32_t * argmax, c
 /* Backward as a deterministic gather: every input element sums dy of the (few) windows whose stored
  * argmax points at it, in ascending output index, which equals the plain backend's scatter
  * (nnforge/plain/max_subsampling_layer_updater_plain.cpp:173-231) run serially with accumulation onto a
- * zeroed buffer. No zero-fill pass, no atomics (reference: nnforge/cuda/max_subsampling_layer_updater_cuda.cuh:822-977). */
+ * zeroed buffer. No zero-fill pass, no atomics (reference: nnforge/cuda/max_subsampling_layer_updater_cuda.cuh:820-977). */
 NNF_API int nnf_maxpool_bwd(nnf_stream_t stream, float * dx, const float * dy, const uint32_t * argmax,
 	int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool, int add_to_destination);
 
