@@ -205,6 +205,21 @@ NNF_API size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw);
 NNF_API int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
 	void * workspace, size_t workspace_bytes);
 
+/* Same result as nnf_bn_train_stats, for callers that cannot supply a workspace. It has no counterpart
+ * in the reference. An nnForge layer object may only use the buffers its scheduler planned from the
+ * layer's size answers, and must not allocate while enqueueing (an allocation can fail once the
+ * scheduler has filled the memory it measured as free, and it stalls every stream of the device); the
+ * stock batch-norm updater plans no working buffer at all. This variant therefore keeps its per-CTA
+ * partial sums in a 1.5 MiB array built into the library (held by every GPU that loads it until the
+ * process ends) and calls no allocating routine.
+ *  - Limit: c <= 1024 channels; more returns NNF_ERR_UNSUPPORTED with a message naming the limit.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current). Make that first call before starting any stream capture on the device.
+ *  - All calls on a device share the array. Calls that overlap on the GPU (issued on different
+ *    streams without ordering between them) race on it; calls on one stream are safe. Nothing in the
+ *    array needs clearing between calls: each call writes every slot it later reads. */
+NNF_API int nnf_bn_train_stats_static(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw);
+
 NNF_API int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved, const float * x,
 	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);

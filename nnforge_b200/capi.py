@@ -61,6 +61,7 @@ _SIGNATURES = {
     "nnf_bn_add_relu_maxpool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _POOLP]),
     "nnf_bn_train_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
     "nnf_bn_train_stats": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_bn_train_stats_static": (_I, [_P, _P, _P, _I64, _I64, _I64]),
     "nnf_bn_train_apply_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _D, _F, _ACTP, _I, _I64, _I64, _I64]),
     "nnf_bn_train_bwd_stats": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
     "nnf_bn_train_bwd_apply": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
@@ -217,6 +218,12 @@ def bn_train_workspace_bytes(n, c, hw):
 def bn_train_stats(sums, x, workspace, stream=None):
     n, c, hw = _nchw(x)
     _check(lib.nnf_bn_train_stats(_stream(stream), _ptr(sums), _ptr(x), n, c, hw, _ptr(workspace), workspace.numel() * workspace.element_size()))
+
+
+def bn_train_stats_static(sums, x, stream=None):
+    """nnf_bn_train_stats without a workspace argument (library-resident scratch, c <= 1024)."""
+    n, c, hw = _nchw(x)
+    _check(lib.nnf_bn_train_stats_static(_stream(stream), _ptr(sums), _ptr(x), n, c, hw))
 
 
 def bn_train_apply_act(y, saved, x, gamma, beta, sums, count_total, eps, acts=(), stream=None):

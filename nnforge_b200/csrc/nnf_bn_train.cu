@@ -14,6 +14,8 @@
 // the workspace), so results are deterministic and independent of the grid.
 #include "nnf_common.cuh"
 
+#include <mutex>
+
 namespace nnf
 {
 	namespace
@@ -552,5 +554,81 @@ extern "C" int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const 
 	if (st != NNF_OK)
 		return st;
 	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(dslope, static_cast<const double *>(workspace), g.c, g.split, 1, 1);
+	return check_launch("bn_reduce_partials_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Batch statistics for callers that have no workspace to hand over.
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: an
+// nnForge layer object is only ever given the buffers the scheduler planned up front from the
+// layer's own size answers (and the stock batch-norm updater asks for no working buffer, so a
+// drop-in that must keep those answers has nowhere to get one); the scheduler also measures free
+// memory once and then fills it, so a later cudaMalloc can fail or stall every stream of the device.
+// For them the per-CTA partial sums live in the fixed array below, which every GPU that loads the
+// library holds until the process exits.
+//
+// Limit: kStaticMaxChannels channels (the array is kStaticMaxChannels * kMaxSplit * kSums doubles =
+// 1.5 MiB). The array is shared by all calls on a device and keeps whatever the last call left in
+// it; nothing in it has to start at zero, because every slot the reduce kernel reads is written by
+// the statistics kernel of the same call first. Two calls that overlap on one GPU (different
+// streams) would race on it.
+constexpr int kStaticMaxChannels = 1024;
+static __device__ __align__(256) double nnf_static_stats_scratch[size_t(kStaticMaxChannels) * nnf::kMaxSplit * nnf::kSums];
+
+namespace
+{
+	constexpr int kStaticMaxDevices = 64;
+	double * g_static_scratch_address[kStaticMaxDevices] = {};
+	std::mutex g_static_scratch_mutex;
+
+	// In host code the array's name is only a handle; the device address has to be asked for, once per
+	// device, with that device current.
+	int static_scratch_for_current_device(double *& address)
+	{
+		int device = -1;
+		cudaError_t e = cudaGetDevice(&device);
+		if (e != cudaSuccess)
+			return set_error(NNF_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+		if (device < 0 || device >= kStaticMaxDevices)
+			return set_error(NNF_ERR_UNSUPPORTED, "device ordinal %d is outside the supported range 0..%d", device, kStaticMaxDevices - 1);
+		std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+		if (!g_static_scratch_address[device])
+		{
+			double * p = nullptr;
+			e = cudaGetSymbolAddress((void **)&p, nnf_static_stats_scratch);
+			if (e != cudaSuccess || !p)
+				return set_error(NNF_ERR_CUDA, "cudaGetSymbolAddress(static statistics scratch): %s", cudaGetErrorString(e));
+			g_static_scratch_address[device] = p;
+		}
+		address = g_static_scratch_address[device];
+		return NNF_OK;
+	}
+}
+
+extern "C" int nnf_bn_train_stats_static(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw)
+{
+	int st = check_train_args("nnf_bn_train_stats_static", n, c, hw);
+	if (st != NNF_OK)
+		return st;
+	if (c > kStaticMaxChannels)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_stats_static: %lld channels exceed the built-in scratch, which holds at most %d; "
+			"use nnf_bn_train_stats with a workspace instead", (long long)c, kStaticMaxChannels);
+	if (!sums || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_stats_static: null pointer");
+	chan_geom g;
+	st = make_chan_geom(g, "nnf_bn_train_stats_static", n, c, hw, aligned16(x));
+	if (st != NNF_OK)
+		return st;
+	double * scratch = nullptr;
+	st = static_scratch_for_current_device(scratch);
+	if (st != NNF_OK)
+		return st;
+	cudaStream_t s = (cudaStream_t)stream;
+	bn_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(scratch, x, g);
+	st = check_launch("bn_stats_kernel");
+	if (st != NNF_OK)
+		return st;
+	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(sums, scratch, g.c, g.split, 2, 0);
 	return check_launch("bn_reduce_partials_kernel");
 }
