@@ -224,6 +224,35 @@ NNF_API int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved
 	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);
 
+/* Single-GPU forward in one call. When one channel's slab (n*hw floats) fits the shared memory of a
+ * thread-block cluster, a single-pass kernel reads x once and writes y once (8 bytes/element); other
+ * shapes run nnf_bn_train_stats + nnf_bn_train_apply_act, for which `sums` (2C floats) and the
+ * workspace are required. saved receives {mean, invstd}; sums (may be NULL for fitting shapes)
+ * receives {sum x, sum x^2}. Replaces batch_norm_layer_updater_cuda::enqueue_forward_propagation
+ * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:60-107) plus the activation layers behind it. */
+NNF_API int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
+	const float * gamma, const float * beta, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes);
+
+/* Single-GPU backward in one call: dx, bsums[3C] = {sum du, sum du*xhat, sum dslope} and the accumulated
+ * per-channel gradients (see nnf_bn_train_bwd_apply). Where a channel's du slab fits a cluster's shared
+ * memory a single-pass kernel reads x and dy from HBM once and writes dx once (12 bytes/element; x is
+ * read a second time a few microseconds later, from L2); other shapes run nnf_bn_train_bwd_stats +
+ * nnf_bn_train_bwd_apply with the workspace. Replaces enqueue_backward_data_and_weights_propagation
+ * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:109-183) plus the activation layers' backward actions. */
+NNF_API int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination,
+	void * workspace, size_t workspace_bytes);
+
+/* Returns 1 (and clears it) when a single-pass kernel gave up a bounded wait since the last check,
+ * 0 otherwise, -1 if the word cannot be read. Synchronises the device: for tests and diagnosis. */
+NNF_API int nnf_fused_error_check(void);
+
 NNF_API int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
 	const float * gamma, const float * beta, const float * saved,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,

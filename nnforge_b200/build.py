@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libnnf_b200.so")
-SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_maxpool.cu", "nnf_bn_train.cu"]
+SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_maxpool.cu", "nnf_bn_train.cu", "nnf_bn_fused.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

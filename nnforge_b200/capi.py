@@ -63,6 +63,9 @@ _SIGNATURES = {
     "nnf_bn_train_stats": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _SZ]),
     "nnf_bn_train_stats_static": (_I, [_P, _P, _P, _I64, _I64, _I64]),
     "nnf_bn_train_apply_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _D, _F, _ACTP, _I, _I64, _I64, _I64]),
+    "nnf_bn_train_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_fused_error_check": (_I, []),
+    "nnf_bn_train_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I, _P, _SZ]),
     "nnf_bn_train_bwd_stats": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
     "nnf_bn_train_bwd_apply": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                     _I64, _I64, _I64, _I]),
@@ -231,6 +234,28 @@ def bn_train_apply_act(y, saved, x, gamma, beta, sums, count_total, eps, acts=()
     arr, k = _acts(acts)
     _check(lib.nnf_bn_train_apply_act(_stream(stream), _ptr(y), _ptr(saved), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(sums), float(count_total), eps,
                                       arr, k, n, c, hw))
+
+
+def bn_train_fwd(y, saved, sums, x, gamma, beta, eps, acts=(), workspace=None, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    _check(lib.nnf_bn_train_fwd(_stream(stream), _ptr(y), _ptr(saved), _ptr(sums), _ptr(x), _ptr(gamma), _ptr(beta), eps, arr, k, n, c, hw,
+                                _ptr(workspace), nbytes))
+
+
+def bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts=(), grad_gamma=None, grad_beta=None, grad_mean=None, grad_invsigma=None,
+                 grad_slope=None, mean=None, invsigma=None, entry_count=0.0, add_to_destination=False, workspace=None, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    _check(lib.nnf_bn_train_bwd(_stream(stream), _ptr(dx), _ptr(bsums), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), arr, k,
+                                _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma), _ptr(grad_slope), _ptr(mean), _ptr(invsigma),
+                                float(entry_count), n, c, hw, int(add_to_destination), _ptr(workspace), nbytes))
+
+
+def fused_error_check():
+    return int(lib.nnf_fused_error_check())
 
 
 def bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, workspace, gsums=None, stream=None):

@@ -23,6 +23,8 @@ namespace nnf
 		constexpr int kThreads = 256;
 		constexpr int kMaxSplit = 64;   // CTAs per channel (upper bound, sizes the workspace)
 		constexpr int kSums = 3;        // partial sums per channel and CTA
+		constexpr int kLoads = 4;       // independent 128-bit loads in flight per thread (statistics kernels)
+		constexpr int kLoads2 = 2;      // same for the kernels that stream two tensors
 
 		__device__ __forceinline__ double warp_sum_d(double v)
 		{
@@ -84,22 +86,51 @@ namespace nnf
 				const uint32_t total = (e1 - e0) * per_plane;
 				const size_t entry_stride = size_t(g.c) * g.hw;
 				const float * base = x + (size_t(e0) * g.c + ch) * g.hw;
-				for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+				// kLoads independent loads are issued before any is consumed: with one load in flight per
+				// thread an SM holds too few bytes in flight to cover the HBM latency
+				for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kThreads * kLoads)
 				{
-					const uint32_t lp = g.d_vpp.div(i);
-					const uint32_t v = i - lp * per_plane;
-					const float * plane = base + lp * entry_stride;
 					if (g.vec)
 					{
-						const float4 a = __ldg(reinterpret_cast<const float4 *>(plane) + v);
-						s += (a.x + a.y) + (a.z + a.w);
-						q += (a.x * a.x + a.y * a.y) + (a.z * a.z + a.w * a.w);
+						float4 a[kLoads];
+						#pragma unroll
+						for (int u = 0; u < kLoads; ++u)
+						{
+							const uint32_t i = i0 + u * kThreads;
+							a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (i < total)
+							{
+								const uint32_t lp = g.d_vpp.div(i);
+								a[u] = ld_stream(reinterpret_cast<const float4 *>(base + lp * entry_stride) + (i - lp * per_plane));
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < kLoads; ++u)
+						{
+							s += (a[u].x + a[u].y) + (a[u].z + a[u].w);
+							q += (a[u].x * a[u].x + a[u].y * a[u].y) + (a[u].z * a[u].z + a[u].w * a[u].w);
+						}
 					}
 					else
 					{
-						const float a = __ldg(plane + v);
-						s += a;
-						q += a * a;
+						float a[kLoads];
+						#pragma unroll
+						for (int u = 0; u < kLoads; ++u)
+						{
+							const uint32_t i = i0 + u * kThreads;
+							a[u] = 0.0F;
+							if (i < total)
+							{
+								const uint32_t lp = g.d_vpp.div(i);
+								a[u] = __ldg(base + lp * entry_stride + (i - lp * per_plane));
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < kLoads; ++u)
+						{
+							s += a[u];
+							q += a[u] * a[u];
+						}
 					}
 				}
 			}
@@ -194,50 +225,7 @@ namespace nnf
 			int add;
 		};
 
-		// Recomputes u = x*mult + add and the activation chain, then carries dy back to du.
-		// dslope_term receives d(out of PReLU) * (in >= 0 ? 0 : in) for the PReLU in the chain (else 0).
-		__device__ __forceinline__ float chain_backward(const act_chain& ch, float u, float dy, float slope, float& dslope_term)
-		{
-			float t[NNF_MAX_ACTS + 1];
-			t[0] = u;
-			#pragma unroll
-			for (int i = 0; i < NNF_MAX_ACTS; ++i)
-				t[i + 1] = (i < ch.n) ? act_fwd_dyn(ch.a[i].kind, t[i], ch.a[i].p0, ch.a[i].p1, slope) : t[i];
-			float g = dy;
-			dslope_term = 0.0F;
-			#pragma unroll
-			for (int i = NNF_MAX_ACTS - 1; i >= 0; --i)
-			{
-				if (i < ch.n)
-				{
-					switch (ch.a[i].kind)
-					{
-					case NNF_ACT_RELU: g = act_bwd<NNF_ACT_RELU>(g, t[i], ch.a[i].p0, 0.0F, 0.0F); break;
-					case NNF_ACT_PRELU:
-						// parametric_rectified_linear_layer_updater_plain.cpp:177-180
-						dslope_term = __fmul_rn(g, (t[i] >= 0.0F ? 0.0F : t[i]));
-						g = act_bwd<NNF_ACT_PRELU>(g, t[i], 0.0F, 0.0F, slope);
-						break;
-					case NNF_ACT_ELU: g = act_bwd<NNF_ACT_ELU>(g, t[i + 1], 0.0F, 0.0F, 0.0F); break;
-					case NNF_ACT_TANH: g = act_bwd<NNF_ACT_TANH>(g, t[i + 1], ch.a[i].p0b, ch.a[i].p1b, 0.0F); break;
-					case NNF_ACT_SIGMOID: g = act_bwd<NNF_ACT_SIGMOID>(g, t[i + 1], 0.0F, 0.0F, 0.0F); break;
-					default: break;
-					}
-				}
-			}
-			return g;
-		}
-
-		__device__ __forceinline__ float chain_slope(const act_chain& ch, uint32_t channel)
-		{
-			float a = 0.0F;
-			#pragma unroll
-			for (int i = 0; i < NNF_MAX_ACTS; ++i)
-				if (i < ch.n && ch.a[i].kind == NNF_ACT_PRELU)
-					a = __ldg(ch.a[i].slope + channel);
-			return a;
-		}
-
+		template <int A0, int A1>
 		__global__ void __launch_bounds__(kThreads) bn_bwd_stats_kernel(double * partial, const bwd_params p, chan_geom g)
 		{
 			__shared__ double s_red[(kThreads / 32) * 3];
@@ -254,7 +242,7 @@ namespace nnf
 			{
 				const float u = __fadd_rn(__fmul_rn(x, mult), add);
 				float term;
-				const float du = chain_backward(p.chain, u, dy, slope, term);
+				const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
 				const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
 				sb += du;
 				sg += du * xhat;
@@ -266,19 +254,44 @@ namespace nnf
 				const uint32_t total = (e1 - e0) * per_plane;
 				const size_t entry_stride = size_t(g.c) * g.hw;
 				const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
-				for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+				for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kThreads * kLoads2)
 				{
-					const uint32_t lp = g.d_vpp.div(i);
-					const uint32_t v = i - lp * per_plane;
-					const size_t off = off0 + lp * entry_stride;
 					if (g.vec)
 					{
-						const float4 a = __ldg(reinterpret_cast<const float4 *>(p.x + off) + v);
-						const float4 d = __ldg(reinterpret_cast<const float4 *>(p.dy + off) + v);
-						element(a.x, d.x); element(a.y, d.y); element(a.z, d.z); element(a.w, d.w);
+						float4 a[kLoads2], d[kLoads2];
+						#pragma unroll
+						for (int u = 0; u < kLoads2; ++u)
+						{
+							const uint32_t i = i0 + u * kThreads;
+							if (i < total)
+							{
+								const uint32_t lp = g.d_vpp.div(i);
+								const size_t off = off0 + lp * entry_stride;
+								a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + off) + (i - lp * per_plane));
+								d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + off) + (i - lp * per_plane));
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < kLoads2; ++u)
+							if (i0 + u * kThreads < total)
+							{
+								element(a[u].x, d[u].x); element(a[u].y, d[u].y); element(a[u].z, d[u].z); element(a[u].w, d[u].w);
+							}
 					}
 					else
-						element(__ldg(p.x + off + v), __ldg(p.dy + off + v));
+					{
+						#pragma unroll
+						for (int u = 0; u < kLoads2; ++u)
+						{
+							const uint32_t i = i0 + u * kThreads;
+							if (i < total)
+							{
+								const uint32_t lp = g.d_vpp.div(i);
+								const size_t off = off0 + lp * entry_stride + (i - lp * per_plane);
+								element(__ldg(p.x + off), __ldg(p.dy + off));
+							}
+						}
+					}
 				}
 			}
 			double acc[3] = {double(sb), double(sg), double(ss)};
@@ -293,6 +306,7 @@ namespace nnf
 		}
 
 		// dx (+)= mult * (du - dbeta/m - xhat*dgamma/m); one CTA per (channel, slice of entries).
+		template <int A0, int A1>
 		__global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const bwd_params p, chan_geom g)
 		{
 			const uint32_t ch = blockIdx.x / g.split;
@@ -320,7 +334,7 @@ namespace nnf
 			{
 				const float u = __fadd_rn(__fmul_rn(x, mult), add);
 				float term;
-				const float du = chain_backward(p.chain, u, dy, slope, term);
+				const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
 				const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
 				const float r = mult * ((du - c2) - xhat * c3);
 				return p.add ? old + r : r;
@@ -331,37 +345,82 @@ namespace nnf
 			const uint32_t total = (e1 - e0) * per_plane;
 			const size_t entry_stride = size_t(g.c) * g.hw;
 			const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
-			for (uint32_t i = threadIdx.x; i < total; i += kThreads)
+			for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kThreads * kLoads2)
 			{
-				const uint32_t lp = g.d_vpp.div(i);
-				const uint32_t v = i - lp * per_plane;
-				const size_t off = off0 + lp * entry_stride;
 				if (g.vec)
 				{
-					const float4 a = ld_stream(reinterpret_cast<const float4 *>(p.x + off) + v);
-					const float4 d = ld_stream(reinterpret_cast<const float4 *>(p.dy + off) + v);
-					float4 o = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-					if (p.add)
-						o = ld_stream(reinterpret_cast<const float4 *>(p.dx + off) + v);
-					o = make_float4(element(a.x, d.x, o.x), element(a.y, d.y, o.y), element(a.z, d.z, o.z), element(a.w, d.w, o.w));
-					st_stream(reinterpret_cast<float4 *>(p.dx + off) + v, o);
+					float4 a[kLoads2], d[kLoads2], o[kLoads2];
+					size_t pos[kLoads2];
+					#pragma unroll
+					for (int u = 0; u < kLoads2; ++u)
+					{
+						const uint32_t i = i0 + u * kThreads;
+						o[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						if (i < total)
+						{
+							const uint32_t lp = g.d_vpp.div(i);
+							pos[u] = off0 + lp * entry_stride + size_t(i - lp * per_plane) * 4;
+							a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos[u]));
+							d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + pos[u]));
+							if (p.add)
+								o[u] = ld_stream(reinterpret_cast<const float4 *>(p.dx + pos[u]));
+						}
+					}
+					#pragma unroll
+					for (int u = 0; u < kLoads2; ++u)
+						if (i0 + u * kThreads < total)
+						{
+							const float4 r = make_float4(element(a[u].x, d[u].x, o[u].x), element(a[u].y, d[u].y, o[u].y),
+								element(a[u].z, d[u].z, o[u].z), element(a[u].w, d[u].w, o[u].w));
+							st_stream(reinterpret_cast<float4 *>(p.dx + pos[u]), r);
+						}
 				}
 				else
 				{
-					const float old = p.add ? p.dx[off + v] : 0.0F;
-					p.dx[off + v] = element(p.x[off + v], p.dy[off + v], old);
+					#pragma unroll
+					for (int u = 0; u < kLoads2; ++u)
+					{
+						const uint32_t i = i0 + u * kThreads;
+						if (i < total)
+						{
+							const uint32_t lp = g.d_vpp.div(i);
+							const size_t off = off0 + lp * entry_stride + (i - lp * per_plane);
+							const float old = p.add ? p.dx[off] : 0.0F;
+							p.dx[off] = element(p.x[off], p.dy[off], old);
+						}
+					}
 				}
 			}
 		}
 
-		int make_chan_geom(chan_geom& g, const char * who, int64_t n, int64_t c, int64_t hw, bool vec_ok)
+		// CTAs of `kernel` that one SM holds at once (queried once per kernel and cached).
+		template <class Kernel>
+		int resident_ctas_per_sm(Kernel kernel)
+		{
+			static int cached = 0;
+			if (cached == 0)
+			{
+				int v = 0;
+				if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, 0) != cudaSuccess || v < 1)
+				{
+					cudaGetLastError();
+					v = 4;
+				}
+				cached = v;
+			}
+			return cached;
+		}
+
+		int make_chan_geom(chan_geom& g, const char * who, int64_t n, int64_t c, int64_t hw, bool vec_ok, int ctas_per_sm)
 		{
 			if (n > 0x7fffffff || c > 0x7fffffff || hw > 0x7fffffff || n * hw > kMaxElemsPerLaunch)
 				return set_error(NNF_ERR_UNSUPPORTED, "%s: n*hw must stay below 2^31 per channel", who);
 			g.n = (uint32_t)n; g.c = (uint32_t)c; g.hw = (uint32_t)hw;
 			g.vec = (vec_ok && (hw % 4 == 0)) ? 1 : 0;
-			// enough CTAs to fill the machine several times over, but at least ~8K elements per CTA
-			int64_t split = div_up(int64_t(kSmCount) * 8, c);
+			// One wave: as many CTAs as the machine holds at once and no more. A grid slightly larger than
+			// that would run a second, nearly empty wave and double the kernel's duration; with more
+			// channels than resident CTAs there are many waves of equal CTAs and the tail is small.
+			int64_t split = (int64_t(kSmCount) * ctas_per_sm) / c;
 			const int64_t max_by_work = (n * hw) / 8192 > 0 ? (n * hw) / 8192 : 1;
 			if (split > max_by_work) split = max_by_work;
 			if (split > n) split = n;
@@ -403,7 +462,7 @@ extern "C" int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float
 	if (!workspace || workspace_bytes < nnf_bn_train_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_stats: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x));
+	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel));
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
@@ -445,18 +504,10 @@ namespace
 		int st = make_chain(p.chain, acts, n_acts, true);
 		if (st != NNF_OK)
 			return st;
+		chain_fill_backward_constants(p.chain, acts, n_acts);
 		int prelus = 0;
 		for (int i = 0; i < p.chain.n; ++i)
-		{
 			prelus += p.chain.a[i].kind == NNF_ACT_PRELU;
-			if (p.chain.a[i].kind == NNF_ACT_TANH)
-			{
-				// backward constants (hyperbolic_tangent_layer_updater_plain.cpp:87-88); p1 holds steepness*2
-				const float steepness = acts[i].p1;
-				p.chain.a[i].p0b = 1.0F / acts[i].p0;
-				p.chain.a[i].p1b = steepness * acts[i].p0;
-			}
-		}
 		if (prelus > 1)
 			return set_error(NNF_ERR_UNSUPPORTED, "%s: at most one PReLU per fused chain", who);
 		p.dy = dy; p.x = x; p.gamma = gamma; p.beta = beta; p.saved = saved;
@@ -481,11 +532,17 @@ extern "C" int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float 
 	if (st != NNF_OK)
 		return st;
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy));
+	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(bn_bwd_stats_kernel<-1, 0>));
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
-	bn_bwd_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g);
+	switch (chain_id(p.chain))
+	{
+	case 0: bn_bwd_stats_kernel<NNF_ACT_NONE, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+	case 1: bn_bwd_stats_kernel<NNF_ACT_PRELU, NNF_ACT_ELU><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+	case 2: bn_bwd_stats_kernel<NNF_ACT_RELU, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+	default: bn_bwd_stats_kernel<-1, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+	}
 	st = check_launch("bn_bwd_stats_kernel");
 	if (st != NNF_OK)
 		return st;
@@ -521,10 +578,16 @@ extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const flo
 	p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 	p.add = add_to_destination ? 1 : 0;
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx));
+	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx), resident_ctas_per_sm(bn_bwd_apply_kernel<-1, 0>));
 	if (st != NNF_OK)
 		return st;
-	bn_bwd_apply_kernel<<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g);
+	switch (chain_id(p.chain))
+	{
+	case 0: bn_bwd_apply_kernel<NNF_ACT_NONE, 0><<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g); break;
+	case 1: bn_bwd_apply_kernel<NNF_ACT_PRELU, NNF_ACT_ELU><<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g); break;
+	case 2: bn_bwd_apply_kernel<NNF_ACT_RELU, 0><<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g); break;
+	default: bn_bwd_apply_kernel<-1, 0><<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g); break;
+	}
 	return check_launch("bn_bwd_apply_kernel");
 }
 
@@ -545,7 +608,7 @@ extern "C" int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const 
 	if (!workspace || workspace_bytes < nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_prelu_bwd_weights: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_prelu_bwd_weights_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy));
+	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(prelu_dslope_kernel));
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
@@ -617,7 +680,7 @@ extern "C" int nnf_bn_train_stats_static(nnf_stream_t stream, float * sums, cons
 	if (!sums || !x)
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_stats_static: null pointer");
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_stats_static", n, c, hw, aligned16(x));
+	st = make_chan_geom(g, "nnf_bn_train_stats_static", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel));
 	if (st != NNF_OK)
 		return st;
 	double * scratch = nullptr;

@@ -93,6 +93,33 @@ namespace nnf
 	int run_elementwise(cudaStream_t s, float * y, const float * x, const float * res, float add_alpha,
 		const bn_source& bn, const act_chain& chain, int64_t n, int64_t c, int64_t hw);
 
+	// ---- exp and division at "tolerance" accuracy ---------------------------------------------------
+	// exp(x) = 2^(x*log2 e) on the ex2 unit. The product x*log2(e) is split into its rounded value and
+	// its exact residual (fma), the residual is applied as a first-order correction, so the relative
+	// error stays at the ~2^-22 of ex2.approx for every finite x instead of growing with |x|.
+	// ~8 instructions instead of ~20; the elementwise kernels are instruction-bound with the library expf.
+	__device__ __forceinline__ float fast_exp(float x)
+	{
+		const float kL2eHi = 1.44269502162933349609375F;
+		const float kL2eLo = 1.925963033500011e-08F;
+		const float kLn2 = 0.693147182464599609375F;
+		const float t = __fmul_rn(x, kL2eHi);
+		float r = fmaf(x, kL2eHi, -t);
+		r = fmaf(x, kL2eLo, r);
+		float e;
+		asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+		// Outside +-87 the result is within a few ulp of overflow / already flushed to zero: the
+		// correction is skipped there, because e may be inf or 0 and inf * r is not a number.
+		return (fabsf(x) < 87.0F) ? fmaf(e, __fmul_rn(r, kLn2), e) : e;
+	}
+
+	__device__ __forceinline__ float fast_rcp(float x)
+	{
+		float r;
+		asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+		return r;
+	}
+
 	// forward of one activation; `a` = PReLU slope of this element's channel
 	template <int KIND>
 	__device__ __forceinline__ float act_fwd(float v, float p0, float p1, float a)
@@ -102,15 +129,21 @@ namespace nnf
 		else if (KIND == NNF_ACT_PRELU)
 			return __fmul_rn(v, (v >= 0.0F ? 1.0F : a));             // parametric_rectified_linear_layer_tester_plain.cpp:66
 		else if (KIND == NNF_ACT_ELU)
-			return v >= 0.0F ? v : __fsub_rn(expf(v), 1.0F);         // exponential_linear_layer_tester_plain.cpp:52
+			return v >= 0.0F ? v : __fsub_rn(fast_exp(v), 1.0F);     // exponential_linear_layer_tester_plain.cpp:52
 		else if (KIND == NNF_ACT_TANH)
 		{
 			// p0 = scale, p1 = steepness*2 (hyperbolic_tangent_layer_tester_plain.cpp:44-57)
-			const float e = expf(__fmul_rn(v, p1));
-			return __fmul_rn(__fdiv_rn(__fsub_rn(e, 1.0F), __fadd_rn(e, 1.0F)), p0);
+			const float e = fast_exp(__fmul_rn(v, p1));
+			const float ep1 = __fadd_rn(e, 1.0F);
+			float q = __fmul_rn(__fsub_rn(e, 1.0F), fast_rcp(ep1));
+			// the approximate reciprocal flushes to zero above 2^126 where the quotient is exactly 1;
+			// e = inf still yields NaN like (inf-1)/(inf+1) does on the CPU
+			if (ep1 > 8.0e37F && ep1 < __int_as_float(0x7f800000))
+				q = 1.0F;
+			return __fmul_rn(q, p0);
 		}
 		else if (KIND == NNF_ACT_SIGMOID)
-			return __fdiv_rn(1.0F, __fadd_rn(expf(-v), 1.0F));       // sigmoid_layer_tester_plain.cpp:51
+			return fast_rcp(__fadd_rn(fast_exp(-v), 1.0F));          // sigmoid_layer_tester_plain.cpp:51
 		else
 			return v;
 	}
@@ -148,6 +181,136 @@ namespace nnf
 			return __fmul_rn(dy, __fmul_rn(t, __fsub_rn(1.0F, t)));   // sigmoid_layer_updater_plain.cpp:88-100
 		else
 			return dy;
+	}
+
+	// ---- activation chains (shared by the training batch-norm kernels) ---------------------------
+	// Backward through one activation. t_in / t_out are its input and output; the plain backend gates
+	// ReLU/PReLU on the input and derives ELU/TanH/Sigmoid from the output.
+	template <int KIND>
+	__device__ __forceinline__ float act_bwd_one(const act_param& a, float g, float t_in, float t_out, float slope, float& dslope_term)
+	{
+		if (KIND == NNF_ACT_RELU)
+			return act_bwd<NNF_ACT_RELU>(g, t_in, a.p0, 0.0F, 0.0F);
+		else if (KIND == NNF_ACT_PRELU)
+		{
+			// parametric_rectified_linear_layer_updater_plain.cpp:177-180
+			dslope_term = __fmul_rn(g, (t_in >= 0.0F ? 0.0F : t_in));
+			return act_bwd<NNF_ACT_PRELU>(g, t_in, 0.0F, 0.0F, slope);
+		}
+		else if (KIND == NNF_ACT_ELU)
+			return act_bwd<NNF_ACT_ELU>(g, t_out, 0.0F, 0.0F, 0.0F);
+		else if (KIND == NNF_ACT_TANH)
+			return act_bwd<NNF_ACT_TANH>(g, t_out, a.p0b, a.p1b, 0.0F);
+		else if (KIND == NNF_ACT_SIGMOID)
+			return act_bwd<NNF_ACT_SIGMOID>(g, t_out, 0.0F, 0.0F, 0.0F);
+		else
+			return g;
+	}
+
+	__device__ __forceinline__ float act_bwd_one_dyn(const act_param& a, float g, float t_in, float t_out, float slope, float& dslope_term)
+	{
+		switch (a.kind)
+		{
+		case NNF_ACT_RELU: return act_bwd_one<NNF_ACT_RELU>(a, g, t_in, t_out, slope, dslope_term);
+		case NNF_ACT_PRELU: return act_bwd_one<NNF_ACT_PRELU>(a, g, t_in, t_out, slope, dslope_term);
+		case NNF_ACT_ELU: return act_bwd_one<NNF_ACT_ELU>(a, g, t_in, t_out, slope, dslope_term);
+		case NNF_ACT_TANH: return act_bwd_one<NNF_ACT_TANH>(a, g, t_in, t_out, slope, dslope_term);
+		case NNF_ACT_SIGMOID: return act_bwd_one<NNF_ACT_SIGMOID>(a, g, t_in, t_out, slope, dslope_term);
+		default: return g;
+		}
+	}
+
+	// Recomputes the activation chain from u = x*mult + add, then carries dy back to du.
+	// dslope_term receives d(out of PReLU) * (in >= 0 ? 0 : in) for the PReLU in the chain (else 0).
+	// A0 >= 0: the chain is known at compile time (A0 then A1, 0 = none); A0 < 0: read from `ch`.
+	template <int A0, int A1>
+	__device__ __forceinline__ float chain_backward(const act_chain& ch, float u, float dy, float slope, float& dslope_term)
+	{
+		dslope_term = 0.0F;
+		if (A0 >= 0)
+		{
+			const float t1 = act_fwd<(A0 >= 0 ? A0 : 0)>(u, ch.a[0].p0, ch.a[0].p1, slope);
+			float g = dy;
+			if (A1 > 0)
+			{
+				const float t2 = act_fwd<(A1 > 0 ? A1 : 0)>(t1, ch.a[1].p0, ch.a[1].p1, slope);
+				g = act_bwd_one<(A1 > 0 ? A1 : 0)>(ch.a[1], g, t1, t2, slope, dslope_term);
+			}
+			return act_bwd_one<(A0 >= 0 ? A0 : 0)>(ch.a[0], g, u, t1, slope, dslope_term);
+		}
+		float t[NNF_MAX_ACTS + 1];
+		t[0] = u;
+		#pragma unroll
+		for (int i = 0; i < NNF_MAX_ACTS; ++i)
+			t[i + 1] = (i < ch.n) ? act_fwd_dyn(ch.a[i].kind, t[i], ch.a[i].p0, ch.a[i].p1, slope) : t[i];
+		float g = dy;
+		#pragma unroll
+		for (int i = NNF_MAX_ACTS - 1; i >= 0; --i)
+			if (i < ch.n)
+				g = act_bwd_one_dyn(ch.a[i], g, t[i], t[i + 1], slope, dslope_term);
+		return g;
+	}
+
+	__device__ __forceinline__ float chain_slope(const act_chain& ch, uint32_t channel)
+	{
+		float a = 0.0F;
+		#pragma unroll
+		for (int i = 0; i < NNF_MAX_ACTS; ++i)
+			if (i < ch.n && ch.a[i].kind == NNF_ACT_PRELU)
+				a = __ldg(ch.a[i].slope + channel);
+		return a;
+	}
+
+
+	// forward through the chain; A0 >= 0: compiled-in kinds (A0 then A1, 0 = none), else read from `ch`
+	template <int A0, int A1>
+	__device__ __forceinline__ float chain_forward(const act_chain& ch, float v, float slope)
+	{
+		if (A0 >= 0)
+		{
+			v = act_fwd<(A0 >= 0 ? A0 : 0)>(v, ch.a[0].p0, ch.a[0].p1, slope);
+			if (A1 > 0)
+				v = act_fwd<(A1 > 0 ? A1 : 0)>(v, ch.a[1].p0, ch.a[1].p1, slope);
+			return v;
+		}
+		else
+		{
+			#pragma unroll
+			for (int i = 0; i < NNF_MAX_ACTS; ++i)
+				if (i < ch.n)
+					v = act_fwd_dyn(ch.a[i].kind, v, ch.a[i].p0, ch.a[i].p1, slope);
+			return v;
+		}
+	}
+
+	// Chains with a compiled-in fast path: 0 = none, 1 = PReLU then ELU, 2 = ReLU; -1 = generic.
+	inline int chain_id(const act_chain& ch)
+	{
+		if (ch.n == 0)
+			return 0;
+		if (ch.n == 2 && ch.a[0].kind == NNF_ACT_PRELU && ch.a[1].kind == NNF_ACT_ELU)
+			return 1;
+		if (ch.n == 1 && ch.a[0].kind == NNF_ACT_RELU)
+			return 2;
+		return -1;
+	}
+
+	// Fills the backward-pass constants of a chain (TanH) from the caller's descriptors.
+	inline void chain_fill_backward_constants(act_chain& chain, const nnf_act * acts, int n_acts)
+	{
+		int j = 0;
+		for (int i = 0; i < n_acts && j < chain.n; ++i)
+		{
+			if (acts[i].kind == NNF_ACT_NONE)
+				continue;
+			if (acts[i].kind == NNF_ACT_TANH)
+			{
+				// hyperbolic_tangent_layer_updater_plain.cpp:87-88
+				chain.a[j].p0b = 1.0F / acts[i].p0;
+				chain.a[j].p1b = acts[i].p1 * acts[i].p0;
+			}
+			++j;
+		}
 	}
 
 	// ---- memory access helpers -----------------------------------------------------------------

@@ -8,7 +8,7 @@
 //             consecutive pixels (coalesced 128-byte rows per channel), column kept in registers
 //             (C <= 32), else a shared-memory tile [C][32 pixels] per CTA.
 // Arithmetic follows nnforge/plain/softmax_layer_tester_plain.cpp:65-88 (max seeded with -1e37,
-// expf(x - max), multiply by the rounded reciprocal of the sum) and
+// fast_exp(x - max), multiply by the rounded reciprocal of the sum) and
 // nnforge/plain/softmax_layer_updater_plain.cpp:139-160; only the order of the sum over C differs
 // (tree instead of ascending), which stays inside the 1e-5 relative tolerance.
 #include "nnf_common.cuh"
@@ -52,21 +52,24 @@ namespace nnf
 				float v[PER_LANE];
 				if (!BACKWARD)
 				{
-					float m = kMaxSeed;
+					// all loads first, so that they are in flight together; the dependent max chain follows
 					#pragma unroll
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
 						v[j] = idx < c ? ld_stream(a + idx) : kMaxSeed;
-						m = ref_max(m, v[j]);
 					}
+					float m = kMaxSeed;
+					#pragma unroll
+					for (int j = 0; j < PER_LANE; ++j)
+						m = ref_max(m, v[j]);
 					m = warp_max(m);
 					float s = 0.0F;
 					#pragma unroll
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						v[j] = idx < c ? expf(__fsub_rn(v[j], m)) : 0.0F;
+						v[j] = idx < c ? fast_exp(__fsub_rn(v[j], m)) : 0.0F;
 						s = __fadd_rn(s, v[j]);
 					}
 					s = warp_sum(s);
@@ -146,7 +149,7 @@ namespace nnf
 					float s = 0.0F;
 					for (int i = threadIdx.x; i < c; i += blockDim.x)
 					{
-						const float e = expf(__fsub_rn(IN_SMEM ? s_row[i] : a[i], m));
+						const float e = fast_exp(__fsub_rn(IN_SMEM ? s_row[i] : a[i], m));
 						if (IN_SMEM)
 							s_row[i] = e;
 						s = __fadd_rn(s, e);
@@ -155,7 +158,7 @@ namespace nnf
 					const float mult = __fdiv_rn(1.0F, s);
 					for (int i = threadIdx.x; i < c; i += blockDim.x)
 					{
-						const float e = IN_SMEM ? s_row[i] : expf(__fsub_rn(a[i], m));
+						const float e = IN_SMEM ? s_row[i] : fast_exp(__fsub_rn(a[i], m));
 						o[i] = __fmul_rn(e, mult);
 					}
 				}
@@ -190,23 +193,20 @@ namespace nnf
 				float v[CMAX];
 				if (!BACKWARD)
 				{
+					#pragma unroll
+					for (int f = 0; f < CMAX; ++f)
+						v[f] = (f < c) ? ld_stream(in0 + base + int64_t(f) * hw) : kMaxSeed;
 					float m = kMaxSeed;
 					#pragma unroll
 					for (int f = 0; f < CMAX; ++f)
-					{
-						if (f < c)
-						{
-							v[f] = ld_stream(in0 + base + int64_t(f) * hw);
-							m = ref_max(m, v[f]);
-						}
-					}
+						m = ref_max(m, v[f]);
 					float s = 0.0F;
 					#pragma unroll
 					for (int f = 0; f < CMAX; ++f)
 					{
 						if (f < c)
 						{
-							v[f] = expf(__fsub_rn(v[f], m));
+							v[f] = fast_exp(__fsub_rn(v[f], m));
 							s = __fadd_rn(s, v[f]); // ascending c: same order as the plain backend
 						}
 					}
@@ -284,7 +284,7 @@ namespace nnf
 					for (int f = grp; f < c; f += 8)
 					{
 						const float x = IN_SMEM ? s_tile[f * 32 + lane] : (valid ? in0[base + int64_t(f) * hw] : 0.0F);
-						const float e = expf(__fsub_rn(x, m));
+						const float e = fast_exp(__fsub_rn(x, m));
 						if (IN_SMEM)
 							s_tile[f * 32 + lane] = e;
 						s = __fadd_rn(s, e);
@@ -299,7 +299,7 @@ namespace nnf
 					if (valid)
 						for (int f = grp; f < c; f += 8)
 						{
-							const float e = IN_SMEM ? s_tile[f * 32 + lane] : expf(__fsub_rn(in0[base + int64_t(f) * hw], m));
+							const float e = IN_SMEM ? s_tile[f * 32 + lane] : fast_exp(__fsub_rn(in0[base + int64_t(f) * hw], m));
 							out[base + int64_t(f) * hw] = __fmul_rn(e, mult);
 						}
 					__syncthreads();

@@ -298,7 +298,7 @@ def test_bn_add_relu_maxpool(capi, oracle, c, hw, round_up):
     assert_bits_equal(host(dx), dx_want, "fused dx")
 
 
-TRAIN_SHAPES = [(16, 32, 28, 28), (5, 3, 7, 7), (4, 6, 1, 1), (3, 2, 5, 3), (64, 8, 14, 14)]
+TRAIN_SHAPES = [(16, 32, 28, 28), (5, 3, 7, 7), (4, 6, 1, 1), (3, 2, 5, 3), (64, 8, 14, 14), (256, 40, 28, 28), (3, 5, 4, 4), (37, 3, 8, 8)]
 TRAIN_CHAINS = [("prelu", "elu"), (), ("relu0",), ("tanh",), ("sigmoid",), ("elu",), ("relu01", "prelu")]
 
 
@@ -337,7 +337,7 @@ def train_oracle(oracle, x, dy, gamma, beta, slope, chain, eps, shards=1):
     return y, saved, dx, db, dg, dslope
 
 
-def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1):
+def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1, fused=False):
     """Same step through the C ABI; with shards > 1 the batch is split and the 2C-float sums are
     added across shards on the host, standing in for the all-reduce."""
     n, c = x.shape[0], x.shape[1]
@@ -360,16 +360,34 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1):
     for xk in xs:
         yk = torch.empty_like(xk)
         saved = torch.empty(2 * c, device="cuda")
-        capi.bn_train_apply_act(yk, saved, xk, gd, bd, total, m, eps, acts)
+        if fused:
+            # single-GPU entry point: single-pass cluster kernel where the channel slab fits, else two kernels
+            fsums = torch.empty(2 * c, device="cuda")
+            capi.bn_train_fwd(yk, saved, fsums, xk, gd, bd, eps, acts, workspace=ws)
+            assert capi.fused_error_check() == 0
+            assert_close(host(fsums), host(total), "sums written by the fused forward")
+        else:
+            capi.bn_train_apply_act(yk, saved, xk, gd, bd, total, m, eps, acts)
         ys.append(yk)
+    grads = {k: torch.zeros(c, device="cuda") for k in ("gamma", "beta", "slope", "mean", "invsigma")}
+    run_mean, run_inv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    if fused:
+        dxk, bsk = torch.empty_like(xs[0]), torch.empty(3 * c, device="cuda")
+        capi.bn_train_bwd(dxk, bsk, dys[0], xs[0], gd, bd, saved, acts, grad_gamma=grads["gamma"], grad_beta=grads["beta"],
+                          grad_mean=grads["mean"], grad_invsigma=grads["invsigma"], grad_slope=grads["slope"] if "prelu" in chain else None,
+                          mean=run_mean, invsigma=run_inv, entry_count=float(n), workspace=ws)
+        assert capi.fused_error_check() == 0
+        # accumulate=True on top of the first result must double it
+        dx2 = dxk.clone()
+        capi.bn_train_bwd(dx2, bsk, dys[0], xs[0], gd, bd, saved, acts, add_to_destination=True, workspace=ws)
+        assert_close(host(dx2), 2.0 * host(dxk).astype(np.float64), "fused backward accumulate", atol=1e-5)
+        return (np.concatenate([host(t) for t in ys]), host(saved), host(dxk), {k: host(v) for k, v in grads.items()})
     bs = []
     for xk, dk in zip(xs, dys):
         t = torch.empty(3 * c, device="cuda")
         capi.bn_train_bwd_stats(t, dk, xk, gd, bd, saved, acts, ws)
         bs.append(t)
     gsum = torch.stack(bs).sum(0)[:2 * c].contiguous()
-    grads = {k: torch.zeros(c, device="cuda") for k in ("gamma", "beta", "slope", "mean", "invsigma")}
-    run_mean, run_inv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
     dxs = []
     for xk, dk, bk in zip(xs, dys, bs):
         dxk = torch.empty_like(xk)
@@ -383,8 +401,10 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1):
 
 @pytest.mark.parametrize("shape", TRAIN_SHAPES)
 @pytest.mark.parametrize("chain", TRAIN_CHAINS)
-@pytest.mark.parametrize("shards", [1, 2])
+@pytest.mark.parametrize("shards", [1, 2, "fused"])
 def test_bn_train(capi, oracle, shape, chain, shards):
+    fused = shards == "fused"
+    shards = 1 if fused else shards
     if shards > shape[0]:
         pytest.skip("fewer entries than shards")
     g = synth.rng(2, salt=sum(shape) + len(chain))
@@ -395,7 +415,7 @@ def test_bn_train(capi, oracle, shape, chain, shards):
     slope = synth.uniform(g, c, 0.0, 0.3)
     eps = 1e-5
     y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, eps)
-    y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards)
+    y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards, fused)
     assert_close(saved, saved_w, "saved mean/invstd")
     assert_close(y, y_w, "train fwd %s" % (chain,), atol=2e-6)
     m = x.size // c
