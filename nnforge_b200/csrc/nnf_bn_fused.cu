@@ -101,6 +101,13 @@ namespace nnf
 			return v;
 		}
 
+		__device__ __forceinline__ unsigned long long global_timer()
+		{
+			unsigned long long t;
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+			return t;
+		}
+
 		struct fused_params
 		{
 			const float * x;
@@ -125,13 +132,20 @@ namespace nnf
 			float eps;
 			int * error;             // raised when a bounded wait ran out
 			unsigned long long * trace; // tuning aid (normally null): per CTA and iteration, 5 globaltimer stamps
+			uint32_t stagger_ns;     // odd clusters start this much later, so that clusters run out of phase
 		};
 
-		__device__ __forceinline__ unsigned long long global_timer()
+		// Clusters that all start together stay in lockstep (every channel costs the same), so HBM sees
+		// alternating bursts of loads and stores with idle gaps in between. Delaying every other cluster by
+		// about half an iteration keeps the two halves out of phase for the whole kernel.
+		__device__ __forceinline__ void stagger_start(uint32_t cluster_id, uint32_t ns)
 		{
-			unsigned long long t;
-			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-			return t;
+			if ((cluster_id & 1) && ns)
+			{
+				const unsigned long long t0 = global_timer();
+				for (int i = 0; i < 4096 && global_timer() - t0 < ns; ++i)
+					__nanosleep(200);
+			}
 		}
 
 		// Block-wide sums in double; every thread returns with the totals (through shared memory).
@@ -201,6 +215,7 @@ namespace nnf
 					bulk_load(dst + size_t(pl) * p.hw, p.x + (size_t(e0 + pl) * p.c + ch) * p.hw, plane_bytes, &s_bar[b]);
 			};
 
+			stagger_start(cluster_id, p.stagger_ns);
 			if (threadIdx.x < 32 && cluster_id < p.c)
 				issue_load(cluster_id, 0);
 
@@ -319,6 +334,7 @@ namespace nnf
 			const uint32_t vpp = p.hw >> 2;
 			const uint32_t nvec = np * vpp;
 			constexpr int kU = 2;
+			stagger_start(cluster_id, p.stagger_ns);
 
 			uint32_t it = 0;
 			for (uint32_t ch = cluster_id; ch < p.c; ch += nclusters, ++it)
@@ -633,6 +649,7 @@ extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, f
 	p.count = double(n) * double(hw);
 	p.eps = eps;
 	p.error = error_word();
+	p.stagger_ns = getenv("NNF_FUSED_STAGGER_NS") ? (uint32_t)atoi(getenv("NNF_FUSED_STAGGER_NS")) : 0;
 	{
 		const char * t = getenv("NNF_FUSED_TRACE"); // tuning aid: address of a device buffer, as a decimal number
 		p.trace = t ? reinterpret_cast<unsigned long long *>(strtoull(t, nullptr, 10)) : nullptr;
@@ -713,5 +730,6 @@ extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, 
 	p.d_vpp = fastdiv((uint32_t)(hw / 4));
 	p.count = double(n) * double(hw);
 	p.error = error_word();
+	p.stagger_ns = getenv("NNF_FUSED_STAGGER_NS") ? (uint32_t)atoi(getenv("NNF_FUSED_STAGGER_NS")) : 0;
 	return launch_fused(kernel, plan, p, (cudaStream_t)stream, "bn_train_bwd_cluster_kernel");
 }

@@ -15,6 +15,7 @@
 #include "nnf_common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace nnf
 {
@@ -411,7 +412,7 @@ namespace nnf
 			return cached;
 		}
 
-		int make_chan_geom(chan_geom& g, const char * who, int64_t n, int64_t c, int64_t hw, bool vec_ok, int ctas_per_sm)
+		int make_chan_geom(chan_geom& g, const char * who, int64_t n, int64_t c, int64_t hw, bool vec_ok, int ctas_per_sm, int waves)
 		{
 			if (n > 0x7fffffff || c > 0x7fffffff || hw > 0x7fffffff || n * hw > kMaxElemsPerLaunch)
 				return set_error(NNF_ERR_UNSUPPORTED, "%s: n*hw must stay below 2^31 per channel", who);
@@ -420,7 +421,14 @@ namespace nnf
 			// One wave: as many CTAs as the machine holds at once and no more. A grid slightly larger than
 			// that would run a second, nearly empty wave and double the kernel's duration; with more
 			// channels than resident CTAs there are many waves of equal CTAs and the tail is small.
-			int64_t split = (int64_t(kSmCount) * ctas_per_sm) / c;
+			// `waves` resident waves of CTAs. Measured on B200 (x[256,256,28,28]): the reducing kernels are
+			// best with 1-2 waves (each CTA ends with a block reduction and a partial-sum store), the
+			// streaming backward-apply kernel with 8 (95% of the measured copy bandwidth against 88% with
+			// one wave: CTAs that start at different times mix their loads and stores instead of moving in
+			// lockstep through load / compute / store phases).
+			if (getenv("NNF_CH_WAVES")) // tuning aid
+				waves = atoi(getenv("NNF_CH_WAVES"));
+			int64_t split = (int64_t(kSmCount) * ctas_per_sm * (waves < 1 ? 1 : waves)) / c;
 			const int64_t max_by_work = (n * hw) / 8192 > 0 ? (n * hw) / 8192 : 1;
 			if (split > max_by_work) split = max_by_work;
 			if (split > n) split = n;
@@ -462,7 +470,7 @@ extern "C" int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float
 	if (!workspace || workspace_bytes < nnf_bn_train_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_stats: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel));
+	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel), 1);
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
@@ -532,7 +540,7 @@ extern "C" int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float 
 	if (st != NNF_OK)
 		return st;
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(bn_bwd_stats_kernel<-1, 0>));
+	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(bn_bwd_stats_kernel<-1, 0>), 2);
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
@@ -578,7 +586,7 @@ extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const flo
 	p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 	p.add = add_to_destination ? 1 : 0;
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx), resident_ctas_per_sm(bn_bwd_apply_kernel<-1, 0>));
+	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx), resident_ctas_per_sm(bn_bwd_apply_kernel<-1, 0>), 8);
 	if (st != NNF_OK)
 		return st;
 	switch (chain_id(p.chain))
@@ -608,7 +616,7 @@ extern "C" int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const 
 	if (!workspace || workspace_bytes < nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_prelu_bwd_weights: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_prelu_bwd_weights_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(prelu_dslope_kernel));
+	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(prelu_dslope_kernel), 1);
 	if (st != NNF_OK)
 		return st;
 	cudaStream_t s = (cudaStream_t)stream;
@@ -680,7 +688,7 @@ extern "C" int nnf_bn_train_stats_static(nnf_stream_t stream, float * sums, cons
 	if (!sums || !x)
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_stats_static: null pointer");
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_stats_static", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel));
+	st = make_chan_geom(g, "nnf_bn_train_stats_static", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel), 1);
 	if (st != NNF_OK)
 		return st;
 	double * scratch = nullptr;

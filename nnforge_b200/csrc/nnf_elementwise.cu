@@ -4,6 +4,8 @@
 // store. HBM-bound: algorithmic bytes per element = 4 * (inputs + outputs).
 #include "nnf_common.cuh"
 
+#include <stdlib.h>
+
 namespace nnf
 {
 	namespace
@@ -31,73 +33,56 @@ namespace nnf
 			uint32_t c;
 			fastdiv hw;
 			fastdiv cdiv;
+			const float * slope;    // the chain's PReLU slopes, or null
 			int need_channel;       // per-channel parameters are used
 			int smem_params;        // mult/add staged in shared memory
 			act_chain chain;
 		};
 
-		template <int A0, int A1>
-		__device__ __forceinline__ float apply_chain(const act_chain& ch, float v, uint32_t channel)
+		// Per-vector parameters: fetched once per 128-bit vector (MODE 0) or per element (MODE 1/2) and
+		// kept in registers, so that the per-element work is only the arithmetic itself.
+		struct elem_params
 		{
-			if (A0 >= 0)
+			float mult, add, slope;
+		};
+
+		__device__ __forceinline__ elem_params fetch_params(const ew_params& p, const float * s_mult, const float * s_add, uint32_t e)
+		{
+			elem_params q;
+			q.mult = 1.0F; q.add = 0.0F; q.slope = 0.0F;
+			if (p.need_channel)
 			{
-				// statically known chain
-				float a = 0.0F;
-				if (A0 == NNF_ACT_PRELU)
-					a = __ldg(ch.a[0].slope + channel);
-				v = act_fwd<A0>(v, ch.a[0].p0, ch.a[0].p1, a);
-				if (A1 > 0)
+				const uint32_t plane = p.hw.div(e);
+				const uint32_t channel = plane - p.cdiv.div(plane) * p.c;
+				if (p.gamma)
 				{
-					float a1 = 0.0F;
-					if (A1 == NNF_ACT_PRELU)
-						a1 = __ldg(ch.a[1].slope + channel);
-					v = act_fwd<(A1 > 0 ? A1 : 0)>(v, ch.a[1].p0, ch.a[1].p1, a1);
-				}
-				return v;
-			}
-			else
-			{
-				#pragma unroll
-				for (int i = 0; i < NNF_MAX_ACTS; ++i)
-				{
-					if (i < ch.n)
+					if (p.smem_params)
 					{
-						float a = 0.0F;
-						if (ch.a[i].kind == NNF_ACT_PRELU)
-							a = __ldg(ch.a[i].slope + channel);
-						v = act_fwd_dyn(ch.a[i].kind, v, ch.a[i].p0, ch.a[i].p1, a);
+						q.mult = s_mult[channel];
+						q.add = s_add[channel];
+					}
+					else
+					{
+						q.mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+						q.add = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(q.mult, __ldg(p.mean + channel)));
 					}
 				}
-				return v;
+				if (p.slope)
+					q.slope = __ldg(p.slope + channel);
 			}
+			return q;
 		}
 
 		// One element: batch norm -> residual add -> activations, in the plain backend's operation order.
 		template <int A0, int A1>
-		__device__ __forceinline__ float ew_element(const ew_params& p, const float * s_mult, const float * s_add, float x, float r, uint32_t channel)
+		__device__ __forceinline__ float ew_element(const ew_params& p, bool has_bn, bool has_res, const elem_params& q, float x, float r)
 		{
 			float t = x;
-			if (p.gamma)
-			{
-				float mult, add;
-				if (p.smem_params)
-				{
-					mult = s_mult[channel];
-					add = s_add[channel];
-				}
-				else
-				{
-					mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
-					add = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(mult, __ldg(p.mean + channel)));
-				}
-				t = __fadd_rn(__fmul_rn(x, mult), add); // batch_norm_layer_tester_plain.cpp:70
-			}
-			if (p.res)
-			{
-				// add_layer_tester_plain.cpp:57-60: the accumulator starts at +0.0f
-				t = __fmul_rn(__fadd_rn(__fadd_rn(0.0F, t), r), p.add_alpha);
-			}
-			return apply_chain<A0, A1>(p.chain, t, channel);
+			if (has_bn)
+				t = __fadd_rn(__fmul_rn(x, q.mult), q.add); // batch_norm_layer_tester_plain.cpp:70
+			if (has_res)
+				t = __fmul_rn(__fadd_rn(__fadd_rn(0.0F, t), r), p.add_alpha); // add_layer_tester_plain.cpp:57-60: the accumulator starts at +0.0f
+			return chain_forward<A0, A1>(p.chain, t, q.slope);
 		}
 
 		// MODE 0: 128-bit accesses, one channel per vector (hw % 4 == 0, or no per-channel parameters)
@@ -109,7 +94,9 @@ namespace nnf
 			extern __shared__ float s_params[];
 			float * s_mult = s_params;
 			float * s_add = s_params + p.c;
-			if (p.gamma && p.smem_params)
+			const bool has_bn = p.gamma != nullptr;
+			const bool has_res = p.res != nullptr;
+			if (has_bn && p.smem_params)
 			{
 				for (uint32_t ch = threadIdx.x; ch < p.c; ch += kThreads)
 				{
@@ -146,14 +133,9 @@ namespace nnf
 				const uint32_t stride = gridDim.x * kThreads;
 				for (uint32_t e = blockIdx.x * kThreads + threadIdx.x; e < p.count; e += stride)
 				{
-					uint32_t channel = 0;
-					if (p.need_channel)
-					{
-						const uint32_t plane = p.hw.div(e);
-						channel = plane - p.cdiv.div(plane) * p.c;
-					}
-					const float r = p.res ? ld_stream(p.res + e) : 0.0F;
-					st_stream(p.y + e, ew_element<A0, A1>(p, s_mult, s_add, ld_stream(p.x + e), r, channel));
+					const elem_params q = fetch_params(p, s_mult, s_add, e);
+					const float r = has_res ? ld_stream(p.res + e) : 0.0F;
+					st_stream(p.y + e, ew_element<A0, A1>(p, has_bn, has_res, q, ld_stream(p.x + e), r));
 				}
 				return;
 			}
@@ -173,10 +155,11 @@ namespace nnf
 				for (int j = 0; j < kUnroll; ++j)
 				{
 					const uint32_t v = v0 + j * kThreads;
+					rv[j] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
 					if (v < nvec)
 					{
 						xv[j] = ld_stream(x4 + v);
-						if (p.res)
+						if (has_res)
 							rv[j] = ld_stream(r4 + v);
 					}
 				}
@@ -187,36 +170,23 @@ namespace nnf
 					if (v < nvec)
 					{
 						const uint32_t e = v << 2;
-						float xin[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
-						float rin[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-						if (p.res)
-						{
-							rin[0] = rv[j].x; rin[1] = rv[j].y; rin[2] = rv[j].z; rin[3] = rv[j].w;
-						}
-						float out[4];
+						float4 o;
 						if (MODE == 0)
 						{
-							uint32_t channel = 0;
-							if (p.need_channel)
-							{
-								const uint32_t plane = p.hw.div(e);
-								channel = plane - p.cdiv.div(plane) * p.c;
-							}
-							#pragma unroll
-							for (int k = 0; k < 4; ++k)
-								out[k] = ew_element<A0, A1>(p, s_mult, s_add, xin[k], rin[k], channel);
+							const elem_params q = fetch_params(p, s_mult, s_add, e);
+							o.x = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].x, rv[j].x);
+							o.y = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].y, rv[j].y);
+							o.z = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].z, rv[j].z);
+							o.w = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].w, rv[j].w);
 						}
 						else
 						{
-							#pragma unroll
-							for (int k = 0; k < 4; ++k)
-							{
-								const uint32_t plane = p.hw.div(e + k);
-								const uint32_t channel = plane - p.cdiv.div(plane) * p.c;
-								out[k] = ew_element<A0, A1>(p, s_mult, s_add, xin[k], rin[k], channel);
-							}
+							o.x = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e), xv[j].x, rv[j].x);
+							o.y = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 1), xv[j].y, rv[j].y);
+							o.z = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 2), xv[j].z, rv[j].z);
+							o.w = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 3), xv[j].w, rv[j].w);
 						}
-						st_stream(y4 + v, make_float4(out[0], out[1], out[2], out[3]));
+						st_stream(y4 + v, o);
 					}
 				}
 			}
@@ -226,23 +196,45 @@ namespace nnf
 			if (blockIdx.x == 0 && tail0 + threadIdx.x < p.count)
 			{
 				const uint32_t e = tail0 + threadIdx.x;
-				uint32_t channel = 0;
-				if (p.need_channel)
-				{
-					const uint32_t plane = p.hw.div(e);
-					channel = plane - p.cdiv.div(plane) * p.c;
-				}
-				const float r = p.res ? p.res[e] : 0.0F;
-				p.y[e] = ew_element<A0, A1>(p, s_mult, s_add, p.x[e], r, channel);
+				const elem_params q = fetch_params(p, s_mult, s_add, e);
+				const float r = has_res ? p.res[e] : 0.0F;
+				p.y[e] = ew_element<A0, A1>(p, has_bn, has_res, q, p.x[e], r);
 			}
 		}
 
+		// Persistent grid: exactly as many CTAs as the machine holds at once (a grid somewhat larger than
+		// that would run a short second wave with most SMs idle), never more than there are tiles.
+		template <int MODE, int A0, int A1>
+		int resident_grid(size_t smem, int64_t work)
+		{
+			// cached per kernel instantiation and shared-memory size (the size changes with the channel count)
+			static int per_sm = 0;
+			static size_t cached_smem = ~size_t(0);
+			if (per_sm == 0 || cached_smem != smem)
+			{
+				int v = 0;
+				if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, bn_act_kernel<MODE, A0, A1>, kThreads, smem) != cudaSuccess || v < 1)
+				{
+					cudaGetLastError();
+					v = 4;
+				}
+				per_sm = v;
+				cached_smem = smem;
+			}
+			static int waves = 0; // tuning aid: NNF_EW_WAVES = grid size in units of one resident wave
+			if (waves == 0)
+				waves = getenv("NNF_EW_WAVES") ? atoi(getenv("NNF_EW_WAVES")) : 32;
+			const int64_t cap = int64_t(kSmCount) * per_sm * (waves < 1 ? 1 : waves);
+			const int64_t g = work < cap ? work : cap;
+			return g < 1 ? 1 : (int)g;
+		}
+
 		template <int MODE>
-		cudaError_t launch_mode(const ew_params& p, int grid, size_t smem, cudaStream_t s)
+		cudaError_t launch_mode(const ew_params& p, int64_t work, size_t smem, cudaStream_t s)
 		{
 			const int k0 = p.chain.n > 0 ? p.chain.a[0].kind : NNF_ACT_NONE;
 			const int k1 = p.chain.n > 1 ? p.chain.a[1].kind : NNF_ACT_NONE;
-#define NNF_EW_CASE(A0, A1) bn_act_kernel<MODE, A0, A1><<<grid, kThreads, smem, s>>>(p)
+#define NNF_EW_CASE(A0, A1) bn_act_kernel<MODE, A0, A1><<<resident_grid<MODE, A0, A1>(smem, work), kThreads, smem, s>>>(p)
 			if (k1 == NNF_ACT_NONE)
 			{
 				switch (k0)
@@ -263,7 +255,6 @@ namespace nnf
 #undef NNF_EW_CASE
 			return cudaGetLastError();
 		}
-
 	}
 
 	int run_elementwise(cudaStream_t s, float * y, const float * x, const float * res, float add_alpha,
@@ -279,8 +270,15 @@ namespace nnf
 			if (total == 0)
 				return NNF_OK;
 			bool need_channel = gamma != nullptr;
+			const float * slope = nullptr;
 			for (int i = 0; i < chain.n; ++i)
-				need_channel = need_channel || chain.a[i].kind == NNF_ACT_PRELU;
+				if (chain.a[i].kind == NNF_ACT_PRELU)
+				{
+					if (slope)
+						return set_error(NNF_ERR_UNSUPPORTED, "at most one PReLU per fused chain");
+					slope = chain.a[i].slope;
+					need_channel = true;
+				}
 
 			// launches are split at entry boundaries when per-channel parameters are in play (so that
 			// plane % C stays valid) and at multiples of 4 elements otherwise
@@ -308,6 +306,7 @@ namespace nnf
 				p.c = (uint32_t)c;
 				p.hw = fastdiv((uint32_t)hw);
 				p.cdiv = fastdiv((uint32_t)c);
+				p.slope = slope;
 				p.need_channel = need_channel ? 1 : 0;
 				p.smem_params = (gamma && c <= kMaxSmemChannels) ? 1 : 0;
 				if (bn.sums && !p.smem_params)
@@ -317,16 +316,13 @@ namespace nnf
 				const bool vec_ok = aligned16(p.y) && aligned16(p.x) && (!p.res || aligned16(p.res));
 				const int mode = !vec_ok ? 2 : ((!need_channel || (hw % 4 == 0)) ? 0 : 1);
 				const int64_t work = (mode == 2) ? div_up(cnt, kThreads) : div_up(cnt / 4 + 1, kThreads * kUnroll);
-				int64_t grid = work < int64_t(kSmCount) * kCtasPerSm ? work : int64_t(kSmCount) * kCtasPerSm;
-				if (grid < 1)
-					grid = 1;
 				cudaError_t e;
 				if (mode == 0)
-					e = launch_mode<0>(p, (int)grid, smem, s);
+					e = launch_mode<0>(p, work, smem, s);
 				else if (mode == 1)
-					e = launch_mode<1>(p, (int)grid, smem, s);
+					e = launch_mode<1>(p, work, smem, s);
 				else
-					e = launch_mode<2>(p, (int)grid, smem, s);
+					e = launch_mode<2>(p, work, smem, s);
 				if (e != cudaSuccess)
 					return set_error(NNF_ERR_CUDA, "bn_act_kernel launch failed: %s", cudaGetErrorString(e));
 			}

@@ -19,6 +19,8 @@
 // Planes too large for shared memory fall back to direct global-memory kernels.
 #include "nnf_common.cuh"
 
+#include <stdlib.h>
+
 namespace nnf
 {
 	namespace
@@ -53,102 +55,150 @@ namespace nnf
 			int vec_ok;
 		};
 
-		__device__ __forceinline__ float fused_element(const pool_fwd_params& p, float x, float r, uint32_t channel)
-		{
-			float t = x;
-			if (p.gamma)
-			{
-				const float mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
-				const float add = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(mult, __ldg(p.mean + channel)));
-				t = __fadd_rn(__fmul_rn(x, mult), add);
-			}
-			if (p.res)
-				t = __fadd_rn(__fadd_rn(0.0F, t), r); // add layer, alpha = 1: (0 + bn) + residual
-			return t >= 0.0F ? t : __fmul_rn(t, p.slope);
-		}
-
 		// Scans one window of plane `src` (row pitch g.w). Returns the winner and its offset within the plane.
+		// WW/WH > 0: window extents known at compile time (fully unrolled); CLIP: the window may stick out
+		// of the input (round-up) and is clipped. The scan order (x fastest) and the strict compare are the
+		// plain backend's (max_subsampling_layer_updater_plain.cpp:146-159).
+		template <int WW, int WH, bool CLIP>
 		__device__ __forceinline__ void scan_window(const pool_geom& g, const float * src, uint32_t oy, uint32_t ox, float& best, uint32_t& best_off)
 		{
+			const int win_w = WW ? WW : g.win_w, win_h = WH ? WH : g.win_h;
 			const uint32_t iy0 = oy * g.sh, ix0 = ox * g.sw;
-			best = g.is_min ? 1.0e37F : -1.0e37F;
-			best_off = iy0 * g.w + ix0;
-			bool first = true;
-			for (int ky = 0; ky < g.win_h; ++ky)
+			const uint32_t off0 = iy0 * g.w + ix0;
+			best = src[off0]; // the first element always seeds the result
+			best_off = off0;
+			#pragma unroll
+			for (int ky = 0; ky < win_h; ++ky)
 			{
-				const uint32_t iy = iy0 + ky;
-				if (iy >= g.h)
+				if (CLIP && iy0 + ky >= g.h)
 					break;
-				for (int kx = 0; kx < g.win_w; ++kx)
+				#pragma unroll
+				for (int kx = 0; kx < win_w; ++kx)
 				{
-					const uint32_t ix = ix0 + kx;
-					if (ix >= g.w)
+					if (ky == 0 && kx == 0)
+						continue;
+					if (CLIP && ix0 + kx >= g.w)
 						break;
-					const float v = src[iy * g.w + ix];
+					const uint32_t off = off0 + ky * g.w + kx;
+					const float v = src[off];
 					const bool better = g.is_min ? (v < best) : (v > best);
-					if (first || better)
+					if (better)
 					{
 						best = v;
-						best_off = iy * g.w + ix;
-						first = false;
+						best_off = off;
 					}
 				}
 			}
 		}
 
-		template <bool FUSED>
+		constexpr int kMaxGroup = 512; // planes per CTA iteration (bounds the per-plane parameter arrays)
+
+		template <bool FUSED, int WW, int WH, bool CLIP>
 		__global__ void __launch_bounds__(kThreads) pool_fwd_staged_kernel(const pool_fwd_params p)
 		{
 			extern __shared__ float s_z[];
+			__shared__ float s_mult[FUSED ? kMaxGroup : 1];
+			__shared__ float s_add[FUSED ? kMaxGroup : 1];
 			const pool_geom& g = p.g;
 			const int64_t ngroups = (p.planes + p.group - 1) / p.group;
+			const bool has_bn = FUSED && p.gamma != nullptr;
+			const bool has_res = FUSED && p.res != nullptr;
 			for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
 			{
 				const int64_t plane0 = grp * p.group;
 				const uint32_t np = (uint32_t)((p.planes - plane0 < p.group) ? (p.planes - plane0) : p.group);
 				const uint32_t count = np * g.hw;
 				const int64_t base = plane0 * g.hw;
-				const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
 				const float * x = p.x + base;
+				if (has_bn)
+				{
+					// batch-norm scale/shift of each plane of the group (batch_norm_layer_tester_plain.cpp:60-61)
+					const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
+					for (uint32_t lp = threadIdx.x; lp < np; lp += kThreads)
+					{
+						uint32_t channel = ch0 + lp;
+						channel -= g.d_c.div(channel) * g.c;
+						const float mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+						s_mult[lp] = mult;
+						s_add[lp] = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(mult, __ldg(p.mean + channel)));
+					}
+					__syncthreads();
+				}
+				auto fused = [&](float v, float r, float mult, float add) -> float
+				{
+					float t = v;
+					if (has_bn)
+						t = __fadd_rn(__fmul_rn(v, mult), add);
+					if (has_res)
+						t = __fadd_rn(__fadd_rn(0.0F, t), r); // add layer, alpha = 1: (0 + bn) + residual
+					return t >= 0.0F ? t : __fmul_rn(t, p.slope);
+				};
 
 				// phase 1: stream the group in, apply the fused per-element chain, keep it in shared memory
 				if (p.vec_ok)
 				{
 					const uint32_t nvec = count >> 2;
 					const float4 * x4 = reinterpret_cast<const float4 *>(x);
-					const float4 * r4 = FUSED && p.res ? reinterpret_cast<const float4 *>(p.res + base) : nullptr;
+					const float4 * r4 = has_res ? reinterpret_cast<const float4 *>(p.res + base) : nullptr;
 					float4 * z4 = FUSED ? reinterpret_cast<float4 *>(p.z + base) : nullptr;
 					float4 * s4 = reinterpret_cast<float4 *>(s_z);
-					for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
+					const bool plane_per_vec = (g.hw & 3) == 0;
+					for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kThreads * 2)
 					{
-						float4 a = ld_stream(x4 + v);
-						if (FUSED)
+						float4 a[2], r[2];
+						#pragma unroll
+						for (int u = 0; u < 2; ++u)
 						{
-							float4 r = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-							if (r4)
-								r = ld_stream(r4 + v);
-							float in[4] = {a.x, a.y, a.z, a.w};
-							const float rr[4] = {r.x, r.y, r.z, r.w};
-							#pragma unroll
-							for (int k = 0; k < 4; ++k)
+							const uint32_t v = v0 + u * kThreads;
+							r[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (v < nvec)
 							{
-								uint32_t channel = ch0 + g.d_hw.div((v << 2) + k);
-								channel -= g.d_c.div(channel) * g.c;
-								in[k] = fused_element(p, in[k], rr[k], channel);
+								a[u] = ld_stream(x4 + v);
+								if (has_res)
+									r[u] = ld_stream(r4 + v);
 							}
-							a = make_float4(in[0], in[1], in[2], in[3]);
-							st_stream(z4 + v, a);
 						}
-						s4[v] = a;
+						#pragma unroll
+						for (int u = 0; u < 2; ++u)
+						{
+							const uint32_t v = v0 + u * kThreads;
+							if (v < nvec)
+							{
+								float4 o = a[u];
+								if (FUSED)
+								{
+									if (plane_per_vec)
+									{
+										const uint32_t lp = g.d_hw.div(v << 2);
+										const float mult = has_bn ? s_mult[lp] : 1.0F, add = has_bn ? s_add[lp] : 0.0F;
+										o.x = fused(a[u].x, r[u].x, mult, add); o.y = fused(a[u].y, r[u].y, mult, add);
+										o.z = fused(a[u].z, r[u].z, mult, add); o.w = fused(a[u].w, r[u].w, mult, add);
+									}
+									else
+									{
+										float in[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+										const float rr[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+										#pragma unroll
+										for (int k = 0; k < 4; ++k)
+										{
+											const uint32_t lp = g.d_hw.div((v << 2) + k);
+											in[k] = fused(in[k], rr[k], has_bn ? s_mult[lp] : 1.0F, has_bn ? s_add[lp] : 0.0F);
+										}
+										o = make_float4(in[0], in[1], in[2], in[3]);
+									}
+									st_stream(z4 + v, o);
+								}
+								s4[v] = o;
+							}
+						}
 					}
 					for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kThreads)
 					{
 						float a = x[e];
 						if (FUSED)
 						{
-							uint32_t channel = ch0 + g.d_hw.div(e);
-							channel -= g.d_c.div(channel) * g.c;
-							a = fused_element(p, a, p.res ? p.res[base + e] : 0.0F, channel);
+							const uint32_t lp = g.d_hw.div(e);
+							a = fused(a, has_res ? p.res[base + e] : 0.0F, has_bn ? s_mult[lp] : 1.0F, has_bn ? s_add[lp] : 0.0F);
 							p.z[base + e] = a;
 						}
 						s_z[e] = a;
@@ -161,9 +211,8 @@ namespace nnf
 						float a = ld_stream(x + e);
 						if (FUSED)
 						{
-							uint32_t channel = ch0 + g.d_hw.div(e);
-							channel -= g.d_c.div(channel) * g.c;
-							a = fused_element(p, a, p.res ? ld_stream(p.res + base + e) : 0.0F, channel);
+							const uint32_t lp = g.d_hw.div(e);
+							a = fused(a, has_res ? ld_stream(p.res + base + e) : 0.0F, has_bn ? s_mult[lp] : 1.0F, has_bn ? s_add[lp] : 0.0F);
 							st_stream(p.z + base + e, a);
 						}
 						s_z[e] = a;
@@ -182,7 +231,7 @@ namespace nnf
 					const uint32_t ox = rem - oy * g.ow;
 					float best;
 					uint32_t off;
-					scan_window(g, s_z + lp * g.hw, oy, ox, best, off);
+					scan_window<WW, WH, CLIP>(g, s_z + lp * g.hw, oy, ox, best, off);
 					st_stream(p.pooled + obase + o, best);
 					if (p.argmax)
 						p.argmax[obase + o] = (uint32_t)(base + int64_t(lp) * g.hw + off);
@@ -204,7 +253,7 @@ namespace nnf
 				const uint32_t ox = rem - oy * g.ow;
 				float best;
 				uint32_t off;
-				scan_window(g, x + plane * g.hw, oy, ox, best, off);
+				scan_window<0, 0, true>(g, x + plane * g.hw, oy, ox, best, off);
 				pooled[o] = best;
 				if (argmax)
 					argmax[o] = (uint32_t)(plane * g.hw + off);
@@ -229,29 +278,55 @@ namespace nnf
 		};
 
 		// Gradient reaching input element (iy, ix) of a plane whose pooled gradients / argmax start at
-		// dyp / idx; abs_off is the element's absolute offset as the argmax stores it.
+		// dyp / idx; abs_off is the element's absolute offset as the argmax stores it. Windows are visited in
+		// ascending output index. WW/WH/SW/SH > 0: compile-time window and stride (divisions become shifts
+		// and the candidate loops unroll to ceil(WH/SH) x ceil(WW/SW) predicated steps).
+		template <int WW, int WH, int SW, int SH>
 		__device__ __forceinline__ float gather_element(const pool_geom& g, const float * dyp, const uint32_t * idx, uint32_t iy, uint32_t ix, uint32_t abs_off, float seed)
 		{
-			const uint32_t oy_lo = iy < (uint32_t)g.win_h ? 0u : g.d_sh.div(iy - g.win_h) + 1u;
-			uint32_t oy_hi = g.d_sh.div(iy);
+			const uint32_t win_w = WW ? WW : g.win_w, win_h = WH ? WH : g.win_h;
+			const uint32_t oy_lo = iy < win_h ? 0u : (SH ? (iy - win_h) / (SH ? SH : 1) : g.d_sh.div(iy - win_h)) + 1u;
+			uint32_t oy_hi = SH ? iy / (SH ? SH : 1) : g.d_sh.div(iy);
 			if (oy_hi > g.oh - 1)
 				oy_hi = g.oh - 1;
-			const uint32_t ox_lo = ix < (uint32_t)g.win_w ? 0u : g.d_sw.div(ix - g.win_w) + 1u;
-			uint32_t ox_hi = g.d_sw.div(ix);
+			const uint32_t ox_lo = ix < win_w ? 0u : (SW ? (ix - win_w) / (SW ? SW : 1) : g.d_sw.div(ix - win_w)) + 1u;
+			uint32_t ox_hi = SW ? ix / (SW ? SW : 1) : g.d_sw.div(ix);
 			if (ox_hi > g.ow - 1)
 				ox_hi = g.ow - 1;
 			float sum = seed;
-			for (uint32_t oy = oy_lo; oy <= oy_hi; ++oy)
-				for (uint32_t ox = ox_lo; ox <= ox_hi; ++ox)
+			if (WW && WH && SW && SH)
+			{
+				constexpr int NY = (WH + (SH ? SH : 1) - 1) / (SH ? SH : 1), NX = (WW + (SW ? SW : 1) - 1) / (SW ? SW : 1);
+				#pragma unroll
+				for (int a = 0; a < NY; ++a)
 				{
-					const uint32_t o = oy * g.ow + ox;
-					if (idx[o] == abs_off)
-						sum = __fadd_rn(sum, dyp[o]);
+					#pragma unroll
+					for (int b = 0; b < NX; ++b)
+					{
+						const uint32_t oy = oy_lo + a, ox = ox_lo + b;
+						if (oy <= oy_hi && ox <= ox_hi)
+						{
+							const uint32_t o = oy * g.ow + ox;
+							if (idx[o] == abs_off)
+								sum = __fadd_rn(sum, dyp[o]);
+						}
+					}
 				}
+			}
+			else
+			{
+				for (uint32_t oy = oy_lo; oy <= oy_hi; ++oy)
+					for (uint32_t ox = ox_lo; ox <= ox_hi; ++ox)
+					{
+						const uint32_t o = oy * g.ow + ox;
+						if (idx[o] == abs_off)
+							sum = __fadd_rn(sum, dyp[o]);
+					}
+			}
 			return sum;
 		}
 
-		template <bool FUSED>
+		template <bool FUSED, int WW, int WH, int SW, int SH>
 		__global__ void __launch_bounds__(kThreads) pool_bwd_staged_kernel(const pool_bwd_params p)
 		{
 			extern __shared__ float s_raw[];
@@ -281,7 +356,7 @@ namespace nnf
 					const uint32_t rem = e - lp * g.hw;
 					const uint32_t iy = g.d_w.div(rem);
 					const uint32_t ix = rem - iy * g.w;
-					const float dz = gather_element(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix, (uint32_t)(base + e), seed);
+					const float dz = gather_element<WW, WH, SW, SH>(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix, (uint32_t)(base + e), seed);
 					if (FUSED)
 					{
 						// ReLU gate from the sign bit of z (negative pre-activations were multiplied by a
@@ -368,7 +443,7 @@ namespace nnf
 				const uint32_t iy = g.d_w.div(rem);
 				const uint32_t ix = rem - iy * g.w;
 				const float seed = (!FUSED && p.add) ? p.dx[e] : 0.0F;
-				const float dz = gather_element(g, p.dpooled + plane * g.ohw, p.argmax + plane * g.ohw, iy, ix, (uint32_t)e, seed);
+				const float dz = gather_element<0, 0, 0, 0>(g, p.dpooled + plane * g.ohw, p.argmax + plane * g.ohw, iy, ix, (uint32_t)e, seed);
 				if (FUSED)
 				{
 					const float ds = (__float_as_uint(p.z[e]) >> 31) ? __fmul_rn(dz, p.slope) : dz;
@@ -383,6 +458,15 @@ namespace nnf
 				else
 					p.dx[e] = dz;
 			}
+		}
+
+		// grid size in units of one resident wave of CTAs (tuning aid: NNF_POOL_WAVES)
+		int pool_waves()
+		{
+			static int waves = 0;
+			if (waves == 0)
+				waves = getenv("NNF_POOL_WAVES") ? atoi(getenv("NNF_POOL_WAVES")) : 1;
+			return waves < 1 ? 1 : waves;
 		}
 
 		int make_geom(pool_geom& g, const char * who, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
@@ -411,7 +495,8 @@ namespace nnf
 		// planes per CTA iteration; 0 -> does not fit shared memory
 		int choose_group(const pool_geom& g, int64_t planes, bool& vec_ok)
 		{
-			int64_t grp = kGroupFloats / g.hw;
+			const int64_t group_floats = getenv("NNF_POOL_GROUP") ? atoi(getenv("NNF_POOL_GROUP")) : kGroupFloats; // tuning aid
+			int64_t grp = group_floats / g.hw;
 			if (grp < 1)
 				grp = 1;
 			if (size_t(grp) * g.hw * sizeof(float) > kMaxDynSmem)
@@ -423,6 +508,8 @@ namespace nnf
 				grp = (grp / 2) & ~int64_t(3);
 			if (grp < 1)
 				grp = 1;
+			if (grp > kMaxGroup)
+				grp = kMaxGroup;
 			if (planes < 0x7fffffff && grp > planes)
 				grp = planes;
 			vec_ok = vec_ok && ((grp * g.hw) % 4 == 0);
@@ -431,6 +518,8 @@ namespace nnf
 
 		int run_pool_fwd(cudaStream_t s, bool fused, pool_fwd_params& p, int64_t n)
 		{
+			// only round-up makes the last window stick out of the input
+			const bool need_clip = (int64_t(p.g.oh - 1) * p.g.sh + p.g.win_h > int64_t(p.g.h)) || (int64_t(p.g.ow - 1) * p.g.sw + p.g.win_w > int64_t(p.g.w));
 			p.planes = n * p.g.c;
 			if (p.planes == 0)
 				return NNF_OK;
@@ -455,20 +544,33 @@ namespace nnf
 			const int64_t ngroups = div_up(p.planes, grp);
 			int per_sm = (int)((220 * 1024) / (smem + 1024));
 			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-			const int grid = (int)(ngroups < int64_t(kSmCount) * per_sm ? ngroups : int64_t(kSmCount) * per_sm);
-			cudaError_t e;
+			const int64_t cap = int64_t(kSmCount) * per_sm * pool_waves();
+			const int grid = (int)(ngroups < cap ? ngroups : cap);
+			const bool clip = need_clip;
+			const int ww = p.g.win_w, wh = p.g.win_h;
+			cudaError_t e = cudaSuccess;
+#define NNF_POOL_FWD(FUSED, WW, WH, CLIP) \
+			{ \
+				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<FUSED, WW, WH, CLIP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				if (e == cudaSuccess) \
+					pool_fwd_staged_kernel<FUSED, WW, WH, CLIP><<<grid, kThreads, smem, s>>>(p); \
+			}
+#define NNF_POOL_FWD_SHAPE(FUSED) \
+			if (!clip && ww == 3 && wh == 3) NNF_POOL_FWD(FUSED, 3, 3, false) \
+			else if (!clip && ww == 2 && wh == 2) NNF_POOL_FWD(FUSED, 2, 2, false) \
+			else if (clip && ww == 3 && wh == 3) NNF_POOL_FWD(FUSED, 3, 3, true) \
+			else if (clip) NNF_POOL_FWD(FUSED, 0, 0, true) \
+			else NNF_POOL_FWD(FUSED, 0, 0, false)
 			if (fused)
 			{
-				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
-				if (e == cudaSuccess)
-					pool_fwd_staged_kernel<true><<<grid, kThreads, smem, s>>>(p);
+				NNF_POOL_FWD_SHAPE(true)
 			}
 			else
 			{
-				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
-				if (e == cudaSuccess)
-					pool_fwd_staged_kernel<false><<<grid, kThreads, smem, s>>>(p);
+				NNF_POOL_FWD_SHAPE(false)
 			}
+#undef NNF_POOL_FWD_SHAPE
+#undef NNF_POOL_FWD
 			if (e != cudaSuccess)
 				return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 			return check_launch("pool_fwd_staged_kernel");
@@ -501,20 +603,30 @@ namespace nnf
 			const int64_t ngroups = div_up(p.planes, grp);
 			int per_sm = (int)((220 * 1024) / (smem + 1024));
 			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-			const int grid = (int)(ngroups < int64_t(kSmCount) * per_sm ? ngroups : int64_t(kSmCount) * per_sm);
-			cudaError_t e;
+			const int64_t cap = int64_t(kSmCount) * per_sm * pool_waves();
+			const int grid = (int)(ngroups < cap ? ngroups : cap);
+			const int ww = p.g.win_w, wh = p.g.win_h, sw = p.g.sw, sh = p.g.sh;
+			cudaError_t e = cudaSuccess;
+#define NNF_POOL_BWD(FUSED, WW, WH, SW, SH) \
+			{ \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				if (e == cudaSuccess) \
+					pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH><<<grid, kThreads, smem, s>>>(p); \
+			}
+#define NNF_POOL_BWD_SHAPE(FUSED) \
+			if (ww == 3 && wh == 3 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 3, 3, 2, 2) \
+			else if (ww == 2 && wh == 2 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 2, 2, 2, 2) \
+			else NNF_POOL_BWD(FUSED, 0, 0, 0, 0)
 			if (fused)
 			{
-				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
-				if (e == cudaSuccess)
-					pool_bwd_staged_kernel<true><<<grid, kThreads, smem, s>>>(p);
+				NNF_POOL_BWD_SHAPE(true)
 			}
 			else
 			{
-				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
-				if (e == cudaSuccess)
-					pool_bwd_staged_kernel<false><<<grid, kThreads, smem, s>>>(p);
+				NNF_POOL_BWD_SHAPE(false)
 			}
+#undef NNF_POOL_BWD_SHAPE
+#undef NNF_POOL_BWD
 			if (e != cudaSuccess)
 				return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 			return check_launch("pool_bwd_staged_kernel");

@@ -111,6 +111,91 @@ namespace nnf
 			}
 		}
 
+		// ---- hw == 1, warp per row, 128-bit accesses (c % 4 == 0, 16-byte aligned rows) -------------------
+		// VPL float4 per lane cover rows of up to 128*VPL logits.
+		template <int VPL, bool BACKWARD>
+		__global__ void __launch_bounds__(256) softmax_rows_warp4_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
+		{
+			const int lane = threadIdx.x & 31;
+			const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+			const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+			const int c4 = c >> 2;
+			for (int64_t row = warp; row < rows; row += nwarps)
+			{
+				const float4 * a = reinterpret_cast<const float4 *>(in0 + row * c);
+				float4 * o = reinterpret_cast<float4 *>(out + row * c);
+				float4 v[VPL];
+				if (!BACKWARD)
+				{
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+					{
+						const int idx = j * 32 + lane;
+						v[j] = idx < c4 ? ld_stream(a + idx) : make_float4(kMaxSeed, kMaxSeed, kMaxSeed, kMaxSeed);
+					}
+					float m = kMaxSeed;
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+						m = ref_max(ref_max(ref_max(ref_max(m, v[j].x), v[j].y), v[j].z), v[j].w);
+					m = warp_max(m);
+					float s = 0.0F;
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+					{
+						const int idx = j * 32 + lane;
+						if (idx < c4)
+						{
+							v[j].x = fast_exp(__fsub_rn(v[j].x, m)); v[j].y = fast_exp(__fsub_rn(v[j].y, m));
+							v[j].z = fast_exp(__fsub_rn(v[j].z, m)); v[j].w = fast_exp(__fsub_rn(v[j].w, m));
+							s = __fadd_rn(s, __fadd_rn(__fadd_rn(v[j].x, v[j].y), __fadd_rn(v[j].z, v[j].w)));
+						}
+					}
+					s = warp_sum(s);
+					const float mult = __fdiv_rn(1.0F, s);
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+					{
+						const int idx = j * 32 + lane;
+						if (idx < c4)
+							st_stream(o + idx, make_float4(__fmul_rn(v[j].x, mult), __fmul_rn(v[j].y, mult), __fmul_rn(v[j].z, mult), __fmul_rn(v[j].w, mult)));
+					}
+				}
+				else
+				{
+					const float4 * y = reinterpret_cast<const float4 *>(in1 + row * c);
+					float4 g[VPL];
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+					{
+						const int idx = j * 32 + lane;
+						g[j] = idx < c4 ? ld_stream(a + idx) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						v[j] = idx < c4 ? ld_stream(y + idx) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					}
+					float s = 0.0F;
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+						s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fmul_rn(g[j].x, v[j].x), __fmul_rn(g[j].y, v[j].y)), __fadd_rn(__fmul_rn(g[j].z, v[j].z), __fmul_rn(g[j].w, v[j].w))));
+					s = warp_sum(s);
+					#pragma unroll
+					for (int j = 0; j < VPL; ++j)
+					{
+						const int idx = j * 32 + lane;
+						if (idx < c4)
+						{
+							float4 r = make_float4(__fmul_rn(v[j].x, __fsub_rn(g[j].x, s)), __fmul_rn(v[j].y, __fsub_rn(g[j].y, s)),
+								__fmul_rn(v[j].z, __fsub_rn(g[j].z, s)), __fmul_rn(v[j].w, __fsub_rn(g[j].w, s)));
+							if (add)
+							{
+								const float4 old = o[idx];
+								r = make_float4(__fadd_rn(old.x, r.x), __fadd_rn(old.y, r.y), __fadd_rn(old.z, r.z), __fadd_rn(old.w, r.w));
+							}
+							st_stream(o + idx, r);
+						}
+					}
+				}
+			}
+		}
+
 		__device__ __forceinline__ float block_reduce(float v, float * s_red, bool is_max)
 		{
 			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -351,7 +436,17 @@ namespace nnf
 				if (c <= 1024)
 				{
 					const int64_t blocks_needed = div_up(rows, 8);
-					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 8 ? blocks_needed : int64_t(kSmCount) * 8);
+					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 64 ? blocks_needed : int64_t(kSmCount) * 64);
+					if ((c & 3) == 0 && aligned16(out) && aligned16(in0) && (!in1 || aligned16(in1)))
+					{
+#define NNF_ROWS4(VPL) softmax_rows_warp4_kernel<VPL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
+						if (c <= 128) NNF_ROWS4(1);
+						else if (c <= 256) NNF_ROWS4(2);
+						else if (c <= 512) NNF_ROWS4(4);
+						else NNF_ROWS4(8);
+#undef NNF_ROWS4
+						return check_launch("softmax_rows_warp4_kernel");
+					}
 #define NNF_ROWS(PL) softmax_rows_warp_kernel<PL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
 					if (c <= 32) NNF_ROWS(1);
 					else if (c <= 64) NNF_ROWS(2);
@@ -393,7 +488,7 @@ namespace nnf
 				if (c <= 32)
 				{
 					const int64_t blocks_needed = div_up(pixels, 256);
-					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 16 ? blocks_needed : int64_t(kSmCount) * 16);
+					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 128 ? blocks_needed : int64_t(kSmCount) * 128);
 					if (c <= 8)
 						softmax_pixels_reg_kernel<8, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
 					else if (c <= 16)
