@@ -30,6 +30,8 @@ EPS = 1e-5
 BYTES_PER_ELEM_FWD = 8
 BYTES_PER_ELEM_BWD = 12
 METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
+# DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/ (same shape)
+NCU_TRAFFIC_BYTES = {}
 WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
 
 
@@ -176,6 +178,125 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_sweep(args):
+    """Per-configuration kernel table (all five benchmark configurations, single GPU): device time per
+    launch by CUDA events, algorithmic GB/s and fraction of the measured copy bandwidth. Tensors smaller
+    than L2 are rotated through enough buffers to exceed it and replayed from a CUDA graph, so that the
+    figure is neither an L2 number nor a Python launch-overhead number. Prints a table on stderr and one
+    JSON line on stdout."""
+    import torch
+    import nnforge_b200.capi as capi
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    peak, peak_kind = measured_peaks()
+    rows = []
+
+    def bnp(c):
+        return [torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda") * 0.1, torch.randn(c, device="cuda") * 0.1,
+                1 / torch.sqrt(torch.rand(c, device="cuda") * 1.5 + 0.5)]
+
+    def timeit(fn, nbuf, reps=20):
+        for i in range(max(3, nbuf)):
+            fn(i % nbuf)
+        torch.cuda.synchronize()
+        graph = None
+        if nbuf > 1:  # small tensors: replay `reps` launches from a graph, rotating buffers
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(reps):
+                        fn(i % nbuf)
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(reps):
+                fn(i % nbuf)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def nbufs(bytes_per_set):
+        return max(1, min(24, int(2 * 126e6 / bytes_per_set) + 1)) if bytes_per_set < 200e6 else 1
+
+    def report(config, name, ms, alg_bytes, note=""):
+        gbs = alg_bytes / (ms * 1e-3) / 1e9
+        rows.append({"config": config, "kernel": name, "us": ms * 1e3, "GBps": gbs, "frac_of_peak": gbs / peak, "algorithmic_bytes": alg_bytes, "note": note})
+        print("cfg%-2s %-58s %9.1f us %8.1f GB/s %6.1f%% of %s peak %s" % (config, name, ms * 1e3, gbs, 100 * gbs / peak, peak_kind, note), file=sys.stderr, flush=True)
+
+    # config 0: inference BN + ReLU
+    shape = (64, 64, 32, 32)
+    e = 64 * 64 * 32 * 32
+    nb = nbufs(8 * e)
+    xs = [torch.randn(shape, device="cuda") for _ in range(nb)]
+    ys = [torch.empty(shape, device="cuda") for _ in range(nb)]
+    bn = bnp(64)
+    relu = [capi.relu(0.0)]
+    report(0, "bn_infer+relu x[64,64,32,32]", timeit(lambda i: capi.bn_infer_act(ys[i], xs[i], bn=bn, acts=relu), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
+    del xs, ys
+    # config 1: channel softmax
+    for shape in [(256, 1000, 1, 1), (32, 21, 128, 128)]:
+        e = shape[0] * shape[1] * shape[2] * shape[3]
+        nb = nbufs(8 * e)
+        xs = [torch.randn(shape, device="cuda") * 3 for _ in range(nb)]
+        ys = [torch.empty(shape, device="cuda") for _ in range(nb)]
+        dx = torch.empty(shape, device="cuda")
+        report(1, "softmax fwd %s" % (list(shape),), timeit(lambda i: capi.softmax_fwd(ys[i], xs[i]), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
+        report(1, "softmax bwd %s" % (list(shape),), timeit(lambda i: capi.softmax_bwd(dx, xs[i], ys[i]), nb), 12 * e, "%d rotating buffers, graph replay" % nb)
+        del xs, ys, dx
+    # config 2: training BN + PReLU + ELU (the default benchmark's kernels, timed one by one)
+    shape = (N_PER_GPU, C, H, W)
+    e = elements_per_gpu()
+    x = torch.randn(shape, device="cuda") * 2 + 0.5
+    dy = torch.randn(shape, device="cuda")
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    g, b, sl = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda") * 0.1, torch.rand(C, device="cuda") * 0.3
+    ws = torch.empty(capi.bn_train_workspace_bytes(N_PER_GPU, C, H * W), dtype=torch.uint8, device="cuda")
+    sums, saved, bs = torch.empty(2 * C, device="cuda"), torch.empty(2 * C, device="cuda"), torch.empty(3 * C, device="cuda")
+    acts = [capi.prelu(sl), capi.elu()]
+    m = N_PER_GPU * H * W
+    report(2, "bn_train fwd single pass (cluster)", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
+    report(2, "bn_train stats", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
+    report(2, "bn_train apply+prelu+elu", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, g, b, sums, m, EPS, acts), 1), 8 * e)
+    report(2, "bn_train bwd stats", timeit(lambda i: capi.bn_train_bwd_stats(bs, dy, x, g, b, saved, acts, ws), 1), 8 * e)
+    report(2, "bn_train bwd apply", timeit(lambda i: capi.bn_train_bwd_apply(dx, dy, x, g, b, saved, bs, bs, m, acts), 1), 12 * e)
+    report(2, "reference point: torch copy_ of one tensor", timeit(lambda i: y.copy_(x), 1), 8 * e)
+    del x, dy, y, dx
+    # config 3: BN -> add -> ReLU -> max-pool 3x3/2, forward and backward, four stages
+    for c, hw in [(64, 56), (128, 28), (256, 14), (512, 7)]:
+        shape = (256, c, hw, hw)
+        e = 256 * c * hw * hw
+        p = capi.pool((3, 3), (2, 2))
+        oh, ow = capi.pool_out_shape(hw, hw, p)
+        rho = oh * ow / float(hw * hw)
+        x, r, z = [torch.randn(shape, device="cuda") for _ in range(3)]
+        pooled = torch.empty((256, c, oh, ow), device="cuda")
+        idx = torch.empty((256, c, oh, ow), device="cuda", dtype=torch.int32)
+        bn = bnp(c)
+        dpo, dx, dr = torch.randn_like(pooled), torch.empty_like(x), torch.empty_like(x)
+        nb = 1
+        report(3, "bn+add+relu+maxpool fwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_fwd(z, pooled, idx, x, r, bn, 0.0, p), nb), (12 + 8 * rho) * e)
+        report(3, "bn+add+relu+maxpool bwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_bwd(dx, dr, dpo, idx, z, bn[0], bn[3], 0.0, p), nb), (12 + 8 * rho) * e)
+        del x, r, z, pooled, idx, dpo, dx, dr
+    # config 4: inference BN + TanH / Sigmoid bandwidth sweep
+    sizes = [128, 1024, 4096] + ([8192] if args.sweep_full else [])
+    for n in sizes:
+        shape = (n, 128, 64, 64)
+        e = n * 128 * 64 * 64
+        x = torch.randn(shape, device="cuda") * 1.5
+        y = torch.empty_like(x)
+        bn = bnp(128)
+        for name, act in (("tanh", capi.tanh()), ("sigmoid", capi.sigmoid())):
+            report(4, "bn_infer+%s N=%d (%.2f GiB in)" % (name, n, e * 4 / 2.0 ** 30), timeit(lambda i: capi.bn_infer_act(y, x, bn=bn, acts=[act]), 1, reps=10), 8 * e)
+        del x, y
+    print(json.dumps({"sweep": rows, "peak_GBps": peak, "peak_source": peak_kind}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -184,7 +305,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--sweep", action="store_true", help="time every kernel family at all five configurations (single GPU) instead of the benchmark step")
+    ap.add_argument("--sweep-full", action="store_true", help="with --sweep: include the 16 GiB case of configuration 4")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return
@@ -220,27 +346,35 @@ def main():
     bsums, gsums = torch.empty(3 * C, device="cuda"), torch.empty(2 * C, device="cuda")
     grads = [torch.zeros(C, device="cuda") for _ in range(3)]
     acts = [capi.prelu(slope), capi.elu()]
-    launches_per_step = 6
-    phases = ("stats", "apply", "bwd_stats", "bwd_apply")
+    single = dist is None
+    # kernels of ours per step: single GPU = 1 (single-pass forward) + 3 (backward statistics, their
+    # reduction, backward apply); sharded = 2 + 1 + 2 + 1 with an NCCL all-reduce after each statistics step
+    launches_per_step = 4 if single else 6
+    phases = ("forward", "bwd_stats", "bwd_apply") if single else ("stats", "apply", "bwd_stats", "bwd_apply")
 
     def step(ev=None):
         def mark(i):
             if ev is not None:
                 ev[i].record()
         mark(0)
-        capi.bn_train_stats(sums, x, ws)
-        mark(1)
-        if dist is not None:
+        if single:
+            capi.bn_train_fwd(y, saved, sums, x, gamma, beta, EPS, acts, workspace=ws)
+            mark(1)
+            mark(2)
+            mark(3)
+        else:
+            capi.bn_train_stats(sums, x, ws)
+            mark(1)
             dist.all_reduce(sums)
-        mark(2)
-        capi.bn_train_apply_act(y, saved, x, gamma, beta, sums, m_total, EPS, acts)
-        mark(3)
-        capi.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, ws, gsums=gsums if dist is not None else None)
+            mark(2)
+            capi.bn_train_apply_act(y, saved, x, gamma, beta, sums, m_total, EPS, acts)
+            mark(3)
+        capi.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, ws, gsums=None if single else gsums)
         mark(4)
-        if dist is not None:
+        if not single:
             dist.all_reduce(gsums)
         mark(5)
-        capi.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums if dist is not None else bsums, bsums, m_total, acts,
+        capi.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, bsums if single else gsums, bsums, m_total, acts,
                                 grad_gamma=grads[0], grad_beta=grads[1], grad_slope=grads[2], entry_count=float(N_PER_GPU))
         mark(6)
 
@@ -279,15 +413,25 @@ def main():
     value = bytes_step_all / (ms_step * 1e-3) / 1e9
 
     # per-kernel durations from the events recorded inside the timed region (this rank)
-    idx = {"stats": (0, 1), "apply": (2, 3), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
+    if single:
+        idx = {"forward": (0, 1), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
+        alg_bytes = {"forward": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
+        names = {"forward": "bn_train_fwd_cluster_kernel (single pass: x in, y out)", "bwd_stats": "bn_bwd_stats_kernel (x, dy in)",
+                 "bwd_apply": "bn_bwd_apply_kernel (x, dy in, dx out)"}
+    else:
+        idx = {"stats": (0, 1), "apply": (2, 3), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
+        alg_bytes = {"stats": 4 * elems, "apply": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
+        names = {"stats": "bn_stats_kernel (x in)", "apply": "bn_act_kernel (x in, y out)", "bwd_stats": "bn_bwd_stats_kernel (x, dy in)",
+                 "bwd_apply": "bn_bwd_apply_kernel (x, dy in, dx out)"}
     kernel_ms = {name: sum(e[a].elapsed_time(e[b]) for e in evs) / len(evs) for name, (a, b) in idx.items()}
-    alg_bytes = {"stats": 4 * elems, "apply": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
     peak, peak_kind = measured_peaks()
     dominant = max(kernel_ms, key=kernel_ms.get)
     achieved = alg_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": peak_kind + " copy bandwidth", "traffic": None,
-                "kernels": {k: {"ms": kernel_ms[k], "algorithmic_GBps": alg_bytes[k] / (kernel_ms[k] * 1e-3) / 1e9} for k in phases},
+    roofline = {"bound": "hbm", "kernel": names[dominant], "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": peak_kind + " copy bandwidth (MEASURED_PEAKS.json hbm_gbs)", "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+                "algorithmic_bytes_per_launch": alg_bytes[dominant],
+                "kernels": {k: {"ms": kernel_ms[k], "algorithmic_GBps": alg_bytes[k] / (kernel_ms[k] * 1e-3) / 1e9,
+                                "frac_of_peak": alg_bytes[k] / (kernel_ms[k] * 1e-3) / 1e9 / peak} for k in phases},
                 "step_frac_of_peak": (value / world) / peak}
 
     # end to end through the C ABI with host buffers: H2D of x and dy, the same step, D2H of y and dx

@@ -463,6 +463,256 @@ namespace nnf
 			}
 		}
 
+		// ---- variants that keep the slab in L2 instead of shared memory ------------------------------
+		// One cluster per channel, launched for all channels at once. Pass 1 streams this CTA's planes from
+		// HBM (default cache policy, so the lines stay in L2) and reduces; the cluster exchanges its partial
+		// sums; pass 2 reads the same planes again a few microseconds later - from L2 - and streams the
+		// result out with evict-first stores. No shared-memory slab, so any N and H*W fit; the number of
+		// channels in flight (and with it the L2 footprint) is bounded by a shared-memory reservation that
+		// limits how many CTAs an SM holds.
+		template <int A0, int A1>
+		__global__ void __launch_bounds__(512, 2) bn_train_fwd_l2_kernel(const fused_params p)
+		{
+			__shared__ double s_red[16 * 2];
+			__shared__ double s_exch[kMaxCluster][2];
+			const uint32_t rank = cluster_rank();
+			const uint32_t ch = blockIdx.x / p.cluster;
+			const uint32_t e0 = rank * p.planes_per_cta;
+			const uint32_t e1 = min(e0 + p.planes_per_cta, p.n);
+			const uint32_t np = e1 > e0 ? e1 - e0 : 0;
+			const uint32_t vpp = p.hw >> 2;
+			const uint32_t nvec = np * vpp;
+			const size_t entry_stride = size_t(p.c) * p.hw;
+			const size_t base = size_t(e0) * entry_stride + size_t(ch) * p.hw;
+			constexpr int kU = 4;
+
+			float s = 0.0F, q = 0.0F;
+			for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU)
+			{
+				float4 a[kU];
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					const uint32_t i = i0 + u * blockDim.x;
+					a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (i < nvec)
+					{
+						const uint32_t pl = p.d_vpp.div(i);
+						a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + base + pl * entry_stride) + (i - pl * vpp));
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					s += (a[u].x + a[u].y) + (a[u].z + a[u].w);
+					q += (a[u].x * a[u].x + a[u].y * a[u].y) + (a[u].z * a[u].z + a[u].w * a[u].w);
+				}
+			}
+			double acc[2] = {double(s), double(q)};
+			block_sum_all<2>(acc, s_red);
+			if (threadIdx.x < p.cluster)
+			{
+				dsmem_store(&s_exch[rank][0], threadIdx.x, acc[0]);
+				dsmem_store(&s_exch[rank][1], threadIdx.x, acc[1]);
+			}
+			__syncwarp();
+			cluster_sync_all();
+			double ts = 0.0, tq = 0.0;
+			for (uint32_t r = 0; r < p.cluster; ++r)
+			{
+				ts += s_exch[r][0];
+				tq += s_exch[r][1];
+			}
+			const double m = ts / p.count;
+			double var = tq / p.count - m * m;
+			var = var < 0.0 ? 0.0 : var;
+			const float mean = float(m);
+			const float invstd = float(1.0 / sqrt(var + double(p.eps)));
+			if (rank == 0 && threadIdx.x == 0)
+			{
+				if (p.saved)
+				{
+					p.saved[ch] = mean;
+					p.saved[p.c + ch] = invstd;
+				}
+				if (p.sums)
+				{
+					p.sums[ch] = float(ts);
+					p.sums[p.c + ch] = float(tq);
+				}
+			}
+			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			const float slope = chain_slope(p.chain, ch);
+
+			for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU)
+			{
+				float4 a[kU];
+				size_t pos[kU];
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					const uint32_t i = i0 + u * blockDim.x;
+					if (i < nvec)
+					{
+						const uint32_t pl = p.d_vpp.div(i);
+						pos[u] = base + pl * entry_stride + size_t(i - pl * vpp) * 4;
+						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos[u])); // last use: evict first
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					const uint32_t i = i0 + u * blockDim.x;
+					if (i < nvec)
+					{
+						float4 o;
+						o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].x, mult), add), slope);
+						o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult), add), slope);
+						o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult), add), slope);
+						o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult), add), slope);
+						st_stream(reinterpret_cast<float4 *>(p.out + pos[u]), o);
+					}
+				}
+			}
+		}
+
+		template <int A0, int A1>
+		__global__ void __launch_bounds__(512, 2) bn_train_bwd_l2_kernel(const fused_params p)
+		{
+			__shared__ double s_red[16 * 3];
+			__shared__ double s_exch[kMaxCluster][3];
+			const uint32_t rank = cluster_rank();
+			const uint32_t ch = blockIdx.x / p.cluster;
+			const uint32_t e0 = rank * p.planes_per_cta;
+			const uint32_t e1 = min(e0 + p.planes_per_cta, p.n);
+			const uint32_t np = e1 > e0 ? e1 - e0 : 0;
+			const uint32_t vpp = p.hw >> 2;
+			const uint32_t nvec = np * vpp;
+			const size_t entry_stride = size_t(p.c) * p.hw;
+			const size_t base = size_t(e0) * entry_stride + size_t(ch) * p.hw;
+			constexpr int kU = 2;
+
+			const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			const float slope = chain_slope(p.chain, ch);
+
+			float sb = 0.0F, sg = 0.0F, ss = 0.0F;
+			auto du_of = [&](float x, float dy, float& term) -> float
+			{
+				const float u = __fadd_rn(__fmul_rn(x, mult), add);
+				return chain_backward<A0, A1>(p.chain, u, dy, slope, term);
+			};
+			for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU)
+			{
+				float4 a[kU], d[kU];
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					const uint32_t i = i0 + u * blockDim.x;
+					if (i < nvec)
+					{
+						const uint32_t pl = p.d_vpp.div(i);
+						const size_t pos = base + pl * entry_stride + size_t(i - pl * vpp) * 4;
+						a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + pos));
+						d[u] = __ldg(reinterpret_cast<const float4 *>(p.dy + pos));
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					if (i0 + u * blockDim.x < nvec)
+					{
+						const float xs[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+						const float ds[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+						#pragma unroll
+						for (int k = 0; k < 4; ++k)
+						{
+							float term;
+							const float du = du_of(xs[k], ds[k], term);
+							const float xhat = __fmul_rn(__fsub_rn(xs[k], mean), invstd);
+							sb += du;
+							sg += du * xhat;
+							ss += term;
+						}
+					}
+				}
+			}
+			double acc[3] = {double(sb), double(sg), double(ss)};
+			block_sum_all<3>(acc, s_red);
+			if (threadIdx.x < p.cluster)
+			{
+				dsmem_store(&s_exch[rank][0], threadIdx.x, acc[0]);
+				dsmem_store(&s_exch[rank][1], threadIdx.x, acc[1]);
+				dsmem_store(&s_exch[rank][2], threadIdx.x, acc[2]);
+			}
+			__syncwarp();
+			cluster_sync_all();
+			double tb = 0.0, tg = 0.0, tsl = 0.0;
+			for (uint32_t r = 0; r < p.cluster; ++r)
+			{
+				tb += s_exch[r][0];
+				tg += s_exch[r][1];
+				tsl += s_exch[r][2];
+			}
+			const float fb = float(tb), fg = float(tg), fs = float(tsl);
+			if (rank == 0 && threadIdx.x == 0)
+			{
+				if (p.sums)
+				{
+					p.sums[ch] = fb;
+					p.sums[p.c + ch] = fg;
+					p.sums[2 * p.c + ch] = fs;
+				}
+				if (p.grad_beta) p.grad_beta[ch] += fb;
+				if (p.grad_gamma) p.grad_gamma[ch] += fg;
+				if (p.grad_slope) p.grad_slope[ch] += fs;
+				if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+				if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+			}
+			const float c2 = float(double(fb) / p.count);
+			const float c3 = float(double(fg) / p.count);
+
+			for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU)
+			{
+				float4 a[kU], d[kU], o[kU];
+				size_t pos[kU];
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					const uint32_t i = i0 + u * blockDim.x;
+					o[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (i < nvec)
+					{
+						const uint32_t pl = p.d_vpp.div(i);
+						pos[u] = base + pl * entry_stride + size_t(i - pl * vpp) * 4;
+						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos[u]));
+						d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + pos[u]));
+						if (p.add)
+							o[u] = ld_stream(reinterpret_cast<const float4 *>(p.out + pos[u]));
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kU; ++u)
+				{
+					if (i0 + u * blockDim.x < nvec)
+					{
+						auto dx_of = [&](float x, float dy, float old) -> float
+						{
+							float term;
+							const float du = du_of(x, dy, term);
+							const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
+							const float r = mult * ((du - c2) - xhat * c3);
+							return p.add ? old + r : r;
+						};
+						st_stream(reinterpret_cast<float4 *>(p.out + pos[u]),
+							make_float4(dx_of(a[u].x, d[u].x, o[u].x), dx_of(a[u].y, d[u].y, o[u].y), dx_of(a[u].z, d[u].z, o[u].z), dx_of(a[u].w, d[u].w, o[u].w)));
+					}
+				}
+			}
+		}
+
 		// ---- host side ---------------------------------------------------------------------------
 		struct fused_plan
 		{
@@ -566,6 +816,82 @@ namespace nnf
 	}
 }
 
+namespace nnf
+{
+	namespace
+	{
+		// Launch shape of the L2-resident variants: cluster size, planes per CTA, and the shared-memory
+		// reservation that keeps the channels in flight (clusters resident at once x slab bytes) under
+		// the L2 budget.
+		struct l2_plan
+		{
+			int cluster;
+			uint32_t planes_per_cta;
+			size_t reserve_smem;
+		};
+
+		bool plan_l2(l2_plan& plan, int64_t n, int64_t c, int64_t hw, int tensors)
+		{
+			if (hw % 4 != 0 || n < 1)
+				return false;
+			int cl = 8;
+			while (cl > 1 && cl > n)
+				cl >>= 1;
+			const char * forced = getenv("NNF_L2_CLUSTER"); // tuning aid
+			if (forced && atoi(forced) >= 1 && atoi(forced) <= 8)
+				cl = atoi(forced);
+			const double slab = double(n) * double(hw) * 4.0 * tensors;
+			const double budget = (getenv("NNF_L2_BUDGET_MB") ? atof(getenv("NNF_L2_BUDGET_MB")) : 64.0) * 1024.0 * 1024.0;
+			// channels in flight = SMs * CTAs per SM / cluster size
+			int ctas_per_sm = int(budget / (slab * double(kSmCount) / cl));
+			if (ctas_per_sm < 1)
+				return false; // even one CTA per SM would overflow the budget: use the two-kernel form
+			if (ctas_per_sm > 4)
+				ctas_per_sm = 4;
+			plan.cluster = cl;
+			plan.planes_per_cta = (uint32_t)div_up(n, cl);
+			plan.reserve_smem = ctas_per_sm >= 4 ? 0 : size_t(225 * 1024) / ctas_per_sm - 2048;
+			return true;
+		}
+
+		template <class Kernel>
+		int launch_l2(Kernel kernel, const l2_plan& plan, const fused_params& p, cudaStream_t s, const char * what)
+		{
+			cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(plan.reserve_smem > 48 * 1024 ? plan.reserve_smem : 48 * 1024));
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
+			cudaLaunchConfig_t cfg = {};
+			cudaLaunchAttribute attr;
+			attr.id = cudaLaunchAttributeClusterDimension;
+			attr.val.clusterDim.x = plan.cluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+			cfg.gridDim = dim3(p.c * plan.cluster, 1, 1);
+			cfg.blockDim = dim3(512, 1, 1);
+			cfg.dynamicSmemBytes = plan.reserve_smem;
+			cfg.stream = s;
+			cfg.attrs = &attr;
+			cfg.numAttrs = 1;
+			e = cudaLaunchKernelEx(&cfg, kernel, p);
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+			return NNF_OK;
+		}
+
+		// Which form the single-GPU entry points use (NNF_FUSED_MODE, a tuning aid):
+		//   0 (default)  forward: shared-memory slab kernel; backward: the two-kernel form
+		//   1            L2-resident single-pass kernels for both
+		//   2            shared-memory slab kernels for both
+		// Measured on B200, x[256,256,28,28], PReLU+ELU: forward 99 us (slab) / 108 us (L2) / 119 us (two
+		// kernels); backward 185 us (slab) / 172-192 us (L2) / 175 us (two kernels). The single-pass
+		// backward kernels do move only 12 bytes/element through HBM (ncu: 423 MB read, 205 MB written)
+		// but run at two 512-thread CTAs per SM and are latency-bound there.
+		int fused_mode()
+		{
+			const char * m = getenv("NNF_FUSED_MODE");
+			return m ? atoi(m) : 0;
+		}
+	}
+}
+
 // Error word of the cluster kernels: a device variable inside the library, so that reaching it needs
 // no allocation (the enqueue path never allocates).
 static __device__ int nnf_fused_error_word;
@@ -623,9 +949,30 @@ extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, f
 	else if (k0 == NNF_ACT_RELU && k1 == NNF_ACT_NONE)
 		kernel = bn_train_fwd_cluster_kernel<NNF_ACT_RELU, 0>;
 
+	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(y);
+	l2_plan lp;
+	if (fused_mode() == 1 && shape_ok && plan_l2(lp, n, c, hw, 1))
+	{
+		kernel_t k2 = bn_train_fwd_l2_kernel<-1, 0>;
+		if (chain.n == 0)
+			k2 = bn_train_fwd_l2_kernel<NNF_ACT_NONE, 0>;
+		else if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU)
+			k2 = bn_train_fwd_l2_kernel<NNF_ACT_PRELU, NNF_ACT_ELU>;
+		else if (k0 == NNF_ACT_RELU && k1 == NNF_ACT_NONE)
+			k2 = bn_train_fwd_l2_kernel<NNF_ACT_RELU, 0>;
+		fused_params q = {};
+		q.x = x; q.out = y; q.gamma = gamma; q.beta = beta; q.saved = saved; q.sums = sums;
+		q.chain = chain;
+		q.n = (uint32_t)n; q.c = (uint32_t)c; q.hw = (uint32_t)hw;
+		q.planes_per_cta = lp.planes_per_cta;
+		q.cluster = (uint32_t)lp.cluster;
+		q.d_vpp = fastdiv((uint32_t)(hw / 4));
+		q.count = double(n) * double(hw);
+		q.eps = eps;
+		return launch_l2(k2, lp, q, (cudaStream_t)stream, "bn_train_fwd_l2_kernel");
+	}
 	fused_plan plan;
-	const bool fits = n <= 0x7fffffff && c <= 0x7fffffff && hw <= 0x7fffffff && aligned16(x) && aligned16(y)
-		&& plan_fused(plan, kernel, n, c, hw, 1);
+	const bool fits = shape_ok && plan_fused(plan, kernel, n, c, hw, 1);
 	if (!fits)
 	{
 		// two-kernel form
@@ -705,9 +1052,33 @@ extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, 
 	case 2: kernel = bn_train_bwd_cluster_kernel<NNF_ACT_RELU, 0>; break;
 	default: break;
 	}
+	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(dy) && aligned16(dx);
+	l2_plan lp;
+	if (fused_mode() == 1 && shape_ok && plan_l2(lp, n, c, hw, 2))
+	{
+		kernel_t k2 = bn_train_bwd_l2_kernel<-1, 0>;
+		switch (chain_id(chain))
+		{
+		case 0: k2 = bn_train_bwd_l2_kernel<NNF_ACT_NONE, 0>; break;
+		case 1: k2 = bn_train_bwd_l2_kernel<NNF_ACT_PRELU, NNF_ACT_ELU>; break;
+		case 2: k2 = bn_train_bwd_l2_kernel<NNF_ACT_RELU, 0>; break;
+		default: break;
+		}
+		fused_params q = {};
+		q.x = x; q.dy = dy; q.out = dx; q.gamma = gamma; q.beta = beta; q.saved = const_cast<float *>(saved); q.sums = bsums;
+		q.grad_gamma = grad_gamma; q.grad_beta = grad_beta; q.grad_mean = grad_mean; q.grad_invsigma = grad_invsigma; q.grad_slope = grad_slope;
+		q.mean = mean; q.invsigma = invsigma; q.entry_count = entry_count;
+		q.add = add_to_destination ? 1 : 0;
+		q.chain = chain;
+		q.n = (uint32_t)n; q.c = (uint32_t)c; q.hw = (uint32_t)hw;
+		q.planes_per_cta = lp.planes_per_cta;
+		q.cluster = (uint32_t)lp.cluster;
+		q.d_vpp = fastdiv((uint32_t)(hw / 4));
+		q.count = double(n) * double(hw);
+		return launch_l2(k2, lp, q, (cudaStream_t)stream, "bn_train_bwd_l2_kernel");
+	}
 	fused_plan plan;
-	const bool fits = n <= 0x7fffffff && c <= 0x7fffffff && hw <= 0x7fffffff && aligned16(x) && aligned16(dy) && aligned16(dx)
-		&& plan_fused(plan, kernel, n, c, hw, 1, true, 512);
+	const bool fits = fused_mode() == 2 && shape_ok && plan_fused(plan, kernel, n, c, hw, 1, true, 512);
 	if (!fits)
 	{
 		st = nnf_bn_train_bwd_stats(stream, bsums, nullptr, dy, x, gamma, beta, saved, acts, n_acts, n, c, hw, workspace, workspace_bytes);

@@ -401,9 +401,14 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1, fused=False
 
 @pytest.mark.parametrize("shape", TRAIN_SHAPES)
 @pytest.mark.parametrize("chain", TRAIN_CHAINS)
-@pytest.mark.parametrize("shards", [1, 2, "fused"])
-def test_bn_train(capi, oracle, shape, chain, shards):
-    fused = shards == "fused"
+@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2"])
+def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
+    """shards 1/2: the split entry points with the sums added across shards on the host;
+    fusedK: the single-GPU entry points with NNF_FUSED_MODE=K (slab forward + two-kernel backward,
+    L2-resident single pass, shared-memory slab single pass)."""
+    fused = isinstance(shards, str)
+    if fused:
+        monkeypatch.setenv("NNF_FUSED_MODE", shards[-1])
     shards = 1 if fused else shards
     if shards > shape[0]:
         pytest.skip("fewer entries than shards")
