@@ -31,7 +31,7 @@ BYTES_PER_ELEM_FWD = 8
 BYTES_PER_ELEM_BWD = 12
 METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
 # DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/ (same shape)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"bwd_apply": 579759360, "forward": 358484736, "bwd_stats": 414813184}
 WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
 
 
