@@ -352,31 +352,30 @@ def main():
     launches_per_step = 4 if single else 6
     phases = ("forward", "bwd_stats", "bwd_apply") if single else ("stats", "apply", "bwd_stats", "bwd_apply")
 
+    from nnforge_b200.sharded import ShardedBatchNormAct
+    current = {"ev": None}
+    order = {"start": 0, "stats": 1, "allreduce_fwd": 2, "apply": 3, "bwd_stats": 4, "allreduce_bwd": 5, "bwd_apply": 6}
+
+    def on_phase(name):
+        if current["ev"] is not None:
+            current["ev"][order[name]].record()
+
+    layer = ShardedBatchNormAct(capi, C, EPS, acts, "cuda", on_phase=on_phase)
+    grad_map = {"gamma": grads[0], "beta": grads[1], "slope": grads[2]}
+
     def step(ev=None):
-        def mark(i):
-            if ev is not None:
-                ev[i].record()
-        mark(0)
+        current["ev"] = ev
         if single:
-            capi.bn_train_fwd(y, saved, sums, x, gamma, beta, EPS, acts, workspace=ws)
-            mark(1)
-            mark(2)
-            mark(3)
+            # one GPU: the single-pass forward entry point, then the same backward sequence as the sharded path
+            on_phase("start")
+            capi.bn_train_fwd(y, layer.saved, layer.sums, x, gamma, beta, EPS, acts, workspace=layer._ws(x))
+            on_phase("stats")
+            on_phase("allreduce_fwd")
+            on_phase("apply")
         else:
-            capi.bn_train_stats(sums, x, ws)
-            mark(1)
-            dist.all_reduce(sums)
-            mark(2)
-            capi.bn_train_apply_act(y, saved, x, gamma, beta, sums, m_total, EPS, acts)
-            mark(3)
-        capi.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, ws, gsums=None if single else gsums)
-        mark(4)
-        if not single:
-            dist.all_reduce(gsums)
-        mark(5)
-        capi.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, bsums if single else gsums, bsums, m_total, acts,
-                                grad_gamma=grads[0], grad_beta=grads[1], grad_slope=grads[2], entry_count=float(N_PER_GPU))
-        mark(6)
+            layer.forward(y, x, gamma, beta)
+        layer.backward(dx, dy, x, gamma, beta, grads=grad_map)
+        current["ev"] = None
 
     def barrier():
         if dist is not None:

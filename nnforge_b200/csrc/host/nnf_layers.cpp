@@ -1,0 +1,600 @@
+// Implementation of the host-side layer objects (see nnf_layers.h) on top of the C ABI, plus a small
+// flat driver interface (nnfh_*) through which the Python tests create these objects by type name
+// and call their members with raw device pointers.
+#include "nnf_layers.h"
+
+#include "../../../include/nnf_b200.h"
+
+#include <cstring>
+
+namespace nnf_b200
+{
+	namespace
+	{
+		void check(int status)
+		{
+			if (status != NNF_OK)
+				throw neural_network_exception(std::string("nnf_b200: ") + nnf_last_error_string());
+		}
+
+		const float * f(const device_buffer::const_ptr& b) { return b ? static_cast<const float *>(*b) : nullptr; }
+		float * f(const device_buffer::ptr& b) { return b ? static_cast<float *>(*b) : nullptr; }
+
+		nnf_act make_act(const layer& l, const float * slope)
+		{
+			nnf_act a;
+			a.kind = NNF_ACT_NONE; a.p0 = 0.0F; a.p1 = 0.0F; a.slope = slope;
+			if (l.type_name == "ReLU") { a.kind = NNF_ACT_RELU; a.p0 = l.negative_slope; }
+			else if (l.type_name == "PReLU") a.kind = NNF_ACT_PRELU;
+			else if (l.type_name == "ELU") a.kind = NNF_ACT_ELU;
+			else if (l.type_name == "TanH") { a.kind = NNF_ACT_TANH; a.p0 = l.scale; a.p1 = l.steepness; }
+			else if (l.type_name == "Sigmoid") a.kind = NNF_ACT_SIGMOID;
+			return a;
+		}
+
+		// ReLU/PReLU read their input in backward, the other three their output (the plain backend's dependencies)
+		bool backward_uses_input(const layer& l) { return l.type_name == "ReLU" || l.type_name == "PReLU"; }
+
+		nnf_pool make_pool(const layer& l, const layer_configuration_specific& in)
+		{
+			if (l.tiling)
+				throw neural_network_exception("max subsampling with tiling is not supported"); // the reference updater refuses it too
+			if (l.feature_map_subsampling_size != 1 || l.entry_subsampling_size != 1)
+				throw neural_network_exception("max subsampling over feature maps or entries is not supported");
+			if (l.subsampling_sizes.empty() || l.subsampling_sizes.size() > 2 || l.subsampling_sizes.size() != in.dimension_sizes.size())
+				throw neural_network_exception("max subsampling supports 1 or 2 spatial dimensions matching the input");
+			nnf_pool p;
+			std::memset(&p, 0, sizeof(p));
+			p.win_w = (int)l.subsampling_sizes[0];
+			p.stride_w = l.strides.empty() ? p.win_w : (int)l.strides[0];
+			p.round_up_w = (!l.round_ups.empty() && l.round_ups[0]) ? 1 : 0;
+			p.win_h = p.stride_h = 1;
+			if (l.subsampling_sizes.size() == 2)
+			{
+				p.win_h = (int)l.subsampling_sizes[1];
+				p.stride_h = l.strides.size() > 1 ? (int)l.strides[1] : p.win_h;
+				p.round_up_h = (l.round_ups.size() > 1 && l.round_ups[1]) ? 1 : 0;
+			}
+			p.is_min = l.is_min ? 1 : 0;
+			return p;
+		}
+
+		unsigned int dim(const layer_configuration_specific& c, size_t i) { return i < c.dimension_sizes.size() ? c.dimension_sizes[i] : 1; }
+
+		// ---- testers ---------------------------------------------------------------------------
+		class batch_norm_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (data.size() != 4)
+					throw neural_network_exception("BatchNorm expects 4 weight chunks: gamma, beta, mean, inverse sigma");
+				check(nnf_bn_infer_act(stream_id, f(output_buffer), f(input_buffers[0]), f(data[0]), f(data[1]), f(data[2]), f(data[3]),
+					nullptr, 1.0F, nullptr, 0, entry_count, output_configuration_specific.feature_map_count, output_elem_count_per_feature_map));
+			}
+			int get_input_index_layer_can_write() const override { return 0; }
+		};
+
+		class activation_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				const nnf_act a = make_act(*layer_schema, data.empty() ? nullptr : f(data[0]));
+				check(nnf_act_fwd(stream_id, f(output_buffer), f(input_buffers[0]), &a, entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map));
+			}
+			int get_input_index_layer_can_write() const override { return 0; }
+		};
+
+		class add_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				std::vector<const float *> in;
+				for (const auto& b : input_buffers)
+					in.push_back(f(b));
+				check(nnf_add_fwd(stream_id, f(output_buffer), in.data(), (int)in.size(), layer_schema->alpha, (int64_t)entry_count * output_elem_count_per_entry));
+			}
+			int get_input_index_layer_can_write() const override { return 0; }
+		};
+
+		class softmax_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				check(nnf_softmax_fwd(stream_id, f(output_buffer), f(input_buffers[0]), entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map));
+			}
+			int get_input_index_layer_can_write() const override { return 0; }
+		};
+
+		class max_subsampling_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_maxpool_fwd(stream_id, f(output_buffer), nullptr, f(input_buffers[0]), entry_count, in.feature_map_count, dim(in, 1), dim(in, 0), &pool));
+			}
+		protected:
+			void tester_configured() override { pool = make_pool(*layer_schema, input_configuration_specific_list[0]); }
+			nnf_pool pool;
+		};
+
+		// ---- updaters --------------------------------------------------------------------------
+		class activation_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				const nnf_act a = make_act(*layer_schema, data.empty() ? nullptr : f(data[0]));
+				check(nnf_act_fwd(stream_id, f(output_buffer), f(input_buffers[0]), &a, entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_neurons_buffers, device_buffer::const_ptr output_neurons_buffer,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				const nnf_act a = make_act(*layer_schema, data.empty() ? nullptr : f(data[0]));
+				const float * neurons = backward_uses_input(*layer_schema) ? f(input_neurons_buffers[0]) : f(output_neurons_buffer);
+				check(nnf_act_bwd(stream_id, f(input_errors_buffer), f(output_errors_buffer), neurons, &a, entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0));
+			}
+			void enqueue_backward_weights_propagation(cudaStream_t stream_id, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::ptr>& gradient, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_neurons_buffers, device_buffer::const_ptr output_errors_buffer,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr temporary_working_fixed_buffer, device_buffer::ptr,
+				device_buffer::const_ptr, device_buffer::const_ptr, unsigned int entry_count) override
+			{
+				if (layer_schema->type_name != "PReLU")
+					throw neural_network_exception("backward_weights requested from a layer without weights: " + layer_schema->type_name);
+				check(nnf_prelu_bwd_weights(stream_id, f(gradient[0]), f(output_errors_buffer), f(input_neurons_buffers[0]), entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map,
+					temporary_working_fixed_buffer ? static_cast<void *>(*temporary_working_fixed_buffer) : nullptr,
+					temporary_working_fixed_buffer ? temporary_working_fixed_buffer->get_size() : 0));
+			}
+			std::pair<size_t, bool> get_temporary_working_fixed_buffer_size(const layer_action& action) const override
+			{
+				if (action.get_action_type() == layer_action::backward_weights)
+					return std::make_pair(nnf_prelu_bwd_weights_workspace_bytes(1, output_configuration_specific.feature_map_count, output_elem_count_per_feature_map), false);
+				return std::make_pair(size_t(0), false);
+			}
+			int get_input_index_layer_can_write(const layer_action&) const override { return 0; }
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return backward_uses_input(*layer_schema); }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return !backward_uses_input(*layer_schema); }
+			bool is_backward_weights_dependent_on_input_buffer(unsigned int) const override { return true; }
+		};
+
+		class add_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				std::vector<const float *> in;
+				for (const auto& b : input_buffers)
+					in.push_back(f(b));
+				check(nnf_add_fwd(stream_id, f(output_buffer), in.data(), (int)in.size(), layer_schema->alpha, (int64_t)entry_count * output_elem_count_per_entry));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				check(nnf_add_bwd(stream_id, f(input_errors_buffer), f(output_errors_buffer), layer_schema->alpha,
+					(int64_t)entry_count * output_elem_count_per_entry, add_update_to_destination ? 1 : 0));
+			}
+			int get_input_index_layer_can_write(const layer_action&) const override { return 0; }
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
+		};
+
+		class softmax_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				check(nnf_softmax_fwd(stream_id, f(output_buffer), f(input_buffers[0]), entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr output_neurons_buffer,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				check(nnf_softmax_bwd(stream_id, f(input_errors_buffer), f(output_errors_buffer), f(output_neurons_buffer), entry_count,
+					output_configuration_specific.feature_map_count, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0));
+			}
+			int get_input_index_layer_can_write(const layer_action& action) const override { return action.get_action_type() == layer_action::backward_data ? 0 : -1; }
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return true; }
+		};
+
+		class max_subsampling_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr temporary_per_entry_buffer, unsigned int entry_count) override
+			{
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_maxpool_fwd(stream_id, f(output_buffer), temporary_per_entry_buffer ? static_cast<unsigned int *>(*temporary_per_entry_buffer) : nullptr,
+					f(input_buffers[0]), entry_count, in.feature_map_count, dim(in, 1), dim(in, 0), &pool));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr,
+				device_buffer::const_ptr temporary_per_entry_buffer, bool add_update_to_destination, unsigned int entry_count) override
+			{
+				if (!temporary_per_entry_buffer)
+					throw neural_network_exception("MaxSubsampling backward needs the argmax buffer written by its forward action");
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_maxpool_bwd(stream_id, f(input_errors_buffer), f(output_errors_buffer), static_cast<const unsigned int *>(*temporary_per_entry_buffer),
+					entry_count, in.feature_map_count, dim(in, 1), dim(in, 0), &pool, add_update_to_destination ? 1 : 0));
+			}
+			// absolute input offsets as unsigned int, the plain backend's format (max_subsampling_layer_updater_plain.cpp:256-264)
+			size_t get_temporary_per_entry_buffer_size() const override
+			{
+				return actions.count(layer_action(layer_action::backward_data, 0)) ? size_t(output_elem_count_per_entry) * sizeof(unsigned int) : 0;
+			}
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
+		protected:
+			void updater_configured() override { pool = make_pool(*layer_schema, input_configuration_specific_list[0]); }
+			nnf_pool pool;
+		};
+
+		// Training-mode batch norm. temporary_fixed_buffer = {mean, inverse std-dev} (2*C floats, as stock);
+		// temporary_working_fixed_buffer = the kernels' workspace followed by 2*C (forward) or 3*C (backward) floats of sums.
+		class batch_norm_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr temporary_working_fixed_buffer, device_buffer::ptr, device_buffer::ptr temporary_fixed_buffer, device_buffer::ptr,
+				unsigned int entry_count) override
+			{
+				const unsigned int c = output_configuration_specific.feature_map_count;
+				char * ws = working(temporary_working_fixed_buffer, 2);
+				float * sums = reinterpret_cast<float *>(ws + workspace_bytes());
+				check(nnf_bn_train_fwd(stream_id, f(output_buffer), f(temporary_fixed_buffer), sums, f(input_buffers[0]), f(data[0]), f(data[1]),
+					layer_schema->epsilon, nullptr, 0, entry_count, c, output_elem_count_per_feature_map, ws, workspace_bytes()));
+			}
+			void enqueue_backward_data_and_weights_propagation(cudaStream_t stream_id, const std::vector<device_buffer::ptr> input_errors_buffers,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::ptr>& gradient,
+				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_neurons_buffers, device_buffer::const_ptr, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr temporary_working_fixed_buffer, device_buffer::ptr, device_buffer::const_ptr temporary_fixed_buffer, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				if (gradient.size() != 4 || data.size() != 4)
+					throw neural_network_exception("BatchNorm expects 4 weight chunks and 4 gradient chunks");
+				const unsigned int c = output_configuration_specific.feature_map_count;
+				char * ws = working(temporary_working_fixed_buffer, 3);
+				float * bsums = reinterpret_cast<float *>(ws + workspace_bytes());
+				// gradient[0..3] = gamma, beta, mean, inverse sigma; running statistics are trained through the
+				// pseudo-gradients of batch_norm_layer_updater_cuda.cu:167-182
+				check(nnf_bn_train_bwd(stream_id, f(input_errors_buffers[0]), bsums, f(output_errors_buffer), f(input_neurons_buffers[0]), f(data[0]), f(data[1]),
+					f(temporary_fixed_buffer), nullptr, 0, f(gradient[0]), f(gradient[1]), f(gradient[2]), f(gradient[3]), nullptr, f(data[2]), f(data[3]),
+					(float)entry_count, entry_count, c, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0, ws, workspace_bytes()));
+			}
+			std::pair<size_t, bool> get_temporary_working_fixed_buffer_size(const layer_action& action) const override
+			{
+				const size_t c = output_configuration_specific.feature_map_count;
+				if (action.get_action_type() == layer_action::forward)
+					return std::make_pair(workspace_bytes() + 2 * c * sizeof(float), false);
+				if (action.get_action_type() == layer_action::backward_data_and_weights)
+					return std::make_pair(workspace_bytes() + 3 * c * sizeof(float), false);
+				return std::make_pair(size_t(0), false);
+			}
+			size_t get_temporary_fixed_buffer_size() const override { return size_t(output_configuration_specific.feature_map_count) * 2 * sizeof(float); }
+			int get_input_index_layer_can_write(const layer_action& action) const override { return action.get_action_type() == layer_action::backward_data_and_weights ? 0 : -1; }
+			bool is_backward_data_and_weights_dependent_on_input_buffer(unsigned int) const override { return true; }
+			bool is_backward_data_and_weights_dependent_on_output_buffer() const override { return false; }
+		private:
+			size_t workspace_bytes() const { return nnf_bn_train_workspace_bytes(1, output_configuration_specific.feature_map_count, output_elem_count_per_feature_map); }
+			char * working(const device_buffer::ptr& b, int sums) const
+			{
+				const size_t need = workspace_bytes() + size_t(sums) * output_configuration_specific.feature_map_count * sizeof(float);
+				if (!b || b->get_size() < need)
+					throw neural_network_exception("BatchNorm: temporary_working_fixed_buffer is missing or smaller than get_temporary_working_fixed_buffer_size()");
+				return static_cast<char *>(static_cast<void *>(*b));
+			}
+		};
+
+		bool is_activation(const std::string& t) { return t == "ReLU" || t == "PReLU" || t == "ELU" || t == "TanH" || t == "Sigmoid"; }
+	}
+
+	void layer_tester_b200::configure(const std::vector<layer_configuration_specific>& in, const layer_configuration_specific& out, layer::const_ptr schema)
+	{
+		layer_schema = schema;
+		input_configuration_specific_list = in;
+		output_configuration_specific = out;
+		output_elem_count_per_entry = out.get_neuron_count();
+		output_elem_count_per_feature_map = out.get_neuron_count_per_feature_map();
+		tester_configured();
+	}
+
+	void layer_updater_b200::configure(const std::vector<layer_configuration_specific>& in, const layer_configuration_specific& out, layer::const_ptr schema,
+		const std::set<layer_action>& acts)
+	{
+		layer_schema = schema;
+		input_configuration_specific_list = in;
+		output_configuration_specific = out;
+		output_elem_count_per_entry = out.get_neuron_count();
+		output_elem_count_per_feature_map = out.get_neuron_count_per_feature_map();
+		actions = acts;
+		updater_configured();
+	}
+
+	// Defaults of the reference base class: an action the layer does not implement is an error
+	// (nnforge/cuda/layer_updater_cuda.cpp throws "... is not implemented").
+	void layer_updater_b200::enqueue_backward_data_propagation(cudaStream_t, unsigned int, device_buffer::ptr, device_buffer::const_ptr,
+		const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+		const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr, const std::vector<device_buffer::const_ptr>&, device_buffer::ptr,
+		device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr, bool, unsigned int)
+	{
+		throw neural_network_exception("enqueue_backward_data_propagation is not implemented for layer " + layer_schema->type_name);
+	}
+
+	void layer_updater_b200::enqueue_backward_weights_propagation(cudaStream_t, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::ptr>&,
+		const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr,
+		const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr, unsigned int)
+	{
+		throw neural_network_exception("enqueue_backward_weights_propagation is not implemented for layer " + layer_schema->type_name);
+	}
+
+	void layer_updater_b200::enqueue_backward_data_and_weights_propagation(cudaStream_t, const std::vector<device_buffer::ptr>, device_buffer::const_ptr,
+		const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::ptr>&, const std::vector<device_buffer::const_ptr>&,
+		const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr,
+		const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr, bool, unsigned int)
+	{
+		throw neural_network_exception("enqueue_backward_data_and_weights_propagation is not implemented for layer " + layer_schema->type_name);
+	}
+
+	layer_factory_b200& layer_factory_b200::get_singleton()
+	{
+		static layer_factory_b200 instance;
+		return instance;
+	}
+
+	std::vector<std::string> layer_factory_b200::get_type_names() const
+	{
+		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling"};
+	}
+
+	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
+		const layer_configuration_specific& out) const
+	{
+		layer_tester_b200::ptr t;
+		const std::string& n = l->type_name;
+		if (n == "BatchNorm") t.reset(new batch_norm_layer_tester_b200());
+		else if (is_activation(n)) t.reset(new activation_layer_tester_b200());
+		else if (n == "Add") t.reset(new add_layer_tester_b200());
+		else if (n == "Softmax") t.reset(new softmax_layer_tester_b200());
+		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
+		else throw neural_network_exception("No layer tester is registered with id " + n);
+		t->configure(in, out, l);
+		return t;
+	}
+
+	layer_updater_b200::ptr layer_factory_b200::create_updater(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
+		const layer_configuration_specific& out, const std::set<layer_action>& actions) const
+	{
+		layer_updater_b200::ptr u;
+		const std::string& n = l->type_name;
+		if (n == "BatchNorm") u.reset(new batch_norm_layer_updater_b200());
+		else if (is_activation(n)) u.reset(new activation_layer_updater_b200());
+		else if (n == "Add") u.reset(new add_layer_updater_b200());
+		else if (n == "Softmax") u.reset(new softmax_layer_updater_b200());
+		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
+		else throw neural_network_exception("No layer updater is registered with id " + n);
+		u->configure(in, out, l, actions);
+		return u;
+	}
+
+	layer_configuration_specific get_output_layer_configuration_specific(const layer& l, const std::vector<layer_configuration_specific>& inputs)
+	{
+		layer_configuration_specific res = inputs.at(0);
+		if (l.type_name == "MaxSubsampling")
+		{
+			const nnf_pool p = make_pool(l, inputs[0]);
+			for (size_t i = 0; i < res.dimension_sizes.size(); ++i)
+			{
+				const int64_t o = nnf_pool_out_size(inputs[0].dimension_sizes[i], i == 0 ? p.win_w : p.win_h, i == 0 ? p.stride_w : p.stride_h, i == 0 ? p.round_up_w : p.round_up_h);
+				if (o <= 0)
+					throw neural_network_exception("Input configuration size of dimension " + std::to_string(i) + " produces 0 output size");
+				res.dimension_sizes[i] = (unsigned int)o;
+			}
+		}
+		return res;
+	}
+}
+
+// ---- flat driver interface for tests (ctypes) ----------------------------------------------------
+// Objects are created by type name through the factory; every call takes raw device pointers, wraps
+// them in non-owning buffers and forwards to the C++ member with the reference's argument order.
+// Return 0 on success; on an exception -1, with the text available from nnfh_last_error().
+using namespace nnf_b200;
+
+namespace
+{
+	thread_local std::string g_error;
+
+	struct handle
+	{
+		std::shared_ptr<layer> schema;
+		layer_tester_b200::ptr tester;
+		layer_updater_b200::ptr updater;
+	};
+
+	device_buffer::ptr buf(void * p, size_t bytes = size_t(1) << 40) { return p ? device_buffer::ptr(new device_buffer(p, bytes)) : device_buffer::ptr(); }
+	device_buffer::const_ptr cbuf(const void * p) { return p ? device_buffer::const_ptr(new device_buffer(const_cast<void *>(p), size_t(1) << 40)) : device_buffer::const_ptr(); }
+	std::vector<device_buffer::const_ptr> cvec(const void * const * p, int n)
+	{
+		std::vector<device_buffer::const_ptr> v;
+		for (int i = 0; i < n; ++i)
+			v.push_back(cbuf(p[i]));
+		return v;
+	}
+	std::vector<device_buffer::ptr> vec(void * const * p, int n)
+	{
+		std::vector<device_buffer::ptr> v;
+		for (int i = 0; i < n; ++i)
+			v.push_back(buf(p[i]));
+		return v;
+	}
+}
+
+#define NNFH_API extern "C" __attribute__((visibility("default")))
+#define NNFH_TRY try {
+#define NNFH_CATCH } catch (const std::exception& e) { g_error = e.what(); return -1; } return 0;
+
+NNFH_API const char * nnfh_last_error() { return g_error.c_str(); }
+
+// params: negative_slope | scale, steepness | alpha | epsilon, by layer type; pool = {win_w, win_h, stride_w, stride_h, round_up_w, round_up_h, is_min}
+NNFH_API void * nnfh_create(const char * type_name, int updater, const float * params, const int * pool, unsigned int feature_maps, unsigned int w, unsigned int h,
+	int input_count, int with_backward)
+{
+	try
+	{
+		std::unique_ptr<handle> hd(new handle());
+		hd->schema.reset(new layer());
+		layer& l = *hd->schema;
+		l.type_name = type_name;
+		if (l.type_name == "ReLU") l.negative_slope = params[0];
+		if (l.type_name == "TanH") { l.scale = params[0]; l.steepness = params[1]; }
+		if (l.type_name == "Add") l.alpha = params[0];
+		if (l.type_name == "BatchNorm") l.epsilon = params[0];
+		if (l.type_name == "MaxSubsampling")
+		{
+			l.subsampling_sizes = {(unsigned int)pool[0], (unsigned int)pool[1]};
+			l.strides = {(unsigned int)pool[2], (unsigned int)pool[3]};
+			l.round_ups = {pool[4] != 0, pool[5] != 0};
+			l.is_min = pool[6] != 0;
+		}
+		layer_configuration_specific in;
+		in.feature_map_count = feature_maps;
+		in.dimension_sizes = {w, h};
+		std::vector<layer_configuration_specific> ins(input_count, in);
+		const layer_configuration_specific out = get_output_layer_configuration_specific(l, ins);
+		if (updater)
+		{
+			std::set<layer_action> actions;
+			actions.insert(layer_action(layer_action::forward));
+			if (with_backward)
+				actions.insert(l.type_name == "BatchNorm" ? layer_action(layer_action::backward_data_and_weights) : layer_action(layer_action::backward_data, 0));
+			hd->updater = layer_factory_b200::get_singleton().create_updater(hd->schema, ins, out, actions);
+		}
+		else
+			hd->tester = layer_factory_b200::get_singleton().create_tester(hd->schema, ins, out);
+		return hd.release();
+	}
+	catch (const std::exception& e)
+	{
+		g_error = e.what();
+		return nullptr;
+	}
+}
+
+NNFH_API void nnfh_destroy(void * h) { delete static_cast<handle *>(h); }
+
+NNFH_API int nnfh_tester_forward(void * h, void * stream, void * out, const void * const * data, int n_data, const void * const * inputs, int n_inputs, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->tester->enqueue_forward_propagation((cudaStream_t)stream, buf(out), {}, cvec(data, n_data), {}, cvec(inputs, n_inputs), {},
+		device_buffer::ptr(), device_buffer::ptr(), entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_tester_can_write(void * h) { return static_cast<handle *>(h)->tester->get_input_index_layer_can_write(); }
+
+NNFH_API long long nnfh_updater_query(void * h, int what, int action)
+{
+	layer_updater_b200& u = *static_cast<handle *>(h)->updater;
+	const layer_action a((layer_action::action_type)action, action == layer_action::backward_data ? 0 : -1);
+	switch (what)
+	{
+	case 0: return (long long)u.get_temporary_working_fixed_buffer_size(a).first;
+	case 1: return (long long)u.get_temporary_fixed_buffer_size();
+	case 2: return (long long)u.get_temporary_per_entry_buffer_size();
+	case 3: return u.get_input_index_layer_can_write(a);
+	case 4: return u.is_backward_data_dependent_on_input_buffer(0, 0);
+	case 5: return u.is_backward_data_dependent_on_output_buffer(0);
+	default: return -1;
+	}
+}
+
+NNFH_API int nnfh_updater_forward(void * h, void * stream, void * out, const void * const * data, int n_data, const void * const * inputs, int n_inputs,
+	void * working_fixed, size_t working_fixed_bytes, void * temp_fixed, void * temp_per_entry, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_forward_propagation((cudaStream_t)stream, buf(out), {}, cvec(data, n_data), {}, cvec(inputs, n_inputs), {},
+		buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), buf(temp_fixed), buf(temp_per_entry), entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_updater_backward_data(void * h, void * stream, void * in_err, const void * out_err, const void * const * data, int n_data,
+	const void * in_neurons, const void * out_neurons, const void * temp_fixed, const void * temp_per_entry, int add_update_to_destination, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_data_propagation((cudaStream_t)stream, 0, buf(in_err), cbuf(out_err), {}, cvec(data, n_data), {},
+		std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), cbuf(out_neurons), {}, device_buffer::ptr(), device_buffer::ptr(),
+		cbuf(temp_fixed), cbuf(temp_per_entry), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_updater_backward_weights(void * h, void * stream, void * const * gradient, int n_gradient, const void * in_neurons, const void * out_err,
+	void * working_fixed, size_t working_fixed_bytes, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_weights_propagation((cudaStream_t)stream, {}, vec(gradient, n_gradient), {},
+		std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), cbuf(out_err), {}, buf(working_fixed, working_fixed_bytes), device_buffer::ptr(),
+		device_buffer::const_ptr(), device_buffer::const_ptr(), entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_updater_backward_data_and_weights(void * h, void * stream, void * in_err, const void * out_err, void * const * gradient, int n_gradient,
+	const void * const * data, int n_data, const void * in_neurons, void * working_fixed, size_t working_fixed_bytes, const void * temp_fixed,
+	int add_update_to_destination, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_data_and_weights_propagation((cudaStream_t)stream, std::vector<device_buffer::ptr>(1, buf(in_err)), cbuf(out_err), {},
+		vec(gradient, n_gradient), cvec(data, n_data), {}, std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), device_buffer::const_ptr(), {},
+		buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), cbuf(temp_fixed), device_buffer::const_ptr(), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}

@@ -1,0 +1,81 @@
+"""Host-side sequence of a batch-sharded (synchronised) training batch norm + activation chain.
+
+One process per GPU; every rank holds a contiguous slab of the batch. The only communication is one
+all-reduce of 2*C floats in the forward pass ({sum x, sum x^2}) and one in the backward pass
+({sum du, sum du*xhat}); everything else is per-rank work. nnForge itself does not synchronise batch
+statistics across devices (its multi-GPU path all-reduces weight gradients only,
+nnforge/cuda/backward_propagation_cuda.cpp:963-971), so with one rank the result equals the reference's.
+
+`kernels` is the compute backend: on a GPU `nnforge_b200.capi`; the CPU tests pass an adapter over the
+checker so that this file's logic (buffer roles, what is reduced, which sums feed which call) runs under
+`gloo` without a GPU. The per-channel weight gradients accumulate the LOCAL sums, as the reference
+leaves their cross-device sum to its own gradient all-reduce.
+"""
+import torch
+import torch.distributed as dist
+
+
+def _world(group):
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+class ShardedBatchNormAct:
+    def __init__(self, kernels, channels, eps, acts, device, group=None, on_phase=None):
+        self.k = kernels
+        self.on_phase = on_phase or (lambda name: None)  # called after each enqueue, e.g. to record CUDA events
+        self.c = channels
+        self.eps = eps
+        self.acts = list(acts)
+        self.group = group
+        self.world = _world(group)
+        f = dict(dtype=torch.float32, device=device)
+        self.sums = torch.zeros(2 * channels, **f)     # forward message
+        self.saved = torch.zeros(2 * channels, **f)    # {mean, invstd}: the reference's temporary_fixed_buffer
+        self.bsums = torch.zeros(3 * channels, **f)    # local {sum du, sum du*xhat, sum dslope}
+        self.gsums = torch.zeros(2 * channels, **f)    # backward message
+        self.workspace = None
+
+    def _ws(self, x):
+        n, c = x.shape[0], x.shape[1]
+        hw = x.numel() // max(n * c, 1)
+        need = self.k.bn_train_workspace_bytes(n, c, hw)
+        if self.workspace is None or self.workspace.numel() < need:
+            self.workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        return self.workspace
+
+    def count_total(self, x, global_entries=None):
+        n, c = x.shape[0], x.shape[1]
+        hw = x.numel() // max(n * c, 1)
+        entries = global_entries if global_entries is not None else n * self.world
+        return float(entries * hw)
+
+    def forward(self, y, x, gamma, beta, global_entries=None):
+        m = self.count_total(x, global_entries)
+        self.on_phase("start")
+        self.k.bn_train_stats(self.sums, x, self._ws(x))
+        self.on_phase("stats")
+        if self.world > 1:
+            dist.all_reduce(self.sums, group=self.group)
+        self.on_phase("allreduce_fwd")
+        self.k.bn_train_apply_act(y, self.saved, x, gamma, beta, self.sums, m, self.eps, self.acts)
+        self.on_phase("apply")
+        return y
+
+    def backward(self, dx, dy, x, gamma, beta, grads=None, running=None, global_entries=None, add_to_destination=False):
+        """grads: dict with optional 'gamma', 'beta', 'slope', 'mean', 'invsigma' accumulators;
+        running: (mean, invsigma) when the running-statistics pseudo-gradients are wanted."""
+        m = self.count_total(x, global_entries)
+        grads = grads or {}
+        sharded = self.world > 1
+        self.k.bn_train_bwd_stats(self.bsums, dy, x, gamma, beta, self.saved, self.acts, self._ws(x), gsums=self.gsums if sharded else None)
+        self.on_phase("bwd_stats")
+        if sharded:
+            dist.all_reduce(self.gsums, group=self.group)
+        self.on_phase("allreduce_bwd")
+        mean, invsigma = running if running is not None else (None, None)
+        self.k.bn_train_bwd_apply(dx, dy, x, gamma, beta, self.saved, self.gsums if sharded else self.bsums, self.bsums, m, self.acts,
+                                  grad_gamma=grads.get("gamma"), grad_beta=grads.get("beta"), grad_mean=grads.get("mean"),
+                                  grad_invsigma=grads.get("invsigma"), grad_slope=grads.get("slope"), mean=mean, invsigma=invsigma,
+                                  entry_count=float(x.shape[0]), add_to_destination=add_to_destination)
+        self.on_phase("bwd_apply")
+        return dx
