@@ -275,6 +275,8 @@ namespace nnf
 			int group;
 			int vec_ok;
 			int add;               // stand-alone only
+			int row4_vec;          // 3x3/2 fast path: rows are whole float4s (W % 4 == 0, aligned buffers)
+			fastdiv d_cpr, d_hcpr; // 3x3/2 fast path with ragged rows: chunks per row, chunks per plane
 		};
 
 		// Gradient reaching input element (iy, ix) of a plane whose pooled gradients / argmax start at
@@ -326,7 +328,50 @@ namespace nnf
 			return sum;
 		}
 
-		template <bool FUSED, int WW, int WH, int SW, int SH>
+		// 3x3 windows, stride 2, four consecutive elements of one input row (W % 4 == 0). The four elements
+		// share their candidate windows: rows {oy_lo..oy_hi} (at most two) and columns {k-1, k, k+1} with
+		// k = ix0/2, so a vector needs 6 (argmax, gradient) pairs instead of 16. Within a row the columns
+		// are visited in ascending order, rows in ascending order: ascending output index per element.
+		__device__ __forceinline__ void gather_row4_3x3s2(const pool_geom& g, const float * dyp, const uint32_t * idp, uint32_t iy, uint32_t ix0,
+			uint32_t abs0, float (&acc)[4])
+		{
+			const uint32_t r0 = iy < 3 ? 0u : ((iy - 3) >> 1) + 1u;
+			const uint32_t r1 = min(iy >> 1, g.oh - 1);
+			const uint32_t k = ix0 >> 1;
+			const bool c0 = k >= 1 && k - 1 <= g.ow - 1, c1 = k <= g.ow - 1, c2 = k + 1 <= g.ow - 1;
+			#pragma unroll
+			for (int a = 0; a < 2; ++a)
+			{
+				const uint32_t oy = r0 + a;
+				if (oy <= r1)
+				{
+					const uint32_t row = oy * g.ow + k;
+					if (c0)
+					{
+						const uint32_t i = idp[row - 1];
+						const float d = dyp[row - 1];
+						if (i == abs0) acc[0] = __fadd_rn(acc[0], d);
+					}
+					if (c1)
+					{
+						const uint32_t i = idp[row];
+						const float d = dyp[row];
+						if (i == abs0) acc[0] = __fadd_rn(acc[0], d);
+						if (i == abs0 + 1) acc[1] = __fadd_rn(acc[1], d);
+						if (i == abs0 + 2) acc[2] = __fadd_rn(acc[2], d);
+					}
+					if (c2)
+					{
+						const uint32_t i = idp[row + 1];
+						const float d = dyp[row + 1];
+						if (i == abs0 + 2) acc[2] = __fadd_rn(acc[2], d);
+						if (i == abs0 + 3) acc[3] = __fadd_rn(acc[3], d);
+					}
+				}
+			}
+		}
+
+		template <bool FUSED, int WW, int WH, int SW, int SH, bool ROW4 = false>
 		__global__ void __launch_bounds__(kThreads) pool_bwd_staged_kernel(const pool_bwd_params p)
 		{
 			extern __shared__ float s_raw[];
@@ -334,6 +379,7 @@ namespace nnf
 			const int64_t ngroups = (p.planes + p.group - 1) / p.group;
 			float * s_dy = s_raw;
 			uint32_t * s_idx = reinterpret_cast<uint32_t *>(s_raw + size_t(p.group) * g.ohw);
+			float * s_dz = s_raw + ((size_t(p.group) * g.ohw * 2 + 3) & ~size_t(3)); // ragged-row fused path only
 			for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
 			{
 				const int64_t plane0 = grp * p.group;
@@ -377,7 +423,81 @@ namespace nnf
 						out_dx = dz;
 				};
 
-				if (p.vec_ok)
+				if (ROW4 && !p.row4_vec)
+				{
+					// rows that are not a multiple of four elements (14x14, 7x7): the same four-element row
+					// chunks, with scalar accesses and the last chunk of a row cut short
+					const uint32_t cpr = (g.w + 3) >> 2;           // chunks per row
+					const uint32_t nchunks = np * g.h * cpr;
+					for (uint32_t q = threadIdx.x; q < nchunks; q += kThreads)
+					{
+						const uint32_t lp = p.d_hcpr.div(q);
+						const uint32_t rem = q - lp * (g.h * cpr);
+						const uint32_t iy = p.d_cpr.div(rem);
+						const uint32_t ix0 = (rem - iy * cpr) << 2;
+						const uint32_t e0 = lp * g.hw + iy * g.w + ix0;
+						const uint32_t nvalid = min(4u, g.w - ix0);
+						float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+						if (!FUSED && p.add)
+						{
+							#pragma unroll
+							for (int k = 0; k < 4; ++k)
+								if ((uint32_t)k < nvalid)
+									acc[k] = p.dx[base + e0 + k];
+						}
+						gather_row4_3x3s2(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix0, (uint32_t)(base + e0), acc);
+						#pragma unroll
+						for (int k = 0; k < 4; ++k)
+							if ((uint32_t)k < nvalid)
+							{
+								if (FUSED)
+									s_dz[e0 + k] = acc[k]; // gathered gradient of the group, consumed with coalesced accesses below
+								else
+									p.dx[base + e0 + k] = acc[k];
+							}
+					}
+					if (FUSED)
+					{
+						__syncthreads();
+						auto finish = [&](uint32_t e, float zval, float dz, float& odx, float& ores)
+						{
+							const float ds = (__float_as_uint(zval) >> 31) ? __fmul_rn(dz, p.slope) : dz;
+							ores = ds;
+							odx = ds;
+							if (p.gamma)
+							{
+								uint32_t channel = ch0 + g.d_hw.div(e);
+								channel -= g.d_c.div(channel) * g.c;
+								odx = __fmul_rn(ds, __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel)));
+							}
+						};
+						const uint32_t nvec = p.vec_ok ? (count >> 2) : 0;
+						for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
+						{
+							const float4 z4 = ld_stream(reinterpret_cast<const float4 *>(p.z + base) + v);
+							const float4 d4 = reinterpret_cast<const float4 *>(s_dz)[v];
+							float4 ox, orr;
+							finish((v << 2), z4.x, d4.x, ox.x, orr.x);
+							finish((v << 2) + 1, z4.y, d4.y, ox.y, orr.y);
+							finish((v << 2) + 2, z4.z, d4.z, ox.z, orr.z);
+							finish((v << 2) + 3, z4.w, d4.w, ox.w, orr.w);
+							if (p.dx)
+								st_stream(reinterpret_cast<float4 *>(p.dx + base) + v, ox);
+							if (p.dres)
+								st_stream(reinterpret_cast<float4 *>(p.dres + base) + v, orr);
+						}
+						for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kThreads)
+						{
+							float odx, ores;
+							finish(e, p.z[base + e], s_dz[e], odx, ores);
+							if (p.dx)
+								p.dx[base + e] = odx;
+							if (p.dres)
+								p.dres[base + e] = ores;
+						}
+					}
+				}
+				else if (p.vec_ok)
 				{
 					const uint32_t nvec = count >> 2;
 					for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
@@ -395,9 +515,39 @@ namespace nnf
 							seed[0] = d4.x; seed[1] = d4.y; seed[2] = d4.z; seed[3] = d4.w;
 						}
 						float odx[4], ores[4];
-						#pragma unroll
-						for (int k = 0; k < 4; ++k)
-							element((v << 2) + k, zv[k], seed[k], odx[k], ores[k]);
+						if (ROW4)
+						{
+							const uint32_t e0 = v << 2;
+							const uint32_t lp = g.d_hw.div(e0);
+							const uint32_t rem = e0 - lp * g.hw;
+							const uint32_t iy = g.d_w.div(rem);
+							gather_row4_3x3s2(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, rem - iy * g.w, (uint32_t)(base + e0), seed);
+							float mult = 1.0F;
+							if (FUSED && p.gamma)
+							{
+								uint32_t channel = ch0 + lp;
+								channel -= g.d_c.div(channel) * g.c;
+								mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+							}
+							#pragma unroll
+							for (int k = 0; k < 4; ++k)
+							{
+								if (FUSED)
+								{
+									const float ds = (__float_as_uint(zv[k]) >> 31) ? __fmul_rn(seed[k], p.slope) : seed[k];
+									ores[k] = ds;
+									odx[k] = p.gamma ? __fmul_rn(ds, mult) : ds;
+								}
+								else
+									odx[k] = seed[k];
+							}
+						}
+						else
+						{
+							#pragma unroll
+							for (int k = 0; k < 4; ++k)
+								element((v << 2) + k, zv[k], seed[k], odx[k], ores[k]);
+						}
 						if (p.dx)
 							st_stream(reinterpret_cast<float4 *>(p.dx + base) + v, make_float4(odx[0], odx[1], odx[2], odx[3]));
 						if (FUSED && p.dres)
@@ -465,7 +615,7 @@ namespace nnf
 		{
 			static int waves = 0;
 			if (waves == 0)
-				waves = getenv("NNF_POOL_WAVES") ? atoi(getenv("NNF_POOL_WAVES")) : 1;
+				waves = getenv("NNF_POOL_WAVES") ? atoi(getenv("NNF_POOL_WAVES")) : 4;
 			return waves < 1 ? 1 : waves;
 		}
 
@@ -495,7 +645,8 @@ namespace nnf
 		// planes per CTA iteration; 0 -> does not fit shared memory
 		int choose_group(const pool_geom& g, int64_t planes, bool& vec_ok)
 		{
-			const int64_t group_floats = getenv("NNF_POOL_GROUP") ? atoi(getenv("NNF_POOL_GROUP")) : kGroupFloats; // tuning aid
+			// measured: 32 KB groups for large planes (56x56), 16 KB for small ones (more CTAs per SM)
+			const int64_t group_floats = getenv("NNF_POOL_GROUP") ? atoi(getenv("NNF_POOL_GROUP")) : (g.hw >= 2048 ? kGroupFloats : kGroupFloats / 2); // env: tuning aid
 			int64_t grp = group_floats / g.hw;
 			if (grp < 1)
 				grp = 1;
@@ -587,7 +738,8 @@ namespace nnf
 				return set_error(NNF_ERR_UNSUPPORTED, "max subsampling: argmax offsets need n*c*h*w < 2^32");
 			bool vec_ok = (!p.dx || aligned16(p.dx)) && (!fused || (aligned16(p.z) && (!p.dres || aligned16(p.dres))));
 			const int grp = choose_group(p.g, p.planes, vec_ok);
-			const size_t smem = size_t(grp) * p.g.ohw * 2 * sizeof(float);
+			const bool ragged_fast = fused && p.g.win_w == 3 && p.g.win_h == 3 && p.g.sw == 2 && p.g.sh == 2 && !((p.g.w & 3) == 0 && vec_ok);
+			const size_t smem = (((size_t(grp) * p.g.ohw * 2 + 3) & ~size_t(3)) + (ragged_fast ? size_t(grp) * p.g.hw : 0)) * sizeof(float);
 			if (grp == 0 || smem > kMaxDynSmem)
 			{
 				const int64_t blocks = div_up(p.planes * p.g.hw, kThreads);
@@ -613,8 +765,17 @@ namespace nnf
 				if (e == cudaSuccess) \
 					pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH><<<grid, kThreads, smem, s>>>(p); \
 			}
+			p.row4_vec = ((p.g.w & 3) == 0 && p.vec_ok) ? 1 : 0;
+			p.d_cpr = fastdiv((p.g.w + 3) / 4);
+			p.d_hcpr = fastdiv(p.g.h * ((p.g.w + 3) / 4));
 #define NNF_POOL_BWD_SHAPE(FUSED) \
-			if (ww == 3 && wh == 3 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 3, 3, 2, 2) \
+			if (ww == 3 && wh == 3 && sw == 2 && sh == 2) \
+			{ \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				if (e == cudaSuccess) \
+					pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true><<<grid, kThreads, smem, s>>>(p); \
+			} \
+			else if (ww == 3 && wh == 3 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 3, 3, 2, 2) \
 			else if (ww == 2 && wh == 2 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 2, 2, 2, 2) \
 			else NNF_POOL_BWD(FUSED, 0, 0, 0, 0)
 			if (fused)
