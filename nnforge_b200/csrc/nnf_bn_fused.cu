@@ -339,6 +339,8 @@ namespace nnf
 			uint32_t it = 0;
 			for (uint32_t ch = cluster_id; ch < p.c; ch += nclusters, ++it)
 			{
+				unsigned long long * tr = (p.trace && threadIdx.x == 0 && it < 32) ? p.trace + (size_t(blockIdx.x) * 32 + it) * 5 : nullptr;
+				if (tr) tr[0] = global_timer();
 				const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
 				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
 				const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
@@ -382,8 +384,10 @@ namespace nnf
 							slab4[i] = make_float4(element(a[u].x, d[u].x), element(a[u].y, d[u].y), element(a[u].z, d[u].z), element(a[u].w, d[u].w));
 					}
 				}
+				if (tr) tr[1] = global_timer();
 				double acc[3] = {double(sb), double(sg), double(ss)};
 				block_sum_all<3>(acc, s_red);
+				if (tr) tr[2] = global_timer();
 
 				// exchange through distributed shared memory, double-buffered by iteration parity
 				const uint32_t buf = it & 1;
@@ -395,6 +399,7 @@ namespace nnf
 				}
 				__syncwarp();
 				cluster_sync_all();
+				if (tr) tr[3] = global_timer();
 				double tb = 0.0, tg = 0.0, tsl = 0.0;
 				for (uint32_t r = 0; r < p.cluster; ++r)
 				{
@@ -460,6 +465,7 @@ namespace nnf
 					}
 				}
 				__syncthreads(); // du of this channel is consumed; the slab may be overwritten
+				if (tr) tr[4] = global_timer();
 			}
 		}
 
@@ -470,10 +476,22 @@ namespace nnf
 		// result out with evict-first stores. No shared-memory slab, so any N and H*W fit; the number of
 		// channels in flight (and with it the L2 footprint) is bounded by a shared-memory reservation that
 		// limits how many CTAs an SM holds.
+#ifndef NNF_L2_THREADS
+#define NNF_L2_THREADS 512
+#endif
+#ifndef NNF_L2_MIN_CTAS
+#define NNF_L2_MIN_CTAS 3
+#endif
+#ifndef NNF_L2_UNROLL
+#define NNF_L2_UNROLL 2
+#endif
+		constexpr int kL2Threads = NNF_L2_THREADS;
+		constexpr int kL2MinCtas = NNF_L2_MIN_CTAS;
+
 		template <int A0, int A1>
-		__global__ void __launch_bounds__(512, 2) bn_train_fwd_l2_kernel(const fused_params p)
+		__global__ void __launch_bounds__(kL2Threads, kL2MinCtas) bn_train_fwd_l2_kernel(const fused_params p)
 		{
-			__shared__ double s_red[16 * 2];
+			__shared__ double s_red[32 * 2];
 			__shared__ double s_exch[kMaxCluster][2];
 			const uint32_t rank = cluster_rank();
 			const uint32_t ch = blockIdx.x / p.cluster;
@@ -484,7 +502,7 @@ namespace nnf
 			const uint32_t nvec = np * vpp;
 			const size_t entry_stride = size_t(p.c) * p.hw;
 			const size_t base = size_t(e0) * entry_stride + size_t(ch) * p.hw;
-			constexpr int kU = 4;
+			constexpr int kU = NNF_L2_UNROLL;
 
 			float s = 0.0F, q = 0.0F;
 			for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU)
@@ -578,9 +596,9 @@ namespace nnf
 		}
 
 		template <int A0, int A1>
-		__global__ void __launch_bounds__(512, 2) bn_train_bwd_l2_kernel(const fused_params p)
+		__global__ void __launch_bounds__(kL2Threads, kL2MinCtas) bn_train_bwd_l2_kernel(const fused_params p)
 		{
-			__shared__ double s_red[16 * 3];
+			__shared__ double s_red[32 * 3];
 			__shared__ double s_exch[kMaxCluster][3];
 			const uint32_t rank = cluster_rank();
 			const uint32_t ch = blockIdx.x / p.cluster;
@@ -846,11 +864,12 @@ namespace nnf
 			int ctas_per_sm = int(budget / (slab * double(kSmCount) / cl));
 			if (ctas_per_sm < 1)
 				return false; // even one CTA per SM would overflow the budget: use the two-kernel form
-			if (ctas_per_sm > 4)
-				ctas_per_sm = 4;
+			const int max_ctas = 2048 / kL2Threads;
+			if (ctas_per_sm >= max_ctas)
+				ctas_per_sm = max_ctas;
 			plan.cluster = cl;
 			plan.planes_per_cta = (uint32_t)div_up(n, cl);
-			plan.reserve_smem = ctas_per_sm >= 4 ? 0 : size_t(225 * 1024) / ctas_per_sm - 2048;
+			plan.reserve_smem = ctas_per_sm >= max_ctas ? 0 : size_t(225 * 1024) / ctas_per_sm - 2048;
 			return true;
 		}
 
@@ -865,7 +884,7 @@ namespace nnf
 			attr.id = cudaLaunchAttributeClusterDimension;
 			attr.val.clusterDim.x = plan.cluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
 			cfg.gridDim = dim3(p.c * plan.cluster, 1, 1);
-			cfg.blockDim = dim3(512, 1, 1);
+			cfg.blockDim = dim3(kL2Threads, 1, 1);
 			cfg.dynamicSmemBytes = plan.reserve_smem;
 			cfg.stream = s;
 			cfg.attrs = &attr;
@@ -1102,5 +1121,9 @@ extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, 
 	p.count = double(n) * double(hw);
 	p.error = error_word();
 	p.stagger_ns = getenv("NNF_FUSED_STAGGER_NS") ? (uint32_t)atoi(getenv("NNF_FUSED_STAGGER_NS")) : 0;
+	{
+		const char * t = getenv("NNF_FUSED_TRACE"); // tuning aid: address of a device buffer, as a decimal number
+		p.trace = t ? reinterpret_cast<unsigned long long *>(strtoull(t, nullptr, 10)) : nullptr;
+	}
 	return launch_fused(kernel, plan, p, (cudaStream_t)stream, "bn_train_bwd_cluster_kernel");
 }

@@ -102,7 +102,7 @@ namespace nnf
 							if (i < total)
 							{
 								const uint32_t lp = g.d_vpp.div(i);
-								a[u] = ld_stream(reinterpret_cast<const float4 *>(base + lp * entry_stride) + (i - lp * per_plane));
+								a[u] = __ldg(reinterpret_cast<const float4 *>(base + lp * entry_stride) + (i - lp * per_plane)); // default policy: stays in L2
 							}
 						}
 						#pragma unroll
@@ -230,8 +230,10 @@ namespace nnf
 		__global__ void __launch_bounds__(kThreads) bn_bwd_stats_kernel(double * partial, const bwd_params p, chan_geom g)
 		{
 			__shared__ double s_red[(kThreads / 32) * 3];
-			const uint32_t ch = blockIdx.x / g.split;
-			const uint32_t sp = blockIdx.x - ch * g.split;
+			// channels in descending order: whatever ran before (the forward kernels walk the channels upwards)
+			// left the highest channels of x in L2; bn_bwd_apply_kernel then walks upwards again
+			const uint32_t ch = g.c - 1 - blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x % g.split;
 			const uint32_t e0 = sp * g.entries_per_cta;
 			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
 			const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + g.c + ch);
@@ -268,8 +270,8 @@ namespace nnf
 							{
 								const uint32_t lp = g.d_vpp.div(i);
 								const size_t off = off0 + lp * entry_stride;
-								a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + off) + (i - lp * per_plane));
-								d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + off) + (i - lp * per_plane));
+								a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + off) + (i - lp * per_plane));   // default policy: the channels
+								d[u] = __ldg(reinterpret_cast<const float4 *>(p.dy + off) + (i - lp * per_plane));  // read last stay in L2 for bn_bwd_apply_kernel
 							}
 						}
 						#pragma unroll
@@ -310,8 +312,10 @@ namespace nnf
 		template <int A0, int A1>
 		__global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const bwd_params p, chan_geom g)
 		{
+			// channels in ascending order: bn_bwd_stats_kernel, which ran just before, walked them downwards with
+			// default-policy loads, so the channels it read last (the lowest, ~100 MB still in L2) come first
 			const uint32_t ch = blockIdx.x / g.split;
-			const uint32_t sp = blockIdx.x - ch * g.split;
+			const uint32_t sp = blockIdx.x % g.split;
 			const uint32_t e0 = sp * g.entries_per_cta;
 			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
 			const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + g.c + ch);
@@ -391,6 +395,81 @@ namespace nnf
 						}
 					}
 				}
+			}
+		}
+
+		// Training-mode normalisation + activation chain, one CTA per (channel, slice of entries), channels in
+		// DESCENDING order. It runs right after bn_stats_kernel, which walked the channels in ascending order
+		// with default-policy loads: the ~100 MB that kernel read last are still in L2 and are consumed first
+		// here, so part of the second read of x never reaches HBM. (The flat streaming kernel of
+		// nnf_elementwise.cu computes the same values in memory order and is used for shapes this one does
+		// not take.)
+		struct apply_params
+		{
+			float * y;
+			const float * x;
+			const float * gamma;
+			const float * beta;
+			const float * sums;
+			float * saved;
+			double count_total;
+			float eps;
+			act_chain chain;
+		};
+
+		template <int A0, int A1>
+		__global__ void __launch_bounds__(kThreads) bn_apply_channel_kernel(const apply_params p, chan_geom g)
+		{
+			const uint32_t ch = g.c - 1 - blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x % g.split;
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			// batch statistics of this channel: biased variance from the (all-reduced) sum and sum of squares
+			const double m = double(__ldg(p.sums + ch)) / p.count_total;
+			double var = double(__ldg(p.sums + g.c + ch)) / p.count_total - m * m;
+			var = var < 0.0 ? 0.0 : var;
+			const float mean = float(m);
+			const float invstd = float(1.0 / sqrt(var + double(p.eps)));
+			if (sp == 0 && threadIdx.x == 0 && p.saved)
+			{
+				p.saved[ch] = mean;
+				p.saved[g.c + ch] = invstd;
+			}
+			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			const float slope = chain_slope(p.chain, ch);
+			if (e0 >= e1)
+				return;
+			const uint32_t per_plane = g.hw >> 2;
+			const uint32_t total = (e1 - e0) * per_plane;
+			const size_t entry_stride = size_t(g.c) * g.hw;
+			const size_t off0 = (size_t(e0) * g.c + ch) * g.hw;
+			for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kThreads * kLoads)
+			{
+				float4 a[kLoads];
+				size_t pos[kLoads];
+				#pragma unroll
+				for (int u = 0; u < kLoads; ++u)
+				{
+					const uint32_t i = i0 + u * kThreads;
+					if (i < total)
+					{
+						const uint32_t lp = g.d_vpp.div(i);
+						pos[u] = off0 + lp * entry_stride + size_t(i - lp * per_plane) * 4;
+						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos[u]));
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kLoads; ++u)
+					if (i0 + u * kThreads < total)
+					{
+						float4 o;
+						o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].x, mult), add), slope);
+						o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult), add), slope);
+						o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult), add), slope);
+						o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult), add), slope);
+						st_stream(reinterpret_cast<float4 *>(p.y + pos[u]), o);
+					}
 			}
 		}
 
@@ -497,6 +576,30 @@ extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * sa
 	st = make_chain(chain, acts, n_acts, true);
 	if (st != NNF_OK)
 		return st;
+	int prelus = 0;
+	for (int i = 0; i < chain.n; ++i)
+		prelus += chain.a[i].kind == NNF_ACT_PRELU;
+	// planes large enough to keep a CTA busy and whole float4s: the channel-ordered kernel (L2 reuse after the
+	// statistics kernel); anything else: the flat streaming kernel
+	if (hw % 4 == 0 && n * hw >= 16384 && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && !getenv("NNF_APPLY_FLAT"))
+	{
+		chan_geom g;
+		st = make_chan_geom(g, "nnf_bn_train_apply_act", n, c, hw, true, resident_ctas_per_sm(bn_apply_channel_kernel<-1, 0>), 8);
+		if (st != NNF_OK)
+			return st;
+		apply_params p = {};
+		p.y = y; p.x = x; p.gamma = gamma; p.beta = beta; p.sums = sums; p.saved = saved; p.count_total = count_total; p.eps = eps;
+		p.chain = chain;
+		cudaStream_t s = (cudaStream_t)stream;
+		switch (chain_id(chain))
+		{
+		case 0: bn_apply_channel_kernel<NNF_ACT_NONE, 0><<<g.c * g.split, kThreads, 0, s>>>(p, g); break;
+		case 1: bn_apply_channel_kernel<NNF_ACT_PRELU, NNF_ACT_ELU><<<g.c * g.split, kThreads, 0, s>>>(p, g); break;
+		case 2: bn_apply_channel_kernel<NNF_ACT_RELU, 0><<<g.c * g.split, kThreads, 0, s>>>(p, g); break;
+		default: bn_apply_channel_kernel<-1, 0><<<g.c * g.split, kThreads, 0, s>>>(p, g); break;
+		}
+		return check_launch("bn_apply_channel_kernel");
+	}
 	bn_source bn = {};
 	bn.gamma = gamma; bn.beta = beta; bn.sums = sums; bn.saved = saved; bn.count_total = count_total; bn.eps = eps;
 	return run_elementwise((cudaStream_t)stream, y, x, nullptr, 1.0F, bn, chain, n, c, hw);
