@@ -249,8 +249,9 @@ NNF_API int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, con
 	int64_t n, int64_t c, int64_t hw, int add_to_destination,
 	void * workspace, size_t workspace_bytes);
 
-/* Returns 1 (and clears it) when a single-pass kernel gave up a bounded wait since the last check,
- * 0 otherwise, -1 if the word cannot be read. Synchronises the device: for tests and diagnosis. */
+/* Returns the error word (and clears it): 1 when a single-pass kernel gave up a bounded wait since the
+ * last check, 2 when a peer exchange did, 0 otherwise, -1 if the word cannot be read. Synchronises the
+ * device: for tests and diagnosis. */
 NNF_API int nnf_fused_error_check(void);
 
 NNF_API int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
@@ -272,6 +273,20 @@ NNF_API int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const float 
 	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
 	const float * mean, const float * invsigma, float entry_count,
 	int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sum of a small message (the 2*C floats of batch-norm statistics) over the GPUs of one machine through
+ * peer memory, in place of the reference's per-part all-reduce (nnforge/cuda/nccl_cuda_communicator.cpp:72-94,
+ * host_staged_cuda_communicator.cpp:39-152). Every rank owns one zero-initialised buffer of
+ * nnf_peer_exchange_bytes(kmax) bytes that all ranks can address; peer_bufs[r] is rank r's buffer as seen
+ * from this GPU. seq is the number of this exchange (1, 2, 3, ... identical on all ranks).
+ * publish stores `local[k]` into every rank's buffer and raises this rank's flag there; gather_sum waits
+ * (bounded; expiry raises the word read by nnf_fused_error_check, value 2) for all ranks' flags in its own
+ * buffer and writes the sum in rank order to `out` (may alias local). exchange_sum = publish + gather_sum. */
+NNF_API size_t nnf_peer_exchange_bytes(int kmax);
+NNF_API int nnf_peer_publish(nnf_stream_t stream, const float * local, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq);
+NNF_API int nnf_peer_gather_sum(nnf_stream_t stream, float * out, const void * my_buf, int world, int k, int kmax, uint32_t seq);
+NNF_API int nnf_peer_exchange_sum(nnf_stream_t stream, float * out, const float * local, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq);
 
 #ifdef __cplusplus
 }

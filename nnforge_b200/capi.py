@@ -66,6 +66,10 @@ _SIGNATURES = {
     "nnf_bn_train_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
     "nnf_fused_error_check": (_I, []),
     "nnf_bn_train_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I, _P, _SZ]),
+    "nnf_peer_exchange_bytes": (_SZ, [_I]),
+    "nnf_peer_publish": (_I, [_P, _P, ct.POINTER(_P), _I, _I, _I, _I, ct.c_uint32]),
+    "nnf_peer_gather_sum": (_I, [_P, _P, _P, _I, _I, _I, ct.c_uint32]),
+    "nnf_peer_exchange_sum": (_I, [_P, _P, _P, ct.POINTER(_P), _I, _I, _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_stats": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
     "nnf_bn_train_bwd_apply": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                     _I64, _I64, _I64, _I]),
@@ -252,6 +256,26 @@ def bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts=(), grad_gamma=None,
     _check(lib.nnf_bn_train_bwd(_stream(stream), _ptr(dx), _ptr(bsums), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), arr, k,
                                 _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma), _ptr(grad_slope), _ptr(mean), _ptr(invsigma),
                                 float(entry_count), n, c, hw, int(add_to_destination), _ptr(workspace), nbytes))
+
+
+def peer_exchange_bytes(kmax):
+    return int(lib.nnf_peer_exchange_bytes(kmax))
+
+
+def _ptr_table(ptrs):
+    return (_P * len(ptrs))(*[int(p) if not hasattr(p, "data_ptr") else p.data_ptr() for p in ptrs])
+
+
+def peer_publish(local, peer_ptrs, rank, world, kmax, seq, stream=None):
+    _check(lib.nnf_peer_publish(_stream(stream), _ptr(local), _ptr_table(peer_ptrs), rank, world, local.numel(), kmax, seq))
+
+
+def peer_gather_sum(out, my_buf, world, kmax, seq, stream=None):
+    _check(lib.nnf_peer_gather_sum(_stream(stream), _ptr(out), _ptr(my_buf), world, out.numel(), kmax, seq))
+
+
+def peer_exchange_sum(out, local, peer_ptrs, rank, world, kmax, seq, stream=None):
+    _check(lib.nnf_peer_exchange_sum(_stream(stream), _ptr(out), _ptr(local), _ptr_table(peer_ptrs), rank, world, local.numel(), kmax, seq))
 
 
 def fused_error_check():

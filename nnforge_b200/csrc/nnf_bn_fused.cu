@@ -942,6 +942,12 @@ namespace nnf
 	}
 }
 
+namespace nnf
+{
+	// the same error word, for the other translation units that have bounded waits
+	int * device_error_word() { return error_word(); }
+}
+
 using namespace nnf;
 
 extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,

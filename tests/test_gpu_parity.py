@@ -448,3 +448,39 @@ def test_errors_are_reported_not_thrown(capi):
     empty = torch.zeros((0, 3, 4, 4), device="cuda")
     capi.bn_infer_act(empty, empty, acts=[capi.relu(0.0)])  # empty batch is a no-op
     capi.softmax_fwd(empty, empty)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_peer_exchange_emulated_on_one_gpu(capi, world):
+    """The peer-memory sum with every 'rank' living on this GPU: all ranks publish, then all gather (in that
+    stream order, so no kernel ever waits for a later launch). Two rounds exercise both slot parities."""
+    kmax, k = 40, 33
+    floats = capi.peer_exchange_bytes(kmax) // 4
+    bufs = [torch.zeros(floats, device="cuda") for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    g = synth.rng(2, salt=world)
+    for seq in (1, 2, 3):
+        msgs = [synth.normal(g, (k,)) for _ in range(world)]
+        dmsgs = [dev(m) for m in msgs]
+        for r in range(world):
+            capi.peer_publish(dmsgs[r], ptrs, r, world, kmax, seq)
+        outs = [torch.empty(k, device="cuda") for _ in range(world)]
+        for r in range(world):
+            capi.peer_gather_sum(outs[r], bufs[r], world, kmax, seq)
+        want = np.zeros(k, np.float32)
+        for m in msgs:
+            want = (want + m).astype(np.float32)  # rank order, fp32
+        for r in range(world):
+            assert_bits_equal(host(outs[r]), want, "rank %d, exchange %d" % (r, seq))
+    assert capi.fused_error_check() == 0
+
+
+def test_peer_exchange_wait_is_bounded(capi):
+    """A flag that nobody raises: the gather gives up after its limit, reports it and returns."""
+    kmax = 8
+    buf = torch.zeros(capi.peer_exchange_bytes(kmax) // 4, device="cuda")
+    out = torch.empty(4, device="cuda")
+    capi.peer_gather_sum(out, buf, 2, kmax, 7)
+    torch.cuda.synchronize()
+    assert capi.fused_error_check() == 2
+    assert capi.fused_error_check() == 0
