@@ -370,10 +370,16 @@ def main():
     if not single:
         from nnforge_b200.sharded import NcclExchange, PeerExchange
         exchange, exchange_name = NcclExchange(), "NCCL all-reduce"
-        if os.environ.get("NNF_EXCHANGE", "nccl") == "peer":  # measured at 2 GPUs: 350 us per step against 339 us with NCCL
+        mode = os.environ.get("NNF_EXCHANGE", "fused")
+        if mode in ("peer", "fused"):
             try:
-                exchange = PeerExchange(capi, 2 * C, torch.device("cuda", local))
-                exchange_name = "peer-memory stores + local sum (nnf_peer_exchange_sum)"
+                if mode == "fused":
+                    from nnforge_b200.sharded import FusedPeerExchange
+                    exchange = FusedPeerExchange(capi, 2 * C, torch.device("cuda", local))
+                    exchange_name = "peer-memory stores from the reducing kernel, summed in the consuming kernel's prologue (no NCCL call)"
+                else:
+                    exchange = PeerExchange(capi, 2 * C, torch.device("cuda", local))
+                    exchange_name = "peer-memory stores + local sum (nnf_peer_exchange_sum)"
             except Exception as e:  # no symmetric memory on this machine: NCCL does the same sum
                 print("peer exchange unavailable (%s); using NCCL" % (e,), file=sys.stderr)
     layer = ShardedBatchNormAct(capi, C, EPS, acts, "cuda", on_phase=on_phase, exchange=exchange)

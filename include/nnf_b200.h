@@ -288,6 +288,29 @@ NNF_API int nnf_peer_publish(nnf_stream_t stream, const float * local, void * co
 NNF_API int nnf_peer_gather_sum(nnf_stream_t stream, float * out, const void * my_buf, int world, int k, int kmax, uint32_t seq);
 NNF_API int nnf_peer_exchange_sum(nnf_stream_t stream, float * out, const float * local, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq);
 
+/* The same exchange folded into the batch-norm kernels, so that it costs no launch of its own: the
+ * *_publish variants store this shard's sums into every rank's peer buffer from the kernel that finishes
+ * the reduction (first 2*C floats, kmax >= 2*C); the *_peer variants take the sums of all ranks from the
+ * rank's own peer buffer in their prologue (bounded wait) instead of from a sums / gsums array. Use the two
+ * of a pass with the same seq. When H*W is not a multiple of 4 (or a buffer is not 16-byte aligned) the
+ * forward _peer variant returns NNF_ERR_UNSUPPORTED: use nnf_peer_exchange_sum and the plain entry points. */
+NNF_API int nnf_bn_train_stats_publish(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, void * const * peer_bufs, int rank, int world, int kmax, uint32_t seq);
+NNF_API int nnf_bn_train_apply_act_peer(nnf_stream_t stream, float * y, float * saved, const float * x,
+	const float * gamma, const float * beta, const void * my_buf, int world, int kmax, uint32_t seq, double count_total, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_bn_train_bwd_stats_publish(nnf_stream_t stream, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, void * const * peer_bufs, int rank, int world, int kmax, uint32_t seq);
+NNF_API int nnf_bn_train_bwd_apply_peer(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const void * my_buf, int world, int kmax, uint32_t seq, const float * bsums, double count_total,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
 #ifdef __cplusplus
 }
 #endif

@@ -66,6 +66,11 @@ _SIGNATURES = {
     "nnf_bn_train_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _P, _SZ]),
     "nnf_fused_error_check": (_I, []),
     "nnf_bn_train_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I, _P, _SZ]),
+    "nnf_bn_train_stats_publish": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _SZ, ct.POINTER(_P), _I, _I, _I, ct.c_uint32]),
+    "nnf_bn_train_apply_act_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _D, _F, _ACTP, _I, _I64, _I64, _I64]),
+    "nnf_bn_train_bwd_stats_publish": (_I, [_P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ, ct.POINTER(_P), _I, _I, _I, ct.c_uint32]),
+    "nnf_bn_train_bwd_apply_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
+                                         _I64, _I64, _I64, _I]),
     "nnf_peer_exchange_bytes": (_SZ, [_I]),
     "nnf_peer_publish": (_I, [_P, _P, ct.POINTER(_P), _I, _I, _I, _I, ct.c_uint32]),
     "nnf_peer_gather_sum": (_I, [_P, _P, _P, _I, _I, _I, ct.c_uint32]),
@@ -296,3 +301,34 @@ def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total,
     _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
                                       float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
                                       _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))
+
+
+def bn_train_stats_publish(sums, x, workspace, peer_ptrs, rank, world, kmax, seq, stream=None):
+    n, c, hw = _nchw(x)
+    _check(lib.nnf_bn_train_stats_publish(_stream(stream), _ptr(sums), _ptr(x), n, c, hw, _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                          _ptr_table(peer_ptrs), rank, world, kmax, seq))
+
+
+def bn_train_apply_act_peer(y, saved, x, gamma, beta, my_buf, world, kmax, seq, count_total, eps, acts=(), stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_apply_act_peer(_stream(stream), _ptr(y), _ptr(saved), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(my_buf), world, kmax, seq,
+                                           float(count_total), eps, arr, k, n, c, hw))
+
+
+def bn_train_bwd_stats_publish(bsums, dy, x, gamma, beta, saved, acts, workspace, peer_ptrs, rank, world, kmax, seq, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_bwd_stats_publish(_stream(stream), _ptr(bsums), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), arr, k, n, c, hw,
+                                              _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr_table(peer_ptrs), rank, world, kmax, seq))
+
+
+def bn_train_bwd_apply_peer(dx, dy, x, gamma, beta, saved, my_buf, world, kmax, seq, bsums, count_total, acts=(), grad_gamma=None, grad_beta=None,
+                            grad_mean=None, grad_invsigma=None, grad_slope=None, mean=None, invsigma=None, entry_count=0.0, add_to_destination=False,
+                            stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_bwd_apply_peer(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(my_buf), world, kmax,
+                                           seq, _ptr(bsums), float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean),
+                                           _ptr(grad_invsigma), _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw,
+                                           int(add_to_destination)))

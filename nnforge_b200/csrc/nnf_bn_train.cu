@@ -165,6 +165,27 @@ namespace nnf
 			}
 		}
 
+		// The same reduction fused with the publication of its first `publish_count` sums to every rank's
+		// peer buffer (see nnf_peer.cu): one CTA, so that a single barrier tells when all stores are issued.
+		__global__ void __launch_bounds__(1024) bn_reduce_publish_kernel(float * sums, const double * partial, uint32_t c, uint32_t split, int count,
+			float * copy, int copy_count, peer_dst dst, int publish_count)
+		{
+			for (uint32_t ch = threadIdx.x; ch < c; ch += blockDim.x)
+				for (int k = 0; k < count; ++k)
+				{
+					double t = 0.0;
+					for (uint32_t sp = 0; sp < split; ++sp)
+						t += partial[(size_t(ch) * split + sp) * kSums + k];
+					const float v = float(t);
+					sums[size_t(k) * c + ch] = v;
+					if (copy && k < copy_count)
+						copy[size_t(k) * c + ch] = v;
+					if (k < publish_count)
+						peer_store(dst, k * c + ch, v);
+				}
+			peer_raise_flags(dst);
+		}
+
 		// PReLU slope gradient partials: sum dy * (x >= 0 ? 0 : x) per (channel, slice of entries)
 		__global__ void __launch_bounds__(kThreads) prelu_dslope_kernel(double * partial, const float * dy, const float * x, chan_geom g)
 		{
@@ -224,6 +245,7 @@ namespace nnf
 			const float * mean, * invsigma;
 			float entry_count;
 			int add;
+			peer_src peer;         // peer.mine != null: gsums come from the peer buffer
 		};
 
 		template <int A0, int A1>
@@ -322,8 +344,20 @@ namespace nnf
 			const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
 			const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
 			const float slope = chain_slope(p.chain, ch);
-			const float c2 = float(double(__ldg(p.gsums + ch)) / p.count_total);
-			const float c3 = float(double(__ldg(p.gsums + g.c + ch)) / p.count_total);
+			float gb, gg;
+			if (p.peer.mine)
+			{
+				peer_wait(p.peer);
+				gb = peer_sum(p.peer, ch);
+				gg = peer_sum(p.peer, g.c + ch);
+			}
+			else
+			{
+				gb = __ldg(p.gsums + ch);
+				gg = __ldg(p.gsums + g.c + ch);
+			}
+			const float c2 = float(double(gb) / p.count_total);
+			const float c3 = float(double(gg) / p.count_total);
 
 			if (sp == 0 && threadIdx.x == 0)
 			{
@@ -415,6 +449,7 @@ namespace nnf
 			double count_total;
 			float eps;
 			act_chain chain;
+			peer_src peer;         // peer.mine != null: the sums of all ranks are taken from the peer buffer
 		};
 
 		template <int A0, int A1>
@@ -425,8 +460,20 @@ namespace nnf
 			const uint32_t e0 = sp * g.entries_per_cta;
 			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
 			// batch statistics of this channel: biased variance from the (all-reduced) sum and sum of squares
-			const double m = double(__ldg(p.sums + ch)) / p.count_total;
-			double var = double(__ldg(p.sums + g.c + ch)) / p.count_total - m * m;
+			float fs, fq;
+			if (p.peer.mine)
+			{
+				peer_wait(p.peer);
+				fs = peer_sum(p.peer, ch);
+				fq = peer_sum(p.peer, g.c + ch);
+			}
+			else
+			{
+				fs = __ldg(p.sums + ch);
+				fq = __ldg(p.sums + g.c + ch);
+			}
+			const double m = double(fs) / p.count_total;
+			double var = double(fq) / p.count_total - m * m;
 			var = var < 0.0 ? 0.0 : var;
 			const float mean = float(m);
 			const float invstd = float(1.0 / sqrt(var + double(p.eps)));
@@ -538,8 +585,32 @@ extern "C" size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw)
 	return size_t(c) * kMaxSplit * kSums * sizeof(double);
 }
 
+namespace
+{
+	int stats_impl(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+		void * workspace, size_t workspace_bytes, const peer_dst * publish);
+}
+
 extern "C" int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
 	void * workspace, size_t workspace_bytes)
+{
+	return stats_impl(stream, sums, x, n, c, hw, workspace, workspace_bytes, nullptr);
+}
+
+extern "C" int nnf_bn_train_stats_publish(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, void * const * peer_bufs, int rank, int world, int kmax, uint32_t seq)
+{
+	peer_dst d;
+	int st = make_peer_dst(d, peer_bufs, rank, world, (int)(2 * c), kmax, seq, "nnf_bn_train_stats_publish");
+	if (st != NNF_OK)
+		return st;
+	return stats_impl(stream, sums, x, n, c, hw, workspace, workspace_bytes, &d);
+}
+
+namespace
+{
+int stats_impl(nnf_stream_t stream, float * sums, const float * x, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, const peer_dst * publish)
 {
 	int st = check_train_args("nnf_bn_train_stats", n, c, hw);
 	if (st != NNF_OK)
@@ -557,18 +628,57 @@ extern "C" int nnf_bn_train_stats(nnf_stream_t stream, float * sums, const float
 	st = check_launch("bn_stats_kernel");
 	if (st != NNF_OK)
 		return st;
+	if (publish)
+	{
+		bn_reduce_publish_kernel<<<1, 1024, 0, s>>>(sums, static_cast<const double *>(workspace), g.c, g.split, 2, nullptr, 0, *publish, 2);
+		return check_launch("bn_reduce_publish_kernel");
+	}
 	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(sums, static_cast<const double *>(workspace), g.c, g.split, 2, 0);
 	return check_launch("bn_reduce_partials_kernel");
+}
+}
+
+namespace
+{
+	int apply_impl(nnf_stream_t stream, float * y, float * saved, const float * x, const float * gamma, const float * beta, const float * sums,
+		const peer_src * peer, double count_total, float eps, const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);
+
+	int make_peer_src(peer_src& s, const void * my_buf, int world, int k, int kmax, uint32_t seq, const char * who)
+	{
+		if (world < 1 || world > kMaxRanks || kmax < k || !my_buf || seq == 0)
+			return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: bad peer arguments (world %d, %d floats, slots of %d)", who, world, k, kmax);
+		s.mine = static_cast<const float *>(my_buf); s.world = world; s.kmax = kmax; s.seq = seq; s.error = device_error_word();
+		return NNF_OK;
+	}
+}
+
+extern "C" int nnf_bn_train_apply_act_peer(nnf_stream_t stream, float * y, float * saved, const float * x,
+	const float * gamma, const float * beta, const void * my_buf, int world, int kmax, uint32_t seq, double count_total, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw)
+{
+	peer_src src;
+	int st = make_peer_src(src, my_buf, world, (int)(2 * c), kmax, seq, "nnf_bn_train_apply_act_peer");
+	if (st != NNF_OK)
+		return st;
+	return apply_impl(stream, y, saved, x, gamma, beta, nullptr, &src, count_total, eps, acts, n_acts, n, c, hw);
 }
 
 extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved, const float * x,
 	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw)
 {
+	return apply_impl(stream, y, saved, x, gamma, beta, sums, nullptr, count_total, eps, acts, n_acts, n, c, hw);
+}
+
+namespace
+{
+int apply_impl(nnf_stream_t stream, float * y, float * saved, const float * x, const float * gamma, const float * beta, const float * sums,
+	const peer_src * peer, double count_total, float eps, const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw)
+{
 	int st = check_train_args("nnf_bn_train_apply_act", n, c, hw);
 	if (st != NNF_OK)
 		return st;
-	if (!y || !x || !gamma || !beta || !sums)
+	if (!y || !x || !gamma || !beta || (!sums && !peer))
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_apply_act: null pointer");
 	if (!(count_total >= 1.0))
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_apply_act: count_total = %g", count_total);
@@ -581,7 +691,7 @@ extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * sa
 		prelus += chain.a[i].kind == NNF_ACT_PRELU;
 	// planes large enough to keep a CTA busy and whole float4s: the channel-ordered kernel (L2 reuse after the
 	// statistics kernel); anything else: the flat streaming kernel
-	if (hw % 4 == 0 && n * hw >= 16384 && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && !getenv("NNF_APPLY_FLAT"))
+	if (hw % 4 == 0 && (n * hw >= 16384 || peer) && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && !getenv("NNF_APPLY_FLAT"))
 	{
 		chan_geom g;
 		st = make_chan_geom(g, "nnf_bn_train_apply_act", n, c, hw, true, resident_ctas_per_sm(bn_apply_channel_kernel<-1, 0>), 8);
@@ -590,6 +700,8 @@ extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * sa
 		apply_params p = {};
 		p.y = y; p.x = x; p.gamma = gamma; p.beta = beta; p.sums = sums; p.saved = saved; p.count_total = count_total; p.eps = eps;
 		p.chain = chain;
+		if (peer)
+			p.peer = *peer;
 		cudaStream_t s = (cudaStream_t)stream;
 		switch (chain_id(chain))
 		{
@@ -600,9 +712,12 @@ extern "C" int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * sa
 		}
 		return check_launch("bn_apply_channel_kernel");
 	}
+	if (peer)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_apply_act_peer: this shape runs the flat kernel, which reads a plain sums buffer; use nnf_peer_exchange_sum + nnf_bn_train_apply_act");
 	bn_source bn = {};
 	bn.gamma = gamma; bn.beta = beta; bn.sums = sums; bn.saved = saved; bn.count_total = count_total; bn.eps = eps;
 	return run_elementwise((cudaStream_t)stream, y, x, nullptr, 1.0F, bn, chain, n, c, hw);
+}
 }
 
 namespace
@@ -626,10 +741,38 @@ namespace
 	}
 }
 
+namespace
+{
+	int bwd_stats_impl(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
+		const float * gamma, const float * beta, const float * saved, const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+		void * workspace, size_t workspace_bytes, const peer_dst * publish);
+}
+
 extern "C" int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
 	const float * gamma, const float * beta, const float * saved,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
 	void * workspace, size_t workspace_bytes)
+{
+	return bwd_stats_impl(stream, bsums, gsums, dy, x, gamma, beta, saved, acts, n_acts, n, c, hw, workspace, workspace_bytes, nullptr);
+}
+
+extern "C" int nnf_bn_train_bwd_stats_publish(nnf_stream_t stream, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, void * const * peer_bufs, int rank, int world, int kmax, uint32_t seq)
+{
+	peer_dst d;
+	int st = make_peer_dst(d, peer_bufs, rank, world, (int)(2 * c), kmax, seq, "nnf_bn_train_bwd_stats_publish");
+	if (st != NNF_OK)
+		return st;
+	return bwd_stats_impl(stream, bsums, nullptr, dy, x, gamma, beta, saved, acts, n_acts, n, c, hw, workspace, workspace_bytes, &d);
+}
+
+namespace
+{
+int bwd_stats_impl(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved, const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes, const peer_dst * publish)
 {
 	int st = check_train_args("nnf_bn_train_bwd_stats", n, c, hw);
 	if (st != NNF_OK)
@@ -657,8 +800,25 @@ extern "C" int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float 
 	st = check_launch("bn_bwd_stats_kernel");
 	if (st != NNF_OK)
 		return st;
+	if (publish)
+	{
+		bn_reduce_publish_kernel<<<1, 1024, 0, s>>>(bsums, static_cast<const double *>(workspace), g.c, g.split, 3, gsums, 2, *publish, 2);
+		return check_launch("bn_reduce_publish_kernel");
+	}
 	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(bsums, static_cast<const double *>(workspace), g.c, g.split, 3, 0, gsums, 2);
 	return check_launch("bn_reduce_partials_kernel");
+}
+}
+
+namespace
+{
+	int bwd_apply_impl(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+		const float * gamma, const float * beta, const float * saved,
+		const float * gsums, const peer_src * peer, const float * bsums, double count_total,
+		const nnf_act * acts, int n_acts,
+		float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+		const float * mean, const float * invsigma, float entry_count,
+		int64_t n, int64_t c, int64_t hw, int add_to_destination);
 }
 
 extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const float * dy, const float * x,
@@ -669,10 +829,40 @@ extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const flo
 	const float * mean, const float * invsigma, float entry_count,
 	int64_t n, int64_t c, int64_t hw, int add_to_destination)
 {
+	return bwd_apply_impl(stream, dx, dy, x, gamma, beta, saved, gsums, nullptr, bsums, count_total, acts, n_acts,
+		grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope, mean, invsigma, entry_count, n, c, hw, add_to_destination);
+}
+
+extern "C" int nnf_bn_train_bwd_apply_peer(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const void * my_buf, int world, int kmax, uint32_t seq, const float * bsums, double count_total,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination)
+{
+	peer_src src;
+	int st = make_peer_src(src, my_buf, world, (int)(2 * c), kmax, seq, "nnf_bn_train_bwd_apply_peer");
+	if (st != NNF_OK)
+		return st;
+	return bwd_apply_impl(stream, dx, dy, x, gamma, beta, saved, nullptr, &src, bsums, count_total, acts, n_acts,
+		grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope, mean, invsigma, entry_count, n, c, hw, add_to_destination);
+}
+
+namespace
+{
+int bwd_apply_impl(nnf_stream_t stream, float * dx, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const float * gsums, const peer_src * peer, const float * bsums, double count_total,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination)
+{
 	int st = check_train_args("nnf_bn_train_bwd_apply", n, c, hw);
 	if (st != NNF_OK)
 		return st;
-	if (!dx || !gsums)
+	if (!dx || (!gsums && !peer))
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: null pointer");
 	if ((grad_gamma || grad_beta || grad_slope) && !bsums)
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_apply: per-channel gradients requested without the local sums");
@@ -685,6 +875,8 @@ extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const flo
 	if (st != NNF_OK)
 		return st;
 	p.dx = dx; p.gsums = gsums; p.bsums = bsums; p.count_total = count_total;
+	if (peer)
+		p.peer = *peer;
 	p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
 	p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 	p.add = add_to_destination ? 1 : 0;
@@ -700,6 +892,7 @@ extern "C" int nnf_bn_train_bwd_apply(nnf_stream_t stream, float * dx, const flo
 	default: bn_bwd_apply_kernel<-1, 0><<<g.c * g.split, kThreads, 0, (cudaStream_t)stream>>>(p, g); break;
 	}
 	return check_launch("bn_bwd_apply_kernel");
+}
 }
 
 extern "C" size_t nnf_prelu_bwd_weights_workspace_bytes(int64_t n, int64_t c, int64_t hw)

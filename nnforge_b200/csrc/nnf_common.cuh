@@ -307,6 +307,86 @@ namespace nnf
 		}
 	}
 
+	// ---- small sums over peer memory (see nnf_peer.cu) ------------------------------------------------
+	// Buffer of one rank: float slots[2 parities][kMaxRanks][kmax], then uint32 flags[2][kMaxRanks].
+	constexpr int kMaxRanks = 8;
+	constexpr uint32_t kPeerSpinLimit = 1u << 22; // x ~200 ns back-off: about a second
+
+	__host__ __device__ inline size_t peer_flags_offset_floats(int kmax) { return size_t(2) * kMaxRanks * kmax; }
+
+	struct peer_src           // where a kernel finds the messages of all ranks (its OWN buffer)
+	{
+		const float * mine;   // null: no peer exchange, read the plain sums buffer instead
+		int world;
+		int kmax;
+		uint32_t seq;
+		int * error;
+	};
+
+	struct peer_dst           // where a kernel publishes this rank's message (EVERY rank's buffer)
+	{
+		float * base[kMaxRanks];
+		int rank;
+		int world;            // 0: do not publish
+		int kmax;
+		uint32_t seq;
+	};
+
+	// Called by all threads of a CTA: the first `world` threads wait (bounded) for the flags of this
+	// exchange in the rank's own buffer; on expiry the error word is raised and the kernel carries on.
+	__device__ __forceinline__ void peer_wait(const peer_src& s)
+	{
+		if ((int)threadIdx.x < s.world)
+		{
+			const uint32_t * flag = reinterpret_cast<const uint32_t *>(s.mine + peer_flags_offset_floats(s.kmax)) + (s.seq & 1u) * kMaxRanks + threadIdx.x;
+			uint32_t seen = 0;
+			bool ok = false;
+			for (uint32_t i = 0; i < kPeerSpinLimit; ++i)
+			{
+				asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+				if (seen == s.seq)
+				{
+					ok = true;
+					break;
+				}
+				__nanosleep(200);
+			}
+			if (!ok && s.error)
+				*s.error = 2;
+		}
+		__syncthreads();
+	}
+
+	// sum over ranks, in rank order, of element `index` of the published messages
+	__device__ __forceinline__ float peer_sum(const peer_src& s, uint32_t index)
+	{
+		float t = 0.0F;
+		for (int r = 0; r < s.world; ++r)
+			t += __ldcv(s.mine + (size_t(s.seq & 1u) * kMaxRanks + r) * s.kmax + index);
+		return t;
+	}
+
+	// Called by all threads of the (single) publishing CTA after their peer stores.
+	__device__ __forceinline__ void peer_raise_flags(const peer_dst& d)
+	{
+		__threadfence_system();
+		__syncthreads();
+		if ((int)threadIdx.x < d.world)
+		{
+			uint32_t * flag = reinterpret_cast<uint32_t *>(d.base[threadIdx.x] + peer_flags_offset_floats(d.kmax)) + (d.seq & 1u) * kMaxRanks + d.rank;
+			asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(d.seq) : "memory");
+		}
+	}
+
+	__device__ __forceinline__ void peer_store(const peer_dst& d, uint32_t index, float v)
+	{
+		for (int r = 0; r < d.world; ++r)
+			d.base[r][(size_t(d.seq & 1u) * kMaxRanks + d.rank) * d.kmax + index] = v;
+	}
+
+	int make_peer_dst(peer_dst& d, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq, const char * who);
+	int * device_error_word();
+
 	// ---- memory access helpers -----------------------------------------------------------------
 	// Streaming (evict-first) 128-bit accesses: every tensor on this path is touched once per kernel.
 	__device__ __forceinline__ float4 ld_stream(const float4 * p) { return __ldcs(p); }

@@ -21,87 +21,42 @@ namespace nnf
 {
 	namespace
 	{
-		constexpr int kMaxRanks = 8;
 		constexpr int kPeerThreads = 1024;
-		constexpr uint32_t kSpinLimit = 1u << 22; // x ~200 ns back-off
 
-		struct peer_table
+		__global__ void __launch_bounds__(kPeerThreads) peer_publish_kernel(const float * local, peer_dst dst, int k)
 		{
-			float * base[kMaxRanks];
-		};
-
-		__host__ __device__ inline size_t flags_offset_floats(int kmax) { return size_t(2) * kMaxRanks * kmax; }
-
-		__global__ void __launch_bounds__(kPeerThreads) peer_publish_kernel(const float * local, peer_table peers, int rank, int world, int k, int kmax, uint32_t seq)
-		{
-			const uint32_t parity = seq & 1u;
-			for (int r = 0; r < world; ++r)
-			{
-				float * dst = peers.base[r] + (size_t(parity) * kMaxRanks + rank) * kmax;
-				for (int i = threadIdx.x; i < k; i += kPeerThreads)
-					dst[i] = local[i];
-			}
-			__threadfence_system(); // every thread orders its own peer stores before the flags below
-			__syncthreads();
-			if ((int)threadIdx.x < world)
-			{
-				uint32_t * flag = reinterpret_cast<uint32_t *>(peers.base[threadIdx.x] + flags_offset_floats(kmax)) + parity * kMaxRanks + rank;
-				asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(seq) : "memory");
-			}
-		}
-
-		__global__ void __launch_bounds__(kPeerThreads) peer_gather_sum_kernel(float * out, const float * mine, int world, int k, int kmax, uint32_t seq, int * error)
-		{
-			const uint32_t parity = seq & 1u;
-			if ((int)threadIdx.x < world)
-			{
-				const uint32_t * flag = reinterpret_cast<const uint32_t *>(mine + flags_offset_floats(kmax)) + parity * kMaxRanks + threadIdx.x;
-				uint32_t seen = 0;
-				bool ok = false;
-				for (uint32_t i = 0; i < kSpinLimit; ++i)
-				{
-					asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-					if (seen == seq)
-					{
-						ok = true;
-						break;
-					}
-					__nanosleep(200);
-				}
-				if (!ok && error)
-					*error = 2;
-			}
-			__syncthreads();
 			for (int i = threadIdx.x; i < k; i += kPeerThreads)
-			{
-				float s = 0.0F;
-				for (int r = 0; r < world; ++r)
-					s += __ldcv(mine + (size_t(parity) * kMaxRanks + r) * kmax + i);
-				out[i] = s;
-			}
+				peer_store(dst, i, local[i]);
+			peer_raise_flags(dst);
 		}
 
-		int fill_table(peer_table& t, void * const * peer_bufs, int rank, int world, int k, int kmax, const char * who)
+		__global__ void __launch_bounds__(kPeerThreads) peer_gather_sum_kernel(float * out, peer_src src, int k)
 		{
-			if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
-				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: rank %d of %d (at most %d ranks)", who, rank, world, kMaxRanks);
-			if (k < 1 || kmax < k)
-				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: %d floats do not fit slots of %d", who, k, kmax);
-			if (!peer_bufs)
-				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: null pointer table", who);
-			for (int r = 0; r < kMaxRanks; ++r)
-				t.base[r] = nullptr;
-			for (int r = 0; r < world; ++r)
-			{
-				if (!peer_bufs[r])
-					return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: buffer of rank %d is null", who, r);
-				t.base[r] = static_cast<float *>(peer_bufs[r]);
-			}
-			return NNF_OK;
+			peer_wait(src);
+			for (int i = threadIdx.x; i < k; i += kPeerThreads)
+				out[i] = peer_sum(src, i);
 		}
 	}
 
-	int * device_error_word(); // nnf_bn_fused.cu
+	int make_peer_dst(peer_dst& d, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq, const char * who)
+	{
+		if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+			return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: rank %d of %d (at most %d ranks)", who, rank, world, kMaxRanks);
+		if (k < 1 || kmax < k)
+			return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: %d floats do not fit slots of %d", who, k, kmax);
+		if (!peer_bufs || seq == 0)
+			return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: null pointer table or seq 0 (sequence numbers start at 1; the buffers start zeroed)", who);
+		for (int r = 0; r < kMaxRanks; ++r)
+			d.base[r] = nullptr;
+		for (int r = 0; r < world; ++r)
+		{
+			if (!peer_bufs[r])
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: buffer of rank %d is null", who, r);
+			d.base[r] = static_cast<float *>(peer_bufs[r]);
+		}
+		d.rank = rank; d.world = world; d.kmax = kmax; d.seq = seq;
+		return NNF_OK;
+	}
 }
 
 using namespace nnf;
@@ -110,18 +65,18 @@ extern "C" size_t nnf_peer_exchange_bytes(int kmax)
 {
 	if (kmax < 1)
 		return 0;
-	return (flags_offset_floats(kmax) + size_t(2) * kMaxRanks) * sizeof(float);
+	return (peer_flags_offset_floats(kmax) + size_t(2) * kMaxRanks) * sizeof(float);
 }
 
 extern "C" int nnf_peer_publish(nnf_stream_t stream, const float * local, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq)
 {
-	peer_table t;
-	int st = fill_table(t, peer_bufs, rank, world, k, kmax, "nnf_peer_publish");
+	peer_dst d;
+	int st = make_peer_dst(d, peer_bufs, rank, world, k, kmax, seq, "nnf_peer_publish");
 	if (st != NNF_OK)
 		return st;
-	if (!local || seq == 0)
-		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_peer_publish: null message or seq 0 (sequence numbers start at 1; the buffer starts zeroed)");
-	peer_publish_kernel<<<1, kPeerThreads, 0, (cudaStream_t)stream>>>(local, t, rank, world, k, kmax, seq);
+	if (!local)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_peer_publish: null message");
+	peer_publish_kernel<<<1, kPeerThreads, 0, (cudaStream_t)stream>>>(local, d, k);
 	return check_launch("peer_publish_kernel");
 }
 
@@ -129,7 +84,9 @@ extern "C" int nnf_peer_gather_sum(nnf_stream_t stream, float * out, const void 
 {
 	if (world < 1 || world > kMaxRanks || k < 1 || kmax < k || !out || !my_buf || seq == 0)
 		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_peer_gather_sum: bad arguments (world %d, k %d, kmax %d)", world, k, kmax);
-	peer_gather_sum_kernel<<<1, kPeerThreads, 0, (cudaStream_t)stream>>>(out, static_cast<const float *>(my_buf), world, k, kmax, seq, device_error_word());
+	peer_src src;
+	src.mine = static_cast<const float *>(my_buf); src.world = world; src.kmax = kmax; src.seq = seq; src.error = device_error_word();
+	peer_gather_sum_kernel<<<1, kPeerThreads, 0, (cudaStream_t)stream>>>(out, src, k);
 	return check_launch("peer_gather_sum_kernel");
 }
 

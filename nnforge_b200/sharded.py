@@ -36,6 +36,9 @@ class PeerExchange:
     torch.distributed._symmetric_memory; construction is collective."""
 
     def __init__(self, kernels, kmax, device, group=None):
+        import os
+        # plain peer loads/stores only: no NVLink multicast object is bound to the buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.k = kernels
         self.kmax = kmax
@@ -54,6 +57,17 @@ class PeerExchange:
     def all_reduce(self, tensor):
         self.seq += 1
         self.k.peer_exchange_sum(tensor, tensor, self.ptrs, self.rank, self.world, self.kmax, self.seq)
+
+    def next_seq(self):
+        self.seq += 1
+        return self.seq
+
+
+class FusedPeerExchange(PeerExchange):
+    """PeerExchange whose two halves run inside the batch-norm kernels: the kernel that finishes a
+    reduction publishes the sums, the kernel that consumes them waits for all ranks in its prologue.
+    No launch of its own; ShardedBatchNormAct picks the *_publish / *_peer entry points when it sees it."""
+    fused = True
 
 
 class ShardedBatchNormAct:
@@ -90,10 +104,20 @@ class ShardedBatchNormAct:
     def forward(self, y, x, gamma, beta, global_entries=None):
         m = self.count_total(x, global_entries)
         self.on_phase("start")
+        ex = self.exchange
+        hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
+        if self.world > 1 and getattr(ex, "fused", False) and hw % 4 == 0:
+            seq = ex.next_seq()
+            self.k.bn_train_stats_publish(self.sums, x, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)
+            self.on_phase("stats")
+            self.on_phase("allreduce_fwd")
+            self.k.bn_train_apply_act_peer(y, self.saved, x, gamma, beta, ex.buf, ex.world, ex.kmax, seq, m, self.eps, self.acts)
+            self.on_phase("apply")
+            return y
         self.k.bn_train_stats(self.sums, x, self._ws(x))
         self.on_phase("stats")
         if self.world > 1:
-            self.exchange.all_reduce(self.sums)
+            ex.all_reduce(self.sums)
         self.on_phase("allreduce_fwd")
         self.k.bn_train_apply_act(y, self.saved, x, gamma, beta, self.sums, m, self.eps, self.acts)
         self.on_phase("apply")
@@ -105,6 +129,19 @@ class ShardedBatchNormAct:
         m = self.count_total(x, global_entries)
         grads = grads or {}
         sharded = self.world > 1
+        mean, invsigma = running if running is not None else (None, None)
+        ex = self.exchange
+        if sharded and getattr(ex, "fused", False):
+            seq = ex.next_seq()
+            self.k.bn_train_bwd_stats_publish(self.bsums, dy, x, gamma, beta, self.saved, self.acts, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)
+            self.on_phase("bwd_stats")
+            self.on_phase("allreduce_bwd")
+            self.k.bn_train_bwd_apply_peer(dx, dy, x, gamma, beta, self.saved, ex.buf, ex.world, ex.kmax, seq, self.bsums, m, self.acts,
+                                           grad_gamma=grads.get("gamma"), grad_beta=grads.get("beta"), grad_mean=grads.get("mean"),
+                                           grad_invsigma=grads.get("invsigma"), grad_slope=grads.get("slope"), mean=mean, invsigma=invsigma,
+                                           entry_count=float(x.shape[0]), add_to_destination=add_to_destination)
+            self.on_phase("bwd_apply")
+            return dx
         self.k.bn_train_bwd_stats(self.bsums, dy, x, gamma, beta, self.saved, self.acts, self._ws(x), gsums=self.gsums if sharded else None)
         self.on_phase("bwd_stats")
         if sharded:

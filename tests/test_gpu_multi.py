@@ -36,7 +36,9 @@ def _rank(rank, world, port, out_dir, use_peer):
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     sd = d(slope)
     acts = [capi.prelu(sd), capi.elu()]
-    exchange = PeerExchange(capi, 2 * c, torch.device("cuda", rank)) if use_peer else NcclExchange()
+    from nnforge_b200.sharded import FusedPeerExchange
+    exchange = [NcclExchange, lambda: PeerExchange(capi, 2 * c, torch.device("cuda", rank)),
+                lambda: FusedPeerExchange(capi, 2 * c, torch.device("cuda", rank))][int(use_peer)]()
     layer = ShardedBatchNormAct(capi, c, 1e-5, acts, "cuda", exchange=exchange)
     xs, dys, gd, bd = d(x[lo:hi]), d(dy[lo:hi]), d(gamma), d(beta)
     y, dx = torch.empty_like(xs), torch.empty_like(xs)
@@ -50,7 +52,7 @@ def _rank(rank, world, port, out_dir, use_peer):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [False, True])
+@pytest.mark.parametrize("use_peer", [0, 1, 2])  # NCCL all-reduce, peer-memory sum, peer-memory sum inside the kernels
 def test_two_gpu_sharded_matches_unsharded_oracle(tmp_path, oracle, use_peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -484,3 +484,46 @@ def test_peer_exchange_wait_is_bounded(capi):
     torch.cuda.synchronize()
     assert capi.fused_error_check() == 2
     assert capi.fused_error_check() == 0
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_bn_train_exchange_inside_the_kernels_emulated(capi, oracle, world):
+    """The *_publish / *_peer entry points with all 'ranks' on this GPU: every rank's statistics kernel
+    publishes before any rank's consuming kernel runs (stream order), so no kernel waits on a later launch."""
+    shape = (12, 8, 14, 14)
+    g = synth.rng(2, salt=4000 + world)
+    x = synth.normal(g, shape, 0.5, 2.0)
+    dy = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    chain = ("prelu", "elu")
+    y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
+    n = shape[0]
+    hw = shape[2] * shape[3]
+    m = n * hw
+    kmax = 2 * c
+    bufs = [torch.zeros(capi.peer_exchange_bytes(kmax) // 4, device="cuda") for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    sd, gd, bd = dev(slope), dev(gamma), dev(beta)
+    acts = make_acts(capi, chain, sd)
+    bounds = [n * k // world for k in range(world + 1)]
+    xs = [dev(x[bounds[k]:bounds[k + 1]]) for k in range(world)]
+    dys = [dev(dy[bounds[k]:bounds[k + 1]]) for k in range(world)]
+    ws = torch.empty(capi.bn_train_workspace_bytes(n, c, hw), dtype=torch.uint8, device="cuda")
+    ys, dxs = [torch.empty_like(t) for t in xs], [torch.empty_like(t) for t in xs]
+    saved = [torch.empty(2 * c, device="cuda") for _ in range(world)]
+    sums = [torch.empty(2 * c, device="cuda") for _ in range(world)]
+    bsums = [torch.empty(3 * c, device="cuda") for _ in range(world)]
+    for r in range(world):
+        capi.bn_train_stats_publish(sums[r], xs[r], ws, ptrs, r, world, kmax, 1)
+    for r in range(world):
+        capi.bn_train_apply_act_peer(ys[r], saved[r], xs[r], gd, bd, bufs[r], world, kmax, 1, m, 1e-5, acts)
+    for r in range(world):
+        capi.bn_train_bwd_stats_publish(bsums[r], dys[r], xs[r], gd, bd, saved[r], acts, ws, ptrs, r, world, kmax, 2)
+    for r in range(world):
+        capi.bn_train_bwd_apply_peer(dxs[r], dys[r], xs[r], gd, bd, saved[r], bufs[r], world, kmax, 2, bsums[r], m, acts)
+    assert capi.fused_error_check() == 0
+    assert_close(host(saved[0]), saved_w, "saved statistics")
+    assert_close(np.concatenate([host(t) for t in ys]), y_w, "forward", atol=2e-6)
+    assert_close(np.concatenate([host(t) for t in dxs]), dx_w, "backward", atol=5e-6)
