@@ -31,7 +31,8 @@ BYTES_PER_ELEM_FWD = 8
 BYTES_PER_ELEM_BWD = 12
 METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
 # DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/ (same shape)
-NCU_TRAFFIC_BYTES = {"bwd_apply": 579759360, "forward": 358484736, "bwd_stats": 414813184}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+NCU_TRAFFIC_BYTES = {"forward": 369928704, "backward": 693663488, "bwd_apply": 579759360, "bwd_stats": 414813184}
 WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
 
 
@@ -260,7 +261,11 @@ def run_sweep(args):
     sums, saved, bs = torch.empty(2 * C, device="cuda"), torch.empty(2 * C, device="cuda"), torch.empty(3 * C, device="cuda")
     acts = [capi.prelu(sl), capi.elu()]
     m = N_PER_GPU * H * W
-    report(2, "bn_train fwd single pass (cluster)", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
+    report(2, "bn_train fwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
+    report(2, "bn_train bwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_bwd(dx, bs, dy, x, g, b, saved, acts, workspace=ws), 1), 12 * e)
+    os.environ["NNF_FUSED_MODE"] = "3"
+    report(2, "bn_train fwd, shared-memory slab cluster kernel", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
+    del os.environ["NNF_FUSED_MODE"]
     report(2, "bn_train stats", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
     report(2, "bn_train apply+prelu+elu", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, g, b, sums, m, EPS, acts), 1), 8 * e)
     report(2, "bn_train bwd stats", timeit(lambda i: capi.bn_train_bwd_stats(bs, dy, x, g, b, saved, acts, ws), 1), 8 * e)
@@ -353,10 +358,10 @@ def main():
     grads = [torch.zeros(C, device="cuda") for _ in range(3)]
     acts = [capi.prelu(slope), capi.elu()]
     single = dist is None
-    # kernels of ours per step: single GPU = 1 (single-pass forward) + 3 (backward statistics, their
-    # reduction, backward apply); sharded = 2 + 1 + 2 + 1 with an NCCL all-reduce after each statistics step
-    launches_per_step = 4 if single else 6  # + 2 x 2 small exchange kernels when the peer-memory exchange is used
-    phases = ("forward", "bwd_stats", "bwd_apply") if single else ("stats", "apply", "bwd_stats", "bwd_apply")
+    # kernels of ours per step: single GPU = 1 forward + 1 backward launch (each holds the statistics and the
+    # apply work items); sharded = 2 + 1 + 2 + 1 with the exchange after each statistics step
+    launches_per_step = 2 if single else 6  # + 2 x 2 small exchange kernels when the peer-memory exchange is used
+    phases = ("forward", "backward") if single else ("stats", "apply", "bwd_stats", "bwd_apply")
 
     from nnforge_b200.sharded import ShardedBatchNormAct
     current = {"ev": None}
@@ -388,15 +393,16 @@ def main():
     def step(ev=None):
         current["ev"] = ev
         if single:
-            # one GPU: the single-pass forward entry point, then the same backward sequence as the sharded path
+            # one GPU: the single-GPU entry points (one launch per direction)
             on_phase("start")
-            capi.bn_train_fwd(y, layer.saved, layer.sums, x, gamma, beta, EPS, acts, workspace=layer._ws(x))
+            capi.bn_train_fwd(y, saved, sums, x, gamma, beta, EPS, acts, workspace=ws)
             on_phase("stats")
-            on_phase("allreduce_fwd")
-            on_phase("apply")
+            on_phase("bwd_stats")
+            capi.bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts, grad_gamma=grads[0], grad_beta=grads[1], grad_slope=grads[2], workspace=ws)
+            on_phase("bwd_apply")
         else:
             layer.forward(y, x, gamma, beta)
-        layer.backward(dx, dy, x, gamma, beta, grads=grad_map)
+            layer.backward(dx, dy, x, gamma, beta, grads=grad_map)
         current["ev"] = None
 
     def barrier():
@@ -435,10 +441,10 @@ def main():
 
     # per-kernel durations from the events recorded inside the timed region (this rank)
     if single:
-        idx = {"forward": (0, 1), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
-        alg_bytes = {"forward": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
-        names = {"forward": "bn_train_fwd_cluster_kernel (single pass: x in, y out)", "bwd_stats": "bn_bwd_stats_kernel (x, dy in)",
-                 "bwd_apply": "bn_bwd_apply_kernel (x, dy in, dx out)"}
+        idx = {"forward": (0, 1), "backward": (4, 6)}
+        alg_bytes = {"forward": 8 * elems, "backward": 12 * elems}
+        names = {"forward": "bn_train_chain_kernel<forward> (x in, y out; statistics and apply items in one launch)",
+                 "backward": "bn_train_chain_kernel<backward> (x, dy in, dx out; statistics and apply items in one launch)"}
     else:
         idx = {"stats": (0, 1), "apply": (2, 3), "bwd_stats": (3, 4), "bwd_apply": (5, 6)}
         alg_bytes = {"stats": 4 * elems, "apply": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}

@@ -1,0 +1,574 @@
+// Single-launch training batch norm (+ activation chain) whose second read of x (and dy) is served
+// by the L2 cache: HBM sees x (and dy) once and the result once - 8 bytes/element forward, 12
+// backward - although the work is still "statistics, then normalise".
+//
+// One launch holds two kinds of work items, each run by one CTA of 256 threads:
+//   S(channel, slice)  statistics: partial per-channel sums over a slice of the entries, written to
+//                      the workspace; the item then counts itself done for its channel
+//   A(channel, slice)  apply: waits until every S item of its channel is done, adds their partial sums
+//                      in slice order (double, deterministic), and normalises its slice
+// The items are ordered in chunks of channels: S(chunk 0), S(chunk 1), A(chunk 0), S(chunk 2),
+// A(chunk 1), ... so that the A items of a chunk run while the next chunk's statistics are being
+// read: the lines of x that the S items pulled in a few microseconds earlier are still in the 126 MB
+// L2 (a chunk is a few tens of MB), and HBM carries a steady mix of reads and writes instead of a
+// read-only kernel followed by a read-write one.
+//
+// A CTA does not use its block index: it draws a ticket from a global counter, and tickets are
+// handed out in the order in which CTAs start running. Every S item of a channel has a smaller
+// ticket than any A item of that channel, so whenever an A item waits, the items it waits for are
+// already running or finished - no assumption about the order in which the hardware dispatches
+// blocks, and no co-residency requirement. The wait is bounded all the same; when it runs out the
+// CTA raises the library's error word (code 4) and carries on with what it has.
+//
+// The counters (one per channel, and the ticket) live in the caller's workspace and are cleared by
+// a memset on the same stream before the launch.
+#include "nnf_common.cuh"
+
+#include <stdlib.h>
+
+namespace nnf
+{
+	int * device_error_word();
+
+	namespace
+	{
+#ifndef NNF_CHAIN_LOADS_FWD
+#define NNF_CHAIN_LOADS_FWD 4
+#endif
+#ifndef NNF_CHAIN_LOADS_BWD
+#define NNF_CHAIN_LOADS_BWD 2
+#endif
+#ifndef NNF_CHAIN_MIN_CTAS
+#define NNF_CHAIN_MIN_CTAS 6
+#endif
+		constexpr int kChainThreads = 256;
+		constexpr int kChainMaxSplit = 64;     // S items per channel (sizes the partial sums)
+		constexpr uint32_t kChainPollLimit = 1u << 22; // rounds of an A item's wait (about half a microsecond each)
+
+		struct chain_params
+		{
+			const float * x;
+			const float * dy;        // backward only
+			float * out;             // y (forward) or dx (backward)
+			const float * gamma;
+			const float * beta;
+			float * saved;           // forward: written {mean, invstd}; backward: read
+			float * sums;            // forward: {sum x, sum x^2} (may be null); backward: bsums[3C]
+			float * grad_gamma, * grad_beta, * grad_mean, * grad_invsigma, * grad_slope;
+			const float * mean, * invsigma;
+			float entry_count;
+			act_chain chain;
+			uint32_t n, c, hw;
+			uint32_t split_s, entries_s; // S items per channel, entries per S item
+			uint32_t split_a, entries_a; // the same for A items
+			uint32_t chunk;              // channels per chunk
+			uint32_t nchunks, lag;       // the A items of chunk k follow the S items of chunk k + lag
+			uint32_t total_items;
+			fastdiv d_vpp, d_split_s, d_split_a;
+			double count;                // elements per channel
+			float eps;
+			double * partial;            // [c][split_s][3]
+			uint32_t * done;             // [c] finished S items per channel; zero at kernel start
+			uint32_t * ticket;           // zero at kernel start
+			int * error;
+		};
+
+		__device__ __forceinline__ uint32_t ld_acquire(const uint32_t * p)
+		{
+			uint32_t v;
+			asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+			return v;
+		}
+
+		__device__ __forceinline__ double chain_warp_sum(double v)
+		{
+			#pragma unroll
+			for (int o = 16; o > 0; o >>= 1)
+				v += __shfl_xor_sync(0xffffffffu, v, o);
+			return v;
+		}
+
+		// Block-wide sum of K doubles; result valid in thread 0.
+		template <int K>
+		__device__ __forceinline__ void chain_block_sum(double (&v)[K], double * s_red)
+		{
+			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+			#pragma unroll
+			for (int k = 0; k < K; ++k)
+				v[k] = chain_warp_sum(v[k]);
+			if (lane == 0)
+			{
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					s_red[w * K + k] = v[k];
+			}
+			__syncthreads();
+			if (threadIdx.x == 0)
+			{
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+				{
+					double t = 0.0;
+					for (int i = 0; i < kChainThreads / 32; ++i)
+						t += s_red[i * K + k];
+					v[k] = t;
+				}
+			}
+		}
+
+		// ticket -> (is_apply, channel, slice)
+		__device__ __forceinline__ void decode_ticket(const chain_params& p, uint32_t t, uint32_t& apply, uint32_t& ch, uint32_t& sp)
+		{
+			uint32_t start = 0;
+			for (uint32_t k = 0; k < p.nchunks + p.lag; ++k)
+			{
+				if (k < p.nchunks)
+				{
+					const uint32_t c0 = k * p.chunk;
+					const uint32_t cc = min(p.chunk, p.c - c0);
+					const uint32_t items = cc * p.split_s;
+					if (t - start < items)
+					{
+						const uint32_t i = t - start;
+						const uint32_t lc = p.d_split_s.div(i);
+						apply = 0;
+						ch = c0 + lc;
+						sp = i - lc * p.split_s;
+						return;
+					}
+					start += items;
+				}
+				if (k >= p.lag)
+				{
+					const uint32_t c0 = (k - p.lag) * p.chunk;
+					const uint32_t cc = min(p.chunk, p.c - c0);
+					const uint32_t items = cc * p.split_a;
+					if (t - start < items)
+					{
+						const uint32_t i = t - start;
+						const uint32_t lc = p.d_split_a.div(i);
+						apply = 1;
+						ch = c0 + lc;
+						sp = i - lc * p.split_a;
+						return;
+					}
+					start += items;
+				}
+			}
+			apply = 2; // past the end: nothing to do
+			ch = sp = 0;
+		}
+
+		template <int A0, int A1, bool BWD>
+		__global__ void __launch_bounds__(kChainThreads, NNF_CHAIN_MIN_CTAS) bn_train_chain_kernel(const chain_params p)
+		{
+			constexpr int K = BWD ? 3 : 2;
+			constexpr int kLoadsS = BWD ? NNF_CHAIN_LOADS_BWD : NNF_CHAIN_LOADS_FWD; // independent 128-bit loads in flight per thread and tensor
+			constexpr int kLoadsA = kLoadsS;
+			__shared__ double s_red[(kChainThreads / 32) * K];
+			__shared__ uint32_t s_item[3];
+			__shared__ float s_tot[4];
+
+			if (threadIdx.x == 0)
+			{
+				const uint32_t t = atomicAdd(p.ticket, 1u);
+				uint32_t apply, ch, sp;
+				decode_ticket(p, t, apply, ch, sp);
+				s_item[0] = apply;
+				s_item[1] = ch;
+				s_item[2] = sp;
+			}
+			__syncthreads();
+			const uint32_t apply = s_item[0], ch = s_item[1], sp = s_item[2];
+			if (apply > 1)
+				return;
+			const uint32_t per_plane = p.hw >> 2;
+			const size_t entry_stride = size_t(p.c) * p.hw;
+
+			if (!apply)
+			{
+				// ---- S item --------------------------------------------------------------------------
+				const uint32_t e0 = sp * p.entries_s;
+				const uint32_t e1 = min(e0 + p.entries_s, p.n);
+				const uint32_t total = e1 > e0 ? (e1 - e0) * per_plane : 0;
+				const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
+				double acc[K];
+				if (!BWD)
+				{
+					float s = 0.0F, q = 0.0F;
+					for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kChainThreads * kLoadsS)
+					{
+						float4 a[kLoadsS];
+						#pragma unroll
+						for (int u = 0; u < kLoadsS; ++u)
+						{
+							const uint32_t i = i0 + u * kChainThreads;
+							a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (i < total)
+							{
+								const uint32_t lp = p.d_vpp.div(i);
+								a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + off0 + lp * entry_stride) + (i - lp * per_plane)); // default policy: stays in L2
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < kLoadsS; ++u)
+						{
+							s += (a[u].x + a[u].y) + (a[u].z + a[u].w);
+							q += (a[u].x * a[u].x + a[u].y * a[u].y) + (a[u].z * a[u].z + a[u].w * a[u].w);
+						}
+					}
+					acc[0] = double(s);
+					acc[1] = double(q);
+				}
+				else
+				{
+					const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+					const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+					const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+					const float slope = chain_slope(p.chain, ch);
+					float sb = 0.0F, sg = 0.0F, ss = 0.0F;
+					auto element = [&](float x, float dy)
+					{
+						const float u = __fadd_rn(__fmul_rn(x, mult), add);
+						float term;
+						const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
+						const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
+						sb += du;
+						sg += du * xhat;
+						ss += term;
+					};
+					for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kChainThreads * kLoadsS)
+					{
+						float4 a[kLoadsS], d[kLoadsS];
+						#pragma unroll
+						for (int u = 0; u < kLoadsS; ++u)
+						{
+							const uint32_t i = i0 + u * kChainThreads;
+							if (i < total)
+							{
+								const uint32_t lp = p.d_vpp.div(i);
+								const size_t off = off0 + lp * entry_stride;
+								a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + off) + (i - lp * per_plane));
+								d[u] = __ldg(reinterpret_cast<const float4 *>(p.dy + off) + (i - lp * per_plane));
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < kLoadsS; ++u)
+							if (i0 + u * kChainThreads < total)
+							{
+								element(a[u].x, d[u].x); element(a[u].y, d[u].y); element(a[u].z, d[u].z); element(a[u].w, d[u].w);
+							}
+					}
+					acc[0] = double(sb);
+					acc[1] = double(sg);
+					acc[2] = double(ss);
+				}
+				chain_block_sum<K>(acc, s_red);
+				if (threadIdx.x == 0)
+				{
+					double * out = p.partial + (size_t(ch) * p.split_s + sp) * 3;
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						out[k] = acc[k];
+					__threadfence(); // the partial sums are visible before the count
+					atomicAdd(p.done + ch, 1u);
+				}
+				return;
+			}
+
+			// ---- A item ------------------------------------------------------------------------------
+			const uint32_t e0 = sp * p.entries_a;
+			const uint32_t e1 = min(e0 + p.entries_a, p.n);
+			const uint32_t total = e1 > e0 ? (e1 - e0) * per_plane : 0;
+			const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
+			auto pos_of = [&](uint32_t i) -> size_t
+			{
+				const uint32_t lp = p.d_vpp.div(i);
+				return off0 + lp * entry_stride + size_t(i - lp * per_plane) * 4;
+			};
+			// the first batch of loads does not depend on the statistics: it is issued before the wait, so
+			// that the CTA has bytes in flight while it polls and folds the partial sums
+			float4 a[kLoadsA];
+			float4 d[BWD ? kLoadsA : 1];
+			auto load_batch = [&](uint32_t i0)
+			{
+				#pragma unroll
+				for (int u = 0; u < kLoadsA; ++u)
+				{
+					const uint32_t i = i0 + u * kChainThreads;
+					if (i < total)
+					{
+						const size_t pos = pos_of(i);
+						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos));
+						if (BWD)
+							d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + pos));
+					}
+				}
+			};
+			load_batch(threadIdx.x);
+			if (threadIdx.x < 32)
+			{
+				// wait (bounded) until every S item of this channel is done, then add their partial sums in
+				// slice order: lane l takes slices l and l + 32, then a fixed shuffle tree
+				bool ready = false;
+				if (threadIdx.x == 0)
+				{
+					for (uint32_t round = 0; round < kChainPollLimit; ++round)
+					{
+						if (ld_acquire(p.done + ch) >= p.split_s)
+						{
+							ready = true;
+							break;
+						}
+						__nanosleep(200);
+					}
+					if (!ready && p.error)
+						*p.error = 4;
+				}
+				__syncwarp();
+				double tot[K];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+				{
+					double t = 0.0;
+					for (uint32_t q = threadIdx.x; q < p.split_s; q += 32)
+						t += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
+					tot[k] = chain_warp_sum(t);
+				}
+				if (threadIdx.x == 0)
+				{
+					if (!BWD)
+					{
+						const double m = tot[0] / p.count;
+						double var = tot[1] / p.count - m * m;
+						var = var < 0.0 ? 0.0 : var;
+						const float fmean = float(m);
+						const float finv = float(1.0 / sqrt(var + double(p.eps)));
+						s_tot[0] = fmean;
+						s_tot[1] = finv;
+						if (sp == 0)
+						{
+							p.saved[ch] = fmean;
+							p.saved[p.c + ch] = finv;
+							if (p.sums)
+							{
+								p.sums[ch] = float(tot[0]);
+								p.sums[p.c + ch] = float(tot[1]);
+							}
+						}
+					}
+					else
+					{
+						const float fb = float(tot[0]), fg = float(tot[1]), fs = float(tot[2]);
+						// the same float-rounded sums the two-kernel form passes between its kernels
+						s_tot[0] = float(double(fb) / p.count);
+						s_tot[1] = float(double(fg) / p.count);
+						if (sp == 0)
+						{
+							const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+							if (p.sums)
+							{
+								p.sums[ch] = fb;
+								p.sums[p.c + ch] = fg;
+								p.sums[2 * p.c + ch] = fs;
+							}
+							// per-channel gradients accumulate (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+							if (p.grad_beta) p.grad_beta[ch] += fb;
+							if (p.grad_gamma) p.grad_gamma[ch] += fg;
+							if (p.grad_slope) p.grad_slope[ch] += fs;
+							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+						}
+					}
+				}
+			}
+			__syncthreads();
+			if (total == 0)
+				return;
+			const float slope = chain_slope(p.chain, ch);
+			if (!BWD)
+			{
+				const float mean = s_tot[0], invstd = s_tot[1];
+				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+				const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+				for (uint32_t i0 = threadIdx.x; ; )
+				{
+					#pragma unroll
+					for (int u = 0; u < kLoadsA; ++u)
+					{
+						const uint32_t i = i0 + u * kChainThreads;
+						if (i < total)
+						{
+							float4 o;
+							o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].x, mult), add), slope);
+							o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult), add), slope);
+							o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult), add), slope);
+							o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult), add), slope);
+							st_stream(reinterpret_cast<float4 *>(p.out + pos_of(i)), o);
+						}
+					}
+					i0 += kChainThreads * kLoadsA;
+					if (i0 >= total)
+						break;
+					load_batch(i0);
+				}
+			}
+			else
+			{
+				const float c2 = s_tot[0], c3 = s_tot[1];
+				const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+				const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+				auto element = [&](float x, float dy) -> float
+				{
+					const float u = __fadd_rn(__fmul_rn(x, mult), add);
+					float term;
+					const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
+					const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
+					return mult * ((du - c2) - xhat * c3);
+				};
+				for (uint32_t i0 = threadIdx.x; ; )
+				{
+					#pragma unroll
+					for (int u = 0; u < kLoadsA; ++u)
+					{
+						const uint32_t i = i0 + u * kChainThreads;
+						if (i < total)
+							st_stream(reinterpret_cast<float4 *>(p.out + pos_of(i)),
+								make_float4(element(a[u].x, d[u].x), element(a[u].y, d[u].y), element(a[u].z, d[u].z), element(a[u].w, d[u].w)));
+					}
+					i0 += kChainThreads * kLoadsA;
+					if (i0 >= total)
+						break;
+					load_batch(i0);
+				}
+			}
+		}
+
+		int chain_env(const char * name, int fallback)
+		{
+			const char * v = getenv(name);
+			return v ? atoi(v) : fallback;
+		}
+
+		// Item sizes and chunking. Defaults measured on B200 with x[256,256,28,28], PReLU+ELU (forward / backward):
+		// S 48 KB, A 64 KB, 16 MB chunks, lag 1: 95 / 154 us; A 32 KB: 99 / 178 us; S 96 KB: 96 / 170 us; chunk 8 MB:
+		// 122 / 216 us (apply items catch up with their statistics); lag 0: 124 / 227 us. Loads in flight per
+		// thread (4 / 2 per tensor against 8 / 4) and CTAs per SM (4 to 6) change the times by a few percent only.
+		// Tuning aids: NNF_CHAIN_S_KB / NNF_CHAIN_A_KB (bytes of one tensor that an
+		// S / A item covers), NNF_CHAIN_CHUNK_MB (bytes of one tensor per chunk), NNF_CHAIN_LAG.
+		bool plan_chain(chain_params& p, int64_t n, int64_t c, int64_t hw, int tensors)
+		{
+			(void)tensors;
+			if (hw % 4 != 0 || n < 1 || c < 1 || n * hw >= (int64_t(1) << 31) || c > 0x7fffffff / 256)
+				return false;
+			const int64_t plane_bytes = hw * 4;
+			const int64_t s_bytes = int64_t(chain_env("NNF_CHAIN_S_KB", 48)) * 1024;
+			const int64_t a_bytes = int64_t(chain_env("NNF_CHAIN_A_KB", 64)) * 1024;
+			int64_t es = s_bytes / plane_bytes, ea = a_bytes / plane_bytes;
+			if (es < 1) es = 1;
+			if (ea < 1) ea = 1;
+			if (es > n) es = n;
+			if (ea > n) ea = n;
+			if (div_up(n, es) > kChainMaxSplit)
+				es = div_up(n, kChainMaxSplit);
+			if (div_up(n, ea) > 4096)
+				ea = div_up(n, 4096);
+			p.entries_s = (uint32_t)es;
+			p.split_s = (uint32_t)div_up(n, es);
+			p.entries_a = (uint32_t)ea;
+			p.split_a = (uint32_t)div_up(n, ea);
+			const double channel_bytes = double(n) * double(plane_bytes);
+			int64_t chunk = (int64_t)(double(chain_env("NNF_CHAIN_CHUNK_MB", 16)) * 1024.0 * 1024.0 / channel_bytes);
+			if (chunk < 1) chunk = 1;
+			if (chunk < div_up(c, 64)) chunk = div_up(c, 64); // at most 64 chunks: a CTA finds its item by walking them
+			if (chunk > c) chunk = c;
+			p.chunk = (uint32_t)chunk;
+			p.nchunks = (uint32_t)div_up(c, chunk);
+			int lag = chain_env("NNF_CHAIN_LAG", 1);
+			p.lag = (uint32_t)(lag < 0 ? 0 : lag);
+			const int64_t items = c * (int64_t(p.split_s) + int64_t(p.split_a));
+			if (items >= (int64_t(1) << 31) || p.nchunks + p.lag > 4096)
+				return false;
+			p.total_items = (uint32_t)items;
+			p.n = (uint32_t)n; p.c = (uint32_t)c; p.hw = (uint32_t)hw;
+			p.d_vpp = fastdiv((uint32_t)(hw / 4));
+			p.d_split_s = fastdiv(p.split_s);
+			p.d_split_a = fastdiv(p.split_a);
+			p.count = double(n) * double(hw);
+			return true;
+		}
+
+		size_t chain_workspace_needed(const chain_params& p)
+		{
+			return size_t(p.c) * p.split_s * 3 * sizeof(double) + (size_t(p.c) + 1) * sizeof(uint32_t);
+		}
+
+		template <class Kernel>
+		int launch_chain(Kernel kernel, chain_params& p, void * workspace, cudaStream_t s, const char * what)
+		{
+			p.partial = static_cast<double *>(workspace);
+			p.done = reinterpret_cast<uint32_t *>(p.partial + size_t(p.c) * p.split_s * 3);
+			p.ticket = p.done + p.c;
+			p.error = device_error_word();
+			cudaError_t e = cudaMemsetAsync(p.done, 0, (size_t(p.c) + 1) * sizeof(uint32_t), s);
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "%s: cudaMemsetAsync: %s", what, cudaGetErrorString(e));
+			kernel<<<p.total_items, kChainThreads, 0, s>>>(p);
+			return check_launch(what);
+		}
+	}
+
+	size_t chain_workspace_bytes(int64_t c)
+	{
+		return size_t(c) * kChainMaxSplit * 3 * sizeof(double) + (size_t(c) + 1) * sizeof(uint32_t);
+	}
+
+	// Returns NNF_OK after enqueueing, a negative status on an error, or 1 when the shape does not suit
+	// this kernel (the caller then uses another form).
+	int chain_forward_launch(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
+		float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
+	{
+		chain_params p = {};
+		if (!aligned16(x) || !aligned16(y) || !plan_chain(p, n, c, hw, 1))
+			return 1;
+		if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
+			return 1;
+		p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
+		p.chain = chain;
+		p.eps = eps;
+		const int k0 = chain.n > 0 ? chain.a[0].kind : NNF_ACT_NONE;
+		const int k1 = chain.n > 1 ? chain.a[1].kind : NNF_ACT_NONE;
+		if (chain.n == 0)
+			return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+		if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU && chain.n == 2)
+			return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+		if (k0 == NNF_ACT_RELU && chain.n == 1)
+			return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+		return launch_chain(bn_train_chain_kernel<-1, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+	}
+
+	int chain_backward_launch(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+		const float * gamma, const float * beta, const float * saved, const act_chain& chain,
+		float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+		const float * mean, const float * invsigma, float entry_count,
+		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
+	{
+		chain_params p = {};
+		if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !plan_chain(p, n, c, hw, 2))
+			return 1;
+		if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
+			return 1;
+		p.x = x; p.dy = dy; p.out = dx; p.gamma = gamma; p.beta = beta; p.saved = const_cast<float *>(saved); p.sums = bsums;
+		p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
+		p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
+		p.chain = chain;
+		switch (chain_id(chain))
+		{
+		case 0: return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+		case 1: return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+		case 2: return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+		default: return launch_chain(bn_train_chain_kernel<-1, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+		}
+	}
+}

@@ -16,6 +16,7 @@
 // Waiting: the only spin is the mbarrier wait for this CTA's own bulk copies; it is bounded, and on
 // expiry the kernel raises an error word and carries on (results are then invalid, nothing hangs).
 #include "nnf_common.cuh"
+#include "nnf_async.cuh"
 
 #include <mutex>
 #include <stdlib.h>
@@ -25,53 +26,6 @@ namespace nnf
 	namespace
 	{
 		constexpr int kMaxCluster = 16;
-		constexpr uint32_t kWaitLimit = 1u << 26; // try_wait rounds before giving up (each suspends up to ~1 us)
-
-		// ---- PTX wrappers ----------------------------------------------------------------------
-		__device__ __forceinline__ uint32_t smem_addr(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-		__device__ __forceinline__ void mbar_init(uint64_t * bar, uint32_t count)
-		{
-			asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_addr(bar)), "r"(count));
-		}
-
-		__device__ __forceinline__ void mbar_expect_tx(uint64_t * bar, uint32_t bytes)
-		{
-			asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
-		}
-
-		__device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity)
-		{
-			uint32_t ok;
-			asm volatile(
-				"{\n"
-				".reg .pred p;\n"
-				"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-				"selp.u32 %0, 1, 0, p;\n"
-				"}\n" : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-			return ok != 0;
-		}
-
-		// Bounded wait; returns false when the limit ran out.
-		__device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity)
-		{
-			for (uint32_t i = 0; i < kWaitLimit; ++i)
-				if (mbar_try_wait(bar, parity))
-					return true;
-			return false;
-		}
-
-		// global -> this CTA's shared memory, `bytes` a multiple of 16, both addresses 16-byte aligned
-		__device__ __forceinline__ void bulk_load(void * dst_smem, const void * src_gmem, uint32_t bytes, uint64_t * bar)
-		{
-			asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-				:: "r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)) : "memory");
-		}
-
-		__device__ __forceinline__ void fence_proxy_async()
-		{
-			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-		}
 
 		__device__ __forceinline__ uint32_t cluster_rank()
 		{
@@ -896,13 +850,16 @@ namespace nnf
 		}
 
 		// Which form the single-GPU entry points use (NNF_FUSED_MODE, a tuning aid):
-		//   0 (default)  forward: shared-memory slab kernel; backward: the two-kernel form
-		//   1            L2-resident single-pass kernels for both
-		//   2            shared-memory slab kernels for both
-		// Measured on B200, x[256,256,28,28], PReLU+ELU: forward 99 us (slab) / 108 us (L2) / 119 us (two
-		// kernels); backward 185 us (slab) / 172-192 us (L2) / 175 us (two kernels). The single-pass
-		// backward kernels do move only 12 bytes/element through HBM (ncu: 423 MB read, 205 MB written)
-		// but run at two 512-thread CTAs per SM and are latency-bound there.
+		//   0 (default)  single launch of statistics and apply items, second read from L2 (nnf_bn_chain.cu);
+		//                shapes it does not take fall through to mode 3
+		//   1            L2-resident cluster kernels for both directions
+		//   2            shared-memory slab cluster kernels for both directions
+		//   3            forward: shared-memory slab cluster kernel; backward: the two-kernel form
+		// Measured on B200, x[256,256,28,28], PReLU+ELU: forward 95 us (single launch) / 98 us (slab) / 108 us
+		// (L2 clusters) / 110 us (two kernels); backward 154-160 us (single launch) / 185 us (slab) / 172-192 us
+		// (L2 clusters) / 176-183 us (two kernels). The slab kernels move only 8 / 12 bytes per element through
+		// HBM (ncu: x and dy read once) but are bound by what an SM keeps in flight; the forms that read twice
+		// run at the rate at which the SMs can exchange data with L2, whether or not the second read hits.
 		int fused_mode()
 		{
 			const char * m = getenv("NNF_FUSED_MODE");
@@ -975,6 +932,12 @@ extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, f
 		kernel = bn_train_fwd_cluster_kernel<NNF_ACT_RELU, 0>;
 
 	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(y);
+	if (fused_mode() == 0 && shape_ok)
+	{
+		st = chain_forward_launch((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes);
+		if (st != 1)
+			return st;
+	}
 	l2_plan lp;
 	if (fused_mode() == 1 && shape_ok && plan_l2(lp, n, c, hw, 1))
 	{
@@ -1078,6 +1041,13 @@ extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, 
 	default: break;
 	}
 	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(dy) && aligned16(dx);
+	if (fused_mode() == 0 && shape_ok && !add_to_destination)
+	{
+		st = chain_backward_launch((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
+			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes);
+		if (st != 1)
+			return st;
+	}
 	l2_plan lp;
 	if (fused_mode() == 1 && shape_ok && plan_l2(lp, n, c, hw, 2))
 	{

@@ -582,7 +582,9 @@ extern "C" size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw)
 	(void)n; (void)hw;
 	if (c <= 0)
 		return 0;
-	return size_t(c) * kMaxSplit * kSums * sizeof(double);
+	const size_t two_kernel = size_t(c) * kMaxSplit * kSums * sizeof(double);
+	const size_t single_launch = chain_workspace_bytes(c);
+	return two_kernel > single_launch ? two_kernel : single_launch;
 }
 
 namespace

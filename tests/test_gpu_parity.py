@@ -401,11 +401,11 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1, fused=False
 
 @pytest.mark.parametrize("shape", TRAIN_SHAPES)
 @pytest.mark.parametrize("chain", TRAIN_CHAINS)
-@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2"])
+@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2", "fused3"])
 def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
     """shards 1/2: the split entry points with the sums added across shards on the host;
-    fusedK: the single-GPU entry points with NNF_FUSED_MODE=K (slab forward + two-kernel backward,
-    L2-resident single pass, shared-memory slab single pass)."""
+    fusedK: the single-GPU entry points with NNF_FUSED_MODE=K (single launch of statistics and apply items,
+    L2-resident cluster kernels, shared-memory slab cluster kernels, slab forward + two-kernel backward)."""
     fused = isinstance(shards, str)
     if fused:
         monkeypatch.setenv("NNF_FUSED_MODE", shards[-1])
@@ -434,6 +434,40 @@ def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
     # running-statistics pseudo-gradients: entry_count*(batch - running), running = (0, 1)
     assert_close(grads["mean"], shape[0] * saved_w[:c], "grad mean", atol=1e-5)
     assert_close(grads["invsigma"], shape[0] * (saved_w[c:] - 1.0), "grad invsigma", atol=1e-5)
+
+
+@pytest.mark.parametrize("shape,s_kb,a_kb,chunk_mb,lag", [
+    ((16, 32, 28, 28), 96, 32, 16, 1),   # defaults: one chunk
+    ((16, 32, 28, 28), 4, 4, 0, 1),      # one entry per item, one channel per chunk
+    ((16, 32, 28, 28), 13, 7, 0, 3),     # ragged slices, lag of three chunks
+    ((37, 3, 8, 8), 1, 1, 0, 0),         # no lag: an apply item may start before its statistics are done
+    ((600, 2, 8, 8), 1, 1, 1, 1),        # more entries than statistics items allowed per channel
+    ((2, 300, 12, 12), 96, 32, 0, 2),    # many channels, one per chunk capped to 64 chunks
+])
+def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chunk_mb, lag, monkeypatch):
+    """The single-launch statistics/apply kernel over item sizes, chunk sizes and lags."""
+    monkeypatch.setenv("NNF_FUSED_MODE", "0")
+    monkeypatch.setenv("NNF_CHAIN_S_KB", str(s_kb))
+    monkeypatch.setenv("NNF_CHAIN_A_KB", str(a_kb))
+    monkeypatch.setenv("NNF_CHAIN_CHUNK_MB", str(chunk_mb))
+    monkeypatch.setenv("NNF_CHAIN_LAG", str(lag))
+    chain = ("prelu", "elu")
+    g = synth.rng(2, salt=sum(shape) + s_kb)
+    x = synth.normal(g, shape, 0.5, 2.0)
+    dy = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
+    for _ in range(2):  # twice: the counters of the first run must not leak into the second
+        y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, 1e-5, 1, True)
+        assert_close(saved, saved_w, "saved mean/invstd")
+        assert_close(y, y_w, "single-launch train fwd", atol=2e-6)
+        assert_close(dx, dx_w, "single-launch train bwd", atol=5e-6)
+        scale = np.sqrt(x.size // c)
+        assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
+        assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
+        assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
 
 
 def test_errors_are_reported_not_thrown(capi):
