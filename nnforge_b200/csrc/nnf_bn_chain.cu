@@ -39,7 +39,7 @@ namespace nnf
 #define NNF_CHAIN_LOADS_BWD 2
 #endif
 #ifndef NNF_CHAIN_MIN_CTAS
-#define NNF_CHAIN_MIN_CTAS 6
+#define NNF_CHAIN_MIN_CTAS 5
 #endif
 		constexpr int kChainThreads = 256;
 		constexpr int kChainMaxSplit = 64;     // S items per channel (sizes the partial sums)
@@ -214,7 +214,7 @@ namespace nnf
 						for (int u = 0; u < kLoadsS; ++u)
 						{
 							s += (a[u].x + a[u].y) + (a[u].z + a[u].w);
-							q += (a[u].x * a[u].x + a[u].y * a[u].y) + (a[u].z * a[u].z + a[u].w * a[u].w);
+							q = fmaf(a[u].x, a[u].x, fmaf(a[u].y, a[u].y, fmaf(a[u].z, a[u].z, fmaf(a[u].w, a[u].w, q))));
 						}
 					}
 					acc[0] = double(s);
@@ -234,7 +234,7 @@ namespace nnf
 						const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
 						const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
 						sb += du;
-						sg += du * xhat;
+						sg = fmaf(du, xhat, sg);
 						ss += term;
 					};
 					for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kChainThreads * kLoadsS)
@@ -281,11 +281,14 @@ namespace nnf
 			const uint32_t e1 = min(e0 + p.entries_a, p.n);
 			const uint32_t total = e1 > e0 ? (e1 - e0) * per_plane : 0;
 			const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
-			auto pos_of = [&](uint32_t i) -> size_t
+			// position of float4 number i of this item, in floats relative to off0 (fits 32 bits: checked by the plan)
+			const uint32_t entry_stride32 = p.c * p.hw;
+			auto rel_of = [&](uint32_t i) -> uint32_t
 			{
 				const uint32_t lp = p.d_vpp.div(i);
-				return off0 + lp * entry_stride + size_t(i - lp * per_plane) * 4;
+				return lp * entry_stride32 + (i - lp * per_plane) * 4;
 			};
+			uint32_t rel[kLoadsA];
 			// the first batch of loads does not depend on the statistics: it is issued before the wait, so
 			// that the CTA has bytes in flight while it polls and folds the partial sums
 			float4 a[kLoadsA];
@@ -298,10 +301,10 @@ namespace nnf
 					const uint32_t i = i0 + u * kChainThreads;
 					if (i < total)
 					{
-						const size_t pos = pos_of(i);
-						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + pos));
+						rel[u] = rel_of(i);
+						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + off0 + rel[u]));
 						if (BWD)
-							d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + pos));
+							d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + off0 + rel[u]));
 					}
 				}
 			};
@@ -404,7 +407,7 @@ namespace nnf
 							o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult), add), slope);
 							o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult), add), slope);
 							o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult), add), slope);
-							st_stream(reinterpret_cast<float4 *>(p.out + pos_of(i)), o);
+							st_stream(reinterpret_cast<float4 *>(p.out + off0 + rel[u]), o);
 						}
 					}
 					i0 += kChainThreads * kLoadsA;
@@ -434,7 +437,7 @@ namespace nnf
 					{
 						const uint32_t i = i0 + u * kChainThreads;
 						if (i < total)
-							st_stream(reinterpret_cast<float4 *>(p.out + pos_of(i)),
+							st_stream(reinterpret_cast<float4 *>(p.out + off0 + rel[u]),
 								make_float4(element(a[u].x, d[u].x), element(a[u].y, d[u].y), element(a[u].z, d[u].z), element(a[u].w, d[u].w)));
 					}
 					i0 += kChainThreads * kLoadsA;
@@ -476,6 +479,8 @@ namespace nnf
 				ea = div_up(n, 4096);
 			p.entries_s = (uint32_t)es;
 			p.split_s = (uint32_t)div_up(n, es);
+			if (ea * c * hw >= (int64_t(1) << 32))
+				return false; // positions inside an apply item are kept in 32 bits
 			p.entries_a = (uint32_t)ea;
 			p.split_a = (uint32_t)div_up(n, ea);
 			const double channel_bytes = double(n) * double(plane_bytes);
