@@ -361,7 +361,10 @@ def main():
     # kernels of ours per step: single GPU = 1 forward + 1 backward launch (each holds the statistics and the
     # apply work items); sharded = 2 + 1 + 2 + 1 with the exchange after each statistics step
     launches_per_step = 2 if single else 6  # + 2 x 2 small exchange kernels when the peer-memory exchange is used
-    phases = ("forward", "backward") if single else ("stats", "apply", "bwd_stats", "bwd_apply")
+    in_launch = (not single) and os.environ.get("NNF_EXCHANGE", "launch") == "launch"
+    if in_launch:
+        launches_per_step = 2
+    phases = ("forward", "backward") if (single or in_launch) else ("stats", "apply", "bwd_stats", "bwd_apply")
 
     from nnforge_b200.sharded import ShardedBatchNormAct
     current = {"ev": None}
@@ -375,10 +378,14 @@ def main():
     if not single:
         from nnforge_b200.sharded import NcclExchange, PeerExchange
         exchange, exchange_name = NcclExchange(), "NCCL all-reduce"
-        mode = os.environ.get("NNF_EXCHANGE", "fused")
-        if mode in ("peer", "fused"):
+        mode = os.environ.get("NNF_EXCHANGE", "launch")
+        if mode in ("peer", "fused", "launch"):
             try:
-                if mode == "fused":
+                if mode == "launch":
+                    from nnforge_b200.sharded import InLaunchExchange
+                    exchange = InLaunchExchange(capi, C, torch.device("cuda", local))
+                    exchange_name = "per-channel peer-memory stores and waits inside the one launch per direction (no NCCL call)"
+                elif mode == "fused":
                     from nnforge_b200.sharded import FusedPeerExchange
                     exchange = FusedPeerExchange(capi, 2 * C, torch.device("cuda", local))
                     exchange_name = "peer-memory stores from the reducing kernel, summed in the consuming kernel's prologue (no NCCL call)"
@@ -440,8 +447,12 @@ def main():
     value = bytes_step_all / (ms_step * 1e-3) / 1e9
 
     # per-kernel durations from the events recorded inside the timed region (this rank)
-    if single:
-        idx = {"forward": (0, 1), "backward": (4, 6)}
+    if in_launch and not getattr(exchange, "in_launch", False):
+        in_launch = False  # symmetric memory was not available: the NCCL sequence ran
+        launches_per_step = 6
+        phases = ("stats", "apply", "bwd_stats", "bwd_apply")
+    if single or in_launch:
+        idx = {"forward": (0, 3), "backward": (4, 6)} if in_launch else {"forward": (0, 1), "backward": (4, 6)}
         alg_bytes = {"forward": 8 * elems, "backward": 12 * elems}
         names = {"forward": "bn_train_chain_kernel<forward> (x in, y out; statistics and apply items in one launch)",
                  "backward": "bn_train_chain_kernel<backward> (x, dy in, dx out; statistics and apply items in one launch)"}

@@ -311,6 +311,31 @@ NNF_API int nnf_bn_train_bwd_apply_peer(nnf_stream_t stream, float * dx, const f
 	const float * mean, const float * invsigma, float entry_count,
 	int64_t n, int64_t c, int64_t hw, int add_to_destination);
 
+/* Batch-sharded training batch norm in ONE launch per direction and GPU (the sharded form of
+ * nnf_bn_train_fwd / nnf_bn_train_bwd): statistics and apply work items share the launch, the second read
+ * of x (and dy) comes from L2, and the per-channel sums cross the GPUs inside the launch - the item that
+ * finishes a channel's statistics stores this rank's two sums into every rank's mailbox, an apply item
+ * waits (bounded, about a second; expiry raises the word read by nnf_fused_error_check, value 2) until
+ * its own mailbox holds the sums of all ranks for its channel and adds them in rank order. Replaces the
+ * sequence statistics kernel -> all-reduce (nnforge/cuda/nccl_cuda_communicator.cpp:72-94) -> apply kernel.
+ * Every rank owns one zero-initialised mailbox of nnf_bn_train_mailbox_bytes(c) bytes that all ranks can
+ * address; mailboxes[r] is rank r's mailbox as seen from this GPU. seq numbers the exchanges (1, 2, 3, ...,
+ * the same on all ranks, one per call). Every rank must make the same call with its own shard; count_total
+ * = elements per channel over all shards. sums / bsums receive THIS shard's sums; the per-channel gradients
+ * accumulate this shard's sums. Needs H*W divisible by 4 and 16-byte aligned tensors (NNF_ERR_UNSUPPORTED
+ * otherwise: use the split entry points); workspace as for nnf_bn_train_stats. No add_to_destination. */
+NNF_API size_t nnf_bn_train_mailbox_bytes(int64_t c);
+NNF_API int nnf_bn_train_fwd_sharded(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
+	const float * gamma, const float * beta, float eps, const nnf_act * acts, int n_acts,
+	int64_t n, int64_t c, int64_t hw, double count_total, void * workspace, size_t workspace_bytes,
+	void * const * mailboxes, int rank, int world, uint32_t seq);
+NNF_API int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved, const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, double count_total, void * workspace, size_t workspace_bytes,
+	void * const * mailboxes, int rank, int world, uint32_t seq);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,6 +71,10 @@ _SIGNATURES = {
     "nnf_bn_train_bwd_stats_publish": (_I, [_P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ, ct.POINTER(_P), _I, _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_apply_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                          _I64, _I64, _I64, _I]),
+    "nnf_bn_train_mailbox_bytes": (_SZ, [_I64]),
+    "nnf_bn_train_fwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _D, _P, _SZ, ct.POINTER(_P), _I, _I, ct.c_uint32]),
+    "nnf_bn_train_bwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _D, _P, _SZ,
+                                      ct.POINTER(_P), _I, _I, ct.c_uint32]),
     "nnf_peer_exchange_bytes": (_SZ, [_I]),
     "nnf_peer_publish": (_I, [_P, _P, ct.POINTER(_P), _I, _I, _I, _I, ct.c_uint32]),
     "nnf_peer_gather_sum": (_I, [_P, _P, _P, _I, _I, _I, ct.c_uint32]),
@@ -301,6 +305,28 @@ def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total,
     _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
                                       float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
                                       _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))
+
+
+def bn_train_mailbox_bytes(c):
+    return int(lib.nnf_bn_train_mailbox_bytes(c))
+
+
+def bn_train_fwd_sharded(y, saved, sums, x, gamma, beta, eps, acts, count_total, workspace, mailbox_ptrs, rank, world, seq, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_fwd_sharded(_stream(stream), _ptr(y), _ptr(saved), _ptr(sums), _ptr(x), _ptr(gamma), _ptr(beta), eps, arr, k, n, c, hw,
+                                        float(count_total), _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                        _ptr_table(mailbox_ptrs), rank, world, seq))
+
+
+def bn_train_bwd_sharded(dx, bsums, dy, x, gamma, beta, saved, acts, count_total, workspace, mailbox_ptrs, rank, world, seq, grad_gamma=None,
+                         grad_beta=None, grad_mean=None, grad_invsigma=None, grad_slope=None, mean=None, invsigma=None, entry_count=0.0, stream=None):
+    n, c, hw = _nchw(x)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bn_train_bwd_sharded(_stream(stream), _ptr(dx), _ptr(bsums), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), arr, k,
+                                        _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma), _ptr(grad_slope), _ptr(mean),
+                                        _ptr(invsigma), float(entry_count), n, c, hw, float(count_total), _ptr(workspace),
+                                        workspace.numel() * workspace.element_size(), _ptr_table(mailbox_ptrs), rank, world, seq))
 
 
 def bn_train_stats_publish(sums, x, workspace, peer_ptrs, rank, world, kmax, seq, stream=None):

@@ -22,6 +22,16 @@
 //
 // The counters (one per channel, and the ticket) live in the caller's workspace and are cleared by
 // a memset on the same stream before the launch.
+//
+// Batch-sharded form (one process per GPU, the same launch on every GPU): the S item that finishes a
+// channel last folds this rank's partial sums and stores them, as two self-validating 8-byte words
+// (32 bits of a float + the exchange's sequence number), into the mailbox of EVERY rank - plain
+// peer stores over NVLink; an A item polls its OWN mailbox until the words of all ranks for its
+// channel carry the sequence number, and adds them in rank order (fp32, as the other exchange forms
+// do). So the exchange is per channel and overlaps the rest of the launch: no collective call, no
+// kernel boundary. An S item never waits, so a rank's statistics always get published and the A
+// items of every rank make progress whatever the skew between the GPUs; the wait is bounded (about a
+// second; code 2), and once the error word is set the remaining waits end at once.
 #include "nnf_common.cuh"
 
 #include <stdlib.h>
@@ -67,6 +77,12 @@ namespace nnf
 			fastdiv d_vpp, d_split_s, d_split_a;
 			double count;                // elements per channel
 			float eps;
+			// batch-sharded runs: mail[r] = mailbox of rank r (peer memory), mail[rank] this GPU's own;
+			// words [2 parities][kMaxRanks source ranks][c][2]
+			unsigned long long * mail[kMaxRanks];
+			int rank, world;
+			uint32_t seq;
+			double count_total;          // elements per channel over all ranks
 			double * partial;            // [c][split_s][3]
 			uint32_t * done;             // [c] finished S items per channel; zero at kernel start
 			uint32_t * ticket;           // zero at kernel start
@@ -78,6 +94,32 @@ namespace nnf
 			uint32_t v;
 			asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
 			return v;
+		}
+
+		__device__ __forceinline__ void st_sys_u64(unsigned long long * p, unsigned long long v)
+		{
+			asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+		}
+
+		__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long * p)
+		{
+			unsigned long long v;
+			asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+			return v;
+		}
+
+		__device__ __forceinline__ unsigned long long chain_timer_ns()
+		{
+			unsigned long long t;
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+			return t;
+		}
+
+		constexpr unsigned long long kChainPeerWaitNs = 1000000000ull; // an A item waits this long for the other ranks
+
+		__device__ __forceinline__ size_t mail_index(const chain_params& p, uint32_t source_rank, uint32_t ch)
+		{
+			return ((size_t(p.seq & 1u) * kMaxRanks + source_rank) * p.c + ch) * 2;
 		}
 
 		__device__ __forceinline__ double chain_warp_sum(double v)
@@ -159,14 +201,14 @@ namespace nnf
 			ch = sp = 0;
 		}
 
-		template <int A0, int A1, bool BWD>
+		template <int A0, int A1, bool BWD, bool PEER>
 		__global__ void __launch_bounds__(kChainThreads, NNF_CHAIN_MIN_CTAS) bn_train_chain_kernel(const chain_params p)
 		{
 			constexpr int K = BWD ? 3 : 2;
 			constexpr int kLoadsS = BWD ? NNF_CHAIN_LOADS_BWD : NNF_CHAIN_LOADS_FWD; // independent 128-bit loads in flight per thread and tensor
 			constexpr int kLoadsA = kLoadsS;
 			__shared__ double s_red[(kChainThreads / 32) * K];
-			__shared__ uint32_t s_item[3];
+			__shared__ uint32_t s_item[4];
 			__shared__ float s_tot[4];
 
 			if (threadIdx.x == 0)
@@ -271,7 +313,60 @@ namespace nnf
 					for (int k = 0; k < K; ++k)
 						out[k] = acc[k];
 					__threadfence(); // the partial sums are visible before the count
-					atomicAdd(p.done + ch, 1u);
+					const uint32_t before = atomicAdd(p.done + ch, 1u);
+					if (PEER)
+					{
+						__threadfence(); // and the other items' partial sums are visible to this one if it is the last
+						s_item[3] = before == p.split_s - 1 ? 1u : 0u;
+					}
+				}
+				if (!PEER)
+					return;
+				__syncthreads();
+				if (s_item[3] == 0 || threadIdx.x >= 32)
+					return;
+				// last S item of this channel on this rank: fold the partial sums (slice order, as the A items of
+				// a single-GPU launch do), write the local per-channel outputs, publish the message to every rank
+				double tot[K];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+				{
+					double t = 0.0;
+					for (uint32_t q = threadIdx.x; q < p.split_s; q += 32)
+						t += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
+					tot[k] = chain_warp_sum(t);
+				}
+				const float m0 = float(tot[0]), m1 = float(tot[1]);
+				if (threadIdx.x == 0)
+				{
+					if (!BWD)
+					{
+						if (p.sums)
+						{
+							p.sums[ch] = m0;
+							p.sums[p.c + ch] = m1;
+						}
+					}
+					else
+					{
+						const float fs = float(tot[2]);
+						if (p.sums)
+						{
+							p.sums[ch] = m0;
+							p.sums[p.c + ch] = m1;
+							p.sums[2 * p.c + ch] = fs;
+						}
+						// per-channel gradients accumulate the LOCAL sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+						if (p.grad_beta) p.grad_beta[ch] += m0;
+						if (p.grad_gamma) p.grad_gamma[ch] += m1;
+						if (p.grad_slope) p.grad_slope[ch] += fs;
+					}
+				}
+				if (threadIdx.x < uint32_t(p.world) * 2)
+				{
+					const uint32_t r = threadIdx.x >> 1, k = threadIdx.x & 1;
+					const unsigned long long word = (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(k ? m1 : m0);
+					st_sys_u64(p.mail[r] + mail_index(p, p.rank, ch) + k, word);
 				}
 				return;
 			}
@@ -309,7 +404,72 @@ namespace nnf
 				}
 			};
 			load_batch(threadIdx.x);
-			if (threadIdx.x < 32)
+			if (PEER && threadIdx.x < 32)
+			{
+				// wait (bounded) until the words of every rank for this channel carry this exchange's number,
+				// then add the messages in rank order
+				const unsigned long long * mine = p.mail[p.rank];
+				unsigned long long w0 = 0, w1 = 0;
+				bool ok = threadIdx.x >= uint32_t(p.world);
+				const unsigned long long t0 = chain_timer_ns();
+				for (uint32_t round = 0; ; ++round)
+				{
+					if (!ok)
+					{
+						w0 = ld_sys_u64(mine + mail_index(p, threadIdx.x, ch));
+						w1 = ld_sys_u64(mine + mail_index(p, threadIdx.x, ch) + 1);
+						ok = uint32_t(w0 >> 32) == p.seq && uint32_t(w1 >> 32) == p.seq;
+					}
+					if (__all_sync(0xffffffffu, ok))
+						break;
+					bool give_up = false;
+					if ((round & 15) == 15 && threadIdx.x == 0)
+						give_up = (p.error && *reinterpret_cast<volatile int *>(p.error) != 0) || chain_timer_ns() - t0 > kChainPeerWaitNs;
+					if (__any_sync(0xffffffffu, give_up))
+					{
+						if (threadIdx.x == 0 && p.error)
+							*p.error = 2;
+						break;
+					}
+					__nanosleep(200);
+				}
+				float f0 = 0.0F, f1 = 0.0F;
+				for (int r = 0; r < p.world; ++r)
+				{
+					f0 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w0, r)));
+					f1 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w1, r)));
+				}
+				if (threadIdx.x == 0)
+				{
+					if (!BWD)
+					{
+						const double m = double(f0) / p.count_total;
+						double var = double(f1) / p.count_total - m * m;
+						var = var < 0.0 ? 0.0 : var;
+						const float fmean = float(m);
+						const float finv = float(1.0 / sqrt(var + double(p.eps)));
+						s_tot[0] = fmean;
+						s_tot[1] = finv;
+						if (sp == 0)
+						{
+							p.saved[ch] = fmean;
+							p.saved[p.c + ch] = finv;
+						}
+					}
+					else
+					{
+						s_tot[0] = float(double(f0) / p.count_total);
+						s_tot[1] = float(double(f1) / p.count_total);
+						if (sp == 0)
+						{
+							const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+						}
+					}
+				}
+			}
+			if (!PEER && threadIdx.x < 32)
 			{
 				// wait (bounded) until every S item of this channel is done, then add their partial sums in
 				// slice order: lane l takes slices l and l + 32, then a fixed shuffle tree
@@ -529,28 +689,98 @@ namespace nnf
 		return size_t(c) * kChainMaxSplit * 3 * sizeof(double) + (size_t(c) + 1) * sizeof(uint32_t);
 	}
 
+	namespace
+	{
+		struct chain_peer
+		{
+			void * const * mailboxes;
+			int rank, world;
+			uint32_t seq;
+			double count_total;
+		};
+
+		int fill_peer(chain_params& p, const chain_peer * peer, const char * who)
+		{
+			p.count_total = p.count;
+			if (!peer)
+				return NNF_OK;
+			if (peer->world < 1 || peer->world > kMaxRanks || peer->rank < 0 || peer->rank >= peer->world || !peer->mailboxes || peer->seq == 0)
+				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: bad peer arguments (rank %d of %d, sequence number %u; at most %d ranks, numbers start at 1)",
+					who, peer->rank, peer->world, peer->seq, kMaxRanks);
+			for (int r = 0; r < peer->world; ++r)
+			{
+				if (!peer->mailboxes[r] || (reinterpret_cast<uintptr_t>(peer->mailboxes[r]) & 7))
+					return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: mailbox of rank %d is null or not 8-byte aligned", who, r);
+				p.mail[r] = static_cast<unsigned long long *>(peer->mailboxes[r]);
+			}
+			p.rank = peer->rank;
+			p.world = peer->world;
+			p.seq = peer->seq;
+			p.count_total = peer->count_total;
+			return NNF_OK;
+		}
+
+		template <bool PEER>
+		int chain_forward_impl(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
+			float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
+		{
+			chain_params p = {};
+			if (!aligned16(x) || !aligned16(y) || !plan_chain(p, n, c, hw, 1))
+				return 1;
+			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
+				return 1;
+			p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
+			p.chain = chain;
+			p.eps = eps;
+			const int st = fill_peer(p, peer, "bn_train_chain_kernel (forward)");
+			if (st != NNF_OK)
+				return st;
+			const int k0 = chain.n > 0 ? chain.a[0].kind : NNF_ACT_NONE;
+			const int k1 = chain.n > 1 ? chain.a[1].kind : NNF_ACT_NONE;
+			if (chain.n == 0)
+				return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+			if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU && chain.n == 2)
+				return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+			if (k0 == NNF_ACT_RELU && chain.n == 1)
+				return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+			return launch_chain(bn_train_chain_kernel<-1, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+		}
+
+		template <bool PEER>
+		int chain_backward_impl(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+			const float * gamma, const float * beta, const float * saved, const act_chain& chain,
+			float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+			const float * mean, const float * invsigma, float entry_count,
+			int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
+		{
+			chain_params p = {};
+			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !plan_chain(p, n, c, hw, 2))
+				return 1;
+			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
+				return 1;
+			p.x = x; p.dy = dy; p.out = dx; p.gamma = gamma; p.beta = beta; p.saved = const_cast<float *>(saved); p.sums = bsums;
+			p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
+			p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
+			p.chain = chain;
+			const int st = fill_peer(p, peer, "bn_train_chain_kernel (backward)");
+			if (st != NNF_OK)
+				return st;
+			switch (chain_id(chain))
+			{
+			case 0: return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+			case 1: return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+			case 2: return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+			default: return launch_chain(bn_train_chain_kernel<-1, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+			}
+		}
+	}
+
 	// Returns NNF_OK after enqueueing, a negative status on an error, or 1 when the shape does not suit
 	// this kernel (the caller then uses another form).
 	int chain_forward_launch(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
 		float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
 	{
-		chain_params p = {};
-		if (!aligned16(x) || !aligned16(y) || !plan_chain(p, n, c, hw, 1))
-			return 1;
-		if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
-			return 1;
-		p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
-		p.chain = chain;
-		p.eps = eps;
-		const int k0 = chain.n > 0 ? chain.a[0].kind : NNF_ACT_NONE;
-		const int k1 = chain.n > 1 ? chain.a[1].kind : NNF_ACT_NONE;
-		if (chain.n == 0)
-			return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-		if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU && chain.n == 2)
-			return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-		if (k0 == NNF_ACT_RELU && chain.n == 1)
-			return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-		return launch_chain(bn_train_chain_kernel<-1, 0, false>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+		return chain_forward_impl<false>(stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, nullptr);
 	}
 
 	int chain_backward_launch(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
@@ -559,21 +789,65 @@ namespace nnf
 		const float * mean, const float * invsigma, float entry_count,
 		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
 	{
-		chain_params p = {};
-		if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !plan_chain(p, n, c, hw, 2))
-			return 1;
-		if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
-			return 1;
-		p.x = x; p.dy = dy; p.out = dx; p.gamma = gamma; p.beta = beta; p.saved = const_cast<float *>(saved); p.sums = bsums;
-		p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
-		p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
-		p.chain = chain;
-		switch (chain_id(chain))
-		{
-		case 0: return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-		case 1: return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-		case 2: return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-		default: return launch_chain(bn_train_chain_kernel<-1, 0, true>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-		}
+		return chain_backward_impl<false>(stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
+			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, nullptr);
 	}
+}
+
+using namespace nnf;
+
+extern "C" size_t nnf_bn_train_mailbox_bytes(int64_t c)
+{
+	return c > 0 ? size_t(2) * kMaxRanks * size_t(c) * 2 * sizeof(unsigned long long) : 0;
+}
+
+extern "C" int nnf_bn_train_fwd_sharded(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
+	const float * gamma, const float * beta, float eps, const nnf_act * acts, int n_acts,
+	int64_t n, int64_t c, int64_t hw, double count_total, void * workspace, size_t workspace_bytes,
+	void * const * mailboxes, int rank, int world, uint32_t seq)
+{
+	if (n <= 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_fwd_sharded: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (!y || !x || !gamma || !beta || !saved)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_fwd_sharded: null pointer");
+	act_chain chain;
+	int st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	const chain_peer peer = {mailboxes, rank, world, seq, count_total};
+	st = chain_forward_impl<true>((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, &peer);
+	if (st == 1)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_fwd_sharded: needs H*W divisible by 4, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
+	return st;
+}
+
+extern "C" int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved, const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, double count_total, void * workspace, size_t workspace_bytes,
+	void * const * mailboxes, int rank, int world, uint32_t seq)
+{
+	if (n <= 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_sharded: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (!dx || !dy || !x || !gamma || !beta || !saved || !bsums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_sharded: null pointer");
+	if ((grad_mean && !mean) || (grad_invsigma && !invsigma))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd_sharded: running-statistics gradients requested without the running statistics");
+	act_chain chain;
+	int st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	chain_fill_backward_constants(chain, acts, n_acts);
+	int prelus = 0;
+	for (int i = 0; i < chain.n; ++i)
+		prelus += chain.a[i].kind == NNF_ACT_PRELU;
+	if (prelus > 1)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd_sharded: at most one PReLU per fused chain");
+	const chain_peer peer = {mailboxes, rank, world, seq, count_total};
+	st = chain_backward_impl<true>((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
+		mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, &peer);
+	if (st == 1)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd_sharded: needs H*W divisible by 4, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
+	return st;
 }

@@ -70,6 +70,40 @@ class FusedPeerExchange(PeerExchange):
     fused = True
 
 
+class InLaunchExchange:
+    """The exchange of the single-launch sharded entry points (nnf_bn_train_fwd_sharded / _bwd_sharded): every
+    rank owns a mailbox in symmetric memory; the launch that computes a channel's statistics stores them into
+    all mailboxes and the same launch's apply work waits for them per channel. Nothing to call between
+    kernels: ShardedBatchNormAct hands the mailbox pointers to the entry points. `all_reduce` (NCCL) is kept
+    for the shapes those entry points do not take."""
+    in_launch = True
+
+    def __init__(self, kernels, channels, device, group=None):
+        import os
+        # plain peer loads/stores only: no NVLink multicast object is bound to the buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.k = kernels
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.channels = channels
+        self.buf = symm_mem.empty(kernels.bn_train_mailbox_bytes(channels) // 8, dtype=torch.int64, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.seq = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)  # every mailbox is zeroed before anyone stores into it
+
+    def next_seq(self):
+        self.seq += 1
+        return self.seq
+
+    def all_reduce(self, tensor):
+        dist.all_reduce(tensor, group=self.group)
+
+
 class ShardedBatchNormAct:
     def __init__(self, kernels, channels, eps, acts, device, group=None, on_phase=None, exchange=None):
         self.k = kernels
@@ -106,6 +140,13 @@ class ShardedBatchNormAct:
         self.on_phase("start")
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
+        if self.world > 1 and getattr(ex, "in_launch", False) and hw % 4 == 0 and x.shape[1] == ex.channels:
+            self.k.bn_train_fwd_sharded(y, self.saved, self.sums, x, gamma, beta, self.eps, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
+                                        ex.next_seq())
+            self.on_phase("stats")
+            self.on_phase("allreduce_fwd")
+            self.on_phase("apply")
+            return y
         if self.world > 1 and getattr(ex, "fused", False) and hw % 4 == 0:
             seq = ex.next_seq()
             self.k.bn_train_stats_publish(self.sums, x, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)
@@ -131,6 +172,16 @@ class ShardedBatchNormAct:
         sharded = self.world > 1
         mean, invsigma = running if running is not None else (None, None)
         ex = self.exchange
+        hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
+        if sharded and getattr(ex, "in_launch", False) and hw % 4 == 0 and x.shape[1] == ex.channels and not add_to_destination:
+            self.on_phase("bwd_stats")
+            self.k.bn_train_bwd_sharded(dx, self.bsums, dy, x, gamma, beta, self.saved, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
+                                        ex.next_seq(), grad_gamma=grads.get("gamma"), grad_beta=grads.get("beta"), grad_mean=grads.get("mean"),
+                                        grad_invsigma=grads.get("invsigma"), grad_slope=grads.get("slope"), mean=mean, invsigma=invsigma,
+                                        entry_count=float(x.shape[0]))
+            self.on_phase("allreduce_bwd")
+            self.on_phase("bwd_apply")
+            return dx
         if sharded and getattr(ex, "fused", False):
             seq = ex.next_seq()
             self.k.bn_train_bwd_stats_publish(self.bsums, dy, x, gamma, beta, self.saved, self.acts, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)

@@ -1,5 +1,6 @@
-"""Two real GPUs: the batch-sharded training batch-norm sequence with both exchanges (NCCL all-reduce and
-the peer-memory sum) against the unsharded CPU oracle. Skipped on machines with one GPU."""
+"""Two real GPUs: the batch-sharded training batch-norm sequence with every exchange (NCCL all-reduce, the
+peer-memory sum as kernels of its own, folded into the batch-norm kernels, and inside the single launch)
+against the unsharded CPU oracle. Skipped on machines with one GPU."""
 import os
 import sys
 
@@ -36,9 +37,10 @@ def _rank(rank, world, port, out_dir, use_peer):
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     sd = d(slope)
     acts = [capi.prelu(sd), capi.elu()]
-    from nnforge_b200.sharded import FusedPeerExchange
+    from nnforge_b200.sharded import FusedPeerExchange, InLaunchExchange
     exchange = [NcclExchange, lambda: PeerExchange(capi, 2 * c, torch.device("cuda", rank)),
-                lambda: FusedPeerExchange(capi, 2 * c, torch.device("cuda", rank))][int(use_peer)]()
+                lambda: FusedPeerExchange(capi, 2 * c, torch.device("cuda", rank)),
+                lambda: InLaunchExchange(capi, c, torch.device("cuda", rank))][int(use_peer)]()
     layer = ShardedBatchNormAct(capi, c, 1e-5, acts, "cuda", exchange=exchange)
     xs, dys, gd, bd = d(x[lo:hi]), d(dy[lo:hi]), d(gamma), d(beta)
     y, dx = torch.empty_like(xs), torch.empty_like(xs)
@@ -52,7 +54,7 @@ def _rank(rank, world, port, out_dir, use_peer):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [0, 1, 2])  # NCCL all-reduce, peer-memory sum, peer-memory sum inside the kernels
+@pytest.mark.parametrize("use_peer", [0, 1, 2, 3])  # NCCL all-reduce, peer-memory sum, the same inside the two kernels, inside the single launch
 def test_two_gpu_sharded_matches_unsharded_oracle(tmp_path, oracle, use_peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

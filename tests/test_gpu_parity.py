@@ -470,6 +470,71 @@ def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chun
         assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
 
 
+def _sharded_single_launch(capi, x, dy, gamma, beta, slope, chain, mailboxes, rank, world, seq, count_total):
+    c = x.shape[1]
+    xd, dyd, gd, bd, sd = dev(x), dev(dy), dev(gamma), dev(beta), dev(slope)
+    acts = make_acts(capi, chain, sd)
+    n, hw = x.shape[0], x.shape[2] * x.shape[3]
+    ws = torch.empty(capi.bn_train_workspace_bytes(n, c, hw), dtype=torch.uint8, device="cuda")
+    y, dx = torch.empty_like(xd), torch.empty_like(xd)
+    saved, sums, bsums = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+    grads = {k: torch.zeros(c, device="cuda") for k in ("gamma", "beta", "slope")}
+    ptrs = [m.data_ptr() for m in mailboxes]
+    capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, count_total, ws, ptrs, rank, world, seq)
+    capi.bn_train_bwd_sharded(dx, bsums, dyd, xd, gd, bd, saved, acts, count_total, ws, ptrs, rank, world, seq + 1,
+                              grad_gamma=grads["gamma"], grad_beta=grads["beta"], grad_slope=grads["slope"])
+    torch.cuda.synchronize()
+    return host(y), host(saved), host(dx), {k: host(v) for k, v in grads.items()}
+
+
+@pytest.mark.parametrize("shape", [(16, 32, 28, 28), (37, 3, 8, 8), (2, 300, 12, 12)])
+def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
+    """The sharded single-launch entry points with a world of one: the whole exchange path (publication by
+    the last statistics item, tagged words, wait in the apply items) runs against this rank's own mailbox."""
+    chain = ("prelu", "elu")
+    g = synth.rng(2, salt=5000 + sum(shape))
+    x = synth.normal(g, shape, 0.5, 2.0)
+    dy = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    slope = synth.uniform(g, c, 0.0, 0.3)
+    y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
+    mailbox = torch.zeros(capi.bn_train_mailbox_bytes(c) // 8, dtype=torch.int64, device="cuda")
+    for seq in (1, 3, 5):  # both mailbox parities, stale words of earlier exchanges in place
+        y, saved, dx, grads = _sharded_single_launch(capi, x, dy, gamma, beta, slope, chain, [mailbox], 0, 1, seq, x.size // c)
+        assert capi.fused_error_check() == 0
+        assert_close(saved, saved_w, "saved mean/invstd")
+        assert_close(y, y_w, "sharded single-launch fwd", atol=2e-6)
+        assert_close(dx, dx_w, "sharded single-launch bwd", atol=5e-6)
+        scale = np.sqrt(x.size // c)
+        assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
+        assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
+        assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
+
+
+def test_bn_train_sharded_single_launch_wait_is_bounded(capi):
+    """A second rank that never publishes: the apply items give up after their limit, the launch returns
+    and reports it; the next call with a complete world works again."""
+    shape = (8, 6, 8, 8)
+    g = synth.rng(2, salt=5100)
+    x, dy = synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta, slope = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1), synth.uniform(g, c, 0.0, 0.3)
+    mine = torch.zeros(capi.bn_train_mailbox_bytes(c) // 8, dtype=torch.int64, device="cuda")
+    absent = torch.zeros_like(mine)  # stands for the mailbox of a rank that is not there
+    xd, gd, bd, sd = dev(x), dev(gamma), dev(beta), dev(slope)
+    acts = make_acts(capi, ("prelu", "elu"), sd)
+    ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, 64), dtype=torch.uint8, device="cuda")
+    y, saved, sums = torch.empty_like(xd), torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda")
+    capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, 2 * x.size // c, ws, [mine.data_ptr(), absent.data_ptr()], 0, 2, 1)
+    torch.cuda.synchronize()
+    assert capi.fused_error_check() == 2
+    assert capi.fused_error_check() == 0
+    capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, x.size // c, ws, [mine.data_ptr()], 0, 1, 2)
+    torch.cuda.synchronize()
+    assert capi.fused_error_check() == 0
+
+
 def test_errors_are_reported_not_thrown(capi):
     x = torch.zeros((2, 3, 4, 4), device="cuda")
     with pytest.raises(capi.NnfError) as e:

@@ -81,6 +81,48 @@ class OracleKernels:
             grad_slope += bsums[2 * c:]
 
 
+    # the single-launch sharded entry points: what the launch does between its statistics and its apply work
+    # (sum of this rank's two sums over all ranks, in rank order) is done here with a gathered sum
+    def _rank_order_sum(self, local):
+        parts = [torch.empty_like(local) for _ in range(dist.get_world_size())]
+        dist.all_gather(parts, local)
+        total = torch.zeros_like(local)
+        for part in parts:
+            total = total + part
+        return total
+
+    def bn_train_fwd_sharded(self, y, saved, sums, x, gamma, beta, eps, acts, count_total, workspace, mailbox_ptrs, rank, world, seq):
+        assert world == dist.get_world_size() and rank == dist.get_rank() and seq >= 1
+        self.bn_train_stats(sums, x, workspace)
+        self.bn_train_apply_act(y, saved, x, gamma, beta, self._rank_order_sum(sums), count_total, eps, acts)
+
+    def bn_train_bwd_sharded(self, dx, bsums, dy, x, gamma, beta, saved, acts, count_total, workspace, mailbox_ptrs, rank, world, seq, grad_gamma=None,
+                             grad_beta=None, grad_mean=None, grad_invsigma=None, grad_slope=None, mean=None, invsigma=None, entry_count=0.0):
+        assert world == dist.get_world_size() and rank == dist.get_rank() and seq >= 1
+        self.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, workspace)
+        gsums = self._rank_order_sum(bsums[:2 * x.shape[1]].clone())
+        self.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total, acts, grad_gamma=grad_gamma, grad_beta=grad_beta,
+                                grad_slope=grad_slope)
+
+
+class FakeInLaunchExchange:
+    """Stands for nnforge_b200.sharded.InLaunchExchange on CPU ranks: same attributes, no mailboxes."""
+    in_launch = True
+
+    def __init__(self, channels):
+        self.channels = channels
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.ptrs = []
+        self.seq = 0
+
+    def next_seq(self):
+        self.seq += 1
+        return self.seq
+
+    def all_reduce(self, tensor):
+        dist.all_reduce(tensor)
+
+
 def _inputs():
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import synth
@@ -93,7 +135,7 @@ def _inputs():
     return x, dy, gamma, beta, slope
 
 
-def _run_rank(rank, world, port, out_dir):
+def _run_rank(rank, world, port, out_dir, in_launch):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -104,7 +146,7 @@ def _run_rank(rank, world, port, out_dir):
     lo, hi = n * rank // world, n * (rank + 1) // world
     t = torch.from_numpy
     acts = [("prelu", slope), ("elu", None)]
-    layer = ShardedBatchNormAct(OracleKernels(), 6, 1e-5, acts, "cpu")
+    layer = ShardedBatchNormAct(OracleKernels(), 6, 1e-5, acts, "cpu", exchange=FakeInLaunchExchange(6) if in_launch else None)
     xs, dys = t(x[lo:hi].copy()), t(dy[lo:hi].copy())
     y, dx = torch.empty_like(xs), torch.empty_like(xs)
     grads = {k: torch.zeros(6) for k in ("gamma", "beta", "slope")}
@@ -118,10 +160,11 @@ def _run_rank(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_sharded_equals_unsharded(tmp_path, world):
-    port = 29600 + world + (os.getpid() % 200)
-    mp.spawn(_run_rank, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+@pytest.mark.parametrize("world,in_launch", [(2, False), (4, False), (2, True)])
+def test_sharded_equals_unsharded(tmp_path, world, in_launch):
+    """in_launch: the host sequence of the single-launch sharded entry points (one call per direction)."""
+    port = 29600 + world + 10 * int(in_launch) + (os.getpid() % 200)
+    mp.spawn(_run_rank, args=(world, port, str(tmp_path), in_launch), nprocs=world, join=True)
     sys.path.insert(0, ROOT)
     from nnforge_b200.sharded import ShardedBatchNormAct
     x, dy, gamma, beta, slope = _inputs()
