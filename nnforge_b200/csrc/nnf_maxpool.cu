@@ -380,6 +380,7 @@ namespace nnf
 			float * s_dy = s_raw;
 			uint32_t * s_idx = reinterpret_cast<uint32_t *>(s_raw + size_t(p.group) * g.ohw);
 			float * s_dz = s_raw + ((size_t(p.group) * g.ohw * 2 + 3) & ~size_t(3)); // ragged-row fused path only
+			float * s_mult = s_dz + ((size_t(p.group) * g.hw + 3) & ~size_t(3));       // same path: gamma*invsigma per plane
 			for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
 			{
 				const int64_t plane0 = grp * p.group;
@@ -391,11 +392,18 @@ namespace nnf
 					s_dy[o] = ld_stream(p.dpooled + obase + o);
 					s_idx[o] = __ldcs(p.argmax + obase + o);
 				}
+				const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
+				if (FUSED && ROW4 && !p.row4_vec)
+					for (uint32_t lp = threadIdx.x; lp < np; lp += kThreads)
+					{
+						uint32_t channel = ch0 + lp;
+						channel -= g.d_c.div(channel) * g.c;
+						s_mult[lp] = p.gamma ? __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel)) : 1.0F;
+					}
 				__syncthreads();
 
 				const uint32_t count = np * g.hw;
 				const int64_t base = plane0 * g.hw;
-				const uint32_t ch0 = (uint32_t)(plane0 - int64_t(g.d_c.div((uint32_t)plane0)) * g.c);
 				auto element = [&](uint32_t e, float zval, float seed, float& out_dx, float& out_dres)
 				{
 					const uint32_t lp = g.d_hw.div(e);
@@ -459,28 +467,28 @@ namespace nnf
 					if (FUSED)
 					{
 						__syncthreads();
-						auto finish = [&](uint32_t e, float zval, float dz, float& odx, float& ores)
+						// the batch-norm factor of a plane comes from shared memory; a vector of four elements lies in
+						// one plane unless it straddles a plane boundary (H*W not a multiple of 4)
+						auto finish = [&](float mult, float zval, float dz, float& odx, float& ores)
 						{
 							const float ds = (__float_as_uint(zval) >> 31) ? __fmul_rn(dz, p.slope) : dz;
 							ores = ds;
-							odx = ds;
-							if (p.gamma)
-							{
-								uint32_t channel = ch0 + g.d_hw.div(e);
-								channel -= g.d_c.div(channel) * g.c;
-								odx = __fmul_rn(ds, __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel)));
-							}
+							odx = p.gamma ? __fmul_rn(ds, mult) : ds;
 						};
 						const uint32_t nvec = p.vec_ok ? (count >> 2) : 0;
 						for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
 						{
 							const float4 z4 = ld_stream(reinterpret_cast<const float4 *>(p.z + base) + v);
 							const float4 d4 = reinterpret_cast<const float4 *>(s_dz)[v];
+							const uint32_t lp0 = g.d_hw.div(v << 2);
+							const uint32_t left = (lp0 + 1) * g.hw - (v << 2); // elements of this vector in plane lp0 (>= 1)
+							const float m0 = s_mult[lp0];
+							const float m1 = left >= 4 ? m0 : s_mult[lp0 + 1];
 							float4 ox, orr;
-							finish((v << 2), z4.x, d4.x, ox.x, orr.x);
-							finish((v << 2) + 1, z4.y, d4.y, ox.y, orr.y);
-							finish((v << 2) + 2, z4.z, d4.z, ox.z, orr.z);
-							finish((v << 2) + 3, z4.w, d4.w, ox.w, orr.w);
+							finish(m0, z4.x, d4.x, ox.x, orr.x);
+							finish(left > 1 ? m0 : m1, z4.y, d4.y, ox.y, orr.y);
+							finish(left > 2 ? m0 : m1, z4.z, d4.z, ox.z, orr.z);
+							finish(left > 3 ? m0 : m1, z4.w, d4.w, ox.w, orr.w);
 							if (p.dx)
 								st_stream(reinterpret_cast<float4 *>(p.dx + base) + v, ox);
 							if (p.dres)
@@ -489,7 +497,7 @@ namespace nnf
 						for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kThreads)
 						{
 							float odx, ores;
-							finish(e, p.z[base + e], s_dz[e], odx, ores);
+							finish(s_mult[g.d_hw.div(e)], p.z[base + e], s_dz[e], odx, ores);
 							if (p.dx)
 								p.dx[base + e] = odx;
 							if (p.dres)
@@ -739,7 +747,7 @@ namespace nnf
 			bool vec_ok = (!p.dx || aligned16(p.dx)) && (!fused || (aligned16(p.z) && (!p.dres || aligned16(p.dres))));
 			const int grp = choose_group(p.g, p.planes, vec_ok);
 			const bool ragged_fast = fused && p.g.win_w == 3 && p.g.win_h == 3 && p.g.sw == 2 && p.g.sh == 2 && !((p.g.w & 3) == 0 && vec_ok);
-			const size_t smem = (((size_t(grp) * p.g.ohw * 2 + 3) & ~size_t(3)) + (ragged_fast ? size_t(grp) * p.g.hw : 0)) * sizeof(float);
+			const size_t smem = (((size_t(grp) * p.g.ohw * 2 + 3) & ~size_t(3)) + (ragged_fast ? ((size_t(grp) * p.g.hw + 3) & ~size_t(3)) + size_t(grp) : 0)) * sizeof(float);
 			if (grp == 0 || smem > kMaxDynSmem)
 			{
 				const int64_t blocks = div_up(p.planes * p.g.hw, kThreads);
