@@ -493,6 +493,8 @@ namespace nnf
 						softmax_pixels_reg_kernel<8, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
 					else if (c <= 16)
 						softmax_pixels_reg_kernel<16, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
+					else if (c <= 24 && BACKWARD) // backward holds two columns: 80 registers and 3 CTAs per SM instead of 102 and 2 (forward measured slower with 24)
+						softmax_pixels_reg_kernel<24, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
 					else
 						softmax_pixels_reg_kernel<32, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
 					int st = check_launch("softmax_pixels_reg_kernel");
