@@ -364,6 +364,7 @@ namespace nnf
 				}
 				if (threadIdx.x < uint32_t(p.world) * 2)
 				{
+					__threadfence(); // everything this rank's S items wrote for the channel comes before the word
 					const uint32_t r = threadIdx.x >> 1, k = threadIdx.x & 1;
 					const unsigned long long word = (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(k ? m1 : m0);
 					st_sys_u64(p.mail[r] + mail_index(p, p.rank, ch) + k, word);
@@ -433,6 +434,7 @@ namespace nnf
 					}
 					__nanosleep(200);
 				}
+				__threadfence(); // what the publishing items wrote before their words is visible from here on
 				float f0 = 0.0F, f1 = 0.0F;
 				for (int r = 0; r < p.world; ++r)
 				{

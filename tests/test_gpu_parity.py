@@ -470,6 +470,32 @@ def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chun
         assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
 
 
+@pytest.mark.parametrize("alias", ["dy", "x"])
+def test_bn_train_bwd_in_place(capi, oracle, alias):
+    """dx written over dy or over x (the reference lets the backward pass overwrite either): both must give the
+    result of the out-of-place call."""
+    shape, chain = (16, 32, 28, 28), ("prelu", "elu")
+    g = synth.rng(2, salt=6100)
+    x, dy = synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta, slope = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1), synth.uniform(g, c, 0.0, 0.3)
+    xd, dyd, gd, bd, sd = dev(x), dev(dy), dev(gamma), dev(beta), dev(slope)
+    acts = make_acts(capi, chain, sd)
+    ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, shape[2] * shape[3]), dtype=torch.uint8, device="cuda")
+    y, saved, sums, bsums = torch.empty_like(xd), torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+    capi.bn_train_fwd(y, saved, sums, xd, gd, bd, 1e-5, acts, workspace=ws)
+    want = torch.empty_like(xd)
+    capi.bn_train_bwd(want, bsums, dyd, xd, gd, bd, saved, acts, workspace=ws)
+    target = dyd.clone() if alias == "dy" else xd.clone()
+    if alias == "dy":
+        capi.bn_train_bwd(target, bsums, target, xd, gd, bd, saved, acts, workspace=ws)
+    else:
+        capi.bn_train_bwd(target, bsums, dyd, target, gd, bd, saved, acts, workspace=ws)
+    torch.cuda.synchronize()
+    assert capi.fused_error_check() == 0
+    assert_bits_equal(host(target), host(want), "in-place backward over %s" % alias)
+
+
 def _sharded_single_launch(capi, x, dy, gamma, beta, slope, chain, mailboxes, rank, world, seq, count_total):
     c = x.shape[1]
     xd, dyd, gd, bd, sd = dev(x), dev(dy), dev(gamma), dev(beta), dev(slope)
