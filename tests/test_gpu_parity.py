@@ -470,6 +470,36 @@ def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chun
         assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
 
 
+@pytest.mark.parametrize("shape", [(16, 32, 28, 28), (37, 3, 8, 8), (5, 3, 7, 7)])
+def test_bn_train_matches_cudnn(capi, shape):
+    """Second opinion for the row that has no CPU reference code: the reference's training batch norm IS two cuDNN
+    calls (cudnnBatchNormalizationForwardTraining / Backward, CUDNN_BATCHNORM_SPATIAL,
+    nnforge/cuda/batch_norm_layer_updater_cuda.cu:89,145); torch exposes the same two calls."""
+    if not torch.backends.cudnn.is_available():
+        pytest.skip("cuDNN not available to torch")
+    g = synth.rng(2, salt=6200 + sum(shape))
+    x, dy = synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    xd, dyd, gd, bd = dev(x), dev(dy), dev(gamma), dev(beta)
+    eps = 1e-5
+    out, save_mean, save_invstd, reserve = torch.ops.aten.cudnn_batch_norm(xd, gd, bd, None, None, True, 0.1, eps)
+    dx_w, dgamma_w, dbeta_w = torch.ops.aten.cudnn_batch_norm_backward(xd, dyd, gd, None, None, save_mean, save_invstd, eps, reserve)
+    ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, shape[2] * shape[3]), dtype=torch.uint8, device="cuda")
+    y, saved, sums, bsums = torch.empty_like(xd), torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+    dx, gg, gb = torch.empty_like(xd), torch.zeros(c, device="cuda"), torch.zeros(c, device="cuda")
+    capi.bn_train_fwd(y, saved, sums, xd, gd, bd, eps, [], workspace=ws)
+    capi.bn_train_bwd(dx, bsums, dyd, xd, gd, bd, saved, [], grad_gamma=gg, grad_beta=gb, workspace=ws)
+    torch.cuda.synchronize()
+    assert_close(host(saved)[:c], host(save_mean), "batch mean vs cuDNN")
+    assert_close(host(saved)[c:], host(save_invstd), "inverse std-dev vs cuDNN")
+    assert_close(host(y), host(out), "forward vs cuDNN", atol=2e-6)
+    assert_close(host(dx), host(dx_w), "backward vs cuDNN", atol=5e-6)
+    scale = np.sqrt(x.size // c)
+    assert np.abs(host(gb) - host(dbeta_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dbeta_w)).max()
+    assert np.abs(host(gg) - host(dgamma_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dgamma_w)).max()
+
+
 @pytest.mark.parametrize("alias", ["dy", "x"])
 def test_bn_train_bwd_in_place(capi, oracle, alias):
     """dx written over dy or over x (the reference lets the backward pass overwrite either): both must give the
