@@ -221,7 +221,9 @@ namespace nnf
 				s_item[2] = sp;
 			}
 			__syncthreads();
-			const uint32_t apply = s_item[0], ch = s_item[1], sp = s_item[2];
+			// the backward launch walks the channels downwards: whatever ran before it (the forward launch walks
+			// upwards) left the highest channels of x in L2
+			const uint32_t apply = s_item[0], ch = BWD ? p.c - 1 - s_item[1] : s_item[1], sp = s_item[2];
 			if (apply > 1)
 				return;
 			const uint32_t per_plane = p.hw >> 2;

@@ -176,15 +176,16 @@ namespace nnf
 									}
 									else
 									{
-										float in[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
-										const float rr[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
-										#pragma unroll
-										for (int k = 0; k < 4; ++k)
-										{
-											const uint32_t lp = g.d_hw.div((v << 2) + k);
-											in[k] = fused(in[k], rr[k], has_bn ? s_mult[lp] : 1.0F, has_bn ? s_add[lp] : 0.0F);
-										}
-										o = make_float4(in[0], in[1], in[2], in[3]);
+										// H*W not a multiple of 4: the vector may straddle one plane boundary
+										const uint32_t lp0 = g.d_hw.div(v << 2);
+										const uint32_t left = (lp0 + 1) * g.hw - (v << 2); // elements of this vector in plane lp0 (>= 1)
+										const uint32_t lp1 = left >= 4 ? lp0 : lp0 + 1;
+										const float m0 = has_bn ? s_mult[lp0] : 1.0F, a0 = has_bn ? s_add[lp0] : 0.0F;
+										const float m1 = has_bn ? s_mult[lp1] : 1.0F, a1 = has_bn ? s_add[lp1] : 0.0F;
+										o.x = fused(a[u].x, r[u].x, m0, a0);
+										o.y = fused(a[u].y, r[u].y, left > 1 ? m0 : m1, left > 1 ? a0 : a1);
+										o.z = fused(a[u].z, r[u].z, left > 2 ? m0 : m1, left > 2 ? a0 : a1);
+										o.w = fused(a[u].w, r[u].w, left > 3 ? m0 : m1, left > 3 ? a0 : a1);
 									}
 									st_stream(z4 + v, o);
 								}
