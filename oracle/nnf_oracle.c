@@ -550,3 +550,62 @@ void orc_bn_train_running_grad(float * grad_mean, float * grad_invsigma, const f
 		grad_invsigma[ch] += entry_count * (saved[c + ch] - invsigma[ch]);
 	}
 }
+
+/* ---- Negative log likelihood over channels (the loss behind softmax) ------------------------------
+ * nnforge/plain/negative_log_likelihood_layer_tester_plain.cpp:60-92 (the updater's forward is the same,
+ * negative_log_likelihood_layer_updater_plain.cpp:60-92): per (entry, pixel)
+ *   err = scale * mask * ( - sum over channels with actual > 0, ascending, of actual * logf(max(predicted, 1e-20)) )
+ * accumulated as err -= term, then multiplied by the total scale; 0 when the total scale is 0. */
+void orc_nll_fwd(float * err, const float * predicted, const float * actual, const float * mask, float scale, i64 n, i64 c, i64 hw)
+{
+	for (i64 e = 0; e < n; ++e)
+		for (i64 p = 0; p < hw; ++p)
+		{
+			float total_scale = scale;
+			if (mask)
+				total_scale *= mask[e * hw + p];
+			float v = 0.0F;
+			if (total_scale != 0.0F)
+			{
+				for (i64 f = 0; f < c; ++f)
+				{
+					const float pr = predicted[(e * c + f) * hw + p];
+					const float ac = actual[(e * c + f) * hw + p];
+					if (ac > 0.0F)
+						v -= ac * logf(pr < 1.0e-20F ? 1.0e-20F : pr); /* std::max(pr, 1e-20): a NaN prediction stays NaN */
+				}
+				v *= total_scale;
+			}
+			err[e * hw + p] = v;
+		}
+}
+
+/* nnforge/plain/negative_log_likelihood_layer_updater_plain.cpp:131-157: gradient with respect to the predictions,
+ *   g = (actual > 0 ? actual / max(predicted, 1e-20) : 0) * total_scale   (0 when the total scale is 0). */
+void orc_nll_bwd(float * dpredicted, const float * predicted, const float * actual, const float * mask, float scale, i64 n, i64 c, i64 hw,
+	int add_to_destination)
+{
+	for (i64 e = 0; e < n; ++e)
+		for (i64 p = 0; p < hw; ++p)
+		{
+			float total_scale = scale;
+			if (mask)
+				total_scale *= mask[e * hw + p];
+			for (i64 f = 0; f < c; ++f)
+			{
+				const i64 off = (e * c + f) * hw + p;
+				float g = 0.0F;
+				if (total_scale != 0.0F)
+				{
+					const float ac = actual[off], pr = predicted[off];
+					if (ac > 0.0F)
+						g = ac / (pr < 1.0e-20F ? 1.0e-20F : pr);
+					g *= total_scale;
+				}
+				if (add_to_destination)
+					dpredicted[off] += g;
+				else
+					dpredicted[off] = g;
+			}
+		}
+}

@@ -76,6 +76,18 @@ def main():
         out[name + "_dx"] = ref.maxpool_bwd(pdy, idx, px.shape)[0]
     y, idx, _ = ref.maxpool_fwd(px, (3, 3), (2, 2), is_min=True)
     out["pool32min_y"], out["pool32min_idx"] = y, idx
+    # negative log likelihood on the softmax outputs above (appended last: the vectors before it keep their draws)
+    for name, probs in (("nll", out["softmax"]), ("nll_row", out["softmax_row"])):
+        probs = probs.copy()
+        probs.flat[0] = 0.0       # clamped to 1e-20
+        probs.flat[1] = 1.0e-30
+        t = synth.targets(g, probs.shape)
+        t.flat[0] = 1.0           # a clamped prediction that counts
+        mask = (synth.uniform(g, (probs.shape[0], 1) + probs.shape[2:], 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (probs.shape[0], 1) + probs.shape[2:], 0.5, 2.0)
+        out[name + "_p"], out[name + "_t"], out[name + "_mask"] = probs, t, mask
+        out[name + "_err"] = ref.nll_fwd(probs, t, mask, 0.7)[0]
+        out[name + "_err_nomask"] = ref.nll_fwd(probs, t, None, 1.0, updater=True)[0]
+        out[name + "_grad"] = ref.nll_bwd(probs, t, mask, 0.7)[0]
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_backend.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -43,3 +43,16 @@ def with_edges(g, a):
         pos = g.choice(flat.size, ev.size, replace=False)
         flat[pos] = ev
     return a
+
+
+def targets(g, shape, soft_entries=1):
+    """Dense target tensor [N,C,H,W] for a loss over channels: one-hot labels per (entry, pixel); the first
+    `soft_entries` entries carry soft targets (random non-negative weights, about half of them zero)."""
+    n, c = shape[0], shape[1]
+    t = np.zeros(shape, np.float32)
+    labels = g.integers(0, c, size=(n,) + tuple(shape[2:]))
+    np.put_along_axis(t, labels[:, None], 1.0, axis=1)
+    for e in range(min(soft_entries, n)):
+        w = g.random(shape[1:], dtype=np.float32)
+        t[e] = w * (g.random(shape[1:]) > 0.5)
+    return t

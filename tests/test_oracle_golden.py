@@ -51,6 +51,14 @@ def test_softmax(oracle):
     assert_bits_equal(oracle.softmax_fwd(G["row"]), G["softmax_row"], "softmax rows")
 
 
+@pytest.mark.parametrize("name", ["nll", "nll_row"])
+def test_negative_log_likelihood(oracle, name):
+    p, t, mask = G[name + "_p"], G[name + "_t"], G[name + "_mask"]
+    assert_bits_equal(oracle.nll_fwd(p, t, mask, 0.7), G[name + "_err"], name + " forward")
+    assert_bits_equal(oracle.nll_fwd(p, t, None, 1.0), G[name + "_err_nomask"], name + " forward, no mask")
+    assert_bits_equal(oracle.nll_bwd(p, t, mask, 0.7), G[name + "_grad"], name + " gradient")
+
+
 @pytest.mark.parametrize("name,win,stride", [("pool32", (3, 3), (2, 2)), ("pool22", (2, 2), (2, 2)), ("pool_3x2_s1x2", (3, 2), (1, 2))])
 def test_maxpool(oracle, name, win, stride):
     y, idx = oracle.maxpool_fwd(G["px"], win, stride)

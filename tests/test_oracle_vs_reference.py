@@ -58,6 +58,23 @@ def test_softmax(oracle, reference, shape):
     assert_bits_equal(oracle.softmax_bwd(dy, y, dx=x), reference.softmax_bwd(dy, y, dx=x)[0], "softmax bwd add")
 
 
+@pytest.mark.parametrize("shape", [(2, 1, 1, 1), (3, 21, 4, 5), (4, 1000, 1, 1), (2, 5, 1, 9)])
+def test_negative_log_likelihood(oracle, reference, shape):
+    g = synth.rng(53, salt=sum(shape))
+    p = oracle.softmax_fwd(synth.normal(g, shape, 0.0, 3.0))
+    p.flat[0] = 0.0  # clamped predictions, one of them under a positive target
+    t = synth.targets(g, shape)
+    t.flat[0] = 1.0
+    mask = (synth.uniform(g, (shape[0], 1) + shape[2:], 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (shape[0], 1) + shape[2:], 0.5, 2.0)
+    for m, scale in ((None, 1.0), (mask, 0.7), (mask, 0.0)):
+        e = oracle.nll_fwd(p, t, m, scale)
+        assert_bits_equal(e, reference.nll_fwd(p, t, m, scale)[0], "nll tester")
+        assert_bits_equal(e, reference.nll_fwd(p, t, m, scale, updater=True)[0], "nll updater")
+        assert_bits_equal(oracle.nll_bwd(p, t, m, scale), reference.nll_bwd(p, t, m, scale)[0], "nll bwd")
+        seed = synth.normal(g, shape)
+        assert_bits_equal(oracle.nll_bwd(p, t, m, scale, dx=seed), reference.nll_bwd(p, t, m, scale, dx=seed)[0], "nll bwd add")
+
+
 @pytest.mark.parametrize("hw", [(7, 7), (9, 11), (14, 14), (5, 8)])
 @pytest.mark.parametrize("win,stride", [((3, 3), (2, 2)), ((2, 2), (2, 2)), ((3, 3), (1, 1)), ((2, 3), (2, 1)), ((1, 1), (1, 1)), ((5, 5), (3, 3))])
 def test_maxpool(oracle, reference, hw, win, stride):
