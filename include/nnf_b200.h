@@ -311,6 +311,26 @@ NNF_API int nnf_bn_train_bwd_apply_peer(nnf_stream_t stream, float * dx, const f
 	const float * mean, const float * invsigma, float entry_count,
 	int64_t n, int64_t c, int64_t hw, int add_to_destination);
 
+/* ---------------------------------------------------------------------------------------------
+ * The loss behind softmax: negative_log_likelihood_layer, stand-alone (replaces
+ * negative_log_likelihood_layer_tester_cuda / _updater_cuda, nnforge/cuda/negative_log_likelihood_layer_*_cuda.cu;
+ * semantics of nnforge/plain/negative_log_likelihood_layer_updater_plain.cpp:60-92, 131-157) and fused with the
+ * softmax layer in front of it (softmax_layer_*_cuda + the loss in one pass over HBM).
+ *   predicted / probs / logits / targets / dlogits / dpredicted: [n][c][hw];  err, mask: [n][hw] (mask may be NULL)
+ *   forward : err = scale*mask * ( - sum over channels with target > 0 of target * logf(max(p, 1e-20)) )
+ *   backward: dpredicted = (target > 0 ? target / max(p, 1e-20) : 0) * scale*mask   (the layer is a loss: no output errors)
+ *   fused forward : probs = softmax(logits) over channels, err as above from probs
+ *   fused backward: dlogits = probs * (g - sum_f g_f*probs_f), g = the gradient above (softmax_layer_updater_plain.cpp:100-166)
+ * add_to_destination accumulates into dpredicted / dlogits. */
+NNF_API int nnf_nll_fwd(nnf_stream_t stream, float * err, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_nll_bwd(nnf_stream_t stream, float * dpredicted, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination);
+NNF_API int nnf_softmax_nll_fwd(nnf_stream_t stream, float * probs, float * err, const float * logits, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_softmax_nll_bwd(nnf_stream_t stream, float * dlogits, const float * probs, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
 /* Batch-sharded training batch norm in ONE launch per direction and GPU (the sharded form of
  * nnf_bn_train_fwd / nnf_bn_train_bwd): statistics and apply work items share the launch, the second read
  * of x (and dy) comes from L2, and the per-channel sums cross the GPUs inside the launch - the item that

@@ -71,6 +71,10 @@ _SIGNATURES = {
     "nnf_bn_train_bwd_stats_publish": (_I, [_P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ, ct.POINTER(_P), _I, _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_apply_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                          _I64, _I64, _I64, _I]),
+    "nnf_nll_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
+    "nnf_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
+    "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
+    "nnf_softmax_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_bn_train_mailbox_bytes": (_SZ, [_I64]),
     "nnf_bn_train_fwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _D, _P, _SZ, ct.POINTER(_P), _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _D, _P, _SZ,
@@ -305,6 +309,26 @@ def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total,
     _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
                                       float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
                                       _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))
+
+
+def nll_fwd(err, predicted, targets, mask=None, scale=1.0, stream=None):
+    n, c, hw = _nchw(predicted)
+    _check(lib.nnf_nll_fwd(_stream(stream), _ptr(err), _ptr(predicted), _ptr(targets), _ptr(mask), scale, n, c, hw))
+
+
+def nll_bwd(dpredicted, predicted, targets, mask=None, scale=1.0, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(predicted)
+    _check(lib.nnf_nll_bwd(_stream(stream), _ptr(dpredicted), _ptr(predicted), _ptr(targets), _ptr(mask), scale, n, c, hw, int(add_to_destination)))
+
+
+def softmax_nll_fwd(probs, err, logits, targets, mask=None, scale=1.0, stream=None):
+    n, c, hw = _nchw(logits)
+    _check(lib.nnf_softmax_nll_fwd(_stream(stream), _ptr(probs), _ptr(err), _ptr(logits), _ptr(targets), _ptr(mask), scale, n, c, hw))
+
+
+def softmax_nll_bwd(dlogits, probs, targets, mask=None, scale=1.0, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(probs)
+    _check(lib.nnf_softmax_nll_bwd(_stream(stream), _ptr(dlogits), _ptr(probs), _ptr(targets), _ptr(mask), scale, n, c, hw, int(add_to_destination)))
 
 
 def bn_train_mailbox_bytes(c):

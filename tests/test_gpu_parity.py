@@ -591,6 +591,79 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi):
     assert capi.fused_error_check() == 0
 
 
+LOSS_SHAPES = [(256, 1000, 1, 1), (7, 1000, 1, 1), (5, 10, 1, 1), (3, 33, 1, 1), (2, 1100, 1, 1), (32, 21, 16, 16), (3, 21, 7, 5), (2, 5, 1, 9),
+               (2, 40, 6, 6)]
+
+
+@pytest.mark.parametrize("shape", LOSS_SHAPES)
+@pytest.mark.parametrize("masked", [False, True])
+def test_negative_log_likelihood(capi, oracle, shape, masked):
+    """Stand-alone loss layer against the plain restatement, on the same probabilities."""
+    g = synth.rng(1, salt=7000 + sum(shape))
+    p = oracle.softmax_fwd(synth.normal(g, shape, 0.0, 3.0))
+    p.flat[0] = 0.0  # clamped prediction under a positive target
+    t = synth.targets(g, shape)
+    t.flat[0] = 1.0
+    mshape = (shape[0], 1) + shape[2:]
+    mask = (synth.uniform(g, mshape, 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, mshape, 0.5, 2.0) if masked else None
+    scale = 0.7
+    pd, td, md = dev(p), dev(t), dev(mask) if masked else None
+    err = torch.empty(mshape, device="cuda")
+    capi.nll_fwd(err, pd, td, md, scale)
+    # logf of the device against glibc's, and for rows a different order of the channel sum: tolerance
+    assert_close(host(err), oracle.nll_fwd(p, t, mask, scale), "nll forward", atol=2e-6)
+    dp = torch.empty_like(pd)
+    capi.nll_bwd(dp, pd, td, md, scale)
+    assert_bits_equal(host(dp), oracle.nll_bwd(p, t, mask, scale), "nll gradient")
+    seed = synth.normal(g, shape)
+    acc = dev(seed)
+    capi.nll_bwd(acc, pd, td, md, scale, add_to_destination=True)
+    assert_bits_equal(host(acc), oracle.nll_bwd(p, t, mask, scale, dx=seed), "nll gradient, accumulated")
+
+
+@pytest.mark.parametrize("shape", LOSS_SHAPES)
+@pytest.mark.parametrize("masked", [False, True])
+def test_softmax_with_loss(capi, oracle, shape, masked):
+    """Softmax and the loss in one pass: forward against softmax then loss of the plain restatement; backward
+    against loss gradient then softmax backward, on the device's own probabilities."""
+    g = synth.rng(1, salt=7100 + sum(shape))
+    logits = synth.normal(g, shape, 0.0, 3.0)
+    t = synth.targets(g, shape)
+    mshape = (shape[0], 1) + shape[2:]
+    mask = (synth.uniform(g, mshape, 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, mshape, 0.5, 2.0) if masked else None
+    scale = 1.3
+    ld, td, md = dev(logits), dev(t), dev(mask) if masked else None
+    probs, err = torch.empty_like(ld), torch.empty(mshape, device="cuda")
+    capi.softmax_nll_fwd(probs, err, ld, td, md, scale)
+    # the same probabilities as the stand-alone softmax kernel, bit for bit
+    alone = torch.empty_like(ld)
+    capi.softmax_fwd(alone, ld)
+    hw = shape[2] * shape[3]
+    if (hw == 1 and shape[1] % 4 == 0 and shape[1] <= 1024) or (hw > 1 and shape[1] <= 32):
+        assert_bits_equal(host(probs), host(alone), "probabilities of the fused forward")  # same kernel structure as the stand-alone softmax
+    else:
+        assert_close(host(probs), host(alone), "probabilities of the fused forward")
+    assert_close(host(probs), oracle.softmax_fwd(logits), "fused softmax")
+    p = host(probs)
+    assert_close(host(err), oracle.nll_fwd(p, t, mask, scale), "fused loss", atol=2e-6)
+    want = oracle.softmax_bwd(oracle.nll_bwd(p, t, mask, scale), p)
+    dl = torch.empty_like(ld)
+    capi.softmax_nll_bwd(dl, probs, td, md, scale)
+    if shape[2] * shape[3] > 1:
+        assert_bits_equal(host(dl), want, "fused backward (ascending channel sums)")
+    else:
+        assert_close(host(dl), want, "fused backward", atol=2e-6)
+    # the two stand-alone kernels one after the other give the same as the fused backward
+    g1, two = torch.empty_like(ld), torch.empty_like(ld)
+    capi.nll_bwd(g1, probs, td, md, scale)
+    capi.softmax_bwd(two, g1, probs)
+    assert_close(host(dl), host(two), "fused against unfused backward", atol=2e-6)
+    seed = synth.normal(g, shape)
+    acc = dev(seed)
+    capi.softmax_nll_bwd(acc, probs, td, md, scale, add_to_destination=True)
+    assert_close(host(acc), seed.astype(np.float64) + host(dl), "fused backward, accumulated", atol=2e-6)
+
+
 def test_errors_are_reported_not_thrown(capi):
     x = torch.zeros((2, 3, 4, 4), device="cuda")
     with pytest.raises(capi.NnfError) as e:
