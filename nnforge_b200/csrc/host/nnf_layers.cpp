@@ -123,6 +123,23 @@ namespace nnf_b200
 			int get_input_index_layer_can_write() const override { return 0; }
 		};
 
+		// negative_log_likelihood_layer: inputs = predicted, actual[, scale mask]; output = one value per (entry, pixel)
+		// (nnforge/cuda/negative_log_likelihood_layer_tester_cuda.cu)
+		class negative_log_likelihood_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("negative_log_likelihood_layer needs the predicted and the actual values");
+				check(nnf_nll_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), input_buffers.size() > 2 ? f(input_buffers[2]) : nullptr,
+					layer_schema->scale, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
+		};
+
 		class max_subsampling_layer_tester_b200 : public layer_tester_b200
 		{
 		public:
@@ -239,6 +256,36 @@ namespace nnf_b200
 			int get_input_index_layer_can_write(const layer_action& action) const override { return action.get_action_type() == layer_action::backward_data ? 0 : -1; }
 			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
 			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return true; }
+		};
+
+		// (nnforge/cuda/negative_log_likelihood_layer_updater_cuda.cu; the layer is a loss: backward reads no output errors)
+		class negative_log_likelihood_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("negative_log_likelihood_layer needs the predicted and the actual values");
+				check(nnf_nll_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), input_buffers.size() > 2 ? f(input_buffers[2]) : nullptr,
+					layer_schema->scale, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int input_index, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>& input_neurons_buffers, device_buffer::const_ptr,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				if (input_index != 0)
+					throw neural_network_exception("negative_log_likelihood_layer_updater cannot do backward propagation for targets or the scale mask");
+				check(nnf_nll_bwd(stream_id, f(input_errors_buffer), f(input_neurons_buffers.at(0)), f(input_neurons_buffers.at(1)),
+					input_neurons_buffers.size() > 2 ? f(input_neurons_buffers[2]) : nullptr, layer_schema->scale, entry_count,
+					input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0));
+			}
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return true; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
 		};
 
 		class max_subsampling_layer_updater_b200 : public layer_updater_b200
@@ -394,7 +441,7 @@ namespace nnf_b200
 
 	std::vector<std::string> layer_factory_b200::get_type_names() const
 	{
-		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling"};
+		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood"};
 	}
 
 	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
@@ -406,6 +453,7 @@ namespace nnf_b200
 		else if (is_activation(n)) t.reset(new activation_layer_tester_b200());
 		else if (n == "Add") t.reset(new add_layer_tester_b200());
 		else if (n == "Softmax") t.reset(new softmax_layer_tester_b200());
+		else if (n == "NegativeLogLikelihood") t.reset(new negative_log_likelihood_layer_tester_b200());
 		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
 		else throw neural_network_exception("No layer tester is registered with id " + n);
 		t->configure(in, out, l);
@@ -421,6 +469,7 @@ namespace nnf_b200
 		else if (is_activation(n)) u.reset(new activation_layer_updater_b200());
 		else if (n == "Add") u.reset(new add_layer_updater_b200());
 		else if (n == "Softmax") u.reset(new softmax_layer_updater_b200());
+		else if (n == "NegativeLogLikelihood") u.reset(new negative_log_likelihood_layer_updater_b200());
 		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
 		else throw neural_network_exception("No layer updater is registered with id " + n);
 		u->configure(in, out, l, actions);
@@ -430,6 +479,8 @@ namespace nnf_b200
 	layer_configuration_specific get_output_layer_configuration_specific(const layer& l, const std::vector<layer_configuration_specific>& inputs)
 	{
 		layer_configuration_specific res = inputs.at(0);
+		if (l.type_name == "NegativeLogLikelihood")
+			res.feature_map_count = 1; // negative_log_likelihood_layer.cpp:66
 		if (l.type_name == "MaxSubsampling")
 		{
 			const nnf_pool p = make_pool(l, inputs[0]);
@@ -486,7 +537,7 @@ namespace
 
 NNFH_API const char * nnfh_last_error() { return g_error.c_str(); }
 
-// params: negative_slope | scale, steepness | alpha | epsilon, by layer type; pool = {win_w, win_h, stride_w, stride_h, round_up_w, round_up_h, is_min}
+// params: negative_slope | scale, steepness | alpha | epsilon | scale (loss), by layer type; pool = {win_w, win_h, stride_w, stride_h, round_up_w, round_up_h, is_min}
 NNFH_API void * nnfh_create(const char * type_name, int updater, const float * params, const int * pool, unsigned int feature_maps, unsigned int w, unsigned int h,
 	int input_count, int with_backward)
 {
@@ -499,6 +550,7 @@ NNFH_API void * nnfh_create(const char * type_name, int updater, const float * p
 		if (l.type_name == "ReLU") l.negative_slope = params[0];
 		if (l.type_name == "TanH") { l.scale = params[0]; l.steepness = params[1]; }
 		if (l.type_name == "Add") l.alpha = params[0];
+		if (l.type_name == "NegativeLogLikelihood") l.scale = params[0];
 		if (l.type_name == "BatchNorm") l.epsilon = params[0];
 		if (l.type_name == "MaxSubsampling")
 		{
@@ -575,6 +627,17 @@ NNFH_API int nnfh_updater_backward_data(void * h, void * stream, void * in_err, 
 	static_cast<handle *>(h)->updater->enqueue_backward_data_propagation((cudaStream_t)stream, 0, buf(in_err), cbuf(out_err), {}, cvec(data, n_data), {},
 		std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), cbuf(out_neurons), {}, device_buffer::ptr(), device_buffer::ptr(),
 		cbuf(temp_fixed), cbuf(temp_per_entry), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+// the same for layers with several inputs (the loss layers): every input's neurons are handed over
+NNFH_API int nnfh_updater_backward_data_inputs(void * h, void * stream, void * in_err, const void * out_err, const void * const * in_neurons, int n_in_neurons,
+	const void * out_neurons, int add_update_to_destination, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_data_propagation((cudaStream_t)stream, 0, buf(in_err), cbuf(out_err), {}, {}, {},
+		cvec(in_neurons, n_in_neurons), cbuf(out_neurons), {}, device_buffer::ptr(), device_buffer::ptr(),
+		device_buffer::const_ptr(), device_buffer::const_ptr(), add_update_to_destination != 0, entry_count);
 	NNFH_CATCH
 }
 

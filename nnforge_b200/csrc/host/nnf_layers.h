@@ -66,7 +66,7 @@ namespace nnf_b200
 		std::string type_name;                      // layer::get_type_name()
 		float epsilon = 2.0e-5F;                    // BatchNorm (default_batch_normalization_epsilon, nnforge/batch_norm_layer.cpp:28)
 		float negative_slope = 0.0F;                // ReLU
-		float scale = 1.0F, steepness = 1.0F;       // TanH
+		float scale = 1.0F, steepness = 1.0F;       // TanH; scale also NegativeLogLikelihood
 		float alpha = 1.0F;                         // Add
 		std::vector<unsigned int> subsampling_sizes; // MaxSubsampling
 		std::vector<unsigned int> strides;

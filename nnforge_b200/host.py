@@ -26,6 +26,7 @@ lib.nnfh_updater_query.restype = ct.c_longlong
 lib.nnfh_updater_query.argtypes = [_P, ct.c_int, ct.c_int]
 lib.nnfh_updater_forward.argtypes = [_P, _P, _P, ct.POINTER(_P), ct.c_int, ct.POINTER(_P), ct.c_int, _P, ct.c_size_t, _P, _P, ct.c_uint]
 lib.nnfh_updater_backward_data.argtypes = [_P, _P, _P, _P, ct.POINTER(_P), ct.c_int, _P, _P, _P, _P, ct.c_int, ct.c_uint]
+lib.nnfh_updater_backward_data_inputs.argtypes = [_P, _P, _P, _P, ct.POINTER(_P), ct.c_int, _P, ct.c_int, ct.c_uint]
 lib.nnfh_updater_backward_weights.argtypes = [_P, _P, ct.POINTER(_P), ct.c_int, _P, _P, _P, ct.c_size_t, ct.c_uint]
 lib.nnfh_updater_backward_data_and_weights.argtypes = [_P, _P, _P, _P, ct.POINTER(_P), ct.c_int, ct.POINTER(_P), ct.c_int, _P, _P, ct.c_size_t, _P, ct.c_int, ct.c_uint]
 
@@ -117,6 +118,13 @@ class Updater(_Layer):
         _check(lib.nnfh_updater_backward_data(self.h, _stream(), _ptr(input_errors_buffer), _ptr(output_errors_buffer), d, nd, _ptr(input_neurons_buffer),
                                               _ptr(output_neurons_buffer), _ptr(temporary_fixed_buffer), _ptr(temporary_per_entry_buffer),
                                               int(add_update_to_destination), entry_count))
+
+    def enqueue_backward_data_propagation_inputs(self, input_errors_buffer, output_errors_buffer, input_neurons_buffers, output_neurons_buffer, entry_count,
+                                                 add_update_to_destination=False):
+        """Backward for layers with several inputs (the loss layers): all input neuron buffers are passed."""
+        i, ni = _arr(input_neurons_buffers)
+        _check(lib.nnfh_updater_backward_data_inputs(self.h, _stream(), _ptr(input_errors_buffer), _ptr(output_errors_buffer), i, ni,
+                                                     _ptr(output_neurons_buffer), int(add_update_to_destination), entry_count))
 
     def enqueue_backward_weights_propagation(self, gradient, input_neurons_buffer, output_errors_buffer, entry_count, temporary_working_fixed_buffer=None):
         g, ng = _arr(gradient)

@@ -139,3 +139,20 @@ def test_batch_norm_updater_fused_backward_data_and_weights(host, oracle):
     assert_close(out(grads[3]), gi, "running inverse-sigma pseudo-gradient", atol=1e-5)
     with pytest.raises(host.HostLayerError):  # too small a working buffer is refused, not overrun
         u.enqueue_forward_propagation(y, data, [dev(x)], n, temporary_working_fixed_buffer=torch.empty(16, dtype=torch.uint8, device="cuda"), temporary_fixed_buffer=saved)
+
+
+def test_negative_log_likelihood_objects(host, oracle):
+    g = synth.rng(3, salt=903)
+    n, c, h, w = SHAPE
+    p = oracle.softmax_fwd(synth.normal(g, SHAPE, 0.0, 2.0))
+    t = synth.targets(g, SHAPE)
+    mask = synth.uniform(g, (n, 1, h, w), 0.0, 2.0)
+    err = torch.empty((n, 1, h, w), device="cuda")
+    host.Tester("NegativeLogLikelihood", c, w, h, params=[0.5], input_count=2).enqueue_forward_propagation(err, [], [dev(p), dev(t)], n)
+    assert_close(out(err), oracle.nll_fwd(p, t, None, 0.5), "loss tester", atol=2e-6)
+    u = host.Updater("NegativeLogLikelihood", c, w, h, params=[0.5], input_count=3)
+    u.enqueue_forward_propagation(err, [], [dev(p), dev(t), dev(mask)], n)
+    assert_close(out(err), oracle.nll_fwd(p, t, mask, 0.5), "loss updater forward", atol=2e-6)
+    dp = torch.empty(SHAPE, device="cuda")
+    u.enqueue_backward_data_propagation_inputs(dp, None, [dev(p), dev(t), dev(mask)], None, n)
+    assert_bits_equal(out(dp), oracle.nll_bwd(p, t, mask, 0.5), "loss updater backward")

@@ -3,12 +3,15 @@ answers and error behaviour. No kernel is launched here."""
 import pytest
 
 
-def test_factory_knows_the_nine_type_names_and_rejects_others():
+def test_factory_knows_its_type_names_and_rejects_others():
     from nnforge_b200 import host
     for name in ("BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add"):
         assert host.Tester(name, 8, 5, 5).h
         assert host.Updater(name, 8, 5, 5).h
     assert host.Tester("MaxSubsampling", 8, 9, 9, pool=[3, 3, 2, 2, 0, 0, 0]).h
+    assert host.Tester("NegativeLogLikelihood", 8, 5, 5, params=[1.0], input_count=2).h
+    loss = host.Updater("NegativeLogLikelihood", 8, 5, 5, params=[1.0], input_count=3)
+    assert loss.is_backward_data_dependent_on_input_buffer() and not loss.is_backward_data_dependent_on_output_buffer()
     with pytest.raises(host.HostLayerError) as e:
         host.Tester("Convolution", 8, 5, 5)
     assert "Convolution" in str(e.value)
