@@ -250,6 +250,17 @@ def run_sweep(args):
         report(1, "softmax fwd %s" % (list(shape),), timeit(lambda i: capi.softmax_fwd(ys[i], xs[i]), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
         report(1, "softmax bwd %s" % (list(shape),), timeit(lambda i: capi.softmax_bwd(dx, xs[i], ys[i]), nb), 12 * e, "%d rotating buffers, graph replay" % nb)
         del xs, ys, dx
+    # beyond the five configurations: softmax fused with the loss behind it, at sizes above L2
+    for shape in [(65536, 1000, 1, 1), (512, 21, 128, 128)]:
+        e = shape[0] * shape[1] * shape[2] * shape[3]
+        logits = torch.randn(shape, device="cuda") * 3
+        labels = torch.randint(0, shape[1], (shape[0],) + shape[2:], device="cuda")
+        targets = torch.zeros(shape, device="cuda").scatter_(1, labels.unsqueeze(1), 1.0)
+        probs, dl = torch.empty_like(logits), torch.empty_like(logits)
+        err = torch.empty((shape[0], 1) + shape[2:], device="cuda")
+        report(1, "softmax+nll fwd fused %s" % (list(shape),), timeit(lambda i: capi.softmax_nll_fwd(probs, err, logits, targets), 1), 12 * e)
+        report(1, "softmax+nll bwd fused %s" % (list(shape),), timeit(lambda i: capi.softmax_nll_bwd(dl, probs, targets), 1), 12 * e)
+        del logits, labels, targets, probs, dl, err
     # config 2: training BN + PReLU + ELU (the default benchmark's kernels, timed one by one)
     shape = (N_PER_GPU, C, H, W)
     e = elements_per_gpu()
