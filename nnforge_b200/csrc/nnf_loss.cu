@@ -317,7 +317,7 @@ namespace nnf
 								if (MODE == kFusedFwd)
 								{
 									pr = __fmul_rn(pr, mult);
-									st_stream(out + int64_t(f) * hw, pr);
+									out[int64_t(f) * hw] = pr;
 								}
 								if (total_scale != 0.0F)
 									e = __fsub_rn(e, nll_term(pr, t[f]));
@@ -331,7 +331,7 @@ namespace nnf
 							if (MODE == kFusedFwd)
 							{
 								pr = __fmul_rn(fast_exp(__fsub_rn(pr, m)), mult);
-								st_stream(out + int64_t(f) * hw, pr);
+								out[int64_t(f) * hw] = pr;
 							}
 							if (total_scale != 0.0F)
 								e = __fsub_rn(e, nll_term(pr, target(f)));
@@ -361,10 +361,7 @@ namespace nnf
 					{
 						const float r = MODE == kFusedBwd ? __fmul_rn(pr, __fsub_rn(g, s)) : g;
 						float * o = out + int64_t(f) * hw;
-						if (p.add)
-							*o = __fadd_rn(*o, r);
-						else
-							st_stream(o, r);
+						*o = p.add ? __fadd_rn(*o, r) : r;
 					};
 					if (CMAX > 0)
 					{

@@ -299,7 +299,7 @@ namespace nnf
 					#pragma unroll
 					for (int f = 0; f < CMAX; ++f)
 						if (f < c)
-							st_stream(out + base + int64_t(f) * hw, __fmul_rn(v[f], mult));
+							out[base + int64_t(f) * hw] = __fmul_rn(v[f], mult);
 				}
 				else
 				{
