@@ -331,6 +331,13 @@ NNF_API int nnf_softmax_nll_fwd(nnf_stream_t stream, float * probs, float * err,
 NNF_API int nnf_softmax_nll_bwd(nnf_stream_t stream, float * dlogits, const float * probs, const float * targets, const float * mask,
 	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination);
 
+/* accuracy_layer (replaces accuracy_layer_tester_cuda / _updater_cuda, nnforge/cuda/accuracy_layer_tester_cuda.cu; semantics of
+ * nnforge/plain/accuracy_layer_tester_plain.cpp:64-110): per (entry, pixel) the actual class is the first channel with the
+ * largest target; rank = number of channels whose prediction is larger than that class's, or equal with a smaller index.
+ * out[n][top_n + 1][hw]: out[k] = (rank <= k ? mask : 0) for k < top_n, out[top_n] = mask (1 without a mask). */
+NNF_API int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * predicted, const float * targets, const float * mask,
+	int top_n, int64_t n, int64_t c, int64_t hw);
+
 /* Batch-sharded training batch norm in ONE launch per direction and GPU (the sharded form of
  * nnf_bn_train_fwd / nnf_bn_train_bwd): statistics and apply work items share the launch, the second read
  * of x (and dy) comes from L2, and the per-channel sums cross the GPUs inside the launch - the item that

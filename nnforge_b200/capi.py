@@ -71,6 +71,7 @@ _SIGNATURES = {
     "nnf_bn_train_bwd_stats_publish": (_I, [_P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _I64, _I64, _I64, _P, _SZ, ct.POINTER(_P), _I, _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_apply_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                          _I64, _I64, _I64, _I]),
+    "nnf_accuracy_fwd": (_I, [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64]),
     "nnf_nll_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
@@ -309,6 +310,11 @@ def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total,
     _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
                                       float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
                                       _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))
+
+
+def accuracy_fwd(out, predicted, targets, mask=None, top_n=1, stream=None):
+    n, c, hw = _nchw(predicted)
+    _check(lib.nnf_accuracy_fwd(_stream(stream), _ptr(out), _ptr(predicted), _ptr(targets), _ptr(mask), top_n, n, c, hw))
 
 
 def nll_fwd(err, predicted, targets, mask=None, scale=1.0, stream=None):

@@ -140,6 +140,22 @@ namespace nnf_b200
 			}
 		};
 
+		// accuracy_layer: inputs = predicted, actual[, mask]; output = top_n + 1 planes per entry (nnforge/cuda/accuracy_layer_tester_cuda.cu)
+		class accuracy_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("accuracy_layer needs the predicted and the actual values");
+				check(nnf_accuracy_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), input_buffers.size() > 2 ? f(input_buffers[2]) : nullptr,
+					(int)layer_schema->top_n, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
+		};
+
 		class max_subsampling_layer_tester_b200 : public layer_tester_b200
 		{
 		public:
@@ -286,6 +302,22 @@ namespace nnf_b200
 			}
 			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return true; }
 			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
+		};
+
+		// forward only, like the stock updater (nnforge/cuda/accuracy_layer_updater_cuda.cu)
+		class accuracy_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("accuracy_layer needs the predicted and the actual values");
+				check(nnf_accuracy_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), input_buffers.size() > 2 ? f(input_buffers[2]) : nullptr,
+					(int)layer_schema->top_n, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
 		};
 
 		class max_subsampling_layer_updater_b200 : public layer_updater_b200
@@ -441,7 +473,7 @@ namespace nnf_b200
 
 	std::vector<std::string> layer_factory_b200::get_type_names() const
 	{
-		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood"};
+		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood", "Accuracy"};
 	}
 
 	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
@@ -454,6 +486,7 @@ namespace nnf_b200
 		else if (n == "Add") t.reset(new add_layer_tester_b200());
 		else if (n == "Softmax") t.reset(new softmax_layer_tester_b200());
 		else if (n == "NegativeLogLikelihood") t.reset(new negative_log_likelihood_layer_tester_b200());
+		else if (n == "Accuracy") t.reset(new accuracy_layer_tester_b200());
 		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
 		else throw neural_network_exception("No layer tester is registered with id " + n);
 		t->configure(in, out, l);
@@ -470,6 +503,7 @@ namespace nnf_b200
 		else if (n == "Add") u.reset(new add_layer_updater_b200());
 		else if (n == "Softmax") u.reset(new softmax_layer_updater_b200());
 		else if (n == "NegativeLogLikelihood") u.reset(new negative_log_likelihood_layer_updater_b200());
+		else if (n == "Accuracy") u.reset(new accuracy_layer_updater_b200());
 		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
 		else throw neural_network_exception("No layer updater is registered with id " + n);
 		u->configure(in, out, l, actions);
@@ -481,6 +515,8 @@ namespace nnf_b200
 		layer_configuration_specific res = inputs.at(0);
 		if (l.type_name == "NegativeLogLikelihood")
 			res.feature_map_count = 1; // negative_log_likelihood_layer.cpp:66
+		if (l.type_name == "Accuracy")
+			res.feature_map_count = l.top_n + 1; // accuracy_layer.cpp:62
 		if (l.type_name == "MaxSubsampling")
 		{
 			const nnf_pool p = make_pool(l, inputs[0]);
@@ -537,7 +573,7 @@ namespace
 
 NNFH_API const char * nnfh_last_error() { return g_error.c_str(); }
 
-// params: negative_slope | scale, steepness | alpha | epsilon | scale (loss), by layer type; pool = {win_w, win_h, stride_w, stride_h, round_up_w, round_up_h, is_min}
+// params: negative_slope | scale, steepness | alpha | epsilon | scale (loss) | top_n, by layer type; pool = {win_w, win_h, stride_w, stride_h, round_up_w, round_up_h, is_min}
 NNFH_API void * nnfh_create(const char * type_name, int updater, const float * params, const int * pool, unsigned int feature_maps, unsigned int w, unsigned int h,
 	int input_count, int with_backward)
 {
@@ -551,6 +587,7 @@ NNFH_API void * nnfh_create(const char * type_name, int updater, const float * p
 		if (l.type_name == "TanH") { l.scale = params[0]; l.steepness = params[1]; }
 		if (l.type_name == "Add") l.alpha = params[0];
 		if (l.type_name == "NegativeLogLikelihood") l.scale = params[0];
+		if (l.type_name == "Accuracy") l.top_n = (unsigned int)params[0];
 		if (l.type_name == "BatchNorm") l.epsilon = params[0];
 		if (l.type_name == "MaxSubsampling")
 		{

@@ -68,6 +68,7 @@ namespace nnf_b200
 		float negative_slope = 0.0F;                // ReLU
 		float scale = 1.0F, steepness = 1.0F;       // TanH; scale also NegativeLogLikelihood
 		float alpha = 1.0F;                         // Add
+		unsigned int top_n = 1;                     // Accuracy
 		std::vector<unsigned int> subsampling_sizes; // MaxSubsampling
 		std::vector<unsigned int> strides;
 		std::vector<bool> round_ups;

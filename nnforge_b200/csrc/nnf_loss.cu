@@ -1,5 +1,6 @@
-// The loss behind channel softmax: negative log likelihood (nnforge/plain/negative_log_likelihood_layer_*_plain.cpp,
-// nnforge/cuda/negative_log_likelihood_layer_*_cuda.cu), stand-alone and fused with the softmax in front of it.
+// The loss side of channel softmax: negative log likelihood (nnforge/plain/negative_log_likelihood_layer_*_plain.cpp,
+// nnforge/cuda/negative_log_likelihood_layer_*_cuda.cu), stand-alone and fused with the softmax in front of it, and
+// the top-n accuracy layer (end of the file).
 //
 //   forward : err[n][pixel]  = total_scale * ( - sum over channels with target > 0 of target * logf(max(p, 1e-20)) )
 //   backward: dp[n][f][pixel] = (target > 0 ? target / max(p, 1e-20) : 0) * total_scale
@@ -440,7 +441,178 @@ namespace nnf
 	}
 }
 
+namespace nnf
+{
+	namespace
+	{
+		// ---- top-n accuracy (nnforge/plain/accuracy_layer_tester_plain.cpp:64-110, nnforge/cuda/accuracy_layer_tester_cuda.cu) ----
+		// The actual class is the first channel with the largest target; rank = channels whose prediction beats that
+		// class's (larger, or equal with a smaller index); out[k] = rank <= k ? mask : 0 for k < top_n, out[top_n] = mask.
+		struct accuracy_params
+		{
+			float * out;            // [n][top_n + 1][hw]
+			const float * predicted;
+			const float * targets;
+			const float * mask;     // [n][hw] or null
+			int c, top_n;
+			int64_t rows;           // H*W == 1: entries; else pixels of this launch
+			uint32_t hw;
+			fastdiv hwdiv;
+		};
+
+		__device__ __forceinline__ void accuracy_emit(const accuracy_params& p, float * out, int64_t plane_stride, int rank, float m)
+		{
+			for (int k = 0; k < p.top_n; ++k)
+				out[k * plane_stride] = rank <= k ? m : 0.0F;
+			out[p.top_n * plane_stride] = m;
+		}
+
+		// H*W == 1: warp per row
+		__global__ void __launch_bounds__(256) accuracy_rows_kernel(const accuracy_params p)
+		{
+			const int lane = threadIdx.x & 31;
+			const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+			const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+			for (int64_t row = warp; row < p.rows; row += nwarps)
+			{
+				const float m = p.mask ? __ldg(p.mask + row) : 1.0F;
+				int rank = 0;
+				if (m != 0.0F)
+				{
+					const float * tg = p.targets + row * p.c;
+					const float * pr = p.predicted + row * p.c;
+					float best = kLossMaxSeed;
+					int cls = -1;
+					for (int f = lane; f < p.c; f += 32)
+					{
+						const float a = ld_stream(tg + f);
+						if (a > best)
+						{
+							best = a;
+							cls = f;
+						}
+					}
+					// first channel holding the largest target over the whole row
+					#pragma unroll
+					for (int o = 16; o > 0; o >>= 1)
+					{
+						const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+						const int oc = __shfl_xor_sync(0xffffffffu, cls, o);
+						if (oc >= 0 && (cls < 0 || ob > best || (ob == best && oc < cls)))
+						{
+							best = ob;
+							cls = oc;
+						}
+					}
+					if (cls >= 0)
+					{
+						const float ref = __ldg(pr + cls);
+						int count = 0;
+						for (int f = lane; f < p.c; f += 32)
+						{
+							const float v = ld_stream(pr + f);
+							count += (v > ref || (v == ref && f < cls)) ? 1 : 0;
+						}
+						#pragma unroll
+						for (int o = 16; o > 0; o >>= 1)
+							count += __shfl_xor_sync(0xffffffffu, count, o);
+						rank = count;
+					}
+				}
+				if (lane == 0)
+					accuracy_emit(p, p.out + row * (p.top_n + 1), 1, rank, m);
+			}
+		}
+
+		// H*W > 1: thread per pixel, channels strided by H*W
+		__global__ void __launch_bounds__(256) accuracy_pixels_kernel(const accuracy_params p)
+		{
+			const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+			for (int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < p.rows; q += stride)
+			{
+				const uint32_t entry = p.hwdiv.div((uint32_t)q);
+				const uint32_t pix = (uint32_t)q - entry * p.hw;
+				const int64_t base = int64_t(entry) * p.c * p.hw + pix;
+				const float m = p.mask ? __ldg(p.mask + q) : 1.0F;
+				int rank = 0;
+				if (m != 0.0F)
+				{
+					float best = kLossMaxSeed;
+					int cls = -1;
+					for (int f = 0; f < p.c; ++f)
+					{
+						const float a = ld_stream(p.targets + base + int64_t(f) * p.hw);
+						if (a > best)
+						{
+							best = a;
+							cls = f;
+						}
+					}
+					if (cls >= 0)
+					{
+						const float ref = p.predicted[base + int64_t(cls) * p.hw];
+						for (int f = 0; f < p.c; ++f)
+						{
+							const float v = ld_stream(p.predicted + base + int64_t(f) * p.hw);
+							rank += (v > ref || (v == ref && f < cls)) ? 1 : 0;
+						}
+					}
+				}
+				accuracy_emit(p, p.out + int64_t(entry) * (p.top_n + 1) * p.hw + pix, p.hw, rank, m);
+			}
+		}
+	}
+}
+
 using namespace nnf;
+
+extern "C" int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * predicted, const float * targets, const float * mask,
+	int top_n, int64_t n, int64_t c, int64_t hw)
+{
+	if (n < 0 || c <= 0 || hw <= 0 || top_n < 1)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_accuracy_fwd: bad extents n=%lld c=%lld hw=%lld top_n=%d", (long long)n, (long long)c, (long long)hw, top_n);
+	if (n == 0)
+		return NNF_OK;
+	if (!out || !predicted || !targets)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_accuracy_fwd: null pointer");
+	if (c > 0x7fffffff || hw > 0x7fffffff)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_accuracy_fwd: extent too large");
+	cudaStream_t s = (cudaStream_t)stream;
+	accuracy_params p = {};
+	p.c = (int)c;
+	p.top_n = top_n;
+	if (hw == 1)
+	{
+		p.out = out; p.predicted = predicted; p.targets = targets; p.mask = mask;
+		p.rows = n;
+		p.hw = 1;
+		const int64_t blocks_needed = div_up(n, 8);
+		const int grid = (int)(blocks_needed < int64_t(kSmCount) * 64 ? blocks_needed : int64_t(kSmCount) * 64);
+		accuracy_rows_kernel<<<grid, 256, 0, s>>>(p);
+		return check_launch("accuracy_rows_kernel");
+	}
+	const int64_t entries_per_launch = kMaxElemsPerLaunch / hw;
+	if (entries_per_launch < 1)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_accuracy_fwd: hw too large");
+	for (int64_t e0 = 0; e0 < n; e0 += entries_per_launch)
+	{
+		const int64_t ne = (n - e0 < entries_per_launch) ? (n - e0) : entries_per_launch;
+		p.out = out + e0 * (top_n + 1) * hw;
+		p.predicted = predicted + e0 * c * hw;
+		p.targets = targets + e0 * c * hw;
+		p.mask = mask ? mask + e0 * hw : nullptr;
+		p.rows = ne * hw;
+		p.hw = (uint32_t)hw;
+		p.hwdiv = fastdiv((uint32_t)hw);
+		const int64_t blocks_needed = div_up(p.rows, 256);
+		const int grid = (int)(blocks_needed < int64_t(kSmCount) * 128 ? blocks_needed : int64_t(kSmCount) * 128);
+		accuracy_pixels_kernel<<<grid, 256, 0, s>>>(p);
+		const int st = check_launch("accuracy_pixels_kernel");
+		if (st != NNF_OK)
+			return st;
+	}
+	return NNF_OK;
+}
 
 extern "C" int nnf_softmax_nll_fwd(nnf_stream_t stream, float * probs, float * err, const float * logits, const float * targets, const float * mask,
 	float scale, int64_t n, int64_t c, int64_t hw)

@@ -184,6 +184,16 @@ class Oracle:
         self.lib.orc_nll_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), _i64(n), _i64(c), _i64(hw), int(add))
         return out
 
+    def accuracy_fwd(self, predicted, actual, mask=None, top_n=1):
+        """predicted, actual [N,C,H,W]; mask [N,1,H,W] or None -> [N,top_n+1,H,W]."""
+        predicted, actual = _c(predicted), _c(actual)
+        n, c = predicted.shape[0], predicted.shape[1]
+        hw = predicted.size // max(n * c, 1)
+        out = np.empty((n, top_n + 1) + predicted.shape[2:], np.float32)
+        m = _c(mask) if mask is not None else None
+        self.lib.orc_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, _i64(top_n), _i64(n), _i64(c), _i64(hw))
+        return out
+
     # ---- max subsampling -----------------------------------------------------------------------
     def maxpool_out_size(self, size, window, stride, round_up=False):
         return int(self.lib.orc_maxpool_out_size(size, window, stride, int(round_up)))
@@ -284,7 +294,7 @@ class Reference:
         for fn in ("ref_bn_infer", "ref_relu_fwd", "ref_relu_bwd", "ref_prelu_fwd", "ref_prelu_bwd_data", "ref_prelu_bwd_weights",
                    "ref_elu_fwd", "ref_elu_bwd", "ref_tanh_fwd", "ref_tanh_bwd", "ref_sigmoid_fwd", "ref_sigmoid_bwd", "ref_softmax_fwd",
                    "ref_softmax_upd_fwd", "ref_softmax_bwd", "ref_add_fwd", "ref_add_bwd", "ref_maxpool_fwd", "ref_maxpool_tester_fwd",
-                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd"):
+                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd"):
             getattr(self.lib, fn).restype = ct.c_double
 
     def _check(self, seconds):
@@ -387,6 +397,15 @@ class Reference:
         m = _c(mask) if mask is not None else None
         s = self.lib.ref_nll_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), *d, int(dx is not None),
                                  self.threads)
+        return out, self._check(s)
+
+    def accuracy_fwd(self, predicted, actual, mask=None, top_n=1, updater=False, reps=1):
+        predicted, d = self._dims(predicted)
+        actual = _c(actual)
+        out = np.empty((predicted.shape[0], top_n + 1) + predicted.shape[2:], np.float32)
+        m = _c(mask) if mask is not None else None
+        s = self.lib.ref_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_uint(top_n), *d, int(updater),
+                                      self.threads, reps)
         return out, self._check(s)
 
     def add_fwd(self, inputs, alpha=1.0, reps=1):

@@ -609,3 +609,47 @@ void orc_nll_bwd(float * dpredicted, const float * predicted, const float * actu
 			}
 		}
 }
+
+/* ---- Top-n accuracy over channels: nnforge/plain/accuracy_layer_tester_plain.cpp:64-110 -------------
+ * Per (entry, pixel): the actual class is the first channel holding the largest target (strict >, seeded
+ * -1e37); rank = number of channels whose prediction beats the prediction of the actual class (larger, or equal
+ * with a smaller channel index). out[k] = (rank <= k ? mask : 0) for k < top_n, out[top_n] = mask; mask = 1
+ * without a mask; a zero mask gives rank 0 without looking at the data. */
+void orc_accuracy_fwd(float * out, const float * predicted, const float * actual, const float * mask, i64 top_n, i64 n, i64 c, i64 hw)
+{
+	for (i64 e = 0; e < n; ++e)
+		for (i64 p = 0; p < hw; ++p)
+		{
+			const float m = mask ? mask[e * hw + p] : 1.0F;
+			int sum = 0;
+			if (m != 0.0F)
+			{
+				float max_val = -1.0e37F;
+				i64 cls = -1;
+				for (i64 f = 0; f < c; ++f)
+				{
+					const float a = actual[(e * c + f) * hw + p];
+					if (a > max_val)
+					{
+						max_val = a;
+						cls = f;
+					}
+				}
+				/* cls stays -1 when no target exceeds the seed (all NaN): the reference then reads one plane before the
+				 * entry; the restatement gives rank 0 for that degenerate input */
+				if (cls >= 0)
+				{
+					max_val = predicted[(e * c + cls) * hw + p];
+					for (i64 f = 0; f < c; ++f)
+					{
+						const float v = predicted[(e * c + f) * hw + p];
+						if (v > max_val || (v == max_val && f < cls))
+							++sum;
+					}
+				}
+			}
+			for (i64 k = 0; k < top_n; ++k)
+				out[(e * (top_n + 1) + k) * hw + p] = sum <= k ? m : 0.0F;
+			out[(e * (top_n + 1) + top_n) * hw + p] = m;
+		}
+}

@@ -23,6 +23,8 @@
 #include "plain/softmax_layer_updater_plain.h"
 #include "plain/negative_log_likelihood_layer_tester_plain.h"
 #include "plain/negative_log_likelihood_layer_updater_plain.h"
+#include "plain/accuracy_layer_tester_plain.h"
+#include "plain/accuracy_layer_updater_plain.h"
 #include "plain/add_layer_tester_plain.h"
 #include "plain/add_layer_updater_plain.h"
 #include "plain/max_subsampling_layer_tester_plain.h"
@@ -36,6 +38,7 @@
 #include "sigmoid_layer.h"
 #include "softmax_layer.h"
 #include "negative_log_likelihood_layer.h"
+#include "accuracy_layer.h"
 #include "add_layer.h"
 #include "max_subsampling_layer.h"
 
@@ -546,6 +549,44 @@ extern "C"
 				plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(), layer_data_custom::const_ptr(), in_cfgs, out_cfg, add_to_destination != 0, actions, n);
 		});
 		memcpy(dpredicted, (const void *)(*in_err), in_bytes);
+		return s;
+		REF_GUARD_END
+	}
+	// nnforge/plain/accuracy_layer_tester_plain.cpp:30-112 (updater == 0) or accuracy_layer_updater_plain.cpp (updater != 0):
+	// out[n][top_n + 1][h][w] from predicted and actual [n][c][h][w] and an optional mask [n][1][h][w].
+	double ref_accuracy_fwd(float * out, const float * predicted, const float * actual, const float * mask_or_null, unsigned int top_n,
+		unsigned int n, unsigned int c, unsigned int h, unsigned int w, int updater, int threads, int reps)
+	{
+		REF_GUARD_BEGIN
+		layer::const_ptr schema(new accuracy_layer(top_n));
+		const size_t in_bytes = (size_t)n * c * h * w * sizeof(float);
+		const size_t mask_bytes = (size_t)n * h * w * sizeof(float);
+		const size_t out_bytes = (size_t)n * (top_n + 1) * h * w * sizeof(float);
+		plain_buffer::ptr outb = make_buffer(0, out_bytes);
+		std::vector<plain_buffer::const_ptr> ins;
+		ins.push_back(make_buffer(predicted, in_bytes));
+		ins.push_back(make_buffer(actual, in_bytes));
+		std::vector<layer_configuration_specific> in_cfgs(2, make_config(c, h, w));
+		if (mask_or_null)
+		{
+			ins.push_back(make_buffer(mask_or_null, mask_bytes));
+			in_cfgs.push_back(make_config(1, h, w));
+		}
+		layer_configuration_specific out_cfg = make_config(top_n + 1, h, w);
+		plain_running_configuration::const_ptr cfg = make_running_config(threads);
+		std::set<layer_action> actions;
+		actions.insert(layer_action(layer_action::forward));
+		accuracy_layer_tester_plain tester;
+		accuracy_layer_updater_plain upd;
+		double s = timed(reps, [&]() {
+			if (updater)
+				upd.run_forward_propagation(outb, ins, plain_buffer::ptr(), plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, actions, n);
+			else
+				tester.run_forward_propagation(outb, ins, plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, n);
+		});
+		memcpy(out, (const void *)(*outb), out_bytes);
 		return s;
 		REF_GUARD_END
 	}

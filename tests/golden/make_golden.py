@@ -88,6 +88,13 @@ def main():
         out[name + "_err"] = ref.nll_fwd(probs, t, mask, 0.7)[0]
         out[name + "_err_nomask"] = ref.nll_fwd(probs, t, None, 1.0, updater=True)[0]
         out[name + "_grad"] = ref.nll_bwd(probs, t, mask, 0.7)[0]
+    # top-n accuracy on the same predictions and targets (ties between predictions included)
+    for name in ("nll", "nll_row"):
+        probs = out[name + "_p"].copy()
+        probs[0, 1] = probs[0, 0]
+        out[name + "_acc_p"] = probs
+        out[name + "_acc3"] = ref.accuracy_fwd(probs, out[name + "_t"], out[name + "_mask"], 3)[0]
+        out[name + "_acc1_nomask"] = ref.accuracy_fwd(probs, out[name + "_t"], None, 1, updater=True)[0]
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_backend.npz"), **out)
     print("wrote", len(out), "arrays")
 

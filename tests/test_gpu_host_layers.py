@@ -156,3 +156,6 @@ def test_negative_log_likelihood_objects(host, oracle):
     dp = torch.empty(SHAPE, device="cuda")
     u.enqueue_backward_data_propagation_inputs(dp, None, [dev(p), dev(t), dev(mask)], None, n)
     assert_bits_equal(out(dp), oracle.nll_bwd(p, t, mask, 0.5), "loss updater backward")
+    acc = torch.empty((n, 4, h, w), device="cuda")
+    host.Tester("Accuracy", c, w, h, params=[3], input_count=3).enqueue_forward_propagation(acc, [], [dev(p), dev(t), dev(mask)], n)
+    assert_bits_equal(out(acc), oracle.accuracy_fwd(p, t, mask, 3), "accuracy tester")

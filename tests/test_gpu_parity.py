@@ -664,6 +664,21 @@ def test_softmax_with_loss(capi, oracle, shape, masked):
     assert_close(host(acc), seed.astype(np.float64) + host(dl), "fused backward, accumulated", atol=2e-6)
 
 
+@pytest.mark.parametrize("shape", LOSS_SHAPES)
+@pytest.mark.parametrize("top_n", [1, 5])
+def test_accuracy(capi, oracle, shape, top_n):
+    g = synth.rng(1, salt=7200 + sum(shape))
+    p = oracle.softmax_fwd(synth.normal(g, shape, 0.0, 3.0))
+    p[0, 1] = p[0, 0]  # equal predictions: the smaller channel index wins
+    t = synth.targets(g, shape)
+    mshape = (shape[0], 1) + shape[2:]
+    mask = (synth.uniform(g, mshape, 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, mshape, 0.5, 2.0)
+    for m in (None, mask):
+        out = torch.empty((shape[0], top_n + 1) + shape[2:], device="cuda")
+        capi.accuracy_fwd(out, dev(p), dev(t), dev(m) if m is not None else None, top_n)
+        assert_bits_equal(host(out), oracle.accuracy_fwd(p, t, m, top_n), "top-%d accuracy" % top_n)
+
+
 def test_errors_are_reported_not_thrown(capi):
     x = torch.zeros((2, 3, 4, 4), device="cuda")
     with pytest.raises(capi.NnfError) as e:

@@ -59,6 +59,13 @@ def test_negative_log_likelihood(oracle, name):
     assert_bits_equal(oracle.nll_bwd(p, t, mask, 0.7), G[name + "_grad"], name + " gradient")
 
 
+@pytest.mark.parametrize("name", ["nll", "nll_row"])
+def test_accuracy(oracle, name):
+    p, t, mask = G[name + "_acc_p"], G[name + "_t"], G[name + "_mask"]
+    assert_bits_equal(oracle.accuracy_fwd(p, t, mask, 3), G[name + "_acc3"], name + " top-3 accuracy")
+    assert_bits_equal(oracle.accuracy_fwd(p, t, None, 1), G[name + "_acc1_nomask"], name + " top-1 accuracy, no mask")
+
+
 @pytest.mark.parametrize("name,win,stride", [("pool32", (3, 3), (2, 2)), ("pool22", (2, 2), (2, 2)), ("pool_3x2_s1x2", (3, 2), (1, 2))])
 def test_maxpool(oracle, name, win, stride):
     y, idx = oracle.maxpool_fwd(G["px"], win, stride)

@@ -75,6 +75,21 @@ def test_negative_log_likelihood(oracle, reference, shape):
         assert_bits_equal(oracle.nll_bwd(p, t, m, scale, dx=seed), reference.nll_bwd(p, t, m, scale, dx=seed)[0], "nll bwd add")
 
 
+@pytest.mark.parametrize("shape", [(2, 1, 1, 1), (3, 21, 4, 5), (4, 1000, 1, 1), (2, 5, 1, 9)])
+def test_accuracy(oracle, reference, shape):
+    g = synth.rng(54, salt=sum(shape))
+    p = oracle.softmax_fwd(synth.normal(g, shape, 0.0, 3.0))
+    if shape[1] > 1:
+        p[0, 1] = p[0, 0]  # equal predictions: the smaller channel index wins
+    t = synth.targets(g, shape)
+    mask = (synth.uniform(g, (shape[0], 1) + shape[2:], 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (shape[0], 1) + shape[2:], 0.5, 2.0)
+    for m in (None, mask):
+        for top_n in (1, 3):
+            a = oracle.accuracy_fwd(p, t, m, top_n)
+            assert_bits_equal(a, reference.accuracy_fwd(p, t, m, top_n)[0], "accuracy tester")
+            assert_bits_equal(a, reference.accuracy_fwd(p, t, m, top_n, updater=True)[0], "accuracy updater")
+
+
 @pytest.mark.parametrize("hw", [(7, 7), (9, 11), (14, 14), (5, 8)])
 @pytest.mark.parametrize("win,stride", [((3, 3), (2, 2)), ((2, 2), (2, 2)), ((3, 3), (1, 1)), ((2, 3), (2, 1)), ((1, 1), (1, 1)), ((5, 5), (3, 3))])
 def test_maxpool(oracle, reference, hw, win, stride):
