@@ -299,6 +299,21 @@ def run_sweep(args):
         report(3, "bn+add+relu+maxpool fwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_fwd(z, pooled, idx, x, r, bn, 0.0, p), nb), (12 + 8 * rho) * e)
         report(3, "bn+add+relu+maxpool bwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_bwd(dx, dr, dpo, idx, z, bn[0], bn[3], 0.0, p), nb), (12 + 8 * rho) * e)
         del x, r, z, pooled, idx, dpo, dx, dr
+    # beyond the five configurations: the tail of a residual network - BN -> add -> ReLU -> global average pooling
+    for c, hw in [(512, 7), (256, 14)]:
+        shape = (1024, c, hw, hw)
+        e = shape[0] * c * hw * hw
+        x, r, z = [torch.randn(shape, device="cuda") for _ in range(3)]
+        pooled = torch.empty((shape[0], c, 1, 1), device="cuda")
+        bn = bnp(c)
+        mult = 1.0 / (hw * hw)
+        report(3, "bn+add+relu+global avgpool fwd N=1024 C=%d %dx%d" % (c, hw, hw),
+               timeit(lambda i: capi.bn_add_relu_avgpool_fwd(z, pooled, x, r, bn, 0.0, (hw, hw), mult), 1), 12 * e)
+        dpo = torch.randn_like(pooled)
+        dx, dr = torch.empty_like(x), torch.empty_like(x)
+        report(3, "bn+add+relu+global avgpool bwd N=1024 C=%d %dx%d" % (c, hw, hw),
+               timeit(lambda i: capi.bn_add_relu_avgpool_bwd(dx, dr, dpo, z, bn[0], bn[3], 0.0, (hw, hw), mult), 1), 12 * e)
+        del x, r, z, pooled, dpo, dx, dr
     # config 4: inference BN + TanH / Sigmoid bandwidth sweep
     sizes = [128, 1024, 4096] + ([8192] if args.sweep_full else [])
     for n in sizes:

@@ -93,6 +93,15 @@ NNF_API int nnf_bn_infer_act(nnf_stream_t stream, float * y, const float * x,
 	const nnf_act * acts, int n_acts,
 	int64_t n, int64_t c, int64_t hw);
 
+/* The same with the bias of the convolution in front folded into the load: t = x + bias[channel] (its own rounded
+ * step, as the reference adds the bias with cudnnAddTensor after the convolution,
+ * nnforge/cuda/convolution_layer_tester_cuda.cpp:115), then everything nnf_bn_infer_act does. The convolution is then
+ * run WITHOUT its bias and writes x; one pass over HBM is saved. bias may be NULL. */
+NNF_API int nnf_bias_bn_infer_act(nnf_stream_t stream, float * y, const float * x, const float * bias,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	const float * residual, float add_alpha, const nnf_act * acts, int n_acts,
+	int64_t n, int64_t c, int64_t hw);
+
 /* Stand-alone activation forward: y = act(x); the updater-side forward of the same layers
  * (nnforge/cuda/*_layer_updater_cuda.cu enqueue_forward_propagation). y may alias x. */
 NNF_API int nnf_act_fwd(nnf_stream_t stream, float * y, const float * x, const nnf_act * act, int64_t n, int64_t c, int64_t hw);
@@ -310,6 +319,31 @@ NNF_API int nnf_bn_train_bwd_apply_peer(nnf_stream_t stream, float * dx, const f
 	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
 	const float * mean, const float * invsigma, float entry_count,
 	int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
+/* ---------------------------------------------------------------------------------------------
+ * average_subsampling_layer over the two spatial dimensions (replaces average_subsampling_layer_tester_cuda /
+ * _updater_cuda; semantics of nnforge/plain/average_subsampling_layer_tester_plain.cpp:120-135 and
+ * average_subsampling_layer_updater_plain.cpp:270-285): windows win_w x win_h that do not overlap (stride = window; they
+ * must divide the plane), global average pooling being win = (w, h).
+ *   forward : y[n][c][h/win_h][w/win_w] = (sum of the window, x fastest then y, from +0) * mult
+ *   backward: dx = dy[window of the element] * mult (accumulated with add_to_destination)
+ * mult is the layer's effective alpha. NOTE: the plain backend's default is 1 / (feature-map x entry subsampling), i.e. 1
+ * for spatial windows - it passes feature-map counts where get_effective_alpha expects layer configurations
+ * (average_subsampling_layer_tester_plain.cpp:82) - so it sums; pass 1.0f / (win_w*win_h) for a true average.
+ * The fused forms run batch norm (running statistics) -> residual add (alpha 1) -> ReLU -> average pooling in one pass and
+ * its backward, like nnf_bn_add_relu_maxpool_fwd/bwd: z = relu(bn(x) + residual) is written for the backward pass;
+ * dresidual = gate(z) * dpooled-window * mult, dx = dresidual * gamma * invsigma. gamma == NULL: no batch norm;
+ * residual == NULL: no add; dx or dresidual may be NULL. */
+NNF_API int nnf_avgpool_fwd(nnf_stream_t stream, float * y, const float * x, int64_t n, int64_t c, int64_t h, int64_t w,
+	int win_w, int win_h, float mult);
+NNF_API int nnf_avgpool_bwd(nnf_stream_t stream, float * dx, const float * dy, int64_t n, int64_t c, int64_t h, int64_t w,
+	int win_w, int win_h, float mult, int add_to_destination);
+NNF_API int nnf_bn_add_relu_avgpool_fwd(nnf_stream_t stream, float * z, float * pooled, const float * x, const float * residual,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	float relu_slope, int64_t n, int64_t c, int64_t h, int64_t w, int win_w, int win_h, float mult);
+NNF_API int nnf_bn_add_relu_avgpool_bwd(nnf_stream_t stream, float * dx, float * dresidual, const float * dpooled, const float * z,
+	const float * gamma, const float * invsigma, float relu_slope,
+	int64_t n, int64_t c, int64_t h, int64_t w, int win_w, int win_h, float mult);
 
 /* ---------------------------------------------------------------------------------------------
  * The loss behind softmax: negative_log_likelihood_layer, stand-alone (replaces

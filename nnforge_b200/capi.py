@@ -46,6 +46,7 @@ _SIGNATURES = {
     "nnf_last_error_string": (ct.c_char_p, []),
     "nnf_version": (_I, []),
     "nnf_bn_infer_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64]),
+    "nnf_bias_bn_infer_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64]),
     "nnf_act_fwd": (_I, [_P, _P, _P, _ACTP, _I64, _I64, _I64]),
     "nnf_act_bwd": (_I, [_P, _P, _P, _P, _ACTP, _I64, _I64, _I64, _I]),
     "nnf_prelu_bwd_weights_workspace_bytes": (_SZ, [_I64, _I64, _I64]),
@@ -72,6 +73,10 @@ _SIGNATURES = {
     "nnf_bn_train_bwd_apply_peer": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, ct.c_uint32, _P, _D, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F,
                                          _I64, _I64, _I64, _I]),
     "nnf_accuracy_fwd": (_I, [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64]),
+    "nnf_avgpool_fwd": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I, _I, _F]),
+    "nnf_avgpool_bwd": (_I, [_P, _P, _P, _I64, _I64, _I64, _I64, _I, _I, _F, _I]),
+    "nnf_bn_add_relu_avgpool_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _I, _I, _F]),
+    "nnf_bn_add_relu_avgpool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _I, _I, _F]),
     "nnf_nll_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
@@ -161,6 +166,15 @@ def bn_infer_act(y, x, bn=None, residual=None, add_alpha=1.0, acts=(), stream=No
     g, b, m, i = bn if bn is not None else (None, None, None, None)
     arr, k = _acts(acts)
     _check(lib.nnf_bn_infer_act(_stream(stream), _ptr(y), _ptr(x), _ptr(g), _ptr(b), _ptr(m), _ptr(i), _ptr(residual), add_alpha, arr, k, n, c, hw))
+
+
+def bias_bn_infer_act(y, x, bias, bn=None, residual=None, add_alpha=1.0, acts=(), stream=None):
+    """bn_infer_act with a per-channel bias added to x first."""
+    n, c, hw = _nchw(x)
+    g, b, m, i = bn if bn is not None else (None, None, None, None)
+    arr, k = _acts(acts)
+    _check(lib.nnf_bias_bn_infer_act(_stream(stream), _ptr(y), _ptr(x), _ptr(bias), _ptr(g), _ptr(b), _ptr(m), _ptr(i), _ptr(residual), add_alpha,
+                                     arr, k, n, c, hw))
 
 
 def act_fwd(y, x, act, stream=None):
@@ -310,6 +324,30 @@ def bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, gsums, bsums, count_total,
     _check(lib.nnf_bn_train_bwd_apply(_stream(stream), _ptr(dx), _ptr(dy), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(saved), _ptr(gsums), _ptr(bsums),
                                       float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean), _ptr(grad_invsigma),
                                       _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw, int(add_to_destination)))
+
+
+def avgpool_fwd(y, x, win, mult, stream=None):
+    """x [N,C,H,W]; win = (w, h)."""
+    n, c, h, w = x.shape
+    _check(lib.nnf_avgpool_fwd(_stream(stream), _ptr(y), _ptr(x), n, c, h, w, win[0], win[1], mult))
+
+
+def avgpool_bwd(dx, dy, win, mult, add_to_destination=False, stream=None):
+    n, c, h, w = dx.shape
+    _check(lib.nnf_avgpool_bwd(_stream(stream), _ptr(dx), _ptr(dy), n, c, h, w, win[0], win[1], mult, int(add_to_destination)))
+
+
+def bn_add_relu_avgpool_fwd(z, pooled, x, residual, bn, relu_slope, win, mult, stream=None):
+    n, c, h, w = x.shape
+    g, b, m, i = bn if bn is not None else (None, None, None, None)
+    _check(lib.nnf_bn_add_relu_avgpool_fwd(_stream(stream), _ptr(z), _ptr(pooled), _ptr(x), _ptr(residual), _ptr(g), _ptr(b), _ptr(m), _ptr(i),
+                                           relu_slope, n, c, h, w, win[0], win[1], mult))
+
+
+def bn_add_relu_avgpool_bwd(dx, dresidual, dpooled, z, gamma, invsigma, relu_slope, win, mult, stream=None):
+    n, c, h, w = z.shape
+    _check(lib.nnf_bn_add_relu_avgpool_bwd(_stream(stream), _ptr(dx), _ptr(dresidual), _ptr(dpooled), _ptr(z), _ptr(gamma), _ptr(invsigma), relu_slope,
+                                           n, c, h, w, win[0], win[1], mult))
 
 
 def accuracy_fwd(out, predicted, targets, mask=None, top_n=1, stream=None):

@@ -123,6 +123,22 @@ namespace nnf_b200
 			int get_input_index_layer_can_write() const override { return 0; }
 		};
 
+		// average_subsampling_layer over the spatial dimensions (nnforge/cuda/average_subsampling_layer_tester_cuda.cu);
+		// layer_schema->alpha is the effective alpha (the plain backend's default for spatial windows is 1)
+		class average_subsampling_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_avgpool_fwd(stream_id, f(output_buffer), f(input_buffers[0]), entry_count, in.feature_map_count, in.dimension_sizes.at(1), in.dimension_sizes.at(0),
+					(int)layer_schema->subsampling_sizes.at(0), (int)layer_schema->subsampling_sizes.at(1), layer_schema->alpha));
+			}
+		};
+
 		// negative_log_likelihood_layer: inputs = predicted, actual[, scale mask]; output = one value per (entry, pixel)
 		// (nnforge/cuda/negative_log_likelihood_layer_tester_cuda.cu)
 		class negative_log_likelihood_layer_tester_b200 : public layer_tester_b200
@@ -272,6 +288,32 @@ namespace nnf_b200
 			int get_input_index_layer_can_write(const layer_action& action) const override { return action.get_action_type() == layer_action::backward_data ? 0 : -1; }
 			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
 			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return true; }
+		};
+
+		class average_subsampling_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_avgpool_fwd(stream_id, f(output_buffer), f(input_buffers[0]), entry_count, in.feature_map_count, in.dimension_sizes.at(1), in.dimension_sizes.at(0),
+					(int)layer_schema->subsampling_sizes.at(0), (int)layer_schema->subsampling_sizes.at(1), layer_schema->alpha));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&, device_buffer::const_ptr,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				const layer_configuration_specific& in = input_configuration_specific_list[0];
+				check(nnf_avgpool_bwd(stream_id, f(input_errors_buffer), f(output_errors_buffer), entry_count, in.feature_map_count, in.dimension_sizes.at(1), in.dimension_sizes.at(0),
+					(int)layer_schema->subsampling_sizes.at(0), (int)layer_schema->subsampling_sizes.at(1), layer_schema->alpha, add_update_to_destination ? 1 : 0));
+			}
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return false; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
 		};
 
 		// (nnforge/cuda/negative_log_likelihood_layer_updater_cuda.cu; the layer is a loss: backward reads no output errors)
@@ -473,7 +515,7 @@ namespace nnf_b200
 
 	std::vector<std::string> layer_factory_b200::get_type_names() const
 	{
-		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood", "Accuracy"};
+		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood", "Accuracy", "AverageSubsampling"};
 	}
 
 	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
@@ -487,6 +529,7 @@ namespace nnf_b200
 		else if (n == "Softmax") t.reset(new softmax_layer_tester_b200());
 		else if (n == "NegativeLogLikelihood") t.reset(new negative_log_likelihood_layer_tester_b200());
 		else if (n == "Accuracy") t.reset(new accuracy_layer_tester_b200());
+		else if (n == "AverageSubsampling") t.reset(new average_subsampling_layer_tester_b200());
 		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
 		else throw neural_network_exception("No layer tester is registered with id " + n);
 		t->configure(in, out, l);
@@ -504,6 +547,7 @@ namespace nnf_b200
 		else if (n == "Softmax") u.reset(new softmax_layer_updater_b200());
 		else if (n == "NegativeLogLikelihood") u.reset(new negative_log_likelihood_layer_updater_b200());
 		else if (n == "Accuracy") u.reset(new accuracy_layer_updater_b200());
+		else if (n == "AverageSubsampling") u.reset(new average_subsampling_layer_updater_b200());
 		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
 		else throw neural_network_exception("No layer updater is registered with id " + n);
 		u->configure(in, out, l, actions);
@@ -517,6 +561,14 @@ namespace nnf_b200
 			res.feature_map_count = 1; // negative_log_likelihood_layer.cpp:66
 		if (l.type_name == "Accuracy")
 			res.feature_map_count = l.top_n + 1; // accuracy_layer.cpp:62
+		if (l.type_name == "AverageSubsampling")
+			for (size_t i = 0; i < res.dimension_sizes.size(); ++i)
+			{
+				const unsigned int win = l.subsampling_sizes.at(i);
+				if (win == 0 || inputs[0].dimension_sizes[i] % win != 0)
+					throw neural_network_exception("Input configuration size of dimension " + std::to_string(i) + " is not evenly divisible by the subsampling size");
+				res.dimension_sizes[i] = inputs[0].dimension_sizes[i] / win;
+			}
 		if (l.type_name == "MaxSubsampling")
 		{
 			const nnf_pool p = make_pool(l, inputs[0]);
@@ -589,6 +641,11 @@ NNFH_API void * nnfh_create(const char * type_name, int updater, const float * p
 		if (l.type_name == "NegativeLogLikelihood") l.scale = params[0];
 		if (l.type_name == "Accuracy") l.top_n = (unsigned int)params[0];
 		if (l.type_name == "BatchNorm") l.epsilon = params[0];
+		if (l.type_name == "AverageSubsampling")
+		{
+			l.subsampling_sizes = {(unsigned int)pool[0], (unsigned int)pool[1]};
+			l.alpha = params[0] != 0.0F ? params[0] : 1.0F; // the plain backend's default effective alpha for spatial windows
+		}
 		if (l.type_name == "MaxSubsampling")
 		{
 			l.subsampling_sizes = {(unsigned int)pool[0], (unsigned int)pool[1]};

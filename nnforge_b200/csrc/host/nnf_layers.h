@@ -67,9 +67,9 @@ namespace nnf_b200
 		float epsilon = 2.0e-5F;                    // BatchNorm (default_batch_normalization_epsilon, nnforge/batch_norm_layer.cpp:28)
 		float negative_slope = 0.0F;                // ReLU
 		float scale = 1.0F, steepness = 1.0F;       // TanH; scale also NegativeLogLikelihood
-		float alpha = 1.0F;                         // Add
+		float alpha = 1.0F;                         // Add; AverageSubsampling: the effective alpha
 		unsigned int top_n = 1;                     // Accuracy
-		std::vector<unsigned int> subsampling_sizes; // MaxSubsampling
+		std::vector<unsigned int> subsampling_sizes; // MaxSubsampling, AverageSubsampling
 		std::vector<unsigned int> strides;
 		std::vector<bool> round_ups;
 		unsigned int feature_map_subsampling_size = 1, entry_subsampling_size = 1;

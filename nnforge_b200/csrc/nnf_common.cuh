@@ -87,9 +87,10 @@ namespace nnf
 		float * saved;
 		double count_total;
 		float eps;
+		const float * bias;     // per-channel bias added to x before everything else (a convolution's bias), or null
 	};
 
-	// y = acts(((0 + bn(x)) + res) * alpha), one streaming pass (nnf_elementwise.cu)
+	// y = acts(((0 + bn(x + bias)) + res) * alpha), one streaming pass (nnf_elementwise.cu)
 	int run_elementwise(cudaStream_t s, float * y, const float * x, const float * res, float add_alpha,
 		const bn_source& bn, const act_chain& chain, int64_t n, int64_t c, int64_t hw);
 

@@ -34,6 +34,7 @@ namespace nnf
 			fastdiv hw;
 			fastdiv cdiv;
 			const float * slope;    // the chain's PReLU slopes, or null
+			const float * bias;     // per-channel bias added to x first, or null
 			int need_channel;       // per-channel parameters are used
 			int smem_params;        // mult/add staged in shared memory
 			act_chain chain;
@@ -43,13 +44,13 @@ namespace nnf
 		// kept in registers, so that the per-element work is only the arithmetic itself.
 		struct elem_params
 		{
-			float mult, add, slope;
+			float mult, add, slope, bias;
 		};
 
 		__device__ __forceinline__ elem_params fetch_params(const ew_params& p, const float * s_mult, const float * s_add, uint32_t e)
 		{
 			elem_params q;
-			q.mult = 1.0F; q.add = 0.0F; q.slope = 0.0F;
+			q.mult = 1.0F; q.add = 0.0F; q.slope = 0.0F; q.bias = 0.0F;
 			if (p.need_channel)
 			{
 				const uint32_t plane = p.hw.div(e);
@@ -69,6 +70,8 @@ namespace nnf
 				}
 				if (p.slope)
 					q.slope = __ldg(p.slope + channel);
+				if (p.bias)
+					q.bias = __ldg(p.bias + channel);
 			}
 			return q;
 		}
@@ -78,8 +81,10 @@ namespace nnf
 		__device__ __forceinline__ float ew_element(const ew_params& p, bool has_bn, bool has_res, const elem_params& q, float x, float r)
 		{
 			float t = x;
+			if (p.bias)
+				t = __fadd_rn(t, q.bias); // the producing convolution's bias, added as its own rounded step (cudnnAddTensor after the convolution)
 			if (has_bn)
-				t = __fadd_rn(__fmul_rn(x, q.mult), q.add); // batch_norm_layer_tester_plain.cpp:70
+				t = __fadd_rn(__fmul_rn(t, q.mult), q.add); // batch_norm_layer_tester_plain.cpp:70
 			if (has_res)
 				t = __fmul_rn(__fadd_rn(__fadd_rn(0.0F, t), r), p.add_alpha); // add_layer_tester_plain.cpp:57-60: the accumulator starts at +0.0f
 			return chain_forward<A0, A1>(p.chain, t, q.slope);
@@ -269,7 +274,7 @@ namespace nnf
 			const int64_t total = n * per_entry;
 			if (total == 0)
 				return NNF_OK;
-			bool need_channel = gamma != nullptr;
+			bool need_channel = gamma != nullptr || bn.bias != nullptr;
 			const float * slope = nullptr;
 			for (int i = 0; i < chain.n; ++i)
 				if (chain.a[i].kind == NNF_ACT_PRELU)
@@ -307,6 +312,7 @@ namespace nnf
 				p.hw = fastdiv((uint32_t)hw);
 				p.cdiv = fastdiv((uint32_t)c);
 				p.slope = slope;
+				p.bias = bn.bias;
 				p.need_channel = need_channel ? 1 : 0;
 				p.smem_params = (gamma && c <= kMaxSmemChannels) ? 1 : 0;
 				if (bn.sums && !p.smem_params)
@@ -611,6 +617,31 @@ extern "C" int nnf_bn_infer_act(nnf_stream_t stream, float * y, const float * x,
 		return st;
 	bn_source bn = {};
 	bn.gamma = gamma; bn.beta = beta; bn.mean = mean; bn.invsigma = invsigma;
+	return run_elementwise((cudaStream_t)stream, y, x, residual, add_alpha, bn, chain, n, c, hw);
+}
+
+extern "C" int nnf_bias_bn_infer_act(nnf_stream_t stream, float * y, const float * x, const float * bias,
+	const float * gamma, const float * beta, const float * mean, const float * invsigma,
+	const float * residual, float add_alpha, const nnf_act * acts, int n_acts,
+	int64_t n, int64_t c, int64_t hw)
+{
+	if (n < 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bias_bn_infer_act: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (n == 0)
+		return NNF_OK;
+	if (!y || !x)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bias_bn_infer_act: null tensor pointer");
+	if (gamma && (!beta || !mean || !invsigma))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bias_bn_infer_act: gamma given but beta/mean/invsigma missing");
+	if (c > 0x7fffffff || hw > 0x7fffffff)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bias_bn_infer_act: extent too large");
+	act_chain chain;
+	int st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	bn_source bn = {};
+	bn.gamma = gamma; bn.beta = beta; bn.mean = mean; bn.invsigma = invsigma;
+	bn.bias = bias;
 	return run_elementwise((cudaStream_t)stream, y, x, residual, add_alpha, bn, chain, n, c, hw);
 }
 

@@ -194,6 +194,25 @@ class Oracle:
         self.lib.orc_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, _i64(top_n), _i64(n), _i64(c), _i64(hw))
         return out
 
+    # ---- average subsampling ------------------------------------------------------------------------
+    def avgpool_fwd(self, x, win, mult=None):
+        """x [N,C,H,W]; win = (w, h); mult defaults to 1 / window elements."""
+        x = _c(x)
+        n, c, h, w = x.shape
+        mult = np.float32(1.0) / np.float32(win[0] * win[1]) if mult is None else np.float32(mult)
+        y = np.empty((n, c, h // win[1], w // win[0]), np.float32)
+        self.lib.orc_avgpool_fwd(_fp(y), _fp(x), _i64(n * c), _i64(h), _i64(w), _i64(win[0]), _i64(win[1]), ct.c_float(mult))
+        return y
+
+    def avgpool_bwd(self, dy, in_shape, win, mult=None, dx=None):
+        dy = _c(dy)
+        n, c, h, w = in_shape
+        mult = np.float32(1.0) / np.float32(win[0] * win[1]) if mult is None else np.float32(mult)
+        add = dx is not None
+        out = _c(dx).copy() if add else np.empty(in_shape, np.float32)
+        self.lib.orc_avgpool_bwd(_fp(out), _fp(dy), _i64(n * c), _i64(h), _i64(w), _i64(win[0]), _i64(win[1]), ct.c_float(mult), int(add))
+        return out
+
     # ---- max subsampling -----------------------------------------------------------------------
     def maxpool_out_size(self, size, window, stride, round_up=False):
         return int(self.lib.orc_maxpool_out_size(size, window, stride, int(round_up)))
@@ -294,7 +313,7 @@ class Reference:
         for fn in ("ref_bn_infer", "ref_relu_fwd", "ref_relu_bwd", "ref_prelu_fwd", "ref_prelu_bwd_data", "ref_prelu_bwd_weights",
                    "ref_elu_fwd", "ref_elu_bwd", "ref_tanh_fwd", "ref_tanh_bwd", "ref_sigmoid_fwd", "ref_sigmoid_bwd", "ref_softmax_fwd",
                    "ref_softmax_upd_fwd", "ref_softmax_bwd", "ref_add_fwd", "ref_add_bwd", "ref_maxpool_fwd", "ref_maxpool_tester_fwd",
-                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd"):
+                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd", "ref_avgpool_fwd", "ref_avgpool_bwd"):
             getattr(self.lib, fn).restype = ct.c_double
 
     def _check(self, seconds):
@@ -406,6 +425,18 @@ class Reference:
         m = _c(mask) if mask is not None else None
         s = self.lib.ref_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_uint(top_n), *d, int(updater),
                                       self.threads, reps)
+        return out, self._check(s)
+
+    def avgpool_fwd(self, x, win, updater=False, reps=1):
+        x, d = self._dims(x)
+        y = np.empty((x.shape[0], x.shape[1], x.shape[2] // win[1], x.shape[3] // win[0]), np.float32)
+        return y, self._check(self.lib.ref_avgpool_fwd(_fp(y), _fp(x), *d, win[0], win[1], int(updater), self.threads, reps))
+
+    def avgpool_bwd(self, dy, in_shape, win, dx=None):
+        dy = _c(dy)
+        out = _c(dx).copy() if dx is not None else np.empty(in_shape, np.float32)
+        n, c, h, w = in_shape
+        s = self.lib.ref_avgpool_bwd(_fp(out), _fp(dy), n, c, h, w, win[0], win[1], int(dx is not None), self.threads)
         return out, self._check(s)
 
     def add_fwd(self, inputs, alpha=1.0, reps=1):

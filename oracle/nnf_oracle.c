@@ -653,3 +653,38 @@ void orc_accuracy_fwd(float * out, const float * predicted, const float * actual
 			out[(e * (top_n + 1) + top_n) * hw + p] = m;
 		}
 }
+
+/* ---- Average subsampling over the two spatial dimensions (windows do not overlap: stride = window) --------
+ * nnforge/plain/average_subsampling_layer_tester_plain.cpp:120-135: the window is summed from +0 with x fastest, then
+ * multiplied by mult (the effective alpha: 1 / window elements by default, average_subsampling_layer.cpp:287-301). */
+void orc_avgpool_fwd(float * y, const float * x, i64 planes, i64 h, i64 w, i64 win_w, i64 win_h, float mult)
+{
+	const i64 oh = h / win_h, ow = w / win_w;
+	for (i64 p = 0; p < planes; ++p)
+		for (i64 oy = 0; oy < oh; ++oy)
+			for (i64 ox = 0; ox < ow; ++ox)
+			{
+				float sum = 0.0F;
+				for (i64 yy = 0; yy < win_h; ++yy)
+					for (i64 xx = 0; xx < win_w; ++xx)
+						sum += x[(p * h + oy * win_h + yy) * w + ox * win_w + xx];
+				y[(p * oh + oy) * ow + ox] = sum * mult;
+			}
+}
+
+/* nnforge/plain/average_subsampling_layer_updater_plain.cpp:270-285: every element of a window receives dy * mult. */
+void orc_avgpool_bwd(float * dx, const float * dy, i64 planes, i64 h, i64 w, i64 win_w, i64 win_h, float mult, int add_to_destination)
+{
+	const i64 oh = h / win_h, ow = w / win_w;
+	for (i64 p = 0; p < planes; ++p)
+		for (i64 yy = 0; yy < h; ++yy)
+			for (i64 xx = 0; xx < w; ++xx)
+			{
+				const float err = dy[(p * oh + yy / win_h) * ow + xx / win_w] * mult;
+				float * o = dx + (p * h + yy) * w + xx;
+				if (add_to_destination)
+					*o += err;
+				else
+					*o = err;
+			}
+}

@@ -25,6 +25,8 @@
 #include "plain/negative_log_likelihood_layer_updater_plain.h"
 #include "plain/accuracy_layer_tester_plain.h"
 #include "plain/accuracy_layer_updater_plain.h"
+#include "plain/average_subsampling_layer_tester_plain.h"
+#include "plain/average_subsampling_layer_updater_plain.h"
 #include "plain/add_layer_tester_plain.h"
 #include "plain/add_layer_updater_plain.h"
 #include "plain/max_subsampling_layer_tester_plain.h"
@@ -39,6 +41,7 @@
 #include "softmax_layer.h"
 #include "negative_log_likelihood_layer.h"
 #include "accuracy_layer.h"
+#include "average_subsampling_layer.h"
 #include "add_layer.h"
 #include "max_subsampling_layer.h"
 
@@ -587,6 +590,68 @@ extern "C"
 					layer_data_custom::const_ptr(), in_cfgs, out_cfg, n);
 		});
 		memcpy(out, (const void *)(*outb), out_bytes);
+		return s;
+		REF_GUARD_END
+	}
+	// nnforge/plain/average_subsampling_layer_tester_plain.cpp:30-148 (updater == 0) or the updater's forward
+	// (average_subsampling_layer_updater_plain.cpp:30-148): windows win_w x win_h, stride = window, default alpha.
+	double ref_avgpool_fwd(float * y, const float * x, unsigned int n, unsigned int c, unsigned int h, unsigned int w,
+		unsigned int win_w, unsigned int win_h, int updater, int threads, int reps)
+	{
+		REF_GUARD_BEGIN
+		std::vector<average_subsampling_factor> sizes;
+		sizes.push_back(average_subsampling_factor(win_w));
+		sizes.push_back(average_subsampling_factor(win_h));
+		layer::const_ptr schema(new average_subsampling_layer(sizes));
+		const unsigned int oh = h / win_h, ow = w / win_w;
+		const size_t in_bytes = (size_t)n * c * h * w * sizeof(float);
+		const size_t out_bytes = (size_t)n * c * oh * ow * sizeof(float);
+		plain_buffer::ptr out = make_buffer(0, out_bytes);
+		std::vector<plain_buffer::const_ptr> ins(1, make_buffer(x, in_bytes));
+		std::vector<layer_configuration_specific> in_cfgs(1, make_config(c, h, w));
+		layer_configuration_specific out_cfg = make_config(c, oh, ow);
+		plain_running_configuration::const_ptr cfg = make_running_config(threads);
+		std::set<layer_action> actions = all_actions();
+		average_subsampling_layer_tester_plain tester;
+		average_subsampling_layer_updater_plain upd;
+		double s = timed(reps, [&]() {
+			if (updater)
+				upd.run_forward_propagation(out, ins, plain_buffer::ptr(), plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, actions, n);
+			else
+				tester.run_forward_propagation(out, ins, plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, n);
+		});
+		memcpy(y, (const void *)(*out), out_bytes);
+		return s;
+		REF_GUARD_END
+	}
+
+	// nnforge/plain/average_subsampling_layer_updater_plain.cpp:151-297
+	double ref_avgpool_bwd(float * dx, const float * dy, unsigned int n, unsigned int c, unsigned int h, unsigned int w,
+		unsigned int win_w, unsigned int win_h, int add_to_destination, int threads)
+	{
+		REF_GUARD_BEGIN
+		std::vector<average_subsampling_factor> sizes;
+		sizes.push_back(average_subsampling_factor(win_w));
+		sizes.push_back(average_subsampling_factor(win_h));
+		layer::const_ptr schema(new average_subsampling_layer(sizes));
+		const unsigned int oh = h / win_h, ow = w / win_w;
+		const size_t in_bytes = (size_t)n * c * h * w * sizeof(float);
+		const size_t out_bytes = (size_t)n * c * oh * ow * sizeof(float);
+		plain_buffer::ptr in_err = make_buffer(dx, in_bytes);
+		plain_buffer::const_ptr out_err = make_buffer(dy, out_bytes);
+		std::vector<plain_buffer::const_ptr> in_neurons(1, plain_buffer::ptr());
+		std::vector<layer_configuration_specific> in_cfgs(1, make_config(c, h, w));
+		layer_configuration_specific out_cfg = make_config(c, oh, ow);
+		plain_running_configuration::const_ptr cfg = make_running_config(threads);
+		std::set<layer_action> actions = all_actions();
+		average_subsampling_layer_updater_plain upd;
+		double s = timed(1, [&]() {
+			upd.run_backward_data_propagation(0, in_err, out_err, in_neurons, plain_buffer::const_ptr(), plain_buffer::ptr(), plain_buffer::ptr(),
+				plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(), layer_data_custom::const_ptr(), in_cfgs, out_cfg, add_to_destination != 0, actions, n);
+		});
+		memcpy(dx, (const void *)(*in_err), in_bytes);
 		return s;
 		REF_GUARD_END
 	}

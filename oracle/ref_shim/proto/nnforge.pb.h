@@ -1,5 +1,5 @@
 // Stand-in for the protobuf-generated accessors that the nnForge layer classes of this path touch in their
-// read_proto / write_proto members (BatchNorm, ReLU, PReLU, TanH, Add, MaxSubsampling, NegativeLogLikelihood, Accuracy;
+// read_proto / write_proto members (BatchNorm, ReLU, PReLU, TanH, Add, MaxSubsampling, NegativeLogLikelihood, Accuracy, AverageSubsampling;
 // the other hot-path layers have no parameters). protoc is not available where the oracle is built and
 // the oracle never (de)serialises a schema, so these are plain structs with the same accessor names.
 // Test infrastructure only.
@@ -52,6 +52,28 @@ namespace nnforge
 			MaxSubsamplingParam_MaxSubsamplingDimensionParam * add_dimension_param() { dims_.emplace_back(); return &dims_.back(); }
 		};
 
+		class AverageSubsamplingParam_AverageSubsamplingDimensionParam
+		{
+			NNF_SHIM_FIELD(unsigned int, subsampling_size) NNF_SHIM_FIELD(unsigned int, subsampled_size)
+		};
+		class AverageSubsamplingParam_AverageSubsamplingFeatureMapParam
+		{
+			NNF_SHIM_FIELD(unsigned int, subsampling_size) NNF_SHIM_FIELD(unsigned int, subsampled_size)
+		};
+		class AverageSubsamplingParam_AverageSubsamplingEntryParam { NNF_SHIM_FIELD(unsigned int, subsampling_size) };
+		class AverageSubsamplingParam
+		{
+			NNF_SHIM_FIELD(float, alpha)
+			NNF_SHIM_MESSAGE(AverageSubsamplingParam_AverageSubsamplingFeatureMapParam, feature_map_param)
+			NNF_SHIM_MESSAGE(AverageSubsamplingParam_AverageSubsamplingEntryParam, entry_param)
+		private:
+			std::vector<AverageSubsamplingParam_AverageSubsamplingDimensionParam> dims_;
+		public:
+			int dimension_param_size() const { return static_cast<int>(dims_.size()); }
+			const AverageSubsamplingParam_AverageSubsamplingDimensionParam& dimension_param(int i) const { return dims_[i]; }
+			AverageSubsamplingParam_AverageSubsamplingDimensionParam * add_dimension_param() { dims_.emplace_back(); return &dims_.back(); }
+		};
+
 		class Layer
 		{
 			NNF_SHIM_MESSAGE(ReLUParam, relu_param)
@@ -61,6 +83,7 @@ namespace nnforge
 			NNF_SHIM_MESSAGE(PReLUParam, prelu_param)
 			NNF_SHIM_MESSAGE(NegativeLogLikelihoodParam, negative_log_likelihood_param)
 			NNF_SHIM_MESSAGE(AccuracyParam, accuracy_param)
+			NNF_SHIM_MESSAGE(AverageSubsamplingParam, average_subsampling_param)
 			NNF_SHIM_MESSAGE(MaxSubsamplingParam, max_subsampling_param)
 		private:
 			std::string type_;

@@ -95,6 +95,16 @@ def main():
         out[name + "_acc_p"] = probs
         out[name + "_acc3"] = ref.accuracy_fwd(probs, out[name + "_t"], out[name + "_mask"], 3)[0]
         out[name + "_acc1_nomask"] = ref.accuracy_fwd(probs, out[name + "_t"], None, 1, updater=True)[0]
+    # average subsampling (the plain backend's default effective alpha for spatial windows is 1: it sums)
+    ax = synth.normal(g, (2, 3, 8, 12))
+    out["avg_x"] = ax
+    out["avg_4x2"] = ref.avgpool_fwd(ax, (4, 2))[0]
+    ady = synth.normal(g, out["avg_4x2"].shape)
+    out["avg_4x2_dy"] = ady
+    out["avg_4x2_dx"] = ref.avgpool_bwd(ady, ax.shape, (4, 2))[0]
+    gx = synth.normal(g, (3, 5, 7, 7))
+    out["avg_gx"] = gx
+    out["avg_global"] = ref.avgpool_fwd(gx, (7, 7), updater=True)[0]
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_backend.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -159,3 +159,21 @@ def test_negative_log_likelihood_objects(host, oracle):
     acc = torch.empty((n, 4, h, w), device="cuda")
     host.Tester("Accuracy", c, w, h, params=[3], input_count=3).enqueue_forward_propagation(acc, [], [dev(p), dev(t), dev(mask)], n)
     assert_bits_equal(out(acc), oracle.accuracy_fwd(p, t, mask, 3), "accuracy tester")
+
+
+def test_average_subsampling_objects(host, oracle):
+    g = synth.rng(3, salt=904)
+    shape = (4, 6, 8, 12)
+    n, c, h, w = shape
+    x = synth.normal(g, shape)
+    win, mult = (4, 2), 0.125
+    u = host.Updater("AverageSubsampling", c, w, h, params=[mult], pool=[win[0], win[1], 0, 0, 0, 0, 0])
+    want = oracle.avgpool_fwd(x, win, mult=mult)
+    y = torch.empty(want.shape, device="cuda")
+    u.enqueue_forward_propagation(y, [], [dev(x)], n)
+    assert_bits_equal(out(y), want, "average subsampling updater forward")
+    dy = synth.normal(g, want.shape)
+    dx = torch.empty(shape, device="cuda")
+    u.enqueue_backward_data_propagation(dx, dev(dy), [], None, None, n)
+    assert_bits_equal(out(dx), oracle.avgpool_bwd(dy, shape, win, mult=mult), "average subsampling updater backward")
+    assert not u.is_backward_data_dependent_on_input_buffer() and not u.is_backward_data_dependent_on_output_buffer()

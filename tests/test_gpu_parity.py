@@ -591,6 +591,86 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi):
     assert capi.fused_error_check() == 0
 
 
+@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 5, 3), (64, 64, 32, 32)])
+@pytest.mark.parametrize("with_bn", [True, False])
+def test_bias_folded_into_bn_infer(capi, oracle, shape, with_bn):
+    """The convolution bias added in the load of the fused inference kernel: bit-exact against
+    bias add (its own rounded step), then batch norm, residual add and ReLU of the plain restatement."""
+    g = synth.rng(0, salt=7300 + sum(shape))
+    x, r = synth.normal(g, shape), synth.normal(g, shape)
+    c = shape[1]
+    bias = synth.normal(g, c, 0.0, 0.5)
+    gamma, beta, mean = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1), synth.normal(g, c, 0.0, 0.1)
+    inv = (1.0 / np.sqrt(synth.uniform(g, c, 0.5, 2.0) + 1e-5)).astype(np.float32)
+    xb = (x + bias[None, :, None, None]).astype(np.float32)  # one rounded add per element
+    t = oracle.bn_infer(xb, gamma, beta, mean, inv) if with_bn else xb
+    want = oracle.relu_fwd(oracle.add_fwd([t, r]), 0.0)
+    y = torch.empty(shape, device="cuda")
+    bn = [dev(gamma), dev(beta), dev(mean), dev(inv)] if with_bn else None
+    capi.bias_bn_infer_act(y, dev(x), dev(bias), bn=bn, residual=dev(r), acts=[capi.relu(0.0)])
+    assert_bits_equal(host(y), want, "bias + bn + add + relu")
+    # unaligned views take the scalar path
+    big = torch.zeros(x.size + 1, device="cuda")
+    big[1:] = dev(x).flatten()
+    yu = torch.empty(x.size + 1, device="cuda")
+    capi.bias_bn_infer_act(yu[1:].view(shape), big[1:].view(shape), dev(bias), bn=bn, residual=None, acts=[])
+    assert_bits_equal(host(yu[1:].view(shape)), t, "bias + bn, unaligned")
+
+
+AVG_CASES = [((2, 3, 8, 12), (4, 2)), ((6, 10, 7, 7), (7, 7)), ((2, 4, 6, 6), (1, 1)), ((3, 5, 14, 14), (2, 2)), ((2, 3, 4, 9), (3, 4)),
+             ((4, 600, 7, 7), (7, 7)), ((1, 1, 240, 240), (8, 8))]
+
+
+@pytest.mark.parametrize("shape,win", AVG_CASES)
+def test_average_subsampling(capi, oracle, shape, win):
+    g = synth.rng(3, salt=7400 + sum(shape))
+    x = synth.normal(g, shape)
+    for mult in (1.0, float(np.float32(1.0) / np.float32(win[0] * win[1]))):
+        want = oracle.avgpool_fwd(x, win, mult=mult)
+        y = torch.empty(want.shape, device="cuda")
+        capi.avgpool_fwd(y, dev(x), win, mult)
+        assert_bits_equal(host(y), want, "average subsampling forward")
+        dy = synth.normal(g, want.shape)
+        dx = torch.empty(shape, device="cuda")
+        capi.avgpool_bwd(dx, dev(dy), win, mult)
+        assert_bits_equal(host(dx), oracle.avgpool_bwd(dy, shape, win, mult=mult), "average subsampling backward")
+        seed = synth.normal(g, shape)
+        acc = dev(seed)
+        capi.avgpool_bwd(acc, dev(dy), win, mult, add_to_destination=True)
+        assert_bits_equal(host(acc), oracle.avgpool_bwd(dy, shape, win, mult=mult, dx=seed), "average subsampling backward, accumulated")
+
+
+@pytest.mark.parametrize("shape,win", AVG_CASES[:6])
+@pytest.mark.parametrize("with_bn,with_res", [(True, True), (True, False), (False, True)])
+def test_fused_bn_add_relu_avgpool(capi, oracle, shape, win, with_bn, with_res):
+    """BN (running statistics) -> add -> ReLU -> average pooling in one pass, and its backward, bit-exact against the
+    layers of the plain restatement run one after the other."""
+    g = synth.rng(3, salt=7500 + sum(shape))
+    x, r = synth.normal(g, shape), synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta, mean = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1), synth.normal(g, c, 0.0, 0.1)
+    inv = (1.0 / np.sqrt(synth.uniform(g, c, 0.5, 2.0) + 1e-5)).astype(np.float32)
+    mult = float(np.float32(1.0) / np.float32(win[0] * win[1]))
+    t = oracle.bn_infer(x, gamma, beta, mean, inv) if with_bn else x
+    if with_res:
+        t = oracle.add_fwd([t, r])
+    zw = oracle.relu_fwd(t, 0.0)
+    pw = oracle.avgpool_fwd(zw, win, mult=mult)
+    z, pooled = torch.empty(shape, device="cuda"), torch.empty(pw.shape, device="cuda")
+    bn = [dev(gamma), dev(beta), dev(mean), dev(inv)] if with_bn else None
+    capi.bn_add_relu_avgpool_fwd(z, pooled, dev(x), dev(r) if with_res else None, bn, 0.0, win, mult)
+    assert_bits_equal(host(z), zw, "fused z")
+    assert_bits_equal(host(pooled), pw, "fused pooled")
+    dp = synth.normal(g, pw.shape)
+    dz = oracle.avgpool_bwd(dp, shape, win, mult=mult)
+    ds = oracle.relu_bwd(dz, t, 0.0)
+    dx_w = (ds * (gamma * inv)[None, :, None, None]).astype(np.float32) if with_bn else ds
+    dx, dres = torch.empty(shape, device="cuda"), torch.empty(shape, device="cuda")
+    capi.bn_add_relu_avgpool_bwd(dx, dres, dev(dp), z, dev(gamma) if with_bn else None, dev(inv) if with_bn else None, 0.0, win, mult)
+    assert_bits_equal(host(dres), ds, "fused d residual")
+    assert_bits_equal(host(dx), dx_w, "fused dx")
+
+
 LOSS_SHAPES = [(256, 1000, 1, 1), (7, 1000, 1, 1), (5, 10, 1, 1), (3, 33, 1, 1), (2, 1100, 1, 1), (32, 21, 16, 16), (3, 21, 7, 5), (2, 5, 1, 9),
                (2, 40, 6, 6)]
 

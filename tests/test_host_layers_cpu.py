@@ -10,6 +10,10 @@ def test_factory_knows_its_type_names_and_rejects_others():
         assert host.Updater(name, 8, 5, 5).h
     assert host.Tester("MaxSubsampling", 8, 9, 9, pool=[3, 3, 2, 2, 0, 0, 0]).h
     assert host.Tester("NegativeLogLikelihood", 8, 5, 5, params=[1.0], input_count=2).h
+    assert host.Tester("AverageSubsampling", 8, 6, 6, pool=[3, 2, 0, 0, 0, 0, 0]).h
+    with pytest.raises(host.HostLayerError) as e:
+        host.Tester("AverageSubsampling", 8, 7, 7, pool=[2, 2, 0, 0, 0, 0, 0])
+    assert "divisible" in str(e.value)
     assert host.Tester("Accuracy", 8, 5, 5, params=[3], input_count=2).h
     assert host.Updater("Accuracy", 8, 5, 5, params=[1], input_count=3, with_backward=False).h
     loss = host.Updater("NegativeLogLikelihood", 8, 5, 5, params=[1.0], input_count=3)

@@ -59,6 +59,13 @@ def test_negative_log_likelihood(oracle, name):
     assert_bits_equal(oracle.nll_bwd(p, t, mask, 0.7), G[name + "_grad"], name + " gradient")
 
 
+def test_average_subsampling(oracle):
+    y = oracle.avgpool_fwd(G["avg_x"], (4, 2), mult=1.0)
+    assert_bits_equal(y, G["avg_4x2"], "average subsampling 4x2")
+    assert_bits_equal(oracle.avgpool_bwd(G["avg_4x2_dy"], G["avg_x"].shape, (4, 2), mult=1.0), G["avg_4x2_dx"], "average subsampling 4x2 bwd")
+    assert_bits_equal(oracle.avgpool_fwd(G["avg_gx"], (7, 7), mult=1.0), G["avg_global"], "global pooling 7x7")
+
+
 @pytest.mark.parametrize("name", ["nll", "nll_row"])
 def test_accuracy(oracle, name):
     p, t, mask = G[name + "_acc_p"], G[name + "_t"], G[name + "_mask"]

@@ -90,6 +90,20 @@ def test_accuracy(oracle, reference, shape):
             assert_bits_equal(a, reference.accuracy_fwd(p, t, m, top_n, updater=True)[0], "accuracy updater")
 
 
+@pytest.mark.parametrize("shape,win", [((2, 3, 8, 12), (4, 2)), ((3, 5, 7, 7), (7, 7)), ((2, 4, 6, 6), (1, 1)), ((1, 2, 14, 14), (2, 2)), ((2, 3, 4, 9), (3, 4))])
+def test_average_subsampling(oracle, reference, shape, win):
+    """mult = 1: the plain backend's default effective alpha for spatial windows (it ignores the window size)."""
+    g = synth.rng(55, salt=sum(shape))
+    x = synth.normal(g, shape)
+    y = oracle.avgpool_fwd(x, win, mult=1.0)
+    assert_bits_equal(y, reference.avgpool_fwd(x, win)[0], "average subsampling tester")
+    assert_bits_equal(y, reference.avgpool_fwd(x, win, updater=True)[0], "average subsampling updater")
+    dy = synth.normal(g, y.shape)
+    assert_bits_equal(oracle.avgpool_bwd(dy, shape, win, mult=1.0), reference.avgpool_bwd(dy, shape, win)[0], "average subsampling bwd")
+    seed = synth.normal(g, shape)
+    assert_bits_equal(oracle.avgpool_bwd(dy, shape, win, mult=1.0, dx=seed), reference.avgpool_bwd(dy, shape, win, dx=seed)[0], "average subsampling bwd add")
+
+
 @pytest.mark.parametrize("hw", [(7, 7), (9, 11), (14, 14), (5, 8)])
 @pytest.mark.parametrize("win,stride", [((3, 3), (2, 2)), ((2, 2), (2, 2)), ((3, 3), (1, 1)), ((2, 3), (2, 1)), ((1, 1), (1, 1)), ((5, 5), (3, 3))])
 def test_maxpool(oracle, reference, hw, win, stride):
