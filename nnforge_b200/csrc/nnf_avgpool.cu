@@ -155,26 +155,51 @@ namespace nnf
 		{
 			// elements [base, base + count) of the input-sized tensors; base is a multiple of hw
 			const int64_t plane_base = base / p.hw;
-			auto element = [&](uint32_t e, float zval, float old, float& odx, float& ores)
+			// position of an element inside the launch: plane (relative), row, column; advanced element by element
+			struct cursor
 			{
-				const uint32_t lp = p.d_hw.div(e);
-				const uint32_t rem = e - lp * p.hw;
-				const uint32_t iy = p.d_w.div(rem);
-				const uint32_t ix = rem - iy * p.w;
+				uint32_t lp, iy, ix;
+			};
+			auto locate = [&](uint32_t e) -> cursor
+			{
+				cursor k;
+				k.lp = p.d_hw.div(e);
+				const uint32_t rem = e - k.lp * p.hw;
+				k.iy = p.d_w.div(rem);
+				k.ix = rem - k.iy * p.w;
+				return k;
+			};
+			auto advance = [&](cursor& k)
+			{
+				if (++k.ix == p.w)
+				{
+					k.ix = 0;
+					if (++k.iy == p.h)
+					{
+						k.iy = 0;
+						++k.lp;
+					}
+				}
+			};
+			auto plane_factor = [&](uint32_t lp) -> float
+			{
+				if (!FUSED || !p.gamma)
+					return 1.0F;
 				const int64_t plane = plane_base + lp;
-				const float dz = __fmul_rn(__ldg(p.dpooled + plane * p.ohw + p.d_win_h.div(iy) * p.ow + p.d_win_w.div(ix)), p.mult);
+				const uint32_t channel = (uint32_t)(plane - int64_t(p.d_c.div((uint32_t)plane)) * p.c);
+				return __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+			};
+			auto element = [&](const cursor& k, float factor, float zval, float old, float& odx, float& ores)
+			{
+				const int64_t plane = plane_base + k.lp;
+				const float dz = __fmul_rn(__ldg(p.dpooled + plane * p.ohw + p.d_win_h.div(k.iy) * p.ow + p.d_win_w.div(k.ix)), p.mult);
 				if (FUSED)
 				{
 					// ReLU gate from the sign bit of z; add layer backward with alpha 1 is the identity; frozen batch
 					// norm scales by gamma*invsigma
 					const float ds = (__float_as_uint(zval) >> 31) ? __fmul_rn(dz, p.slope) : dz;
 					ores = ds;
-					odx = ds;
-					if (p.gamma)
-					{
-						const uint32_t channel = (uint32_t)(plane - int64_t(p.d_c.div((uint32_t)plane)) * p.c);
-						odx = __fmul_rn(ds, __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel)));
-					}
+					odx = p.gamma ? __fmul_rn(ds, factor) : ds;
 				}
 				else
 					odx = p.add ? __fadd_rn(old, dz) : dz;
@@ -188,10 +213,19 @@ namespace nnf
 					z4 = ld_stream(reinterpret_cast<const float4 *>(p.zin + base) + v);
 				else if (p.add)
 					old = ld_stream(reinterpret_cast<const float4 *>(p.dx + base) + v);
-				element(v << 2, z4.x, old.x, ox.x, orr.x);
-				element((v << 2) + 1, z4.y, old.y, ox.y, orr.y);
-				element((v << 2) + 2, z4.z, old.z, ox.z, orr.z);
-				element((v << 2) + 3, z4.w, old.w, ox.w, orr.w);
+				cursor k = locate(v << 2);
+				const uint32_t lp0 = k.lp;
+				const float f0 = plane_factor(lp0);
+				float f1 = f0;
+				if ((lp0 + 1) * p.hw - (v << 2) < 4) // the vector straddles a plane boundary
+					f1 = plane_factor(lp0 + 1);
+				element(k, f0, z4.x, old.x, ox.x, orr.x);
+				advance(k);
+				element(k, k.lp == lp0 ? f0 : f1, z4.y, old.y, ox.y, orr.y);
+				advance(k);
+				element(k, k.lp == lp0 ? f0 : f1, z4.z, old.z, ox.z, orr.z);
+				advance(k);
+				element(k, k.lp == lp0 ? f0 : f1, z4.w, old.w, ox.w, orr.w);
 				if (p.dx)
 					st_stream(reinterpret_cast<float4 *>(p.dx + base) + v, ox);
 				if (FUSED && p.dres)
@@ -200,7 +234,8 @@ namespace nnf
 			for (uint32_t e = (nvec << 2) + blockIdx.x * kAvgThreads + threadIdx.x; e < count; e += stride)
 			{
 				float odx, ores;
-				element(e, FUSED ? p.zin[base + e] : 0.0F, (!FUSED && p.add) ? p.dx[base + e] : 0.0F, odx, ores);
+				const cursor k = locate(e);
+				element(k, plane_factor(k.lp), FUSED ? p.zin[base + e] : 0.0F, (!FUSED && p.add) ? p.dx[base + e] : 0.0F, odx, ores);
 				if (p.dx)
 					p.dx[base + e] = odx;
 				if (FUSED && p.dres)
@@ -231,7 +266,7 @@ namespace nnf
 			if (p.planes == 0)
 				return NNF_OK;
 			const size_t plane_bytes = size_t(p.hw) * sizeof(float);
-			int64_t group = int64_t(8 * 1024 / plane_bytes);
+			int64_t group = int64_t(16 * 1024 / plane_bytes);
 			if (group < 1) group = 1;
 			if (group > kAvgMaxGroup) group = kAvgMaxGroup;
 			if (group > p.planes) group = p.planes;
