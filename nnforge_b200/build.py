@@ -17,6 +17,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libnnf_b200.so")
 HOST_LIB = os.path.join(HERE, "libnnf_b200_host.so")
 HOST_SRC = os.path.join(CSRC, "host", "nnf_layers.cpp")
+HOST_SOURCES = [HOST_SRC, os.path.join(CSRC, "host", "nnf_fusion.cpp")]
 SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_loss.cu", "nnf_maxpool.cu", "nnf_avgpool.cu", "nnf_bn_train.cu", "nnf_bn_fused.cu", "nnf_bn_chain.cu", "nnf_peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -62,11 +63,12 @@ def build(verbose=False):
 
 def build_host():
     """C++ host-side layer objects (nnForge-shaped testers / updaters over the C ABI)."""
-    deps = [HOST_SRC, os.path.join(CSRC, "host", "nnf_layers.h"), os.path.join(os.path.dirname(HERE), "include", "nnf_b200.h"), LIB]
+    deps = HOST_SOURCES + [os.path.join(CSRC, "host", "nnf_layers.h"), os.path.join(CSRC, "host", "nnf_fusion.h"),
+            os.path.join(os.path.dirname(HERE), "include", "nnf_b200.h"), LIB]
     if os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(os.path.getmtime(d) for d in deps):
         return HOST_LIB
     cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include") if os.path.sep in _nvcc() else "/usr/local/cuda/include"
-    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I", cuda_inc, HOST_SRC, "-o", HOST_LIB,
+    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I", cuda_inc] + HOST_SOURCES + ["-o", HOST_LIB,
                            "-L", HERE, "-lnnf_b200", "-Wl,-rpath,$ORIGIN"])
     return HOST_LIB
 

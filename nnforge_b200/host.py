@@ -30,6 +30,9 @@ lib.nnfh_updater_backward_data_inputs.argtypes = [_P, _P, _P, _P, ct.POINTER(_P)
 lib.nnfh_updater_backward_weights.argtypes = [_P, _P, ct.POINTER(_P), ct.c_int, _P, _P, _P, ct.c_size_t, ct.c_uint]
 lib.nnfh_updater_backward_data_and_weights.argtypes = [_P, _P, _P, _P, ct.POINTER(_P), ct.c_int, ct.POINTER(_P), ct.c_int, _P, _P, ct.c_size_t, _P, ct.c_int, ct.c_uint]
 
+lib.nnfh_fusion_last_error.restype = ct.c_char_p
+lib.nnfh_plan_fusion.argtypes = [ct.c_char_p, ct.c_int, ct.c_char_p, ct.c_size_t]
+
 FORWARD, BACKWARD_DATA, BACKWARD_WEIGHTS, BACKWARD_DATA_AND_WEIGHTS = 0, 1, 2, 3
 
 
@@ -140,3 +143,19 @@ class Updater(_Layer):
         _check(lib.nnfh_updater_backward_data_and_weights(self.h, _stream(), _ptr(input_errors_buffer), _ptr(output_errors_buffer), g, ng, d, nd,
                                                           _ptr(input_neurons_buffer), _ptr(wf), wf.numel() * wf.element_size() if wf is not None else 0,
                                                           _ptr(temporary_fixed_buffer), int(add_update_to_destination), entry_count))
+
+
+def plan_fusion(spec, training=False):
+    """Runs the schema peephole (csrc/host/nnf_fusion.h) on a textual schema: one layer per line,
+    "name type inputs [needed] [key=value ...]" (inputs: comma-separated layer names or "-"). Returns one dict per
+    fused group: kind, entry_point, members, residual, elided."""
+    buf = ct.create_string_buffer(1 << 16)
+    if lib.nnfh_plan_fusion(spec.encode(), int(training), buf, len(buf)) != 0:
+        raise HostLayerError(lib.nnfh_fusion_last_error().decode())
+    groups = []
+    for line in buf.value.decode().splitlines():
+        kind, entry, members, residual, elided = line.split(" ")
+        val = lambda t: [] if t.split("=", 1)[1] == "-" else t.split("=", 1)[1].split(",")
+        groups.append({"kind": kind, "entry_point": None if entry == "-" else entry, "members": val(members),
+                       "residual": (val(residual) or [None])[0], "elided": val(elided)})
+    return groups
