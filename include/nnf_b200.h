@@ -397,6 +397,60 @@ NNF_API int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float * bs
 	int64_t n, int64_t c, int64_t hw, double count_total, void * workspace, size_t workspace_bytes,
 	void * const * mailboxes, int rank, int world, uint32_t seq);
 
+/* ---------------------------------------------------------------------------------------------
+ * Optimiser step for many weight chunks in one launch (replaces cuda_util::apply_gradient,
+ * apply_gradient_with_vanilla_momentum, _nesterov_momentum and _adam_momentum, nnforge/cuda/util_cuda.cu:337-596,
+ * which backward_propagation_cuda::enqueue_apply_gradient calls once per chunk, nnforge/cuda/backward_propagation_cuda.cpp:2008-2096;
+ * arithmetic order of nnforge/plain/backward_propagation_plain.cpp:826-985). Per weight, with g = gradient*normalizer - w*weight_decay:
+ *   NONE      upd = lr*g
+ *   VANILLA   upd = prev*momentum + lr*g;                         prev_upd = upd
+ *   NESTEROV  fresh = prev*momentum + lr*g; upd = (momentum+1)*fresh - momentum*prev;   prev_upd = fresh
+ *   ADAM      m1 = beta1*prev + (1-beta1)*g; m2 = beta2*prev2 + (1-beta2)*g*g;  (momentum = beta1, momentum2 = beta2)
+ *             upd = lr*(m1/(1-beta1^t)) / (sqrt(m2/(1-beta2^t)) + 1e-8), t = iteration_id >= 1;   prev_upd = m1, prev_upd2 = m2
+ *   w += upd; gradient = 0; *update_accum += sum |upd| (double; skipped when update_accum is NULL).
+ * `parts` is a HOST array; the chunk table travels in the kernel parameters (48 chunks per launch), so a batch-norm
+ * layer's four chunks, or all per-channel chunks of a network, cost one launch. weight_decay is the value that applies
+ * to the chunk (0 for chunks outside layer::get_weight_decay_part_id_set()). Results are bit-identical to the plain
+ * backend's expressions compiled without FMA contraction; a chunk of up to 1024 weights sums |upd| in a fixed order. */
+typedef enum nnf_momentum_type
+{
+	NNF_MOMENTUM_NONE = 0,      /* training_momentum::no_momentum (nnforge/training_momentum.h) */
+	NNF_MOMENTUM_VANILLA = 1,
+	NNF_MOMENTUM_NESTEROV = 2,
+	NNF_MOMENTUM_ADAM = 3
+} nnf_momentum_type;
+
+typedef struct nnf_opt_part
+{
+	float * data;            /* weights, updated in place */
+	float * gradient;        /* accumulated gradient, zeroed */
+	float * prev_upd;        /* previous update / first moment (not NONE) */
+	float * prev_upd2;       /* second moment (ADAM) */
+	double * update_accum;   /* one double, or NULL */
+	float learning_rate;
+	float weight_decay;
+	int64_t elem_count;
+} nnf_opt_part;
+
+NNF_API int nnf_apply_gradient(nnf_stream_t stream, const nnf_opt_part * parts, int n_parts, int momentum_type, float momentum,
+	float momentum2, float normalizer, unsigned int iteration_id);
+
+/* Recalibration of a batch-norm layer's running statistics on a data set (the GPU form of toolset::update_bn_weights,
+ * nnforge/toolset.cpp:1562-1630, which runs the network with gamma = 1 and beta = 0 up to the layer, collects per-feature-map
+ * statistics of its output on the host with stat_data_bunch_writer, nnforge/stat_data_bunch_writer.cpp:44-111, and rewrites
+ * mean and inverse sigma). nnf_bn_calibrate_accumulate reads the layer's INPUT x once, forms y = x*invsigma + (0 - invsigma*mean)
+ * exactly as the inference kernel does and merges count, mean, M2 (double) and min, max of y per feature map into the
+ * accumulator (nnf_bn_calibrate_accumulator_bytes(c) bytes, zeroed before the first batch; batches may have any size).
+ * nnf_bn_calibrate_finish writes stats[4][c] = {min, max, average, std_dev} (may be NULL) and, when mean / invsigma are given,
+ * invsigma' = invsigma / std_dev, mean' = mean + average / invsigma. The reference accumulates value by value (Welford) in
+ * double; sums of y and y*y in double followed by a pairwise merge agree with it to double rounding, i.e. to the last
+ * bit or two of the fp32 results. */
+NNF_API size_t nnf_bn_calibrate_workspace_bytes(int64_t c);
+NNF_API size_t nnf_bn_calibrate_accumulator_bytes(int64_t c);
+NNF_API int nnf_bn_calibrate_accumulate(nnf_stream_t stream, void * accumulator, const float * x, const float * mean, const float * invsigma,
+	int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
+NNF_API int nnf_bn_calibrate_finish(nnf_stream_t stream, float * mean, float * invsigma, float * stats, const void * accumulator, int64_t c);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,13 @@ class Pool(ct.Structure):
 
 
 _P, _I64, _F, _I, _D, _SZ = ct.c_void_p, ct.c_int64, ct.c_float, ct.c_int, ct.c_double, ct.c_size_t
+class OptPart(ct.Structure):
+    _fields_ = [("data", ct.c_void_p), ("gradient", ct.c_void_p), ("prev_upd", ct.c_void_p), ("prev_upd2", ct.c_void_p),
+                ("update_accum", ct.c_void_p), ("learning_rate", ct.c_float), ("weight_decay", ct.c_float), ("elem_count", ct.c_int64)]
+
+
+MOMENTUM_NONE, MOMENTUM_VANILLA, MOMENTUM_NESTEROV, MOMENTUM_ADAM = range(4)
+
 _ACTP, _POOLP = ct.POINTER(Act), ct.POINTER(Pool)
 
 _SIGNATURES = {
@@ -85,6 +92,11 @@ _SIGNATURES = {
     "nnf_bn_train_fwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _D, _P, _SZ, ct.POINTER(_P), _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _D, _P, _SZ,
                                       ct.POINTER(_P), _I, _I, ct.c_uint32]),
+    "nnf_apply_gradient": (_I, [_P, ct.POINTER(OptPart), _I, _I, _F, _F, _F, ct.c_uint]),
+    "nnf_bn_calibrate_workspace_bytes": (_SZ, [_I64]),
+    "nnf_bn_calibrate_accumulator_bytes": (_SZ, [_I64]),
+    "nnf_bn_calibrate_accumulate": (_I, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ]),
+    "nnf_bn_calibrate_finish": (_I, [_P, _P, _P, _P, _P, _I64]),
     "nnf_peer_exchange_bytes": (_SZ, [_I]),
     "nnf_peer_publish": (_I, [_P, _P, ct.POINTER(_P), _I, _I, _I, _I, ct.c_uint32]),
     "nnf_peer_gather_sum": (_I, [_P, _P, _P, _I, _I, _I, ct.c_uint32]),
@@ -426,3 +438,29 @@ def bn_train_bwd_apply_peer(dx, dy, x, gamma, beta, saved, my_buf, world, kmax, 
                                            seq, _ptr(bsums), float(count_total), arr, k, _ptr(grad_gamma), _ptr(grad_beta), _ptr(grad_mean),
                                            _ptr(grad_invsigma), _ptr(grad_slope), _ptr(mean), _ptr(invsigma), float(entry_count), n, c, hw,
                                            int(add_to_destination)))
+
+
+def apply_gradient(parts, momentum_type=MOMENTUM_NONE, momentum=0.9, momentum2=0.999, normalizer=1.0, iteration_id=1, stream=None):
+    """parts: list of dicts {data, gradient, [prev_upd], [prev_upd2], [update_accum (float64 tensor of 1)], learning_rate,
+    [weight_decay]}; every chunk of the list is updated by one launch (48 chunks per launch)."""
+    arr = (OptPart * max(len(parts), 1))()
+    for k, part in enumerate(parts):
+        arr[k] = OptPart(_ptr(part["data"]), _ptr(part["gradient"]), _ptr(part.get("prev_upd")), _ptr(part.get("prev_upd2")),
+                         _ptr(part.get("update_accum")), part["learning_rate"], part.get("weight_decay", 0.0), part["data"].numel())
+    _check(lib.nnf_apply_gradient(_stream(stream), arr, len(parts), momentum_type, momentum, momentum2, normalizer, iteration_id))
+
+
+def bn_calibrate_accumulator(c, device="cuda"):
+    return torch.zeros(lib.nnf_bn_calibrate_accumulator_bytes(c) // 8, dtype=torch.float64, device=device)
+
+
+def bn_calibrate_accumulate(accumulator, x, mean, invsigma, workspace=None, stream=None):
+    n, c, hw = _nchw(x)
+    if workspace is None:
+        workspace = torch.empty(lib.nnf_bn_calibrate_workspace_bytes(c), dtype=torch.uint8, device=x.device)
+    _check(lib.nnf_bn_calibrate_accumulate(_stream(stream), _ptr(accumulator), _ptr(x), _ptr(mean), _ptr(invsigma), n, c, hw,
+                                           _ptr(workspace), workspace.numel() * workspace.element_size()))
+
+
+def bn_calibrate_finish(accumulator, c, mean=None, invsigma=None, stats=None, stream=None):
+    _check(lib.nnf_bn_calibrate_finish(_stream(stream), _ptr(mean), _ptr(invsigma), _ptr(stats), _ptr(accumulator), c))

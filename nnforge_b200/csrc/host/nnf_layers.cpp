@@ -582,6 +582,53 @@ namespace nnf_b200
 		}
 		return res;
 	}
+
+	void enqueue_apply_gradient(
+		cudaStream_t stream_id,
+		const std::vector<std::vector<device_buffer::ptr>>& data,
+		const std::vector<std::vector<device_buffer::ptr>>& gradient,
+		const std::vector<std::vector<device_buffer::ptr>>& prev_upd,
+		const std::vector<std::vector<device_buffer::ptr>>& prev_upd2,
+		const std::vector<std::vector<float>>& learning_rates,
+		const std::vector<std::vector<device_buffer::ptr>>& update_accum_buffers,
+		const std::vector<std::set<unsigned int>>& weight_decay_part_ids,
+		float gradient_normalizer,
+		float weight_decay,
+		training_momentum momentum,
+		unsigned int iteration_id)
+	{
+		const size_t layers = data.size();
+		if (gradient.size() != layers || learning_rates.size() != layers || weight_decay_part_ids.size() != layers
+			|| (momentum.is_momentum_data() && prev_upd.size() != layers) || (momentum.is_momentum_data2() && prev_upd2.size() != layers)
+			|| (!update_accum_buffers.empty() && update_accum_buffers.size() != layers))
+			throw neural_network_exception("enqueue_apply_gradient: the per-layer lists differ in length");
+		std::vector<nnf_opt_part> parts;
+		for (size_t l = 0; l < layers; ++l)
+		{
+			const size_t n = data[l].size();
+			if (gradient[l].size() != n || learning_rates[l].size() != n || (momentum.is_momentum_data() && prev_upd[l].size() != n)
+				|| (momentum.is_momentum_data2() && prev_upd2[l].size() != n))
+				throw neural_network_exception("enqueue_apply_gradient: the chunk lists of a layer differ in length");
+			const bool accum = !update_accum_buffers.empty() && !update_accum_buffers[l].empty();
+			if (accum && update_accum_buffers[l].size() != n)
+				throw neural_network_exception("enqueue_apply_gradient: one update accumulator per chunk expected");
+			for (size_t part_id = 0; part_id < n; ++part_id)
+			{
+				nnf_opt_part p;
+				p.data = *data[l][part_id];
+				p.gradient = *gradient[l][part_id];
+				p.prev_upd = momentum.is_momentum_data() ? (float *)*prev_upd[l][part_id] : nullptr;
+				p.prev_upd2 = momentum.is_momentum_data2() ? (float *)*prev_upd2[l][part_id] : nullptr;
+				p.update_accum = accum ? static_cast<double *>((void *)*update_accum_buffers[l][part_id]) : nullptr;
+				p.learning_rate = learning_rates[l][part_id];
+				p.weight_decay = weight_decay_part_ids[l].count((unsigned int)part_id) ? weight_decay : 0.0F;
+				p.elem_count = (int64_t)(data[l][part_id]->get_size() / sizeof(float));
+				parts.push_back(p);
+			}
+		}
+		check(nnf_apply_gradient(stream_id, parts.data(), (int)parts.size(), (int)momentum.type, momentum.momentum_val, momentum.momentum_val2,
+			gradient_normalizer, iteration_id));
+	}
 }
 
 // ---- flat driver interface for tests (ctypes) ----------------------------------------------------
@@ -753,5 +800,27 @@ NNFH_API int nnfh_updater_backward_data_and_weights(void * h, void * stream, voi
 	static_cast<handle *>(h)->updater->enqueue_backward_data_and_weights_propagation((cudaStream_t)stream, std::vector<device_buffer::ptr>(1, buf(in_err)), cbuf(out_err), {},
 		vec(gradient, n_gradient), cvec(data, n_data), {}, std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), device_buffer::const_ptr(), {},
 		buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), cbuf(temp_fixed), device_buffer::const_ptr(), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+// One layer's chunks: sizes in elements; prev_upd / prev_upd2 / update_accum may be null
+NNFH_API int nnfh_apply_gradient(void * stream, int n_parts, void * const * data, void * const * gradient, void * const * prev_upd, void * const * prev_upd2,
+	void * const * update_accum, const float * learning_rates, const long long * elem_counts, const int * weight_decay_parts, int n_weight_decay_parts,
+	float gradient_normalizer, float weight_decay, int momentum_type, float momentum_val, float momentum_val2, unsigned int iteration_id)
+{
+	NNFH_TRY
+	auto sized = [&](void * const * p) {
+		std::vector<device_buffer::ptr> v;
+		for (int i = 0; p && i < n_parts; ++i)
+			v.push_back(device_buffer::ptr(new device_buffer(p[i], size_t(elem_counts[i]) * sizeof(float))));
+		return std::vector<std::vector<device_buffer::ptr>>(1, v);
+	};
+	std::vector<std::vector<device_buffer::ptr>> accum;
+	if (update_accum)
+		accum = sized(update_accum);
+	enqueue_apply_gradient((cudaStream_t)stream, sized(data), sized(gradient), sized(prev_upd), sized(prev_upd2),
+		std::vector<std::vector<float>>(1, std::vector<float>(learning_rates, learning_rates + n_parts)), accum,
+		std::vector<std::set<unsigned int>>(1, std::set<unsigned int>(weight_decay_parts, weight_decay_parts + n_weight_decay_parts)),
+		gradient_normalizer, weight_decay, training_momentum((training_momentum::momentum_type)momentum_type, momentum_val, momentum_val2), iteration_id);
 	NNFH_CATCH
 }

@@ -253,6 +253,37 @@ namespace nnf_b200
 		std::vector<std::string> get_type_names() const;
 	};
 
+	// nnforge/training_momentum.h
+	struct training_momentum
+	{
+		enum momentum_type { no_momentum, vanilla_momentum, nesterov_momentum, adam_momentum };
+		training_momentum(momentum_type type = no_momentum, float momentum_val = 0.0F, float momentum_val2 = 0.0F)
+			: type(type), momentum_val(momentum_val), momentum_val2(momentum_val2) {}
+		bool is_momentum_data() const { return type != no_momentum; }
+		bool is_momentum_data2() const { return type == adam_momentum; }
+		momentum_type type;
+		float momentum_val, momentum_val2;
+	};
+
+	// The optimiser step of backward_propagation_cuda::enqueue_apply_gradient (nnforge/cuda/backward_propagation_cuda.cpp:2008-2096)
+	// for ALL weight chunks of ALL layers given, in one launch per 48 chunks instead of one launch per chunk. One element of
+	// each list per layer; data[l][part] sizes give the element counts; update_accum_buffers[l] may be empty (no statistics)
+	// or hold one buffer of one double per chunk. weight_decay applies to the chunks in weight_decay_part_ids[l]
+	// (layer::get_weight_decay_part_id_set(): empty for BatchNorm and PReLU).
+	void enqueue_apply_gradient(
+		cudaStream_t stream_id,
+		const std::vector<std::vector<device_buffer::ptr>>& data,
+		const std::vector<std::vector<device_buffer::ptr>>& gradient,
+		const std::vector<std::vector<device_buffer::ptr>>& prev_upd,
+		const std::vector<std::vector<device_buffer::ptr>>& prev_upd2,
+		const std::vector<std::vector<float>>& learning_rates,
+		const std::vector<std::vector<device_buffer::ptr>>& update_accum_buffers,
+		const std::vector<std::set<unsigned int>>& weight_decay_part_ids,
+		float gradient_normalizer,
+		float weight_decay,
+		training_momentum momentum,
+		unsigned int iteration_id);
+
 	// Output shape of a layer for given inputs (max_subsampling_layer.cpp:106-137; identity for the rest).
 	layer_configuration_specific get_output_layer_configuration_specific(const layer& l, const std::vector<layer_configuration_specific>& inputs);
 }

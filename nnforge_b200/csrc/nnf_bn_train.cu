@@ -566,6 +566,412 @@ namespace nnf
 			return NNF_OK;
 		}
 
+		// ---- planes that are not whole float4s (7x7, 13x13, fully connected: H*W % 4 != 0) -----------------------
+		// A single plane is then neither 16-byte aligned nor a whole number of vectors, and the kernels above fall
+		// back to scalar loads of 49-float runs. `unit` = 4 / gcd(H*W, 4) adjacent channels of one entry do form an
+		// aligned run of whole vectors, so here a CTA owns a GROUP of G channels (a multiple of `unit`) and a slice of
+		// entries; the group's run of G*H*W floats per entry is read with coalesced 128-bit loads. A thread owns the
+		// same vector positions of the run in every entry, so the channel of each of its elements - and every
+		// per-channel constant - is fixed for the whole loop and sits in registers, and it accumulates per POSITION;
+		// at the end the positions are folded per channel through shared memory in a fixed order.
+		constexpr int kGroupMaxRun = 2048;      // floats of one group's run (R <= 2 vectors per thread)
+
+		struct group_geom
+		{
+			uint32_t n, c, hw;
+			uint32_t group;            // channels per group
+			uint32_t groups;
+			uint32_t split, entries_per_cta;
+			int vectors_per_thread;    // 1 or 2
+			fastdiv d_hw;
+		};
+
+		// false: the shape keeps the per-channel kernels
+		bool make_group_geom(group_geom& g, int64_t n, int64_t c, int64_t hw, bool aligned)
+		{
+			if (!aligned || hw % 4 == 0 || getenv("NNF_NO_GROUPED"))
+				return false;
+			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
+			const int64_t vpu = unit * hw / 4;        // vectors of one unit of channels
+			if (c % unit != 0 || vpu > 2 * kThreads || n > 0x7fffffff || c > 0x7fffffff)
+				return false;
+			const int64_t k1 = kThreads / vpu, k2 = (2 * kThreads) / vpu;
+			int r = 1;
+			int64_t k = k1;
+			if (k1 == 0 || double(k2 * vpu) / (2 * kThreads) > double(k1 * vpu) / kThreads + 0.1)
+			{
+				r = 2;
+				k = k2;
+			}
+			int64_t group = unit * k;
+			if (group > c)
+				group = c;
+			if (group > 1024)   // kGroupMaxChannels: the per-group tables of bn_apply_grouped_kernel
+				group = 1024;
+			g.n = (uint32_t)n; g.c = (uint32_t)c; g.hw = (uint32_t)hw;
+			g.group = (uint32_t)group;
+			g.groups = (uint32_t)div_up(c, group);
+			g.vectors_per_thread = r;
+			int64_t split = (int64_t(kSmCount) * 8) / g.groups;
+			if (split > n / 4) split = n / 4;
+			if (split > kMaxSplit) split = kMaxSplit;
+			if (split < 1) split = 1;
+			g.entries_per_cta = (uint32_t)div_up(n, split);
+			g.split = (uint32_t)div_up(n, g.entries_per_cta);
+			g.d_hw = fastdiv((uint32_t)hw);
+			return true;
+		}
+
+		struct group_cta
+		{
+			uint32_t ch0, channels, vectors, sp, e0, e1;
+			size_t stride4;            // float4s between the same position of consecutive entries
+			size_t base4;              // float4 offset of the group's run in entry e0
+		};
+
+		__device__ __forceinline__ group_cta group_locate(const group_geom& g)
+		{
+			group_cta t;
+			const uint32_t grp = blockIdx.x / g.split;
+			t.sp = blockIdx.x - grp * g.split;
+			t.ch0 = grp * g.group;
+			t.channels = min(g.group, g.c - t.ch0);
+			t.vectors = (t.channels * g.hw) >> 2;
+			t.e0 = t.sp * g.entries_per_cta;
+			t.e1 = min(t.e0 + g.entries_per_cta, g.n);
+			t.stride4 = (size_t(g.c) * g.hw) >> 2;
+			t.base4 = ((size_t(t.e0) * g.c + t.ch0) * g.hw) >> 2;
+			return t;
+		}
+
+		// per-channel sum of K position arrays held in shared memory -> this CTA's partials
+		template <int K>
+		__device__ __forceinline__ void group_fold(double * partial, const float (*s_pos)[kGroupMaxRun], const group_geom& g, const group_cta& t)
+		{
+			for (uint32_t ch = threadIdx.x; ch < t.channels; ch += kThreads)
+			{
+				double acc[K];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					acc[k] = 0.0;
+				for (uint32_t i = 0; i < g.hw; ++i)
+				{
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						acc[k] += double(s_pos[k][ch * g.hw + i]);
+				}
+				double * out = partial + (size_t(t.ch0 + ch) * g.split + t.sp) * kSums;
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					out[k] = acc[k];
+			}
+		}
+
+		template <int R>
+		__global__ void __launch_bounds__(kThreads) bn_stats_grouped_kernel(double * partial, const float * x, const group_geom g)
+		{
+			__shared__ float s_pos[2][kGroupMaxRun];
+			constexpr int U = 4;   // entries in flight
+			const group_cta t = group_locate(g);
+			float s[R][4], q[R][4];
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+					s[r][j] = q[r][j] = 0.0F;
+			const float4 * base = reinterpret_cast<const float4 *>(x) + t.base4;
+			for (uint32_t e = t.e0; e < t.e1; e += U)
+			{
+				float4 a[U][R];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						a[u][r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						if (e + u < t.e1 && v < t.vectors)
+							a[u][r] = __ldg(base + size_t(e + u - t.e0) * t.stride4 + v);
+					}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						s[r][0] += a[u][r].x; s[r][1] += a[u][r].y; s[r][2] += a[u][r].z; s[r][3] += a[u][r].w;
+						q[r][0] = fmaf(a[u][r].x, a[u][r].x, q[r][0]); q[r][1] = fmaf(a[u][r].y, a[u][r].y, q[r][1]);
+						q[r][2] = fmaf(a[u][r].z, a[u][r].z, q[r][2]); q[r][3] = fmaf(a[u][r].w, a[u][r].w, q[r][3]);
+					}
+			}
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+			{
+				const uint32_t v = threadIdx.x + r * kThreads;
+				if (v < t.vectors)
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+					{
+						s_pos[0][v * 4 + j] = s[r][j];
+						s_pos[1][v * 4 + j] = q[r][j];
+					}
+			}
+			__syncthreads();
+			group_fold<2>(partial, s_pos, g, t);
+		}
+
+		// the constants of one owned element
+		struct group_elem
+		{
+			float mean, invstd, mult, add, slope, c2, c3;
+		};
+
+		template <int R>
+		__device__ __forceinline__ void group_constants(group_elem (&k)[R][4], const bwd_params& p, const group_geom& g, const group_cta& t, bool with_sums)
+		{
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+			{
+				const uint32_t v = threadIdx.x + r * kThreads;
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+				{
+					const uint32_t pos = min(v * 4 + j, t.channels * g.hw - 1);
+					const uint32_t ch = t.ch0 + g.d_hw.div(pos);
+					group_elem& el = k[r][j];
+					el.mean = __ldg(p.saved + ch);
+					el.invstd = __ldg(p.saved + g.c + ch);
+					el.mult = __fmul_rn(__ldg(p.gamma + ch), el.invstd);
+					el.add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(el.mult, el.mean));
+					el.slope = chain_slope(p.chain, ch);
+					el.c2 = el.c3 = 0.0F;
+					if (with_sums)
+					{
+						el.c2 = float(double(__ldg(p.gsums + ch)) / p.count_total);
+						el.c3 = float(double(__ldg(p.gsums + g.c + ch)) / p.count_total);
+					}
+				}
+			}
+		}
+
+		template <int A0, int A1, int R>
+		__global__ void __launch_bounds__(kThreads) bn_bwd_stats_grouped_kernel(double * partial, const bwd_params p, const group_geom g)
+		{
+			__shared__ float s_pos[3][kGroupMaxRun];
+			constexpr int U = 2;
+			const group_cta t = group_locate(g);
+			group_elem k[R][4];
+			group_constants<R>(k, p, g, t, false);
+			float sb[R][4], sg[R][4], ss[R][4];
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+					sb[r][j] = sg[r][j] = ss[r][j] = 0.0F;
+			const float4 * bx = reinterpret_cast<const float4 *>(p.x) + t.base4;
+			const float4 * bd = reinterpret_cast<const float4 *>(p.dy) + t.base4;
+			for (uint32_t e = t.e0; e < t.e1; e += U)
+			{
+				float4 a[U][R], d[U][R];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						a[u][r] = d[u][r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						if (e + u < t.e1 && v < t.vectors)
+						{
+							const size_t off = size_t(e + u - t.e0) * t.stride4 + v;
+							a[u][r] = __ldg(bx + off);
+							d[u][r] = __ldg(bd + off);
+						}
+					}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					if (e + u < t.e1)
+					{
+						#pragma unroll
+						for (int r = 0; r < R; ++r)
+						{
+							const float xs[4] = {a[u][r].x, a[u][r].y, a[u][r].z, a[u][r].w};
+							const float ds[4] = {d[u][r].x, d[u][r].y, d[u][r].z, d[u][r].w};
+							#pragma unroll
+							for (int j = 0; j < 4; ++j)
+							{
+								const group_elem& el = k[r][j];
+								const float uu = __fadd_rn(__fmul_rn(xs[j], el.mult), el.add);
+								float term;
+								const float du = chain_backward<A0, A1>(p.chain, uu, ds[j], el.slope, term);
+								const float xhat = __fmul_rn(__fsub_rn(xs[j], el.mean), el.invstd);
+								sb[r][j] += du;
+								sg[r][j] += du * xhat;
+								ss[r][j] += term;
+							}
+						}
+					}
+			}
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+			{
+				const uint32_t v = threadIdx.x + r * kThreads;
+				if (v < t.vectors)
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+					{
+						s_pos[0][v * 4 + j] = sb[r][j];
+						s_pos[1][v * 4 + j] = sg[r][j];
+						s_pos[2][v * 4 + j] = ss[r][j];
+					}
+			}
+			__syncthreads();
+			group_fold<3>(partial, s_pos, g, t);
+		}
+
+		template <int A0, int A1, int R>
+		__global__ void __launch_bounds__(kThreads) bn_bwd_apply_grouped_kernel(const bwd_params p, const group_geom g)
+		{
+			constexpr int U = 2;
+			const group_cta t = group_locate(g);
+			if (t.sp == 0)
+				for (uint32_t i = threadIdx.x; i < t.channels; i += kThreads)
+				{
+					// per-channel gradients accumulate the LOCAL sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+					const uint32_t ch = t.ch0 + i;
+					if (p.grad_beta) p.grad_beta[ch] += p.bsums[ch];
+					if (p.grad_gamma) p.grad_gamma[ch] += p.bsums[g.c + ch];
+					if (p.grad_slope) p.grad_slope[ch] += p.bsums[2 * g.c + ch];
+					if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (__ldg(p.saved + ch) - p.mean[ch]);
+					if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (__ldg(p.saved + g.c + ch) - p.invsigma[ch]);
+				}
+			group_elem k[R][4];
+			group_constants<R>(k, p, g, t, true);
+			const float4 * bx = reinterpret_cast<const float4 *>(p.x) + t.base4;
+			const float4 * bd = reinterpret_cast<const float4 *>(p.dy) + t.base4;
+			float4 * bo = reinterpret_cast<float4 *>(p.dx) + t.base4;
+			for (uint32_t e = t.e0; e < t.e1; e += U)
+			{
+				float4 a[U][R], d[U][R], o[U][R];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						o[u][r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						if (e + u < t.e1 && v < t.vectors)
+						{
+							const size_t off = size_t(e + u - t.e0) * t.stride4 + v;
+							a[u][r] = ld_stream(bx + off);
+							d[u][r] = ld_stream(bd + off);
+							if (p.add)
+								o[u][r] = ld_stream(bo + off);
+						}
+					}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						if (e + u < t.e1 && v < t.vectors)
+						{
+							const float xs[4] = {a[u][r].x, a[u][r].y, a[u][r].z, a[u][r].w};
+							const float ds[4] = {d[u][r].x, d[u][r].y, d[u][r].z, d[u][r].w};
+							const float os[4] = {o[u][r].x, o[u][r].y, o[u][r].z, o[u][r].w};
+							float rs[4];
+							#pragma unroll
+							for (int j = 0; j < 4; ++j)
+							{
+								const group_elem& el = k[r][j];
+								const float uu = __fadd_rn(__fmul_rn(xs[j], el.mult), el.add);
+								float term;
+								const float du = chain_backward<A0, A1>(p.chain, uu, ds[j], el.slope, term);
+								const float xhat = __fmul_rn(__fsub_rn(xs[j], el.mean), el.invstd);
+								const float res = el.mult * ((du - el.c2) - xhat * el.c3);
+								rs[j] = p.add ? os[j] + res : res;
+							}
+							st_stream(bo + size_t(e + u - t.e0) * t.stride4 + v, make_float4(rs[0], rs[1], rs[2], rs[3]));
+						}
+					}
+			}
+		}
+
+		constexpr int kGroupMaxChannels = 1024;   // channels of one group (reached by fully connected shapes, H*W = 1)
+
+		// Training-mode normalisation + activation chain on a channel group: scale and shift of the group's channels
+		// are derived once per CTA into shared memory (same expressions as bn_apply_channel_kernel), every thread then
+		// keeps the constants of the elements it owns in registers.
+		template <int A0, int A1, int R>
+		__global__ void __launch_bounds__(kThreads) bn_apply_grouped_kernel(const apply_params p, const group_geom g)
+		{
+			__shared__ float s_mult[kGroupMaxChannels], s_add[kGroupMaxChannels];
+			constexpr int U = 4;
+			const group_cta t = group_locate(g);
+			for (uint32_t i = threadIdx.x; i < t.channels; i += kThreads)
+			{
+				const uint32_t ch = t.ch0 + i;
+				const double m = double(__ldg(p.sums + ch)) / p.count_total;
+				double var = double(__ldg(p.sums + g.c + ch)) / p.count_total - m * m;
+				var = var < 0.0 ? 0.0 : var;
+				const float mean = float(m);
+				const float invstd = float(1.0 / sqrt(var + double(p.eps)));
+				if (t.sp == 0 && p.saved)
+				{
+					p.saved[ch] = mean;
+					p.saved[g.c + ch] = invstd;
+				}
+				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+				s_mult[i] = mult;
+				s_add[i] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+			}
+			__syncthreads();
+			float mult[R][4], add[R][4], slope[R][4];
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+			{
+				const uint32_t v = threadIdx.x + r * kThreads;
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+				{
+					const uint32_t local = g.d_hw.div(min(v * 4 + j, t.channels * g.hw - 1));
+					mult[r][j] = s_mult[local];
+					add[r][j] = s_add[local];
+					slope[r][j] = chain_slope(p.chain, t.ch0 + local);
+				}
+			}
+			const float4 * bx = reinterpret_cast<const float4 *>(p.x) + t.base4;
+			float4 * by = reinterpret_cast<float4 *>(p.y) + t.base4;
+			for (uint32_t e = t.e0; e < t.e1; e += U)
+			{
+				float4 a[U][R];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						if (e + u < t.e1 && v < t.vectors)
+							a[u][r] = ld_stream(bx + size_t(e + u - t.e0) * t.stride4 + v);
+					}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						if (e + u < t.e1 && v < t.vectors)
+						{
+							float4 o;
+							o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u][r].x, mult[r][0]), add[r][0]), slope[r][0]);
+							o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u][r].y, mult[r][1]), add[r][1]), slope[r][1]);
+							o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u][r].z, mult[r][2]), add[r][2]), slope[r][2]);
+							o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u][r].w, mult[r][3]), add[r][3]), slope[r][3]);
+							st_stream(by + size_t(e + u - t.e0) * t.stride4 + v, o);
+						}
+					}
+			}
+		}
+
 		int check_train_args(const char * who, int64_t n, int64_t c, int64_t hw)
 		{
 			if (n <= 0 || c <= 0 || hw <= 0)
@@ -622,12 +1028,26 @@ int stats_impl(nnf_stream_t stream, float * sums, const float * x, int64_t n, in
 	if (!workspace || workspace_bytes < nnf_bn_train_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_stats: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel), 1);
-	if (st != NNF_OK)
-		return st;
+	group_geom gg;
 	cudaStream_t s = (cudaStream_t)stream;
-	bn_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), x, g);
-	st = check_launch("bn_stats_kernel");
+	if (make_group_geom(gg, n, c, hw, aligned16(x)))
+	{
+		if (gg.vectors_per_thread == 1)
+			bn_stats_grouped_kernel<1><<<gg.groups * gg.split, kThreads, 0, s>>>(static_cast<double *>(workspace), x, gg);
+		else
+			bn_stats_grouped_kernel<2><<<gg.groups * gg.split, kThreads, 0, s>>>(static_cast<double *>(workspace), x, gg);
+		st = check_launch("bn_stats_grouped_kernel");
+		g.c = gg.c;
+		g.split = gg.split;
+	}
+	else
+	{
+		st = make_chan_geom(g, "nnf_bn_train_stats", n, c, hw, aligned16(x), resident_ctas_per_sm(bn_stats_kernel), 1);
+		if (st != NNF_OK)
+			return st;
+		bn_stats_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), x, g);
+		st = check_launch("bn_stats_kernel");
+	}
 	if (st != NNF_OK)
 		return st;
 	if (publish)
@@ -691,6 +1111,27 @@ int apply_impl(nnf_stream_t stream, float * y, float * saved, const float * x, c
 	int prelus = 0;
 	for (int i = 0; i < chain.n; ++i)
 		prelus += chain.a[i].kind == NNF_ACT_PRELU;
+	group_geom gg;
+	if (!peer && prelus <= 1 && make_group_geom(gg, n, c, hw, aligned16(x) && aligned16(y)))
+	{
+		apply_params p = {};
+		p.y = y; p.x = x; p.gamma = gamma; p.beta = beta; p.sums = sums; p.saved = saved; p.count_total = count_total; p.eps = eps;
+		p.chain = chain;
+		const unsigned grid = gg.groups * gg.split;
+		cudaStream_t s = (cudaStream_t)stream;
+		#define NNF_GROUPED_APPLY(A0, A1) \
+			do { if (gg.vectors_per_thread == 1) bn_apply_grouped_kernel<A0, A1, 1><<<grid, kThreads, 0, s>>>(p, gg); \
+			     else bn_apply_grouped_kernel<A0, A1, 2><<<grid, kThreads, 0, s>>>(p, gg); } while (0)
+		switch (chain_id(chain))
+		{
+		case 0: NNF_GROUPED_APPLY(NNF_ACT_NONE, 0); break;
+		case 1: NNF_GROUPED_APPLY(NNF_ACT_PRELU, NNF_ACT_ELU); break;
+		case 2: NNF_GROUPED_APPLY(NNF_ACT_RELU, 0); break;
+		default: NNF_GROUPED_APPLY(-1, 0); break;
+		}
+		#undef NNF_GROUPED_APPLY
+		return check_launch("bn_apply_grouped_kernel");
+	}
 	// planes large enough to keep a CTA busy and whole float4s: the channel-ordered kernel (L2 reuse after the
 	// statistics kernel); anything else: the flat streaming kernel
 	if (hw % 4 == 0 && (n * hw >= 16384 || peer) && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && !getenv("NNF_APPLY_FLAT"))
@@ -788,18 +1229,41 @@ int bwd_stats_impl(nnf_stream_t stream, float * bsums, float * gsums, const floa
 	if (st != NNF_OK)
 		return st;
 	chan_geom g;
-	st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(bn_bwd_stats_kernel<-1, 0>), 2);
-	if (st != NNF_OK)
-		return st;
+	group_geom gg;
 	cudaStream_t s = (cudaStream_t)stream;
-	switch (chain_id(p.chain))
+	if (make_group_geom(gg, n, c, hw, aligned16(x) && aligned16(dy)))
 	{
-	case 0: bn_bwd_stats_kernel<NNF_ACT_NONE, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
-	case 1: bn_bwd_stats_kernel<NNF_ACT_PRELU, NNF_ACT_ELU><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
-	case 2: bn_bwd_stats_kernel<NNF_ACT_RELU, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
-	default: bn_bwd_stats_kernel<-1, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+		double * ws = static_cast<double *>(workspace);
+		const unsigned grid = gg.groups * gg.split;
+		#define NNF_GROUPED_BWD_STATS(A0, A1) \
+			do { if (gg.vectors_per_thread == 1) bn_bwd_stats_grouped_kernel<A0, A1, 1><<<grid, kThreads, 0, s>>>(ws, p, gg); \
+			     else bn_bwd_stats_grouped_kernel<A0, A1, 2><<<grid, kThreads, 0, s>>>(ws, p, gg); } while (0)
+		switch (chain_id(p.chain))
+		{
+		case 0: NNF_GROUPED_BWD_STATS(NNF_ACT_NONE, 0); break;
+		case 1: NNF_GROUPED_BWD_STATS(NNF_ACT_PRELU, NNF_ACT_ELU); break;
+		case 2: NNF_GROUPED_BWD_STATS(NNF_ACT_RELU, 0); break;
+		default: NNF_GROUPED_BWD_STATS(-1, 0); break;
+		}
+		#undef NNF_GROUPED_BWD_STATS
+		st = check_launch("bn_bwd_stats_grouped_kernel");
+		g.c = gg.c;
+		g.split = gg.split;
 	}
-	st = check_launch("bn_bwd_stats_kernel");
+	else
+	{
+		st = make_chan_geom(g, "nnf_bn_train_bwd_stats", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(bn_bwd_stats_kernel<-1, 0>), 2);
+		if (st != NNF_OK)
+			return st;
+		switch (chain_id(p.chain))
+		{
+		case 0: bn_bwd_stats_kernel<NNF_ACT_NONE, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+		case 1: bn_bwd_stats_kernel<NNF_ACT_PRELU, NNF_ACT_ELU><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+		case 2: bn_bwd_stats_kernel<NNF_ACT_RELU, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+		default: bn_bwd_stats_kernel<-1, 0><<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), p, g); break;
+		}
+		st = check_launch("bn_bwd_stats_kernel");
+	}
 	if (st != NNF_OK)
 		return st;
 	if (publish)
@@ -882,6 +1346,24 @@ int bwd_apply_impl(nnf_stream_t stream, float * dx, const float * dy, const floa
 	p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
 	p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 	p.add = add_to_destination ? 1 : 0;
+	group_geom gg;
+	if (!peer && make_group_geom(gg, n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx)))
+	{
+		const unsigned grid = gg.groups * gg.split;
+		cudaStream_t s = (cudaStream_t)stream;
+		#define NNF_GROUPED_BWD_APPLY(A0, A1) \
+			do { if (gg.vectors_per_thread == 1) bn_bwd_apply_grouped_kernel<A0, A1, 1><<<grid, kThreads, 0, s>>>(p, gg); \
+			     else bn_bwd_apply_grouped_kernel<A0, A1, 2><<<grid, kThreads, 0, s>>>(p, gg); } while (0)
+		switch (chain_id(p.chain))
+		{
+		case 0: NNF_GROUPED_BWD_APPLY(NNF_ACT_NONE, 0); break;
+		case 1: NNF_GROUPED_BWD_APPLY(NNF_ACT_PRELU, NNF_ACT_ELU); break;
+		case 2: NNF_GROUPED_BWD_APPLY(NNF_ACT_RELU, 0); break;
+		default: NNF_GROUPED_BWD_APPLY(-1, 0); break;
+		}
+		#undef NNF_GROUPED_BWD_APPLY
+		return check_launch("bn_bwd_apply_grouped_kernel");
+	}
 	chan_geom g;
 	st = make_chan_geom(g, "nnf_bn_train_bwd_apply", n, c, hw, aligned16(x) && aligned16(dy) && aligned16(dx), resident_ctas_per_sm(bn_bwd_apply_kernel<-1, 0>), 8);
 	if (st != NNF_OK)

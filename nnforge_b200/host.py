@@ -159,3 +159,20 @@ def plan_fusion(spec, training=False):
         groups.append({"kind": kind, "entry_point": None if entry == "-" else entry, "members": val(members),
                        "residual": (val(residual) or [None])[0], "elided": val(elided)})
     return groups
+
+
+NO_MOMENTUM, VANILLA_MOMENTUM, NESTEROV_MOMENTUM, ADAM_MOMENTUM = range(4)
+
+
+def enqueue_apply_gradient(data, gradient, learning_rates, prev_upd=None, prev_upd2=None, update_accum_buffers=None, weight_decay_part_ids=(),
+                           gradient_normalizer=1.0, weight_decay=0.0, momentum_type=NO_MOMENTUM, momentum_val=0.0, momentum_val2=0.0, iteration_id=1):
+    """One layer's weight chunks through nnf_b200::enqueue_apply_gradient (the mirror of
+    backward_propagation_cuda::enqueue_apply_gradient): lists of CUDA tensors, one entry per chunk."""
+    n = len(data)
+    arr = lambda ts: _arr(ts)[0] if ts is not None else None
+    lrs = (ct.c_float * max(n, 1))(*learning_rates)
+    counts = (ct.c_longlong * max(n, 1))(*[t.numel() for t in data])
+    wd = (ct.c_int * max(len(weight_decay_part_ids), 1))(*weight_decay_part_ids)
+    _check(lib.nnfh_apply_gradient(_stream(), n, arr(data), arr(gradient), arr(prev_upd), arr(prev_upd2), arr(update_accum_buffers), lrs, counts, wd,
+                                   len(weight_decay_part_ids), ct.c_float(gradient_normalizer), ct.c_float(weight_decay), momentum_type,
+                                   ct.c_float(momentum_val), ct.c_float(momentum_val2), iteration_id))

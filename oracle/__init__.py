@@ -194,6 +194,36 @@ class Oracle:
         self.lib.orc_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, _i64(top_n), _i64(n), _i64(c), _i64(hw))
         return out
 
+    # ---- optimiser step and batch-norm recalibration ------------------------------------------------------
+    MOMENTUM = {"none": 0, "vanilla": 1, "nesterov": 2, "adam": 3}
+
+    def apply_gradient(self, data, gradient, prev_upd=None, prev_upd2=None, momentum_type="none", learning_rate=0.01, normalizer=1.0,
+                       weight_decay=0.0, momentum=0.9, momentum2=0.999, iteration_id=1):
+        """One weight chunk, updated IN PLACE (float32 arrays); returns the sum of |update|."""
+        self.lib.orc_apply_gradient.restype = ct.c_double
+        return self.lib.orc_apply_gradient(_fp(data), _fp(gradient), _fp(prev_upd), _fp(prev_upd2), _i64(data.size), self.MOMENTUM[momentum_type],
+                                           ct.c_float(learning_rate), ct.c_float(normalizer), ct.c_float(weight_decay), ct.c_float(momentum),
+                                           ct.c_float(momentum2), ct.c_uint(iteration_id))
+
+    def feature_map_stats(self, batches):
+        """batches: iterable of [N,C,...] arrays -> stats[4][C] = min, max, average, std_dev over all of them."""
+        state = minmax = None
+        for y in batches:
+            y = _c(y)
+            n, c = y.shape[0], y.shape[1]
+            if state is None:
+                state = np.zeros((c, 3), np.float64)
+                minmax = np.tile(np.array([np.finfo(np.float32).max, -np.finfo(np.float32).max], np.float32), (c, 1)).copy()
+            self.lib.orc_feature_map_stats_update(_dp(state), _fp(minmax), _fp(y), _i64(n), _i64(c), _i64(y.size // (n * c)))
+        stats = np.empty((4, state.shape[0]), np.float32)
+        self.lib.orc_feature_map_stats_get(_fp(stats), _dp(state), _fp(minmax), _i64(state.shape[0]))
+        return stats
+
+    def bn_recalibrate(self, mean, invsigma, stats):
+        mean, invsigma = _c(mean).copy(), _c(invsigma).copy()
+        self.lib.orc_bn_recalibrate(_fp(mean), _fp(invsigma), _fp(_c(stats)), _i64(mean.size))
+        return mean, invsigma
+
     # ---- average subsampling ------------------------------------------------------------------------
     def avgpool_fwd(self, x, win, mult=None):
         """x [N,C,H,W]; win = (w, h); mult defaults to 1 / window elements."""
@@ -313,7 +343,7 @@ class Reference:
         for fn in ("ref_bn_infer", "ref_relu_fwd", "ref_relu_bwd", "ref_prelu_fwd", "ref_prelu_bwd_data", "ref_prelu_bwd_weights",
                    "ref_elu_fwd", "ref_elu_bwd", "ref_tanh_fwd", "ref_tanh_bwd", "ref_sigmoid_fwd", "ref_sigmoid_bwd", "ref_softmax_fwd",
                    "ref_softmax_upd_fwd", "ref_softmax_bwd", "ref_add_fwd", "ref_add_bwd", "ref_maxpool_fwd", "ref_maxpool_tester_fwd",
-                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd", "ref_avgpool_fwd", "ref_avgpool_bwd"):
+                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd", "ref_avgpool_fwd", "ref_avgpool_bwd", "ref_feature_map_stats"):
             getattr(self.lib, fn).restype = ct.c_double
 
     def _check(self, seconds):
@@ -426,6 +456,13 @@ class Reference:
         s = self.lib.ref_accuracy_fwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_uint(top_n), *d, int(updater),
                                       self.threads, reps)
         return out, self._check(s)
+
+    def feature_map_stats(self, y):
+        """y [N,C,H,W] -> stats[4][C] = min, max, average, std_dev (stat_data_bunch_writer)."""
+        y, d = self._dims(y)
+        stats = np.empty((4, y.shape[1]), np.float32)
+        self._check(self.lib.ref_feature_map_stats(_fp(stats), _fp(y), *d))
+        return stats
 
     def avgpool_fwd(self, x, win, updater=False, reps=1):
         x, d = self._dims(x)

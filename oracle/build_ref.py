@@ -42,7 +42,8 @@ PLAIN = (
 CORE = (
     ["%s_layer.cpp" % n for n in LAYERS + ["negative_log_likelihood", "accuracy", "average_subsampling"]]
     + ["layer.cpp", "layer_configuration_specific.cpp", "layer_data.cpp", "layer_data_custom.cpp",
-       "layer_data_configuration.cpp", "rnd.cpp", "neural_network_exception.cpp", "tiling_factor.cpp"]
+       "layer_data_configuration.cpp", "rnd.cpp", "neural_network_exception.cpp", "tiling_factor.cpp",
+       "stat_data_bunch_writer.cpp"]
 )
 
 COMMON = ["-std=c++11", "-O2", "-fPIC", "-ffp-contract=off", "-include", "algorithm", "-include", "cmath",

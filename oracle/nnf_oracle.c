@@ -688,3 +688,111 @@ void orc_avgpool_bwd(float * dx, const float * dy, i64 planes, i64 h, i64 w, i64
 					*o = err;
 			}
 }
+
+/* ---- optimiser step: nnforge/plain/backward_propagation_plain.cpp:826-985 (one weight chunk) ------------
+ * momentum_type 0 none, 1 vanilla, 2 Nesterov, 3 ADAM (momentum = beta1, momentum2 = beta2, iteration counted from 1).
+ * Returns the sum of |update| in double. weight_decay is the value that applies to this chunk, as in the CUDA
+ * backend (nnforge/cuda/backward_propagation_cuda.cpp:2029-2031); the plain backend's ADAM branch uses the
+ * ungated value and its no-momentum branch carries the |update| sum over from chunk to chunk.
+ * This file of the reference needs Boost to compile, so this function is checked against the source by reading
+ * only: parity unpinned. */
+double orc_apply_gradient(float * data, float * gradient, float * prev_upd, float * prev_upd2, i64 count, int momentum_type,
+	float learning_rate, float normalizer, float weight_decay, float momentum, float momentum2, unsigned int iteration_id)
+{
+	double accum = 0.0;
+	const float mp1 = momentum + 1.0F;
+	float inv1 = 0.0F, inv2 = 0.0F;
+	const float epsilon = 1.0e-8F;
+	i64 i;
+	if (momentum_type == 3)
+	{
+		inv1 = 1.0F / (1.0F - powf(momentum, (float)iteration_id));
+		inv2 = 1.0F / (1.0F - powf(momentum2, (float)iteration_id));
+	}
+	for (i = 0; i < count; ++i)
+	{
+		const float w = data[i], gr = gradient[i];
+		float upd;
+		if (momentum_type == 0)
+			upd = learning_rate * (gr * normalizer - w * weight_decay);
+		else if (momentum_type == 1)
+		{
+			upd = prev_upd[i] * momentum + learning_rate * (gr * normalizer - w * weight_decay);
+			prev_upd[i] = upd;
+		}
+		else if (momentum_type == 2)
+		{
+			const float prev = prev_upd[i];
+			const float fresh = prev * momentum + learning_rate * (gr * normalizer - w * weight_decay);
+			upd = mp1 * fresh - momentum * prev;
+			prev_upd[i] = fresh;
+		}
+		else
+		{
+			const float total = gr * normalizer - w * weight_decay;
+			const float m1 = momentum * prev_upd[i] + (1.0F - momentum) * total;
+			const float m2 = momentum2 * prev_upd2[i] + (1.0F - momentum2) * total * total;
+			const float u1 = m1 * inv1, u2 = m2 * inv2;
+			upd = learning_rate * u1 / (sqrtf(u2) + epsilon);
+			prev_upd[i] = m1;
+			prev_upd2[i] = m2;
+		}
+		accum += (double)fabsf(upd);
+		data[i] = w + upd;
+		gradient[i] = 0.0F;
+	}
+	return accum;
+}
+
+/* ---- per-feature-map statistics: nnforge/stat_data_bunch_writer.cpp:44-111 -------------------------------
+ * state[c][3] = {n, mean, m2} (double) and minmax[c][2] carry over between calls (one call per batch of entries);
+ * value by value update of Welford's single-pass algorithm, as the reference does per entry. */
+void orc_feature_map_stats_update(double * state, float * minmax, const float * y, i64 n, i64 c, i64 hw)
+{
+	i64 e, ch, i;
+	for (e = 0; e < n; ++e)
+		for (ch = 0; ch < c; ++ch)
+		{
+			double * st = state + ch * 3;
+			const float * in = y + (e * c + ch) * hw;
+			for (i = 0; i < hw; ++i)
+			{
+				const float val = in[i];
+				double val_d, delta, delta2;
+				if (val < minmax[ch * 2]) minmax[ch * 2] = val;
+				if (val > minmax[ch * 2 + 1]) minmax[ch * 2 + 1] = val;
+				st[0] += 1.0;
+				val_d = (double)val;
+				delta = val_d - st[1];
+				st[1] += delta / st[0];
+				delta2 = val_d - st[1];
+				st[2] += delta * delta2;
+			}
+		}
+}
+
+/* stats[4][c] = {min, max, average, std_dev}: stat_data_bunch_writer::get_stat, nnforge/stat_data_bunch_writer.cpp:83-111 */
+void orc_feature_map_stats_get(float * stats, const double * state, const float * minmax, i64 c)
+{
+	i64 ch;
+	for (ch = 0; ch < c; ++ch)
+	{
+		stats[ch] = minmax[ch * 2];
+		stats[c + ch] = minmax[ch * 2 + 1];
+		stats[2 * c + ch] = (float)state[ch * 3 + 1];
+		stats[3 * c + ch] = sqrtf((float)(state[ch * 3 + 2] / state[ch * 3]));
+	}
+}
+
+/* toolset::update_bn_weights, nnforge/toolset.cpp:1613-1620: the running statistics rewritten from the statistics of the
+ * layer's output under gamma 1, beta 0. (toolset.cpp needs Boost to compile: checked against the source by reading.) */
+void orc_bn_recalibrate(float * mean, float * invsigma, const float * stats, i64 c)
+{
+	i64 ch;
+	for (ch = 0; ch < c; ++ch)
+	{
+		const float old_mean = mean[ch], old_invsigma = invsigma[ch];
+		invsigma[ch] = old_invsigma / stats[3 * c + ch];
+		mean[ch] = old_mean + stats[2 * c + ch] / old_invsigma;
+	}
+}

@@ -44,6 +44,7 @@
 #include "average_subsampling_layer.h"
 #include "add_layer.h"
 #include "max_subsampling_layer.h"
+#include "stat_data_bunch_writer.h"
 
 #include <chrono>
 #include <cstring>
@@ -653,6 +654,34 @@ extern "C"
 		});
 		memcpy(dx, (const void *)(*in_err), in_bytes);
 		return s;
+		REF_GUARD_END
+	}
+
+	// nnforge/stat_data_bunch_writer.cpp:44-111: stats[4][c] = {min, max, average, std_dev} of y[n][c][hw], entries fed one by
+	// one as forward_propagation hands them to the writer
+	double ref_feature_map_stats(float * stats, const float * y, unsigned int n, unsigned int c, unsigned int h, unsigned int w)
+	{
+		REF_GUARD_BEGIN
+		stat_data_bunch_writer writer;
+		std::map<std::string, layer_configuration_specific> cfg;
+		cfg.insert(std::make_pair(std::string("bn"), make_config(c, h, w)));
+		writer.set_config_map(cfg);
+		const size_t per_entry = (size_t)c * h * w;
+		for (unsigned int e = 0; e < n; ++e)
+		{
+			std::map<std::string, const float *> data;
+			data.insert(std::make_pair(std::string("bn"), y + e * per_entry));
+			writer.write(e, data);
+		}
+		const std::vector<feature_map_data_stat> st = writer.get_stat().find("bn")->second;
+		for (unsigned int ch = 0; ch < c; ++ch)
+		{
+			stats[ch] = st[ch].min;
+			stats[c + ch] = st[ch].max;
+			stats[2 * c + ch] = st[ch].average;
+			stats[3 * c + ch] = st[ch].std_dev;
+		}
+		return 0.0;
 		REF_GUARD_END
 	}
 }

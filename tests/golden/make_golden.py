@@ -105,6 +105,10 @@ def main():
     gx = synth.normal(g, (3, 5, 7, 7))
     out["avg_gx"] = gx
     out["avg_global"] = ref.avgpool_fwd(gx, (7, 7), updater=True)[0]
+    # per-feature-map statistics of a layer output (stat_data_bunch_writer), values far from zero mean
+    sy = synth.normal(g, (6, 5, 7, 3), 100.0, 3.0)
+    out["stat_y"] = sy
+    out["stat_minmaxavgstd"] = ref.feature_map_stats(sy)
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_backend.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -177,3 +177,29 @@ def test_average_subsampling_objects(host, oracle):
     u.enqueue_backward_data_propagation(dx, dev(dy), [], None, None, n)
     assert_bits_equal(out(dx), oracle.avgpool_bwd(dy, shape, win, mult=mult), "average subsampling updater backward")
     assert not u.is_backward_data_dependent_on_input_buffer() and not u.is_backward_data_dependent_on_output_buffer()
+
+
+@pytest.mark.parametrize("kind", ["none", "vanilla", "nesterov", "adam"])
+def test_apply_gradient_for_a_batch_norm_layer(host, oracle, kind):
+    """The scheduler's optimiser step for a batch-norm layer's four chunks (gamma, beta, mean, inverse sigma): one call, one
+    launch. No chunk of a batch-norm layer is in the weight-decay set, so the decay given must not be applied."""
+    g = synth.rng(4, salt=905 + len(kind))
+    c = 96
+    mtype = {"none": host.NO_MOMENTUM, "vanilla": host.VANILLA_MOMENTUM, "nesterov": host.NESTEROV_MOMENTUM, "adam": host.ADAM_MOMENTUM}[kind]
+    data = [synth.normal(g, (c,)) for _ in range(4)]
+    grad = [synth.normal(g, (c,), 0.0, 3.0) for _ in range(4)]
+    prev = [synth.normal(g, (c,), 0.0, 0.01) for _ in range(4)]
+    prev2 = [np.abs(synth.normal(g, (c,), 0.0, 0.1)) for _ in range(4)]
+    lrs = [0.01, 0.01, 0.1, 0.1]
+    d_data, d_grad, d_prev, d_prev2 = ([dev(a) for a in arrs] for arrs in (data, grad, prev, prev2))
+    accum = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(4)]
+    host.enqueue_apply_gradient(d_data, d_grad, lrs, d_prev if kind != "none" else None, d_prev2 if kind == "adam" else None, accum,
+                                weight_decay_part_ids=[], gradient_normalizer=1.0 / 64, weight_decay=0.01, momentum_type=mtype, momentum_val=0.9,
+                                momentum_val2=0.999, iteration_id=3)
+    for k in range(4):
+        want_acc = oracle.apply_gradient(data[k], grad[k], prev[k], prev2[k], kind, lrs[k], 1.0 / 64, 0.0, 0.9, 0.999, 3)
+        assert_bits_equal(out(d_data[k]), data[k], "chunk %d weights" % k)
+        assert not out(d_grad[k]).any()
+        assert abs(float(out(accum[k])[0]) - want_acc) <= 1e-12 * want_acc
+    with pytest.raises(host.HostLayerError):   # momentum without the previous updates
+        host.enqueue_apply_gradient(d_data, d_grad, lrs, momentum_type=host.VANILLA_MOMENTUM, momentum_val=0.9)

@@ -759,6 +759,82 @@ def test_accuracy(capi, oracle, shape, top_n):
         assert_bits_equal(host(out), oracle.accuracy_fwd(p, t, m, top_n), "top-%d accuracy" % top_n)
 
 
+@pytest.mark.parametrize("kind", ["none", "vanilla", "nesterov", "adam"])
+def test_optimiser_step_many_chunks_one_launch(capi, oracle, kind):
+    """A batch-norm layer's four chunks, a PReLU chunk, an empty chunk and a chunk that spans several CTAs, all in one call;
+    three consecutive steps. Weights and optimiser state bit for bit, the |update| sums to double rounding."""
+    g = synth.rng(1, salt=7300 + len(kind))
+    counts = [64, 64, 64, 64, 1, 0, 1000, 1024, 1025, 5000] + [7] * 50   # > 48 chunks: more than one launch
+    mtype = {"none": capi.MOMENTUM_NONE, "vanilla": capi.MOMENTUM_VANILLA, "nesterov": capi.MOMENTUM_NESTEROV, "adam": capi.MOMENTUM_ADAM}[kind]
+    hostp, devp = [], []
+    for k, n in enumerate(counts):
+        hp = {"data": synth.normal(g, (n,)), "prev_upd": synth.normal(g, (n,), 0.0, 0.01), "prev_upd2": np.abs(synth.normal(g, (n,), 0.0, 0.1)),
+              "learning_rate": 0.01 * (1 + k % 3), "weight_decay": 0.0005 if k % 2 == 0 else 0.0, "accum": 0.0}
+        dp = {"data": dev(hp["data"]), "gradient": None, "learning_rate": hp["learning_rate"], "weight_decay": hp["weight_decay"],
+              "update_accum": torch.zeros(1, dtype=torch.float64, device="cuda") if k % 4 != 3 else None}
+        if kind != "none":
+            dp["prev_upd"] = dev(hp["prev_upd"])
+        if kind == "adam":
+            dp["prev_upd2"] = dev(hp["prev_upd2"])
+        hostp.append(hp)
+        devp.append(dp)
+    for it in (1, 2, 3):
+        for hp, dp in zip(hostp, devp):
+            hp["gradient"] = synth.normal(g, hp["data"].shape, 0.0, 5.0)
+            dp["gradient"] = dev(hp["gradient"])
+        capi.apply_gradient(devp, mtype, 0.9, 0.999, 1.0 / 32, it)
+        for k, (hp, dp) in enumerate(zip(hostp, devp)):
+            hp["accum"] += oracle.apply_gradient(hp["data"], hp["gradient"], hp["prev_upd"], hp["prev_upd2"], kind, hp["learning_rate"], 1.0 / 32,
+                                                 hp["weight_decay"], 0.9, 0.999, it)
+            assert_bits_equal(host(dp["data"]), hp["data"], "%s weights, chunk %d, step %d" % (kind, k, it))
+            assert not host(dp["gradient"]).any(), "gradient is zeroed"
+            if kind != "none":
+                assert_bits_equal(host(dp["prev_upd"]), hp["prev_upd"], "%s previous update, chunk %d" % (kind, k))
+            if kind == "adam":
+                assert_bits_equal(host(dp["prev_upd2"]), hp["prev_upd2"], "%s second moment, chunk %d" % (kind, k))
+            if dp["update_accum"] is not None:
+                got = float(host(dp["update_accum"])[0])
+                assert abs(got - hp["accum"]) <= 1e-12 * abs(hp["accum"]) + 1e-300, (k, got, hp["accum"])
+    with pytest.raises(capi.NnfError):
+        capi.apply_gradient(devp[:1], capi.MOMENTUM_ADAM, 0.9, 0.999, 1.0, 0)   # ADAM counts from 1
+    with pytest.raises(capi.NnfError):
+        capi.apply_gradient([{"data": devp[0]["data"], "gradient": devp[0]["gradient"], "learning_rate": 0.1}], capi.MOMENTUM_VANILLA)
+
+
+@pytest.mark.parametrize("shape,mean,std", [((6, 5, 7, 3), 100.0, 3.0), ((16, 8, 1, 1), 0.0, 1.0), ((4, 3, 14, 14), -7.5, 0.01), ((5, 70, 28, 28), 2.0, 4.0),
+                                            ((3, 2000, 2, 2), 0.0, 1.0)])
+def test_bn_recalibration(capi, oracle, shape, mean, std):
+    """update_bn_weights on the GPU: statistics of the gamma-1 / beta-0 output over a data set fed in uneven batches, then
+    the rewrite of mean and inverse sigma. The oracle feeds the same values one by one through Welford's update."""
+    g = synth.rng(1, salt=7400 + sum(shape))
+    c = shape[1]
+    x = synth.normal(g, shape, mean, std)
+    old_mean = synth.normal(g, (c,), mean, 0.3 * std)
+    old_invsigma = (1.0 / (synth.uniform(g, (c,), 0.5, 2.0) * np.float32(std))).astype(np.float32)
+    ones, zeros = np.ones(c, np.float32), np.zeros(c, np.float32)
+    y = oracle.bn_infer(x, ones, zeros, old_mean, old_invsigma)
+    want = oracle.feature_map_stats([y])
+    want_mean, want_invsigma = oracle.bn_recalibrate(old_mean, old_invsigma, want)
+    acc = capi.bn_calibrate_accumulator(c)
+    dm, di = dev(old_mean), dev(old_invsigma)
+    cuts = [0, 1, shape[0] // 2, shape[0]] if shape[0] > 2 else [0, shape[0]]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        if b > a:
+            capi.bn_calibrate_accumulate(acc, dev(x[a:b]), dm, di)
+    stats = torch.empty((4, c), device="cuda")
+    capi.bn_calibrate_finish(acc, c, dm, di, stats)
+    got = host(stats)
+    assert_bits_equal(got[:2], want[:2], "min, max")
+    assert_close(got[2], want[2], "average", rtol=1e-6, atol=1e-7)
+    assert_close(got[3], want[3], "std_dev", rtol=1e-6, atol=0.0)
+    assert_close(host(dm), want_mean, "recalibrated mean", rtol=1e-6, atol=1e-6 * float(np.abs(want_mean).max()))
+    assert_close(host(di), want_invsigma, "recalibrated inverse sigma", rtol=2e-6, atol=0.0)
+    # after recalibration the output of the layer has zero mean and unit deviation per feature map
+    y2 = oracle.bn_infer(x, ones, zeros, host(dm), host(di))
+    check = oracle.feature_map_stats([y2])
+    assert np.abs(check[2]).max() < 1e-3 and np.abs(check[3] - 1.0).max() < 1e-3
+
+
 def test_errors_are_reported_not_thrown(capi):
     x = torch.zeros((2, 3, 4, 4), device="cuda")
     with pytest.raises(capi.NnfError) as e:

@@ -6,6 +6,7 @@ import os
 import numpy as np
 import pytest
 
+import synth
 from util import assert_bits_equal
 
 G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "plain_backend.npz"))
@@ -85,3 +86,63 @@ def test_maxpool_min(oracle):
     y, idx = oracle.maxpool_fwd(G["px"], (3, 3), (2, 2), is_min=True)
     assert_bits_equal(y, G["pool32min_y"], "min values")
     assert_bits_equal(idx, G["pool32min_idx"], "min argmax")
+
+
+def test_feature_map_statistics(oracle):
+    y = G["stat_y"]
+    assert_bits_equal(oracle.feature_map_stats([y]), G["stat_minmaxavgstd"], "per-feature-map min / max / average / std_dev")
+    assert_bits_equal(oracle.feature_map_stats([y[:1], y[1:4], y[4:]]), G["stat_minmaxavgstd"], "same, fed in three batches")
+
+
+def _np_apply_gradient(kind, w, gr, prev, prev2, lr, norm, wd, m, m2, it):
+    """The optimiser expressions of nnforge/plain/backward_propagation_plain.cpp:826-985 written with numpy float32 scalars
+    (every numpy operation rounds once, like C compiled without contraction): an independent statement of the same formulas,
+    because that file of the reference cannot be compiled here."""
+    f = np.float32
+    lr, norm, wd, m, m2 = f(lr), f(norm), f(wd), f(m), f(m2)
+    total = gr * norm - w * wd
+    if kind == "none":
+        upd = lr * total
+    elif kind == "vanilla":
+        upd = prev * m + lr * total
+        prev[...] = upd
+    elif kind == "nesterov":
+        fresh = prev * m + lr * total
+        upd = (m + f(1.0)) * fresh - m * prev
+        prev[...] = fresh
+    else:
+        import math
+        import ctypes
+        libm = ctypes.CDLL("libm.so.6")
+        libm.powf.restype = ctypes.c_float
+        libm.powf.argtypes = [ctypes.c_float, ctypes.c_float]
+        inv1 = f(1.0) / (f(1.0) - f(libm.powf(m, float(it))))
+        inv2 = f(1.0) / (f(1.0) - f(libm.powf(m2, float(it))))
+        b1 = m * prev + (f(1.0) - m) * total
+        b2 = m2 * prev2 + (f(1.0) - m2) * total * total
+        upd = lr * (b1 * inv1) / (np.sqrt(b2 * inv2) + f(1.0e-8))
+        prev[...] = b1
+        prev2[...] = b2
+    return (w + upd).astype(np.float32), float(np.sum(np.abs(upd).astype(np.float64)))
+
+
+@pytest.mark.parametrize("kind", ["none", "vanilla", "nesterov", "adam"])
+def test_optimiser_step_matches_an_independent_statement(oracle, kind):
+    g = synth.rng(81, salt=len(kind))
+    count = 301
+    w, gr = synth.normal(g, (count,)), synth.normal(g, (count,), 0.0, 5.0)
+    prev, prev2 = synth.normal(g, (count,), 0.0, 0.01), np.abs(synth.normal(g, (count,), 0.0, 0.1))
+    for it in (1, 2, 50):
+        ow, ogr, op, op2 = w.copy(), gr.copy(), prev.copy(), prev2.copy()
+        acc = oracle.apply_gradient(ow, ogr, op, op2, kind, 0.02, 1.0 / 32, 0.0005, 0.9, 0.999, it)
+        ep, ep2 = prev.copy(), prev2.copy()
+        ew, eacc = _np_apply_gradient(kind, w, gr, ep, ep2, 0.02, 1.0 / 32, 0.0005, 0.9, 0.999, it)
+        assert_bits_equal(ow, ew, kind + " weights")
+        assert not ogr.any()
+        if kind != "none":
+            assert_bits_equal(op, ep, kind + " previous update")
+        if kind == "adam":
+            assert_bits_equal(op2, ep2, kind + " second moment")
+        assert abs(acc - eacc) <= 1e-12 * abs(eacc)
+        w, prev, prev2 = ow, op, op2
+        gr = synth.normal(g, (count,), 0.0, 5.0)

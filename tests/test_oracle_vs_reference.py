@@ -118,3 +118,15 @@ def test_maxpool(oracle, reference, hw, win, stride):
     y, idx = oracle.maxpool_fwd(x, win, stride)
     dy = synth.normal(g, y.shape)
     assert_bits_equal(oracle.maxpool_bwd(dy, idx, x.shape), reference.maxpool_bwd(dy, idx, x.shape)[0], "pool bwd")
+
+
+@pytest.mark.parametrize("shape,mean,std", [((6, 5, 7, 3), 100.0, 3.0), ((3, 8, 1, 1), 0.0, 1.0), ((2, 3, 14, 14), -7.5, 0.01), ((1, 4, 5, 5), 0.0, 1000.0)])
+def test_feature_map_statistics(oracle, reference, shape, mean, std):
+    """stat_data_bunch_writer: Welford's update value by value in double; the restatement must give the same bits however the
+    entries are cut into batches."""
+    g = synth.rng(56, salt=sum(shape))
+    y = synth.normal(g, shape, mean, std)
+    expect = reference.feature_map_stats(y)
+    assert_bits_equal(oracle.feature_map_stats([y]), expect, "statistics, one batch")
+    if shape[0] > 2:
+        assert_bits_equal(oracle.feature_map_stats([y[:1], y[1:]]), expect, "statistics, two batches")
