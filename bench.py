@@ -314,6 +314,21 @@ def run_sweep(args):
         report(3, "bn+add+relu+global avgpool bwd N=1024 C=%d %dx%d" % (c, hw, hw),
                timeit(lambda i: capi.bn_add_relu_avgpool_bwd(dx, dr, dpo, z, bn[0], bn[3], 0.0, (hw, hw), mult), 1), 12 * e)
         del x, r, z, pooled, dpo, dx, dr
+    # training batch norm + ReLU on the last stage's 7x7 planes (not whole float4s: the channel-group kernels)
+    for n, c, hw in [(1024, 512, 7), (256, 2048, 7)]:
+        shape = (n, c, hw, hw)
+        e = n * c * hw * hw
+        x, dy = torch.randn(shape, device="cuda"), torch.randn(shape, device="cuda")
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        gamma, beta = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda") * 0.1
+        saved, sums, bsums = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+        ws = torch.empty(capi.bn_train_workspace_bytes(n, c, hw * hw), dtype=torch.uint8, device="cuda")
+        acts = [capi.relu(0.0)]
+        report(3, "bn_train+relu fwd N=%d C=%d %dx%d, one launch (channel-group items)" % (n, c, hw, hw),
+               timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, gamma, beta, 1e-5, acts, workspace=ws), 1), 8 * e)
+        report(3, "bn_train+relu bwd N=%d C=%d %dx%d, one launch (channel-group items)" % (n, c, hw, hw),
+               timeit(lambda i: capi.bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts, workspace=ws), 1), 12 * e)
+        del x, dy, y, dx
     # config 4: inference BN + TanH / Sigmoid bandwidth sweep
     sizes = [128, 1024, 4096] + ([8192] if args.sweep_full else [])
     for n in sizes:

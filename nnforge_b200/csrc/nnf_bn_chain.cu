@@ -69,6 +69,9 @@ namespace nnf
 			float entry_count;
 			act_chain chain;
 			uint32_t n, c, hw;
+			uint32_t units;              // what the items are numbered by: channels, or channel groups (grouped kernel)
+			uint32_t group, groups;      // grouped kernel: channels per group, number of groups
+			fastdiv d_hw;
 			uint32_t split_s, entries_s; // S items per channel, entries per S item
 			uint32_t split_a, entries_a; // the same for A items
 			uint32_t chunk;              // channels per chunk
@@ -167,7 +170,7 @@ namespace nnf
 				if (k < p.nchunks)
 				{
 					const uint32_t c0 = k * p.chunk;
-					const uint32_t cc = min(p.chunk, p.c - c0);
+					const uint32_t cc = min(p.chunk, p.units - c0);
 					const uint32_t items = cc * p.split_s;
 					if (t - start < items)
 					{
@@ -183,7 +186,7 @@ namespace nnf
 				if (k >= p.lag)
 				{
 					const uint32_t c0 = (k - p.lag) * p.chunk;
-					const uint32_t cc = min(p.chunk, p.c - c0);
+					const uint32_t cc = min(p.chunk, p.units - c0);
 					const uint32_t items = cc * p.split_a;
 					if (t - start < items)
 					{
@@ -612,6 +615,369 @@ namespace nnf
 			}
 		}
 
+		// ---- the same single launch for planes that are not whole float4s (7x7, 13x13) ----------------------------
+		// Items are numbered by channel GROUP: 4 / gcd(H*W, 4) adjacent channels of one entry form an aligned run of
+		// whole vectors, a group is as many of those as fill the CTA's 256 vector lanes (20 channels for 7x7). A thread
+		// owns one vector position of the group's run in every entry of its item, so the channels of its four
+		// elements and their constants are loop invariants; an S item sums per position and folds the positions per
+		// channel through shared memory, an A item folds the S items' partial sums of all the group's channels.
+		constexpr int kChainGroupRun = 1024;       // floats of a group's run in one entry (one vector per thread)
+		constexpr int kChainGroupChannels = 256;
+
+		template <int A0, int A1, bool BWD>
+		__global__ void __launch_bounds__(kChainThreads, 4) bn_train_chain_grouped_kernel(const chain_params p)
+		{
+			constexpr int K = BWD ? 3 : 2;
+			constexpr int U = BWD ? 2 : 4;              // entries in flight per thread and tensor
+			constexpr int NC = BWD ? 6 : 2;             // per-channel constants an A item derives
+			constexpr uint32_t kLanes = 8;              // lanes that share a channel when sums are folded
+			__shared__ float s_pos[K][kChainGroupRun];
+			__shared__ float s_const[NC][kChainGroupChannels];
+			__shared__ uint32_t s_item[4];
+
+			if (threadIdx.x == 0)
+			{
+				const uint32_t t = atomicAdd(p.ticket, 1u);
+				uint32_t apply, unit, sp;
+				decode_ticket(p, t, apply, unit, sp);
+				s_item[0] = apply;
+				s_item[1] = unit;
+				s_item[2] = sp;
+				s_item[3] = 1;
+			}
+			__syncthreads();
+			const uint32_t apply = s_item[0], grp = BWD ? p.groups - 1 - s_item[1] : s_item[1], sp = s_item[2];
+			if (apply > 1)
+				return;
+			const uint32_t ch0 = grp * p.group;
+			const uint32_t channels = min(p.group, p.c - ch0);
+			const uint32_t run = channels * p.hw;
+			const uint32_t v = threadIdx.x;
+			const bool active = v < (run >> 2);
+			const size_t stride4 = (size_t(p.c) * p.hw) >> 2;
+			const uint32_t lane = threadIdx.x % kLanes;
+			// channel (within the group) of each of this thread's four elements
+			uint32_t local[4];
+			#pragma unroll
+			for (int j = 0; j < 4; ++j)
+				local[j] = p.d_hw.div(min(v * 4 + j, run - 1));
+
+			if (!apply)
+			{
+				// ---- S item --------------------------------------------------------------------------
+				const uint32_t e0 = sp * p.entries_s;
+				const uint32_t e1 = min(e0 + p.entries_s, p.n);
+				const size_t base4 = (((size_t(e0) * p.c + ch0) * p.hw) >> 2) + v;
+				float acc[K][4];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+						acc[k][j] = 0.0F;
+				if constexpr (!BWD)
+				{
+					const float4 * bx = reinterpret_cast<const float4 *>(p.x) + base4;
+					for (uint32_t e = e0; e < e1; e += U)
+					{
+						float4 a[U];
+						#pragma unroll
+						for (int u = 0; u < U; ++u)
+						{
+							a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (active && e + u < e1)
+								a[u] = __ldg(bx + size_t(e + u - e0) * stride4); // default policy: stays in L2
+						}
+						#pragma unroll
+						for (int u = 0; u < U; ++u)
+						{
+							acc[0][0] += a[u].x; acc[0][1] += a[u].y; acc[0][2] += a[u].z; acc[0][3] += a[u].w;
+							acc[1][0] = fmaf(a[u].x, a[u].x, acc[1][0]); acc[1][1] = fmaf(a[u].y, a[u].y, acc[1][1]);
+							acc[1][2] = fmaf(a[u].z, a[u].z, acc[1][2]); acc[1][3] = fmaf(a[u].w, a[u].w, acc[1][3]);
+						}
+					}
+				}
+				else
+				{
+					float mean[4], invstd[4], mult[4], add[4], slope[4];
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+					{
+						const uint32_t ch = ch0 + local[j];
+						mean[j] = __ldg(p.saved + ch);
+						invstd[j] = __ldg(p.saved + p.c + ch);
+						mult[j] = __fmul_rn(__ldg(p.gamma + ch), invstd[j]);
+						add[j] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult[j], mean[j]));
+						slope[j] = chain_slope(p.chain, ch);
+					}
+					const float4 * bx = reinterpret_cast<const float4 *>(p.x) + base4;
+					const float4 * bd = reinterpret_cast<const float4 *>(p.dy) + base4;
+					for (uint32_t e = e0; e < e1; e += U)
+					{
+						float4 a[U], d[U];
+						#pragma unroll
+						for (int u = 0; u < U; ++u)
+						{
+							a[u] = d[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							if (active && e + u < e1)
+							{
+								a[u] = __ldg(bx + size_t(e + u - e0) * stride4);
+								d[u] = __ldg(bd + size_t(e + u - e0) * stride4);
+							}
+						}
+						#pragma unroll
+						for (int u = 0; u < U; ++u)
+							if (e + u < e1)
+							{
+								const float xs[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+								const float ds[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+								#pragma unroll
+								for (int j = 0; j < 4; ++j)
+								{
+									const float uu = __fadd_rn(__fmul_rn(xs[j], mult[j]), add[j]);
+									float term;
+									const float du = chain_backward<A0, A1>(p.chain, uu, ds[j], slope[j], term);
+									const float xhat = __fmul_rn(__fsub_rn(xs[j], mean[j]), invstd[j]);
+									acc[0][j] += du;
+									acc[1][j] = fmaf(du, xhat, acc[1][j]);
+									acc[2][j] += term;
+								}
+							}
+					}
+				}
+				if (active)
+				{
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						#pragma unroll
+						for (int j = 0; j < 4; ++j)
+							s_pos[k][v * 4 + j] = acc[k][j];
+				}
+				__syncthreads();
+				// positions -> channels: eight lanes per channel, every eighth position each, then a butterfly
+				for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
+				{
+					const uint32_t lc = first + threadIdx.x / kLanes;
+					double t[K];
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						t[k] = 0.0;
+					if (lc < channels)
+						for (uint32_t i = lane; i < p.hw; i += kLanes)
+						{
+							#pragma unroll
+							for (int k = 0; k < K; ++k)
+								t[k] += double(s_pos[k][lc * p.hw + i]);
+						}
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+					{
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 4);
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 2);
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 1);
+					}
+					if (lc < channels && lane == 0)
+					{
+						double * out = p.partial + (size_t(ch0 + lc) * p.split_s + sp) * 3;
+						#pragma unroll
+						for (int k = 0; k < K; ++k)
+							out[k] = t[k];
+						__threadfence(); // the partial sums are visible before the count
+					}
+				}
+				__syncthreads();
+				if (threadIdx.x == 0)
+				{
+					__threadfence(); // every partial sum of this item, whichever thread wrote it, comes before the count
+					atomicAdd(p.done + grp, 1u);
+				}
+				return;
+			}
+
+			// ---- A item ------------------------------------------------------------------------------
+			const uint32_t e0 = sp * p.entries_a;
+			const uint32_t e1 = min(e0 + p.entries_a, p.n);
+			const size_t base4 = (((size_t(e0) * p.c + ch0) * p.hw) >> 2) + v;
+			const float4 * bx = reinterpret_cast<const float4 *>(p.x) + base4;
+			const float4 * bd = reinterpret_cast<const float4 *>(BWD ? p.dy : p.x) + base4;
+			float4 * bo = reinterpret_cast<float4 *>(p.out) + base4;
+			float4 a[U];
+			float4 d[BWD ? U : 1];
+			auto load_batch = [&](uint32_t e)
+			{
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					if (active && e + u < e1)
+					{
+						a[u] = ld_stream(bx + size_t(e + u - e0) * stride4);
+						if (BWD)
+							d[u] = ld_stream(bd + size_t(e + u - e0) * stride4);
+					}
+			};
+			// the first loads do not depend on the statistics: they are in flight while the item waits
+			load_batch(e0);
+			if (threadIdx.x == 0)
+			{
+				bool ready = false;
+				for (uint32_t round = 0; round < kChainPollLimit; ++round)
+				{
+					if (ld_acquire(p.done + grp) >= p.split_s)
+					{
+						ready = true;
+						break;
+					}
+					__nanosleep(200);
+				}
+				if (!ready && p.error)
+					*p.error = 4;
+			}
+			__syncthreads();
+			// the S items' partial sums of every channel of the group, in slice order: eight lanes per channel
+			for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
+			{
+				const uint32_t lc = first + threadIdx.x / kLanes;
+				const uint32_t ch = ch0 + lc;
+				double t[K];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					t[k] = 0.0;
+				if (lc < channels)
+					for (uint32_t q = lane; q < p.split_s; q += kLanes)
+					{
+						#pragma unroll
+						for (int k = 0; k < K; ++k)
+							t[k] += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
+					}
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+				{
+					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 4);
+					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 2);
+					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 1);
+				}
+				if (lc < channels && lane == 0)
+				{
+					if constexpr (!BWD)
+					{
+						const double m = t[0] / p.count;
+						double var = t[1] / p.count - m * m;
+						var = var < 0.0 ? 0.0 : var;
+						const float fmean = float(m);
+						const float finv = float(1.0 / sqrt(var + double(p.eps)));
+						const float mult = __fmul_rn(__ldg(p.gamma + ch), finv);
+						s_const[0][lc] = mult;
+						s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, fmean));
+						if (sp == 0)
+						{
+							p.saved[ch] = fmean;
+							p.saved[p.c + ch] = finv;
+							if (p.sums)
+							{
+								p.sums[ch] = float(t[0]);
+								p.sums[p.c + ch] = float(t[1]);
+							}
+						}
+					}
+					else
+					{
+						const float fb = float(t[0]), fg = float(t[1]), fs = float(t[K - 1]);
+						const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+						const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+						s_const[0][lc] = mult;
+						s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+						s_const[NC - 4][lc] = mean;
+						s_const[NC - 3][lc] = invstd;
+						// the same float-rounded sums the two-kernel form passes between its kernels
+						s_const[NC - 2][lc] = float(double(fb) / p.count);
+						s_const[NC - 1][lc] = float(double(fg) / p.count);
+						if (sp == 0)
+						{
+							if (p.sums)
+							{
+								p.sums[ch] = fb;
+								p.sums[p.c + ch] = fg;
+								p.sums[2 * p.c + ch] = fs;
+							}
+							// per-channel gradients accumulate (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+							if (p.grad_beta) p.grad_beta[ch] += fb;
+							if (p.grad_gamma) p.grad_gamma[ch] += fg;
+							if (p.grad_slope) p.grad_slope[ch] += fs;
+							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+						}
+					}
+				}
+			}
+			__syncthreads();
+			if (!active || e0 >= e1)
+				return;
+			float mult[4], add[4], slope[4];
+			#pragma unroll
+			for (int j = 0; j < 4; ++j)
+			{
+				mult[j] = s_const[0][local[j]];
+				add[j] = s_const[1][local[j]];
+				slope[j] = chain_slope(p.chain, ch0 + local[j]);
+			}
+			if constexpr (!BWD)
+			{
+				for (uint32_t e = e0; ; )
+				{
+					#pragma unroll
+					for (int u = 0; u < U; ++u)
+						if (e + u < e1)
+						{
+							float4 o;
+							o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].x, mult[0]), add[0]), slope[0]);
+							o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult[1]), add[1]), slope[1]);
+							o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult[2]), add[2]), slope[2]);
+							o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult[3]), add[3]), slope[3]);
+							st_stream(bo + size_t(e + u - e0) * stride4, o);
+						}
+					e += U;
+					if (e >= e1)
+						break;
+					load_batch(e);
+				}
+			}
+			else
+			{
+				float mean[4], invstd[4], c2[4], c3[4];
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+				{
+					mean[j] = s_const[NC - 4][local[j]];
+					invstd[j] = s_const[NC - 3][local[j]];
+					c2[j] = s_const[NC - 2][local[j]];
+					c3[j] = s_const[NC - 1][local[j]];
+				}
+				for (uint32_t e = e0; ; )
+				{
+					#pragma unroll
+					for (int u = 0; u < U; ++u)
+						if (e + u < e1)
+						{
+							const float xs[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+							const float ds[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+							float rs[4];
+							#pragma unroll
+							for (int j = 0; j < 4; ++j)
+							{
+								const float uu = __fadd_rn(__fmul_rn(xs[j], mult[j]), add[j]);
+								float term;
+								const float du = chain_backward<A0, A1>(p.chain, uu, ds[j], slope[j], term);
+								const float xhat = __fmul_rn(__fsub_rn(xs[j], mean[j]), invstd[j]);
+								rs[j] = mult[j] * ((du - c2[j]) - xhat * c3[j]);
+							}
+							st_stream(bo + size_t(e + u - e0) * stride4, make_float4(rs[0], rs[1], rs[2], rs[3]));
+						}
+					e += U;
+					if (e >= e1)
+						break;
+					load_batch(e);
+				}
+			}
+		}
+
 		int chain_env(const char * name, int fallback)
 		{
 			const char * v = getenv(name);
@@ -661,7 +1027,64 @@ namespace nnf
 				return false;
 			p.total_items = (uint32_t)items;
 			p.n = (uint32_t)n; p.c = (uint32_t)c; p.hw = (uint32_t)hw;
+			p.units = p.c;
 			p.d_vpp = fastdiv((uint32_t)(hw / 4));
+			p.d_split_s = fastdiv(p.split_s);
+			p.d_split_a = fastdiv(p.split_a);
+			p.count = double(n) * double(hw);
+			return true;
+		}
+
+		// The grouped kernel's plan: items are channel groups. Returns false where the shape does not suit it (planes
+		// of whole float4s take the kernel above; runs shorter than 16 vectors or longer than 256 the separate kernels).
+		bool plan_chain_grouped(chain_params& p, int64_t n, int64_t c, int64_t hw)
+		{
+			if (hw % 4 == 0 || n < 1 || c < 1 || n >= (int64_t(1) << 31) || c >= (int64_t(1) << 24) || getenv("NNF_NO_GROUPED_CHAIN"))
+				return false;
+			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
+			const int64_t vpu = unit * hw / 4;
+			if (c % unit != 0 || vpu > kChainThreads)
+				return false;
+			int64_t group = unit * (kChainThreads / vpu);
+			if (group > c) group = c;
+			if (group > kChainGroupChannels) group = kChainGroupChannels;
+			if (group * hw / 4 < 16)
+				return false;
+			const int64_t groups = div_up(c, group);
+			const int64_t run_bytes = group * hw * 4;
+			const int64_t s_bytes = int64_t(chain_env("NNF_CHAIN_S_KB", 48)) * 1024;
+			const int64_t a_bytes = int64_t(chain_env("NNF_CHAIN_A_KB", 64)) * 1024;
+			int64_t es = s_bytes / run_bytes, ea = a_bytes / run_bytes;
+			if (es < 1) es = 1;
+			if (ea < 1) ea = 1;
+			if (es > n) es = n;
+			if (ea > n) ea = n;
+			if (div_up(n, es) > kChainMaxSplit)
+				es = div_up(n, kChainMaxSplit);
+			if (div_up(n, ea) > 4096)
+				ea = div_up(n, 4096);
+			p.entries_s = (uint32_t)es;
+			p.split_s = (uint32_t)div_up(n, es);
+			p.entries_a = (uint32_t)ea;
+			p.split_a = (uint32_t)div_up(n, ea);
+			const double group_bytes = double(n) * double(run_bytes);
+			int64_t chunk = (int64_t)(double(chain_env("NNF_CHAIN_CHUNK_MB", 16)) * 1024.0 * 1024.0 / group_bytes);
+			if (chunk < 1) chunk = 1;
+			if (chunk < div_up(groups, 64)) chunk = div_up(groups, 64);
+			if (chunk > groups) chunk = groups;
+			p.chunk = (uint32_t)chunk;
+			p.nchunks = (uint32_t)div_up(groups, chunk);
+			int lag = chain_env("NNF_CHAIN_LAG", 1);
+			p.lag = (uint32_t)(lag < 0 ? 0 : lag);
+			const int64_t items = groups * (int64_t(p.split_s) + int64_t(p.split_a));
+			if (items >= (int64_t(1) << 31))
+				return false;
+			p.total_items = (uint32_t)items;
+			p.n = (uint32_t)n; p.c = (uint32_t)c; p.hw = (uint32_t)hw;
+			p.units = (uint32_t)groups;
+			p.group = (uint32_t)group;
+			p.groups = (uint32_t)groups;
+			p.d_hw = fastdiv((uint32_t)hw);
 			p.d_split_s = fastdiv(p.split_s);
 			p.d_split_a = fastdiv(p.split_a);
 			p.count = double(n) * double(hw);
@@ -729,13 +1152,27 @@ namespace nnf
 			float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
 		{
 			chain_params p = {};
-			if (!aligned16(x) || !aligned16(y) || !plan_chain(p, n, c, hw, 1))
+			if (!aligned16(x) || !aligned16(y))
+				return 1;
+			const bool grouped = !PEER && plan_chain_grouped(p, n, c, hw);
+			if (!grouped && !plan_chain(p, n, c, hw, 1))
 				return 1;
 			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
 				return 1;
 			p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
 			p.chain = chain;
 			p.eps = eps;
+			if (grouped)
+			{
+				const char * what = "bn_train_chain_grouped_kernel (forward)";
+				switch (chain_id(chain))
+				{
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, false>, p, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false>, p, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, false>, p, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, false>, p, workspace, stream, what);
+				}
+			}
 			const int st = fill_peer(p, peer, "bn_train_chain_kernel (forward)");
 			if (st != NNF_OK)
 				return st;
@@ -758,7 +1195,10 @@ namespace nnf
 			int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
 		{
 			chain_params p = {};
-			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !plan_chain(p, n, c, hw, 2))
+			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx))
+				return 1;
+			const bool grouped = !PEER && plan_chain_grouped(p, n, c, hw);
+			if (!grouped && !plan_chain(p, n, c, hw, 2))
 				return 1;
 			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
 				return 1;
@@ -766,6 +1206,17 @@ namespace nnf
 			p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
 			p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 			p.chain = chain;
+			if (grouped)
+			{
+				const char * what = "bn_train_chain_grouped_kernel (backward)";
+				switch (chain_id(chain))
+				{
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, true>, p, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true>, p, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, true>, p, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, true>, p, workspace, stream, what);
+				}
+			}
 			const int st = fill_peer(p, peer, "bn_train_chain_kernel (backward)");
 			if (st != NNF_OK)
 				return st;

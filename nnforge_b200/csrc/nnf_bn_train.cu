@@ -612,7 +612,8 @@ namespace nnf
 			g.group = (uint32_t)group;
 			g.groups = (uint32_t)div_up(c, group);
 			g.vectors_per_thread = r;
-			int64_t split = (int64_t(kSmCount) * 8) / g.groups;
+			const int64_t waves = getenv("NNF_GROUP_WAVES") ? atoi(getenv("NNF_GROUP_WAVES")) : 1;   // tuning aid
+			int64_t split = div_up(int64_t(kSmCount) * 8 * waves, g.groups);
 			if (split > n / 4) split = n / 4;
 			if (split > kMaxSplit) split = kMaxSplit;
 			if (split < 1) split = 1;
@@ -629,11 +630,14 @@ namespace nnf
 			size_t base4;              // float4 offset of the group's run in entry e0
 		};
 
-		__device__ __forceinline__ group_cta group_locate(const group_geom& g)
+		// descending: the groups are walked downwards (a kernel that follows one that walked upwards finds the data
+		// that kernel touched last, up to the size of L2, still cached)
+		__device__ __forceinline__ group_cta group_locate(const group_geom& g, bool descending = false)
 		{
 			group_cta t;
-			const uint32_t grp = blockIdx.x / g.split;
-			t.sp = blockIdx.x - grp * g.split;
+			const uint32_t walk = blockIdx.x / g.split;
+			const uint32_t grp = descending ? g.groups - 1 - walk : walk;
+			t.sp = blockIdx.x - walk * g.split;
 			t.ch0 = grp * g.group;
 			t.channels = min(g.group, g.c - t.ch0);
 			t.vectors = (t.channels * g.hw) >> 2;
@@ -644,26 +648,41 @@ namespace nnf
 			return t;
 		}
 
-		// per-channel sum of K position arrays held in shared memory -> this CTA's partials
+		// per-channel sum of K position arrays held in shared memory -> this CTA's partials. Eight lanes share a
+		// channel: each sums every eighth position in double, a three-step butterfly joins them (a fixed order).
 		template <int K>
 		__device__ __forceinline__ void group_fold(double * partial, const float (*s_pos)[kGroupMaxRun], const group_geom& g, const group_cta& t)
 		{
-			for (uint32_t ch = threadIdx.x; ch < t.channels; ch += kThreads)
+			constexpr uint32_t kLanes = 8;
+			const uint32_t lane = threadIdx.x % kLanes;
+			for (uint32_t first = 0; first < t.channels; first += kThreads / kLanes)
 			{
+				const uint32_t ch = first + threadIdx.x / kLanes;
 				double acc[K];
 				#pragma unroll
 				for (int k = 0; k < K; ++k)
 					acc[k] = 0.0;
-				for (uint32_t i = 0; i < g.hw; ++i)
-				{
-					#pragma unroll
-					for (int k = 0; k < K; ++k)
-						acc[k] += double(s_pos[k][ch * g.hw + i]);
-				}
-				double * out = partial + (size_t(t.ch0 + ch) * g.split + t.sp) * kSums;
+				if (ch < t.channels)
+					for (uint32_t i = lane; i < g.hw; i += kLanes)
+					{
+						#pragma unroll
+						for (int k = 0; k < K; ++k)
+							acc[k] += double(s_pos[k][ch * g.hw + i]);
+					}
 				#pragma unroll
 				for (int k = 0; k < K; ++k)
-					out[k] = acc[k];
+				{
+					acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 4);
+					acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 2);
+					acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 1);
+				}
+				if (ch < t.channels && lane == 0)
+				{
+					double * out = partial + (size_t(t.ch0 + ch) * g.split + t.sp) * kSums;
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						out[k] = acc[k];
+				}
 			}
 		}
 
@@ -758,7 +777,7 @@ namespace nnf
 		{
 			__shared__ float s_pos[3][kGroupMaxRun];
 			constexpr int U = 2;
-			const group_cta t = group_locate(g);
+			const group_cta t = group_locate(g, true);
 			group_elem k[R][4];
 			group_constants<R>(k, p, g, t, false);
 			float sb[R][4], sg[R][4], ss[R][4];
@@ -906,7 +925,7 @@ namespace nnf
 		{
 			__shared__ float s_mult[kGroupMaxChannels], s_add[kGroupMaxChannels];
 			constexpr int U = 4;
-			const group_cta t = group_locate(g);
+			const group_cta t = group_locate(g, true);
 			for (uint32_t i = threadIdx.x; i < t.channels; i += kThreads)
 			{
 				const uint32_t ch = t.ch0 + i;

@@ -51,7 +51,8 @@ COMMON = ["-std=c++11", "-O2", "-fPIC", "-ffp-contract=off", "-include", "algori
 
 
 def reference_dir():
-    root = os.environ.get("NNFORGE_REFERENCE_DIR", "/root/reference")
+    # default: a checkout named "reference" beside this repository
+    root = os.environ.get("NNFORGE_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(HERE))), "reference"))
     src = os.path.join(root, "nnforge")
     return src if os.path.isdir(os.path.join(src, "plain")) else None
 

@@ -443,6 +443,14 @@ def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
     ((37, 3, 8, 8), 1, 1, 0, 0),         # no lag: an apply item may start before its statistics are done
     ((600, 2, 8, 8), 1, 1, 1, 1),        # more entries than statistics items allowed per channel
     ((2, 300, 12, 12), 96, 32, 0, 2),    # many channels, one per chunk capped to 64 chunks
+    # planes that are not whole float4s: items are channel groups (units of 4 channels for odd planes, 2 for even)
+    ((33, 48, 7, 7), 48, 64, 16, 1),     # 7x7: groups of 20 channels and a tail group of 8
+    ((33, 48, 7, 7), 4, 4, 0, 1),        # one entry per item, one group per chunk
+    ((9, 8, 9, 7), 13, 7, 0, 3),         # a single group smaller than the lanes, lag of three chunks
+    ((70, 12, 13, 13), 1, 1, 0, 0),      # 13x13: one unit per group; no lag
+    ((600, 8, 3, 3), 1, 1, 1, 1),        # more entries than statistics items allowed per group
+    ((5, 300, 5, 2), 96, 32, 0, 2),      # even plane of 10: units of 2 channels, many groups
+    ((6, 6, 3, 5), 48, 64, 16, 1),       # channels not a multiple of the unit: falls back to the separate kernels
 ])
 def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chunk_mb, lag, monkeypatch):
     """The single-launch statistics/apply kernel over item sizes, chunk sizes and lags."""
