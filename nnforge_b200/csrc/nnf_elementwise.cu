@@ -76,6 +76,41 @@ namespace nnf
 			return q;
 		}
 
+		// the per-channel parameters of one channel
+		__device__ __forceinline__ elem_params fetch_channel(const ew_params& p, const float * s_mult, const float * s_add, uint32_t channel)
+		{
+			elem_params q;
+			q.mult = 1.0F; q.add = 0.0F; q.slope = 0.0F; q.bias = 0.0F;
+			if (p.gamma)
+			{
+				if (p.smem_params)
+				{
+					q.mult = s_mult[channel];
+					q.add = s_add[channel];
+				}
+				else
+				{
+					q.mult = __fmul_rn(__ldg(p.gamma + channel), __ldg(p.invsigma + channel));
+					q.add = __fsub_rn(__ldg(p.beta + channel), __fmul_rn(q.mult, __ldg(p.mean + channel)));
+				}
+			}
+			if (p.slope)
+				q.slope = __ldg(p.slope + channel);
+			if (p.bias)
+				q.bias = __ldg(p.bias + channel);
+			return q;
+		}
+
+		__device__ __forceinline__ elem_params select_params(bool second, const elem_params& a, const elem_params& b)
+		{
+			elem_params q;
+			q.mult = second ? b.mult : a.mult;
+			q.add = second ? b.add : a.add;
+			q.slope = second ? b.slope : a.slope;
+			q.bias = second ? b.bias : a.bias;
+			return q;
+		}
+
 		// One element: batch norm -> residual add -> activations, in the plain backend's operation order.
 		template <int A0, int A1>
 		__device__ __forceinline__ float ew_element(const ew_params& p, bool has_bn, bool has_res, const elem_params& q, float x, float r)
@@ -101,7 +136,41 @@ namespace nnf
 			float * s_add = s_params + p.c;
 			const bool has_bn = p.gamma != nullptr;
 			const bool has_res = p.res != nullptr;
-			if (has_bn && p.smem_params)
+			if (has_bn && p.smem_params && !p.sums)
+			{
+				// running statistics: four channels per thread in flight (the table is filled once per CTA, and with
+				// thousands of channels a chain of dependent loads per channel would cost microseconds)
+				for (uint32_t ch0 = threadIdx.x; ch0 < p.c; ch0 += kThreads * 4)
+				{
+					float g[4], b[4], m[4], is[4];
+					#pragma unroll
+					for (int u = 0; u < 4; ++u)
+					{
+						const uint32_t ch = ch0 + u * kThreads;
+						if (ch < p.c)
+						{
+							g[u] = __ldg(p.gamma + ch);
+							b[u] = __ldg(p.beta + ch);
+							m[u] = __ldg(p.mean + ch);
+							is[u] = __ldg(p.invsigma + ch);
+						}
+					}
+					#pragma unroll
+					for (int u = 0; u < 4; ++u)
+					{
+						const uint32_t ch = ch0 + u * kThreads;
+						if (ch < p.c)
+						{
+							// batch_norm_layer_tester_plain.cpp:60-61
+							const float mult = __fmul_rn(g[u], is[u]);
+							s_mult[ch] = mult;
+							s_add[ch] = __fsub_rn(b[u], __fmul_rn(mult, m[u]));
+						}
+					}
+				}
+				__syncthreads();
+			}
+			else if (has_bn && p.smem_params)
 			{
 				for (uint32_t ch = threadIdx.x; ch < p.c; ch += kThreads)
 				{
@@ -184,12 +253,42 @@ namespace nnf
 							o.z = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].z, rv[j].z);
 							o.w = ew_element<A0, A1>(p, has_bn, has_res, q, xv[j].w, rv[j].w);
 						}
+						else if (p.hw.d >= 4)
+						{
+							// planes of at least four elements that are not whole vectors: a vector touches at most two
+							// channels, so plane and channel are derived once per vector (two divisions instead of eight)
+							// and the parameters of the vector's first channel and of the next are selected per element
+							const uint32_t plane = p.hw.div(e);
+							const uint32_t left = (plane + 1) * p.hw.d - e;   // elements of the vector's first plane from e on (>= 1)
+							const uint32_t channel = plane - p.cdiv.div(plane) * p.c;
+							const elem_params qa = fetch_channel(p, s_mult, s_add, channel);
+							const elem_params qb = fetch_channel(p, s_mult, s_add, channel + 1 == p.c ? 0 : channel + 1);
+							o.x = ew_element<A0, A1>(p, has_bn, has_res, qa, xv[j].x, rv[j].x);
+							o.y = ew_element<A0, A1>(p, has_bn, has_res, select_params(left <= 1, qa, qb), xv[j].y, rv[j].y);
+							o.z = ew_element<A0, A1>(p, has_bn, has_res, select_params(left <= 2, qa, qb), xv[j].z, rv[j].z);
+							o.w = ew_element<A0, A1>(p, has_bn, has_res, select_params(left <= 3, qa, qb), xv[j].w, rv[j].w);
+						}
 						else
 						{
-							o.x = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e), xv[j].x, rv[j].x);
-							o.y = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 1), xv[j].y, rv[j].y);
-							o.z = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 2), xv[j].z, rv[j].z);
-							o.w = ew_element<A0, A1>(p, has_bn, has_res, fetch_params(p, s_mult, s_add, e + 3), xv[j].w, rv[j].w);
+							// planes of one to three elements (fully connected shapes): the channel advances inside the vector
+							const uint32_t plane = p.hw.div(e);
+							uint32_t pos = e - plane * p.hw.d;
+							uint32_t channel = plane - p.cdiv.div(plane) * p.c;
+							auto advance = [&]()
+							{
+								if (++pos == p.hw.d)
+								{
+									pos = 0;
+									channel = channel + 1 == p.c ? 0 : channel + 1;
+								}
+							};
+							o.x = ew_element<A0, A1>(p, has_bn, has_res, fetch_channel(p, s_mult, s_add, channel), xv[j].x, rv[j].x);
+							advance();
+							o.y = ew_element<A0, A1>(p, has_bn, has_res, fetch_channel(p, s_mult, s_add, channel), xv[j].y, rv[j].y);
+							advance();
+							o.z = ew_element<A0, A1>(p, has_bn, has_res, fetch_channel(p, s_mult, s_add, channel), xv[j].z, rv[j].z);
+							advance();
+							o.w = ew_element<A0, A1>(p, has_bn, has_res, fetch_channel(p, s_mult, s_add, channel), xv[j].w, rv[j].w);
 						}
 						st_stream(y4 + v, o);
 					}
