@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libnnf_b200.so")
 HOST_LIB = os.path.join(HERE, "libnnf_b200_host.so")
 HOST_SRC = os.path.join(CSRC, "host", "nnf_layers.cpp")
 HOST_SOURCES = [HOST_SRC, os.path.join(CSRC, "host", "nnf_fusion.cpp")]
-SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_loss.cu", "nnf_maxpool.cu", "nnf_avgpool.cu", "nnf_optimizer.cu", "nnf_bn_train.cu", "nnf_bn_fused.cu", "nnf_bn_chain.cu", "nnf_bn_resident.cu", "nnf_peer.cu"]
+SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_loss.cu", "nnf_maxpool.cu", "nnf_avgpool.cu", "nnf_optimizer.cu", "nnf_bn_train.cu", "nnf_bn_fused.cu", "nnf_bn_chain.cu", "nnf_peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -932,13 +932,7 @@ extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, f
 		kernel = bn_train_fwd_cluster_kernel<NNF_ACT_RELU, 0>;
 
 	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(y);
-	if (fused_mode() == 4 && shape_ok)
-	{
-		st = resident_forward_launch((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes);
-		if (st != 1)
-			return st;
-	}
-	if ((fused_mode() == 0 || fused_mode() == 4) && shape_ok)
+	if (fused_mode() == 0 && shape_ok)
 	{
 		st = chain_forward_launch((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes);
 		if (st != 1)
@@ -1047,14 +1041,7 @@ extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, 
 	default: break;
 	}
 	const bool shape_ok = n <= 0x7fffffff && c <= 0x7fffffff / 8 && hw <= 0x7fffffff && n * hw < (int64_t(1) << 31) && aligned16(x) && aligned16(dy) && aligned16(dx);
-	if (fused_mode() == 4 && shape_ok && !add_to_destination)
-	{
-		st = resident_backward_launch((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
-			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes);
-		if (st != 1)
-			return st;
-	}
-	if ((fused_mode() == 0 || fused_mode() == 4) && shape_ok && !add_to_destination)
+	if (fused_mode() == 0 && shape_ok && !add_to_destination)
 	{
 		st = chain_backward_launch((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
 			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes);

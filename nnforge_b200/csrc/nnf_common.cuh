@@ -398,16 +398,6 @@ namespace nnf
 		const float * mean, const float * invsigma, float entry_count,
 		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
 
-	// single-launch training batch norm that reads its inputs once: channel pieces resident in shared memory
-	// (nnf_bn_resident.cu); same workspace; 1 = shape not suited
-	int resident_forward_launch(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
-		float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
-	int resident_backward_launch(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
-		const float * gamma, const float * beta, const float * saved, const act_chain& chain,
-		float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
-		const float * mean, const float * invsigma, float entry_count,
-		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
-
 	// ---- memory access helpers -----------------------------------------------------------------
 	// Streaming (evict-first) 128-bit accesses: every tensor on this path is touched once per kernel.
 	__device__ __forceinline__ float4 ld_stream(const float4 * p) { return __ldcs(p); }

@@ -401,12 +401,11 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1, fused=False
 
 @pytest.mark.parametrize("shape", TRAIN_SHAPES)
 @pytest.mark.parametrize("chain", TRAIN_CHAINS)
-@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2", "fused3", "fused4"])
+@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2", "fused3"])
 def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
     """shards 1/2: the split entry points with the sums added across shards on the host;
     fusedK: the single-GPU entry points with NNF_FUSED_MODE=K (single launch of statistics and apply items,
-    L2-resident cluster kernels, shared-memory slab cluster kernels, slab forward + two-kernel backward, channel pieces
-    resident in shared memory)."""
+    L2-resident cluster kernels, shared-memory slab cluster kernels, slab forward + two-kernel backward)."""
     fused = isinstance(shards, str)
     if fused:
         monkeypatch.setenv("NNF_FUSED_MODE", shards[-1])
@@ -473,39 +472,6 @@ def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chun
         assert_close(saved, saved_w, "saved mean/invstd")
         assert_close(y, y_w, "single-launch train fwd", atol=2e-6)
         assert_close(dx, dx_w, "single-launch train bwd", atol=5e-6)
-        scale = np.sqrt(x.size // c)
-        assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
-        assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
-        assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
-
-
-@pytest.mark.parametrize("shape,piece_kb", [
-    ((16, 32, 28, 28), 52),    # the default piece size: one piece per channel here
-    ((16, 32, 28, 28), 4),     # one entry per piece: 16 sibling pieces per channel wait for one another
-    ((37, 3, 8, 8), 1),        # a ragged last piece
-    ((600, 2, 8, 8), 1),       # more entries than pieces allowed per channel: larger pieces
-    ((3, 300, 12, 12), 2),     # many channels
-    ((130, 5, 56, 56), 52),    # 12.5 KB planes: four entries per piece
-])
-def test_bn_train_resident_pieces(capi, oracle, shape, piece_kb, monkeypatch):
-    """The kernel that keeps a channel's pieces in shared memory between its statistics and its apply phase, over piece
-    sizes; twice, so that counters of the first run cannot leak into the second."""
-    monkeypatch.setenv("NNF_FUSED_MODE", "4")
-    monkeypatch.setenv("NNF_RES_PIECE_KB", str(piece_kb))
-    chain = ("prelu", "elu")
-    g = synth.rng(2, salt=6100 + sum(shape) + piece_kb)
-    x = synth.normal(g, shape, 0.5, 2.0)
-    dy = synth.normal(g, shape)
-    c = shape[1]
-    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
-    slope = synth.uniform(g, c, 0.0, 0.3)
-    y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
-    for _ in range(2):
-        y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, 1e-5, 1, True)
-        assert capi.fused_error_check() == 0
-        assert_close(saved, saved_w, "saved mean/invstd")
-        assert_close(y, y_w, "resident-piece train fwd", atol=2e-6)
-        assert_close(dx, dx_w, "resident-piece train bwd", atol=5e-6)
         scale = np.sqrt(x.size // c)
         assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
         assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
