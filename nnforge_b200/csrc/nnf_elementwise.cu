@@ -306,6 +306,161 @@ namespace nnf
 			}
 		}
 
+		// ---- planes that are not whole float4s (7x7, 13x13): channel groups ---------------------------------------------
+		// The flat kernel above must find the channel of every vector by two divisions and fetch two channels'
+		// parameters per vector, and stays instruction- and latency-bound on such planes (x[1024,512,7,7] BN+ReLU: 68 % of
+		// the copy bandwidth). Here a CTA owns a group of adjacent channels (a multiple of 4 / gcd(H*W, 4), so that the
+		// group's run in one entry is aligned and a whole number of vectors; as many as fill the 256 vector lanes: 20 for
+		// 7x7) and a slice of entries; a thread owns one vector position of the run in every entry, so the parameters of
+		// its four elements are loop invariants in registers and the loop is loads, arithmetic and stores only.
+		struct ewg_geom
+		{
+			uint32_t n, group, groups, split, entries_per_cta;
+			fastdiv d_hw;
+		};
+
+		template <int A0, int A1>
+		__global__ void __launch_bounds__(kThreads) bn_act_grouped_kernel(const ew_params p, const ewg_geom g)
+		{
+			extern __shared__ float s_params[];
+			float * s_mult = s_params;
+			float * s_add = s_params + g.group;
+			constexpr int U = 4;   // entries in flight per thread and tensor
+			const bool has_bn = p.gamma != nullptr;
+			const bool has_res = p.res != nullptr;
+			const uint32_t hw = p.hw.d;
+			const uint32_t walk = blockIdx.x / g.split;
+			const uint32_t sp = blockIdx.x - walk * g.split;
+			const uint32_t ch0 = walk * g.group;
+			const uint32_t channels = min(g.group, p.c - ch0);
+			const uint32_t run = channels * hw;
+			const uint32_t v = threadIdx.x;
+			const bool active = v < (run >> 2);
+			const uint32_t e0 = sp * g.entries_per_cta;
+			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
+			if (has_bn)
+			{
+				for (uint32_t i = threadIdx.x; i < channels; i += kThreads)
+				{
+					const uint32_t ch = ch0 + i;
+					float mean, invsigma;
+					if (p.sums)
+					{
+						// batch statistics: biased variance from the (all-reduced) sum and sum of squares
+						const double m = double(__ldg(p.sums + ch)) / p.count_total;
+						double var = double(__ldg(p.sums + p.c + ch)) / p.count_total - m * m;
+						var = var < 0.0 ? 0.0 : var;
+						mean = float(m);
+						invsigma = float(1.0 / sqrt(var + double(p.eps)));
+						if (sp == 0 && p.saved)
+						{
+							p.saved[ch] = mean;
+							p.saved[p.c + ch] = invsigma;
+						}
+					}
+					else
+					{
+						mean = __ldg(p.mean + ch);
+						invsigma = __ldg(p.invsigma + ch);
+					}
+					// batch_norm_layer_tester_plain.cpp:60-61
+					const float mult = __fmul_rn(__ldg(p.gamma + ch), invsigma);
+					s_mult[i] = mult;
+					s_add[i] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+				}
+				__syncthreads();
+			}
+			if (!active || e0 >= e1)
+				return;
+			elem_params q[4];
+			#pragma unroll
+			for (int j = 0; j < 4; ++j)
+			{
+				const uint32_t local = g.d_hw.div(min(v * 4 + j, run - 1));
+				q[j].mult = has_bn ? s_mult[local] : 1.0F;
+				q[j].add = has_bn ? s_add[local] : 0.0F;
+				q[j].slope = p.slope ? __ldg(p.slope + ch0 + local) : 0.0F;
+				q[j].bias = p.bias ? __ldg(p.bias + ch0 + local) : 0.0F;
+			}
+			const size_t stride4 = (size_t(p.c) * hw) >> 2;
+			const size_t base4 = (((size_t(e0) * p.c + ch0) * hw) >> 2) + v;
+			const float4 * x4 = reinterpret_cast<const float4 *>(p.x) + base4;
+			const float4 * r4 = reinterpret_cast<const float4 *>(has_res ? p.res : p.x) + base4;
+			float4 * y4 = reinterpret_cast<float4 *>(p.y) + base4;
+			for (uint32_t e = e0; e < e1; e += U)
+			{
+				float4 xv[U], rv[U];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+				{
+					rv[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (e + u < e1)
+					{
+						xv[u] = ld_stream(x4 + size_t(e + u - e0) * stride4);
+						if (has_res)
+							rv[u] = ld_stream(r4 + size_t(e + u - e0) * stride4);
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					if (e + u < e1)
+					{
+						float4 o;
+						o.x = ew_element<A0, A1>(p, has_bn, has_res, q[0], xv[u].x, rv[u].x);
+						o.y = ew_element<A0, A1>(p, has_bn, has_res, q[1], xv[u].y, rv[u].y);
+						o.z = ew_element<A0, A1>(p, has_bn, has_res, q[2], xv[u].z, rv[u].z);
+						o.w = ew_element<A0, A1>(p, has_bn, has_res, q[3], xv[u].w, rv[u].w);
+						st_stream(y4 + size_t(e + u - e0) * stride4, o);
+					}
+			}
+		}
+
+		// false: the shape keeps the flat kernel
+		bool plan_grouped(ewg_geom& g, int64_t n, int64_t c, int64_t hw)
+		{
+			if (hw % 4 == 0 || getenv("NNF_EW_NO_GROUPED") || n < 8 || n > 0x7fffffff || c > 0x7fffffff)
+				return false;
+			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
+			const int64_t vpu = unit * hw / 4;       // vectors of one unit of channels
+			if (c % unit != 0 || vpu > kThreads)
+				return false;
+			int64_t group = unit * (kThreads / vpu);
+			if (group > c)
+				group = c;
+			if (group * hw / 4 < kThreads / 2)       // fewer than half of the lanes busy: the flat kernel does better
+				return false;
+			g.n = (uint32_t)n;
+			g.group = (uint32_t)group;
+			g.groups = (uint32_t)div_up(c, group);
+			const int64_t waves = getenv("NNF_EWG_WAVES") ? atoi(getenv("NNF_EWG_WAVES")) : 2;   // tuning aid
+			int64_t split = div_up(int64_t(kSmCount) * 8 * waves, g.groups);
+			if (split > n / 4) split = n / 4;
+			if (split < 1) split = 1;
+			g.entries_per_cta = (uint32_t)div_up(n, split);
+			g.split = (uint32_t)div_up(n, g.entries_per_cta);
+			g.d_hw = fastdiv((uint32_t)hw);
+			return true;
+		}
+
+		cudaError_t launch_grouped(const ew_params& p, const ewg_geom& g, cudaStream_t s)
+		{
+			const int k0 = p.chain.n > 0 ? p.chain.a[0].kind : NNF_ACT_NONE;
+			const int k1 = p.chain.n > 1 ? p.chain.a[1].kind : NNF_ACT_NONE;
+			const unsigned grid = g.groups * g.split;
+			const size_t smem = size_t(2) * g.group * sizeof(float);
+#define NNF_EWG_CASE(A0, A1) bn_act_grouped_kernel<A0, A1><<<grid, kThreads, smem, s>>>(p, g)
+			if (p.chain.n == 0)
+				NNF_EWG_CASE(NNF_ACT_NONE, 0);
+			else if (k0 == NNF_ACT_RELU && k1 == NNF_ACT_NONE)
+				NNF_EWG_CASE(NNF_ACT_RELU, 0);
+			else if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU)
+				NNF_EWG_CASE(NNF_ACT_PRELU, NNF_ACT_ELU);
+			else
+				NNF_EWG_CASE(-1, 0);
+#undef NNF_EWG_CASE
+			return cudaGetLastError();
+		}
+
 		// Grid: a whole number of resident waves (a grid somewhat larger than one wave would run a short second wave
 		// with most SMs idle), never more than there are tiles. Eight waves, measured on B200: CTAs that start at
 		// different times mix their loads and stores, which a single wave moving in lockstep does not (x[1024,256,14,14]
@@ -425,7 +580,10 @@ namespace nnf
 				const int mode = !vec_ok ? 2 : ((!need_channel || (hw % 4 == 0)) ? 0 : 1);
 				const int64_t work = (mode == 2) ? div_up(cnt, kThreads) : div_up(cnt / 4 + 1, kThreads * kUnroll);
 				cudaError_t e;
-				if (mode == 0)
+				ewg_geom gg;
+				if (mode == 1 && plan_grouped(gg, cnt / per_entry, c, hw))
+					e = launch_grouped(p, gg, s);
+				else if (mode == 0)
 					e = launch_mode<0>(p, work, smem, s);
 				else if (mode == 1)
 					e = launch_mode<1>(p, work, smem, s);
