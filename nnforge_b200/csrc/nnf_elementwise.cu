@@ -571,7 +571,7 @@ namespace nnf
 				p.slope = slope;
 				p.bias = bn.bias;
 				p.need_channel = need_channel ? 1 : 0;
-				p.smem_params = (gamma && c <= kMaxSmemChannels && !(getenv("NNF_EW_NO_SMEM") && !bn.sums)) ? 1 : 0;
+				p.smem_params = (gamma && c <= kMaxSmemChannels) ? 1 : 0;
 				if (bn.sums && !p.smem_params)
 					return set_error(NNF_ERR_UNSUPPORTED, "training batch norm supports at most %d channels", kMaxSmemChannels);
 				p.chain = chain;

@@ -68,7 +68,10 @@ def oracle_acts(oracle, names, v, slope):
 
 
 EXACT = {"relu0", "relu01", "prelu"}
-SHAPES = [(64, 64, 32, 32), (3, 5, 7, 7), (2, 3, 1, 1), (1, 1, 1, 1), (5, 4, 3, 2), (2, 130, 9, 5), (7, 2, 16, 4)]
+# the last five reach the channel-group kernel (planes that are not whole float4s, at least eight entries, channels a
+# multiple of 4 / gcd(H*W, 4)): 7x7 with a tail group, 5x5 in one group, 3x3, fully connected, an even plane of 10
+SHAPES = [(64, 64, 32, 32), (3, 5, 7, 7), (2, 3, 1, 1), (1, 1, 1, 1), (5, 4, 3, 2), (2, 130, 9, 5), (7, 2, 16, 4),
+          (16, 24, 7, 7), (9, 40, 5, 5), (12, 64, 3, 3), (33, 512, 1, 1), (10, 52, 5, 2)]
 CHAINS = [(), ("relu0",), ("relu01",), ("prelu",), ("elu",), ("tanh",), ("sigmoid",), ("prelu", "elu"), ("relu01", "tanh")]
 
 
@@ -98,7 +101,7 @@ def test_bn_infer_act(capi, oracle, shape, chain):
     compare(host(xd), want, chain, "in-place bn+%s %s" % (chain, shape))
 
 
-@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 1, 1)])
+@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 1, 1), (16, 24, 7, 7), (33, 512, 1, 1)])
 def test_bn_add_act_and_plain_activation(capi, oracle, shape):
     g = synth.rng(3, salt=sum(shape))
     x = synth.with_edges(g, synth.normal(g, shape))
@@ -298,7 +301,10 @@ def test_bn_add_relu_maxpool(capi, oracle, c, hw, round_up):
     assert_bits_equal(host(dx), dx_want, "fused dx")
 
 
-TRAIN_SHAPES = [(16, 32, 28, 28), (5, 3, 7, 7), (4, 6, 1, 1), (3, 2, 5, 3), (64, 8, 14, 14), (256, 40, 28, 28), (3, 5, 4, 4), (37, 3, 8, 8)]
+# the last three take the channel-group kernels (planes that are not whole float4s, channels a multiple of 4 / gcd(H*W, 4)):
+# 7x7 with a tail group, 9x7 in one group, 13x13 with two vectors per thread
+TRAIN_SHAPES = [(16, 32, 28, 28), (5, 3, 7, 7), (4, 6, 1, 1), (3, 2, 5, 3), (64, 8, 14, 14), (256, 40, 28, 28), (3, 5, 4, 4), (37, 3, 8, 8),
+                (16, 24, 7, 7), (9, 8, 9, 7), (40, 8, 13, 13)]
 TRAIN_CHAINS = [("prelu", "elu"), (), ("relu0",), ("tanh",), ("sigmoid",), ("elu",), ("relu01", "prelu")]
 
 
@@ -599,7 +605,7 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi):
     assert capi.fused_error_check() == 0
 
 
-@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 5, 3), (64, 64, 32, 32)])
+@pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 5, 3), (64, 64, 32, 32), (16, 24, 7, 7), (9, 40, 5, 5)])
 @pytest.mark.parametrize("with_bn", [True, False])
 def test_bias_folded_into_bn_infer(capi, oracle, shape, with_bn):
     """The convolution bias added in the load of the fused inference kernel: bit-exact against
