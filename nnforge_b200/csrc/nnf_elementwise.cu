@@ -462,10 +462,11 @@ namespace nnf
 		}
 
 		// Grid: a whole number of resident waves (a grid somewhat larger than one wave would run a short second wave
-		// with most SMs idle), never more than there are tiles. Eight waves, measured on B200: CTAs that start at
-		// different times mix their loads and stores, which a single wave moving in lockstep does not (x[1024,256,14,14]
-		// BN+ReLU: 74 us with one wave, 66 us with eight, 69 us with 32); every CTA fills the per-channel table first,
-		// so many more CTAs than that pay for it again and again (x[1024,2048,7,7]: 181 us with 32 waves, 157 us with eight).
+		// with most SMs idle), never more than there are tiles. Measured on B200: CTAs that start at different times mix
+		// their loads and stores, which a single wave moving in lockstep does not (2 GiB BN+TanH: 84 % of the copy
+		// bandwidth with one wave, 94 % with 4, 102 % with 16, 104 % with 32); but every CTA fills the per-channel table
+		// first, and below 64 tiles per resident CTA slot that cost shows (x[1024,256,14,14] BN+ReLU: 74 us with one wave,
+		// 66 us with eight, 69 us with 32). So 32 waves for large tensors, eight otherwise.
 		template <int MODE, int A0, int A1>
 		int resident_grid(size_t smem, int64_t work)
 		{
@@ -483,10 +484,12 @@ namespace nnf
 				per_sm = v;
 				cached_smem = smem;
 			}
-			static int waves = 0; // tuning aid: NNF_EW_WAVES = grid size in units of one resident wave
-			if (waves == 0)
-				waves = getenv("NNF_EW_WAVES") ? atoi(getenv("NNF_EW_WAVES")) : 8;
-			const int64_t cap = int64_t(kSmCount) * per_sm * (waves < 1 ? 1 : waves);
+			static int forced = -1; // tuning aid: NNF_EW_WAVES = grid size in units of one resident wave
+			if (forced < 0)
+				forced = getenv("NNF_EW_WAVES") ? atoi(getenv("NNF_EW_WAVES")) : 0;
+			const int64_t wave = int64_t(kSmCount) * per_sm;
+			const int waves = forced > 0 ? forced : (work >= 64 * wave ? 32 : 8);
+			const int64_t cap = wave * waves;
 			const int64_t g = work < cap ? work : cap;
 			return g < 1 ? 1 : (int)g;
 		}

@@ -15,11 +15,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _inputs():
+def _inputs(use_peer=0):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import synth
     g = synth.rng(2, salt=777)
-    shape = (16, 24, 14, 14)
+    # case 4: 7x7 planes are not whole float4s - the in-launch exchange does not take them, the layer falls back to
+    # statistics kernel -> all-reduce -> apply kernel on the channel-group kernels
+    shape = (16, 24, 7, 7) if int(use_peer) == 4 else (16, 24, 14, 14)
     return (synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape), synth.uniform(g, 24, 0.5, 1.5), synth.normal(g, 24, 0.0, 0.1),
             synth.uniform(g, 24, 0.0, 0.3))
 
@@ -31,7 +33,7 @@ def _rank(rank, world, port, out_dir, use_peer):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     import nnforge_b200.capi as capi
     from nnforge_b200.sharded import NcclExchange, PeerExchange, ShardedBatchNormAct
-    x, dy, gamma, beta, slope = _inputs()
+    x, dy, gamma, beta, slope = _inputs(use_peer)
     n, c = x.shape[0], x.shape[1]
     lo, hi = n * rank // world, n * (rank + 1) // world
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
@@ -40,7 +42,7 @@ def _rank(rank, world, port, out_dir, use_peer):
     from nnforge_b200.sharded import FusedPeerExchange, InLaunchExchange
     exchange = [NcclExchange, lambda: PeerExchange(capi, 2 * c, torch.device("cuda", rank)),
                 lambda: FusedPeerExchange(capi, 2 * c, torch.device("cuda", rank)),
-                lambda: InLaunchExchange(capi, c, torch.device("cuda", rank))][int(use_peer)]()
+                lambda: InLaunchExchange(capi, c, torch.device("cuda", rank))][min(int(use_peer), 3)]()
     layer = ShardedBatchNormAct(capi, c, 1e-5, acts, "cuda", exchange=exchange)
     xs, dys, gd, bd = d(x[lo:hi]), d(dy[lo:hi]), d(gamma), d(beta)
     y, dx = torch.empty_like(xs), torch.empty_like(xs)
@@ -54,14 +56,15 @@ def _rank(rank, world, port, out_dir, use_peer):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [0, 1, 2, 3])  # NCCL all-reduce, peer-memory sum, the same inside the two kernels, inside the single launch
+# NCCL all-reduce, peer-memory sum, the same inside the two kernels, inside the single launch, and (4) the last on 7x7 planes
+@pytest.mark.parametrize("use_peer", [0, 1, 2, 3, 4])
 def test_two_gpu_sharded_matches_unsharded_oracle(tmp_path, oracle, use_peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     port = 29700 + int(use_peer) + (os.getpid() % 200)
     mp.spawn(_rank, args=(world, port, str(tmp_path), use_peer), nprocs=world, join=True)
-    x, dy, gamma, beta, slope = _inputs()
+    x, dy, gamma, beta, slope = _inputs(use_peer)
     u, sv = oracle.bn_train_fwd(x, gamma, beta, 1e-5)
     v = oracle.prelu_fwd(u, slope)
     yw = oracle.elu_fwd(v)
