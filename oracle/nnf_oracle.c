@@ -15,7 +15,11 @@
  * Training-mode batch norm (orc_bn_train_*) has NO reference CPU implementation - the reference
  * calls cuDNN there - so its parity is UNPINNED by reference code; it restates the documented
  * spatial batch-norm formulas and is cross-checked against a double-precision twin and against
- * PyTorch's CPU batch_norm in the tests.
+ * PyTorch's CPU batch_norm in the tests. The optimiser step (orc_apply_gradient) and the three-line rewrite of the
+ * running statistics (orc_bn_recalibrate) follow reference files that need Boost to compile
+ * (plain/backward_propagation_plain.cpp, toolset.cpp): their parity is UNPINNED too; the optimiser is checked bit for bit
+ * against an independent numpy float32 statement of the same formulas (tests/test_oracle_golden.py). The statistics the
+ * recalibration consumes (orc_feature_map_stats_*) ARE pinned, to the reference's stat_data_bunch_writer.cpp.
  *
  * Layout everywhere: planar fp32, offset = ((n*C + c)*H + y)*W + x.
  * With -fopenmp the outer loops run in parallel exactly where the reference has its
