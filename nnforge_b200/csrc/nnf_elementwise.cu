@@ -316,6 +316,7 @@ namespace nnf
 		struct ewg_geom
 		{
 			uint32_t n, group, groups, split, entries_per_cta;
+			uint32_t threads;          // vectors of a full group's run, rounded up to whole warps
 			fastdiv d_hw;
 		};
 
@@ -340,7 +341,7 @@ namespace nnf
 			const uint32_t e1 = min(e0 + g.entries_per_cta, g.n);
 			if (has_bn)
 			{
-				for (uint32_t i = threadIdx.x; i < channels; i += kThreads)
+				for (uint32_t i = threadIdx.x; i < channels; i += blockDim.x)
 				{
 					const uint32_t ch = ch0 + i;
 					float mean, invsigma;
@@ -427,11 +428,12 @@ namespace nnf
 			int64_t group = unit * (kThreads / vpu);
 			if (group > c)
 				group = c;
-			if (group * hw / 4 < kThreads / 2)       // fewer than half of the lanes busy: the flat kernel does better
+			if (group * hw / 4 < 64)                 // CTAs of fewer than two warps: the flat kernel does better
 				return false;
 			g.n = (uint32_t)n;
 			g.group = (uint32_t)group;
 			g.groups = (uint32_t)div_up(c, group);
+			g.threads = (uint32_t)(div_up(group * hw / 4, 32) * 32);
 			const int64_t waves = getenv("NNF_EWG_WAVES") ? atoi(getenv("NNF_EWG_WAVES")) : 2;   // tuning aid
 			int64_t split = div_up(int64_t(kSmCount) * 8 * waves, g.groups);
 			if (split > n / 4) split = n / 4;
@@ -448,7 +450,7 @@ namespace nnf
 			const int k1 = p.chain.n > 1 ? p.chain.a[1].kind : NNF_ACT_NONE;
 			const unsigned grid = g.groups * g.split;
 			const size_t smem = size_t(2) * g.group * sizeof(float);
-#define NNF_EWG_CASE(A0, A1) bn_act_grouped_kernel<A0, A1><<<grid, kThreads, smem, s>>>(p, g)
+#define NNF_EWG_CASE(A0, A1) bn_act_grouped_kernel<A0, A1><<<grid, g.threads, smem, s>>>(p, g)
 			if (p.chain.n == 0)
 				NNF_EWG_CASE(NNF_ACT_NONE, 0);
 			else if (k0 == NNF_ACT_RELU && k1 == NNF_ACT_NONE)
