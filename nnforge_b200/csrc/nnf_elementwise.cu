@@ -672,15 +672,26 @@ namespace nnf
 						{
 							o[0] = ov[j].x; o[1] = ov[j].y; o[2] = ov[j].z; o[3] = ov[j].w;
 						}
-						float a = 0.0F;
+						float a = 0.0F, a_next = 0.0F;
+						uint32_t left = 4;   // elements of the vector that belong to its first channel
 						if (KIND == NNF_ACT_PRELU && MODE == 0)
 							a = __ldg(p.slope + channel_of(e));
+						if (KIND == NNF_ACT_PRELU && MODE == 1 && p.hw.d >= 4)
+						{
+							// planes of at least four elements that are not whole vectors: a vector touches at most two channels
+							const uint32_t plane = p.hw.div(e);
+							const uint32_t channel = plane - p.cdiv.div(plane) * p.c;
+							left = (plane + 1) * p.hw.d - e;
+							a = __ldg(p.slope + channel);
+							a_next = __ldg(p.slope + (channel + 1 == p.c ? 0 : channel + 1));
+						}
 						#pragma unroll
 						for (int k = 0; k < 4; ++k)
 						{
+							float ak = a;
 							if (KIND == NNF_ACT_PRELU && MODE == 1)
-								a = __ldg(p.slope + channel_of(e + k));
-							const float r = act_bwd<KIND>(g[k], t[k], p.p0, p.p1, a);
+								ak = p.hw.d >= 4 ? (uint32_t(k) >= left ? a_next : a) : __ldg(p.slope + channel_of(e + k));
+							const float r = act_bwd<KIND>(g[k], t[k], p.p0, p.p1, ak);
 							o[k] = p.add ? __fadd_rn(o[k], r) : r;
 						}
 						st_stream(dx4 + v, make_float4(o[0], o[1], o[2], o[3]));
