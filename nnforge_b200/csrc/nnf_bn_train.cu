@@ -738,6 +738,63 @@ namespace nnf
 			group_fold<2>(partial, s_pos, g, t);
 		}
 
+		// PReLU slope gradient partials on channel groups: sum dy * (x >= 0 ? 0 : x) per position, folded per channel
+		template <int R>
+		__global__ void __launch_bounds__(kThreads) prelu_dslope_grouped_kernel(double * partial, const float * dy, const float * x, const group_geom g)
+		{
+			__shared__ float s_pos[1][kGroupMaxRun];
+			constexpr int U = 2;
+			const group_cta t = group_locate(g);
+			float acc[R][4];
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+				#pragma unroll
+				for (int j = 0; j < 4; ++j)
+					acc[r][j] = 0.0F;
+			const float4 * bx = reinterpret_cast<const float4 *>(x) + t.base4;
+			const float4 * bd = reinterpret_cast<const float4 *>(dy) + t.base4;
+			for (uint32_t e = t.e0; e < t.e1; e += U)
+			{
+				float4 a[U][R], d[U][R];
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						const uint32_t v = threadIdx.x + r * kThreads;
+						a[u][r] = d[u][r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						if (e + u < t.e1 && v < t.vectors)
+						{
+							const size_t off = size_t(e + u - t.e0) * t.stride4 + v;
+							a[u][r] = ld_stream(bx + off);
+							d[u][r] = ld_stream(bd + off);
+						}
+					}
+				#pragma unroll
+				for (int u = 0; u < U; ++u)
+					#pragma unroll
+					for (int r = 0; r < R; ++r)
+					{
+						// parametric_rectified_linear_layer_updater_plain.cpp:177-180
+						acc[r][0] += d[u][r].x * (a[u][r].x >= 0.0F ? 0.0F : a[u][r].x);
+						acc[r][1] += d[u][r].y * (a[u][r].y >= 0.0F ? 0.0F : a[u][r].y);
+						acc[r][2] += d[u][r].z * (a[u][r].z >= 0.0F ? 0.0F : a[u][r].z);
+						acc[r][3] += d[u][r].w * (a[u][r].w >= 0.0F ? 0.0F : a[u][r].w);
+					}
+			}
+			#pragma unroll
+			for (int r = 0; r < R; ++r)
+			{
+				const uint32_t v = threadIdx.x + r * kThreads;
+				if (v < t.vectors)
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+						s_pos[0][v * 4 + j] = acc[r][j];
+			}
+			__syncthreads();
+			group_fold<1>(partial, s_pos, g, t);
+		}
+
 		// the constants of one owned element
 		struct group_elem
 		{
@@ -1415,12 +1472,27 @@ extern "C" int nnf_prelu_bwd_weights(nnf_stream_t stream, float * dslope, const 
 	if (!workspace || workspace_bytes < nnf_prelu_bwd_weights_workspace_bytes(n, c, hw) || (reinterpret_cast<uintptr_t>(workspace) & 7))
 		return set_error(NNF_ERR_WORKSPACE, "nnf_prelu_bwd_weights: workspace of %zu bytes (8-byte aligned) required, got %zu", nnf_prelu_bwd_weights_workspace_bytes(n, c, hw), workspace_bytes);
 	chan_geom g;
-	int st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(prelu_dslope_kernel), 1);
-	if (st != NNF_OK)
-		return st;
+	group_geom gg;
+	int st;
 	cudaStream_t s = (cudaStream_t)stream;
-	prelu_dslope_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), dy, x, g);
-	st = check_launch("prelu_dslope_kernel");
+	if (make_group_geom(gg, n, c, hw, aligned16(x) && aligned16(dy)))
+	{
+		if (gg.vectors_per_thread == 1)
+			prelu_dslope_grouped_kernel<1><<<gg.groups * gg.split, kThreads, 0, s>>>(static_cast<double *>(workspace), dy, x, gg);
+		else
+			prelu_dslope_grouped_kernel<2><<<gg.groups * gg.split, kThreads, 0, s>>>(static_cast<double *>(workspace), dy, x, gg);
+		st = check_launch("prelu_dslope_grouped_kernel");
+		g.c = gg.c;
+		g.split = gg.split;
+	}
+	else
+	{
+		st = make_chan_geom(g, "nnf_prelu_bwd_weights", n, c, hw, aligned16(x) && aligned16(dy), resident_ctas_per_sm(prelu_dslope_kernel), 1);
+		if (st != NNF_OK)
+			return st;
+		prelu_dslope_kernel<<<g.c * g.split, kThreads, 0, s>>>(static_cast<double *>(workspace), dy, x, g);
+		st = check_launch("prelu_dslope_kernel");
+	}
 	if (st != NNF_OK)
 		return st;
 	bn_reduce_partials_kernel<<<(unsigned)div_up(c, 128), 128, 0, s>>>(dslope, static_cast<const double *>(workspace), g.c, g.split, 1, 1);

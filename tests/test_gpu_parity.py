@@ -169,7 +169,7 @@ def test_act_bwd(capi, oracle, shape, add):
         assert_bits_equal(host(dx), want, "%s bwd add=%s" % (name, add))
 
 
-@pytest.mark.parametrize("shape", [(256, 16, 28, 28), (5, 7, 3, 3), (3, 2, 1, 1), (9, 4, 7, 7)])
+@pytest.mark.parametrize("shape", [(256, 16, 28, 28), (5, 7, 3, 3), (3, 2, 1, 1), (9, 4, 7, 7), (40, 24, 7, 7), (40, 8, 13, 13), (64, 512, 1, 1)])
 def test_prelu_bwd_weights(capi, oracle, shape):
     g = synth.rng(6, salt=sum(shape))
     x = synth.normal(g, shape, 0.5, 2.0)
