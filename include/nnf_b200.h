@@ -383,8 +383,11 @@ NNF_API int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * pre
  * address; mailboxes[r] is rank r's mailbox as seen from this GPU. seq numbers the exchanges (1, 2, 3, ...,
  * the same on all ranks, one per call). Every rank must make the same call with its own shard; count_total
  * = elements per channel over all shards. sums / bsums receive THIS shard's sums; the per-channel gradients
- * accumulate this shard's sums. Needs H*W divisible by 4 and 16-byte aligned tensors (NNF_ERR_UNSUPPORTED
- * otherwise: use the split entry points); workspace as for nnf_bn_train_stats. No add_to_destination. */
+ * accumulate this shard's sums. Needs 16-byte aligned tensors and a shape for which
+ * nnf_bn_train_sharded_supported(n, c, hw) answers 1: planes of whole float4s, or planes whose channel groups fill a
+ * CTA (7x7, 13x13, ...: channels a multiple of 4 / gcd(H*W, 4)); NNF_ERR_UNSUPPORTED otherwise: use the split entry
+ * points. Workspace as for nnf_bn_train_stats. No add_to_destination. */
+NNF_API int nnf_bn_train_sharded_supported(int64_t n, int64_t c, int64_t hw);
 NNF_API size_t nnf_bn_train_mailbox_bytes(int64_t c);
 NNF_API int nnf_bn_train_fwd_sharded(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
 	const float * gamma, const float * beta, float eps, const nnf_act * acts, int n_acts,

@@ -89,6 +89,7 @@ _SIGNATURES = {
     "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_softmax_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_bn_train_mailbox_bytes": (_SZ, [_I64]),
+    "nnf_bn_train_sharded_supported": (_I, [_I64, _I64, _I64]),
     "nnf_bn_train_fwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64, _D, _P, _SZ, ct.POINTER(_P), _I, _I, ct.c_uint32]),
     "nnf_bn_train_bwd_sharded": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _ACTP, _I, _P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _D, _P, _SZ,
                                       ct.POINTER(_P), _I, _I, ct.c_uint32]),
@@ -385,6 +386,10 @@ def softmax_nll_fwd(probs, err, logits, targets, mask=None, scale=1.0, stream=No
 def softmax_nll_bwd(dlogits, probs, targets, mask=None, scale=1.0, add_to_destination=False, stream=None):
     n, c, hw = _nchw(probs)
     _check(lib.nnf_softmax_nll_bwd(_stream(stream), _ptr(dlogits), _ptr(probs), _ptr(targets), _ptr(mask), scale, n, c, hw, int(add_to_destination)))
+
+
+def bn_train_sharded_supported(n, c, hw):
+    return bool(lib.nnf_bn_train_sharded_supported(n, c, hw))
 
 
 def bn_train_mailbox_bytes(c):

@@ -624,7 +624,7 @@ namespace nnf
 		constexpr int kChainGroupRun = 1024;       // floats of a group's run in one entry (one vector per thread)
 		constexpr int kChainGroupChannels = 256;
 
-		template <int A0, int A1, bool BWD>
+		template <int A0, int A1, bool BWD, bool PEER>
 		__global__ void __launch_bounds__(kChainThreads, 4) bn_train_chain_grouped_kernel(const chain_params p)
 		{
 			constexpr int K = BWD ? 3 : 2;
@@ -788,7 +788,70 @@ namespace nnf
 				if (threadIdx.x == 0)
 				{
 					__threadfence(); // every partial sum of this item, whichever thread wrote it, comes before the count
-					atomicAdd(p.done + grp, 1u);
+					const uint32_t before = atomicAdd(p.done + grp, 1u);
+					if (PEER)
+					{
+						__threadfence(); // and the other items' partial sums are visible to this one if it is the last
+						s_item[3] = before == p.split_s - 1 ? 1u : 0u;
+					}
+				}
+				if (!PEER)
+					return;
+				__syncthreads();
+				if (s_item[3] == 0)
+					return;
+				// last S item of this group on this rank: fold the partial sums of every channel of the group (slice
+				// order, eight lanes per channel), write the local per-channel outputs, publish the messages to every rank
+				for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
+				{
+					const uint32_t lc = first + threadIdx.x / kLanes;
+					const uint32_t ch = ch0 + lc;
+					double t[K];
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						t[k] = 0.0;
+					if (lc < channels)
+						for (uint32_t q = lane; q < p.split_s; q += kLanes)
+						{
+							#pragma unroll
+							for (int k = 0; k < K; ++k)
+								t[k] += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
+						}
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+					{
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 4);
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 2);
+						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 1);
+					}
+					if (lc < channels)
+					{
+						const float m0 = float(t[0]), m1 = float(t[1]);
+						if (lane == 0)
+						{
+							if (p.sums)
+							{
+								p.sums[ch] = m0;
+								p.sums[p.c + ch] = m1;
+								if (BWD)
+									p.sums[2 * p.c + ch] = float(t[K - 1]);
+							}
+							if (BWD)
+							{
+								// per-channel gradients accumulate the LOCAL sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+								if (p.grad_beta) p.grad_beta[ch] += m0;
+								if (p.grad_gamma) p.grad_gamma[ch] += m1;
+								if (p.grad_slope) p.grad_slope[ch] += float(t[K - 1]);
+							}
+						}
+						// lane r of the channel's eight sends both words to rank r
+						if (lane < uint32_t(p.world))
+						{
+							__threadfence(); // everything this rank's S items wrote for the channel comes before the words
+							st_sys_u64(p.mail[lane] + mail_index(p, p.rank, ch), (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(m0));
+							st_sys_u64(p.mail[lane] + mail_index(p, p.rank, ch) + 1, (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(m1));
+						}
+					}
 				}
 				return;
 			}
@@ -815,7 +878,85 @@ namespace nnf
 			};
 			// the first loads do not depend on the statistics: they are in flight while the item waits
 			load_batch(e0);
-			if (threadIdx.x == 0)
+			if constexpr (PEER)
+			{
+				// every channel of the group: lane r of the channel's eight waits (bounded) until rank r's two words carry this
+				// exchange's number, then the messages are added in rank order
+				for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
+				{
+					const uint32_t lc = first + threadIdx.x / kLanes;
+					const uint32_t ch = ch0 + min(lc, channels - 1);
+					const unsigned long long * mine = p.mail[p.rank];
+					unsigned long long w0 = 0, w1 = 0;
+					bool ok = lc >= channels || lane >= uint32_t(p.world);
+					const unsigned long long t0 = chain_timer_ns();
+					for (uint32_t round = 0; ; ++round)
+					{
+						if (!ok)
+						{
+							w0 = ld_sys_u64(mine + mail_index(p, lane, ch));
+							w1 = ld_sys_u64(mine + mail_index(p, lane, ch) + 1);
+							ok = uint32_t(w0 >> 32) == p.seq && uint32_t(w1 >> 32) == p.seq;
+						}
+						if (__all_sync(0xffffffffu, ok))
+							break;
+						bool give_up = false;
+						if ((round & 15) == 15 && (threadIdx.x & 31) == 0)
+							give_up = (p.error && *reinterpret_cast<volatile int *>(p.error) != 0) || chain_timer_ns() - t0 > kChainPeerWaitNs;
+						if (__any_sync(0xffffffffu, give_up))
+						{
+							if ((threadIdx.x & 31) == 0 && p.error)
+								*p.error = 2;
+							break;
+						}
+						__nanosleep(200);
+					}
+					__threadfence(); // what the publishing items wrote before their words is visible from here on
+					float f0 = 0.0F, f1 = 0.0F;
+					const int lane0 = int(threadIdx.x & 31u) & ~int(kLanes - 1);   // first lane of this channel's eight
+					for (int r = 0; r < p.world; ++r)
+					{
+						f0 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w0, lane0 + r)));
+						f1 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w1, lane0 + r)));
+					}
+					if (lc < channels && lane == 0)
+					{
+						if constexpr (!BWD)
+						{
+							const double m = double(f0) / p.count_total;
+							double var = double(f1) / p.count_total - m * m;
+							var = var < 0.0 ? 0.0 : var;
+							const float fmean = float(m);
+							const float finv = float(1.0 / sqrt(var + double(p.eps)));
+							const float mult = __fmul_rn(__ldg(p.gamma + ch), finv);
+							s_const[0][lc] = mult;
+							s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, fmean));
+							if (sp == 0)
+							{
+								p.saved[ch] = fmean;
+								p.saved[p.c + ch] = finv;
+							}
+						}
+						else
+						{
+							const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+							const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+							s_const[0][lc] = mult;
+							s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
+							s_const[NC - 4][lc] = mean;
+							s_const[NC - 3][lc] = invstd;
+							s_const[NC - 2][lc] = float(double(f0) / p.count_total);
+							s_const[NC - 1][lc] = float(double(f1) / p.count_total);
+							if (sp == 0)
+							{
+								if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+								if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+							}
+						}
+					}
+				}
+			}
+			if (!PEER && threadIdx.x == 0)
 			{
 				bool ready = false;
 				for (uint32_t round = 0; round < kChainPollLimit; ++round)
@@ -832,7 +973,7 @@ namespace nnf
 			}
 			__syncthreads();
 			// the S items' partial sums of every channel of the group, in slice order: eight lanes per channel
-			for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
+			for (uint32_t first = 0; !PEER && first < channels; first += kChainThreads / kLanes)
 			{
 				const uint32_t lc = first + threadIdx.x / kLanes;
 				const uint32_t ch = ch0 + lc;
@@ -1154,7 +1295,7 @@ namespace nnf
 			chain_params p = {};
 			if (!aligned16(x) || !aligned16(y))
 				return 1;
-			const bool grouped = !PEER && plan_chain_grouped(p, n, c, hw);
+			const bool grouped = plan_chain_grouped(p, n, c, hw);
 			if (!grouped && !plan_chain(p, n, c, hw, 1))
 				return 1;
 			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
@@ -1162,20 +1303,20 @@ namespace nnf
 			p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
 			p.chain = chain;
 			p.eps = eps;
+			const int st = fill_peer(p, peer, "bn_train_chain_kernel (forward)");
+			if (st != NNF_OK)
+				return st;
 			if (grouped)
 			{
 				const char * what = "bn_train_chain_grouped_kernel (forward)";
 				switch (chain_id(chain))
 				{
-				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, false>, p, workspace, stream, what);
-				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false>, p, workspace, stream, what);
-				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, false>, p, workspace, stream, what);
-				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, false>, p, workspace, stream, what);
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, false, PEER>, p, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, p, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, false, PEER>, p, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, false, PEER>, p, workspace, stream, what);
 				}
 			}
-			const int st = fill_peer(p, peer, "bn_train_chain_kernel (forward)");
-			if (st != NNF_OK)
-				return st;
 			const int k0 = chain.n > 0 ? chain.a[0].kind : NNF_ACT_NONE;
 			const int k1 = chain.n > 1 ? chain.a[1].kind : NNF_ACT_NONE;
 			if (chain.n == 0)
@@ -1197,7 +1338,7 @@ namespace nnf
 			chain_params p = {};
 			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx))
 				return 1;
-			const bool grouped = !PEER && plan_chain_grouped(p, n, c, hw);
+			const bool grouped = plan_chain_grouped(p, n, c, hw);
 			if (!grouped && !plan_chain(p, n, c, hw, 2))
 				return 1;
 			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
@@ -1206,20 +1347,20 @@ namespace nnf
 			p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
 			p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 			p.chain = chain;
+			const int st = fill_peer(p, peer, "bn_train_chain_kernel (backward)");
+			if (st != NNF_OK)
+				return st;
 			if (grouped)
 			{
 				const char * what = "bn_train_chain_grouped_kernel (backward)";
 				switch (chain_id(chain))
 				{
-				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, true>, p, workspace, stream, what);
-				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true>, p, workspace, stream, what);
-				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, true>, p, workspace, stream, what);
-				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, true>, p, workspace, stream, what);
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, p, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, true, PEER>, p, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, true, PEER>, p, workspace, stream, what);
 				}
 			}
-			const int st = fill_peer(p, peer, "bn_train_chain_kernel (backward)");
-			if (st != NNF_OK)
-				return st;
 			switch (chain_id(chain))
 			{
 			case 0: return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
@@ -1251,6 +1392,12 @@ namespace nnf
 
 using namespace nnf;
 
+extern "C" int nnf_bn_train_sharded_supported(int64_t n, int64_t c, int64_t hw)
+{
+	chain_params p = {};
+	return (plan_chain_grouped(p, n, c, hw) || plan_chain(p, n, c, hw, 1)) ? 1 : 0;
+}
+
 extern "C" size_t nnf_bn_train_mailbox_bytes(int64_t c)
 {
 	return c > 0 ? size_t(2) * kMaxRanks * size_t(c) * 2 * sizeof(unsigned long long) : 0;
@@ -1272,7 +1419,7 @@ extern "C" int nnf_bn_train_fwd_sharded(nnf_stream_t stream, float * y, float * 
 	const chain_peer peer = {mailboxes, rank, world, seq, count_total};
 	st = chain_forward_impl<true>((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, &peer);
 	if (st == 1)
-		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_fwd_sharded: needs H*W divisible by 4, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_fwd_sharded: needs a shape for which nnf_bn_train_sharded_supported() answers 1, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
 	return st;
 }
 
@@ -1303,6 +1450,6 @@ extern "C" int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float *
 	st = chain_backward_impl<true>((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
 		mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, &peer);
 	if (st == 1)
-		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd_sharded: needs H*W divisible by 4, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd_sharded: needs a shape for which nnf_bn_train_sharded_supported() answers 1, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
 	return st;
 }

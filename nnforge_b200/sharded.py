@@ -135,12 +135,17 @@ class ShardedBatchNormAct:
         entries = global_entries if global_entries is not None else n * self.world
         return float(entries * hw)
 
+    def _in_launch_ok(self, x, hw):
+        """Shapes the one-launch sharded entry points take (the library decides; planes of whole float4s always are)."""
+        supported = getattr(self.k, "bn_train_sharded_supported", None)
+        return supported(x.shape[0], x.shape[1], hw) if supported is not None else hw % 4 == 0
+
     def forward(self, y, x, gamma, beta, global_entries=None):
         m = self.count_total(x, global_entries)
         self.on_phase("start")
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
-        if self.world > 1 and getattr(ex, "in_launch", False) and hw % 4 == 0 and x.shape[1] == ex.channels:
+        if self.world > 1 and getattr(ex, "in_launch", False) and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels:
             self.k.bn_train_fwd_sharded(y, self.saved, self.sums, x, gamma, beta, self.eps, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
                                         ex.next_seq())
             self.on_phase("stats")
@@ -173,7 +178,7 @@ class ShardedBatchNormAct:
         mean, invsigma = running if running is not None else (None, None)
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
-        if sharded and getattr(ex, "in_launch", False) and hw % 4 == 0 and x.shape[1] == ex.channels and not add_to_destination:
+        if sharded and getattr(ex, "in_launch", False) and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels and not add_to_destination:
             self.on_phase("bwd_stats")
             self.k.bn_train_bwd_sharded(dx, self.bsums, dy, x, gamma, beta, self.saved, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
                                         ex.next_seq(), grad_gamma=grads.get("gamma"), grad_beta=grads.get("beta"), grad_mean=grads.get("mean"),

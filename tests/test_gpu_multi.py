@@ -19,8 +19,7 @@ def _inputs(use_peer=0):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import synth
     g = synth.rng(2, salt=777)
-    # case 4: 7x7 planes are not whole float4s - the in-launch exchange does not take them, the layer falls back to
-    # statistics kernel -> all-reduce -> apply kernel on the channel-group kernels
+    # case 4: 7x7 planes are not whole float4s - the in-launch exchange runs on channel groups
     shape = (16, 24, 7, 7) if int(use_peer) == 4 else (16, 24, 14, 14)
     return (synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape), synth.uniform(g, 24, 0.5, 1.5), synth.normal(g, 24, 0.0, 0.1),
             synth.uniform(g, 24, 0.0, 0.3))

@@ -557,7 +557,7 @@ def _sharded_single_launch(capi, x, dy, gamma, beta, slope, chain, mailboxes, ra
     return host(y), host(saved), host(dx), {k: host(v) for k, v in grads.items()}
 
 
-@pytest.mark.parametrize("shape", [(16, 32, 28, 28), (37, 3, 8, 8), (2, 300, 12, 12)])
+@pytest.mark.parametrize("shape", [(16, 32, 28, 28), (37, 3, 8, 8), (2, 300, 12, 12), (33, 48, 7, 7), (70, 12, 13, 13), (9, 300, 5, 2)])
 def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
     """The sharded single-launch entry points with a world of one: the whole exchange path (publication by
     the last statistics item, tagged words, wait in the apply items) runs against this rank's own mailbox."""
@@ -582,10 +582,10 @@ def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
         assert np.abs(grads["slope"] - dslope_w).max() <= 1e-5 * scale + 1e-5 * np.abs(dslope_w).max()
 
 
-def test_bn_train_sharded_single_launch_wait_is_bounded(capi):
+@pytest.mark.parametrize("shape", [(8, 6, 8, 8), (8, 8, 7, 7)])   # planes of whole float4s; channel groups
+def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape):
     """A second rank that never publishes: the apply items give up after their limit, the launch returns
     and reports it; the next call with a complete world works again."""
-    shape = (8, 6, 8, 8)
     g = synth.rng(2, salt=5100)
     x, dy = synth.normal(g, shape, 0.5, 2.0), synth.normal(g, shape)
     c = shape[1]
