@@ -81,12 +81,33 @@ namespace nnf
 					return t >= 0.0F ? t : __fmul_rn(t, p.slope);
 				};
 				const uint32_t nvec = (p.vec_ok && (base & 3) == 0) ? (count >> 2) : 0;
-				for (uint32_t v = threadIdx.x; v < nvec; v += kAvgThreads)
+				// independent 128-bit loads per thread before any is consumed: the stand-alone layer reads one tensor and needs
+				// them to cover the latency (7x7 global pooling 35 -> 27 us); the fused form has two input streams and a store
+				// per vector already and is slower with more (14x14: 119 -> 143 us)
+				constexpr int kInFlight = FUSED ? 1 : 4;
+				for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kAvgThreads * kInFlight)
 				{
-					const float4 a = ld_stream(reinterpret_cast<const float4 *>(p.x + base) + v);
-					float4 r = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-					if (has_res)
-						r = ld_stream(reinterpret_cast<const float4 *>(p.res + base) + v);
+				float4 av[kInFlight], rv[kInFlight];
+				#pragma unroll
+				for (int u = 0; u < kInFlight; ++u)
+				{
+					const uint32_t v = v0 + u * kAvgThreads;
+					rv[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (v < nvec)
+					{
+						av[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + base) + v);
+						if (has_res)
+							rv[u] = ld_stream(reinterpret_cast<const float4 *>(p.res + base) + v);
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < kInFlight; ++u)
+				{
+					const uint32_t v = v0 + u * kAvgThreads;
+					if (v >= nvec)
+						break;
+					const float4 a = av[u];
+					const float4 r = rv[u];
 					// a vector lies in one plane unless it straddles a plane boundary (H*W not a multiple of 4)
 					float m0 = 1.0F, a0 = 0.0F, m1 = 1.0F, a1 = 0.0F;
 					uint32_t left = 4;
@@ -103,6 +124,7 @@ namespace nnf
 					if (FUSED)
 						st_stream(reinterpret_cast<float4 *>(p.z + base) + v, o);
 					reinterpret_cast<float4 *>(s_z)[v] = o;
+				}
 				}
 				for (uint32_t e = (nvec << 2) + threadIdx.x; e < count; e += kAvgThreads)
 				{
@@ -270,6 +292,11 @@ namespace nnf
 			if (group < 1) group = 1;
 			if (group > kAvgMaxGroup) group = kAvgMaxGroup;
 			if (group > p.planes) group = p.planes;
+			// planes that are not whole float4s (7x7): a group of a multiple of 4 / gcd(H*W, 4) planes still starts and
+			// ends on a vector boundary, so the vector path below applies to every group
+			const int64_t unit = (p.hw % 4 == 0) ? 1 : ((p.hw % 2 == 0) ? 2 : 4);
+			if (group > unit)
+				group -= group % unit;
 			const size_t smem = size_t(group) * plane_bytes;
 			if (smem > kAvgMaxSmem)
 			{

@@ -632,7 +632,7 @@ def test_bias_folded_into_bn_infer(capi, oracle, shape, with_bn):
 
 
 AVG_CASES = [((2, 3, 8, 12), (4, 2)), ((6, 10, 7, 7), (7, 7)), ((2, 4, 6, 6), (1, 1)), ((3, 5, 14, 14), (2, 2)), ((2, 3, 4, 9), (3, 4)),
-             ((4, 600, 7, 7), (7, 7)), ((1, 1, 240, 240), (8, 8))]
+             ((4, 600, 7, 7), (7, 7)), ((3, 5, 7, 7), (7, 7)), ((5, 6, 9, 9), (3, 3)), ((1, 1, 240, 240), (8, 8))]
 
 
 @pytest.mark.parametrize("shape,win", AVG_CASES)
@@ -654,7 +654,7 @@ def test_average_subsampling(capi, oracle, shape, win):
         assert_bits_equal(host(acc), oracle.avgpool_bwd(dy, shape, win, mult=mult, dx=seed), "average subsampling backward, accumulated")
 
 
-@pytest.mark.parametrize("shape,win", AVG_CASES[:6])
+@pytest.mark.parametrize("shape,win", AVG_CASES[:8])
 @pytest.mark.parametrize("with_bn,with_res", [(True, True), (True, False), (False, True)])
 def test_fused_bn_add_relu_avgpool(capi, oracle, shape, win, with_bn, with_res):
     """BN (running statistics) -> add -> ReLU -> average pooling in one pass, and its backward, bit-exact against the
