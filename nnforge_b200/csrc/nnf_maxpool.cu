@@ -143,11 +143,12 @@ namespace nnf
 					float4 * z4 = FUSED ? reinterpret_cast<float4 *>(p.z + base) : nullptr;
 					float4 * s4 = reinterpret_cast<float4 *>(s_z);
 					const bool plane_per_vec = (g.hw & 3) == 0;
-					for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kThreads * 2)
+					constexpr int kInFlight = 2;   // independent 128-bit loads per thread and tensor before any is consumed (4: no gain)
+					for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kThreads * kInFlight)
 					{
-						float4 a[2], r[2];
+						float4 a[kInFlight], r[kInFlight];
 						#pragma unroll
-						for (int u = 0; u < 2; ++u)
+						for (int u = 0; u < kInFlight; ++u)
 						{
 							const uint32_t v = v0 + u * kThreads;
 							r[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
@@ -159,7 +160,7 @@ namespace nnf
 							}
 						}
 						#pragma unroll
-						for (int u = 0; u < 2; ++u)
+						for (int u = 0; u < kInFlight; ++u)
 						{
 							const uint32_t v = v0 + u * kThreads;
 							if (v < nvec)
@@ -372,6 +373,42 @@ namespace nnf
 			}
 		}
 
+		// 2x2 windows, stride 2, four consecutive elements of one input row: windows do not overlap, the four elements
+		// belong to the two windows {k, k + 1} of output row iy / 2, k = ix0 / 2 - two (argmax, gradient) pairs per vector
+		__device__ __forceinline__ void gather_row4_2x2s2(const pool_geom& g, const float * dyp, const uint32_t * idp, uint32_t iy, uint32_t ix0,
+			uint32_t abs0, float (&acc)[4])
+		{
+			const uint32_t oy = iy >> 1;
+			if (oy > g.oh - 1)
+				return;
+			const uint32_t k = ix0 >> 1;
+			const uint32_t row = oy * g.ow + k;
+			if (k <= g.ow - 1)
+			{
+				const uint32_t i = idp[row];
+				const float d = dyp[row];
+				if (i == abs0) acc[0] = __fadd_rn(acc[0], d);
+				if (i == abs0 + 1) acc[1] = __fadd_rn(acc[1], d);
+			}
+			if (k + 1 <= g.ow - 1)
+			{
+				const uint32_t i = idp[row + 1];
+				const float d = dyp[row + 1];
+				if (i == abs0 + 2) acc[2] = __fadd_rn(acc[2], d);
+				if (i == abs0 + 3) acc[3] = __fadd_rn(acc[3], d);
+			}
+		}
+
+		template <int WW>
+		__device__ __forceinline__ void gather_row4(const pool_geom& g, const float * dyp, const uint32_t * idp, uint32_t iy, uint32_t ix0,
+			uint32_t abs0, float (&acc)[4])
+		{
+			if (WW == 2)
+				gather_row4_2x2s2(g, dyp, idp, iy, ix0, abs0, acc);
+			else
+				gather_row4_3x3s2(g, dyp, idp, iy, ix0, abs0, acc);
+		}
+
 		template <bool FUSED, int WW, int WH, int SW, int SH, bool ROW4 = false>
 		__global__ void __launch_bounds__(kThreads) pool_bwd_staged_kernel(const pool_bwd_params p)
 		{
@@ -454,11 +491,13 @@ namespace nnf
 								if ((uint32_t)k < nvalid)
 									acc[k] = p.dx[base + e0 + k];
 						}
-						gather_row4_3x3s2(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix0, (uint32_t)(base + e0), acc);
+						gather_row4<WW>(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, ix0, (uint32_t)(base + e0), acc);
 						#pragma unroll
 						for (int k = 0; k < 4; ++k)
 							if ((uint32_t)k < nvalid)
 							{
+								// (staging the stand-alone result too and storing it with 128-bit stores was measured slower:
+								// 14x14 81 -> 100 us)
 								if (FUSED)
 									s_dz[e0 + k] = acc[k]; // gathered gradient of the group, consumed with coalesced accesses below
 								else
@@ -530,7 +569,7 @@ namespace nnf
 							const uint32_t lp = g.d_hw.div(e0);
 							const uint32_t rem = e0 - lp * g.hw;
 							const uint32_t iy = g.d_w.div(rem);
-							gather_row4_3x3s2(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, rem - iy * g.w, (uint32_t)(base + e0), seed);
+							gather_row4<WW>(g, s_dy + lp * g.ohw, s_idx + lp * g.ohw, iy, rem - iy * g.w, (uint32_t)(base + e0), seed);
 							float mult = 1.0F;
 							if (FUSED && p.gamma)
 							{
@@ -784,7 +823,12 @@ namespace nnf
 				if (e == cudaSuccess) \
 					pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true><<<grid, kThreads, smem, s>>>(p); \
 			} \
-			else if (ww == 3 && wh == 3 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 3, 3, 2, 2) \
+			else if (ww == 2 && wh == 2 && sw == 2 && sh == 2 && (p.row4_vec || !FUSED)) \
+			{ \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 2, 2, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				if (e == cudaSuccess) \
+					pool_bwd_staged_kernel<FUSED, 2, 2, 2, 2, true><<<grid, kThreads, smem, s>>>(p); \
+			} \
 			else if (ww == 2 && wh == 2 && sw == 2 && sh == 2) NNF_POOL_BWD(FUSED, 2, 2, 2, 2) \
 			else NNF_POOL_BWD(FUSED, 0, 0, 0, 0)
 			if (fused)
