@@ -168,6 +168,116 @@ namespace nnf
 			}
 		}
 
+		// 2x2 windows on rows of whole float4s (stand-alone layer): a thread reads the same float4 column of the two input
+		// rows of an output row and writes two outputs; each window is summed in the plain backend's order
+		// (((0 + x00) + x01) + x10) + x11. No shared memory, every access 8 or 16 bytes wide.
+		__global__ void __launch_bounds__(kAvgThreads) avgpool_fwd_2x2_kernel(float * pooled, const float * x, int64_t out_rows, uint32_t w4, fastdiv d_w4, float mult)
+		{
+			const int64_t total = out_rows * w4;
+			const int64_t stride = int64_t(gridDim.x) * kAvgThreads * 2;
+			for (int64_t i0 = int64_t(blockIdx.x) * kAvgThreads * 2 + threadIdx.x; i0 < total; i0 += stride)
+			{
+				float4 a[2], b[2];
+				int64_t row[2];
+				uint32_t col[2];
+				#pragma unroll
+				for (int u = 0; u < 2; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+					{
+						// out_rows * w4 < 2^31 per launch (checked by the caller)
+						row[u] = d_w4.div((uint32_t)i);
+						col[u] = (uint32_t)(i - row[u] * w4);
+						const float4 * in = reinterpret_cast<const float4 *>(x) + row[u] * 2 * w4 + col[u];
+						a[u] = ld_stream(in);
+						b[u] = ld_stream(in + w4);
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < 2; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+					{
+						const float s0 = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(0.0F, a[u].x), a[u].y), b[u].x), b[u].y);
+						const float s1 = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(0.0F, a[u].z), a[u].w), b[u].z), b[u].w);
+						__stcs(reinterpret_cast<float2 *>(pooled) + row[u] * w4 + col[u], make_float2(__fmul_rn(s0, mult), __fmul_rn(s1, mult)));
+					}
+				}
+			}
+		}
+
+		// the same for rows of whole float2s only (14x14): one output per thread
+		__global__ void __launch_bounds__(kAvgThreads) avgpool_fwd_2x2_pair_kernel(float * pooled, const float * x, int64_t out_rows, uint32_t w2, fastdiv d_w2, float mult)
+		{
+			const int64_t total = out_rows * w2;
+			const int64_t stride = int64_t(gridDim.x) * kAvgThreads * 4;
+			for (int64_t i0 = int64_t(blockIdx.x) * kAvgThreads * 4 + threadIdx.x; i0 < total; i0 += stride)
+			{
+				float2 a[4], b[4];
+				#pragma unroll
+				for (int u = 0; u < 4; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+					{
+						const int64_t row = d_w2.div((uint32_t)i);
+						const float2 * in = reinterpret_cast<const float2 *>(x) + row * 2 * w2 + (i - row * w2);
+						a[u] = __ldcs(in);
+						b[u] = __ldcs(in + w2);
+					}
+				}
+				#pragma unroll
+				for (int u = 0; u < 4; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+						__stcs(pooled + i, __fmul_rn(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(0.0F, a[u].x), a[u].y), b[u].x), b[u].y), mult));
+				}
+			}
+		}
+
+		// backward of the 2x2 stand-alone layer on rows of whole float2s: every element of a window receives dy * mult
+		// (average_subsampling_layer_updater_plain.cpp:270-285); a thread takes one gradient and writes, or accumulates
+		// into, the two float2s of its window
+		__global__ void __launch_bounds__(kAvgThreads) avgpool_bwd_2x2_pair_kernel(float * dx, const float * dy, int64_t out_rows, uint32_t w2, fastdiv d_w2, float mult, int add)
+		{
+			const int64_t total = out_rows * w2;
+			const int64_t stride = int64_t(gridDim.x) * kAvgThreads * 4;
+			for (int64_t i0 = int64_t(blockIdx.x) * kAvgThreads * 4 + threadIdx.x; i0 < total; i0 += stride)
+			{
+				float g[4];
+				#pragma unroll
+				for (int u = 0; u < 4; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+						g[u] = __ldcs(dy + i);
+				}
+				#pragma unroll
+				for (int u = 0; u < 4; ++u)
+				{
+					const int64_t i = i0 + int64_t(u) * kAvgThreads;
+					if (i < total)
+					{
+						const int64_t row = d_w2.div((uint32_t)i);
+						float2 * out = reinterpret_cast<float2 *>(dx) + row * 2 * w2 + (i - row * w2);
+						const float err = __fmul_rn(g[u], mult);
+						float2 top = make_float2(err, err), bottom = make_float2(err, err);
+						if (add)
+						{
+							const float2 t = out[0], b = out[w2];
+							top = make_float2(__fadd_rn(t.x, err), __fadd_rn(t.y, err));
+							bottom = make_float2(__fadd_rn(b.x, err), __fadd_rn(b.y, err));
+						}
+						__stcs(out, top);
+						__stcs(out + w2, bottom);
+					}
+				}
+			}
+		}
+
 		// planes too large for shared memory: one thread per output reads its window from global memory
 		__global__ void __launch_bounds__(kAvgThreads) avgpool_fwd_direct_kernel(const avg_params p)
 		{
@@ -303,6 +413,26 @@ namespace nnf
 		{
 			if (p.planes == 0)
 				return NNF_OK;
+			if (!fused && p.win_w == 2 && p.win_h == 2 && p.w % 4 == 0 && p.h % 2 == 0 && aligned16(p.x) && (reinterpret_cast<uintptr_t>(p.pooled) & 7) == 0
+				&& p.planes * p.oh * (p.w / 4) < (int64_t(1) << 31))
+			{
+				const int64_t out_rows = p.planes * p.oh;
+				const uint32_t w4 = p.w / 4;
+				const int64_t blocks = div_up(out_rows * w4, kAvgThreads * 2);
+				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				avgpool_fwd_2x2_kernel<<<grid, kAvgThreads, 0, s>>>(p.pooled, p.x, out_rows, w4, fastdiv(w4), p.mult);
+				return check_launch("avgpool_fwd_2x2_kernel");
+			}
+			if (!fused && p.win_w == 2 && p.win_h == 2 && p.w % 2 == 0 && p.h % 2 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 7) == 0
+				&& p.planes * p.oh * (p.w / 2) < (int64_t(1) << 31))
+			{
+				const int64_t out_rows = p.planes * p.oh;
+				const uint32_t w2 = p.w / 2;
+				const int64_t blocks = div_up(out_rows * w2, kAvgThreads * 4);
+				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				avgpool_fwd_2x2_pair_kernel<<<grid, kAvgThreads, 0, s>>>(p.pooled, p.x, out_rows, w2, fastdiv(w2), p.mult);
+				return check_launch("avgpool_fwd_2x2_pair_kernel");
+			}
 			const size_t plane_bytes = size_t(p.hw) * sizeof(float);
 			int64_t group = int64_t(16 * 1024 / plane_bytes);
 			if (group < 1) group = 1;
@@ -352,6 +482,16 @@ namespace nnf
 			const int64_t total = p.planes * p.hw;
 			if (total == 0)
 				return NNF_OK;
+			if (!fused && p.win_w == 2 && p.win_h == 2 && p.w % 2 == 0 && p.h % 2 == 0 && p.dx && (reinterpret_cast<uintptr_t>(p.dx) & 7) == 0
+				&& p.planes * p.oh * (p.w / 2) < (int64_t(1) << 31))
+			{
+				const int64_t out_rows = p.planes * p.oh;
+				const uint32_t w2 = p.w / 2;
+				const int64_t blocks = div_up(out_rows * w2, kAvgThreads * 4);
+				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				avgpool_bwd_2x2_pair_kernel<<<grid, kAvgThreads, 0, s>>>(p.dx, p.dpooled, out_rows, w2, fastdiv(w2), p.mult, p.add);
+				return check_launch("avgpool_bwd_2x2_pair_kernel");
+			}
 			p.vec_ok = ((!p.dx || aligned16(p.dx)) && (!fused || (aligned16(p.zin) && (!p.dres || aligned16(p.dres))))) ? 1 : 0;
 			// launches of at most 2^31 elements, split at plane boundaries (and at multiples of 4 elements for the vector path)
 			int64_t planes_per_launch = kMaxElemsPerLaunch / p.hw;

@@ -632,7 +632,8 @@ def test_bias_folded_into_bn_infer(capi, oracle, shape, with_bn):
 
 
 AVG_CASES = [((2, 3, 8, 12), (4, 2)), ((6, 10, 7, 7), (7, 7)), ((2, 4, 6, 6), (1, 1)), ((3, 5, 14, 14), (2, 2)), ((2, 3, 4, 9), (3, 4)),
-             ((4, 600, 7, 7), (7, 7)), ((3, 5, 7, 7), (7, 7)), ((5, 6, 9, 9), (3, 3)), ((1, 1, 240, 240), (8, 8))]
+             ((4, 600, 7, 7), (7, 7)), ((3, 5, 7, 7), (7, 7)), ((5, 6, 9, 9), (3, 3)), ((1, 1, 240, 240), (8, 8)),
+             ((4, 6, 8, 12), (2, 2)), ((3, 2, 16, 16), (2, 2))]   # 2x2 windows on rows of whole float4s: the direct kernel
 
 
 @pytest.mark.parametrize("shape,win", AVG_CASES)
