@@ -314,6 +314,24 @@ def run_sweep(args):
         report(3, "bn+add+relu+global avgpool bwd N=1024 C=%d %dx%d" % (c, hw, hw),
                timeit(lambda i: capi.bn_add_relu_avgpool_bwd(dx, dr, dpo, z, bn[0], bn[3], 0.0, (hw, hw), mult), 1), 12 * e)
         del x, r, z, pooled, dpo, dx, dr
+    # the stand-alone subsampling layers (no batch norm in front): max 3x3/2 and 2x2/2, average 2x2
+    for c, hw, win in [(64, 56, 3), (128, 28, 3), (128, 28, 2), (256, 14, 2)]:
+        n = 1024
+        shape = (n, c, hw, hw)
+        e = n * c * hw * hw
+        p = capi.pool((win, win), (2, 2))
+        oh, ow = capi.pool_out_shape(hw, hw, p)
+        rho = oh * ow / float(hw * hw)
+        x = torch.randn(shape, device="cuda")
+        pooled = torch.empty((n, c, oh, ow), device="cuda")
+        idx = torch.empty((n, c, oh, ow), device="cuda", dtype=torch.int32)
+        dpo, dx = torch.randn_like(pooled), torch.empty_like(x)
+        report(3, "maxpool %dx%d/2 fwd N=%d C=%d %dx%d" % (win, win, n, c, hw, hw), timeit(lambda i: capi.maxpool_fwd(pooled, idx, x, p), 1), (4 + 8 * rho) * e)
+        report(3, "maxpool %dx%d/2 bwd N=%d C=%d %dx%d" % (win, win, n, c, hw, hw), timeit(lambda i: capi.maxpool_bwd(dx, dpo, idx, p), 1), (4 + 8 * rho) * e)
+        if win == 2:
+            report(3, "avgpool 2x2 fwd N=%d C=%d %dx%d" % (n, c, hw, hw), timeit(lambda i: capi.avgpool_fwd(pooled, x, (2, 2), 0.25), 1), 5 * e)
+            report(3, "avgpool 2x2 bwd N=%d C=%d %dx%d" % (n, c, hw, hw), timeit(lambda i: capi.avgpool_bwd(dx, dpo, (2, 2), 0.25), 1), 5 * e)
+        del x, pooled, idx, dpo, dx
     # training batch norm + ReLU on the last stage's 7x7 planes (not whole float4s: the channel-group kernels)
     for n, c, hw in [(1024, 512, 7), (256, 2048, 7)]:
         shape = (n, c, hw, hw)
