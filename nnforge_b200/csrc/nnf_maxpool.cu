@@ -59,7 +59,8 @@ namespace nnf
 		// WW/WH > 0: window extents known at compile time (fully unrolled); CLIP: the window may stick out
 		// of the input (round-up) and is clipped. The scan order (x fastest) and the strict compare are the
 		// plain backend's (max_subsampling_layer_updater_plain.cpp:146-159).
-		template <int WW, int WH, bool CLIP>
+		// MINMAX: 0 = the layer's is_min flag is read per candidate, 1 = maximum, 2 = minimum (decided once per call site)
+		template <int WW, int WH, bool CLIP, int MINMAX = 0>
 		__device__ __forceinline__ void scan_window(const pool_geom& g, const float * src, uint32_t oy, uint32_t ox, float& best, uint32_t& best_off)
 		{
 			const int win_w = WW ? WW : g.win_w, win_h = WH ? WH : g.win_h;
@@ -81,7 +82,7 @@ namespace nnf
 						break;
 					const uint32_t off = off0 + ky * g.w + kx;
 					const float v = src[off];
-					const bool better = g.is_min ? (v < best) : (v > best);
+					const bool better = MINMAX == 1 ? (v > best) : (MINMAX == 2 ? (v < best) : (g.is_min ? (v < best) : (v > best)));
 					if (better)
 					{
 						best = v;
@@ -225,6 +226,7 @@ namespace nnf
 				// phase 2: windows from shared memory
 				const uint32_t nout = np * g.ohw;
 				const int64_t obase = plane0 * g.ohw;
+				const bool is_min = g.is_min != 0;   // uniform: the comparison is chosen once, not per candidate
 				for (uint32_t o = threadIdx.x; o < nout; o += kThreads)
 				{
 					const uint32_t lp = g.d_ohw.div(o);
@@ -233,7 +235,10 @@ namespace nnf
 					const uint32_t ox = rem - oy * g.ow;
 					float best;
 					uint32_t off;
-					scan_window<WW, WH, CLIP>(g, s_z + lp * g.hw, oy, ox, best, off);
+					if (is_min)
+						scan_window<WW, WH, CLIP, 2>(g, s_z + lp * g.hw, oy, ox, best, off);
+					else
+						scan_window<WW, WH, CLIP, 1>(g, s_z + lp * g.hw, oy, ox, best, off);
 					st_stream(p.pooled + obase + o, best);
 					if (p.argmax)
 						p.argmax[obase + o] = (uint32_t)(base + int64_t(lp) * g.hw + off);
