@@ -274,9 +274,6 @@ def run_sweep(args):
     m = N_PER_GPU * H * W
     report(2, "bn_train fwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
     report(2, "bn_train bwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_bwd(dx, bs, dy, x, g, b, saved, acts, workspace=ws), 1), 12 * e)
-    os.environ["NNF_FUSED_MODE"] = "3"
-    report(2, "bn_train fwd, shared-memory slab cluster kernel", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
-    del os.environ["NNF_FUSED_MODE"]
     report(2, "bn_train stats", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
     report(2, "bn_train apply+prelu+elu", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, g, b, sums, m, EPS, acts), 1), 8 * e)
     report(2, "bn_train bwd stats", timeit(lambda i: capi.bn_train_bwd_stats(bs, dy, x, g, b, saved, acts, ws), 1), 8 * e)

@@ -73,6 +73,33 @@ typedef struct nnf_act
 NNF_API const char * nnf_last_error_string(void);
 NNF_API int nnf_version(void);
 
+/* What the current device offers, by the field names of nnForge's cuda_running_configuration
+ * (nnforge/cuda/cuda_running_configuration.h:126-153: device_id, compute_capability_major/minor,
+ * multiprocessor_count, ...), filled from cudaDeviceGetAttribute once per device. The launch plans of
+ * this library size their grids and shared-memory tiles from it; the host-side layer objects hand it to
+ * their factory the way layer_testing_schema::create_tester receives the cuda_running_configuration
+ * (nnforge/cuda/layer_testing_schema.cpp:25-51). */
+typedef struct nnf_running_configuration
+{
+	int32_t device_id;
+	int32_t compute_capability_major, compute_capability_minor;
+	int32_t multiprocessor_count;
+	int32_t max_threads_per_multiprocessor;
+	int32_t max_shared_memory_per_block_optin;
+	int32_t max_shared_memory_per_multiprocessor;
+	int32_t l2_cache_size;
+	int32_t max_registers_per_multiprocessor;
+} nnf_running_configuration;
+NNF_API int nnf_get_running_configuration(nnf_running_configuration * out);
+
+/* Knobs of the launch plans (process-wide; nothing in the library reads the environment). No counterpart in
+ * the reference. name: "elementwise_waves", "elementwise_group_waves", "pool_waves", "pool_group_floats",
+ * "channel_waves", "group_waves", "chain_s_kb", "chain_a_kb", "chain_dist" (-1: built-in), "chain_chunk_mb",
+ * "chain_lag" (lag + 1), "no_grouped", "apply_flat", "peer_wait_ns" (how long a batch-sharded launch waits for
+ * another rank's statistics before it gives up; default 10 s), or "reset" (all back to the built-in choices).
+ * A value <= 0 selects the built-in choice. Meant for tests that walk the geometries and for tuning. */
+NNF_API int nnf_set_tuning(const char * name, long long value);
+
 /* ---------------------------------------------------------------------------------------------
  * Inference batch norm (+ residual add) (+ activation chain), one HBM pass.
  *   t = x*mult + add,  mult = gamma*invsigma,  add = beta - mult*mean        (gamma != NULL)
@@ -233,11 +260,13 @@ NNF_API int nnf_bn_train_apply_act(nnf_stream_t stream, float * y, float * saved
 	const float * gamma, const float * beta, const float * sums, double count_total, float eps,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw);
 
-/* Single-GPU forward in one call. When one channel's slab (n*hw floats) fits the shared memory of a
- * thread-block cluster, a single-pass kernel reads x once and writes y once (8 bytes/element); other
- * shapes run nnf_bn_train_stats + nnf_bn_train_apply_act, for which `sums` (2C floats) and the
- * workspace are required. saved receives {mean, invstd}; sums (may be NULL for fitting shapes)
- * receives {sum x, sum x^2}. Replaces batch_norm_layer_updater_cuda::enqueue_forward_propagation
+/* Single-GPU forward in one call and, for 16-byte aligned tensors whose planes are whole float4s or fill
+ * channel groups, one launch: statistics items and apply items share it and the second read of x comes
+ * from L2 (8 bytes/element through HBM). Other shapes run nnf_bn_train_stats + nnf_bn_train_apply_act,
+ * for which `sums` (2C floats) is required. The workspace (nnf_bn_train_workspace_bytes, 16-byte aligned)
+ * is always required: NNF_ERR_WORKSPACE without it. saved receives {mean, invstd}; sums (may be NULL for
+ * single-launch shapes) receives {sum x, sum x^2}. Replaces
+ * batch_norm_layer_updater_cuda::enqueue_forward_propagation
  * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:60-107) plus the activation layers behind it. */
 NNF_API int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
 	const float * gamma, const float * beta, float eps,
@@ -245,10 +274,10 @@ NNF_API int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, floa
 	void * workspace, size_t workspace_bytes);
 
 /* Single-GPU backward in one call: dx, bsums[3C] = {sum du, sum du*xhat, sum dslope} and the accumulated
- * per-channel gradients (see nnf_bn_train_bwd_apply). Where a channel's du slab fits a cluster's shared
- * memory a single-pass kernel reads x and dy from HBM once and writes dx once (12 bytes/element; x is
- * read a second time a few microseconds later, from L2); other shapes run nnf_bn_train_bwd_stats +
- * nnf_bn_train_bwd_apply with the workspace. Replaces enqueue_backward_data_and_weights_propagation
+ * per-channel gradients (see nnf_bn_train_bwd_apply). The shapes of nnf_bn_train_fwd's single launch take
+ * one launch here too (x and dy read from HBM once, a second time from L2, dx written once: 12
+ * bytes/element); other shapes, and add_to_destination, run nnf_bn_train_bwd_stats +
+ * nnf_bn_train_bwd_apply. dx may be dy or x. Replaces enqueue_backward_data_and_weights_propagation
  * (nnforge/cuda/batch_norm_layer_updater_cuda.cu:109-183) plus the activation layers' backward actions. */
 NNF_API int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, const float * dy, const float * x,
 	const float * gamma, const float * beta, const float * saved,
@@ -258,9 +287,30 @@ NNF_API int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, con
 	int64_t n, int64_t c, int64_t hw, int add_to_destination,
 	void * workspace, size_t workspace_bytes);
 
-/* Returns the error word (and clears it): 1 when a single-pass kernel gave up a bounded wait since the
- * last check, 2 when a peer exchange did, 0 otherwise, -1 if the word cannot be read. Synchronises the
- * device: for tests and diagnosis. */
+/* What a single-launch training batch-norm call (nnf_bn_train_fwd / _bwd and their _sharded forms) reports:
+ * every such launch starts by clearing this block at the head of its workspace and leaves in it
+ *   status        0, or the code of a bounded wait that ran out: 2 = another rank's statistics did not
+ *                 arrive within the limit ("peer_wait_ns"), 4 = this GPU's own items did not finish;
+ *                 the launch then completed with what it had and its outputs are not to be used
+ *   wait_ns_*     how long its waiting items waited, summed and the longest
+ * nnf_bn_train_read_report enqueues the copy of the block into host memory (pinned, for an asynchronous
+ * copy) on `stream`, after the launches already enqueued there; the caller looks at it once the stream
+ * has passed that point - e.g. before the next step - and repeats the step another way (the split entry
+ * points with an NCCL all-reduce) when status is not 0. A failed launch does not affect later ones. No
+ * counterpart in the reference, whose layers cannot fail on the device. */
+typedef struct nnf_launch_report
+{
+	uint64_t wait_ns_total;
+	uint64_t wait_ns_max;
+	uint32_t reserved;
+	int32_t status;
+} nnf_launch_report;
+NNF_API int nnf_bn_train_read_report(nnf_stream_t stream, nnf_launch_report * host_report, const void * workspace);
+
+/* Returns the library's process-wide error word (and clears it): the code of the last bounded wait that
+ * ran out anywhere since the last check (2 = a peer exchange, 4 = a single-launch kernel's own items), 0
+ * otherwise, -1 if the word cannot be read. Kernels only ever raise it. Synchronises the device: for
+ * tests and diagnosis; nnf_bn_train_read_report is the per-launch, asynchronous way. */
 NNF_API int nnf_fused_error_check(void);
 
 NNF_API int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
@@ -376,7 +426,7 @@ NNF_API int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * pre
  * nnf_bn_train_fwd / nnf_bn_train_bwd): statistics and apply work items share the launch, the second read
  * of x (and dy) comes from L2, and the per-channel sums cross the GPUs inside the launch - the item that
  * finishes a channel's statistics stores this rank's two sums into every rank's mailbox, an apply item
- * waits (bounded, about a second; expiry raises the word read by nnf_fused_error_check, value 2) until
+ * waits (bounded by "peer_wait_ns"; expiry sets status 2 in the launch's report, see nnf_bn_train_read_report) until
  * its own mailbox holds the sums of all ranks for its channel and adds them in rank order. Replaces the
  * sequence statistics kernel -> all-reduce (nnforge/cuda/nccl_cuda_communicator.cpp:72-94) -> apply kernel.
  * Every rank owns one zero-initialised mailbox of nnf_bn_train_mailbox_bytes(c) bytes that all ranks can

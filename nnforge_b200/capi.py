@@ -49,9 +49,22 @@ MOMENTUM_NONE, MOMENTUM_VANILLA, MOMENTUM_NESTEROV, MOMENTUM_ADAM = range(4)
 
 _ACTP, _POOLP = ct.POINTER(Act), ct.POINTER(Pool)
 
+class RunningConfiguration(ct.Structure):
+    _fields_ = [(name, ct.c_int32) for name in (
+        "device_id", "compute_capability_major", "compute_capability_minor", "multiprocessor_count", "max_threads_per_multiprocessor",
+        "max_shared_memory_per_block_optin", "max_shared_memory_per_multiprocessor", "l2_cache_size", "max_registers_per_multiprocessor")]
+
+
+class LaunchReport(ct.Structure):
+    _fields_ = [("wait_ns_total", ct.c_uint64), ("wait_ns_max", ct.c_uint64), ("reserved", ct.c_uint32), ("status", ct.c_int32)]
+
+
 _SIGNATURES = {
     "nnf_last_error_string": (ct.c_char_p, []),
     "nnf_version": (_I, []),
+    "nnf_get_running_configuration": (_I, [ct.POINTER(RunningConfiguration)]),
+    "nnf_set_tuning": (_I, [ct.c_char_p, ct.c_longlong]),
+    "nnf_bn_train_read_report": (_I, [_P, _P, _P]),
     "nnf_bn_infer_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64]),
     "nnf_bias_bn_infer_act": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _ACTP, _I, _I64, _I64, _I64]),
     "nnf_act_fwd": (_I, [_P, _P, _P, _ACTP, _I64, _I64, _I64]),
@@ -321,6 +334,36 @@ def peer_exchange_sum(out, local, peer_ptrs, rank, world, kmax, seq, stream=None
 
 def fused_error_check():
     return int(lib.nnf_fused_error_check())
+
+
+def running_configuration():
+    """The current device as the launch plans see it (a dict by nnForge's cuda_running_configuration field names)."""
+    cfg = RunningConfiguration()
+    _check(lib.nnf_get_running_configuration(ct.byref(cfg)))
+    return {name: int(getattr(cfg, name)) for name, _ in RunningConfiguration._fields_}
+
+
+def set_tuning(name, value):
+    """One knob of the launch plans (see nnf_set_tuning in the header); set_tuning("reset", 0) restores the built-in choices."""
+    _check(lib.nnf_set_tuning(name.encode(), int(value)))
+
+
+REPORT_WORDS = ct.sizeof(LaunchReport) // 8
+
+
+def read_report(host_words, workspace, stream=None):
+    """Enqueues the copy of the launch report at the head of `workspace` into `host_words` (a pinned int64 tensor of
+    REPORT_WORDS elements); parse it with parse_report() once the stream has passed this point."""
+    assert host_words.dtype == torch.int64 and host_words.numel() >= REPORT_WORDS and not host_words.is_cuda
+    _check(lib.nnf_bn_train_read_report(_stream(stream), host_words.data_ptr(), _ptr(workspace)))
+
+
+def parse_report(host_words):
+    w = [int(v) & 0xFFFFFFFFFFFFFFFF for v in host_words[:REPORT_WORDS].tolist()]
+    status = (w[2] >> 32) & 0xFFFFFFFF
+    if status >= 1 << 31:
+        status -= 1 << 32
+    return {"wait_ns_total": w[0], "wait_ns_max": w[1], "status": status}
 
 
 def bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, workspace, gsums=None, stream=None):

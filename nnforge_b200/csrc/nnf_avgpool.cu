@@ -18,7 +18,6 @@ namespace nnf
 	{
 		constexpr int kAvgThreads = 256;
 		constexpr int kAvgMaxGroup = 512;
-		constexpr size_t kAvgMaxSmem = 200 * 1024;
 
 		struct avg_params
 		{
@@ -419,7 +418,7 @@ namespace nnf
 				const int64_t out_rows = p.planes * p.oh;
 				const uint32_t w4 = p.w / 4;
 				const int64_t blocks = div_up(out_rows * w4, kAvgThreads * 2);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 64 ? blocks : int64_t(sm_count()) * 64);
 				avgpool_fwd_2x2_kernel<<<grid, kAvgThreads, 0, s>>>(p.pooled, p.x, out_rows, w4, fastdiv(w4), p.mult);
 				return check_launch("avgpool_fwd_2x2_kernel");
 			}
@@ -429,7 +428,7 @@ namespace nnf
 				const int64_t out_rows = p.planes * p.oh;
 				const uint32_t w2 = p.w / 2;
 				const int64_t blocks = div_up(out_rows * w2, kAvgThreads * 4);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 64 ? blocks : int64_t(sm_count()) * 64);
 				avgpool_fwd_2x2_pair_kernel<<<grid, kAvgThreads, 0, s>>>(p.pooled, p.x, out_rows, w2, fastdiv(w2), p.mult);
 				return check_launch("avgpool_fwd_2x2_pair_kernel");
 			}
@@ -444,31 +443,31 @@ namespace nnf
 			if (group > unit)
 				group -= group % unit;
 			const size_t smem = size_t(group) * plane_bytes;
-			if (smem > kAvgMaxSmem)
+			if (smem > staging_smem_limit())
 			{
 				if (fused)
-					return set_error(NNF_ERR_UNSUPPORTED, "fused average pooling needs planes of at most %zu bytes", kAvgMaxSmem);
+					return set_error(NNF_ERR_UNSUPPORTED, "fused average pooling needs planes of at most %zu bytes", staging_smem_limit());
 				const int64_t blocks = div_up(p.planes * p.ohw, kAvgThreads);
-				avgpool_fwd_direct_kernel<<<(int)(blocks < int64_t(kSmCount) * 8 ? blocks : int64_t(kSmCount) * 8), kAvgThreads, 0, s>>>(p);
+				avgpool_fwd_direct_kernel<<<(int)(blocks < int64_t(sm_count()) * 8 ? blocks : int64_t(sm_count()) * 8), kAvgThreads, 0, s>>>(p);
 				return check_launch("avgpool_fwd_direct_kernel");
 			}
 			p.group = (uint32_t)group;
 			p.vec_ok = ((group * p.hw) % 4 == 0 && aligned16(p.x) && (!p.res || aligned16(p.res)) && (!p.z || aligned16(p.z))) ? 1 : 0;
 			const int64_t ngroups = div_up(p.planes, group);
-			int per_sm = (int)((200 * 1024) / (smem + 4096 + 1024));
+			int per_sm = (int)(staging_smem_limit() / (smem + 4096 + 1024));
 			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-			const int64_t cap = int64_t(kSmCount) * per_sm * 4;
+			const int64_t cap = int64_t(sm_count()) * per_sm * 4;
 			const int grid = (int)(ngroups < cap ? ngroups : cap);
 			cudaError_t e;
 			if (fused)
 			{
-				e = cudaFuncSetAttribute(avgpool_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAvgMaxSmem);
+				e = cudaFuncSetAttribute(avgpool_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit());
 				if (e == cudaSuccess)
 					avgpool_fwd_kernel<true><<<grid, kAvgThreads, smem, s>>>(p);
 			}
 			else
 			{
-				e = cudaFuncSetAttribute(avgpool_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAvgMaxSmem);
+				e = cudaFuncSetAttribute(avgpool_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit());
 				if (e == cudaSuccess)
 					avgpool_fwd_kernel<false><<<grid, kAvgThreads, smem, s>>>(p);
 			}
@@ -488,7 +487,7 @@ namespace nnf
 				const int64_t out_rows = p.planes * p.oh;
 				const uint32_t w2 = p.w / 2;
 				const int64_t blocks = div_up(out_rows * w2, kAvgThreads * 4);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 64 ? blocks : int64_t(sm_count()) * 64);
 				avgpool_bwd_2x2_pair_kernel<<<grid, kAvgThreads, 0, s>>>(p.dx, p.dpooled, out_rows, w2, fastdiv(w2), p.mult, p.add);
 				return check_launch("avgpool_bwd_2x2_pair_kernel");
 			}
@@ -508,7 +507,7 @@ namespace nnf
 				if ((base & 3) != 0)
 					q.vec_ok = 0;
 				const int64_t blocks = div_up(int64_t(count) / 4 + 1, kAvgThreads);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 64 ? blocks : int64_t(kSmCount) * 64);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 64 ? blocks : int64_t(sm_count()) * 64);
 				if (fused)
 					avgpool_bwd_kernel<true><<<grid, kAvgThreads, 0, s>>>(q, base, count);
 				else

@@ -2,39 +2,44 @@
 // by the L2 cache: HBM sees x (and dy) once and the result once - 8 bytes/element forward, 12
 // backward - although the work is still "statistics, then normalise".
 //
-// One launch holds two kinds of work items, each run by one CTA of 256 threads:
-//   S(channel, slice)  statistics: partial per-channel sums over a slice of the entries, written to
-//                      the workspace; the item then counts itself done for its channel
-//   A(channel, slice)  apply: waits until every S item of its channel is done, adds their partial sums
-//                      in slice order (double, deterministic), and normalises its slice
-// The items are ordered in chunks of channels: S(chunk 0), S(chunk 1), A(chunk 0), S(chunk 2),
-// A(chunk 1), ... so that the A items of a chunk run while the next chunk's statistics are being
-// read: the lines of x that the S items pulled in a few microseconds earlier are still in the 126 MB
-// L2 (a chunk is a few tens of MB), and HBM carries a steady mix of reads and writes instead of a
-// read-only kernel followed by a read-write one.
+// One launch holds three kinds of work items, each run by one CTA of 256 threads that draws a ticket
+// from a global counter (tickets are handed out in the order in which CTAs start running, so no
+// assumption is made about the order in which the hardware dispatches blocks):
+//   S(channel, slice)  statistics over a slice of the entries: every warp leaves its partial sums in the
+//                      workspace as 8-byte words that carry the launch's tag next to the value, so a
+//                      reader can tell them from stale ones - no counter, no fence, nothing to wait for
+//   F(channel)         one warp: waits (bounded) until every deposit of the channel carries the tag, adds
+//                      them in a fixed order in double, derives the channel's constants (and writes the
+//                      per-channel outputs), releases the channel's apply items
+//   A(channel, slice)  apply: issues its first copies, then waits (bounded) for F(channel), normalises
+// Ticket step k holds S(k), F(k - dist/2) and A(k - dist), interleaved, so that the apply items of a
+// channel run while later channels' statistics are being read: the lines of x that the S items pulled in
+// a few microseconds earlier are still in the 126 MB L2 (they are loaded with an evict-last hint, the
+// second read with evict-first, the result with streaming stores), and HBM carries a steady mix of
+// reads and writes. Every item with a smaller ticket than a waiting one is running or finished, so the
+// waits cannot deadlock; they are bounded all the same, and on expiry the launch's own status word (in
+// the workspace, cleared by the memset that precedes every launch) is raised and the launch finishes
+// with what it has.
 //
-// A CTA does not use its block index: it draws a ticket from a global counter, and tickets are
-// handed out in the order in which CTAs start running. Every S item of a channel has a smaller
-// ticket than any A item of that channel, so whenever an A item waits, the items it waits for are
-// already running or finished - no assumption about the order in which the hardware dispatches
-// blocks, and no co-residency requirement. The wait is bounded all the same; when it runs out the
-// CTA raises the library's error word (code 4) and carries on with what it has.
+// Global memory reaches the threads through shared memory without occupying registers: a thread copies
+// its 16-byte pieces of the next sweeps with cp.async into slots that only it reads back (no barrier),
+// two or three sweeps ahead. A sweep is as many whole planes of the channel (consecutive entries) as fill
+// the CTA's 1024 vector slots; a thread's slot offsets inside a sweep never change, so the loop has no
+// index division.
 //
-// The counters (one per channel, and the ticket) live in the caller's workspace and are cleared by
-// a memset on the same stream before the launch.
+// Batch-sharded form (one process per GPU, the same launch on every GPU): F(channel) folds this rank's
+// deposits, stores the rank's two sums into the mailbox of EVERY rank as two self-validating 8-byte
+// words (32 bits of a float + the exchange's sequence number; plain peer stores over NVLink), waits
+// (bounded by the configured limit) until its own mailbox holds the words of all ranks, adds them in
+// rank order and releases the apply items. Only the finishing warps ever look at peer memory; S items
+// never wait, so a rank's statistics always get published whatever the skew between the GPUs.
 //
-// Batch-sharded form (one process per GPU, the same launch on every GPU): the S item that finishes a
-// channel last folds this rank's partial sums and stores them, as two self-validating 8-byte words
-// (32 bits of a float + the exchange's sequence number), into the mailbox of EVERY rank - plain
-// peer stores over NVLink; an A item polls its OWN mailbox until the words of all ranks for its
-// channel carry the sequence number, and adds them in rank order (fp32, as the other exchange forms
-// do). So the exchange is per channel and overlaps the rest of the launch: no collective call, no
-// kernel boundary. An S item never waits, so a rank's statistics always get published and the A
-// items of every rank make progress whatever the skew between the GPUs; the wait is bounded (about a
-// second; code 2), and once the error word is set the remaining waits end at once.
+// Planes that are not whole float4s (7x7, 13x13) take the channel-group kernel further down, whose
+// items follow an older scheme (counters, chunks of channel groups, apply items that fold the sums).
 #include "nnf_common.cuh"
 
-#include <stdlib.h>
+#include <atomic>
+#include <mutex>
 
 namespace nnf
 {
@@ -89,7 +94,10 @@ namespace nnf
 			double * partial;            // [c][split_s][3]
 			uint32_t * done;             // [c] finished S items per channel; zero at kernel start
 			uint32_t * ticket;           // zero at kernel start
-			int * error;
+			int * error;                 // the launch's status word (in the workspace head; zero at kernel start)
+			int * error_word;            // the library's process-wide word: raised too, never consulted
+			unsigned long long wait_limit_ns;
+			unsigned long long * wait_ns; // the launch report's {sum, longest} of the waits for other ranks
 		};
 
 		__device__ __forceinline__ uint32_t ld_acquire(const uint32_t * p)
@@ -118,7 +126,7 @@ namespace nnf
 			return t;
 		}
 
-		constexpr unsigned long long kChainPeerWaitNs = 1000000000ull; // an A item waits this long for the other ranks
+		constexpr unsigned long long kDefaultPeerWaitNs = 10000000000ull; // a launch waits this long for another rank's statistics unless told otherwise
 
 		__device__ __forceinline__ size_t mail_index(const chain_params& p, uint32_t source_rank, uint32_t ch)
 		{
@@ -204,148 +212,306 @@ namespace nnf
 			ch = sp = 0;
 		}
 
+		// ---- the kernel for planes of whole float4s ------------------------------------------------------------
+		constexpr int kStreamSlots = 4;                 // 16-byte slots of a thread in one sweep
+		constexpr int kStreamWarps = kChainThreads / 32;
+		constexpr int kStagesFwd = 3, kStagesBwd = 2;   // sweeps in flight per thread
+		constexpr int kCtasFwd = 4, kCtasBwd = 3;       // resident CTAs per SM the register budget is cut for
+
+		// The head of every workspace: what a launch reports. Cleared by the memset in front of the launch.
+		struct launch_report
+		{
+			unsigned long long wait_ns_total;   // time the waiting items spent waiting, summed
+			unsigned long long wait_ns_max;     // the longest single wait
+			uint32_t reserved;
+			int status;                         // 0, or the code of the bounded wait that ran out (2: another rank, 4: this GPU's own items)
+			uint32_t pad0[26];
+			uint32_t ticket;                    // every CTA of the launch draws from it: alone on its 128-byte line
+			uint32_t pad1[31];
+		};
+		static_assert(sizeof(launch_report) == 256, "the report is two 128-byte lines");
+
+		struct stream_params
+		{
+			const float * x;
+			const float * dy;        // backward only
+			float * out;             // y (forward) or dx (backward)
+			const float * gamma;
+			const float * beta;
+			float * saved;           // forward: written {mean, invstd}; backward: read
+			float * sums;            // forward: {sum x, sum x^2} of this shard (may be null); backward: bsums[3C]
+			float * grad_gamma, * grad_beta, * grad_mean, * grad_invsigma, * grad_slope;
+			const float * mean, * invsigma;
+			float entry_count;
+			act_chain chain;
+			uint32_t n, c, hw, vpp;
+			uint32_t rows, cols, tiles;        // a sweep: `rows` whole planes of `cols` vectors, or one column tile of a wide plane
+			uint32_t es, ea, ss, sa;           // entries per S / A item, items per channel
+			uint32_t dist, dist_f;             // A(k - dist) and F(k - dist_f) share ticket step k with S(k)
+			uint32_t total;
+			fastdiv d_cols, d_per, d_both, d_rows;
+			double count, count_total;         // elements per channel on this rank / over all ranks
+			float eps;
+			uint32_t tag;                      // this launch's tag in the deposit words
+			unsigned long long * deposit;      // [c][ss][4] tagged words
+			float4 * fin;                      // [c][2] per-channel constants for the A items
+			uint32_t * ready;                  // [c]
+			launch_report * report;
+			int * error_word;                  // the library's process-wide word: raised too, never consulted
+			// batch-sharded runs: mail[r] = mailbox of rank r (peer memory), mail[rank] this GPU's own;
+			// words [2 parities][kMaxRanks source ranks][c][2]
+			unsigned long long * mail[kMaxRanks];
+			int rank, world;
+			uint32_t seq;
+			unsigned long long wait_limit_ns;
+		};
+
+		__device__ __forceinline__ void st_relaxed_u64(unsigned long long * p, unsigned long long v)
+		{
+			asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+		}
+
+		__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long * p)
+		{
+			unsigned long long v;
+			asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+			return v;
+		}
+
+		__device__ __forceinline__ void st_release_u32(uint32_t * p, uint32_t v)
+		{
+			asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+		}
+
+		__device__ __forceinline__ void cp_async16(void * dst_smem, const char * src, uint64_t policy)
+		{
+			asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+				:: "r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src), "l"(policy) : "memory");
+		}
+
+		__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+		template <int N>
+		__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+		__device__ __forceinline__ float stream_warp_sum(float v)
+		{
+			#pragma unroll
+			for (int o = 16; o > 0; o >>= 1)
+				v += __shfl_xor_sync(0xffffffffu, v, o);
+			return v;
+		}
+
+		__device__ __forceinline__ size_t mail_index(const stream_params& p, uint32_t source_rank, uint32_t ch)
+		{
+			return ((size_t(p.seq & 1u) * kMaxRanks + source_rank) * p.c + ch) * 2;
+		}
+
+		// Backward through the chain from u = bn output: returns du, `term` = the PReLU slope gradient's term. PReLU
+		// followed by ELU, the chain the kernel is measured on, has a shorter form: the ELU's derivative for a
+		// negative input, (e^t - 1) + 1 in the layer-by-layer arithmetic, is taken as e^t itself (they differ by
+		// one rounding of a number near 1, far inside the tolerance of this row).
+		template <int A0, int A1>
+		__device__ __forceinline__ float stream_backward(const act_chain& ch, float u, float dy, float slope, float& term)
+		{
+			if constexpr (A0 == NNF_ACT_PRELU && A1 == NNF_ACT_ELU)
+			{
+				const float k = u >= 0.0F ? 1.0F : slope;
+				const float t1 = u * k;
+				const float e = fast_exp(t1);
+				const float g = dy * (t1 >= 0.0F ? 1.0F : e);
+				term = g * fminf(u, 0.0F);
+				return g * k;
+			}
+			else
+				return chain_backward<A0, A1>(ch, u, dy, slope, term);
+		}
+
 		template <int A0, int A1, bool BWD, bool PEER>
-		__global__ void __launch_bounds__(kChainThreads, NNF_CHAIN_MIN_CTAS) bn_train_chain_kernel(const chain_params p)
+		__global__ void __launch_bounds__(kChainThreads, BWD ? kCtasBwd : kCtasFwd) bn_train_chain_kernel(const stream_params p)
 		{
 			constexpr int K = BWD ? 3 : 2;
-			constexpr int kLoadsS = BWD ? NNF_CHAIN_LOADS_BWD : NNF_CHAIN_LOADS_FWD; // independent 128-bit loads in flight per thread and tensor
-			constexpr int kLoadsA = kLoadsS;
-			__shared__ double s_red[(kChainThreads / 32) * K];
+			constexpr int T = BWD ? 2 : 1;
+			constexpr int L = kStreamSlots;
+			constexpr int STAGES = BWD ? kStagesBwd : kStagesFwd;
+			extern __shared__ float4 ring[];   // [STAGES][T][L][kChainThreads]: a thread reads back only what it copied itself
 			__shared__ uint32_t s_item[4];
-			__shared__ float s_tot[4];
+			__shared__ float4 s_fin[2];
+			__shared__ float s_sum[kStreamWarps][3];
 
 			if (threadIdx.x == 0)
 			{
-				const uint32_t t = atomicAdd(p.ticket, 1u);
-				uint32_t apply, ch, sp;
-				decode_ticket(p, t, apply, ch, sp);
-				s_item[0] = apply;
-				s_item[1] = ch;
-				s_item[2] = sp;
+				// step k of the ticket order holds the finishing item of channel k - dist_f, then the statistics items of
+				// channel k and the apply items of channel k - dist, interleaved; items of channels outside [0, c) are empty
+				const uint32_t t = atomicAdd(&p.report->ticket, 1u);
+				uint32_t kind = 3, chq = 0, sp = 0;
+				const uint32_t per = p.ss + p.sa + 1;
+				const uint32_t step = p.d_per.div(t);
+				const uint32_t i = t - step * per;
+				if (i == 0)
+				{
+					if (step >= p.dist_f && step - p.dist_f < p.c) { kind = 2; chq = step - p.dist_f; }
+				}
+				else
+				{
+					const uint32_t j = i - 1;
+					const uint32_t s0 = p.d_both.div(j * p.ss), s1 = p.d_both.div((j + 1) * p.ss);
+					if (s1 > s0) { if (step < p.c) { kind = 0; chq = step; sp = s0; } }
+					else if (step >= p.dist && step - p.dist < p.c) { kind = 1; chq = step - p.dist; sp = j - s0; }
+				}
+				s_item[0] = kind; s_item[1] = chq; s_item[2] = sp;
 			}
 			__syncthreads();
 			// the backward launch walks the channels downwards: whatever ran before it (the forward launch walks
 			// upwards) left the highest channels of x in L2
-			const uint32_t apply = s_item[0], ch = BWD ? p.c - 1 - s_item[1] : s_item[1], sp = s_item[2];
-			if (apply > 1)
+			const uint32_t kind = s_item[0], ch = BWD ? p.c - 1 - s_item[1] : s_item[1], sp = s_item[2];
+			if (kind > 2)
 				return;
-			const uint32_t per_plane = p.hw >> 2;
-			const size_t entry_stride = size_t(p.c) * p.hw;
+			const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+			const uint32_t deposits = p.ss;
 
-			if (!apply)
+			if (kind == 2)
 			{
-				// ---- S item --------------------------------------------------------------------------
-				const uint32_t e0 = sp * p.entries_s;
-				const uint32_t e1 = min(e0 + p.entries_s, p.n);
-				const uint32_t total = e1 > e0 ? (e1 - e0) * per_plane : 0;
-				const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
-				double acc[K];
-				if (!BWD)
+				// ---- F item ------------------------------------------------------------------------------
+				if (warp != 0)
+					return;
+				const unsigned long long * part = p.deposit + size_t(ch) * deposits * 4;
+				double tot[K];
+				bool ok = false;
+				const unsigned long long t0 = chain_timer_ns();
+				for (uint32_t round = 0; round < kChainPollLimit; ++round)
 				{
-					float s = 0.0F, q = 0.0F;
-					for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kChainThreads * kLoadsS)
+					bool all = true;
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						tot[k] = 0.0;
+					for (uint32_t e = lane; e < deposits; e += 32)
 					{
-						float4 a[kLoadsS];
 						#pragma unroll
-						for (int u = 0; u < kLoadsS; ++u)
+						for (int k = 0; k < K; ++k)
 						{
-							const uint32_t i = i0 + u * kChainThreads;
-							a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-							if (i < total)
-							{
-								const uint32_t lp = p.d_vpp.div(i);
-								a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + off0 + lp * entry_stride) + (i - lp * per_plane)); // default policy: stays in L2
-							}
-						}
-						#pragma unroll
-						for (int u = 0; u < kLoadsS; ++u)
-						{
-							s += (a[u].x + a[u].y) + (a[u].z + a[u].w);
-							q = fmaf(a[u].x, a[u].x, fmaf(a[u].y, a[u].y, fmaf(a[u].z, a[u].z, fmaf(a[u].w, a[u].w, q))));
+							const unsigned long long w = ld_relaxed_u64(part + e * 4 + k);
+							all = all && uint32_t(w >> 32) == p.tag;
+							tot[k] += double(__uint_as_float(uint32_t(w)));
 						}
 					}
-					acc[0] = double(s);
-					acc[1] = double(q);
+					if (__all_sync(0xffffffffu, all))
+					{
+						ok = true;
+						break;
+					}
+					if ((round & 63) == 63 && *reinterpret_cast<volatile int *>(&p.report->status) != 0)
+						break;
+					__nanosleep(200);
+				}
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					tot[k] = chain_warp_sum(tot[k]);
+				if (!ok && lane == 0)
+				{
+					p.report->status = 4;
+					if (p.error_word) *p.error_word = 4;
+				}
+				// this rank's sums as the other entry points define them: {sum x, sum x^2} forward (the deposits are taken
+				// around the channel's first element, undone here in double), {sum du, sum du*xhat, sum slope terms} backward
+				float m0, m1, m2 = 0.0F;
+				const float saved_mean = BWD ? __ldg(p.saved + ch) : 0.0F, saved_invstd = BWD ? __ldg(p.saved + p.c + ch) : 0.0F;
+				const double shift = BWD ? 0.0 : double(__ldg(p.x + size_t(ch) * p.hw));
+				if (!BWD)
+				{
+					m0 = float(tot[0] + p.count * shift);
+					m1 = float(tot[1] + 2.0 * shift * tot[0] + p.count * shift * shift);
 				}
 				else
 				{
-					const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
-					const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
-					const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
-					const float slope = chain_slope(p.chain, ch);
-					float sb = 0.0F, sg = 0.0F, ss = 0.0F;
-					auto element = [&](float x, float dy)
-					{
-						const float u = __fadd_rn(__fmul_rn(x, mult), add);
-						float term;
-						const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
-						const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
-						sb += du;
-						sg = fmaf(du, xhat, sg);
-						ss += term;
-					};
-					for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kChainThreads * kLoadsS)
-					{
-						float4 a[kLoadsS], d[kLoadsS];
-						#pragma unroll
-						for (int u = 0; u < kLoadsS; ++u)
-						{
-							const uint32_t i = i0 + u * kChainThreads;
-							if (i < total)
-							{
-								const uint32_t lp = p.d_vpp.div(i);
-								const size_t off = off0 + lp * entry_stride;
-								a[u] = __ldg(reinterpret_cast<const float4 *>(p.x + off) + (i - lp * per_plane));
-								d[u] = __ldg(reinterpret_cast<const float4 *>(p.dy + off) + (i - lp * per_plane));
-							}
-						}
-						#pragma unroll
-						for (int u = 0; u < kLoadsS; ++u)
-							if (i0 + u * kChainThreads < total)
-							{
-								element(a[u].x, d[u].x); element(a[u].y, d[u].y); element(a[u].z, d[u].z); element(a[u].w, d[u].w);
-							}
-					}
-					acc[0] = double(sb);
-					acc[1] = double(sg);
-					acc[2] = double(ss);
+					m0 = float(tot[0]);
+					m1 = float(tot[1] * double(saved_invstd));
+					m2 = float(tot[2]);
 				}
-				chain_block_sum<K>(acc, s_red);
-				if (threadIdx.x == 0)
-				{
-					double * out = p.partial + (size_t(ch) * p.split_s + sp) * 3;
-					#pragma unroll
-					for (int k = 0; k < K; ++k)
-						out[k] = acc[k];
-					__threadfence(); // the partial sums are visible before the count
-					const uint32_t before = atomicAdd(p.done + ch, 1u);
-					if (PEER)
-					{
-						__threadfence(); // and the other items' partial sums are visible to this one if it is the last
-						s_item[3] = before == p.split_s - 1 ? 1u : 0u;
-					}
-				}
+				double mean_d = 0.0, var_d = 0.0;   // forward
+				float c2 = 0.0F, c3 = 0.0F;          // backward
 				if (!PEER)
-					return;
-				__syncthreads();
-				if (s_item[3] == 0 || threadIdx.x >= 32)
-					return;
-				// last S item of this channel on this rank: fold the partial sums (slice order, as the A items of
-				// a single-GPU launch do), write the local per-channel outputs, publish the message to every rank
-				double tot[K];
-				#pragma unroll
-				for (int k = 0; k < K; ++k)
-				{
-					double t = 0.0;
-					for (uint32_t q = threadIdx.x; q < p.split_s; q += 32)
-						t += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
-					tot[k] = chain_warp_sum(t);
-				}
-				const float m0 = float(tot[0]), m1 = float(tot[1]);
-				if (threadIdx.x == 0)
 				{
 					if (!BWD)
 					{
+						const double ms = tot[0] / p.count;
+						mean_d = shift + ms;
+						var_d = tot[1] / p.count - ms * ms;
+					}
+					else
+					{
+						c2 = float(double(m0) / p.count);
+						c3 = float(double(m1) / p.count);
+					}
+				}
+				else
+				{
+					// publish this rank's two sums to every rank, wait (bounded) for the words of all ranks, add in rank order
+					if (lane < uint32_t(p.world) * 2)
+					{
+						const uint32_t r = lane >> 1, k = lane & 1;
+						st_sys_u64(p.mail[r] + mail_index(p, p.rank, ch) + k, (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(k ? m1 : m0));
+					}
+					const unsigned long long * mine = p.mail[p.rank];
+					unsigned long long w0 = 0, w1 = 0;
+					bool have = lane >= uint32_t(p.world);
+					const unsigned long long t1 = chain_timer_ns();
+					for (uint32_t round = 0; ; ++round)
+					{
+						if (!have)
+						{
+							w0 = ld_sys_u64(mine + mail_index(p, lane, ch));
+							w1 = ld_sys_u64(mine + mail_index(p, lane, ch) + 1);
+							have = uint32_t(w0 >> 32) == p.seq && uint32_t(w1 >> 32) == p.seq;
+						}
+						if (__all_sync(0xffffffffu, have))
+							break;
+						bool give_up = false;
+						if ((round & 15) == 15 && lane == 0)
+							give_up = *reinterpret_cast<volatile int *>(&p.report->status) != 0 || chain_timer_ns() - t1 > p.wait_limit_ns;
+						if (__any_sync(0xffffffffu, give_up))
+						{
+							if (lane == 0)
+							{
+								p.report->status = 2;
+								if (p.error_word) *p.error_word = 2;
+							}
+							break;
+						}
+						__nanosleep(200);
+					}
+					float f0 = 0.0F, f1 = 0.0F;
+					for (int r = 0; r < p.world; ++r)
+					{
+						f0 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w0, r)));
+						f1 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w1, r)));
+					}
+					if (!BWD)
+					{
+						mean_d = double(f0) / p.count_total;
+						var_d = double(f1) / p.count_total - mean_d * mean_d;
+					}
+					else
+					{
+						c2 = float(double(f0) / p.count_total);
+						c3 = float(double(f1) / p.count_total);
+					}
+				}
+				if (lane == 0)
+				{
+					const unsigned long long waited = chain_timer_ns() - t0;
+					atomicAdd(&p.report->wait_ns_total, waited);
+					atomicMax(&p.report->wait_ns_max, waited);
+					float4 f0v, f1v = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					if (!BWD)
+					{
+						var_d = var_d < 0.0 ? 0.0 : var_d;
+						const float fmean = float(mean_d);
+						const float finv = float(1.0 / sqrt(var_d + double(p.eps)));
+						const float mult = __ldg(p.gamma + ch) * finv;
+						f0v = make_float4(mult, fmaf(-mult, fmean, __ldg(p.beta + ch)), 0.0F, 0.0F);
+						p.saved[ch] = fmean;
+						p.saved[p.c + ch] = finv;
 						if (p.sums)
 						{
 							p.sums[ch] = m0;
@@ -354,265 +520,292 @@ namespace nnf
 					}
 					else
 					{
-						const float fs = float(tot[2]);
+						const float mult = __ldg(p.gamma + ch) * saved_invstd;
+						// dx = mult * ((du - c2) - xhat * c3) with xhat = (x - mean) * invstd, as two fused multiply-adds
+						f0v = make_float4(mult, -(mult * c3 * saved_invstd), -(mult * c2), saved_mean);
+						f1v = make_float4(__ldg(p.beta + ch), 0.0F, 0.0F, 0.0F);
 						if (p.sums)
 						{
 							p.sums[ch] = m0;
 							p.sums[p.c + ch] = m1;
-							p.sums[2 * p.c + ch] = fs;
+							p.sums[2 * p.c + ch] = m2;
 						}
-						// per-channel gradients accumulate the LOCAL sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+						// per-channel gradients accumulate this rank's sums (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
 						if (p.grad_beta) p.grad_beta[ch] += m0;
 						if (p.grad_gamma) p.grad_gamma[ch] += m1;
-						if (p.grad_slope) p.grad_slope[ch] += fs;
+						if (p.grad_slope) p.grad_slope[ch] += m2;
+						if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (saved_mean - p.mean[ch]);
+						if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (saved_invstd - p.invsigma[ch]);
 					}
+					p.fin[2 * ch] = f0v;
+					p.fin[2 * ch + 1] = f1v;
+					st_release_u32(p.ready + ch, 1u);
 				}
-				if (threadIdx.x < uint32_t(p.world) * 2)
+				return;
+			}
+
+			// ---- this thread's slots: fixed byte offsets inside a sweep ------------------------------------
+			const uint32_t rows = p.rows, cols = p.cols, tiles = p.tiles;
+			const uint32_t entry_stride_b = p.c * p.hw * 4;
+			const uint32_t per_item = kind == 0 ? p.es : p.ea;
+			const uint32_t e0 = sp * per_item;
+			const uint32_t e1 = min(e0 + per_item, p.n);
+			const uint32_t nrows = e1 > e0 ? e1 - e0 : 0;
+			const uint32_t row_sweeps = p.d_rows.div(nrows + rows - 1);
+			const uint32_t rem_rows = nrows - (row_sweeps ? row_sweeps - 1 : 0) * rows;   // rows of the last row sweep
+			const uint32_t last_cols = p.vpp - (tiles - 1) * cols;                         // vectors of the last column tile
+			uint32_t ob[L];
+			uint32_t m_slots = 0, m_rows = 0, m_cols = 0;   // bit u: slot u exists / lies in the last row sweep's rows / in the last column tile
+			#pragma unroll
+			for (int u = 0; u < L; ++u)
+			{
+				const uint32_t s = threadIdx.x + u * kChainThreads;
+				const uint32_t r = p.d_cols.div(s);
+				const uint32_t cidx = s - r * cols;
+				ob[u] = r * entry_stride_b + cidx * 16;
+				m_slots |= (r < rows ? 1u : 0u) << u;
+				m_rows |= (r < rem_rows ? 1u : 0u) << u;
+				m_cols |= (cidx < last_cols ? 1u : 0u) << u;
+			}
+			const uint32_t row_step_b = rows * entry_stride_b;
+			const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
+			auto sweep_mask = [&](uint32_t rs, uint32_t ct) -> uint32_t
+			{
+				uint32_t m = rs < row_sweeps ? m_slots : 0u;
+				if (rs + 1 == row_sweeps) m &= m_rows;
+				if (ct + 1 == tiles) m &= m_cols;
+				return m;
+			};
+			float4 * const my = ring + threadIdx.x;
+			auto slot = [&](int g, int t, int u) -> float4 * { return my + ((g * T + t) * L + u) * kChainThreads; };
+			const float slope = chain_slope(p.chain, ch);
+
+			if (kind == 0)
+			{
+				// ---- S item --------------------------------------------------------------------------
+				uint64_t policy;
+				asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+				float acc[K];
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					acc[k] = 0.0F;
+				uint32_t irs = 0, ict = 0, icoff = 0;    // the next sweep to ask for
+				const char * ibx = reinterpret_cast<const char *>(p.x + off0);
+				const char * ibd = reinterpret_cast<const char *>(BWD ? p.dy + off0 : p.x + off0);
+				auto issue = [&](int g)
 				{
-					__threadfence(); // everything this rank's S items wrote for the channel comes before the word
-					const uint32_t r = threadIdx.x >> 1, k = threadIdx.x & 1;
-					const unsigned long long word = (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(k ? m1 : m0);
-					st_sys_u64(p.mail[r] + mail_index(p, p.rank, ch) + k, word);
+					if (irs < row_sweeps)
+					{
+						const uint32_t m = sweep_mask(irs, ict);
+						#pragma unroll
+						for (int u = 0; u < L; ++u)
+							if (m & (1u << u))
+							{
+								cp_async16(slot(g, 0, u), ibx + icoff + ob[u], policy);
+								if (BWD) cp_async16(slot(g, T - 1, u), ibd + icoff + ob[u], policy);
+							}
+						icoff += cols * 16;
+						if (++ict == tiles)
+						{
+							ict = 0; icoff = 0; ++irs;
+							ibx += row_step_b; ibd += row_step_b;
+						}
+					}
+					cp_async_commit();
+				};
+				#pragma unroll
+				for (int g = 0; g < STAGES; ++g)
+					issue(g);
+				// forward: the sums are taken around the channel's first element, so that a mean far from zero costs no digits
+				const float shift = BWD ? 0.0F : __ldg(p.x + size_t(ch) * p.hw);
+				const float mean = BWD ? __ldg(p.saved + ch) : 0.0F;
+				const float mult = BWD ? __ldg(p.gamma + ch) * __ldg(p.saved + p.c + ch) : 0.0F;
+				const float beta = BWD ? __ldg(p.beta + ch) : 0.0F;
+				uint32_t crs = 0, cct = 0;
+				int g = 0;
+				while (row_sweeps)
+				{
+					cp_async_wait<STAGES - 1>();
+					const uint32_t m = sweep_mask(crs, cct);
+					#pragma unroll
+					for (int u = 0; u < L; ++u)
+					{
+						if (!(m & (1u << u)))
+							continue;
+						const float4 a = *slot(g, 0, u);
+						if (!BWD)
+						{
+							const float v0 = a.x - shift, v1 = a.y - shift, v2 = a.z - shift, v3 = a.w - shift;
+							acc[0] += (v0 + v1) + (v2 + v3);
+							acc[1] = fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, fmaf(v3, v3, acc[1]))));
+						}
+						else
+						{
+							const float4 d = *slot(g, T - 1, u);
+							const float xs[4] = {a.x, a.y, a.z, a.w};
+							const float ds[4] = {d.x, d.y, d.z, d.w};
+							#pragma unroll
+							for (int j = 0; j < 4; ++j)
+							{
+								const float xc = xs[j] - mean;
+								const float uu = fmaf(xc, mult, beta);
+								float term;
+								const float du = stream_backward<A0, A1>(p.chain, uu, ds[j], slope, term);
+								acc[0] += du;
+								acc[1] = fmaf(du, xc, acc[1]);
+								acc[K - 1] += term;
+							}
+						}
+					}
+					if (++cct == tiles)
+					{
+						cct = 0;
+						if (++crs == row_sweeps)
+							break;
+					}
+					issue(g);
+					if (++g == STAGES) g = 0;
+				}
+				cp_async_wait<0>();
+				// the item's deposit: warp sums, then the warps' sums in warp order; each sum travels with the launch's tag
+				#pragma unroll
+				for (int k = 0; k < K; ++k)
+					acc[k] = stream_warp_sum(acc[k]);
+				if (lane == 0)
+				{
+					#pragma unroll
+					for (int k = 0; k < K; ++k)
+						s_sum[warp][k] = acc[k];
+				}
+				__syncthreads();
+				if (threadIdx.x < K)
+				{
+					float t = 0.0F;
+					#pragma unroll
+					for (int w = 0; w < kStreamWarps; ++w)
+						t += s_sum[w][threadIdx.x];
+					st_relaxed_u64(p.deposit + (size_t(ch) * p.ss + sp) * 4 + threadIdx.x, (static_cast<unsigned long long>(p.tag) << 32) | __float_as_uint(t));
 				}
 				return;
 			}
 
 			// ---- A item ------------------------------------------------------------------------------
-			const uint32_t e0 = sp * p.entries_a;
-			const uint32_t e1 = min(e0 + p.entries_a, p.n);
-			const uint32_t total = e1 > e0 ? (e1 - e0) * per_plane : 0;
-			const size_t off0 = (size_t(e0) * p.c + ch) * p.hw;
-			// position of float4 number i of this item, in floats relative to off0 (fits 32 bits: checked by the plan)
-			const uint32_t entry_stride32 = p.c * p.hw;
-			auto rel_of = [&](uint32_t i) -> uint32_t
+			uint64_t policy;
+			asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+			uint32_t irs = 0, ict = 0, icoff = 0;
+			const char * ibx = reinterpret_cast<const char *>(p.x + off0);
+			const char * ibd = reinterpret_cast<const char *>(BWD ? p.dy + off0 : p.x + off0);
+			char * bo = reinterpret_cast<char *>(p.out + off0);
+			auto issue = [&](int g)
 			{
-				const uint32_t lp = p.d_vpp.div(i);
-				return lp * entry_stride32 + (i - lp * per_plane) * 4;
-			};
-			uint32_t rel[kLoadsA];
-			// the first batch of loads does not depend on the statistics: it is issued before the wait, so
-			// that the CTA has bytes in flight while it polls and folds the partial sums
-			float4 a[kLoadsA];
-			float4 d[BWD ? kLoadsA : 1];
-			auto load_batch = [&](uint32_t i0)
-			{
-				#pragma unroll
-				for (int u = 0; u < kLoadsA; ++u)
+				if (irs < row_sweeps)
 				{
-					const uint32_t i = i0 + u * kChainThreads;
-					if (i < total)
+					const uint32_t m = sweep_mask(irs, ict);
+					#pragma unroll
+					for (int u = 0; u < L; ++u)
+						if (m & (1u << u))
+						{
+							cp_async16(slot(g, 0, u), ibx + icoff + ob[u], policy);
+							if (BWD) cp_async16(slot(g, T - 1, u), ibd + icoff + ob[u], policy);
+						}
+					icoff += cols * 16;
+					if (++ict == tiles)
 					{
-						rel[u] = rel_of(i);
-						a[u] = ld_stream(reinterpret_cast<const float4 *>(p.x + off0 + rel[u]));
-						if (BWD)
-							d[u] = ld_stream(reinterpret_cast<const float4 *>(p.dy + off0 + rel[u]));
+						ict = 0; icoff = 0; ++irs;
+						ibx += row_step_b; ibd += row_step_b;
 					}
 				}
+				cp_async_commit();
 			};
-			load_batch(threadIdx.x);
-			if (PEER && threadIdx.x < 32)
+			// the first copies do not depend on the statistics: they are on their way while the item waits
+			#pragma unroll
+			for (int g = 0; g < STAGES; ++g)
+				issue(g);
+			if (threadIdx.x == 0)
 			{
-				// wait (bounded) until the words of every rank for this channel carry this exchange's number,
-				// then add the messages in rank order
-				const unsigned long long * mine = p.mail[p.rank];
-				unsigned long long w0 = 0, w1 = 0;
-				bool ok = threadIdx.x >= uint32_t(p.world);
-				const unsigned long long t0 = chain_timer_ns();
-				for (uint32_t round = 0; ; ++round)
+				bool ok = false;
+				unsigned long long t0 = 0;
+				for (uint32_t round = 0; round < kChainPollLimit; ++round)
 				{
-					if (!ok)
+					if (ld_acquire(p.ready + ch) != 0)
 					{
-						w0 = ld_sys_u64(mine + mail_index(p, threadIdx.x, ch));
-						w1 = ld_sys_u64(mine + mail_index(p, threadIdx.x, ch) + 1);
-						ok = uint32_t(w0 >> 32) == p.seq && uint32_t(w1 >> 32) == p.seq;
-					}
-					if (__all_sync(0xffffffffu, ok))
-						break;
-					bool give_up = false;
-					if ((round & 15) == 15 && threadIdx.x == 0)
-						give_up = (p.error && *reinterpret_cast<volatile int *>(p.error) != 0) || chain_timer_ns() - t0 > kChainPeerWaitNs;
-					if (__any_sync(0xffffffffu, give_up))
-					{
-						if (threadIdx.x == 0 && p.error)
-							*p.error = 2;
+						ok = true;
 						break;
 					}
-					__nanosleep(200);
+					if (round == 0)
+						t0 = chain_timer_ns();
+					if ((round & 63) == 63 && *reinterpret_cast<volatile int *>(&p.report->status) != 0)
+						break;
+					__nanosleep(100);
 				}
-				__threadfence(); // what the publishing items wrote before their words is visible from here on
-				float f0 = 0.0F, f1 = 0.0F;
-				for (int r = 0; r < p.world; ++r)
+				if (t0)
 				{
-					f0 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w0, r)));
-					f1 += __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, w1, r)));
+					const unsigned long long waited = chain_timer_ns() - t0;
+					atomicAdd(&p.report->wait_ns_total, waited);
+					atomicMax(&p.report->wait_ns_max, waited);
 				}
-				if (threadIdx.x == 0)
+				if (!ok && p.report->status == 0)
 				{
-					if (!BWD)
-					{
-						const double m = double(f0) / p.count_total;
-						double var = double(f1) / p.count_total - m * m;
-						var = var < 0.0 ? 0.0 : var;
-						const float fmean = float(m);
-						const float finv = float(1.0 / sqrt(var + double(p.eps)));
-						s_tot[0] = fmean;
-						s_tot[1] = finv;
-						if (sp == 0)
-						{
-							p.saved[ch] = fmean;
-							p.saved[p.c + ch] = finv;
-						}
-					}
-					else
-					{
-						s_tot[0] = float(double(f0) / p.count_total);
-						s_tot[1] = float(double(f1) / p.count_total);
-						if (sp == 0)
-						{
-							const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
-							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
-							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
-						}
-					}
+					p.report->status = 4;
+					if (p.error_word) *p.error_word = 4;
 				}
-			}
-			if (!PEER && threadIdx.x < 32)
-			{
-				// wait (bounded) until every S item of this channel is done, then add their partial sums in
-				// slice order: lane l takes slices l and l + 32, then a fixed shuffle tree
-				bool ready = false;
-				if (threadIdx.x == 0)
-				{
-					for (uint32_t round = 0; round < kChainPollLimit; ++round)
-					{
-						if (ld_acquire(p.done + ch) >= p.split_s)
-						{
-							ready = true;
-							break;
-						}
-						__nanosleep(200);
-					}
-					if (!ready && p.error)
-						*p.error = 4;
-				}
-				__syncwarp();
-				double tot[K];
-				#pragma unroll
-				for (int k = 0; k < K; ++k)
-				{
-					double t = 0.0;
-					for (uint32_t q = threadIdx.x; q < p.split_s; q += 32)
-						t += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
-					tot[k] = chain_warp_sum(t);
-				}
-				if (threadIdx.x == 0)
-				{
-					if (!BWD)
-					{
-						const double m = tot[0] / p.count;
-						double var = tot[1] / p.count - m * m;
-						var = var < 0.0 ? 0.0 : var;
-						const float fmean = float(m);
-						const float finv = float(1.0 / sqrt(var + double(p.eps)));
-						s_tot[0] = fmean;
-						s_tot[1] = finv;
-						if (sp == 0)
-						{
-							p.saved[ch] = fmean;
-							p.saved[p.c + ch] = finv;
-							if (p.sums)
-							{
-								p.sums[ch] = float(tot[0]);
-								p.sums[p.c + ch] = float(tot[1]);
-							}
-						}
-					}
-					else
-					{
-						const float fb = float(tot[0]), fg = float(tot[1]), fs = float(tot[2]);
-						// the same float-rounded sums the two-kernel form passes between its kernels
-						s_tot[0] = float(double(fb) / p.count);
-						s_tot[1] = float(double(fg) / p.count);
-						if (sp == 0)
-						{
-							const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
-							if (p.sums)
-							{
-								p.sums[ch] = fb;
-								p.sums[p.c + ch] = fg;
-								p.sums[2 * p.c + ch] = fs;
-							}
-							// per-channel gradients accumulate (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
-							if (p.grad_beta) p.grad_beta[ch] += fb;
-							if (p.grad_gamma) p.grad_gamma[ch] += fg;
-							if (p.grad_slope) p.grad_slope[ch] += fs;
-							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
-							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
-						}
-					}
-				}
+				s_fin[0] = __ldcg(p.fin + 2 * ch);
+				s_fin[1] = __ldcg(p.fin + 2 * ch + 1);
 			}
 			__syncthreads();
-			if (total == 0)
-				return;
-			const float slope = chain_slope(p.chain, ch);
-			if (!BWD)
+			const float4 f0 = s_fin[0];
+			const float4 f1 = s_fin[1];
+			uint32_t crs = 0, cct = 0, coff = 0;
+			int g = 0;
+			while (row_sweeps)
 			{
-				const float mean = s_tot[0], invstd = s_tot[1];
-				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
-				const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
-				for (uint32_t i0 = threadIdx.x; ; )
+				cp_async_wait<STAGES - 1>();
+				const uint32_t m = sweep_mask(crs, cct);
+				#pragma unroll
+				for (int u = 0; u < L; ++u)
 				{
-					#pragma unroll
-					for (int u = 0; u < kLoadsA; ++u)
+					if (!(m & (1u << u)))
+						continue;
+					const float4 a = *slot(g, 0, u);
+					float4 o;
+					if (!BWD)
 					{
-						const uint32_t i = i0 + u * kChainThreads;
-						if (i < total)
+						o.x = chain_forward<A0, A1>(p.chain, fmaf(a.x, f0.x, f0.y), slope);
+						o.y = chain_forward<A0, A1>(p.chain, fmaf(a.y, f0.x, f0.y), slope);
+						o.z = chain_forward<A0, A1>(p.chain, fmaf(a.z, f0.x, f0.y), slope);
+						o.w = chain_forward<A0, A1>(p.chain, fmaf(a.w, f0.x, f0.y), slope);
+					}
+					else
+					{
+						const float4 d = *slot(g, T - 1, u);
+						const float xs[4] = {a.x, a.y, a.z, a.w};
+						const float ds[4] = {d.x, d.y, d.z, d.w};
+						float r_[4];
+						#pragma unroll
+						for (int j = 0; j < 4; ++j)
 						{
-							float4 o;
-							o.x = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].x, mult), add), slope);
-							o.y = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].y, mult), add), slope);
-							o.z = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].z, mult), add), slope);
-							o.w = chain_forward<A0, A1>(p.chain, __fadd_rn(__fmul_rn(a[u].w, mult), add), slope);
-							st_stream(reinterpret_cast<float4 *>(p.out + off0 + rel[u]), o);
+							const float xc = xs[j] - f0.w;
+							const float uu = fmaf(xc, f0.x, f1.x);
+							float term;
+							const float du = stream_backward<A0, A1>(p.chain, uu, ds[j], slope, term);
+							r_[j] = fmaf(du, f0.x, fmaf(xc, f0.y, f0.z));
 						}
+						o = make_float4(r_[0], r_[1], r_[2], r_[3]);
 					}
-					i0 += kChainThreads * kLoadsA;
-					if (i0 >= total)
-						break;
-					load_batch(i0);
+					st_stream(reinterpret_cast<float4 *>(bo + coff + ob[u]), o);
 				}
-			}
-			else
-			{
-				const float c2 = s_tot[0], c3 = s_tot[1];
-				const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
-				const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
-				const float add = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
-				auto element = [&](float x, float dy) -> float
+				coff += cols * 16;
+				if (++cct == tiles)
 				{
-					const float u = __fadd_rn(__fmul_rn(x, mult), add);
-					float term;
-					const float du = chain_backward<A0, A1>(p.chain, u, dy, slope, term);
-					const float xhat = __fmul_rn(__fsub_rn(x, mean), invstd);
-					return mult * ((du - c2) - xhat * c3);
-				};
-				for (uint32_t i0 = threadIdx.x; ; )
-				{
-					#pragma unroll
-					for (int u = 0; u < kLoadsA; ++u)
-					{
-						const uint32_t i = i0 + u * kChainThreads;
-						if (i < total)
-							st_stream(reinterpret_cast<float4 *>(p.out + off0 + rel[u]),
-								make_float4(element(a[u].x, d[u].x), element(a[u].y, d[u].y), element(a[u].z, d[u].z), element(a[u].w, d[u].w)));
-					}
-					i0 += kChainThreads * kLoadsA;
-					if (i0 >= total)
+					cct = 0; coff = 0;
+					bo += row_step_b;
+					if (++crs == row_sweeps)
 						break;
-					load_batch(i0);
 				}
+				issue(g);
+				if (++g == STAGES) g = 0;
 			}
+			cp_async_wait<0>();
 		}
 
 		// ---- the same single launch for planes that are not whole float4s (7x7, 13x13) ----------------------------
@@ -902,14 +1095,23 @@ namespace nnf
 							break;
 						bool give_up = false;
 						if ((round & 15) == 15 && (threadIdx.x & 31) == 0)
-							give_up = (p.error && *reinterpret_cast<volatile int *>(p.error) != 0) || chain_timer_ns() - t0 > kChainPeerWaitNs;
+							give_up = (p.error && *reinterpret_cast<volatile int *>(p.error) != 0) || chain_timer_ns() - t0 > p.wait_limit_ns;
 						if (__any_sync(0xffffffffu, give_up))
 						{
 							if ((threadIdx.x & 31) == 0 && p.error)
+							{
 								*p.error = 2;
+								if (p.error_word) *p.error_word = 2;
+							}
 							break;
 						}
 						__nanosleep(200);
+					}
+					if ((threadIdx.x & 31) == 0 && p.wait_ns)
+					{
+						const unsigned long long waited = chain_timer_ns() - t0;
+						atomicAdd(p.wait_ns, waited);
+						atomicMax(p.wait_ns + 1, waited);
 					}
 					__threadfence(); // what the publishing items wrote before their words is visible from here on
 					float f0 = 0.0F, f1 = 0.0F;
@@ -969,7 +1171,10 @@ namespace nnf
 					__nanosleep(200);
 				}
 				if (!ready && p.error)
+				{
 					*p.error = 4;
+					if (p.error_word) *p.error_word = 4;
+				}
 			}
 			__syncthreads();
 			// the S items' partial sums of every channel of the group, in slice order: eight lanes per channel
@@ -1119,68 +1324,67 @@ namespace nnf
 			}
 		}
 
-		int chain_env(const char * name, int fallback)
+		// Geometry of the kernel for planes of whole float4s. Defaults measured on B200 with x[256,256,28,28],
+		// PReLU+ELU (forward / backward): items of 48 KB (statistics) and 64 KB (apply) of one tensor, apply items 32 /
+		// 24 channels behind the statistics items: 86 / 150 us. Shorter distances make every apply item wait for its
+		// channel (16 channels: 94 / 164 us), longer ones push the first read out of L2 before the second.
+		// Knobs: chain_s_kb, chain_a_kb, chain_dist (nnf_set_tuning).
+		bool plan_stream(stream_params& p, int64_t n, int64_t c, int64_t hw, bool backward)
 		{
-			const char * v = getenv(name);
-			return v ? atoi(v) : fallback;
-		}
-
-		// Item sizes and chunking. Defaults measured on B200 with x[256,256,28,28], PReLU+ELU (forward / backward):
-		// S 48 KB, A 64 KB, 16 MB chunks, lag 1: 95 / 154 us; A 32 KB: 99 / 178 us; S 96 KB: 96 / 170 us; chunk 8 MB:
-		// 122 / 216 us (apply items catch up with their statistics); lag 0: 124 / 227 us. Loads in flight per
-		// thread (4 / 2 per tensor against 8 / 4) and CTAs per SM (4 to 6) change the times by a few percent only.
-		// Tuning aids: NNF_CHAIN_S_KB / NNF_CHAIN_A_KB (bytes of one tensor that an
-		// S / A item covers), NNF_CHAIN_CHUNK_MB (bytes of one tensor per chunk), NNF_CHAIN_LAG.
-		bool plan_chain(chain_params& p, int64_t n, int64_t c, int64_t hw, int tensors)
-		{
-			(void)tensors;
 			if (hw % 4 != 0 || n < 1 || c < 1 || n * hw >= (int64_t(1) << 31) || c > 0x7fffffff / 256)
 				return false;
-			const int64_t plane_bytes = hw * 4;
-			const int64_t s_bytes = int64_t(chain_env("NNF_CHAIN_S_KB", 48)) * 1024;
-			const int64_t a_bytes = int64_t(chain_env("NNF_CHAIN_A_KB", 64)) * 1024;
-			int64_t es = s_bytes / plane_bytes, ea = a_bytes / plane_bytes;
-			if (es < 1) es = 1;
-			if (ea < 1) ea = 1;
-			if (es > n) es = n;
-			if (ea > n) ea = n;
-			if (div_up(n, es) > kChainMaxSplit)
-				es = div_up(n, kChainMaxSplit);
-			if (div_up(n, ea) > 4096)
-				ea = div_up(n, 4096);
-			p.entries_s = (uint32_t)es;
-			p.split_s = (uint32_t)div_up(n, es);
-			if (ea * c * hw >= (int64_t(1) << 32))
-				return false; // positions inside an apply item are kept in 32 bits
-			p.entries_a = (uint32_t)ea;
-			p.split_a = (uint32_t)div_up(n, ea);
-			const double channel_bytes = double(n) * double(plane_bytes);
-			int64_t chunk = (int64_t)(double(chain_env("NNF_CHAIN_CHUNK_MB", 16)) * 1024.0 * 1024.0 / channel_bytes);
-			if (chunk < 1) chunk = 1;
-			if (chunk < div_up(c, 64)) chunk = div_up(c, 64); // at most 64 chunks: a CTA finds its item by walking them
-			if (chunk > c) chunk = c;
-			p.chunk = (uint32_t)chunk;
-			p.nchunks = (uint32_t)div_up(c, chunk);
-			int lag = chain_env("NNF_CHAIN_LAG", 1);
-			p.lag = (uint32_t)(lag < 0 ? 0 : lag);
-			const int64_t items = c * (int64_t(p.split_s) + int64_t(p.split_a));
-			if (items >= (int64_t(1) << 31) || p.nchunks + p.lag > 4096)
+			const int64_t vpp = hw / 4;
+			const int64_t slots = int64_t(kChainThreads) * kStreamSlots;
+			int64_t rows, cols, tiles;
+			if (vpp <= slots) { cols = vpp; rows = slots / vpp; tiles = 1; }
+			else { cols = slots; rows = 1; tiles = div_up(vpp, slots); }
+			if (rows > n) rows = n;
+			// slot offsets inside a sweep and the step between sweeps are kept in 32 bits
+			if (rows * c * hw * 4 >= (int64_t(1) << 32))
 				return false;
-			p.total_items = (uint32_t)items;
-			p.n = (uint32_t)n; p.c = (uint32_t)c; p.hw = (uint32_t)hw;
-			p.units = p.c;
-			p.d_vpp = fastdiv((uint32_t)(hw / 4));
-			p.d_split_s = fastdiv(p.split_s);
-			p.d_split_a = fastdiv(p.split_a);
+			const int64_t plane_bytes = hw * 4;
+			auto entries = [&](int kb)
+			{
+				int64_t e = int64_t(kb) * 1024 / plane_bytes;
+				e = e / rows * rows;
+				if (e < rows) e = rows;
+				if (e > n) e = n;
+				return e;
+			};
+			const tuning& t = tune();
+			int64_t es = entries(t.chain_s_kb > 0 ? t.chain_s_kb : 48), ea = entries(t.chain_a_kb > 0 ? t.chain_a_kb : 64);
+			if (div_up(n, es) > kChainMaxSplit)
+				es = div_up(div_up(n, kChainMaxSplit), rows) * rows;
+			if (div_up(n, ea) > 4096)
+				ea = div_up(div_up(n, 4096), rows) * rows;
+			p.es = (uint32_t)es; p.ea = (uint32_t)ea;
+			p.ss = (uint32_t)div_up(n, es); p.sa = (uint32_t)div_up(n, ea);
+			int64_t dist = t.chain_dist >= 0 ? t.chain_dist : (backward ? 24 : 32);
+			if (dist > c) dist = c;
+			p.dist = (uint32_t)dist;
+			p.dist_f = (uint32_t)(dist / 2);
+			const int64_t total = (c + dist) * (int64_t(p.ss) + p.sa + 1);
+			if (total >= (int64_t(1) << 31))
+				return false;
+			p.total = (uint32_t)total;
+			p.n = (uint32_t)n; p.c = (uint32_t)c; p.hw = (uint32_t)hw; p.vpp = (uint32_t)vpp;
+			p.rows = (uint32_t)rows; p.cols = (uint32_t)cols; p.tiles = (uint32_t)tiles;
+			p.d_cols = fastdiv(p.cols); p.d_per = fastdiv(p.ss + p.sa + 1); p.d_both = fastdiv(p.ss + p.sa); p.d_rows = fastdiv(p.rows);
 			p.count = double(n) * double(hw);
 			return true;
+		}
+
+		size_t stream_workspace_needed(const stream_params& p)
+		{
+			return sizeof(launch_report) + size_t(p.c) * sizeof(uint32_t) + 16 + size_t(p.c) * 2 * sizeof(float4)
+				+ size_t(p.c) * p.ss * 4 * sizeof(unsigned long long);
 		}
 
 		// The grouped kernel's plan: items are channel groups. Returns false where the shape does not suit it (planes
 		// of whole float4s take the kernel above; runs shorter than 16 vectors or longer than 256 the separate kernels).
 		bool plan_chain_grouped(chain_params& p, int64_t n, int64_t c, int64_t hw)
 		{
-			if (hw % 4 == 0 || n < 1 || c < 1 || n >= (int64_t(1) << 31) || c >= (int64_t(1) << 24) || getenv("NNF_NO_GROUPED_CHAIN"))
+			if (hw % 4 == 0 || n < 1 || c < 1 || n >= (int64_t(1) << 31) || c >= (int64_t(1) << 24) || tune().no_grouped == 1)
 				return false;
 			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
 			const int64_t vpu = unit * hw / 4;
@@ -1193,8 +1397,8 @@ namespace nnf
 				return false;
 			const int64_t groups = div_up(c, group);
 			const int64_t run_bytes = group * hw * 4;
-			const int64_t s_bytes = int64_t(chain_env("NNF_CHAIN_S_KB", 48)) * 1024;
-			const int64_t a_bytes = int64_t(chain_env("NNF_CHAIN_A_KB", 64)) * 1024;
+			const int64_t s_bytes = int64_t(tune().chain_s_kb > 0 ? tune().chain_s_kb : 48) * 1024;
+			const int64_t a_bytes = int64_t(tune().chain_a_kb > 0 ? tune().chain_a_kb : 64) * 1024;
 			int64_t es = s_bytes / run_bytes, ea = a_bytes / run_bytes;
 			if (es < 1) es = 1;
 			if (ea < 1) ea = 1;
@@ -1209,13 +1413,13 @@ namespace nnf
 			p.entries_a = (uint32_t)ea;
 			p.split_a = (uint32_t)div_up(n, ea);
 			const double group_bytes = double(n) * double(run_bytes);
-			int64_t chunk = (int64_t)(double(chain_env("NNF_CHAIN_CHUNK_MB", 16)) * 1024.0 * 1024.0 / group_bytes);
+			int64_t chunk = (int64_t)(double(tune().chain_chunk_mb > 0 ? tune().chain_chunk_mb : 16) * 1024.0 * 1024.0 / group_bytes);
 			if (chunk < 1) chunk = 1;
 			if (chunk < div_up(groups, 64)) chunk = div_up(groups, 64);
 			if (chunk > groups) chunk = groups;
 			p.chunk = (uint32_t)chunk;
 			p.nchunks = (uint32_t)div_up(groups, chunk);
-			int lag = chain_env("NNF_CHAIN_LAG", 1);
+			int lag = tune().chain_lag > 0 ? tune().chain_lag - 1 : 1;   // the knob is lag + 1, so that 0 keeps the default
 			p.lag = (uint32_t)(lag < 0 ? 0 : lag);
 			const int64_t items = groups * (int64_t(p.split_s) + int64_t(p.split_a));
 			if (items >= (int64_t(1) << 31))
@@ -1232,29 +1436,74 @@ namespace nnf
 			return true;
 		}
 
+		// Workspace of the channel-group kernel: the report, the counters (one per channel + padding), the partial sums.
 		size_t chain_workspace_needed(const chain_params& p)
 		{
-			return size_t(p.c) * p.split_s * 3 * sizeof(double) + (size_t(p.c) + 1) * sizeof(uint32_t);
+			return sizeof(launch_report) + (size_t(p.c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(p.c) * p.split_s * 3 * sizeof(double);
+		}
+
+		unsigned long long peer_wait_limit()
+		{
+			const long long v = tune().peer_wait_ns;
+			return v > 0 ? (unsigned long long)v : kDefaultPeerWaitNs;
 		}
 
 		template <class Kernel>
 		int launch_chain(Kernel kernel, chain_params& p, void * workspace, cudaStream_t s, const char * what)
 		{
-			p.partial = static_cast<double *>(workspace);
-			p.done = reinterpret_cast<uint32_t *>(p.partial + size_t(p.c) * p.split_s * 3);
-			p.ticket = p.done + p.c;
-			p.error = device_error_word();
-			cudaError_t e = cudaMemsetAsync(p.done, 0, (size_t(p.c) + 1) * sizeof(uint32_t), s);
+			launch_report * report = static_cast<launch_report *>(workspace);
+			p.done = reinterpret_cast<uint32_t *>(report + 1);
+			p.partial = reinterpret_cast<double *>(p.done + (size_t(p.c) + 2) / 2 * 2);
+			p.ticket = &report->ticket;
+			p.error = &report->status;
+			p.wait_ns = &report->wait_ns_total;
+			p.error_word = device_error_word();
+			p.wait_limit_ns = peer_wait_limit();
+			cudaError_t e = cudaMemsetAsync(workspace, 0, sizeof(launch_report) + size_t(p.c) * sizeof(uint32_t), s);
 			if (e != cudaSuccess)
 				return set_error(NNF_ERR_CUDA, "%s: cudaMemsetAsync: %s", what, cudaGetErrorString(e));
 			kernel<<<p.total_items, kChainThreads, 0, s>>>(p);
 			return check_launch(what);
 		}
+
+		std::atomic<uint32_t> g_launch_tag{0};
+
+		template <class Kernel>
+		int launch_stream(Kernel kernel, stream_params& p, void * workspace, cudaStream_t s, bool backward, const char * what)
+		{
+			launch_report * report = static_cast<launch_report *>(workspace);
+			p.report = report;
+			p.ready = reinterpret_cast<uint32_t *>(report + 1);
+			char * after = reinterpret_cast<char *>(p.ready) + (size_t(p.c) * sizeof(uint32_t) + 15) / 16 * 16;
+			p.fin = reinterpret_cast<float4 *>(after);
+			p.deposit = reinterpret_cast<unsigned long long *>(p.fin + size_t(p.c) * 2);
+			p.error_word = device_error_word();
+			p.wait_limit_ns = peer_wait_limit();
+			uint32_t tag = ++g_launch_tag;
+			if (tag == 0)
+				tag = ++g_launch_tag;   // zero is what a fresh workspace holds
+			p.tag = tag;
+			const size_t smem = size_t(backward ? kStagesBwd * 2 : kStagesFwd) * kStreamSlots * kChainThreads * sizeof(float4);
+			cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
+			e = cudaMemsetAsync(workspace, 0, sizeof(launch_report) + size_t(p.c) * sizeof(uint32_t), s);
+			if (e != cudaSuccess)
+				return set_error(NNF_ERR_CUDA, "%s: cudaMemsetAsync: %s", what, cudaGetErrorString(e));
+			kernel<<<p.total, kChainThreads, smem, s>>>(p);
+			return check_launch(what);
+		}
 	}
 
-	size_t chain_workspace_bytes(int64_t c)
+	size_t chain_workspace_bytes(int64_t n, int64_t c, int64_t hw)
 	{
-		return size_t(c) * kChainMaxSplit * 3 * sizeof(double) + (size_t(c) + 1) * sizeof(uint32_t);
+		// the larger of what the two kernels plan for this shape, forward or backward (the plans share their item counts)
+		// the knobs may change between the size query and the launch: sized for the most items a plan can make
+		(void)n; (void)hw;
+		const size_t grouped = sizeof(launch_report) + (size_t(c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(c) * kChainMaxSplit * 3 * sizeof(double);
+		const size_t stream = sizeof(launch_report) + size_t(c) * sizeof(uint32_t) + 16 + size_t(c) * 2 * sizeof(float4)
+			+ size_t(c) * kChainMaxSplit * 4 * sizeof(unsigned long long);
+		return grouped > stream ? grouped : stream;
 	}
 
 	namespace
@@ -1267,7 +1516,8 @@ namespace nnf
 			double count_total;
 		};
 
-		int fill_peer(chain_params& p, const chain_peer * peer, const char * who)
+		template <class Params>
+		int fill_peer(Params& p, const chain_peer * peer, const char * who)
 		{
 			p.count_total = p.count;
 			if (!peer)
@@ -1288,44 +1538,56 @@ namespace nnf
 			return NNF_OK;
 		}
 
+		bool workspace_ok(const void * workspace, size_t have, size_t need)
+		{
+			return workspace && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 && have >= need;
+		}
+
 		template <bool PEER>
 		int chain_forward_impl(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
 			float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
 		{
-			chain_params p = {};
 			if (!aligned16(x) || !aligned16(y))
 				return 1;
-			const bool grouped = plan_chain_grouped(p, n, c, hw);
-			if (!grouped && !plan_chain(p, n, c, hw, 1))
-				return 1;
-			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
-				return 1;
-			p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
-			p.chain = chain;
-			p.eps = eps;
-			const int st = fill_peer(p, peer, "bn_train_chain_kernel (forward)");
-			if (st != NNF_OK)
-				return st;
-			if (grouped)
+			chain_params gp = {};
+			if (plan_chain_grouped(gp, n, c, hw))
 			{
+				if (!workspace_ok(workspace, workspace_bytes, chain_workspace_needed(gp)))
+					return 2;
+				gp.x = x; gp.out = y; gp.gamma = gamma; gp.beta = beta; gp.saved = saved; gp.sums = sums;
+				gp.chain = chain;
+				gp.eps = eps;
+				const int st = fill_peer(gp, peer, "bn_train_chain_grouped_kernel (forward)");
+				if (st != NNF_OK)
+					return st;
 				const char * what = "bn_train_chain_grouped_kernel (forward)";
 				switch (chain_id(chain))
 				{
-				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, false, PEER>, p, workspace, stream, what);
-				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, p, workspace, stream, what);
-				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, false, PEER>, p, workspace, stream, what);
-				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, false, PEER>, p, workspace, stream, what);
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, false, PEER>, gp, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, gp, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, false, PEER>, gp, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, false, PEER>, gp, workspace, stream, what);
 				}
 			}
-			const int k0 = chain.n > 0 ? chain.a[0].kind : NNF_ACT_NONE;
-			const int k1 = chain.n > 1 ? chain.a[1].kind : NNF_ACT_NONE;
-			if (chain.n == 0)
-				return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-			if (k0 == NNF_ACT_PRELU && k1 == NNF_ACT_ELU && chain.n == 2)
-				return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-			if (k0 == NNF_ACT_RELU && chain.n == 1)
-				return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
-			return launch_chain(bn_train_chain_kernel<-1, 0, false, PEER>, p, workspace, stream, "bn_train_chain_kernel (forward)");
+			stream_params p = {};
+			if (!plan_stream(p, n, c, hw, false))
+				return 1;
+			if (!workspace_ok(workspace, workspace_bytes, stream_workspace_needed(p)))
+				return 2;
+			p.x = x; p.out = y; p.gamma = gamma; p.beta = beta; p.saved = saved; p.sums = sums;
+			p.chain = chain;
+			p.eps = eps;
+			const char * what = "bn_train_chain_kernel (forward)";
+			const int st = fill_peer(p, peer, what);
+			if (st != NNF_OK)
+				return st;
+			switch (chain_id(chain))
+			{
+			case 0: return launch_stream(bn_train_chain_kernel<NNF_ACT_NONE, 0, false, PEER>, p, workspace, stream, false, what);
+			case 1: return launch_stream(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, false, PEER>, p, workspace, stream, false, what);
+			case 2: return launch_stream(bn_train_chain_kernel<NNF_ACT_RELU, 0, false, PEER>, p, workspace, stream, false, what);
+			default: return launch_stream(bn_train_chain_kernel<-1, 0, false, PEER>, p, workspace, stream, false, what);
+			}
 		}
 
 		template <bool PEER>
@@ -1335,59 +1597,52 @@ namespace nnf
 			const float * mean, const float * invsigma, float entry_count,
 			int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes, const chain_peer * peer)
 		{
-			chain_params p = {};
 			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx))
 				return 1;
-			const bool grouped = plan_chain_grouped(p, n, c, hw);
-			if (!grouped && !plan_chain(p, n, c, hw, 2))
+			chain_params gp = {};
+			if (plan_chain_grouped(gp, n, c, hw))
+			{
+				if (!workspace_ok(workspace, workspace_bytes, chain_workspace_needed(gp)))
+					return 2;
+				gp.x = x; gp.dy = dy; gp.out = dx; gp.gamma = gamma; gp.beta = beta; gp.saved = const_cast<float *>(saved); gp.sums = bsums;
+				gp.grad_gamma = grad_gamma; gp.grad_beta = grad_beta; gp.grad_mean = grad_mean; gp.grad_invsigma = grad_invsigma; gp.grad_slope = grad_slope;
+				gp.mean = mean; gp.invsigma = invsigma; gp.entry_count = entry_count;
+				gp.chain = chain;
+				const int st = fill_peer(gp, peer, "bn_train_chain_grouped_kernel (backward)");
+				if (st != NNF_OK)
+					return st;
+				const char * what = "bn_train_chain_grouped_kernel (backward)";
+				switch (chain_id(chain))
+				{
+				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, true, PEER>, gp, workspace, stream, what);
+				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, gp, workspace, stream, what);
+				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, true, PEER>, gp, workspace, stream, what);
+				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, true, PEER>, gp, workspace, stream, what);
+				}
+			}
+			stream_params p = {};
+			if (!plan_stream(p, n, c, hw, true))
 				return 1;
-			if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < chain_workspace_needed(p))
-				return 1;
+			if (!workspace_ok(workspace, workspace_bytes, stream_workspace_needed(p)))
+				return 2;
 			p.x = x; p.dy = dy; p.out = dx; p.gamma = gamma; p.beta = beta; p.saved = const_cast<float *>(saved); p.sums = bsums;
 			p.grad_gamma = grad_gamma; p.grad_beta = grad_beta; p.grad_mean = grad_mean; p.grad_invsigma = grad_invsigma; p.grad_slope = grad_slope;
 			p.mean = mean; p.invsigma = invsigma; p.entry_count = entry_count;
 			p.chain = chain;
-			const int st = fill_peer(p, peer, "bn_train_chain_kernel (backward)");
+			const char * what = "bn_train_chain_kernel (backward)";
+			const int st = fill_peer(p, peer, what);
 			if (st != NNF_OK)
 				return st;
-			if (grouped)
-			{
-				const char * what = "bn_train_chain_grouped_kernel (backward)";
-				switch (chain_id(chain))
-				{
-				case 0: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, what);
-				case 1: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, p, workspace, stream, what);
-				case 2: return launch_chain(bn_train_chain_grouped_kernel<NNF_ACT_RELU, 0, true, PEER>, p, workspace, stream, what);
-				default: return launch_chain(bn_train_chain_grouped_kernel<-1, 0, true, PEER>, p, workspace, stream, what);
-				}
-			}
 			switch (chain_id(chain))
 			{
-			case 0: return launch_chain(bn_train_chain_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-			case 1: return launch_chain(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-			case 2: return launch_chain(bn_train_chain_kernel<NNF_ACT_RELU, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
-			default: return launch_chain(bn_train_chain_kernel<-1, 0, true, PEER>, p, workspace, stream, "bn_train_chain_kernel (backward)");
+			case 0: return launch_stream(bn_train_chain_kernel<NNF_ACT_NONE, 0, true, PEER>, p, workspace, stream, true, what);
+			case 1: return launch_stream(bn_train_chain_kernel<NNF_ACT_PRELU, NNF_ACT_ELU, true, PEER>, p, workspace, stream, true, what);
+			case 2: return launch_stream(bn_train_chain_kernel<NNF_ACT_RELU, 0, true, PEER>, p, workspace, stream, true, what);
+			default: return launch_stream(bn_train_chain_kernel<-1, 0, true, PEER>, p, workspace, stream, true, what);
 			}
 		}
 	}
 
-	// Returns NNF_OK after enqueueing, a negative status on an error, or 1 when the shape does not suit
-	// this kernel (the caller then uses another form).
-	int chain_forward_launch(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
-		float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
-	{
-		return chain_forward_impl<false>(stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, nullptr);
-	}
-
-	int chain_backward_launch(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
-		const float * gamma, const float * beta, const float * saved, const act_chain& chain,
-		float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
-		const float * mean, const float * invsigma, float entry_count,
-		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes)
-	{
-		return chain_backward_impl<false>(stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
-			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, nullptr);
-	}
 }
 
 using namespace nnf;
@@ -1395,7 +1650,8 @@ using namespace nnf;
 extern "C" int nnf_bn_train_sharded_supported(int64_t n, int64_t c, int64_t hw)
 {
 	chain_params p = {};
-	return (plan_chain_grouped(p, n, c, hw) || plan_chain(p, n, c, hw, 1)) ? 1 : 0;
+	stream_params q = {};
+	return (plan_chain_grouped(p, n, c, hw) || plan_stream(q, n, c, hw, false)) ? 1 : 0;
 }
 
 extern "C" size_t nnf_bn_train_mailbox_bytes(int64_t c)
@@ -1418,6 +1674,8 @@ extern "C" int nnf_bn_train_fwd_sharded(nnf_stream_t stream, float * y, float * 
 		return st;
 	const chain_peer peer = {mailboxes, rank, world, seq, count_total};
 	st = chain_forward_impl<true>((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, &peer);
+	if (st == 2)
+		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_fwd_sharded: a 16-byte aligned workspace of nnf_bn_train_workspace_bytes() bytes is required");
 	if (st == 1)
 		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_fwd_sharded: needs a shape for which nnf_bn_train_sharded_supported() answers 1, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
 	return st;
@@ -1449,7 +1707,135 @@ extern "C" int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float *
 	const chain_peer peer = {mailboxes, rank, world, seq, count_total};
 	st = chain_backward_impl<true>((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
 		mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, &peer);
+	if (st == 2)
+		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_bwd_sharded: a 16-byte aligned workspace of nnf_bn_train_workspace_bytes() bytes is required");
 	if (st == 1)
 		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd_sharded: needs a shape for which nnf_bn_train_sharded_supported() answers 1, 16-byte aligned tensors and a workspace of nnf_bn_train_workspace_bytes()");
 	return st;
+}
+
+// The library's process-wide error word: a device variable inside the library, so that reaching it needs no
+// allocation. Kernels raise it next to their launch's own status word; no kernel reads it, so an old failure
+// cannot make a later launch give up its waits.
+static __device__ int nnf_error_word_storage;
+
+namespace nnf
+{
+	int * device_error_word()
+	{
+		static std::mutex mu;
+		static int * words[64] = {};
+		int dev = 0;
+		if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+			return nullptr;
+		std::lock_guard<std::mutex> lock(mu);
+		if (!words[dev])
+		{
+			int * w = nullptr;
+			if (cudaGetSymbolAddress((void **)&w, nnf_error_word_storage) != cudaSuccess)
+			{
+				cudaGetLastError();
+				return nullptr;
+			}
+			words[dev] = w;
+		}
+		return words[dev];
+	}
+}
+
+// Reads and clears the process-wide error word. Synchronises the device; meant for tests and diagnosis, not
+// for the enqueue path (nnf_bn_train_read_report is the asynchronous, per-launch way).
+extern "C" int nnf_fused_error_check(void)
+{
+	int * w = device_error_word();
+	if (!w)
+		return 0;
+	int v = 0;
+	if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+		return -1;
+	if (v)
+		cudaMemset(w, 0, sizeof(int));
+	return v;
+}
+
+extern "C" int nnf_bn_train_read_report(nnf_stream_t stream, nnf_launch_report * host_report, const void * workspace)
+{
+	static_assert(sizeof(nnf_launch_report) <= sizeof(launch_report), "the public report is a prefix of the workspace head");
+	if (!host_report || !workspace)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_read_report: null pointer");
+	const cudaError_t e = cudaMemcpyAsync(host_report, workspace, sizeof(nnf_launch_report), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+	if (e != cudaSuccess)
+		return set_error(NNF_ERR_CUDA, "nnf_bn_train_read_report: cudaMemcpyAsync: %s", cudaGetErrorString(e));
+	return NNF_OK;
+}
+
+extern "C" int nnf_bn_train_fwd(nnf_stream_t stream, float * y, float * saved, float * sums, const float * x,
+	const float * gamma, const float * beta, float eps,
+	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,
+	void * workspace, size_t workspace_bytes)
+{
+	if (n <= 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_fwd: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (!y || !x || !gamma || !beta || !saved)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_fwd: null pointer");
+	act_chain chain;
+	int st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	st = chain_forward_impl<false>((cudaStream_t)stream, y, saved, sums, x, gamma, beta, eps, chain, n, c, hw, workspace, workspace_bytes, nullptr);
+	if (st == 2)
+		return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_fwd: a 16-byte aligned workspace of %zu bytes is required, got %zu",
+			nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
+	if (st != 1)
+		return st;
+	// shapes the single launch does not take (unaligned tensors, planes that neither are whole float4s nor fill
+	// channel groups, extents beyond its index range): statistics kernel, then apply kernel
+	if (!sums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_fwd: this shape needs the two-kernel form, which requires the sums buffer");
+	st = nnf_bn_train_stats(stream, sums, x, n, c, hw, workspace, workspace_bytes);
+	if (st != NNF_OK)
+		return st;
+	return nnf_bn_train_apply_act(stream, y, saved, x, gamma, beta, sums, double(n) * double(hw), eps, acts, n_acts, n, c, hw);
+}
+
+extern "C" int nnf_bn_train_bwd(nnf_stream_t stream, float * dx, float * bsums, const float * dy, const float * x,
+	const float * gamma, const float * beta, const float * saved,
+	const nnf_act * acts, int n_acts,
+	float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
+	const float * mean, const float * invsigma, float entry_count,
+	int64_t n, int64_t c, int64_t hw, int add_to_destination,
+	void * workspace, size_t workspace_bytes)
+{
+	if (n <= 0 || c <= 0 || hw <= 0)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd: bad extents n=%lld c=%lld hw=%lld", (long long)n, (long long)c, (long long)hw);
+	if (!dx || !dy || !x || !gamma || !beta || !saved || !bsums)
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd: null pointer");
+	if ((grad_mean && !mean) || (grad_invsigma && !invsigma))
+		return set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_bn_train_bwd: running-statistics gradients requested without the running statistics");
+	act_chain chain;
+	int st = make_chain(chain, acts, n_acts, true);
+	if (st != NNF_OK)
+		return st;
+	chain_fill_backward_constants(chain, acts, n_acts);
+	int prelus = 0;
+	for (int i = 0; i < chain.n; ++i)
+		prelus += chain.a[i].kind == NNF_ACT_PRELU;
+	if (prelus > 1)
+		return set_error(NNF_ERR_UNSUPPORTED, "nnf_bn_train_bwd: at most one PReLU per fused chain");
+	if (!add_to_destination)
+	{
+		st = chain_backward_impl<false>((cudaStream_t)stream, dx, bsums, dy, x, gamma, beta, saved, chain, grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope,
+			mean, invsigma, entry_count, n, c, hw, workspace, workspace_bytes, nullptr);
+		if (st == 2)
+			return set_error(NNF_ERR_WORKSPACE, "nnf_bn_train_bwd: a 16-byte aligned workspace of %zu bytes is required, got %zu",
+				nnf_bn_train_workspace_bytes(n, c, hw), workspace_bytes);
+		if (st != 1)
+			return st;
+	}
+	// dx accumulated into its destination, or a shape the single launch does not take: two kernels
+	st = nnf_bn_train_bwd_stats(stream, bsums, nullptr, dy, x, gamma, beta, saved, acts, n_acts, n, c, hw, workspace, workspace_bytes);
+	if (st != NNF_OK)
+		return st;
+	return nnf_bn_train_bwd_apply(stream, dx, dy, x, gamma, beta, saved, bsums, bsums, double(n) * double(hw), acts, n_acts,
+		grad_gamma, grad_beta, grad_mean, grad_invsigma, grad_slope, mean, invsigma, entry_count, n, c, hw, add_to_destination);
 }

@@ -552,9 +552,9 @@ namespace nnf
 			// streaming backward-apply kernel with 8 (95% of the measured copy bandwidth against 88% with
 			// one wave: CTAs that start at different times mix their loads and stores instead of moving in
 			// lockstep through load / compute / store phases).
-			if (getenv("NNF_CH_WAVES")) // tuning aid
-				waves = atoi(getenv("NNF_CH_WAVES"));
-			int64_t split = (int64_t(kSmCount) * ctas_per_sm * (waves < 1 ? 1 : waves)) / c;
+			if (tune().channel_waves > 0)
+				waves = tune().channel_waves;
+			int64_t split = (int64_t(sm_count()) * ctas_per_sm * (waves < 1 ? 1 : waves)) / c;
 			const int64_t max_by_work = (n * hw) / 8192 > 0 ? (n * hw) / 8192 : 1;
 			if (split > max_by_work) split = max_by_work;
 			if (split > n) split = n;
@@ -589,7 +589,7 @@ namespace nnf
 		// false: the shape keeps the per-channel kernels
 		bool make_group_geom(group_geom& g, int64_t n, int64_t c, int64_t hw, bool aligned)
 		{
-			if (!aligned || hw % 4 == 0 || getenv("NNF_NO_GROUPED"))
+			if (!aligned || hw % 4 == 0 || tune().no_grouped == 1)
 				return false;
 			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
 			const int64_t vpu = unit * hw / 4;        // vectors of one unit of channels
@@ -612,8 +612,8 @@ namespace nnf
 			g.group = (uint32_t)group;
 			g.groups = (uint32_t)div_up(c, group);
 			g.vectors_per_thread = r;
-			const int64_t waves = getenv("NNF_GROUP_WAVES") ? atoi(getenv("NNF_GROUP_WAVES")) : 1;   // tuning aid
-			int64_t split = div_up(int64_t(kSmCount) * 8 * waves, g.groups);
+			const int64_t waves = tune().group_waves > 0 ? tune().group_waves : 1;
+			int64_t split = div_up(int64_t(sm_count()) * 8 * waves, g.groups);
 			if (split > n / 4) split = n / 4;
 			if (split > kMaxSplit) split = kMaxSplit;
 			if (split < 1) split = 1;
@@ -1061,11 +1061,10 @@ using namespace nnf;
 
 extern "C" size_t nnf_bn_train_workspace_bytes(int64_t n, int64_t c, int64_t hw)
 {
-	(void)n; (void)hw;
-	if (c <= 0)
+	if (c <= 0 || n <= 0 || hw <= 0)
 		return 0;
 	const size_t two_kernel = size_t(c) * kMaxSplit * kSums * sizeof(double);
-	const size_t single_launch = chain_workspace_bytes(c);
+	const size_t single_launch = chain_workspace_bytes(n, c, hw);
 	return two_kernel > single_launch ? two_kernel : single_launch;
 }
 
@@ -1210,7 +1209,7 @@ int apply_impl(nnf_stream_t stream, float * y, float * saved, const float * x, c
 	}
 	// planes large enough to keep a CTA busy and whole float4s: the channel-ordered kernel (L2 reuse after the
 	// statistics kernel); anything else: the flat streaming kernel
-	if (hw % 4 == 0 && (n * hw >= 16384 || peer) && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && !getenv("NNF_APPLY_FLAT"))
+	if (hw % 4 == 0 && (n * hw >= 16384 || peer) && prelus <= 1 && aligned16(x) && aligned16(y) && n * hw <= kMaxElemsPerLaunch && tune().apply_flat != 1)
 	{
 		chan_geom g;
 		st = make_chan_geom(g, "nnf_bn_train_apply_act", n, c, hw, true, resident_ctas_per_sm(bn_apply_channel_kernel<-1, 0>), 8);

@@ -13,7 +13,54 @@ namespace nnf
 	int set_error(int status, const char * fmt, ...);
 	int check_launch(const char * what);
 
-	constexpr int kSmCount = 148; // B200; grids are sized in multiples of this
+	// ---- what the device offers (nnforge/cuda/cuda_running_configuration.h:126-153) ---------------
+	// Filled once per device from cudaDeviceGetAttribute; grids are sized in multiples of the SM count and
+	// shared-memory tiles against the opt-in limit, instead of literals for one chip.
+	struct running_configuration
+	{
+		int device_id;
+		int compute_capability_major, compute_capability_minor;
+		int multiprocessor_count;
+		int max_threads_per_multiprocessor;
+		int max_shared_memory_per_block_optin;   // bytes a kernel may ask for with cudaFuncSetAttribute
+		int max_shared_memory_per_multiprocessor;
+		int l2_cache_size;
+		int max_registers_per_multiprocessor;
+	};
+	const running_configuration& running_config();   // of the calling thread's current device
+	inline int sm_count() { return running_config().multiprocessor_count; }
+	// Most shared memory one CTA of a staging kernel asks for (the opt-in limit less room for static data
+	// and a second resident CTA's reserve: 200 KB on B200), and what all CTAs of an SM can share.
+	inline size_t staging_smem_limit()
+	{
+		const int lim = running_config().max_shared_memory_per_block_optin;
+		return size_t(lim > 64 * 1024 ? lim - 27 * 1024 : lim);
+	}
+	inline size_t sm_smem_budget()
+	{
+		const int lim = running_config().max_shared_memory_per_multiprocessor;
+		return size_t(lim > 64 * 1024 ? lim - 8 * 1024 : lim);
+	}
+
+	// ---- knobs of the launch plans -----------------------------------------------------------------
+	// Process-wide, set through nnf_set_tuning() (tests walk the geometries with it; nothing reads the
+	// environment). Values <= 0 mean "the built-in choice".
+	struct tuning
+	{
+		int elementwise_waves;        // grid of the streaming kernel in resident waves
+		int elementwise_group_waves;  // the same for the channel-group inference kernel
+		int pool_waves;               // max / average subsampling grids
+		int pool_group_floats;        // floats of one staged plane group
+		int channel_waves;            // training kernels with one CTA per (channel, slice)
+		int group_waves;              // the same for the channel-group training kernels
+		int chain_s_kb, chain_a_kb;   // single-launch training kernel: KB of one tensor per statistics / apply item
+		int chain_dist;               // channels between an apply item and the statistics items it shares a step with
+		int chain_chunk_mb, chain_lag;// channel-group form of that kernel: chunk size and lag in chunks
+		int no_grouped;               // 1: planes that are not whole float4s take the per-channel kernels
+		int apply_flat;               // 1: training apply through the flat streaming kernel
+		long long peer_wait_ns;       // how long a launch waits for another rank's statistics before it gives up
+	};
+	tuning& tune();
 
 	// Largest element count one launch indexes with 32-bit arithmetic. Bigger tensors are split on
 	// the host into several launches at entry boundaries (or flat boundaries for shapeless ops).
@@ -388,15 +435,8 @@ namespace nnf
 	int make_peer_dst(peer_dst& d, void * const * peer_bufs, int rank, int world, int k, int kmax, uint32_t seq, const char * who);
 	int * device_error_word();
 
-	// single-launch training batch norm whose second read comes from L2 (nnf_bn_chain.cu); 1 = shape not suited
-	size_t chain_workspace_bytes(int64_t c);
-	int chain_forward_launch(cudaStream_t stream, float * y, float * saved, float * sums, const float * x, const float * gamma, const float * beta,
-		float eps, const act_chain& chain, int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
-	int chain_backward_launch(cudaStream_t stream, float * dx, float * bsums, const float * dy, const float * x,
-		const float * gamma, const float * beta, const float * saved, const act_chain& chain,
-		float * grad_gamma, float * grad_beta, float * grad_mean, float * grad_invsigma, float * grad_slope,
-		const float * mean, const float * invsigma, float entry_count,
-		int64_t n, int64_t c, int64_t hw, void * workspace, size_t workspace_bytes);
+	// workspace of the single-launch training batch norm (nnf_bn_chain.cu)
+	size_t chain_workspace_bytes(int64_t n, int64_t c, int64_t hw);
 
 	// ---- memory access helpers -----------------------------------------------------------------
 	// Streaming (evict-first) 128-bit accesses: every tensor on this path is touched once per kernel.

@@ -419,7 +419,7 @@ namespace nnf
 		// false: the shape keeps the flat kernel
 		bool plan_grouped(ewg_geom& g, int64_t n, int64_t c, int64_t hw)
 		{
-			if (hw % 4 == 0 || getenv("NNF_EW_NO_GROUPED") || n < 8 || n > 0x7fffffff || c > 0x7fffffff)
+			if (hw % 4 == 0 || tune().no_grouped == 1 || n < 8 || n > 0x7fffffff || c > 0x7fffffff)
 				return false;
 			const int64_t unit = (hw % 2 == 0) ? 2 : 4;
 			const int64_t vpu = unit * hw / 4;       // vectors of one unit of channels
@@ -434,8 +434,8 @@ namespace nnf
 			g.group = (uint32_t)group;
 			g.groups = (uint32_t)div_up(c, group);
 			g.threads = (uint32_t)(div_up(group * hw / 4, 32) * 32);
-			const int64_t waves = getenv("NNF_EWG_WAVES") ? atoi(getenv("NNF_EWG_WAVES")) : 2;   // tuning aid
-			int64_t split = div_up(int64_t(kSmCount) * 8 * waves, g.groups);
+			const int64_t waves = tune().elementwise_group_waves > 0 ? tune().elementwise_group_waves : 2;
+			int64_t split = div_up(int64_t(sm_count()) * 8 * waves, g.groups);
 			if (split > n / 4) split = n / 4;
 			if (split < 1) split = 1;
 			g.entries_per_cta = (uint32_t)div_up(n, split);
@@ -486,10 +486,8 @@ namespace nnf
 				per_sm = v;
 				cached_smem = smem;
 			}
-			static int forced = -1; // tuning aid: NNF_EW_WAVES = grid size in units of one resident wave
-			if (forced < 0)
-				forced = getenv("NNF_EW_WAVES") ? atoi(getenv("NNF_EW_WAVES")) : 0;
-			const int64_t wave = int64_t(kSmCount) * per_sm;
+			const int forced = tune().elementwise_waves;   // grid size in units of one resident wave
+			const int64_t wave = int64_t(sm_count()) * per_sm;
 			const int waves = forced > 0 ? forced : (work >= 64 * wave ? 32 : 8);
 			const int64_t cap = wave * waves;
 			const int64_t g = work < cap ? work : cap;
@@ -815,7 +813,7 @@ namespace nnf
 		int grid_for(int64_t cnt, int per_thread_vec)
 		{
 			int64_t work = div_up(cnt / 4 + 1, int64_t(kThreads) * per_thread_vec);
-			const int64_t cap = int64_t(kSmCount) * kCtasPerSm;
+			const int64_t cap = int64_t(sm_count()) * kCtasPerSm;
 			if (work > cap)
 				work = cap;
 			return work < 1 ? 1 : (int)work;

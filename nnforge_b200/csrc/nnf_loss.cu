@@ -401,7 +401,7 @@ namespace nnf
 				p.rows = n;
 				p.hw = 1;
 				const int64_t blocks_needed = div_up(n, 8); // 8 warps per CTA
-				const int grid = (int)(blocks_needed < int64_t(kSmCount) * 64 ? blocks_needed : int64_t(kSmCount) * 64);
+				const int grid = (int)(blocks_needed < int64_t(sm_count()) * 64 ? blocks_needed : int64_t(sm_count()) * 64);
 				const bool vec = (c & 3) == 0 && c <= 1024 && aligned16(in) && aligned16(targets) && (!out || aligned16(out));
 				if (vec && c <= 128) loss_rows_kernel<1, MODE><<<grid, 256, 0, s>>>(p);
 				else if (vec && c <= 256) loss_rows_kernel<2, MODE><<<grid, 256, 0, s>>>(p);
@@ -426,7 +426,7 @@ namespace nnf
 				p.hw = (uint32_t)hw;
 				p.hwdiv = fastdiv((uint32_t)hw);
 				const int64_t blocks_needed = div_up(p.rows, 256);
-				const int grid = (int)(blocks_needed < int64_t(kSmCount) * 128 ? blocks_needed : int64_t(kSmCount) * 128);
+				const int grid = (int)(blocks_needed < int64_t(sm_count()) * 128 ? blocks_needed : int64_t(sm_count()) * 128);
 				if (c <= 8) loss_pixels_kernel<8, MODE><<<grid, 256, 0, s>>>(p);
 				else if (c <= 16) loss_pixels_kernel<16, MODE><<<grid, 256, 0, s>>>(p);
 				else if (c <= 24) loss_pixels_kernel<24, MODE><<<grid, 256, 0, s>>>(p);
@@ -587,7 +587,7 @@ extern "C" int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * 
 		p.rows = n;
 		p.hw = 1;
 		const int64_t blocks_needed = div_up(n, 8);
-		const int grid = (int)(blocks_needed < int64_t(kSmCount) * 64 ? blocks_needed : int64_t(kSmCount) * 64);
+		const int grid = (int)(blocks_needed < int64_t(sm_count()) * 64 ? blocks_needed : int64_t(sm_count()) * 64);
 		accuracy_rows_kernel<<<grid, 256, 0, s>>>(p);
 		return check_launch("accuracy_rows_kernel");
 	}
@@ -605,7 +605,7 @@ extern "C" int nnf_accuracy_fwd(nnf_stream_t stream, float * out, const float * 
 		p.hw = (uint32_t)hw;
 		p.hwdiv = fastdiv((uint32_t)hw);
 		const int64_t blocks_needed = div_up(p.rows, 256);
-		const int grid = (int)(blocks_needed < int64_t(kSmCount) * 128 ? blocks_needed : int64_t(kSmCount) * 128);
+		const int grid = (int)(blocks_needed < int64_t(sm_count()) * 128 ? blocks_needed : int64_t(sm_count()) * 128);
 		accuracy_pixels_kernel<<<grid, 256, 0, s>>>(p);
 		const int st = check_launch("accuracy_pixels_kernel");
 		if (st != NNF_OK)

@@ -27,7 +27,6 @@ namespace nnf
 	{
 		constexpr int kThreads = 256;
 		constexpr int64_t kGroupFloats = 8192;       // target staged floats per CTA iteration (32 KB)
-		constexpr size_t kMaxDynSmem = 200 * 1024;
 
 		struct pool_geom
 		{
@@ -666,10 +665,7 @@ namespace nnf
 		// grid size in units of one resident wave of CTAs (tuning aid: NNF_POOL_WAVES)
 		int pool_waves()
 		{
-			static int waves = 0;
-			if (waves == 0)
-				waves = getenv("NNF_POOL_WAVES") ? atoi(getenv("NNF_POOL_WAVES")) : 4;
-			return waves < 1 ? 1 : waves;
+			return tune().pool_waves > 0 ? tune().pool_waves : 4;
 		}
 
 		int make_geom(pool_geom& g, const char * who, int64_t n, int64_t c, int64_t h, int64_t w, const nnf_pool * pool)
@@ -699,16 +695,16 @@ namespace nnf
 		int choose_group(const pool_geom& g, int64_t planes, bool& vec_ok)
 		{
 			// measured: 32 KB groups for large planes (56x56), 16 KB for small ones (more CTAs per SM)
-			const int64_t group_floats = getenv("NNF_POOL_GROUP") ? atoi(getenv("NNF_POOL_GROUP")) : (g.hw >= 2048 ? kGroupFloats : kGroupFloats / 2); // env: tuning aid
+			const int64_t group_floats = tune().pool_group_floats > 0 ? tune().pool_group_floats : (g.hw >= 2048 ? kGroupFloats : kGroupFloats / 2);
 			int64_t grp = group_floats / g.hw;
 			if (grp < 1)
 				grp = 1;
-			if (size_t(grp) * g.hw * sizeof(float) > kMaxDynSmem)
+			if (size_t(grp) * g.hw * sizeof(float) > staging_smem_limit())
 				return 0;
 			if (grp >= 4 && (g.hw % 4) != 0)
 				grp &= ~int64_t(3);
 			// keep at least ~4 groups per SM so that the grid stays balanced
-			while (grp > 4 && div_up(planes, grp) < int64_t(kSmCount) * 4)
+			while (grp > 4 && div_up(planes, grp) < int64_t(sm_count()) * 4)
 				grp = (grp / 2) & ~int64_t(3);
 			if (grp < 1)
 				grp = 1;
@@ -738,7 +734,7 @@ namespace nnf
 				if (fused)
 					return set_error(NNF_ERR_UNSUPPORTED, "fused max subsampling: a %ux%u plane does not fit shared memory", p.g.w, p.g.h);
 				const int64_t blocks = div_up(p.planes * p.g.ohw, kThreads);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 8 ? blocks : int64_t(kSmCount) * 8);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 8 ? blocks : int64_t(sm_count()) * 8);
 				pool_fwd_direct_kernel<<<grid, kThreads, 0, s>>>(p.pooled, p.argmax, p.x, p.g, p.planes);
 				return check_launch("pool_fwd_direct_kernel");
 			}
@@ -746,16 +742,16 @@ namespace nnf
 			p.vec_ok = vec_ok ? 1 : 0;
 			const size_t smem = size_t(grp) * p.g.hw * sizeof(float);
 			const int64_t ngroups = div_up(p.planes, grp);
-			int per_sm = (int)((220 * 1024) / (smem + 1024));
+			int per_sm = (int)(sm_smem_budget() / (smem + 1024));
 			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-			const int64_t cap = int64_t(kSmCount) * per_sm * pool_waves();
+			const int64_t cap = int64_t(sm_count()) * per_sm * pool_waves();
 			const int grid = (int)(ngroups < cap ? ngroups : cap);
 			const bool clip = need_clip;
 			const int ww = p.g.win_w, wh = p.g.win_h;
 			cudaError_t e = cudaSuccess;
 #define NNF_POOL_FWD(FUSED, WW, WH, CLIP) \
 			{ \
-				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<FUSED, WW, WH, CLIP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				e = cudaFuncSetAttribute(pool_fwd_staged_kernel<FUSED, WW, WH, CLIP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit()); \
 				if (e == cudaSuccess) \
 					pool_fwd_staged_kernel<FUSED, WW, WH, CLIP><<<grid, kThreads, smem, s>>>(p); \
 			}
@@ -793,10 +789,10 @@ namespace nnf
 			const int grp = choose_group(p.g, p.planes, vec_ok);
 			const bool ragged_fast = fused && p.g.win_w == 3 && p.g.win_h == 3 && p.g.sw == 2 && p.g.sh == 2 && !((p.g.w & 3) == 0 && vec_ok);
 			const size_t smem = (((size_t(grp) * p.g.ohw * 2 + 3) & ~size_t(3)) + (ragged_fast ? ((size_t(grp) * p.g.hw + 3) & ~size_t(3)) + size_t(grp) : 0)) * sizeof(float);
-			if (grp == 0 || smem > kMaxDynSmem)
+			if (grp == 0 || smem > staging_smem_limit())
 			{
 				const int64_t blocks = div_up(p.planes * p.g.hw, kThreads);
-				const int grid = (int)(blocks < int64_t(kSmCount) * 8 ? blocks : int64_t(kSmCount) * 8);
+				const int grid = (int)(blocks < int64_t(sm_count()) * 8 ? blocks : int64_t(sm_count()) * 8);
 				if (fused)
 					pool_bwd_direct_kernel<true><<<grid, kThreads, 0, s>>>(p);
 				else
@@ -806,15 +802,15 @@ namespace nnf
 			p.group = grp;
 			p.vec_ok = vec_ok ? 1 : 0;
 			const int64_t ngroups = div_up(p.planes, grp);
-			int per_sm = (int)((220 * 1024) / (smem + 1024));
+			int per_sm = (int)(sm_smem_budget() / (smem + 1024));
 			per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-			const int64_t cap = int64_t(kSmCount) * per_sm * pool_waves();
+			const int64_t cap = int64_t(sm_count()) * per_sm * pool_waves();
 			const int grid = (int)(ngroups < cap ? ngroups : cap);
 			const int ww = p.g.win_w, wh = p.g.win_h, sw = p.g.sw, sh = p.g.sh;
 			cudaError_t e = cudaSuccess;
 #define NNF_POOL_BWD(FUSED, WW, WH, SW, SH) \
 			{ \
-				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit()); \
 				if (e == cudaSuccess) \
 					pool_bwd_staged_kernel<FUSED, WW, WH, SW, SH><<<grid, kThreads, smem, s>>>(p); \
 			}
@@ -824,13 +820,13 @@ namespace nnf
 #define NNF_POOL_BWD_SHAPE(FUSED) \
 			if (ww == 3 && wh == 3 && sw == 2 && sh == 2) \
 			{ \
-				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit()); \
 				if (e == cudaSuccess) \
 					pool_bwd_staged_kernel<FUSED, 3, 3, 2, 2, true><<<grid, kThreads, smem, s>>>(p); \
 			} \
 			else if (ww == 2 && wh == 2 && sw == 2 && sh == 2 && (p.row4_vec || !FUSED)) \
 			{ \
-				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 2, 2, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem); \
+				e = cudaFuncSetAttribute(pool_bwd_staged_kernel<FUSED, 2, 2, 2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit()); \
 				if (e == cudaSuccess) \
 					pool_bwd_staged_kernel<FUSED, 2, 2, 2, 2, true><<<grid, kThreads, smem, s>>>(p); \
 			} \

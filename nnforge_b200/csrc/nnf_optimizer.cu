@@ -429,7 +429,7 @@ extern "C" int nnf_bn_calibrate_accumulate(nnf_stream_t stream, void * accumulat
 	p.c = uint32_t(c);
 	p.hw = uint32_t(hw);
 	p.vec = (hw % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
-	int64_t split = (int64_t(kSmCount) * 8 + c - 1) / c;
+	int64_t split = (int64_t(sm_count()) * 8 + c - 1) / c;
 	split = split < 1 ? 1 : split;
 	split = split > kCalMaxSplit ? kCalMaxSplit : split;
 	split = split > n ? n : split;

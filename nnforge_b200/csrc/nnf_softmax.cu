@@ -425,7 +425,6 @@ namespace nnf
 			}
 		}
 
-		constexpr size_t kMaxDynSmem = 200 * 1024;
 
 		template <bool BACKWARD>
 		int run_softmax(cudaStream_t s, float * out, const float * in0, const float * in1, int64_t n, int64_t c, int64_t hw, int add)
@@ -436,7 +435,7 @@ namespace nnf
 				if (c <= 1024)
 				{
 					const int64_t blocks_needed = div_up(rows, 8);
-					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 64 ? blocks_needed : int64_t(kSmCount) * 64);
+					const int grid = (int)(blocks_needed < int64_t(sm_count()) * 64 ? blocks_needed : int64_t(sm_count()) * 64);
 					if ((c & 3) == 0 && aligned16(out) && aligned16(in0) && (!in1 || aligned16(in1)))
 					{
 #define NNF_ROWS4(VPL) softmax_rows_warp4_kernel<VPL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
@@ -457,11 +456,11 @@ namespace nnf
 #undef NNF_ROWS
 					return check_launch("softmax_rows_warp_kernel");
 				}
-				const int grid = (int)(rows < int64_t(kSmCount) * 4 ? rows : int64_t(kSmCount) * 4);
+				const int grid = (int)(rows < int64_t(sm_count()) * 4 ? rows : int64_t(sm_count()) * 4);
 				const size_t smem = size_t(c) * sizeof(float);
-				if (!BACKWARD && smem <= kMaxDynSmem)
+				if (!BACKWARD && smem <= staging_smem_limit())
 				{
-					cudaError_t e = cudaFuncSetAttribute(softmax_rows_block_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+					cudaError_t e = cudaFuncSetAttribute(softmax_rows_block_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit());
 					if (e != cudaSuccess)
 						return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 					softmax_rows_block_kernel<BACKWARD, true><<<grid, 256, smem, s>>>(out, in0, in1, rows, (int)c, add);
@@ -488,7 +487,7 @@ namespace nnf
 				if (c <= 32)
 				{
 					const int64_t blocks_needed = div_up(pixels, 256);
-					const int grid = (int)(blocks_needed < int64_t(kSmCount) * 128 ? blocks_needed : int64_t(kSmCount) * 128);
+					const int grid = (int)(blocks_needed < int64_t(sm_count()) * 128 ? blocks_needed : int64_t(sm_count()) * 128);
 					if (c <= 8)
 						softmax_pixels_reg_kernel<8, BACKWARD><<<grid, 256, 0, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);
 					else if (c <= 16)
@@ -505,13 +504,13 @@ namespace nnf
 				{
 					const int64_t ntiles = div_up(pixels, 32);
 					const size_t smem = size_t(c) * 32 * sizeof(float) * (BACKWARD ? 2 : 1);
-					const bool in_smem = smem <= kMaxDynSmem;
-					const int per_sm = in_smem ? (int)(kMaxDynSmem / (smem < 1024 ? 1024 : smem)) : 8;
-					const int64_t cap = int64_t(kSmCount) * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+					const bool in_smem = smem <= staging_smem_limit();
+					const int per_sm = in_smem ? (int)(staging_smem_limit() / (smem < 1024 ? 1024 : smem)) : 8;
+					const int64_t cap = int64_t(sm_count()) * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
 					const int grid = (int)(ntiles < cap ? ntiles : cap);
 					if (in_smem)
 					{
-						cudaError_t e = cudaFuncSetAttribute(softmax_pixels_tile_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+						cudaError_t e = cudaFuncSetAttribute(softmax_pixels_tile_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit());
 						if (e != cudaSuccess)
 							return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 						softmax_pixels_tile_kernel<BACKWARD, true><<<grid, 256, smem, s>>>(o, a, b, pixels, (uint32_t)hw, fastdiv((uint32_t)hw), (int)c, add);

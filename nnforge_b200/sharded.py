@@ -104,9 +104,21 @@ class InLaunchExchange:
         dist.all_reduce(tensor, group=self.group)
 
 
+class ExchangeTimeout(RuntimeError):
+    """A single-launch sharded step gave up waiting for another rank's statistics (or for this GPU's own items): the
+    outputs of that step are not to be used. `reports` holds the launch reports that said so."""
+
+    def __init__(self, reports):
+        super().__init__("a batch-sharded batch-norm launch ran out of its bounded wait: %s" % (reports,))
+        self.reports = reports
+
+
 class ShardedBatchNormAct:
     def __init__(self, kernels, channels, eps, acts, device, group=None, on_phase=None, exchange=None):
         self.k = kernels
+        self._pending = []        # (event, pinned report words, what) of single-launch steps not yet looked at
+        self._free_reports = []
+        self.degraded = False     # after a timed-out step: the NCCL sequence until reset_exchange()
         self.exchange = exchange if exchange is not None else NcclExchange(group)
         self.on_phase = on_phase or (lambda name: None)  # called after each enqueue, e.g. to record CUDA events
         self.c = channels
@@ -135,6 +147,54 @@ class ShardedBatchNormAct:
         entries = global_entries if global_entries is not None else n * self.world
         return float(entries * hw)
 
+    # ---- what the single-launch steps report ------------------------------------------------------------------
+    def _note_launch(self, what, workspace):
+        """Enqueues the copy of the launch's report behind the launch; looked at by check()."""
+        read = getattr(self.k, "read_report", None)
+        if read is None:
+            return
+        words = self._free_reports.pop() if self._free_reports else self._new_report()
+        read(words, workspace)
+        event = self.k.make_event() if hasattr(self.k, "make_event") else torch.cuda.Event()
+        event.record()
+        self._pending.append((event, words, what))
+
+    def _new_report(self):
+        words = torch.zeros(self.k.REPORT_WORDS, dtype=torch.int64)
+        return words.pin_memory() if torch.cuda.is_available() else words
+
+    def check(self, block=True):
+        """Looks at the reports of the single-launch steps enqueued so far (all of them with block=True, else those the
+        GPU has already finished). A step whose wait ran out raises ExchangeTimeout; from then on the layer runs the
+        statistics kernel / NCCL all-reduce / apply kernel sequence, which cannot time out silently, until
+        reset_exchange() is called. Call it at a step boundary, before the outputs of the step are trusted."""
+        bad, still = [], []
+        for event, words, what in self._pending:
+            if not block and not event.query():
+                still.append((event, words, what))
+                continue
+            event.synchronize()
+            report = self.k.parse_report(words)
+            self._free_reports.append(words)
+            if report["status"] != 0:
+                bad.append((what, report))
+        self._pending = still
+        if bad:
+            self.degraded = True
+            raise ExchangeTimeout(bad)
+
+    def reset_exchange(self):
+        self.degraded = False
+
+    def last_wait_ns(self):
+        """(sum, max) of the waits inside the most recent single-launch step whose report has arrived; (0, 0) if none."""
+        total = longest = 0
+        for event, words, what in self._pending:
+            if event.query():
+                r = self.k.parse_report(words)
+                total, longest = total + r["wait_ns_total"], max(longest, r["wait_ns_max"])
+        return total, longest
+
     def _in_launch_ok(self, x, hw):
         """Shapes the one-launch sharded entry points take (the library decides; planes of whole float4s always are)."""
         supported = getattr(self.k, "bn_train_sharded_supported", None)
@@ -145,14 +205,17 @@ class ShardedBatchNormAct:
         self.on_phase("start")
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
-        if self.world > 1 and getattr(ex, "in_launch", False) and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels:
+        if self._pending:
+            self.check(block=False)
+        if self.world > 1 and getattr(ex, "in_launch", False) and not self.degraded and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels:
             self.k.bn_train_fwd_sharded(y, self.saved, self.sums, x, gamma, beta, self.eps, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
                                         ex.next_seq())
+            self._note_launch("forward", self.workspace)
             self.on_phase("stats")
             self.on_phase("allreduce_fwd")
             self.on_phase("apply")
             return y
-        if self.world > 1 and getattr(ex, "fused", False) and hw % 4 == 0:
+        if self.world > 1 and getattr(ex, "fused", False) and not self.degraded and hw % 4 == 0:
             seq = ex.next_seq()
             self.k.bn_train_stats_publish(self.sums, x, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)
             self.on_phase("stats")
@@ -178,16 +241,17 @@ class ShardedBatchNormAct:
         mean, invsigma = running if running is not None else (None, None)
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
-        if sharded and getattr(ex, "in_launch", False) and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels and not add_to_destination:
+        if sharded and getattr(ex, "in_launch", False) and not self.degraded and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels and not add_to_destination:
             self.on_phase("bwd_stats")
             self.k.bn_train_bwd_sharded(dx, self.bsums, dy, x, gamma, beta, self.saved, self.acts, m, self._ws(x), ex.ptrs, ex.rank, ex.world,
                                         ex.next_seq(), grad_gamma=grads.get("gamma"), grad_beta=grads.get("beta"), grad_mean=grads.get("mean"),
                                         grad_invsigma=grads.get("invsigma"), grad_slope=grads.get("slope"), mean=mean, invsigma=invsigma,
                                         entry_count=float(x.shape[0]))
+            self._note_launch("backward", self.workspace)
             self.on_phase("allreduce_bwd")
             self.on_phase("bwd_apply")
             return dx
-        if sharded and getattr(ex, "fused", False):
+        if sharded and getattr(ex, "fused", False) and not self.degraded:
             seq = ex.next_seq()
             self.k.bn_train_bwd_stats_publish(self.bsums, dy, x, gamma, beta, self.saved, self.acts, self._ws(x), ex.ptrs, ex.rank, ex.world, ex.kmax, seq)
             self.on_phase("bwd_stats")

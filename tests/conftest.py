@@ -25,3 +25,11 @@ def reference():
     if not ref.available:
         pytest.skip("reference plain-backend build (oracle/_ref) not present on this machine")
     return ref
+
+
+@pytest.fixture
+def tuning():
+    """Sets knobs of the library's launch plans for one test (nnf_set_tuning) and restores the built-in choices afterwards."""
+    import nnforge_b200.capi as capi
+    yield capi.set_tuning
+    capi.set_tuning("reset", 0)

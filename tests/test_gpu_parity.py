@@ -407,14 +407,11 @@ def gpu_train(capi, x, dy, gamma, beta, slope, chain, eps, shards=1, fused=False
 
 @pytest.mark.parametrize("shape", TRAIN_SHAPES)
 @pytest.mark.parametrize("chain", TRAIN_CHAINS)
-@pytest.mark.parametrize("shards", [1, 2, "fused0", "fused1", "fused2", "fused3"])
-def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
+@pytest.mark.parametrize("shards", [1, 2, "fused"])
+def test_bn_train(capi, oracle, shape, chain, shards):
     """shards 1/2: the split entry points with the sums added across shards on the host;
-    fusedK: the single-GPU entry points with NNF_FUSED_MODE=K (single launch of statistics and apply items,
-    L2-resident cluster kernels, shared-memory slab cluster kernels, slab forward + two-kernel backward)."""
+    fused: the single-GPU entry points (one launch of statistics, finishing and apply items per direction)."""
     fused = isinstance(shards, str)
-    if fused:
-        monkeypatch.setenv("NNF_FUSED_MODE", shards[-1])
     shards = 1 if fused else shards
     if shards > shape[0]:
         pytest.skip("fewer entries than shards")
@@ -443,12 +440,14 @@ def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
 
 
 @pytest.mark.parametrize("shape,s_kb,a_kb,chunk_mb,lag", [
-    ((16, 32, 28, 28), 96, 32, 16, 1),   # defaults: one chunk
-    ((16, 32, 28, 28), 4, 4, 0, 1),      # one entry per item, one channel per chunk
-    ((16, 32, 28, 28), 13, 7, 0, 3),     # ragged slices, lag of three chunks
-    ((37, 3, 8, 8), 1, 1, 0, 0),         # no lag: an apply item may start before its statistics are done
+    ((16, 32, 28, 28), 96, 32, 16, 1),   # one item per channel and kind; apply items one channel behind
+    ((16, 32, 28, 28), 4, 4, 0, 1),      # one sweep per item
+    ((16, 32, 28, 28), 13, 7, 0, 3),     # ragged slices, apply items three channels behind
+    ((37, 3, 8, 8), 1, 1, 0, 0),         # no distance: every apply item starts before its statistics are done
     ((600, 2, 8, 8), 1, 1, 1, 1),        # more entries than statistics items allowed per channel
-    ((2, 300, 12, 12), 96, 32, 0, 2),    # many channels, one per chunk capped to 64 chunks
+    ((2, 300, 12, 12), 96, 32, 0, 2),    # many channels, fewer entries than a sweep holds
+    ((3, 5, 72, 72), 16, 16, 0, 2),      # planes wider than a sweep: column tiles, the last one ragged
+    ((40, 4, 36, 36), 48, 64, 0, 40),    # more distance than channels: all statistics first
     # planes that are not whole float4s: items are channel groups (units of 4 channels for odd planes, 2 for even)
     ((33, 48, 7, 7), 48, 64, 16, 1),     # 7x7: groups of 20 channels and a tail group of 8
     ((33, 48, 7, 7), 4, 4, 0, 1),        # one entry per item, one group per chunk
@@ -458,13 +457,14 @@ def test_bn_train(capi, oracle, shape, chain, shards, monkeypatch):
     ((5, 300, 5, 2), 96, 32, 0, 2),      # even plane of 10: units of 2 channels, many groups
     ((6, 6, 3, 5), 48, 64, 16, 1),       # channels not a multiple of the unit: falls back to the separate kernels
 ])
-def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chunk_mb, lag, monkeypatch):
-    """The single-launch statistics/apply kernel over item sizes, chunk sizes and lags."""
-    monkeypatch.setenv("NNF_FUSED_MODE", "0")
-    monkeypatch.setenv("NNF_CHAIN_S_KB", str(s_kb))
-    monkeypatch.setenv("NNF_CHAIN_A_KB", str(a_kb))
-    monkeypatch.setenv("NNF_CHAIN_CHUNK_MB", str(chunk_mb))
-    monkeypatch.setenv("NNF_CHAIN_LAG", str(lag))
+def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chunk_mb, lag, tuning):
+    """The single-launch kernels over item sizes and distances between statistics and apply items (`lag` is the distance in
+    channels for planes of whole float4s, the lag in chunks of channel groups for the others)."""
+    tuning("chain_s_kb", s_kb)
+    tuning("chain_a_kb", a_kb)
+    tuning("chain_dist", lag)
+    tuning("chain_chunk_mb", chunk_mb)
+    tuning("chain_lag", lag + 1)
     chain = ("prelu", "elu")
     g = synth.rng(2, salt=sum(shape) + s_kb)
     x = synth.normal(g, shape, 0.5, 2.0)
@@ -583,7 +583,7 @@ def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
 
 
 @pytest.mark.parametrize("shape", [(8, 6, 8, 8), (8, 8, 7, 7)])   # planes of whole float4s; channel groups
-def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape):
+def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape, tuning):
     """A second rank that never publishes: the apply items give up after their limit, the launch returns
     and reports it; the next call with a complete world works again."""
     g = synth.rng(2, salt=5100)
@@ -596,13 +596,29 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape):
     acts = make_acts(capi, ("prelu", "elu"), sd)
     ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, 64), dtype=torch.uint8, device="cuda")
     y, saved, sums = torch.empty_like(xd), torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda")
+    tuning("peer_wait_ns", 200 * 1000 * 1000)   # production waits ten seconds; the test a fifth of one
+    report = torch.zeros(capi.REPORT_WORDS, dtype=torch.int64).pin_memory()
     capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, 2 * x.size // c, ws, [mine.data_ptr(), absent.data_ptr()], 0, 2, 1)
+    capi.read_report(report, ws)
     torch.cuda.synchronize()
-    assert capi.fused_error_check() == 2
-    assert capi.fused_error_check() == 0
+    first = capi.parse_report(report)
+    assert first["status"] == 2 and first["wait_ns_max"] >= 150 * 1000 * 1000
+    # the next launch starts clean - nobody had to read or clear anything in between - and waits in full again
     capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, x.size // c, ws, [mine.data_ptr()], 0, 1, 2)
+    capi.read_report(report, ws)
     torch.cuda.synchronize()
-    assert capi.fused_error_check() == 0
+    assert capi.parse_report(report)["status"] == 0
+    y_ok = host(y).copy()
+    capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, 2 * x.size // c, ws, [mine.data_ptr(), absent.data_ptr()], 0, 2, 3)
+    capi.read_report(report, ws)
+    torch.cuda.synchronize()
+    again = capi.parse_report(report)
+    assert again["status"] == 2 and again["wait_ns_max"] >= 150 * 1000 * 1000, "a failure long ago must not shorten this wait"
+    capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, x.size // c, ws, [mine.data_ptr()], 0, 1, 4)
+    torch.cuda.synchronize()
+    assert_bits_equal(host(y), y_ok, "the step after a failed one")
+    assert capi.fused_error_check() == 2   # the process-wide word remembers that something failed ...
+    assert capi.fused_error_check() == 0   # ... until it is read
 
 
 @pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 5, 3), (64, 64, 32, 32), (16, 24, 7, 7), (9, 40, 5, 5)])

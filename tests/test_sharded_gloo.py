@@ -105,6 +105,52 @@ class OracleKernels:
                                 grad_slope=grad_slope)
 
 
+class _DoneEvent:
+    def record(self):
+        pass
+
+    def query(self):
+        return True
+
+    def synchronize(self):
+        pass
+
+
+class ReportingKernels(OracleKernels):
+    """OracleKernels plus the launch report of the single-launch entry points; `fail_calls` lists the calls
+    (counted from 1) whose report says that the wait for another rank ran out."""
+    REPORT_WORDS = 3
+
+    def __init__(self, fail_calls=()):
+        super().__init__()
+        self.fail_calls = set(fail_calls)
+        self.calls = 0
+        self.single_launch_calls = 0
+        self.last_status = 0
+
+    def make_event(self):
+        return _DoneEvent()
+
+    def bn_train_fwd_sharded(self, *args, **kwargs):
+        self.calls += 1
+        self.single_launch_calls += 1
+        self.last_status = 2 if self.calls in self.fail_calls else 0
+        super().bn_train_fwd_sharded(*args, **kwargs)
+
+    def bn_train_bwd_sharded(self, *args, **kwargs):
+        self.calls += 1
+        self.single_launch_calls += 1
+        self.last_status = 2 if self.calls in self.fail_calls else 0
+        super().bn_train_bwd_sharded(*args, **kwargs)
+
+    def read_report(self, words, workspace, stream=None):
+        words[0], words[1], words[2] = 1000, 1000, self.last_status << 32
+
+    @staticmethod
+    def parse_report(words):
+        return {"wait_ns_total": int(words[0]), "wait_ns_max": int(words[1]), "status": int(words[2]) >> 32}
+
+
 class FakeInLaunchExchange:
     """Stands for nnforge_b200.sharded.InLaunchExchange on CPU ranks: same attributes, no mailboxes."""
     in_launch = True
@@ -182,3 +228,62 @@ def test_sharded_equals_unsharded(tmp_path, world, in_launch):
         np.testing.assert_allclose(p["saved"], layer.saved.numpy(), rtol=1e-6)
         for k in grads:
             np.testing.assert_allclose(p["g_" + k], grads[k].numpy(), rtol=1e-4, atol=1e-5)
+
+
+def _run_rank_timeout(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from nnforge_b200.sharded import ShardedBatchNormAct, ExchangeTimeout
+    x, dy, gamma, beta, slope = _inputs()
+    n = x.shape[0]
+    lo, hi = n * rank // world, n * (rank + 1) // world
+    t = torch.from_numpy
+    acts = [("prelu", slope), ("elu", None)]
+    kernels = ReportingKernels(fail_calls=(2,))       # the first backward launch reports a wait that ran out, on every rank
+    layer = ShardedBatchNormAct(kernels, 6, 1e-5, acts, "cpu", exchange=FakeInLaunchExchange(6))
+    xs, dys = t(x[lo:hi].copy()), t(dy[lo:hi].copy())
+    y, dx = torch.empty_like(xs), torch.empty_like(xs)
+    layer.forward(y, xs, t(gamma), t(beta))
+    layer.backward(dx, dys, xs, t(gamma), t(beta))
+    raised = False
+    try:
+        layer.check()                                  # the step boundary
+    except ExchangeTimeout as e:
+        raised = True
+        assert [what for what, _ in e.reports] == ["backward"]
+    assert raised and layer.degraded
+    # the step is repeated: the layer now runs the statistics / all-reduce / apply sequence, and the result is right
+    before = kernels.single_launch_calls
+    layer.forward(y, xs, t(gamma), t(beta))
+    layer.backward(dx, dys, xs, t(gamma), t(beta))
+    layer.check()
+    assert kernels.single_launch_calls == before
+    np.savez(os.path.join(out_dir, "rank%d.npz" % rank), y=y.numpy(), dx=dx.numpy())
+    # once the cause is gone the single launch can be switched back on
+    layer.reset_exchange()
+    layer.forward(y, xs, t(gamma), t(beta))
+    layer.check()
+    assert kernels.single_launch_calls == before + 1
+    dist.destroy_process_group()
+
+
+def test_timed_out_step_is_reported_and_redone(tmp_path):
+    """A single-launch step whose report says that a wait ran out: the next check raises, the layer falls back to the
+    statistics kernel / all-reduce / apply kernel sequence, and the repeated step gives the unsharded result."""
+    world = 2
+    port = 29900 + (os.getpid() % 200)
+    mp.spawn(_run_rank_timeout, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, ROOT)
+    from nnforge_b200.sharded import ShardedBatchNormAct
+    x, dy, gamma, beta, slope = _inputs()
+    t = torch.from_numpy
+    acts = [("prelu", slope), ("elu", None)]
+    layer = ShardedBatchNormAct(OracleKernels(), 6, 1e-5, acts, "cpu")
+    y, dx = torch.empty(x.shape), torch.empty(x.shape)
+    layer.forward(y, t(x), t(gamma), t(beta))
+    layer.backward(dx, t(dy), t(x), t(gamma), t(beta))
+    parts = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
+    np.testing.assert_allclose(np.concatenate([p["y"] for p in parts]), y.numpy(), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(np.concatenate([p["dx"] for p in parts]), dx.numpy(), rtol=1e-5, atol=5e-6)
