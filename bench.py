@@ -153,26 +153,52 @@ def cpu_step_seconds(n_sample, threads_hint=None, reps=2):
     return best, orc.threads, kind, desc
 
 
+def make_config(world):
+    """The `config` object of the JSON line: the same for the GPU arm and the reference arm at a given N."""
+    return {"workload": WORKLOAD, "global_batch": N_PER_GPU * world, "parallelism": "dp%d" % world,
+            "collective": "2 x sum of 2*C floats per step" if world > 1 else "none",
+            "l2": "inputs larger than L2 (205 MB per tensor vs 126 MB), no flush needed",
+            "bytes_per_element": {"forward": BYTES_PER_ELEM_FWD, "backward": BYTES_PER_ELEM_BWD}}
+
+
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core."""
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    return cores
+
+
 def run_reference(args):
-    """The reference arm: the reference's CPU path for the same workload, timed on the host cores."""
+    """The reference arm: the reference's CPU path for the same workload, timed on the host cores (rank 0 only; the
+    other ranks leave at once). One step = the whole per-GPU batch of 256 entries, unfused, layer by layer."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_sample = 32
-    # steps are bounded samples; warm-up steps are run too (page faults, thread pool spin-up)
-    for _ in range(min(args.warmup, 2)):
+    use_all_host_threads()
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    n_sample = N_PER_GPU
+    warmup = max(args.warmup, 1)
+    for _ in range(min(warmup, 3)):
         cpu_step_seconds(n_sample, reps=1)
     times = []
-    for _ in range(max(1, min(args.steps, 5))):
+    budget_end = time.time() + 150.0          # the arm ends within a few minutes whatever the host
+    for _ in range(max(1, args.steps)):
         sec, threads, kind, desc = cpu_step_seconds(n_sample, reps=1)
         times.append(sec)
+        if time.time() > budget_end:
+            break
     sec = sum(times) / len(times)
     elems = n_sample * C * H * W
     gbs = elems * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD) / sec / 1e9
     line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 2),
-        "ms_per_step": sec * 1e3 * (N_PER_GPU / n_sample), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2", "note": "CPU path; ms_per_step extrapolated from the sample to the full per-GPU batch"},
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": len(times), "warmup": warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": make_config(world),
+        "note": "CPU path on rank 0's host cores; one step = one GPU's batch of %d entries (the CPU arm does not grow with N)" % n_sample,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind, "sample": desc},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -180,14 +206,22 @@ def run_reference(args):
 
 
 def run_sweep(args):
+    """Prints the per-configuration kernel table on stderr and one JSON line on stdout."""
+    import torch
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    peak, peak_kind = measured_peaks()
+    rows = collect_sweep(args, quick=False)
+    print(json.dumps({"sweep": rows, "peak_GBps": peak, "peak_source": peak_kind}))
+
+
+def collect_sweep(args, quick):
     """Per-configuration kernel table (all five benchmark configurations, single GPU): device time per
     launch by CUDA events, algorithmic GB/s and fraction of the measured copy bandwidth. Tensors smaller
     than L2 are rotated through enough buffers to exceed it and replayed from a CUDA graph, so that the
-    figure is neither an L2 number nor a Python launch-overhead number. Prints a table on stderr and one
-    JSON line on stdout."""
+    figure is neither an L2 number nor a Python launch-overhead number. quick: only the rows of the five
+    configurations themselves (what the benchmark line carries under "configs"), a few seconds in all."""
     import torch
     import nnforge_b200.capi as capi
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     peak, peak_kind = measured_peaks()
     rows = []
 
@@ -251,7 +285,7 @@ def run_sweep(args):
         report(1, "softmax bwd %s" % (list(shape),), timeit(lambda i: capi.softmax_bwd(dx, xs[i], ys[i]), nb), 12 * e, "%d rotating buffers, graph replay" % nb)
         del xs, ys, dx
     # beyond the five configurations: softmax fused with the loss behind it, at sizes above L2
-    for shape in [(65536, 1000, 1, 1), (512, 21, 128, 128)]:
+    for shape in ([] if quick else [(65536, 1000, 1, 1), (512, 21, 128, 128)]):
         e = shape[0] * shape[1] * shape[2] * shape[3]
         logits = torch.randn(shape, device="cuda") * 3
         labels = torch.randint(0, shape[1], (shape[0],) + shape[2:], device="cuda")
@@ -274,11 +308,12 @@ def run_sweep(args):
     m = N_PER_GPU * H * W
     report(2, "bn_train fwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_fwd(y, saved, sums, x, g, b, EPS, acts, workspace=ws), 1), 8 * e)
     report(2, "bn_train bwd, one launch (statistics + apply items)", timeit(lambda i: capi.bn_train_bwd(dx, bs, dy, x, g, b, saved, acts, workspace=ws), 1), 12 * e)
-    report(2, "bn_train stats", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
-    report(2, "bn_train apply+prelu+elu", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, g, b, sums, m, EPS, acts), 1), 8 * e)
-    report(2, "bn_train bwd stats", timeit(lambda i: capi.bn_train_bwd_stats(bs, dy, x, g, b, saved, acts, ws), 1), 8 * e)
-    report(2, "bn_train bwd apply", timeit(lambda i: capi.bn_train_bwd_apply(dx, dy, x, g, b, saved, bs, bs, m, acts), 1), 12 * e)
-    report(2, "reference point: torch copy_ of one tensor", timeit(lambda i: y.copy_(x), 1), 8 * e)
+    if not quick:
+        report(2, "bn_train stats", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
+        report(2, "bn_train apply+prelu+elu", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, g, b, sums, m, EPS, acts), 1), 8 * e)
+        report(2, "bn_train bwd stats", timeit(lambda i: capi.bn_train_bwd_stats(bs, dy, x, g, b, saved, acts, ws), 1), 8 * e)
+        report(2, "bn_train bwd apply", timeit(lambda i: capi.bn_train_bwd_apply(dx, dy, x, g, b, saved, bs, bs, m, acts), 1), 12 * e)
+        report(2, "reference point: torch copy_ of one tensor", timeit(lambda i: y.copy_(x), 1), 8 * e)
     del x, dy, y, dx
     # config 3: BN -> add -> ReLU -> max-pool 3x3/2, forward and backward, four stages
     for c, hw in [(64, 56), (128, 28), (256, 14), (512, 7)]:
@@ -297,7 +332,7 @@ def run_sweep(args):
         report(3, "bn+add+relu+maxpool bwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_bwd(dx, dr, dpo, idx, z, bn[0], bn[3], 0.0, p), nb), (12 + 8 * rho) * e)
         del x, r, z, pooled, idx, dpo, dx, dr
     # beyond the five configurations: the tail of a residual network - BN -> add -> ReLU -> global average pooling
-    for c, hw in [(512, 7), (256, 14)]:
+    for c, hw in ([] if quick else [(512, 7), (256, 14)]):
         shape = (1024, c, hw, hw)
         e = shape[0] * c * hw * hw
         x, r, z = [torch.randn(shape, device="cuda") for _ in range(3)]
@@ -312,7 +347,7 @@ def run_sweep(args):
                timeit(lambda i: capi.bn_add_relu_avgpool_bwd(dx, dr, dpo, z, bn[0], bn[3], 0.0, (hw, hw), mult), 1), 12 * e)
         del x, r, z, pooled, dpo, dx, dr
     # the stand-alone subsampling layers (no batch norm in front): max 3x3/2 and 2x2/2, average 2x2
-    for c, hw, win in [(64, 56, 3), (128, 28, 3), (128, 28, 2), (256, 14, 2)]:
+    for c, hw, win in ([] if quick else [(64, 56, 3), (128, 28, 3), (128, 28, 2), (256, 14, 2)]):
         n = 1024
         shape = (n, c, hw, hw)
         e = n * c * hw * hw
@@ -330,7 +365,7 @@ def run_sweep(args):
             report(3, "avgpool 2x2 bwd N=%d C=%d %dx%d" % (n, c, hw, hw), timeit(lambda i: capi.avgpool_bwd(dx, dpo, (2, 2), 0.25), 1), 5 * e)
         del x, pooled, idx, dpo, dx
     # training batch norm + ReLU on the last stage's 7x7 planes (not whole float4s: the channel-group kernels)
-    for n, c, hw in [(1024, 512, 7), (256, 2048, 7)]:
+    for n, c, hw in ([] if quick else [(1024, 512, 7), (256, 2048, 7)]):
         shape = (n, c, hw, hw)
         e = n * c * hw * hw
         x, dy = torch.randn(shape, device="cuda"), torch.randn(shape, device="cuda")
@@ -345,7 +380,7 @@ def run_sweep(args):
                timeit(lambda i: capi.bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts, workspace=ws), 1), 12 * e)
         del x, dy, y, dx
     # config 4: inference BN + TanH / Sigmoid bandwidth sweep
-    sizes = [128, 1024, 4096] + ([8192] if args.sweep_full else [])
+    sizes = [128, 1024] if quick else [128, 1024, 4096] + ([8192] if args.sweep_full else [])
     for n in sizes:
         shape = (n, 128, 64, 64)
         e = n * 128 * 64 * 64
@@ -355,7 +390,7 @@ def run_sweep(args):
         for name, act in (("tanh", capi.tanh()), ("sigmoid", capi.sigmoid())):
             report(4, "bn_infer+%s N=%d (%.2f GiB in)" % (name, n, e * 4 / 2.0 ** 30), timeit(lambda i: capi.bn_infer_act(y, x, bn=bn, acts=[act]), 1, reps=10), 8 * e)
         del x, y
-    print(json.dumps({"sweep": rows, "peak_GBps": peak, "peak_source": peak_kind}))
+    return rows
 
 
 def main():
@@ -366,6 +401,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--no-configs", action="store_true", help="leave out the table of the other four configurations")
     ap.add_argument("--sweep", action="store_true", help="time every kernel family at all five configurations (single GPU) instead of the benchmark step")
     ap.add_argument("--sweep-full", action="store_true", help="with --sweep: include the 16 GiB case of configuration 4")
     args = ap.parse_args()
@@ -528,6 +564,78 @@ def main():
                                 "frac_of_peak": alg_bytes[k] / (kernel_ms[k] * 1e-3) / 1e9 / peak} for k in phases},
                 "step_frac_of_peak": (value / world) / peak}
 
+    # ---- checks, outside the timed region: nothing above is a number unless these hold ------------------------
+    checks = []
+
+    def note(name, ok, **detail):
+        checks.append(dict({"check": name, "ok": bool(ok)}, **detail))
+
+    def worst(got, want, rtol=1e-5, atol=1e-6):
+        """max over elements of |got - want| / (atol + rtol |want|): <= 1 is inside the tolerance"""
+        return float(((got - want).abs() / (atol + rtol * want.abs())).max().item())
+
+    err_word = capi.fused_error_check()
+    timed_out = None
+    if not single:
+        from nnforge_b200.sharded import ExchangeTimeout
+        try:
+            layer.check(block=True)
+        except ExchangeTimeout as e:
+            timed_out = str(e)
+    note("no bounded wait ran out in the warm-up and timed steps", err_word == 0 and timed_out is None, error_word=err_word, report=timed_out)
+    step()
+    torch.cuda.synchronize()
+    y_run, dx_run, saved_run = y.clone(), dx.clone(), (saved if single else layer.saved).clone()
+    y2, dx2 = torch.empty_like(x), torch.empty_like(x)
+    if single:
+        # (a) another path of this library: statistics kernel, apply kernel, backward statistics kernel, backward apply kernel
+        saved2, sums2, bsums2 = torch.empty(2 * C, device="cuda"), torch.empty(2 * C, device="cuda"), torch.empty(3 * C, device="cuda")
+        capi.bn_train_stats(sums2, x, ws)
+        capi.bn_train_apply_act(y2, saved2, x, gamma, beta, sums2, float(N_PER_GPU * hw), EPS, acts)
+        capi.bn_train_bwd_stats(bsums2, dy, x, gamma, beta, saved2, acts, ws)
+        capi.bn_train_bwd_apply(dx2, dy, x, gamma, beta, saved2, bsums2, bsums2, float(N_PER_GPU * hw), acts)
+        torch.cuda.synchronize()
+        note("single launch against the two-kernel form of this library (1e-5 relative + 1e-6 absolute)",
+             max(worst(saved_run, saved2), worst(y_run, y2), worst(dx_run, dx2)) <= 1.0,
+             saved=worst(saved_run, saved2), y=worst(y_run, y2), dx=worst(dx_run, dx2))
+        # (b) the reference's own arithmetic for this layer: cuDNN's spatial batch norm (the two calls of
+        # nnforge/cuda/batch_norm_layer_updater_cuda.cu:89,145), followed by torch's PReLU and ELU, forward and autograd backward
+        if torch.backends.cudnn.is_available():
+            xr = x.detach().clone().requires_grad_(True)
+            u = torch.nn.functional.batch_norm(xr, None, None, gamma, beta, training=True, momentum=0.1, eps=EPS)
+            yr = torch.nn.functional.elu(torch.nn.functional.prelu(u, slope))
+            yr.backward(dy)
+            torch.cuda.synchronize()
+            wy = worst(y_run, yr.detach(), atol=2e-6)
+            wdx = worst(dx_run, xr.grad, atol=5e-6)
+            note("single launch against cuDNN batch norm + torch PReLU, ELU (1e-5 relative + 2e-6 / 5e-6 absolute: du and dx cancel)",
+                 wy <= 1.0 and wdx <= 1.0, y=wy, dx=wdx)
+            del xr, u, yr
+    else:
+        from nnforge_b200.sharded import NcclExchange
+        other = ShardedBatchNormAct(capi, C, EPS, acts, "cuda", exchange=NcclExchange())
+        other.forward(y2, x, gamma, beta)
+        other.backward(dx2, dy, x, gamma, beta)
+        torch.cuda.synchronize()
+        w = (worst(saved_run, other.saved), worst(y_run, y2), worst(dx_run, dx2))
+        t = torch.tensor([max(w)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        note("%s against statistics kernel + NCCL all-reduce + apply kernel on the same shards (1e-5 relative + 1e-6 absolute), worst rank" % exchange_name,
+             float(t.item()) <= 1.0, worst=float(t.item()), this_rank={"saved": w[0], "y": w[1], "dx": w[2]})
+        gathered = [torch.empty_like(saved_run) for _ in range(world)]
+        dist.all_gather(gathered, saved_run)
+        same = all(bool((g.view(torch.int32) == gathered[0].view(torch.int32)).all().item()) for g in gathered)
+        note("saved {mean, invstd} bit-identical on all ranks", same)
+        err_word = capi.fused_error_check()
+        note("no bounded wait ran out in the checked steps", err_word == 0, error_word=err_word)
+    del y2, dx2
+    parity = {"ok": all(c["ok"] for c in checks), "checks": checks}
+    if dist is not None:
+        ok = torch.tensor([1 if parity["ok"] else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        parity["ok"] = bool(ok.item())       # every rank's checks
+        parity["ranks"] = world
+
     # End to end through the C ABI with HOST buffers: every step copies its x and dy from pinned host memory and
     # its y and dx back, all inside the timed region. The copies of one step overlap the kernels and the opposite
     # copies of its neighbours (three streams, two sets of device buffers): host->device of x, forward, device->host
@@ -597,6 +705,14 @@ def main():
            "h2d_bytes_per_step": 2 * tensor_bytes, "d2h_bytes_per_step": 2 * tensor_bytes, "steps": args.e2e_steps,
            "overlap": "copies of neighbouring steps overlap the kernels (3 streams, 2 buffer sets)"}
 
+    # the other configurations of the benchmark (one GPU each), outside the headline's timed region
+    configs = None
+    if world == 1 and not args.no_configs:
+        del sets, xh, dyh, yh, dxh
+        torch.cuda.empty_cache()
+        configs = [{"config": r["config"], "kernel": r["kernel"], "us": r["us"], "GBps": r["GBps"], "frac": r["frac_of_peak"], "note": r["note"]}
+                   for r in collect_sweep(args, quick=True)]
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sec, threads, kind, desc = cpu_step_seconds(32, reps=2)
@@ -606,17 +722,18 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": N_PER_GPU * world, "parallelism": "dp%d" % world,
-                       "collective": ("2 x sum of 2*C floats per step: " + exchange_name) if world > 1 else "none",
-                       "l2": "inputs larger than L2 (205 MB per tensor vs 126 MB), no flush needed",
-                       "bytes_per_element": {"forward": BYTES_PER_ELEM_FWD, "backward": BYTES_PER_ELEM_BWD}},
+            "config": make_config(world), "exchange": exchange_name,
             "gelem_per_s": elems * world / (ms_step * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "parity_check": parity, "configs": configs,
         }
         result_out.write(json.dumps(line) + "\n")
         result_out.flush()
     if dist is not None:
         dist.destroy_process_group()
+    if not parity["ok"]:
+        print("parity check failed: %s" % json.dumps(parity), file=sys.stderr)
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -50,6 +50,12 @@ class Oracle:
         build_oracle.build()
         self.lib = ct.CDLL(build_oracle.LIB_OMP if parallel else build_oracle.LIB)
         self.lib.orc_max_threads.restype = ct.c_int
+        if parallel:
+            try:
+                cores = len(os.sched_getaffinity(0))
+            except Exception:
+                cores = os.cpu_count() or 1
+            self.lib.orc_set_threads(ct.c_int(cores))
         self.lib.orc_maxpool_out_size.restype = _i64
         self.lib.orc_maxpool_out_size.argtypes = [_i64, _i64, _i64, ct.c_int]
         self.threads = self.lib.orc_max_threads()

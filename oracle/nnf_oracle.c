@@ -49,6 +49,18 @@ int orc_max_threads(void)
 #endif
 }
 
+/* The OpenMP build only: how many threads the loops below use (a launcher may have set OMP_NUM_THREADS=1 for the
+ * process; the timed CPU baseline is meant to use every core it is allowed). */
+void orc_set_threads(int n)
+{
+#ifdef _OPENMP
+	if (n > 0)
+		omp_set_num_threads(n);
+#else
+	(void)n;
+#endif
+}
+
 /* ---- batch norm, inference: nnforge/plain/batch_norm_layer_tester_plain.cpp:30-75 ------------
  * mult = gamma*invsigma; add = beta - mult*mean (both rounded to fp32, per (entry, channel));
  * y = x*mult + add with a separately rounded product (no fused multiply-add). */
