@@ -34,6 +34,7 @@ METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 NCU_TRAFFIC_BYTES = {"forward": 369928704, "backward": 693663488, "bwd_apply": 579759360, "bwd_stats": 414813184}
 WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
+KINK = 1e-5   # |bn output| below which an element is at PReLU's kink for the parity checks of dx
 
 
 def measured_peaks():
@@ -402,6 +403,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--no-configs", action="store_true", help="leave out the table of the other four configurations")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE", help="a knob of the launch plans (nnf_set_tuning), for experiments")
     ap.add_argument("--sweep", action="store_true", help="time every kernel family at all five configurations (single GPU) instead of the benchmark step")
     ap.add_argument("--sweep-full", action="store_true", help="with --sweep: include the 16 GiB case of configuration 4")
     args = ap.parse_args()
@@ -430,6 +432,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
+    for item in args.tune:
+        knob, value = item.split("=")
+        capi.set_tuning(knob, int(value))
 
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1002 + rank)
@@ -570,9 +575,41 @@ def main():
     def note(name, ok, **detail):
         checks.append(dict({"check": name, "ok": bool(ok)}, **detail))
 
-    def worst(got, want, rtol=1e-5, atol=1e-6):
+    def worst(got, want, rtol=1e-5, atol=1e-6, skip=None):
         """max over elements of |got - want| / (atol + rtol |want|): <= 1 is inside the tolerance"""
-        return float(((got - want).abs() / (atol + rtol * want.abs())).max().item())
+        ratio = (got - want).abs() / (atol + rtol * want.abs())
+        if skip is not None:
+            ratio = ratio.masked_fill(skip, 0.0)
+        return float(ratio.max().item())
+
+    def exact_step():
+        """The step in float64 (torch on the GPU; per-channel sums all-reduced in float64 over the ranks)."""
+        m = float(N_PER_GPU * world * hw)
+        xd = x.double()
+        s1, s2 = xd.sum(dim=(0, 2, 3)), (xd * xd).sum(dim=(0, 2, 3))
+        if dist is not None:
+            dist.all_reduce(s1)
+            dist.all_reduce(s2)
+        mean = s1 / m
+        inv = 1.0 / torch.sqrt(s2 / m - mean * mean + EPS)
+        xh = (xd - mean[None, :, None, None]) * inv[None, :, None, None]
+        del xd
+        u = xh * gamma.double()[None, :, None, None] + beta.double()[None, :, None, None]
+        a = slope.double()[None, :, None, None]
+        t1 = torch.where(u >= 0, u, u * a)
+        yw = torch.where(t1 >= 0, t1, torch.expm1(t1))
+        du = dy.double() * torch.where(t1 >= 0, torch.ones_like(t1), yw + 1.0) * torch.where(u >= 0, torch.ones_like(u), a.expand_as(u))
+        del u, t1
+        sb, sg = du.sum(dim=(0, 2, 3)), (du * xh).sum(dim=(0, 2, 3))
+        if dist is not None:
+            dist.all_reduce(sb)
+            dist.all_reduce(sg)
+        dxw = (gamma.double() * inv)[None, :, None, None] * ((du - sb[None, :, None, None] / m) - xh * sg[None, :, None, None] / m)
+        # PReLU's derivative jumps at u = 0 (from the slope to 1): an element whose u is within rounding of 0 may fall on either
+        # side in fp32, and two correct implementations then differ there by |dy| * (1 - slope) * gamma * invstd. Such elements
+        # (a few hundred of 51 million) are left out of the comparisons of dx, and counted.
+        kink = (xh * gamma.double()[None, :, None, None] + beta.double()[None, :, None, None]).abs() < KINK
+        return yw, dxw, kink
 
     err_word = capi.fused_error_check()
     timed_out = None
@@ -583,9 +620,32 @@ def main():
         except ExchangeTimeout as e:
             timed_out = str(e)
     note("no bounded wait ran out in the warm-up and timed steps", err_word == 0 and timed_out is None, error_word=err_word, report=timed_out)
+    waits = None
+    if not single and getattr(exchange, "in_launch", False):
+        # how long the items of one step's two launches waited (for this GPU's statistics and for the other ranks'), per rank
+        step()
+        torch.cuda.synchronize()
+        total_ns, longest_ns = layer.last_wait_ns()
+        layer.check(block=True)
+        t = torch.tensor([float(total_ns), float(longest_ns)], device="cuda")
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        waits = {"per_rank_item_wait_us_summed": [round(float(g[0]) / 1e3, 1) for g in gathered],
+                 "per_rank_longest_wait_us": [round(float(g[1]) / 1e3, 1) for g in gathered]}
     step()
     torch.cuda.synchronize()
     y_run, dx_run, saved_run = y.clone(), dx.clone(), (saved if single else layer.saved).clone()
+    yw, dxw, kink = exact_step()
+    kinks = int(kink.sum().item())
+    wy, wdx = worst(y_run, yw, atol=2e-6), worst(dx_run, dxw, atol=5e-6, skip=kink)
+    if dist is not None:
+        t = torch.tensor([wy, wdx], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wy, wdx = float(t[0].item()), float(t[1].item())
+    note("the timed path against a float64 evaluation of the step with all-reduced sums (1e-5 relative + 2e-6 / 5e-6 absolute: the fp32 "
+         "chain itself is that far from it where du and dx cancel), worst rank", wy <= 1.0 and wdx <= 1.0 and kinks <= 2e-5 * elements_per_gpu(), y=wy, dx=wdx,
+         elements_left_out_at_the_prelu_kink=kinks, kink_halfwidth=KINK)
+    del yw
     y2, dx2 = torch.empty_like(x), torch.empty_like(x)
     if single:
         # (a) another path of this library: statistics kernel, apply kernel, backward statistics kernel, backward apply kernel
@@ -596,8 +656,8 @@ def main():
         capi.bn_train_bwd_apply(dx2, dy, x, gamma, beta, saved2, bsums2, bsums2, float(N_PER_GPU * hw), acts)
         torch.cuda.synchronize()
         note("single launch against the two-kernel form of this library (1e-5 relative + 1e-6 absolute)",
-             max(worst(saved_run, saved2), worst(y_run, y2), worst(dx_run, dx2)) <= 1.0,
-             saved=worst(saved_run, saved2), y=worst(y_run, y2), dx=worst(dx_run, dx2))
+             max(worst(saved_run, saved2), worst(y_run, y2), worst(dx_run, dx2, skip=kink)) <= 1.0,
+             saved=worst(saved_run, saved2), y=worst(y_run, y2), dx=worst(dx_run, dx2, skip=kink))
         # (b) the reference's own arithmetic for this layer: cuDNN's spatial batch norm (the two calls of
         # nnforge/cuda/batch_norm_layer_updater_cuda.cu:89,145), followed by torch's PReLU and ELU, forward and autograd backward
         if torch.backends.cudnn.is_available():
@@ -607,7 +667,7 @@ def main():
             yr.backward(dy)
             torch.cuda.synchronize()
             wy = worst(y_run, yr.detach(), atol=2e-6)
-            wdx = worst(dx_run, xr.grad, atol=5e-6)
+            wdx = worst(dx_run, xr.grad, atol=5e-6, skip=kink)
             note("single launch against cuDNN batch norm + torch PReLU, ELU (1e-5 relative + 2e-6 / 5e-6 absolute: du and dx cancel)",
                  wy <= 1.0 and wdx <= 1.0, y=wy, dx=wdx)
             del xr, u, yr
@@ -617,18 +677,18 @@ def main():
         other.forward(y2, x, gamma, beta)
         other.backward(dx2, dy, x, gamma, beta)
         torch.cuda.synchronize()
-        w = (worst(saved_run, other.saved), worst(y_run, y2), worst(dx_run, dx2))
-        t = torch.tensor([max(w)], device="cuda")
+        w = (worst(saved_run, other.saved), worst(y_run, y2), worst(dx_run, dx2, atol=5e-6, skip=kink), worst(dx2, dxw, atol=5e-6, skip=kink))
+        t = torch.tensor([max(w[:3])], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        note("%s against statistics kernel + NCCL all-reduce + apply kernel on the same shards (1e-5 relative + 1e-6 absolute), worst rank" % exchange_name,
-             float(t.item()) <= 1.0, worst=float(t.item()), this_rank={"saved": w[0], "y": w[1], "dx": w[2]})
+        note("%s against statistics kernel + NCCL all-reduce + apply kernel on the same shards (1e-5 relative + 1e-6 absolute; dx 5e-6), worst rank" % exchange_name,
+             float(t.item()) <= 1.0, worst=float(t.item()), this_rank={"saved": w[0], "y": w[1], "dx": w[2], "dx of the NCCL form against float64": w[3]})
         gathered = [torch.empty_like(saved_run) for _ in range(world)]
         dist.all_gather(gathered, saved_run)
         same = all(bool((g.view(torch.int32) == gathered[0].view(torch.int32)).all().item()) for g in gathered)
         note("saved {mean, invstd} bit-identical on all ranks", same)
         err_word = capi.fused_error_check()
         note("no bounded wait ran out in the checked steps", err_word == 0, error_word=err_word)
-    del y2, dx2
+    del y2, dx2, dxw, kink
     parity = {"ok": all(c["ok"] for c in checks), "checks": checks}
     if dist is not None:
         ok = torch.tensor([1 if parity["ok"] else 0], device="cuda")
@@ -725,7 +785,7 @@ def main():
             "config": make_config(world), "exchange": exchange_name,
             "gelem_per_s": elems * world / (ms_step * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-            "parity_check": parity, "configs": configs,
+            "parity_check": parity, "configs": configs, "waits": waits, "tuning": args.tune,
         }
         result_out.write(json.dumps(line) + "\n")
         result_out.flush()

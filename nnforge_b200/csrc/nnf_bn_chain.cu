@@ -1329,7 +1329,7 @@ namespace nnf
 		// 24 channels behind the statistics items: 86 / 150 us. Shorter distances make every apply item wait for its
 		// channel (16 channels: 94 / 164 us), longer ones push the first read out of L2 before the second.
 		// Knobs: chain_s_kb, chain_a_kb, chain_dist (nnf_set_tuning).
-		bool plan_stream(stream_params& p, int64_t n, int64_t c, int64_t hw, bool backward)
+		bool plan_stream(stream_params& p, int64_t n, int64_t c, int64_t hw, bool backward, bool sharded = false)
 		{
 			if (hw % 4 != 0 || n < 1 || c < 1 || n * hw >= (int64_t(1) << 31) || c > 0x7fffffff / 256)
 				return false;
@@ -1359,7 +1359,9 @@ namespace nnf
 				ea = div_up(div_up(n, 4096), rows) * rows;
 			p.es = (uint32_t)es; p.ea = (uint32_t)ea;
 			p.ss = (uint32_t)div_up(n, es); p.sa = (uint32_t)div_up(n, ea);
-			int64_t dist = t.chain_dist >= 0 ? t.chain_dist : (backward ? 24 : 32);
+			// batch-sharded launches: a channel's constants also wait for the other ranks' sums (an NVLink round trip and whatever
+			// the ranks are apart), so the forward launch keeps a longer distance (two GPUs: 119 us at 48 against 127-130 at 32)
+			int64_t dist = t.chain_dist >= 0 ? t.chain_dist : (backward ? 24 : (sharded ? 48 : 32));
 			if (dist > c) dist = c;
 			p.dist = (uint32_t)dist;
 			p.dist_f = (uint32_t)(dist / 2);
@@ -1570,7 +1572,7 @@ namespace nnf
 				}
 			}
 			stream_params p = {};
-			if (!plan_stream(p, n, c, hw, false))
+			if (!plan_stream(p, n, c, hw, false, PEER))
 				return 1;
 			if (!workspace_ok(workspace, workspace_bytes, stream_workspace_needed(p)))
 				return 2;
@@ -1621,7 +1623,7 @@ namespace nnf
 				}
 			}
 			stream_params p = {};
-			if (!plan_stream(p, n, c, hw, true))
+			if (!plan_stream(p, n, c, hw, true, PEER))
 				return 1;
 			if (!workspace_ok(workspace, workspace_bytes, stream_workspace_needed(p)))
 				return 2;

@@ -36,3 +36,14 @@ def assert_close(got, want, what="", rtol=RTOL, atol=ATOL):
         pos = tuple(np.argwhere(bad)[0])
         raise AssertionError("%s: %d of %d outside tolerance; first at %s: got %r want %r"
                              % (what, int(bad.sum()), got.size, pos, got[pos], want[pos]))
+
+
+def assert_close_off_kink(got, want, u, what="", rtol=RTOL, atol=ATOL, halfwidth=1e-5, max_fraction=1e-4):
+    """assert_close for the gradient behind a rectifier (ReLU, PReLU) whose input u was itself computed in fp32: the
+    derivative jumps at u = 0, so an element whose u is within rounding of 0 may take either side, and two correct
+    implementations differ there by a finite amount. Those elements (|u| < halfwidth) are left out - and must be few."""
+    near = np.abs(np.asarray(u, dtype=np.float64)) < halfwidth
+    assert near.mean() <= max_fraction, "%s: %d elements at the kink" % (what, int(near.sum()))
+    got = np.where(near, 0.0, np.asarray(got, dtype=np.float64))
+    want = np.where(near, 0.0, np.asarray(want, dtype=np.float64))
+    assert_close(got, want, what, rtol, atol)
