@@ -700,6 +700,69 @@ def main():
     # its y and dx back, all inside the timed region. The copies of one step overlap the kernels and the opposite
     # copies of its neighbours (three streams, two sets of device buffers): host->device of x, forward, device->host
     # of y while dy comes in, backward, device->host of dx while the next step's x comes in.
+    # The calls of this leg are those of an nnForge scheduler: the schema of the benchmarked chain is planned, the C++ factory
+    # makes the fused head (and the two no-op follower objects), and every step enqueues the head's forward and
+    # backward_data_and_weights actions with the buffers its size queries asked for. With several GPUs each rank's head owns
+    # a mailbox in symmetric memory of its own (published with the peers' mapped addresses before the objects are created).
+    from nnforge_b200 import host as nnf_host
+    objects = None
+    peers = None
+    if not single and in_launch and getattr(exchange, "in_launch", False):
+        from nnforge_b200.sharded import InLaunchExchange
+        object_mailboxes = InLaunchExchange(capi, C, torch.device("cuda", local))
+        peers = nnf_host.PeerDirectory()
+        for r, address in enumerate(object_mailboxes.ptrs):
+            peers.publish("bn", r, address)
+    if single or peers is not None:
+        net = nnf_host.Net("bn BatchNorm x eps=%r\nprelu PReLU bn\nelu ELU prelu\n" % EPS, {"x": (C, W, H)}, training=True,
+                           device_pos=rank, device_count=world, peers=peers)
+        head = net.objects[0]
+        assert (head.role, head.kind, head.data, head.outputs) == ("head", "bn_train_act", ["bn", "prelu"], ["elu"])
+        objects = {
+            "net": net, "head": head, "followers": net.objects[1:],
+            "data": [gamma, beta, torch.zeros(C, device="cuda"), torch.ones(C, device="cuda"), slope],
+            "gradient": [torch.zeros(C, device="cuda") for _ in range(5)],
+            "saved": torch.empty(head.get_temporary_fixed_buffer_size() // 4, device="cuda"),
+            "ws_fwd": torch.empty(head.get_temporary_working_fixed_buffer_size(nnf_host.FORWARD), dtype=torch.uint8, device="cuda"),
+            "ws_bwd": torch.empty(head.get_temporary_working_fixed_buffer_size(nnf_host.BACKWARD_DATA_AND_WEIGHTS), dtype=torch.uint8, device="cuda"),
+        }
+
+    def objects_forward(st):
+        o = objects
+        o["head"].enqueue_forward_propagation([st["y"]], o["data"], [st["x"]], N_PER_GPU, temporary_working_fixed_buffer=o["ws_fwd"], temporary_fixed_buffer=o["saved"])
+        for f in o["followers"]:   # a per-layer scheduler enqueues them too; they launch nothing
+            f.enqueue_forward_propagation([st["y"]], [], [st["y"]], N_PER_GPU)
+
+    def objects_backward(st):
+        o = objects
+        for f in reversed(o["followers"]):
+            f.enqueue_backward_data_propagation(0, st["dy"], st["dy"], [], [None], None, N_PER_GPU)
+        o["head"].enqueue_backward_data_and_weights_propagation([st["dx"]], st["dy"], o["gradient"], o["data"], [st["x"]], None, N_PER_GPU,
+                                                                temporary_working_fixed_buffer=o["ws_bwd"], temporary_fixed_buffer=o["saved"])
+
+    if objects is not None:
+        # the objects' step gives what the entry points gave (checked once, outside any timed region)
+        y_obj, dx_obj = torch.empty_like(x), torch.empty_like(x)
+        st0 = {"x": x, "dy": dy, "y": y_obj, "dx": dx_obj}
+        objects_forward(st0)
+        objects_backward(st0)
+        report_words = torch.zeros(capi.REPORT_WORDS, dtype=torch.int64).pin_memory()
+        capi.read_report(report_words, objects["ws_bwd"])
+        step()
+        torch.cuda.synchronize()
+        report = capi.parse_report(report_words)
+        # the same kernels on the same inputs: the same bits (several GPUs: unless a timed-out exchange made the host layer fall back)
+        differing = int((y_obj != y).sum().item()) + int((dx_obj != dx).sum().item())
+        note_ok = differing == 0 and report["status"] == 0
+        parity["checks"].append({"check": "layer objects (planned schema -> fused head) reproduce the entry points' y and dx bit for bit", "ok": note_ok,
+                                 "differing_elements": differing, "launch_status": report["status"]})
+        if dist is not None:
+            flag = torch.tensor([1 if note_ok else 0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            note_ok = bool(flag.item())
+        parity["ok"] = parity["ok"] and note_ok
+        del y_obj, dx_obj
+
     xh, dyh = x.cpu().pin_memory(), dy.cpu().pin_memory()
     yh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
     s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
@@ -720,15 +783,14 @@ def main():
         with torch.cuda.stream(s_comp):
             s_comp.wait_event(st["ev_x"])
             s_comp.wait_event(st["ev_out"])       # ... and its y and dx have been copied out
-            if single:
-                capi.bn_train_fwd(st["y"], saved, sums, st["x"], gamma, beta, EPS, acts, workspace=ws)
+            if objects is not None:
+                objects_forward(st)
             else:
                 layer.forward(st["y"], st["x"], gamma, beta)
             st["ev_y"].record(s_comp)
             s_comp.wait_event(st["ev_dy"])
-            if single:
-                capi.bn_train_bwd(st["dx"], bsums, st["dy"], st["x"], gamma, beta, saved, acts, grad_gamma=grads[0], grad_beta=grads[1],
-                                  grad_slope=grads[2], workspace=ws)
+            if objects is not None:
+                objects_backward(st)
             else:
                 layer.backward(st["dx"], st["dy"], st["x"], gamma, beta, grads=grad_map)
             st["ev_dx"].record(s_comp)
@@ -763,7 +825,9 @@ def main():
     tensor_bytes = elems * 4
     e2e = {"value": bytes_step_all / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": 2 * tensor_bytes, "d2h_bytes_per_step": 2 * tensor_bytes, "steps": args.e2e_steps,
-           "overlap": "copies of neighbouring steps overlap the kernels (3 streams, 2 buffer sets)"}
+           "overlap": "copies of neighbouring steps overlap the kernels (3 streams, 2 buffer sets)",
+           "api": "layer_updater objects made by the C++ factory from the planned schema (fused head + no-op followers)" if objects is not None
+                  else "ShardedBatchNormAct over the C ABI"}
 
     # the other configurations of the benchmark (one GPU each), outside the headline's timed region
     configs = None

@@ -18,7 +18,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libnnf_b200.so")
 HOST_LIB = os.path.join(HERE, "libnnf_b200_host.so")
 HOST_SRC = os.path.join(CSRC, "host", "nnf_layers.cpp")
-HOST_SOURCES = [HOST_SRC, os.path.join(CSRC, "host", "nnf_fusion.cpp")]
+HOST_SOURCES = [HOST_SRC, os.path.join(CSRC, "host", "nnf_fusion.cpp"), os.path.join(CSRC, "host", "nnf_fused_layers.cpp")]
 SOURCES = ["nnf_api.cu", "nnf_elementwise.cu", "nnf_softmax.cu", "nnf_loss.cu", "nnf_maxpool.cu", "nnf_avgpool.cu", "nnf_optimizer.cu", "nnf_bn_train.cu", "nnf_bn_chain.cu", "nnf_peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -67,12 +67,14 @@ def build(verbose=False):
 def build_host():
     """C++ host-side layer objects (nnForge-shaped testers / updaters over the C ABI)."""
     deps = HOST_SOURCES + [os.path.join(CSRC, "host", "nnf_layers.h"), os.path.join(CSRC, "host", "nnf_fusion.h"),
-            os.path.join(os.path.dirname(HERE), "include", "nnf_b200.h"), LIB]
+            os.path.join(CSRC, "host", "nnf_layers_detail.h"), os.path.join(os.path.dirname(HERE), "include", "nnf_b200.h"), LIB]
     if os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(os.path.getmtime(d) for d in deps):
         return HOST_LIB
-    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include") if os.path.sep in _nvcc() else "/usr/local/cuda/include"
-    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I", cuda_inc] + HOST_SOURCES + ["-o", HOST_LIB,
-                           "-L", HERE, "-lnnf_b200", "-Wl,-rpath,$ORIGIN"])
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc())) if os.path.sep in _nvcc() else "/usr/local/cuda"
+    # the CUDA runtime is linked statically (weights upload, mailbox allocation): no libcudart.so is needed at run time
+    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I", os.path.join(cuda_home, "include")] + HOST_SOURCES
+                          + ["-o", HOST_LIB, "-L", HERE, "-lnnf_b200", "-Wl,-rpath,$ORIGIN",
+                             "-L", os.path.join(cuda_home, "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-Wl,--exclude-libs,ALL"])
     return HOST_LIB
 
 

@@ -224,33 +224,31 @@ namespace nnf_b200
 	}
 }
 
-// ---- flat driver for tests -------------------------------------------------------------------------
-// spec: one layer per line, "name type inputs [needed] [key=value ...]" with inputs a comma-separated list of
-// layer names or "-" for none; keys: alpha, win (e.g. win=3x3), fm (feature-map subsampling), tiling.
-// result: one group per line, "kind entry_point members=a,b,c residual=name elided=a,b".
-using namespace nnf_b200;
-
-namespace
+namespace nnf_b200
 {
-	std::string g_fusion_error;
-
-	std::vector<std::string> split(const std::string& s, char sep)
+	namespace
 	{
-		std::vector<std::string> out;
-		std::stringstream ss(s);
-		std::string item;
-		while (std::getline(ss, item, sep))
-			if (!item.empty())
-				out.push_back(item);
-		return out;
+		std::vector<std::string> split(const std::string& s, char sep)
+		{
+			std::vector<std::string> out;
+			std::stringstream ss(s);
+			std::string item;
+			while (std::getline(ss, item, sep))
+				if (!item.empty())
+					out.push_back(item);
+			return out;
+		}
+
+		std::vector<unsigned int> sizes(const std::string& val)
+		{
+			std::vector<unsigned int> r;
+			for (const std::string& v : split(val, 'x'))
+				r.push_back((unsigned int)std::stoul(v));
+			return r;
+		}
 	}
-}
 
-extern "C" __attribute__((visibility("default"))) const char * nnfh_fusion_last_error() { return g_fusion_error.c_str(); }
-
-extern "C" __attribute__((visibility("default"))) int nnfh_plan_fusion(const char * spec, int training, char * out, size_t out_size)
-{
-	try
+	std::vector<schema_node> parse_schema(const std::string& spec)
 	{
 		std::vector<schema_node> nodes;
 		for (const std::string& line : split(spec, '\n'))
@@ -261,21 +259,30 @@ extern "C" __attribute__((visibility("default"))) int nnfh_plan_fusion(const cha
 			schema_node n;
 			n.name = tok[0];
 			n.params.type_name = tok[1];
+			n.params.instance_name = tok[0];
 			if (tok[2] != "-")
 				n.inputs = split(tok[2], ',');
 			for (size_t k = 3; k < tok.size(); ++k)
 			{
 				if (tok[k] == "needed") { n.output_needed = true; continue; }
+				if (tok[k] == "min") { n.params.is_min = true; continue; }
 				const size_t eq = tok[k].find('=');
 				if (eq == std::string::npos)
 					throw neural_network_exception("Bad schema token: " + tok[k]);
 				const std::string key = tok[k].substr(0, eq), val = tok[k].substr(eq + 1);
 				if (key == "alpha") n.params.alpha = std::stof(val);
-				else if (key == "win")
+				else if (key == "slope") n.params.negative_slope = std::stof(val);
+				else if (key == "scale") n.params.scale = std::stof(val);
+				else if (key == "steepness") n.params.steepness = std::stof(val);
+				else if (key == "eps") n.params.epsilon = std::stof(val);
+				else if (key == "topn") n.params.top_n = (unsigned int)std::stoul(val);
+				else if (key == "win") n.params.subsampling_sizes = sizes(val);
+				else if (key == "stride") n.params.strides = sizes(val);
+				else if (key == "roundup")
 				{
-					const std::vector<std::string> d = split(val, 'x');
-					for (const std::string& v : d)
-						n.params.subsampling_sizes.push_back((unsigned int)std::stoul(v));
+					n.params.round_ups.clear();
+					for (unsigned int v : sizes(val))
+						n.params.round_ups.push_back(v != 0);
 				}
 				else if (key == "fm") n.params.feature_map_subsampling_size = (unsigned int)std::stoul(val);
 				else if (key == "tiling") n.params.tiling = val != "0";
@@ -283,6 +290,27 @@ extern "C" __attribute__((visibility("default"))) int nnfh_plan_fusion(const cha
 			}
 			nodes.push_back(n);
 		}
+		return nodes;
+	}
+}
+
+// ---- flat driver for tests -------------------------------------------------------------------------
+// spec: the text form of parse_schema.
+// result: one group per line, "kind entry_point members=a,b,c residual=name elided=a,b".
+using namespace nnf_b200;
+
+namespace
+{
+	std::string g_fusion_error;
+}
+
+extern "C" __attribute__((visibility("default"))) const char * nnfh_fusion_last_error() { return g_fusion_error.c_str(); }
+
+extern "C" __attribute__((visibility("default"))) int nnfh_plan_fusion(const char * spec, int training, char * out, size_t out_size)
+{
+	try
+	{
+		const std::vector<schema_node> nodes = parse_schema(spec);
 		static const char * kKinds[] = {"single", "bn_act", "bn_add_relu_maxpool", "bn_add_relu_avgpool", "bn_train_act", "softmax_nll"};
 		std::stringstream res;
 		for (const fused_group& grp : plan_fusion(nodes, training != 0))

@@ -52,4 +52,13 @@ namespace nnf_b200
 
 	// nodes must be in execution (topological) order. Every node ends up in exactly one group.
 	std::vector<fused_group> plan_fusion(const std::vector<schema_node>& nodes, bool training);
+
+	// The objects that run the plan are made by layer_factory_b200::create_testers / create_updaters (nnf_layers.h).
+
+	// A schema in text form, one layer per line: "name type inputs [needed] [key=value ...]" with inputs a
+	// comma-separated list of layer names or "-" for none. Keys: alpha (Add, AverageSubsampling), slope (ReLU),
+	// scale and steepness (TanH; scale also NegativeLogLikelihood), eps (BatchNorm), topn (Accuracy),
+	// win / stride / roundup (subsampling, e.g. win=3x3 stride=2x2 roundup=0x0), min, fm (feature-map
+	// subsampling size), tiling. Stands in for the protobuf schema of the reference in tests and examples.
+	std::vector<schema_node> parse_schema(const std::string& spec);
 }

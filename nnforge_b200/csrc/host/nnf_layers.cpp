@@ -1,66 +1,14 @@
 // Implementation of the host-side layer objects (see nnf_layers.h) on top of the C ABI, plus a small
 // flat driver interface (nnfh_*) through which the Python tests create these objects by type name
 // and call their members with raw device pointers.
-#include "nnf_layers.h"
-
-#include "../../../include/nnf_b200.h"
-
-#include <cstring>
+#include "nnf_layers_detail.h"
 
 namespace nnf_b200
 {
+	using namespace detail;
+
 	namespace
 	{
-		void check(int status)
-		{
-			if (status != NNF_OK)
-				throw neural_network_exception(std::string("nnf_b200: ") + nnf_last_error_string());
-		}
-
-		const float * f(const device_buffer::const_ptr& b) { return b ? static_cast<const float *>(*b) : nullptr; }
-		float * f(const device_buffer::ptr& b) { return b ? static_cast<float *>(*b) : nullptr; }
-
-		nnf_act make_act(const layer& l, const float * slope)
-		{
-			nnf_act a;
-			a.kind = NNF_ACT_NONE; a.p0 = 0.0F; a.p1 = 0.0F; a.slope = slope;
-			if (l.type_name == "ReLU") { a.kind = NNF_ACT_RELU; a.p0 = l.negative_slope; }
-			else if (l.type_name == "PReLU") a.kind = NNF_ACT_PRELU;
-			else if (l.type_name == "ELU") a.kind = NNF_ACT_ELU;
-			else if (l.type_name == "TanH") { a.kind = NNF_ACT_TANH; a.p0 = l.scale; a.p1 = l.steepness; }
-			else if (l.type_name == "Sigmoid") a.kind = NNF_ACT_SIGMOID;
-			return a;
-		}
-
-		// ReLU/PReLU read their input in backward, the other three their output (the plain backend's dependencies)
-		bool backward_uses_input(const layer& l) { return l.type_name == "ReLU" || l.type_name == "PReLU"; }
-
-		nnf_pool make_pool(const layer& l, const layer_configuration_specific& in)
-		{
-			if (l.tiling)
-				throw neural_network_exception("max subsampling with tiling is not supported"); // the reference updater refuses it too
-			if (l.feature_map_subsampling_size != 1 || l.entry_subsampling_size != 1)
-				throw neural_network_exception("max subsampling over feature maps or entries is not supported");
-			if (l.subsampling_sizes.empty() || l.subsampling_sizes.size() > 2 || l.subsampling_sizes.size() != in.dimension_sizes.size())
-				throw neural_network_exception("max subsampling supports 1 or 2 spatial dimensions matching the input");
-			nnf_pool p;
-			std::memset(&p, 0, sizeof(p));
-			p.win_w = (int)l.subsampling_sizes[0];
-			p.stride_w = l.strides.empty() ? p.win_w : (int)l.strides[0];
-			p.round_up_w = (!l.round_ups.empty() && l.round_ups[0]) ? 1 : 0;
-			p.win_h = p.stride_h = 1;
-			if (l.subsampling_sizes.size() == 2)
-			{
-				p.win_h = (int)l.subsampling_sizes[1];
-				p.stride_h = l.strides.size() > 1 ? (int)l.strides[1] : p.win_h;
-				p.round_up_h = (l.round_ups.size() > 1 && l.round_ups[1]) ? 1 : 0;
-			}
-			p.is_min = l.is_min ? 1 : 0;
-			return p;
-		}
-
-		unsigned int dim(const layer_configuration_specific& c, size_t i) { return i < c.dimension_sizes.size() ? c.dimension_sizes[i] : 1; }
-
 		// ---- testers ---------------------------------------------------------------------------
 		class batch_norm_layer_tester_b200 : public layer_tester_b200
 		{
@@ -398,22 +346,41 @@ namespace nnf_b200
 			nnf_pool pool;
 		};
 
-		// Training-mode batch norm. temporary_fixed_buffer = {mean, inverse std-dev} (2*C floats, as stock);
+		// Training-mode batch norm, alone or as the head of a fused BatchNorm -> activations group (the followers'
+		// parameters are then in `followers`, their weight chunks behind the batch norm's four in data / gradient).
+		// temporary_fixed_buffer = {mean, inverse std-dev} (2*C floats, as stock);
 		// temporary_working_fixed_buffer = the kernels' workspace followed by 2*C (forward) or 3*C (backward) floats of sums.
+		// With more than one device sharing the batch (cuda_config->device_count > 1) the statistics are those of the
+		// whole batch: the object owns a mailbox (get_persistent_working_data), publishes its address in
+		// cuda_config->peers under the layer's instance name and runs the batch-sharded single-launch entry points;
+		// every device must enqueue the same action with the same entry_count.
 		class batch_norm_layer_updater_b200 : public layer_updater_b200
 		{
 		public:
+			explicit batch_norm_layer_updater_b200(const std::vector<layer>& followers = std::vector<layer>()) : followers(followers) {}
+
 			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
 				const std::vector<device_buffer::const_ptr>& data, const std::vector<device_buffer::const_ptr>&,
 				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
 				device_buffer::ptr temporary_working_fixed_buffer, device_buffer::ptr, device_buffer::ptr temporary_fixed_buffer, device_buffer::ptr,
 				unsigned int entry_count) override
 			{
+				if (data.size() != chunk_count())
+					throw neural_network_exception("BatchNorm expects " + std::to_string(chunk_count()) + " weight chunks: gamma, beta, mean, inverse sigma and one slope chunk per fused PReLU");
 				const unsigned int c = output_configuration_specific.feature_map_count;
 				char * ws = working(temporary_working_fixed_buffer, 2);
 				float * sums = reinterpret_cast<float *>(ws + workspace_bytes());
-				check(nnf_bn_train_fwd(stream_id, f(output_buffer), f(temporary_fixed_buffer), sums, f(input_buffers[0]), f(data[0]), f(data[1]),
-					layer_schema->epsilon, nullptr, 0, entry_count, c, output_elem_count_per_feature_map, ws, workspace_bytes()));
+				const std::vector<nnf_act> acts = make_acts(data);
+				if (sharded())
+				{
+					const std::vector<void *> boxes = mailboxes();
+					check(nnf_bn_train_fwd_sharded(stream_id, f(output_buffer), f(temporary_fixed_buffer), sums, f(input_buffers[0]), f(data[0]), f(data[1]),
+						layer_schema->epsilon, acts.data(), (int)acts.size(), entry_count, c, output_elem_count_per_feature_map, count_total(entry_count),
+						ws, workspace_bytes(), boxes.data(), cuda_config->device_pos, cuda_config->device_count, ++seq));
+				}
+				else
+					check(nnf_bn_train_fwd(stream_id, f(output_buffer), f(temporary_fixed_buffer), sums, f(input_buffers[0]), f(data[0]), f(data[1]),
+						layer_schema->epsilon, acts.empty() ? nullptr : acts.data(), (int)acts.size(), entry_count, c, output_elem_count_per_feature_map, ws, workspace_bytes()));
 			}
 			void enqueue_backward_data_and_weights_propagation(cudaStream_t stream_id, const std::vector<device_buffer::ptr> input_errors_buffers,
 				device_buffer::const_ptr output_errors_buffer, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::ptr>& gradient,
@@ -422,16 +389,37 @@ namespace nnf_b200
 				device_buffer::ptr temporary_working_fixed_buffer, device_buffer::ptr, device_buffer::const_ptr temporary_fixed_buffer, device_buffer::const_ptr,
 				bool add_update_to_destination, unsigned int entry_count) override
 			{
-				if (gradient.size() != 4 || data.size() != 4)
-					throw neural_network_exception("BatchNorm expects 4 weight chunks and 4 gradient chunks");
+				if (gradient.size() != chunk_count() || data.size() != chunk_count())
+					throw neural_network_exception("BatchNorm expects " + std::to_string(chunk_count()) + " weight chunks and as many gradient chunks");
 				const unsigned int c = output_configuration_specific.feature_map_count;
 				char * ws = working(temporary_working_fixed_buffer, 3);
 				float * bsums = reinterpret_cast<float *>(ws + workspace_bytes());
+				const std::vector<nnf_act> acts = make_acts(data);
+				float * grad_slope = nullptr;
+				for (size_t k = 0, chunk = 4; k < followers.size(); ++k)
+					if (followers[k].type_name == "PReLU")
+						grad_slope = f(gradient[chunk++]);
 				// gradient[0..3] = gamma, beta, mean, inverse sigma; running statistics are trained through the
 				// pseudo-gradients of batch_norm_layer_updater_cuda.cu:167-182
-				check(nnf_bn_train_bwd(stream_id, f(input_errors_buffers[0]), bsums, f(output_errors_buffer), f(input_neurons_buffers[0]), f(data[0]), f(data[1]),
-					f(temporary_fixed_buffer), nullptr, 0, f(gradient[0]), f(gradient[1]), f(gradient[2]), f(gradient[3]), nullptr, f(data[2]), f(data[3]),
-					(float)entry_count, entry_count, c, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0, ws, workspace_bytes()));
+				if (sharded())
+				{
+					if (add_update_to_destination)
+						throw neural_network_exception("BatchNorm: add_update_to_destination is not available when the batch is shared by several devices");
+					const std::vector<void *> boxes = mailboxes();
+					check(nnf_bn_train_bwd_sharded(stream_id, f(input_errors_buffers[0]), bsums, f(output_errors_buffer), f(input_neurons_buffers[0]), f(data[0]), f(data[1]),
+						f(temporary_fixed_buffer), acts.data(), (int)acts.size(), f(gradient[0]), f(gradient[1]), f(gradient[2]), f(gradient[3]), grad_slope,
+						f(data[2]), f(data[3]), (float)entry_count, entry_count, c, output_elem_count_per_feature_map, count_total(entry_count),
+						ws, workspace_bytes(), boxes.data(), cuda_config->device_pos, cuda_config->device_count, ++seq));
+				}
+				else
+					check(nnf_bn_train_bwd(stream_id, f(input_errors_buffers[0]), bsums, f(output_errors_buffer), f(input_neurons_buffers[0]), f(data[0]), f(data[1]),
+						f(temporary_fixed_buffer), acts.empty() ? nullptr : acts.data(), (int)acts.size(), f(gradient[0]), f(gradient[1]), f(gradient[2]), f(gradient[3]),
+						grad_slope, f(data[2]), f(data[3]), (float)entry_count, entry_count, c, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0,
+						ws, workspace_bytes()));
+			}
+			std::vector<device_buffer::const_ptr> get_persistent_working_data() const override
+			{
+				return mailbox ? std::vector<device_buffer::const_ptr>(1, mailbox) : std::vector<device_buffer::const_ptr>();
 			}
 			std::pair<size_t, bool> get_temporary_working_fixed_buffer_size(const layer_action& action) const override
 			{
@@ -444,9 +432,56 @@ namespace nnf_b200
 			}
 			size_t get_temporary_fixed_buffer_size() const override { return size_t(output_configuration_specific.feature_map_count) * 2 * sizeof(float); }
 			int get_input_index_layer_can_write(const layer_action& action) const override { return action.get_action_type() == layer_action::backward_data_and_weights ? 0 : -1; }
+			// backward recomputes the chain from x and the saved statistics: the group's output is not read
 			bool is_backward_data_and_weights_dependent_on_input_buffer(unsigned int) const override { return true; }
 			bool is_backward_data_and_weights_dependent_on_output_buffer() const override { return false; }
+			bool is_backward_data_and_weights_dependent_on_temporary_fixed_buffer() const override { return true; }
+			bool is_backward_data_and_weights_dependent_on_temporary_per_entry_buffer() const override { return false; }
+		protected:
+			void updater_configured() override
+			{
+				if (followers.size() > 2)
+					throw neural_network_exception("BatchNorm can carry at most two fused activation layers");
+				if (!sharded())
+					return;
+				if (!cuda_config->peers)
+					throw neural_network_exception("BatchNorm: several devices share the batch but the running configuration has no peer directory");
+				if (layer_schema->instance_name.empty())
+					throw neural_network_exception("BatchNorm: several devices share the batch: the layer needs an instance name to publish its mailbox under");
+				const size_t bytes = nnf_bn_train_mailbox_bytes(output_configuration_specific.feature_map_count);
+				if (void * given = cuda_config->peers->find(layer_schema->instance_name, cuda_config->device_pos))
+				{
+					// one process per GPU: the process made a mailbox the others can map, and cleared it
+					mailbox.reset(new device_buffer(given, bytes));
+					return;
+				}
+				mailbox.reset(new device_buffer(bytes));
+				if (cudaMemset(static_cast<void *>(*mailbox), 0, bytes) != cudaSuccess)
+					throw neural_network_exception("BatchNorm: clearing the mailbox failed");
+				cuda_config->peers->publish(layer_schema->instance_name, cuda_config->device_pos, static_cast<void *>(*mailbox));
+			}
 		private:
+			bool sharded() const { return cuda_config && cuda_config->device_count > 1; }
+			size_t chunk_count() const
+			{
+				size_t n = 4;
+				for (const layer& l : followers)
+					n += l.type_name == "PReLU";
+				return n;
+			}
+			std::vector<nnf_act> make_acts(const std::vector<device_buffer::const_ptr>& data) const
+			{
+				std::vector<nnf_act> acts;
+				size_t chunk = 4;
+				for (const layer& l : followers)
+					acts.push_back(make_act(l, l.type_name == "PReLU" ? f(data[chunk++]) : nullptr));
+				return acts;
+			}
+			std::vector<void *> mailboxes() const { return cuda_config->peers->lookup(layer_schema->instance_name, cuda_config->device_count); }
+			double count_total(unsigned int entry_count) const
+			{
+				return (double)entry_count * (double)cuda_config->device_count * (double)output_elem_count_per_feature_map;
+			}
 			size_t workspace_bytes() const { return nnf_bn_train_workspace_bytes(1, output_configuration_specific.feature_map_count, output_elem_count_per_feature_map); }
 			char * working(const device_buffer::ptr& b, int sums) const
 			{
@@ -455,14 +490,124 @@ namespace nnf_b200
 					throw neural_network_exception("BatchNorm: temporary_working_fixed_buffer is missing or smaller than get_temporary_working_fixed_buffer_size()");
 				return static_cast<char *>(static_cast<void *>(*b));
 			}
+			std::vector<layer> followers;
+			device_buffer::ptr mailbox;
+			uint32_t seq = 0;
 		};
-
-		bool is_activation(const std::string& t) { return t == "ReLU" || t == "PReLU" || t == "ELU" || t == "TanH" || t == "Sigmoid"; }
 	}
 
-	void layer_tester_b200::configure(const std::vector<layer_configuration_specific>& in, const layer_configuration_specific& out, layer::const_ptr schema)
+	namespace detail
+	{
+		layer_updater_b200::ptr make_batch_norm_updater(const std::vector<layer>& followers)
+		{
+			return layer_updater_b200::ptr(new batch_norm_layer_updater_b200(followers));
+		}
+	}
+
+	// ---- plumbing types ---------------------------------------------------------------------------
+	namespace
+	{
+		void cuda_check(cudaError_t e, const char * what)
+		{
+			if (e != cudaSuccess)
+				throw neural_network_exception(std::string(what) + ": " + cudaGetErrorString(e));
+		}
+	}
+
+	device_buffer::device_buffer(size_t bytes) : p(nullptr), bytes(bytes), owned(true)
+	{
+		cuda_check(cudaMalloc(&p, bytes > 0 ? bytes : 1), "cudaMalloc");
+	}
+
+	device_buffer::~device_buffer()
+	{
+		if (owned && p)
+			cudaFree(p);
+	}
+
+	void peer_directory::publish(const std::string& key, int device_pos, void * address)
+	{
+		std::lock_guard<std::mutex> lock(m);
+		entries[key][device_pos] = address;
+	}
+
+	void * peer_directory::find(const std::string& key, int device_pos) const
+	{
+		std::lock_guard<std::mutex> lock(m);
+		auto it = entries.find(key);
+		if (it == entries.end() || !it->second.count(device_pos))
+			return nullptr;
+		return it->second.at(device_pos);
+	}
+
+	std::vector<void *> peer_directory::lookup(const std::string& key, int device_count) const
+	{
+		std::lock_guard<std::mutex> lock(m);
+		std::vector<void *> res;
+		auto it = entries.find(key);
+		for (int pos = 0; pos < device_count; ++pos)
+		{
+			if (it == entries.end() || !it->second.count(pos))
+				throw neural_network_exception("peer_directory: no address published for " + key + " by device position " + std::to_string(pos));
+			res.push_back(it->second.at(pos));
+		}
+		return res;
+	}
+
+	running_configuration_b200::running_configuration_b200(int device_id, int device_pos, int device_count, peer_directory::ptr peers)
+		: device_id(device_id), device_pos(device_pos), device_count(device_count), peers(peers)
+	{
+		if (device_count < 1 || device_pos < 0 || device_pos >= device_count)
+			throw neural_network_exception("running_configuration_b200: device position outside the device count");
+		// without a device (build checks, host-logic tests) the library answers with its built-in figures
+		int previous = 0;
+		const bool have_device = cudaGetDevice(&previous) == cudaSuccess;
+		if (have_device)
+			cuda_check(cudaSetDevice(device_id), "cudaSetDevice");
+		else
+			cudaGetLastError();
+		nnf_running_configuration rc;
+		const int status = nnf_get_running_configuration(&rc);
+		if (have_device)
+			cudaSetDevice(previous);
+		check(status);
+		compute_capability_major = rc.compute_capability_major;
+		compute_capability_minor = rc.compute_capability_minor;
+		multiprocessor_count = rc.multiprocessor_count;
+		max_threads_per_multiprocessor = rc.max_threads_per_multiprocessor;
+		smem_per_block = (size_t)rc.max_shared_memory_per_block_optin;
+		smem_per_multiprocessor = (size_t)rc.max_shared_memory_per_multiprocessor;
+		l2_cache_size = rc.l2_cache_size;
+		max_registers_per_multiprocessor = rc.max_registers_per_multiprocessor;
+	}
+
+	running_configuration_b200::const_ptr running_configuration_b200::get_current()
+	{
+		static std::mutex m;
+		static std::map<int, const_ptr> cache;
+		int device = 0;
+		if (cudaGetDevice(&device) != cudaSuccess)
+		{
+			cudaGetLastError();
+			device = 0;
+		}
+		std::lock_guard<std::mutex> lock(m);
+		auto it = cache.find(device);
+		if (it == cache.end())
+			it = cache.insert(std::make_pair(device, const_ptr(new running_configuration_b200(device)))).first;
+		return it->second;
+	}
+
+	void running_configuration_b200::set_device() const
+	{
+		cuda_check(cudaSetDevice(device_id), "cudaSetDevice");
+	}
+
+	void layer_tester_b200::configure(const std::vector<layer_configuration_specific>& in, const layer_configuration_specific& out, layer::const_ptr schema,
+		running_configuration_b200::const_ptr config)
 	{
 		layer_schema = schema;
+		cuda_config = config;
 		input_configuration_specific_list = in;
 		output_configuration_specific = out;
 		output_elem_count_per_entry = out.get_neuron_count();
@@ -471,15 +616,92 @@ namespace nnf_b200
 	}
 
 	void layer_updater_b200::configure(const std::vector<layer_configuration_specific>& in, const layer_configuration_specific& out, layer::const_ptr schema,
-		const std::set<layer_action>& acts)
+		running_configuration_b200::const_ptr config, const std::set<layer_action>& acts)
 	{
 		layer_schema = schema;
+		cuda_config = config;
 		input_configuration_specific_list = in;
 		output_configuration_specific = out;
 		output_elem_count_per_entry = out.get_neuron_count();
 		output_elem_count_per_feature_map = out.get_neuron_count_per_feature_map();
 		actions = acts;
 		updater_configured();
+	}
+
+	void layer_tester_b200::enqueue_forward_propagation(cudaStream_t stream_id, const std::vector<device_buffer::ptr>& output_buffers,
+		const std::vector<device_buffer::const_ptr>& schema_data, const std::vector<device_buffer::const_ptr>& data,
+		const std::vector<device_buffer::const_ptr>& data_custom, const std::vector<device_buffer::const_ptr>& input_buffers,
+		const std::vector<device_buffer::const_ptr>& persistent_working_data, device_buffer::ptr temporary_working_fixed_buffer,
+		device_buffer::ptr temporary_working_per_entry_buffer, unsigned int entry_count)
+	{
+		if (output_buffers.size() != 1)
+			throw neural_network_exception("layer " + layer_schema->type_name + " writes one output, " + std::to_string(output_buffers.size()) + " output buffers given");
+		enqueue_forward_propagation(stream_id, output_buffers[0], schema_data, data, data_custom, input_buffers, persistent_working_data,
+			temporary_working_fixed_buffer, temporary_working_per_entry_buffer, entry_count);
+	}
+
+	void layer_updater_b200::enqueue_forward_propagation(cudaStream_t stream_id, const std::vector<device_buffer::ptr>& output_buffers,
+		const std::vector<device_buffer::const_ptr>& schema_data, const std::vector<device_buffer::const_ptr>& data,
+		const std::vector<device_buffer::const_ptr>& data_custom, const std::vector<device_buffer::const_ptr>& input_buffers,
+		const std::vector<device_buffer::const_ptr>& persistent_working_data, device_buffer::ptr temporary_working_fixed_buffer,
+		device_buffer::ptr temporary_working_per_entry_buffer, device_buffer::ptr temporary_fixed_buffer, device_buffer::ptr temporary_per_entry_buffer,
+		unsigned int entry_count)
+	{
+		if (output_buffers.size() != 1)
+			throw neural_network_exception("layer " + layer_schema->type_name + " writes one output, " + std::to_string(output_buffers.size()) + " output buffers given");
+		enqueue_forward_propagation(stream_id, output_buffers[0], schema_data, data, data_custom, input_buffers, persistent_working_data,
+			temporary_working_fixed_buffer, temporary_working_per_entry_buffer, temporary_fixed_buffer, temporary_per_entry_buffer, entry_count);
+	}
+
+	namespace
+	{
+		template<class T, class P>
+		std::vector<P> upload(const std::vector<std::vector<T>>& host)
+		{
+			std::vector<P> res;
+			for (const std::vector<T>& part : host)
+			{
+				device_buffer::ptr b(new device_buffer(part.size() * sizeof(T)));
+				if (!part.empty())
+					cuda_check(cudaMemcpy(static_cast<void *>(*b), part.data(), part.size() * sizeof(T), cudaMemcpyHostToDevice), "cudaMemcpy");
+				res.push_back(b);
+			}
+			return res;
+		}
+	}
+
+	std::vector<device_buffer::const_ptr> layer_tester_b200::get_data(layer_data::const_ptr host_data) const
+	{
+		return upload<float, device_buffer::const_ptr>(*host_data);
+	}
+
+	std::vector<device_buffer::const_ptr> layer_tester_b200::set_get_data_custom(layer_data_custom::const_ptr host_data)
+	{
+		notify_data_custom(host_data);
+		return upload<int, device_buffer::const_ptr>(*host_data);
+	}
+
+	std::vector<device_buffer::ptr> layer_updater_b200::get_data(layer_data::const_ptr host_data) const
+	{
+		return upload<float, device_buffer::ptr>(*host_data);
+	}
+
+	std::vector<device_buffer::const_ptr> layer_updater_b200::set_get_data_custom(layer_data_custom::const_ptr host_data)
+	{
+		notify_data_custom(host_data);
+		return upload<int, device_buffer::const_ptr>(*host_data);
+	}
+
+	void layer_updater_b200::get_data_from_device(const std::vector<device_buffer::ptr>& device_data, layer_data::ptr host_data) const
+	{
+		if (device_data.size() != host_data->size())
+			throw neural_network_exception("get_data_from_device: chunk counts differ");
+		for (size_t part_id = 0; part_id < host_data->size(); ++part_id)
+		{
+			std::vector<float>& part = (*host_data)[part_id];
+			if (!part.empty())
+				cuda_check(cudaMemcpy(part.data(), static_cast<const void *>(*device_data[part_id]), part.size() * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy");
+		}
 	}
 
 	// Defaults of the reference base class: an action the layer does not implement is an error
@@ -519,7 +741,7 @@ namespace nnf_b200
 	}
 
 	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
-		const layer_configuration_specific& out) const
+		const layer_configuration_specific& out, running_configuration_b200::const_ptr cuda_config) const
 	{
 		layer_tester_b200::ptr t;
 		const std::string& n = l->type_name;
@@ -532,12 +754,12 @@ namespace nnf_b200
 		else if (n == "AverageSubsampling") t.reset(new average_subsampling_layer_tester_b200());
 		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
 		else throw neural_network_exception("No layer tester is registered with id " + n);
-		t->configure(in, out, l);
+		t->configure(in, out, l, cuda_config ? cuda_config : running_configuration_b200::get_current());
 		return t;
 	}
 
 	layer_updater_b200::ptr layer_factory_b200::create_updater(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
-		const layer_configuration_specific& out, const std::set<layer_action>& actions) const
+		const layer_configuration_specific& out, const std::set<layer_action>& actions, running_configuration_b200::const_ptr cuda_config) const
 	{
 		layer_updater_b200::ptr u;
 		const std::string& n = l->type_name;
@@ -550,7 +772,7 @@ namespace nnf_b200
 		else if (n == "AverageSubsampling") u.reset(new average_subsampling_layer_updater_b200());
 		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
 		else throw neural_network_exception("No layer updater is registered with id " + n);
-		u->configure(in, out, l, actions);
+		u->configure(in, out, l, cuda_config ? cuda_config : running_configuration_b200::get_current(), actions);
 		return u;
 	}
 
@@ -641,12 +863,7 @@ namespace
 {
 	thread_local std::string g_error;
 
-	struct handle
-	{
-		std::shared_ptr<layer> schema;
-		layer_tester_b200::ptr tester;
-		layer_updater_b200::ptr updater;
-	};
+	typedef nnf_b200::detail::flat_handle handle;
 
 	device_buffer::ptr buf(void * p, size_t bytes = size_t(1) << 40) { return p ? device_buffer::ptr(new device_buffer(p, bytes)) : device_buffer::ptr(); }
 	device_buffer::const_ptr cbuf(const void * p) { return p ? device_buffer::const_ptr(new device_buffer(const_cast<void *>(p), size_t(1) << 40)) : device_buffer::const_ptr(); }
@@ -800,6 +1017,165 @@ NNFH_API int nnfh_updater_backward_data_and_weights(void * h, void * stream, voi
 	static_cast<handle *>(h)->updater->enqueue_backward_data_and_weights_propagation((cudaStream_t)stream, std::vector<device_buffer::ptr>(1, buf(in_err)), cbuf(out_err), {},
 		vec(gradient, n_gradient), cvec(data, n_data), {}, std::vector<device_buffer::const_ptr>(1, cbuf(in_neurons)), device_buffer::const_ptr(), {},
 		buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), cbuf(temp_fixed), device_buffer::const_ptr(), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+// ---- the same members in their general form: lists of inputs, outputs and chunks, every query --------------
+// Used for the objects of fused groups (nnfh_net_*), whose heads take several inputs and may write two outputs.
+NNFH_API int nnfh_forward(void * h, void * stream, void * const * outs, int n_outs, const void * const * data, int n_data, const void * const * inputs, int n_inputs,
+	void * working_fixed, size_t working_fixed_bytes, void * temp_fixed, void * temp_per_entry, unsigned int entry_count)
+{
+	NNFH_TRY
+	handle& hd = *static_cast<handle *>(h);
+	if (hd.tester)
+		hd.tester->enqueue_forward_propagation((cudaStream_t)stream, vec(outs, n_outs), {}, cvec(data, n_data), {}, cvec(inputs, n_inputs), {},
+			buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), entry_count);
+	else
+		hd.updater->enqueue_forward_propagation((cudaStream_t)stream, vec(outs, n_outs), {}, cvec(data, n_data), {}, cvec(inputs, n_inputs), {},
+			buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), buf(temp_fixed), buf(temp_per_entry), entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_backward_data(void * h, void * stream, unsigned int input_index, void * in_err, const void * out_err, const void * const * data, int n_data,
+	const void * const * in_neurons, int n_in_neurons, const void * out_neurons, const void * temp_fixed, const void * temp_per_entry,
+	int add_update_to_destination, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_data_propagation((cudaStream_t)stream, input_index, buf(in_err), cbuf(out_err), {}, cvec(data, n_data), {},
+		cvec(in_neurons, n_in_neurons), cbuf(out_neurons), {}, device_buffer::ptr(), device_buffer::ptr(), cbuf(temp_fixed), cbuf(temp_per_entry),
+		add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_backward_weights(void * h, void * stream, void * const * gradient, int n_gradient, const void * const * in_neurons, int n_in_neurons,
+	const void * out_err, void * working_fixed, size_t working_fixed_bytes, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_weights_propagation((cudaStream_t)stream, {}, vec(gradient, n_gradient), {},
+		cvec(in_neurons, n_in_neurons), cbuf(out_err), {}, buf(working_fixed, working_fixed_bytes), device_buffer::ptr(),
+		device_buffer::const_ptr(), device_buffer::const_ptr(), entry_count);
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_backward_data_and_weights(void * h, void * stream, void * const * in_errs, int n_in_errs, const void * out_err, void * const * gradient, int n_gradient,
+	const void * const * data, int n_data, const void * const * in_neurons, int n_in_neurons, const void * out_neurons, void * working_fixed, size_t working_fixed_bytes,
+	const void * temp_fixed, int add_update_to_destination, unsigned int entry_count)
+{
+	NNFH_TRY
+	static_cast<handle *>(h)->updater->enqueue_backward_data_and_weights_propagation((cudaStream_t)stream, vec(in_errs, n_in_errs), cbuf(out_err), {},
+		vec(gradient, n_gradient), cvec(data, n_data), {}, cvec(in_neurons, n_in_neurons), cbuf(out_neurons), {},
+		buf(working_fixed, working_fixed_bytes), device_buffer::ptr(), cbuf(temp_fixed), device_buffer::const_ptr(), add_update_to_destination != 0, entry_count);
+	NNFH_CATCH
+}
+
+// what: 0 temporary_working_fixed size, 1 temporary_fixed size, 2 temporary_per_entry size, 3 input index the layer can write,
+// 4-7 backward_data depends on input buffer b / output buffer / temporary fixed / temporary per entry (a = action input index),
+// 8-11 the same for backward_data_and_weights, 12-14 backward_weights on input buffer b / temporary fixed / temporary per entry,
+// 15 output count, 16 temporary_working_per_entry size, 17 persistent working buffers, 18 inputs read through a texture
+NNFH_API long long nnfh_query(void * h, int what, int action_type, int backprop_index, unsigned int a, unsigned int b)
+{
+	handle& hd = *static_cast<handle *>(h);
+	const layer_action act((layer_action::action_type)action_type, backprop_index);
+	try
+	{
+		if (hd.tester)
+		{
+			layer_tester_b200& t = *hd.tester;
+			switch (what)
+			{
+			case 0: return (long long)t.get_temporary_working_fixed_buffer_size().first;
+			case 3: return t.get_input_index_layer_can_write();
+			case 15: return t.get_output_count();
+			case 16: return (long long)t.get_temporary_working_per_entry_buffer_size();
+			case 17: return (long long)t.get_persistent_working_data().size();
+			case 18: return (long long)t.get_linear_addressing_through_texture_per_entry().size();
+			default: return -1;
+			}
+		}
+		layer_updater_b200& u = *hd.updater;
+		switch (what)
+		{
+		case 0: return (long long)u.get_temporary_working_fixed_buffer_size(act).first;
+		case 1: return (long long)u.get_temporary_fixed_buffer_size();
+		case 2: return (long long)u.get_temporary_per_entry_buffer_size();
+		case 3: return u.get_input_index_layer_can_write(act);
+		case 4: return u.is_backward_data_dependent_on_input_buffer(a, b);
+		case 5: return u.is_backward_data_dependent_on_output_buffer(a);
+		case 6: return u.is_backward_data_dependent_on_temporary_fixed_buffer(a);
+		case 7: return u.is_backward_data_dependent_on_temporary_per_entry_buffer(a);
+		case 8: return u.is_backward_data_and_weights_dependent_on_input_buffer(b);
+		case 9: return u.is_backward_data_and_weights_dependent_on_output_buffer();
+		case 10: return u.is_backward_data_and_weights_dependent_on_temporary_fixed_buffer();
+		case 11: return u.is_backward_data_and_weights_dependent_on_temporary_per_entry_buffer();
+		case 12: return u.is_backward_weights_dependent_on_input_buffer(b);
+		case 13: return u.is_backward_weights_dependent_on_temporary_fixed_buffer();
+		case 14: return u.is_backward_weights_dependent_on_temporary_per_entry_buffer();
+		case 15: return u.get_output_count();
+		case 16: return (long long)u.get_temporary_working_per_entry_buffer_size(act);
+		case 17: return (long long)u.get_persistent_working_data().size();
+		case 18: return (long long)u.get_linear_addressing_through_texture_per_entry().size();
+		default: return -1;
+		}
+	}
+	catch (const std::exception& e)
+	{
+		g_error = e.what();
+		return -2;
+	}
+}
+
+// Weights to the device through the object's get_data; the device pointers land in out_device (one per chunk) and stay
+// valid while the handle lives. nnfh_get_data_from_device copies them back through get_data_from_device (updaters).
+NNFH_API int nnfh_get_data(void * h, const float * const * parts, const long long * elem_counts, int n_parts, void ** out_device)
+{
+	NNFH_TRY
+	handle& hd = *static_cast<handle *>(h);
+	layer_data::ptr host(new layer_data());
+	for (int i = 0; i < n_parts; ++i)
+		host->push_back(std::vector<float>(parts[i], parts[i] + elem_counts[i]));
+	hd.uploaded.clear();
+	hd.uploaded_const.clear();
+	if (hd.tester)
+	{
+		hd.uploaded_const = hd.tester->get_data(host);
+		for (int i = 0; i < n_parts; ++i)
+			out_device[i] = const_cast<void *>(static_cast<const void *>(*hd.uploaded_const[i]));
+	}
+	else
+	{
+		hd.uploaded = hd.updater->get_data(host);
+		for (int i = 0; i < n_parts; ++i)
+			out_device[i] = static_cast<void *>(*hd.uploaded[i]);
+	}
+	NNFH_CATCH
+}
+
+NNFH_API int nnfh_get_data_from_device(void * h, float * const * parts, const long long * elem_counts, int n_parts)
+{
+	NNFH_TRY
+	handle& hd = *static_cast<handle *>(h);
+	if (!hd.updater || (int)hd.uploaded.size() != n_parts)
+		throw neural_network_exception("nnfh_get_data_from_device: call nnfh_get_data on an updater first");
+	layer_data::ptr host(new layer_data());
+	for (int i = 0; i < n_parts; ++i)
+		host->push_back(std::vector<float>((size_t)elem_counts[i]));
+	hd.updater->get_data_from_device(hd.uploaded, host);
+	for (int i = 0; i < n_parts; ++i)
+		std::memcpy(parts[i], (*host)[i].data(), (size_t)elem_counts[i] * sizeof(float));
+	NNFH_CATCH
+}
+
+// the fields of running_configuration_b200 for the current device: device_id, compute capability major and minor,
+// multiprocessor_count, max_threads_per_multiprocessor, smem_per_block, smem_per_multiprocessor, l2_cache_size,
+// max_registers_per_multiprocessor, device_pos, device_count
+NNFH_API int nnfh_running_configuration(long long * out11)
+{
+	NNFH_TRY
+	const running_configuration_b200::const_ptr rc = running_configuration_b200::get_current();
+	const long long v[11] = {rc->device_id, rc->compute_capability_major, rc->compute_capability_minor, rc->multiprocessor_count,
+		rc->max_threads_per_multiprocessor, (long long)rc->smem_per_block, (long long)rc->smem_per_multiprocessor, rc->l2_cache_size,
+		rc->max_registers_per_multiprocessor, rc->device_pos, rc->device_count};
+	std::memcpy(out11, v, sizeof(v));
 	NNFH_CATCH
 }
 

@@ -127,3 +127,51 @@ def test_fusion_peephole_training_patterns():
     from nnforge_b200 import host
     with pytest.raises(host.HostLayerError):
         host.plan_fusion("b ReLU a\na BatchNorm x\n")    # not in execution order
+
+
+def test_fused_group_objects_and_their_buffer_plan_answers():
+    """create_testers / create_updaters on planned groups: one head that takes the group's inputs, weights and outputs,
+    followers pinned to the head's buffer, and a two-output head for the pooled and the loss forms."""
+    from nnforge_b200 import host
+    net = host.Net("bn BatchNorm x\nadd Add r,bn\nrelu ReLU add\npool MaxSubsampling relu win=3x3 stride=2x2\n", {"x": (8, 14, 14), "r": (8, 14, 14)})
+    head, add, relu, pool = net.objects
+    assert (head.role, head.kind, head.entry) == ("head", "bn_add_relu_maxpool", "nnf_bn_add_relu_maxpool_fwd")
+    assert head.inputs == ["x", "r"] and head.data == ["bn"] and head.outputs == ["relu", "pool"] and head.elided == ["bn", "add"]
+    assert head.get_output_count() == 2 and pool.shape == (8, 6, 6)
+    assert [o.role for o in (add, relu, pool)] == ["follower"] * 3
+    assert add.get_input_index_layer_can_write() == 0 and relu.get_input_index_layer_can_write() == 0 and pool.get_input_index_layer_can_write() == -1
+    assert add.inputs == [] and add.outputs == []      # a follower takes and writes nothing
+
+    net = host.Net("a PReLU x\nb ELU a\n", {"x": (4, 5, 5)})
+    assert net.objects[0].kind == "bn_act" and net.objects[0].data == ["a"] and net.objects[0].outputs == ["b"]
+
+    net = host.Net("bn BatchNorm x eps=1e-5\np PReLU bn\ne ELU p\nsm Softmax e\nl NegativeLogLikelihood sm,t,m scale=0.5\nacc Accuracy sm,t topn=3\n",
+                   {"x": (8, 14, 14), "t": (8, 14, 14), "m": (1, 14, 14)}, training=True)
+    head, p, e, sm, loss, acc = net.objects
+    assert (head.kind, head.data, head.outputs) == ("bn_train_act", ["bn", "p"], ["e"])
+    assert head.get_temporary_fixed_buffer_size() == 8 * 2 * 4 and head.get_temporary_working_fixed_buffer_size(host.FORWARD) > 0
+    assert head.get_input_index_layer_can_write(host.BACKWARD_DATA_AND_WEIGHTS) == 0
+    assert head.is_backward_data_and_weights_dependent_on_temporary_fixed_buffer() and not head.is_backward_data_and_weights_dependent_on_output_buffer()
+    for f in (p, e):
+        assert f.get_input_index_layer_can_write(host.FORWARD) == 0 and f.get_input_index_layer_can_write(host.BACKWARD_DATA) == 0
+        assert not f.is_backward_data_dependent_on_input_buffer() and not f.is_backward_weights_dependent_on_input_buffer()
+        assert not f.is_backward_data_dependent_on_temporary_fixed_buffer() and not f.is_backward_weights_dependent_on_temporary_per_entry_buffer()
+    assert (sm.kind, sm.inputs, sm.outputs, sm.get_output_count()) == ("softmax_nll", ["e", "t", "m"], ["sm", "l"], 2)
+    assert not sm.is_backward_data_dependent_on_input_buffer(0, 0) and sm.is_backward_data_dependent_on_input_buffer(0, 2)
+    assert loss.role == "follower" and loss.shape == (1, 14, 14) and acc.role == "single" and acc.shape == (4, 14, 14)
+    assert head.get_persistent_working_data_count() == 0 and head.get_linear_addressing_through_texture_per_entry() == []
+
+    with pytest.raises(host.HostLayerError) as err:
+        host.Net("bn BatchNorm x\n", {})
+    assert "x" in str(err.value)
+    # several devices share the batch: the running configuration must bring a directory for the mailboxes
+    with pytest.raises(host.HostLayerError) as err:
+        host.Net("bn BatchNorm x\n", {"x": (8, 4, 4)}, training=True, device_pos=0, device_count=2)
+    assert "peer directory" in str(err.value)
+
+
+def test_running_configuration_has_the_reference_fields():
+    from nnforge_b200 import host
+    rc = host.running_configuration()
+    assert rc["multiprocessor_count"] > 0 and rc["smem_per_block"] > 48 * 1024 and rc["l2_cache_size"] > 0
+    assert rc["compute_capability_major"] >= 1 and (rc["device_pos"], rc["device_count"]) == (0, 1)
