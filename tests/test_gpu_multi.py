@@ -76,3 +76,65 @@ def test_two_gpu_sharded_matches_unsharded_oracle(tmp_path, oracle, use_peer):
     from util import assert_close
     assert_close(np.concatenate([p["y"] for p in parts]), yw, "sharded forward", atol=2e-6)
     assert_close(np.concatenate([p["dx"] for p in parts]), dxw, "sharded backward", atol=5e-6)
+
+
+def test_two_devices_in_one_process_through_the_layer_objects(oracle):
+    """nnForge drives all its GPUs from one process. Two sets of layer objects, one per device, share a peer directory: each
+    fused BatchNorm head owns a mailbox (its persistent working data), finds the other's through the directory, and the two
+    single launches per direction exchange the batch statistics between them."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from nnforge_b200 import host
+    import nnforge_b200.capi as capi
+    from util import assert_close
+    x, dy, gamma, beta, slope = _inputs(0)
+    n, c, h, w = x.shape
+    world = 2
+    host.enable_peer_access(0, 1)
+    host.enable_peer_access(1, 0)
+    peers = host.PeerDirectory()
+    spec = "bn BatchNorm x eps=1e-5\nprelu PReLU bn\nelu ELU prelu\n"
+    per = n // world
+    state = []
+    for pos in range(world):
+        with torch.cuda.device(pos):
+            net = host.Net(spec, {"x": (c, w, h)}, training=True, device_pos=pos, device_count=world, peers=peers)
+            head = net.objects[0]
+            assert head.kind == "bn_train_act" and head.get_persistent_working_data_count() == 1
+            d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+            state.append({"net": net, "head": head, "x": d(x[pos * per:(pos + 1) * per]), "dy": d(dy[pos * per:(pos + 1) * per]),
+                          "data": [d(gamma), d(beta), torch.zeros(c, device="cuda"), torch.ones(c, device="cuda"), d(slope)],
+                          "grad": [torch.zeros(c, device="cuda") for _ in range(5)],
+                          "saved": torch.empty(2 * c, device="cuda"), "y": torch.empty(per, c, h, w, device="cuda"), "dx": torch.empty(per, c, h, w, device="cuda"),
+                          "ws_f": torch.empty(head.get_temporary_working_fixed_buffer_size(host.FORWARD), dtype=torch.uint8, device="cuda"),
+                          "ws_b": torch.empty(head.get_temporary_working_fixed_buffer_size(host.BACKWARD_DATA_AND_WEIGHTS), dtype=torch.uint8, device="cuda"),
+                          "report": torch.zeros(2 * capi.REPORT_WORDS, dtype=torch.int64).pin_memory()})
+    for _ in range(3):   # sequence numbers advance in step on both devices
+        for pos, s in enumerate(state):
+            with torch.cuda.device(pos):
+                s["head"].enqueue_forward_propagation([s["y"]], s["data"], [s["x"]], per, temporary_working_fixed_buffer=s["ws_f"], temporary_fixed_buffer=s["saved"])
+        for pos, s in enumerate(state):
+            with torch.cuda.device(pos):
+                s["head"].enqueue_backward_data_and_weights_propagation([s["dx"]], s["dy"], s["grad"], s["data"], [s["x"]], None, per,
+                                                                        temporary_working_fixed_buffer=s["ws_b"], temporary_fixed_buffer=s["saved"])
+    for pos, s in enumerate(state):
+        with torch.cuda.device(pos):
+            capi.read_report(s["report"][:capi.REPORT_WORDS], s["ws_f"])
+            capi.read_report(s["report"][capi.REPORT_WORDS:], s["ws_b"])
+            torch.cuda.synchronize()
+            assert capi.parse_report(s["report"][:capi.REPORT_WORDS])["status"] == 0 and capi.parse_report(s["report"][capi.REPORT_WORDS:])["status"] == 0
+    u, sv = oracle.bn_train_fwd(x, gamma, beta, 1e-5)
+    yw = oracle.elu_fwd(oracle.prelu_fwd(u, slope))
+    du = oracle.prelu_bwd_data(oracle.elu_bwd(dy, yw), u, slope)
+    db, dg = oracle.bn_train_bwd_sums(du, x, sv)
+    dxw = oracle.bn_train_bwd_apply(du, x, gamma, sv, db, dg, x.size // c)
+    assert_close(np.concatenate([s["y"].cpu().numpy() for s in state]), yw, "forward over two devices", atol=2e-6)
+    assert_close(np.concatenate([s["dx"].cpu().numpy() for s in state]), dxw, "backward over two devices", atol=5e-6)
+    for s in state:   # whole-batch statistics on both devices, the same bits
+        assert_close(s["saved"].cpu().numpy(), sv, "saved statistics")
+    assert torch.equal(state[0]["saved"].cpu(), state[1]["saved"].cpu())
+    # the per-channel gradients hold each device's own sums (their cross-device sum is the gradient all-reduce's job)
+    total_gamma = sum(s["grad"][0].cpu().numpy().astype(np.float64) for s in state) / 3
+    assert np.abs(total_gamma - dg).max() <= 2e-6 * np.sqrt(x.size // c) + 1e-5 * np.abs(dg).max()
