@@ -213,10 +213,11 @@ namespace nnf
 		}
 
 		// ---- the kernel for planes of whole float4s ------------------------------------------------------------
-		constexpr int kStreamSlots = 4;                 // 16-byte slots of a thread in one sweep
+		constexpr int kStreamSlots = 4;                 // 16-byte slots of a thread in one sweep (forward)
+		constexpr int kStreamSlotsBwd = 2;              // the same, backward: two tensors are staged
 		constexpr int kStreamWarps = kChainThreads / 32;
-		constexpr int kStagesFwd = 3, kStagesBwd = 2;   // sweeps in flight per thread
-		constexpr int kCtasFwd = 4, kCtasBwd = 3;       // resident CTAs per SM the register budget is cut for
+		constexpr int kStagesFwd = 3, kStagesBwd = 3;   // sweeps in flight per thread (48 KB of shared memory per CTA in both directions)
+		constexpr int kCtasFwd = 4, kCtasBwd = 4;       // resident CTAs per SM the register budget is cut for
 
 		// The head of every workspace: what a launch reports. Cleared by the memset in front of the launch.
 		struct launch_report
@@ -332,7 +333,7 @@ namespace nnf
 		{
 			constexpr int K = BWD ? 3 : 2;
 			constexpr int T = BWD ? 2 : 1;
-			constexpr int L = kStreamSlots;
+			constexpr int L = BWD ? kStreamSlotsBwd : kStreamSlots;
 			constexpr int STAGES = BWD ? kStagesBwd : kStagesFwd;
 			extern __shared__ float4 ring[];   // [STAGES][T][L][kChainThreads]: a thread reads back only what it copied itself
 			__shared__ uint32_t s_item[4];
@@ -1334,7 +1335,7 @@ namespace nnf
 			if (hw % 4 != 0 || n < 1 || c < 1 || n * hw >= (int64_t(1) << 31) || c > 0x7fffffff / 256)
 				return false;
 			const int64_t vpp = hw / 4;
-			const int64_t slots = int64_t(kChainThreads) * kStreamSlots;
+			const int64_t slots = int64_t(kChainThreads) * (backward ? kStreamSlotsBwd : kStreamSlots);
 			int64_t rows, cols, tiles;
 			if (vpp <= slots) { cols = vpp; rows = slots / vpp; tiles = 1; }
 			else { cols = slots; rows = 1; tiles = div_up(vpp, slots); }
@@ -1485,7 +1486,7 @@ namespace nnf
 			if (tag == 0)
 				tag = ++g_launch_tag;   // zero is what a fresh workspace holds
 			p.tag = tag;
-			const size_t smem = size_t(backward ? kStagesBwd * 2 : kStagesFwd) * kStreamSlots * kChainThreads * sizeof(float4);
+			const size_t smem = size_t(backward ? kStagesBwd * 2 * kStreamSlotsBwd : kStagesFwd * kStreamSlots) * kChainThreads * sizeof(float4);
 			cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 			if (e != cudaSuccess)
 				return set_error(NNF_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));

@@ -8,7 +8,8 @@ import numpy as np
 import pytest
 
 import synth
-from util import assert_bits_equal, assert_close, assert_close_off_kink
+from util import assert_bits_equal, assert_close, assert_close_off_kink, assert_no_worse_than_fp32_checker
+import exact64
 
 pytestmark = pytest.mark.gpu
 
@@ -226,9 +227,11 @@ def test_softmax(capi, oracle, shape):
     capi.softmax_bwd(dx, dev(dy), yd)
     # dx = y*(dy - s): cancellation in (dy - s) leaves an absolute error ~ eps*|dy|*y
     assert_close(host(dx), oracle.softmax_bwd(dy, want), "softmax bwd", atol=2e-6)
+    assert_no_worse_than_fp32_checker(host(dx), oracle.softmax_bwd(dy, want), exact64.softmax_bwd(dy, want), "softmax bwd against float64")
     dx = dev(dx0.copy())
     capi.softmax_bwd(dx, dev(dy), yd, add_to_destination=True)
     assert_close(host(dx), oracle.softmax_bwd(dy, want, dx=dx0), "softmax bwd accumulate", atol=2e-6)
+    assert_no_worse_than_fp32_checker(host(dx), oracle.softmax_bwd(dy, want, dx=dx0), exact64.softmax_bwd(dy, want, dx0), "softmax bwd accumulate against float64")
 
 
 POOLS = [((3, 3), (2, 2), (False, False)), ((3, 3), (2, 2), (True, True)), ((2, 2), (2, 2), (False, False)), ((2, 2), (2, 2), (True, False)),
@@ -436,6 +439,12 @@ def test_bn_train(capi, oracle, shape, chain, shards):
     # straight behind the batch norm has a derivative that jumps where the batch-norm output is 0
     u_w = oracle.bn_train_apply(x, gamma, beta, saved_w)
     assert_close_off_kink(dx, dx_w, u_w if chain and chain[0] in ("prelu", "relu0", "relu01") else np.ones_like(x), "train bwd %s" % (chain,), atol=5e-6)
+    # the two absolute tolerances above are wider than the path's 1e-6: wherever the kernels are further than that from the
+    # float64 value of the step, the fp32 checker is too
+    y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, chain, eps)
+    kink = (np.abs(u_x) < 1e-5) if chain and chain[0] in ("prelu", "relu0", "relu01") else None
+    assert_no_worse_than_fp32_checker(y, y_w, y_x, "train fwd %s against float64" % (chain,))
+    assert_no_worse_than_fp32_checker(dx, dx_w, dx_x, "train bwd %s against float64" % (chain,), leave_out=kink)
     # running-statistics pseudo-gradients: entry_count*(batch - running), running = (0, 1)
     assert_close(grads["mean"], shape[0] * saved_w[:c], "grad mean", atol=1e-5)
     assert_close(grads["invsigma"], shape[0] * (saved_w[c:] - 1.0), "grad invsigma", atol=1e-5)
@@ -475,11 +484,14 @@ def test_bn_train_single_launch_geometries(capi, oracle, shape, s_kb, a_kb, chun
     gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
     slope = synth.uniform(g, c, 0.0, 0.3)
     y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
+    y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, chain, 1e-5)
     for _ in range(2):  # twice: the counters of the first run must not leak into the second
         y, saved, dx, grads = gpu_train(capi, x, dy, gamma, beta, slope, chain, 1e-5, 1, True)
         assert_close(saved, saved_w, "saved mean/invstd")
         assert_close(y, y_w, "single-launch train fwd", atol=2e-6)
         assert_close(dx, dx_w, "single-launch train bwd", atol=5e-6)
+        assert_no_worse_than_fp32_checker(y, y_w, y_x, "single-launch train fwd against float64")
+        assert_no_worse_than_fp32_checker(dx, dx_w, dx_x, "single-launch train bwd against float64", leave_out=np.abs(u_x) < 1e-5)
         scale = np.sqrt(x.size // c)
         assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
         assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
@@ -517,6 +529,10 @@ def test_bn_train_matches_cudnn(capi, shape):
     assert_close(host(saved)[c:], host(save_invstd), "inverse std-dev vs cuDNN")
     assert_close(host(y), host(out), "forward vs cuDNN", atol=2e-6)
     assert_close(host(dx), host(dx_w), "backward vs cuDNN", atol=5e-6)
+    # the widened absolute tolerances: cuDNN's own fp32 results are as far from the float64 value as this library's
+    y_x, _, dx_x, _ = exact64.bn_train_chain(x, dy, gamma, beta, None, (), eps)
+    assert_no_worse_than_fp32_checker(host(y), host(out), y_x, "forward against float64 (cuDNN as the fp32 yardstick)")
+    assert_no_worse_than_fp32_checker(host(dx), host(dx_w), dx_x, "backward against float64 (cuDNN as the fp32 yardstick)")
     scale = np.sqrt(x.size // c)
     assert np.abs(host(gb) - host(dbeta_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dbeta_w)).max()
     assert np.abs(host(gg) - host(dgamma_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dgamma_w)).max()
@@ -564,6 +580,11 @@ def test_bn_train_chain_matches_cudnn_and_plain_layers(capi, oracle, shape):
     assert_close(host(y), y_w, "fused forward vs cuDNN + plain PReLU, ELU", atol=2e-6)
     # PReLU's derivative jumps at 0: elements whose batch-norm output is within rounding of 0 may take either side
     assert_close_off_kink(host(dx), host(dx_w), u, "fused backward vs plain ELU', PReLU' + cuDNN", atol=5e-6)
+    y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, ("prelu", "elu"), eps)
+    assert_no_worse_than_fp32_checker(host(y), y_w, y_x, "fused forward against float64 (cuDNN + plain layers as the fp32 yardstick)")
+    assert_no_worse_than_fp32_checker(host(dx), host(dx_w), dx_x, "fused backward against float64 (cuDNN + plain layers as the fp32 yardstick)",
+                                      leave_out=np.abs(u_x) < 1e-5)
+    del y_x, dx_x, u_x
     scale = np.sqrt(x.size // c)
     assert np.abs(host(grads["beta"]) - host(dbeta_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dbeta_w)).max()
     assert np.abs(host(grads["gamma"]) - host(dgamma_w)).max() <= 2e-6 * scale + 1e-5 * np.abs(host(dgamma_w)).max()
@@ -627,6 +648,7 @@ def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
     gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
     slope = synth.uniform(g, c, 0.0, 0.3)
     y_w, saved_w, dx_w, db_w, dg_w, dslope_w = train_oracle(oracle, x, dy, gamma, beta, slope, chain, 1e-5)
+    y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, chain, 1e-5)
     mailbox = torch.zeros(capi.bn_train_mailbox_bytes(c) // 8, dtype=torch.int64, device="cuda")
     for seq in (1, 3, 5):  # both mailbox parities, stale words of earlier exchanges in place
         y, saved, dx, grads = _sharded_single_launch(capi, x, dy, gamma, beta, slope, chain, [mailbox], 0, 1, seq, x.size // c)
@@ -634,6 +656,8 @@ def test_bn_train_sharded_single_launch_one_rank(capi, oracle, shape):
         assert_close(saved, saved_w, "saved mean/invstd")
         assert_close(y, y_w, "sharded single-launch fwd", atol=2e-6)
         assert_close(dx, dx_w, "sharded single-launch bwd", atol=5e-6)
+        assert_no_worse_than_fp32_checker(y, y_w, y_x, "sharded single-launch fwd against float64")
+        assert_no_worse_than_fp32_checker(dx, dx_w, dx_x, "sharded single-launch bwd against float64", leave_out=np.abs(u_x) < 1e-5)
         scale = np.sqrt(x.size // c)
         assert np.abs(grads["beta"] - db_w).max() <= 2e-6 * scale + 1e-5 * np.abs(db_w).max()
         assert np.abs(grads["gamma"] - dg_w).max() <= 2e-6 * scale + 1e-5 * np.abs(dg_w).max()
@@ -781,6 +805,7 @@ def test_negative_log_likelihood(capi, oracle, shape, masked):
     capi.nll_fwd(err, pd, td, md, scale)
     # logf of the device against glibc's, and for rows a different order of the channel sum: tolerance
     assert_close(host(err), oracle.nll_fwd(p, t, mask, scale), "nll forward", atol=2e-6)
+    assert_no_worse_than_fp32_checker(host(err), oracle.nll_fwd(p, t, mask, scale), exact64.nll_fwd(p, t, mask, scale), "nll forward against float64")
     dp = torch.empty_like(pd)
     capi.nll_bwd(dp, pd, td, md, scale)
     assert_bits_equal(host(dp), oracle.nll_bwd(p, t, mask, scale), "nll gradient")
@@ -815,6 +840,7 @@ def test_softmax_with_loss(capi, oracle, shape, masked):
     assert_close(host(probs), oracle.softmax_fwd(logits), "fused softmax")
     p = host(probs)
     assert_close(host(err), oracle.nll_fwd(p, t, mask, scale), "fused loss", atol=2e-6)
+    assert_no_worse_than_fp32_checker(host(err), oracle.nll_fwd(p, t, mask, scale), exact64.nll_fwd(p, t, mask, scale), "fused loss against float64")
     want = oracle.softmax_bwd(oracle.nll_bwd(p, t, mask, scale), p)
     dl = torch.empty_like(ld)
     capi.softmax_nll_bwd(dl, probs, td, md, scale)
@@ -822,6 +848,8 @@ def test_softmax_with_loss(capi, oracle, shape, masked):
         assert_bits_equal(host(dl), want, "fused backward (ascending channel sums)")
     else:
         assert_close(host(dl), want, "fused backward", atol=2e-6)
+        g64 = np.where(t > 0, t.astype(np.float64) / np.maximum(p.astype(np.float64), 1e-20), 0.0) * np.float64(np.float32(scale)) * (1.0 if mask is None else mask.astype(np.float64))
+        assert_no_worse_than_fp32_checker(host(dl), want, exact64.softmax_bwd(g64, p), "fused backward against float64")
     # the two stand-alone kernels one after the other give the same as the fused backward
     g1, two = torch.empty_like(ld), torch.empty_like(ld)
     capi.nll_bwd(g1, probs, td, md, scale)
@@ -1015,3 +1043,6 @@ def test_bn_train_exchange_inside_the_kernels_emulated(capi, oracle, world):
     assert_close(host(saved[0]), saved_w, "saved statistics")
     assert_close(np.concatenate([host(t) for t in ys]), y_w, "forward", atol=2e-6)
     assert_close(np.concatenate([host(t) for t in dxs]), dx_w, "backward", atol=5e-6)
+    y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, chain, 1e-5)
+    assert_no_worse_than_fp32_checker(np.concatenate([host(t) for t in ys]), y_w, y_x, "forward against float64")
+    assert_no_worse_than_fp32_checker(np.concatenate([host(t) for t in dxs]), dx_w, dx_x, "backward against float64", leave_out=np.abs(u_x) < 1e-5)

@@ -47,3 +47,22 @@ def assert_close_off_kink(got, want, u, what="", rtol=RTOL, atol=ATOL, halfwidth
     got = np.where(near, 0.0, np.asarray(got, dtype=np.float64))
     want = np.where(near, 0.0, np.asarray(want, dtype=np.float64))
     assert_close(got, want, what, rtol, atol)
+
+
+def assert_no_worse_than_fp32_checker(got, want32, exact64, what="", rtol=RTOL, atol=ATOL, factor=2.0, leave_out=None):
+    """The companion of a comparison made at a widened absolute tolerance. Errors are measured against the float64 twin in
+    units of the path's tolerance (atol + rtol*|exact|). Where the GPU result is further than one unit from the exact value, the
+    fp32 checker must be that far from it too (within `factor`): the widening then absorbs the rounding of an fp32 evaluation
+    of the expression, which the checker shows just as much, and not an error of the kernel."""
+    exact = np.asarray(exact64, dtype=np.float64)
+    unit = atol + rtol * np.abs(exact)
+    with np.errstate(invalid="ignore"):
+        e_got = np.abs(np.asarray(got, dtype=np.float64) - exact) / unit
+        e_own = np.abs(np.asarray(want32, dtype=np.float64) - exact) / unit
+    keep = np.isfinite(e_got) & np.isfinite(e_own)
+    if leave_out is not None:
+        keep &= ~leave_out
+    worst_got, worst_own = float(e_got[keep].max(initial=0.0)), float(e_own[keep].max(initial=0.0))
+    assert worst_got <= max(1.0, factor * worst_own), \
+        "%s: the GPU result is %.2f tolerance units from the float64 value, the fp32 checker only %.2f" % (what, worst_got, worst_own)
+    return worst_got, worst_own
