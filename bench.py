@@ -274,6 +274,10 @@ def collect_sweep(args, quick):
     bn = bnp(64)
     relu = [capi.relu(0.0)]
     report(0, "bn_infer+relu x[64,64,32,32]", timeit(lambda i: capi.bn_infer_act(ys[i], xs[i], bn=bn, acts=relu), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
+    if not quick:
+        # what a plain copy of a tensor this small reaches under the same procedure: the launch's ramp-up and tail are a fixed
+        # few microseconds, so 16.8 MB in and out cannot reach the figure of a 200 MB copy
+        report(0, "reference point: torch copy_ of x[64,64,32,32]", timeit(lambda i: ys[i].copy_(xs[i]), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
     del xs, ys
     # config 1: channel softmax
     for shape in [(256, 1000, 1, 1), (32, 21, 128, 128)]:
@@ -284,6 +288,8 @@ def collect_sweep(args, quick):
         dx = torch.empty(shape, device="cuda")
         report(1, "softmax fwd %s" % (list(shape),), timeit(lambda i: capi.softmax_fwd(ys[i], xs[i]), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
         report(1, "softmax bwd %s" % (list(shape),), timeit(lambda i: capi.softmax_bwd(dx, xs[i], ys[i]), nb), 12 * e, "%d rotating buffers, graph replay" % nb)
+        if not quick:
+            report(1, "reference point: torch copy_ of %s" % (list(shape),), timeit(lambda i: ys[i].copy_(xs[i]), nb), 8 * e, "%d rotating buffers, graph replay" % nb)
         del xs, ys, dx
     # beyond the five configurations: softmax fused with the loss behind it, at sizes above L2
     for shape in ([] if quick else [(65536, 1000, 1, 1), (512, 21, 128, 128)]):
@@ -331,6 +337,12 @@ def collect_sweep(args, quick):
         nb = 1
         report(3, "bn+add+relu+maxpool fwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_fwd(z, pooled, idx, x, r, bn, 0.0, p), nb), (12 + 8 * rho) * e)
         report(3, "bn+add+relu+maxpool bwd C=%d %dx%d" % (c, hw, hw), timeit(lambda i: capi.bn_add_relu_maxpool_bwd(dx, dr, dpo, idx, z, bn[0], bn[3], 0.0, p), nb), (12 + 8 * rho) * e)
+        if not quick and hw <= 14:
+            # the ceiling for launches this short: two plain copies back to back move the same 16 bytes per element
+            def two_copies(i):
+                dx.copy_(x)
+                dr.copy_(r)
+            report(3, "reference point: two torch copy_ back to back C=%d %dx%d" % (c, hw, hw), timeit(two_copies, nb) , 16 * e, "two launches")
         del x, r, z, pooled, idx, dpo, dx, dr
     # beyond the five configurations: the tail of a residual network - BN -> add -> ReLU -> global average pooling
     for c, hw in ([] if quick else [(512, 7), (256, 14)]):

@@ -1046,3 +1046,60 @@ def test_bn_train_exchange_inside_the_kernels_emulated(capi, oracle, world):
     y_x, _, dx_x, u_x = exact64.bn_train_chain(x, dy, gamma, beta, slope, chain, 1e-5)
     assert_no_worse_than_fp32_checker(np.concatenate([host(t) for t in ys]), y_w, y_x, "forward against float64")
     assert_no_worse_than_fp32_checker(np.concatenate([host(t) for t in dxs]), dx_w, dx_x, "backward against float64", leave_out=np.abs(u_x) < 1e-5)
+
+
+@pytest.mark.parametrize("shape", [(16, 32, 28, 28), (33, 48, 7, 7)])
+@pytest.mark.parametrize("mean,std", [(50.0, 0.5), (-300.0, 2.0)])
+def test_bn_train_far_from_zero_mean(capi, shape, mean, std):
+    """Channels whose mean is large against their spread (|mean|/std = 100 and 150), plus one channel that is a constant with a little
+    noise: E[x^2] - mean^2 in fp32 would lose four to five digits of the variance. The single launches take their sums around the
+    channel's first element and fold them in double, so {mean, invstd}, y and dx stay inside the path's tolerance of a float64
+    evaluation - and as close to it as cuDNN, which the reference calls."""
+    g = synth.rng(2, salt=8800 + sum(shape) + int(abs(mean)))
+    x = synth.normal(g, shape, mean, std)
+    x[:, 0] = np.float32(mean) + synth.normal(g, (shape[0],) + shape[2:], 0.0, 1e-3)   # a nearly constant channel
+    dy = synth.normal(g, shape)
+    c = shape[1]
+    gamma, beta = synth.uniform(g, c, 0.5, 1.5), synth.normal(g, c, 0.0, 0.1)
+    eps = 1e-5
+    xd, dyd, gd, bd = dev(x), dev(dy), dev(gamma), dev(beta)
+    ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, shape[2] * shape[3]), dtype=torch.uint8, device="cuda")
+    y, saved, sums, bsums = torch.empty_like(xd), torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+    dx = torch.empty_like(xd)
+    capi.bn_train_fwd(y, saved, sums, xd, gd, bd, eps, [], workspace=ws)
+    capi.bn_train_bwd(dx, bsums, dyd, xd, gd, bd, saved, [], workspace=ws)
+    torch.cuda.synchronize()
+    assert capi.fused_error_check() == 0
+    y_x, saved_x, dx_x, _ = exact64.bn_train_chain(x, dy, gamma, beta, None, (), eps)
+    assert_close(host(saved)[:c], saved_x[:c], "batch mean, far from zero")
+    assert_close(host(saved)[c:], saved_x[c:], "inverse std-dev, far from zero")
+    # y = (x - mean)*invstd*gamma + beta inherits the rounding of x - mean (x itself carries eps*|mean|): compare at the size of that
+    spread_ulp = float(np.abs(x).max()) * 6e-8 * float(saved_x[c:].max()) * 1.5
+    assert_close(host(y), y_x, "forward, far from zero", atol=2e-6 + 4 * spread_ulp)
+    assert_close(host(dx), dx_x, "backward, far from zero", atol=5e-6 + 4 * spread_ulp)
+    if torch.backends.cudnn.is_available():
+        out, save_mean, save_invstd, backward = _cudnn_train_step(xd, dyd, gd, bd, eps)
+        worst = lambda a: float(np.abs(np.asarray(a, np.float64) - saved_x[c:]).max() / np.abs(saved_x[c:]).max())
+        assert worst(host(saved)[c:]) <= max(1e-5, 2.0 * worst(host(save_invstd))), "inverse std-dev further from float64 than cuDNN's"
+
+
+def test_bn_train_split_entry_points_far_from_zero_mean(capi):
+    """The split entry points exchange {sum x, sum x^2} as 2*C floats (the message a multi-GPU caller all-reduces). That
+    format holds the variance of a channel with |mean|/std = 100 to no better than eps * (mean/std)^2 = 6e-4 relative, whatever
+    the kernel does: the test pins the loss to that bound, so that nobody reads the 1e-5 bar into this form."""
+    shape = (16, 8, 12, 12)
+    g = synth.rng(2, salt=8900)
+    x = synth.normal(g, shape, 50.0, 0.5)
+    c = shape[1]
+    xd = dev(x)
+    ws = torch.empty(capi.bn_train_workspace_bytes(shape[0], c, shape[2] * shape[3]), dtype=torch.uint8, device="cuda")
+    sums, saved, y = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty_like(xd)
+    capi.bn_train_stats(sums, xd, ws)
+    capi.bn_train_apply_act(y, saved, xd, dev(np.ones(c, np.float32)), dev(np.zeros(c, np.float32)), sums, x.size // c, 1e-5, [])
+    torch.cuda.synchronize()
+    xd64 = x.astype(np.float64)
+    inv_x = 1.0 / np.sqrt(xd64.var(axis=(0, 2, 3)) + 1e-5)
+    rel = np.abs(host(saved)[c:] - inv_x) / inv_x
+    assert rel.max() <= 6e-8 * (50.0 / 0.5) ** 2 * 1.5, rel.max()
+    assert_close(host(sums)[:c], xd64.sum(axis=(0, 2, 3)), "sum x")
+    assert_close(host(sums)[c:], (xd64 ** 2).sum(axis=(0, 2, 3)), "sum x^2")
