@@ -30,9 +30,10 @@ EPS = 1e-5
 BYTES_PER_ELEM_FWD = 8
 BYTES_PER_ELEM_BWD = 12
 METRIC = "fused BN+activation fwd/bwd achieved HBM GB/s"
-# DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/ (same shape)
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-NCU_TRAFFIC_BYTES = {"forward": 369928704, "backward": 693663488, "bwd_apply": 579759360, "bwd_stats": 414813184}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/ (same shape:
+# bn_train_chain_kernel_x256x256x28x28.md, bn_bwd_apply_kernel_cfg2_..., bn_bwd_stats_kernel_cfg2_..., bn_stats_..., bn_apply_channel_...)
+NCU_TRAFFIC_BYTES = {"forward": 364772352, "backward": 625849344, "bwd_apply": 580634624, "bwd_stats": 417700000, "stats": 210000000,
+                     "apply": 363633664}
 WORKLOAD = "bn_train+prelu+elu fwd+bwd, x[256,256,28,28] fp32 per GPU"
 KINK = 1e-5   # |bn output| below which an element is at PReLU's kink for the parity checks of dx
 
@@ -418,7 +419,17 @@ def main():
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE", help="a knob of the launch plans (nnf_set_tuning), for experiments")
     ap.add_argument("--sweep", action="store_true", help="time every kernel family at all five configurations (single GPU) instead of the benchmark step")
     ap.add_argument("--sweep-full", action="store_true", help="with --sweep: include the 16 GiB case of configuration 4")
+    ap.add_argument("--ceilings", action="store_true", help="run the stand-alone memory-ceiling program (copy, read-only, L2 re-reads, the two-read launch "
+                    "without arithmetic) and print its table")
     args = ap.parse_args()
+    if args.ceilings:
+        import subprocess
+        exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nnforge_b200", "nnf_ceilings")
+        if not os.path.exists(exe):
+            sys.exit("nnforge_b200/nnf_ceilings is missing: build it with `python -m nnforge_b200.build`")
+        peak, kind = measured_peaks()
+        print("rates against the %s copy bandwidth, %.1f GB/s" % (kind, peak), flush=True)
+        sys.exit(subprocess.call([exe, "%.1f" % peak]))
     if args.sweep:
         run_sweep(args)
         return
@@ -479,8 +490,14 @@ def main():
     current = {"ev": None}
     order = {"start": 0, "stats": 1, "allreduce_fwd": 2, "apply": 3, "bwd_stats": 4, "allreduce_bwd": 5, "bwd_apply": 6}
 
+    # One launch per direction: an event record between two launches costs about 2.5 us of device time (the step ran 229 us
+    # with no marks inside it, 239 us with four, 249 us with seven), so only every fourth step of the timed region is marked,
+    # at the start of its forward launch, between its two launches and at its end; the launches' durations are averages over
+    # the marked steps. The forms with several kernels per direction mark every phase of every step.
+    lean = single   # set again below, once it is known which exchange runs
+
     def on_phase(name):
-        if current["ev"] is not None:
+        if current["ev"] is not None and (not lean or name in ("start", "bwd_stats", "bwd_apply")):
             current["ev"][order[name]].record()
 
     exchange, exchange_name = None, "none"
@@ -503,6 +520,7 @@ def main():
                     exchange_name = "peer-memory stores + local sum (nnf_peer_exchange_sum)"
             except Exception as e:  # no symmetric memory on this machine: NCCL does the same sum
                 print("peer exchange unavailable (%s); using NCCL" % (e,), file=sys.stderr)
+    lean = single or getattr(exchange, "in_launch", False)
     layer = ShardedBatchNormAct(capi, C, EPS, acts, "cuda", on_phase=on_phase, exchange=exchange)
     grad_map = {"gamma": grads[0], "beta": grads[1], "slope": grads[2]}
 
@@ -538,8 +556,12 @@ def main():
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(args.steps)]
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
+    host_t0 = time.perf_counter()
+    # (not the first steps after the pause in front of the timed region: the clocks are still coming up)
+    marked = [k for k in range(args.steps) if not lean or args.steps <= 4 or k % 4 == 2]
     for k in range(args.steps):
-        step(evs[k])
+        step(evs[k] if k in marked else None)
+    host_enqueue_us = (time.perf_counter() - host_t0) * 1e6 / args.steps   # how long the host took to enqueue a step
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
@@ -560,8 +582,8 @@ def main():
         in_launch = False  # symmetric memory was not available: the NCCL sequence ran
         launches_per_step = 6
         phases = ("stats", "apply", "bwd_stats", "bwd_apply")
-    if single or in_launch:
-        idx = {"forward": (0, 3), "backward": (4, 6)} if in_launch else {"forward": (0, 1), "backward": (4, 6)}
+    if lean:
+        idx = None
         alg_bytes = {"forward": 8 * elems, "backward": 12 * elems}
         names = {"forward": "bn_train_chain_kernel<forward> (x in, y out; statistics and apply items in one launch)",
                  "backward": "bn_train_chain_kernel<backward> (x, dy in, dx out; statistics and apply items in one launch)"}
@@ -570,7 +592,13 @@ def main():
         alg_bytes = {"stats": 4 * elems, "apply": 8 * elems, "bwd_stats": 8 * elems, "bwd_apply": 12 * elems}
         names = {"stats": "bn_stats_kernel (x in)", "apply": "bn_act_kernel (x in, y out)", "bwd_stats": "bn_bwd_stats_kernel (x, dy in)",
                  "bwd_apply": "bn_bwd_apply_kernel (x, dy in, dx out)"}
-    kernel_ms = {name: sum(e[a].elapsed_time(e[b]) for e in evs) / len(evs) for name, (a, b) in idx.items()}
+    evs = [evs[k] for k in marked]
+    if idx is None:
+        # marks: [0] before the forward launch, [4] before the backward launch, [6] behind it
+        kernel_ms = {"forward": sum(e[0].elapsed_time(e[4]) for e in evs) / len(evs),
+                     "backward": sum(e[4].elapsed_time(e[6]) for e in evs) / len(evs)}
+    else:
+        kernel_ms = {name: sum(e[a].elapsed_time(e[b]) for e in evs) / len(evs) for name, (a, b) in idx.items()}
     peak, peak_kind = measured_peaks()
     dominant = max(kernel_ms, key=kernel_ms.get)
     achieved = alg_bytes[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
@@ -861,6 +889,7 @@ def main():
             "config": make_config(world), "exchange": exchange_name,
             "gelem_per_s": elems * world / (ms_step * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "host_enqueue_us_per_step": host_enqueue_us,
             "parity_check": parity, "configs": configs, "waits": waits, "tuning": args.tune,
         }
         result_out.write(json.dumps(line) + "\n")

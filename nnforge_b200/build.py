@@ -61,7 +61,20 @@ def build(verbose=False):
     if not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         subprocess.check_call([_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
     build_host()
+    build_ceilings()
     return LIB
+
+
+CEILINGS = os.path.join(HERE, "nnf_ceilings")
+
+
+def build_ceilings():
+    """The stand-alone program that measures the device's memory ceilings for this path's access patterns (bench.py --ceilings)."""
+    src = os.path.join(CSRC, "probe", "nnf_ceilings.cu")
+    if os.path.exists(CEILINGS) and os.path.getmtime(CEILINGS) >= os.path.getmtime(src):
+        return CEILINGS
+    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", src, "-o", CEILINGS])
+    return CEILINGS
 
 
 def build_host():

@@ -23,8 +23,9 @@
 //
 // Global memory reaches the threads through shared memory without occupying registers: a thread copies
 // its 16-byte pieces of the next sweeps with cp.async into slots that only it reads back (no barrier),
-// two or three sweeps ahead. A sweep is as many whole planes of the channel (consecutive entries) as fill
-// the CTA's 1024 vector slots; a thread's slot offsets inside a sweep never change, so the loop has no
+// three sweeps ahead. A sweep is as many whole planes of the channel (consecutive entries) as fill
+// the CTA's vector slots (1024 forward; 512 backward, where two tensors are staged, so that four CTAs
+// fit an SM in both directions); a thread's slot offsets inside a sweep never change, so the loop has no
 // index division.
 //
 // Batch-sharded form (one process per GPU, the same launch on every GPU): F(channel) folds this rank's
@@ -47,15 +48,6 @@ namespace nnf
 
 	namespace
 	{
-#ifndef NNF_CHAIN_LOADS_FWD
-#define NNF_CHAIN_LOADS_FWD 4
-#endif
-#ifndef NNF_CHAIN_LOADS_BWD
-#define NNF_CHAIN_LOADS_BWD 2
-#endif
-#ifndef NNF_CHAIN_MIN_CTAS
-#define NNF_CHAIN_MIN_CTAS 5
-#endif
 		constexpr int kChainThreads = 256;
 		constexpr int kChainMaxSplit = 64;     // S items per channel (sizes the partial sums)
 		constexpr uint32_t kChainPollLimit = 1u << 22; // rounds of an A item's wait (about half a microsecond each)
@@ -870,6 +862,12 @@ namespace nnf
 						acc[k][j] = 0.0F;
 				if constexpr (!BWD)
 				{
+					// the sums are taken around each channel's first element (undone in double where they are folded), so that a
+					// mean far from zero costs no digits of the variance
+					float shift[4];
+					#pragma unroll
+					for (int j = 0; j < 4; ++j)
+						shift[j] = __ldg(p.x + size_t(ch0 + local[j]) * p.hw);
 					const float4 * bx = reinterpret_cast<const float4 *>(p.x) + base4;
 					for (uint32_t e = e0; e < e1; e += U)
 					{
@@ -877,16 +875,17 @@ namespace nnf
 						#pragma unroll
 						for (int u = 0; u < U; ++u)
 						{
-							a[u] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+							a[u] = make_float4(shift[0], shift[1], shift[2], shift[3]);
 							if (active && e + u < e1)
 								a[u] = __ldg(bx + size_t(e + u - e0) * stride4); // default policy: stays in L2
 						}
 						#pragma unroll
 						for (int u = 0; u < U; ++u)
 						{
-							acc[0][0] += a[u].x; acc[0][1] += a[u].y; acc[0][2] += a[u].z; acc[0][3] += a[u].w;
-							acc[1][0] = fmaf(a[u].x, a[u].x, acc[1][0]); acc[1][1] = fmaf(a[u].y, a[u].y, acc[1][1]);
-							acc[1][2] = fmaf(a[u].z, a[u].z, acc[1][2]); acc[1][3] = fmaf(a[u].w, a[u].w, acc[1][3]);
+							const float v0 = a[u].x - shift[0], v1 = a[u].y - shift[1], v2 = a[u].z - shift[2], v3 = a[u].w - shift[3];
+							acc[0][0] += v0; acc[0][1] += v1; acc[0][2] += v2; acc[0][3] += v3;
+							acc[1][0] = fmaf(v0, v0, acc[1][0]); acc[1][1] = fmaf(v1, v1, acc[1][1]);
+							acc[1][2] = fmaf(v2, v2, acc[1][2]); acc[1][3] = fmaf(v3, v3, acc[1][3]);
 						}
 					}
 				}
@@ -1020,6 +1019,14 @@ namespace nnf
 					}
 					if (lc < channels)
 					{
+						if constexpr (!BWD)
+						{
+							// back to {sum x, sum x^2}, the message the ranks exchange
+							const double sh = double(__ldg(p.x + size_t(ch) * p.hw));
+							const double s0 = t[0];
+							t[0] = s0 + p.count * sh;
+							t[1] = t[1] + 2.0 * sh * s0 + p.count * sh * sh;
+						}
 						const float m0 = float(t[0]), m1 = float(t[1]);
 						if (lane == 0)
 						{
@@ -1205,10 +1212,13 @@ namespace nnf
 				{
 					if constexpr (!BWD)
 					{
-						const double m = t[0] / p.count;
-						double var = t[1] / p.count - m * m;
+						const double sh = double(__ldg(p.x + size_t(ch) * p.hw));
+						const double ms = t[0] / p.count;       // mean of x - shift
+						double var = t[1] / p.count - ms * ms;
 						var = var < 0.0 ? 0.0 : var;
-						const float fmean = float(m);
+						const float fmean = float(sh + ms);
+						t[1] = t[1] + 2.0 * sh * t[0] + p.count * sh * sh;   // {sum x, sum x^2} as the other entry points define them
+						t[0] = t[0] + p.count * sh;
 						const float finv = float(1.0 / sqrt(var + double(p.eps)));
 						const float mult = __fmul_rn(__ldg(p.gamma + ch), finv);
 						s_const[0][lc] = mult;

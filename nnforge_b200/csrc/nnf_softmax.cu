@@ -438,7 +438,12 @@ namespace nnf
 					const int grid = (int)(blocks_needed < int64_t(sm_count()) * 64 ? blocks_needed : int64_t(sm_count()) * 64);
 					if ((c & 3) == 0 && aligned16(out) && aligned16(in0) && (!in1 || aligned16(in1)))
 					{
-#define NNF_ROWS4(VPL) softmax_rows_warp4_kernel<VPL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
+						// a few hundred rows (x[256,1000]: 256 warps) are a launch-latency case: one or two warps per CTA put every
+						// row on an SM of its own instead of eight rows on each of 32 SMs
+						const int threads4 = rows <= int64_t(sm_count()) * 2 ? 32 : (rows <= int64_t(sm_count()) * 8 ? 64 : 256);
+						const int64_t blocks4 = div_up(rows, threads4 / 32);
+						const int grid4 = (int)(blocks4 < int64_t(sm_count()) * 64 ? blocks4 : int64_t(sm_count()) * 64);
+#define NNF_ROWS4(VPL) softmax_rows_warp4_kernel<VPL, BACKWARD><<<grid4, threads4, 0, s>>>(out, in0, in1, rows, (int)c, add)
 						if (c <= 128) NNF_ROWS4(1);
 						else if (c <= 256) NNF_ROWS4(2);
 						else if (c <= 512) NNF_ROWS4(4);

@@ -136,6 +136,7 @@ class ShardedBatchNormAct:
         self.workspaces = {}
         self._report_copied = {}   # direction -> event after which that direction's workspace may be cleared again
         self._side = None
+        self._shape_ok = {}
 
     def _ws(self, x, which="forward"):
         n, c = x.shape[0], x.shape[1]
@@ -217,8 +218,11 @@ class ShardedBatchNormAct:
 
     def _in_launch_ok(self, x, hw):
         """Shapes the one-launch sharded entry points take (the library decides; planes of whole float4s always are)."""
-        supported = getattr(self.k, "bn_train_sharded_supported", None)
-        return supported(x.shape[0], x.shape[1], hw) if supported is not None else hw % 4 == 0
+        key = (x.shape[0], x.shape[1], hw)
+        if key not in self._shape_ok:
+            supported = getattr(self.k, "bn_train_sharded_supported", None)
+            self._shape_ok[key] = bool(supported(*key)) if supported is not None else hw % 4 == 0
+        return self._shape_ok[key]
 
     def forward(self, y, x, gamma, beta, global_entries=None):
         m = self.count_total(x, global_entries)
