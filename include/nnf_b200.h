@@ -415,6 +415,19 @@ NNF_API int nnf_softmax_nll_fwd(nnf_stream_t stream, float * probs, float * err,
 NNF_API int nnf_softmax_nll_bwd(nnf_stream_t stream, float * dlogits, const float * probs, const float * targets, const float * mask,
 	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination);
 
+/* cross_entropy_layer, the loss behind sigmoid outputs (replaces cross_entropy_layer_tester_cuda / _updater_cuda,
+ * nnforge/cuda/cross_entropy_layer_*_cuda.cu; semantics of nnforge/plain/cross_entropy_layer_updater_plain.cpp:60-101, 131-173):
+ *   forward : err = scale*mask * sum over channels of ( t > 0 ? -t*logf(max(p, 1e-20)) : 0 ) + ( t < 1 ? -(1-t)*logf(max(1-p, 1e-20)) : 0 )
+ *   backward: dpredicted = ( (t > 0 ? t/max(p, 1e-20) : 0) - (t < 1 ? (1-t)/max(1-p, 1e-20) : 0) ) * scale*mask
+ * Layouts as for the negative log likelihood. Two remarks on the reference: its plain TESTER takes the mask INSTEAD of the scale
+ * when a mask is given (cross_entropy_layer_tester_plain.cpp:72-74) - a tester adapter passes scale = 1 then; and its plain
+ * updater computes this gradient into a variable that shadows the stored one and so writes zeros (:150-168) - the value here is
+ * the one the expression in that file and the CUDA backend (cross_entropy_layer_updater_cuda.cu:115-183) define. */
+NNF_API int nnf_cross_entropy_fwd(nnf_stream_t stream, float * err, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw);
+NNF_API int nnf_cross_entropy_bwd(nnf_stream_t stream, float * dpredicted, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination);
+
 /* accuracy_layer (replaces accuracy_layer_tester_cuda / _updater_cuda, nnforge/cuda/accuracy_layer_tester_cuda.cu; semantics of
  * nnforge/plain/accuracy_layer_tester_plain.cpp:64-110): per (entry, pixel) the actual class is the first channel with the
  * largest target; rank = number of channels whose prediction is larger than that class's, or equal with a smaller index.

@@ -99,6 +99,8 @@ _SIGNATURES = {
     "nnf_bn_add_relu_avgpool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _I, _I, _F]),
     "nnf_nll_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
+    "nnf_cross_entropy_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
+    "nnf_cross_entropy_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_softmax_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_bn_train_mailbox_bytes": (_SZ, [_I64]),
@@ -419,6 +421,16 @@ def nll_fwd(err, predicted, targets, mask=None, scale=1.0, stream=None):
 def nll_bwd(dpredicted, predicted, targets, mask=None, scale=1.0, add_to_destination=False, stream=None):
     n, c, hw = _nchw(predicted)
     _check(lib.nnf_nll_bwd(_stream(stream), _ptr(dpredicted), _ptr(predicted), _ptr(targets), _ptr(mask), scale, n, c, hw, int(add_to_destination)))
+
+
+def cross_entropy_fwd(err, predicted, targets, mask=None, scale=1.0, stream=None):
+    n, c, hw = _nchw(predicted)
+    _check(lib.nnf_cross_entropy_fwd(_stream(stream), _ptr(err), _ptr(predicted), _ptr(targets), _ptr(mask), scale, n, c, hw))
+
+
+def cross_entropy_bwd(dpredicted, predicted, targets, mask=None, scale=1.0, add_to_destination=False, stream=None):
+    n, c, hw = _nchw(predicted)
+    _check(lib.nnf_cross_entropy_bwd(_stream(stream), _ptr(dpredicted), _ptr(predicted), _ptr(targets), _ptr(mask), scale, n, c, hw, int(add_to_destination)))
 
 
 def softmax_nll_fwd(probs, err, logits, targets, mask=None, scale=1.0, stream=None):

@@ -468,7 +468,7 @@ namespace
 			a.insert(layer_action(layer_action::backward_data_and_weights));
 		else if (t == "Accuracy")
 			;
-		else if (t == "NegativeLogLikelihood")
+		else if (t == "NegativeLogLikelihood" || t == "CrossEntropy")
 			a.insert(layer_action(layer_action::backward_data, 0));
 		else
 		{

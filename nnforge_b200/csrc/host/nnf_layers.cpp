@@ -104,6 +104,25 @@ namespace nnf_b200
 			}
 		};
 
+		// cross_entropy_layer: inputs = predicted, actual[, scale mask]; output = one value per (entry, pixel)
+		// (nnforge/cuda/cross_entropy_layer_tester_cuda.cu). The plain tester takes the mask INSTEAD of the scale when a mask is
+		// given (nnforge/plain/cross_entropy_layer_tester_plain.cpp:72-74): a scale of 1 reproduces it.
+		class cross_entropy_layer_tester_b200 : public layer_tester_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("cross_entropy_layer needs the predicted and the actual values");
+				const bool masked = input_buffers.size() > 2;
+				check(nnf_cross_entropy_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), masked ? f(input_buffers[2]) : nullptr,
+					masked ? 1.0F : layer_schema->scale, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
+		};
+
 		// accuracy_layer: inputs = predicted, actual[, mask]; output = top_n + 1 planes per entry (nnforge/cuda/accuracy_layer_tester_cuda.cu)
 		class accuracy_layer_tester_b200 : public layer_tester_b200
 		{
@@ -287,6 +306,38 @@ namespace nnf_b200
 				if (input_index != 0)
 					throw neural_network_exception("negative_log_likelihood_layer_updater cannot do backward propagation for targets or the scale mask");
 				check(nnf_nll_bwd(stream_id, f(input_errors_buffer), f(input_neurons_buffers.at(0)), f(input_neurons_buffers.at(1)),
+					input_neurons_buffers.size() > 2 ? f(input_neurons_buffers[2]) : nullptr, layer_schema->scale, entry_count,
+					input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0));
+			}
+			bool is_backward_data_dependent_on_input_buffer(unsigned int, unsigned int) const override { return true; }
+			bool is_backward_data_dependent_on_output_buffer(unsigned int) const override { return false; }
+		};
+
+		// (nnforge/cuda/cross_entropy_layer_updater_cuda.cu; the layer is a loss: backward reads no output errors)
+		class cross_entropy_layer_updater_b200 : public layer_updater_b200
+		{
+		public:
+			void enqueue_forward_propagation(cudaStream_t stream_id, device_buffer::ptr output_buffer, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>& input_buffers, const std::vector<device_buffer::const_ptr>&,
+				device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, device_buffer::ptr, unsigned int entry_count) override
+			{
+				if (input_buffers.size() < 2)
+					throw neural_network_exception("cross_entropy_layer needs the predicted and the actual values");
+				check(nnf_cross_entropy_fwd(stream_id, f(output_buffer), f(input_buffers[0]), f(input_buffers[1]), input_buffers.size() > 2 ? f(input_buffers[2]) : nullptr,
+					layer_schema->scale, entry_count, input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map));
+			}
+			void enqueue_backward_data_propagation(cudaStream_t stream_id, unsigned int input_index, device_buffer::ptr input_errors_buffer,
+				device_buffer::const_ptr, const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>&,
+				const std::vector<device_buffer::const_ptr>&, const std::vector<device_buffer::const_ptr>& input_neurons_buffers, device_buffer::const_ptr,
+				const std::vector<device_buffer::const_ptr>&, device_buffer::ptr, device_buffer::ptr, device_buffer::const_ptr, device_buffer::const_ptr,
+				bool add_update_to_destination, unsigned int entry_count) override
+			{
+				if (input_index == 1)
+					throw neural_network_exception("cross_entropy_layer_updater cannot do backward propagation for targets");
+				if (input_index == 2)
+					throw neural_network_exception("cross_entropy_layer_updater cannot do backward propagation for scale mask");
+				check(nnf_cross_entropy_bwd(stream_id, f(input_errors_buffer), f(input_neurons_buffers.at(0)), f(input_neurons_buffers.at(1)),
 					input_neurons_buffers.size() > 2 ? f(input_neurons_buffers[2]) : nullptr, layer_schema->scale, entry_count,
 					input_configuration_specific_list[0].feature_map_count, output_elem_count_per_feature_map, add_update_to_destination ? 1 : 0));
 			}
@@ -737,7 +788,7 @@ namespace nnf_b200
 
 	std::vector<std::string> layer_factory_b200::get_type_names() const
 	{
-		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood", "Accuracy", "AverageSubsampling"};
+		return {"BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax", "Add", "MaxSubsampling", "NegativeLogLikelihood", "CrossEntropy", "Accuracy", "AverageSubsampling"};
 	}
 
 	layer_tester_b200::ptr layer_factory_b200::create_tester(layer::const_ptr l, const std::vector<layer_configuration_specific>& in,
@@ -750,6 +801,7 @@ namespace nnf_b200
 		else if (n == "Add") t.reset(new add_layer_tester_b200());
 		else if (n == "Softmax") t.reset(new softmax_layer_tester_b200());
 		else if (n == "NegativeLogLikelihood") t.reset(new negative_log_likelihood_layer_tester_b200());
+		else if (n == "CrossEntropy") t.reset(new cross_entropy_layer_tester_b200());
 		else if (n == "Accuracy") t.reset(new accuracy_layer_tester_b200());
 		else if (n == "AverageSubsampling") t.reset(new average_subsampling_layer_tester_b200());
 		else if (n == "MaxSubsampling") t.reset(new max_subsampling_layer_tester_b200());
@@ -768,6 +820,7 @@ namespace nnf_b200
 		else if (n == "Add") u.reset(new add_layer_updater_b200());
 		else if (n == "Softmax") u.reset(new softmax_layer_updater_b200());
 		else if (n == "NegativeLogLikelihood") u.reset(new negative_log_likelihood_layer_updater_b200());
+		else if (n == "CrossEntropy") u.reset(new cross_entropy_layer_updater_b200());
 		else if (n == "Accuracy") u.reset(new accuracy_layer_updater_b200());
 		else if (n == "AverageSubsampling") u.reset(new average_subsampling_layer_updater_b200());
 		else if (n == "MaxSubsampling") u.reset(new max_subsampling_layer_updater_b200());
@@ -779,8 +832,8 @@ namespace nnf_b200
 	layer_configuration_specific get_output_layer_configuration_specific(const layer& l, const std::vector<layer_configuration_specific>& inputs)
 	{
 		layer_configuration_specific res = inputs.at(0);
-		if (l.type_name == "NegativeLogLikelihood")
-			res.feature_map_count = 1; // negative_log_likelihood_layer.cpp:66
+		if (l.type_name == "NegativeLogLikelihood" || l.type_name == "CrossEntropy")
+			res.feature_map_count = 1; // negative_log_likelihood_layer.cpp:66, cross_entropy_layer.cpp:62
 		if (l.type_name == "Accuracy")
 			res.feature_map_count = l.top_n + 1; // accuracy_layer.cpp:62
 		if (l.type_name == "AverageSubsampling")
@@ -902,7 +955,7 @@ NNFH_API void * nnfh_create(const char * type_name, int updater, const float * p
 		if (l.type_name == "ReLU") l.negative_slope = params[0];
 		if (l.type_name == "TanH") { l.scale = params[0]; l.steepness = params[1]; }
 		if (l.type_name == "Add") l.alpha = params[0];
-		if (l.type_name == "NegativeLogLikelihood") l.scale = params[0];
+		if (l.type_name == "NegativeLogLikelihood" || l.type_name == "CrossEntropy") l.scale = params[0];
 		if (l.type_name == "Accuracy") l.top_n = (unsigned int)params[0];
 		if (l.type_name == "BatchNorm") l.epsilon = params[0];
 		if (l.type_name == "AverageSubsampling")

@@ -3,7 +3,8 @@
 // (nnforge/cuda/layer_tester_cuda.h:47-72), a `layer_updater_b200` what layer_updater_cuda does
 // (nnforge/cuda/layer_updater_cuda.h:50-169), and both are created through string-keyed factories by
 // the reference's layer type names ("BatchNorm", "ReLU", "PReLU", "ELU", "TanH", "Sigmoid", "Softmax",
-// "Add", "MaxSubsampling"; nnforge/cuda/layer_testing_schema_factory.cpp:36-44). Method names, argument
+// "Add", "MaxSubsampling", and their neighbours "AverageSubsampling", "NegativeLogLikelihood", "CrossEntropy", "Accuracy";
+// nnforge/cuda/layer_testing_schema_factory.cpp:36-44). Method names, argument
 // order and meaning, buffer-plan queries and the error convention (exceptions derived from
 // std::runtime_error thrown on the calling host thread) are the reference's, so an nnForge scheduler
 // can drive these objects the way it drives its own; the arithmetic behind them is libnnf_b200.
@@ -73,7 +74,7 @@ namespace nnf_b200
 		std::string instance_name;                  // layer::instance_name
 		float epsilon = 2.0e-5F;                    // BatchNorm (default_batch_normalization_epsilon, nnforge/batch_norm_layer.cpp:28)
 		float negative_slope = 0.0F;                // ReLU
-		float scale = 1.0F, steepness = 1.0F;       // TanH; scale also NegativeLogLikelihood
+		float scale = 1.0F, steepness = 1.0F;       // TanH; scale also NegativeLogLikelihood, CrossEntropy
 		float alpha = 1.0F;                         // Add; AverageSubsampling: the effective alpha
 		unsigned int top_n = 1;                     // Accuracy
 		std::vector<unsigned int> subsampling_sizes; // MaxSubsampling, AverageSubsampling

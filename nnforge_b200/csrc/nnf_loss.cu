@@ -79,7 +79,49 @@ namespace nnf
 			fastdiv hwdiv;
 		};
 
-		enum { kFusedFwd = 0, kFusedBwd = 1, kLossFwd = 2, kLossBwd = 3 };
+		enum { kFusedFwd = 0, kFusedBwd = 1, kLossFwd = 2, kLossBwd = 3, kCeFwd = 4, kCeBwd = 5 };
+
+		// cross entropy (nnforge/plain/cross_entropy_layer_tester_plain.cpp:79-92): two terms per element, each subtracted on its own
+		__device__ __forceinline__ float ce_accumulate(float e, float p, float t)
+		{
+			if (t > 0.0F)
+				e = __fsub_rn(e, __fmul_rn(t, __logf(loss_ref_max(p, kLossFloor))));
+			if (t < 1.0F)
+				e = __fsub_rn(e, __fmul_rn(__fsub_rn(1.0F, t), __logf(loss_ref_max(__fsub_rn(1.0F, p), kLossFloor))));
+			return e;
+		}
+
+		// the gradient cross_entropy_layer_updater_plain.cpp:146-166 computes (and, through a shadowed variable, fails to store;
+		// the CUDA backend stores it, cross_entropy_layer_updater_cuda.cu:115-183)
+		__device__ __forceinline__ float ce_grad(float p, float t, float total_scale)
+		{
+			float g = 0.0F;
+			if (total_scale != 0.0F)
+			{
+				if (t > 0.0F)
+					g = __fdiv_rn(t, loss_ref_max(p, kLossFloor));
+				if (t < 1.0F)
+					g = __fsub_rn(g, __fdiv_rn(__fsub_rn(1.0F, t), loss_ref_max(__fsub_rn(1.0F, p), kLossFloor)));
+				g = __fmul_rn(g, total_scale);
+			}
+			return g;
+		}
+
+		template <int MODE>
+		__device__ __forceinline__ float loss_accumulate(float e, float p, float t)
+		{
+			if (MODE == kCeFwd)
+				return ce_accumulate(e, p, t);
+			return __fsub_rn(e, nll_term(p, t));
+		}
+
+		template <int MODE>
+		__device__ __forceinline__ float loss_gradient(float p, float t, float total_scale)
+		{
+			if (MODE == kCeBwd)
+				return ce_grad(p, t, total_scale);
+			return nll_grad(p, t, total_scale);
+		}
 
 		// ---- H*W == 1: warp per row. VPL > 0: the row is kept in registers as VPL float4 per lane (C % 4 == 0,
 		// aligned rows); VPL == 0: scalar accesses, the row is read again by every pass --------------------
@@ -140,7 +182,7 @@ namespace nnf
 								st_stream(out4 + (j * 32 + lane), v[j]);
 							}
 					}
-					if (MODE == kFusedFwd || MODE == kLossFwd)
+					if (MODE == kFusedFwd || MODE == kLossFwd || MODE == kCeFwd)
 					{
 						float e = 0.0F;
 						if (total_scale != 0.0F)
@@ -149,8 +191,8 @@ namespace nnf
 							for (int j = 0; j < N; ++j)
 								if (j * 32 + lane < c4)
 								{
-									e = __fsub_rn(e, nll_term(v[j].x, t[j].x)); e = __fsub_rn(e, nll_term(v[j].y, t[j].y));
-									e = __fsub_rn(e, nll_term(v[j].z, t[j].z)); e = __fsub_rn(e, nll_term(v[j].w, t[j].w));
+									e = loss_accumulate<MODE>(e, v[j].x, t[j].x); e = loss_accumulate<MODE>(e, v[j].y, t[j].y);
+									e = loss_accumulate<MODE>(e, v[j].z, t[j].z); e = loss_accumulate<MODE>(e, v[j].w, t[j].w);
 								}
 						}
 						e = loss_warp_sum(e);
@@ -165,8 +207,8 @@ namespace nnf
 						#pragma unroll
 						for (int j = 0; j < N; ++j)
 						{
-							g[j] = make_float4(nll_grad(v[j].x, t[j].x, total_scale), nll_grad(v[j].y, t[j].y, total_scale),
-								nll_grad(v[j].z, t[j].z, total_scale), nll_grad(v[j].w, t[j].w, total_scale));
+							g[j] = make_float4(loss_gradient<MODE>(v[j].x, t[j].x, total_scale), loss_gradient<MODE>(v[j].y, t[j].y, total_scale),
+								loss_gradient<MODE>(v[j].z, t[j].z, total_scale), loss_gradient<MODE>(v[j].w, t[j].w, total_scale));
 							if (MODE == kFusedBwd)
 								s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fmul_rn(g[j].x, v[j].x), __fmul_rn(g[j].y, v[j].y)),
 									__fadd_rn(__fmul_rn(g[j].z, v[j].z), __fmul_rn(g[j].w, v[j].w))));
@@ -208,7 +250,7 @@ namespace nnf
 						s = loss_warp_sum(s);
 						mult = __fdiv_rn(1.0F, s);
 					}
-					if (MODE == kFusedFwd || MODE == kLossFwd)
+					if (MODE == kFusedFwd || MODE == kLossFwd || MODE == kCeFwd)
 					{
 						float e = 0.0F;
 						for (int f = lane; f < c; f += 32)
@@ -220,7 +262,7 @@ namespace nnf
 								out[f] = pr;
 							}
 							if (total_scale != 0.0F)
-								e = __fsub_rn(e, nll_term(pr, tg[f]));
+								e = loss_accumulate<MODE>(e, pr, tg[f]);
 						}
 						e = loss_warp_sum(e);
 						if (lane == 0)
@@ -232,12 +274,12 @@ namespace nnf
 						if (MODE == kFusedBwd)
 						{
 							for (int f = lane; f < c; f += 32)
-								s = __fadd_rn(s, __fmul_rn(nll_grad(in[f], tg[f], total_scale), in[f]));
+								s = __fadd_rn(s, __fmul_rn(loss_gradient<MODE>(in[f], tg[f], total_scale), in[f]));
 							s = loss_warp_sum(s);
 						}
 						for (int f = lane; f < c; f += 32)
 						{
-							const float g = nll_grad(in[f], tg[f], total_scale);
+							const float g = loss_gradient<MODE>(in[f], tg[f], total_scale);
 							const float r = MODE == kFusedBwd ? __fmul_rn(in[f], __fsub_rn(g, s)) : g;
 							out[f] = p.add ? __fadd_rn(out[f], r) : r;
 						}
@@ -278,7 +320,7 @@ namespace nnf
 						t[f] = f < c ? ld_stream(tg + int64_t(f) * hw) : 0.0F;
 					}
 				}
-				if (MODE == kFusedFwd || MODE == kLossFwd)
+				if (MODE == kFusedFwd || MODE == kLossFwd || MODE == kCeFwd)
 				{
 					float m = kLossMaxSeed, mult = 1.0F;
 					if (MODE == kFusedFwd)
@@ -321,7 +363,7 @@ namespace nnf
 									out[int64_t(f) * hw] = pr;
 								}
 								if (total_scale != 0.0F)
-									e = __fsub_rn(e, nll_term(pr, t[f]));
+									e = loss_accumulate<MODE>(e, pr, t[f]);
 							}
 					}
 					else
@@ -335,7 +377,7 @@ namespace nnf
 								out[int64_t(f) * hw] = pr;
 							}
 							if (total_scale != 0.0F)
-								e = __fsub_rn(e, nll_term(pr, target(f)));
+								e = loss_accumulate<MODE>(e, pr, target(f));
 						}
 					}
 					p.err[q] = total_scale != 0.0F ? __fmul_rn(e, total_scale) : 0.0F;
@@ -350,14 +392,14 @@ namespace nnf
 						for (int f = 0; f < N; ++f)
 							if (f < c)
 							{
-								t[f] = nll_grad(v[f], t[f], total_scale);
+								t[f] = loss_gradient<MODE>(v[f], t[f], total_scale);
 								if (MODE == kFusedBwd)
 									s = __fadd_rn(s, __fmul_rn(t[f], v[f]));
 							}
 					}
 					else if (MODE == kFusedBwd)
 						for (int f = 0; f < c; ++f)
-							s = __fadd_rn(s, __fmul_rn(nll_grad(value(f), target(f), total_scale), value(f)));
+							s = __fadd_rn(s, __fmul_rn(loss_gradient<MODE>(value(f), target(f), total_scale), value(f)));
 					auto emit = [&](int f, float pr, float g)
 					{
 						const float r = MODE == kFusedBwd ? __fmul_rn(pr, __fsub_rn(g, s)) : g;
@@ -373,7 +415,7 @@ namespace nnf
 					}
 					else
 						for (int f = 0; f < c; ++f)
-							emit(f, value(f), nll_grad(value(f), target(f), total_scale));
+							emit(f, value(f), loss_gradient<MODE>(value(f), target(f), total_scale));
 				}
 			}
 		}
@@ -386,8 +428,8 @@ namespace nnf
 				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: bad extents n=%lld c=%lld hw=%lld", who, (long long)n, (long long)c, (long long)hw);
 			if (n == 0)
 				return NNF_OK;
-			const bool forward = MODE == kFusedFwd || MODE == kLossFwd;
-			if (!in || !targets || (forward && !err) || (MODE != kLossFwd && !out))
+			const bool forward = MODE == kFusedFwd || MODE == kLossFwd || MODE == kCeFwd;
+			if (!in || !targets || (forward && !err) || (MODE != kLossFwd && MODE != kCeFwd && !out))
 				return set_error(NNF_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
 			if (c > 0x7fffffff || hw > 0x7fffffff)
 				return set_error(NNF_ERR_UNSUPPORTED, "%s: extent too large", who);
@@ -630,6 +672,18 @@ extern "C" int nnf_nll_fwd(nnf_stream_t stream, float * err, const float * predi
 	float scale, int64_t n, int64_t c, int64_t hw)
 {
 	return run_loss<kLossFwd>((cudaStream_t)stream, "nnf_nll_fwd", nullptr, err, predicted, targets, mask, scale, n, c, hw, 0);
+}
+
+extern "C" int nnf_cross_entropy_fwd(nnf_stream_t stream, float * err, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw)
+{
+	return run_loss<kCeFwd>((cudaStream_t)stream, "nnf_cross_entropy_fwd", nullptr, err, predicted, targets, mask, scale, n, c, hw, 0);
+}
+
+extern "C" int nnf_cross_entropy_bwd(nnf_stream_t stream, float * dpredicted, const float * predicted, const float * targets, const float * mask,
+	float scale, int64_t n, int64_t c, int64_t hw, int add_to_destination)
+{
+	return run_loss<kCeBwd>((cudaStream_t)stream, "nnf_cross_entropy_bwd", dpredicted, nullptr, predicted, targets, mask, scale, n, c, hw, add_to_destination ? 1 : 0);
 }
 
 extern "C" int nnf_nll_bwd(nnf_stream_t stream, float * dpredicted, const float * predicted, const float * targets, const float * mask,

@@ -190,6 +190,30 @@ class Oracle:
         self.lib.orc_nll_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), _i64(n), _i64(c), _i64(hw), int(add))
         return out
 
+    # ---- cross entropy ------------------------------------------------------------------------------
+    def cross_entropy_fwd(self, predicted, actual, mask=None, scale=1.0, mask_replaces_scale=False):
+        """predicted, actual [N,C,H,W]; mask [N,1,H,W] or None -> err [N,1,H,W]. mask_replaces_scale: the reference tester's
+        total scale (the mask alone) instead of the updater's (scale * mask)."""
+        predicted, actual = _c(predicted), _c(actual)
+        n, c = predicted.shape[0], predicted.shape[1]
+        hw = predicted.size // max(n * c, 1)
+        err = np.empty((n, 1) + predicted.shape[2:], np.float32)
+        m = _c(mask) if mask is not None else None
+        self.lib.orc_cross_entropy_fwd(_fp(err), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), _i64(n), _i64(c),
+                                       _i64(hw), int(mask_replaces_scale))
+        return err
+
+    def cross_entropy_bwd(self, predicted, actual, mask=None, scale=1.0, dx=None):
+        predicted, actual = _c(predicted), _c(actual)
+        n, c = predicted.shape[0], predicted.shape[1]
+        hw = predicted.size // max(n * c, 1)
+        add = dx is not None
+        out = _c(dx).copy() if add else np.empty_like(predicted)
+        m = _c(mask) if mask is not None else None
+        self.lib.orc_cross_entropy_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), _i64(n), _i64(c),
+                                       _i64(hw), int(add))
+        return out
+
     def accuracy_fwd(self, predicted, actual, mask=None, top_n=1):
         """predicted, actual [N,C,H,W]; mask [N,1,H,W] or None -> [N,top_n+1,H,W]."""
         predicted, actual = _c(predicted), _c(actual)
@@ -349,7 +373,7 @@ class Reference:
         for fn in ("ref_bn_infer", "ref_relu_fwd", "ref_relu_bwd", "ref_prelu_fwd", "ref_prelu_bwd_data", "ref_prelu_bwd_weights",
                    "ref_elu_fwd", "ref_elu_bwd", "ref_tanh_fwd", "ref_tanh_bwd", "ref_sigmoid_fwd", "ref_sigmoid_bwd", "ref_softmax_fwd",
                    "ref_softmax_upd_fwd", "ref_softmax_bwd", "ref_add_fwd", "ref_add_bwd", "ref_maxpool_fwd", "ref_maxpool_tester_fwd",
-                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_accuracy_fwd", "ref_avgpool_fwd", "ref_avgpool_bwd", "ref_feature_map_stats"):
+                   "ref_maxpool_bwd", "ref_nll_fwd", "ref_nll_bwd", "ref_cross_entropy_fwd", "ref_cross_entropy_bwd", "ref_accuracy_fwd", "ref_avgpool_fwd", "ref_avgpool_bwd", "ref_feature_map_stats"):
             getattr(self.lib, fn).restype = ct.c_double
 
     def _check(self, seconds):
@@ -452,6 +476,25 @@ class Reference:
         m = _c(mask) if mask is not None else None
         s = self.lib.ref_nll_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), *d, int(dx is not None),
                                  self.threads)
+        return out, self._check(s)
+
+    def cross_entropy_fwd(self, predicted, actual, mask=None, scale=1.0, updater=False, reps=1):
+        predicted, d = self._dims(predicted)
+        actual = _c(actual)
+        err = np.empty((predicted.shape[0], 1) + predicted.shape[2:], np.float32)
+        m = _c(mask) if mask is not None else None
+        s = self.lib.ref_cross_entropy_fwd(_fp(err), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), *d, int(updater),
+                                           self.threads, reps)
+        return err, self._check(s)
+
+    def cross_entropy_bwd(self, predicted, actual, mask=None, scale=1.0, dx=None):
+        """The plain backend's backward action as it is: it stores zeros (see orc_cross_entropy_bwd)."""
+        predicted, d = self._dims(predicted)
+        actual = _c(actual)
+        out = _c(dx).copy() if dx is not None else np.empty_like(predicted)
+        m = _c(mask) if mask is not None else None
+        s = self.lib.ref_cross_entropy_bwd(_fp(out), _fp(predicted), _fp(actual), _fp(m) if m is not None else None, ct.c_float(scale), *d,
+                                           int(dx is not None), self.threads)
         return out, self._check(s)
 
     def accuracy_fwd(self, predicted, actual, mask=None, top_n=1, updater=False, reps=1):

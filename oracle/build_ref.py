@@ -34,13 +34,14 @@ PLAIN = (
     + ["plain/%s_layer_tester_plain.cpp" % n for n in LAYERS[1:]]
     + ["plain/%s_layer_updater_plain.cpp" % n for n in LAYERS[1:]]
     + ["plain/negative_log_likelihood_layer_tester_plain.cpp", "plain/negative_log_likelihood_layer_updater_plain.cpp",
+       "plain/cross_entropy_layer_tester_plain.cpp", "plain/cross_entropy_layer_updater_plain.cpp",
        "plain/accuracy_layer_tester_plain.cpp", "plain/accuracy_layer_updater_plain.cpp",
        "plain/average_subsampling_layer_tester_plain.cpp", "plain/average_subsampling_layer_updater_plain.cpp"]
     + ["plain/layer_tester_plain.cpp", "plain/layer_updater_plain.cpp", "plain/plain_buffer.cpp",
        "plain/plain_running_configuration.cpp"]
 )
 CORE = (
-    ["%s_layer.cpp" % n for n in LAYERS + ["negative_log_likelihood", "accuracy", "average_subsampling"]]
+    ["%s_layer.cpp" % n for n in LAYERS + ["negative_log_likelihood", "cross_entropy", "accuracy", "average_subsampling"]]
     + ["layer.cpp", "layer_configuration_specific.cpp", "layer_data.cpp", "layer_data_custom.cpp",
        "layer_data_configuration.cpp", "rnd.cpp", "neural_network_exception.cpp", "tiling_factor.cpp",
        "stat_data_bunch_writer.cpp"]

@@ -626,6 +626,86 @@ void orc_nll_bwd(float * dpredicted, const float * predicted, const float * actu
 		}
 }
 
+/* ---- Cross entropy over channels (the loss behind sigmoid outputs) -----------------------------------
+ * nnforge/plain/cross_entropy_layer_tester_plain.cpp:60-97 and cross_entropy_layer_updater_plain.cpp:62-99: per (entry, pixel)
+ *   err = total_scale * sum over channels, ascending, of
+ *           ( actual > 0 ? -actual * logf(max(predicted, 1e-20)) : 0 ) + ( actual < 1 ? -(1 - actual) * logf(max(1 - predicted, 1e-20)) : 0 )
+ * accumulated as two separate err -= term steps per channel; 0 when the total scale is 0. The two files differ in the total scale
+ * when a mask is given: the updater multiplies, total_scale = scale * mask (:71-73), the tester REPLACES the scale by the mask,
+ * total_scale = mask (:72-74). mask_replaces_scale selects the tester's form. */
+void orc_cross_entropy_fwd(float * err, const float * predicted, const float * actual, const float * mask, float scale, i64 n, i64 c, i64 hw,
+	int mask_replaces_scale)
+{
+	for (i64 e = 0; e < n; ++e)
+		for (i64 p = 0; p < hw; ++p)
+		{
+			float total_scale = scale;
+			if (mask)
+			{
+				if (mask_replaces_scale)
+					total_scale = mask[e * hw + p];
+				else
+					total_scale *= mask[e * hw + p];
+			}
+			float v = 0.0F;
+			if (total_scale != 0.0F)
+			{
+				for (i64 f = 0; f < c; ++f)
+				{
+					const float pr = predicted[(e * c + f) * hw + p];
+					const float ac = actual[(e * c + f) * hw + p];
+					if (ac > 0.0F)
+						v -= ac * logf(pr < 1.0e-20F ? 1.0e-20F : pr);
+					if (ac < 1.0F)
+					{
+						const float q = 1.0F - pr;
+						v -= (1.0F - ac) * logf(q < 1.0e-20F ? 1.0e-20F : q);
+					}
+				}
+				v *= total_scale;
+			}
+			err[e * hw + p] = v;
+		}
+}
+
+/* Gradient with respect to the predictions,
+ *   g = ( (actual > 0 ? actual / max(predicted, 1e-20) : 0) - (actual < 1 ? (1 - actual) / max(1 - predicted, 1e-20) : 0) ) * scale * mask,
+ * 0 when the total scale is 0. This is what cross_entropy_layer_updater_plain.cpp:146-166 computes - into a local `float gradient`
+ * that shadows the one which is stored (:150 against :157), so the plain backend itself writes zeros; the CUDA backend stores the
+ * value (nnforge/cuda/cross_entropy_layer_updater_cuda.cu:115-183). The one deviation from the plain backend on this path. */
+void orc_cross_entropy_bwd(float * dpredicted, const float * predicted, const float * actual, const float * mask, float scale, i64 n, i64 c, i64 hw,
+	int add_to_destination)
+{
+	for (i64 e = 0; e < n; ++e)
+		for (i64 p = 0; p < hw; ++p)
+		{
+			float total_scale = scale;
+			if (mask)
+				total_scale *= mask[e * hw + p];
+			for (i64 f = 0; f < c; ++f)
+			{
+				const i64 off = (e * c + f) * hw + p;
+				float g = 0.0F;
+				if (total_scale != 0.0F)
+				{
+					const float ac = actual[off], pr = predicted[off];
+					if (ac > 0.0F)
+						g = ac / (pr < 1.0e-20F ? 1.0e-20F : pr);
+					if (ac < 1.0F)
+					{
+						const float q = 1.0F - pr;
+						g -= (1.0F - ac) / (q < 1.0e-20F ? 1.0e-20F : q);
+					}
+					g *= total_scale;
+				}
+				if (add_to_destination)
+					dpredicted[off] += g;
+				else
+					dpredicted[off] = g;
+			}
+		}
+}
+
 /* ---- Top-n accuracy over channels: nnforge/plain/accuracy_layer_tester_plain.cpp:64-110 -------------
  * Per (entry, pixel): the actual class is the first channel holding the largest target (strict >, seeded
  * -1e37); rank = number of channels whose prediction beats the prediction of the actual class (larger, or equal

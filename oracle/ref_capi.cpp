@@ -23,6 +23,8 @@
 #include "plain/softmax_layer_updater_plain.h"
 #include "plain/negative_log_likelihood_layer_tester_plain.h"
 #include "plain/negative_log_likelihood_layer_updater_plain.h"
+#include "plain/cross_entropy_layer_tester_plain.h"
+#include "plain/cross_entropy_layer_updater_plain.h"
 #include "plain/accuracy_layer_tester_plain.h"
 #include "plain/accuracy_layer_updater_plain.h"
 #include "plain/average_subsampling_layer_tester_plain.h"
@@ -40,6 +42,7 @@
 #include "sigmoid_layer.h"
 #include "softmax_layer.h"
 #include "negative_log_likelihood_layer.h"
+#include "cross_entropy_layer.h"
 #include "accuracy_layer.h"
 #include "average_subsampling_layer.h"
 #include "add_layer.h"
@@ -548,6 +551,74 @@ extern "C"
 		plain_running_configuration::const_ptr cfg = make_running_config(threads);
 		std::set<layer_action> actions = all_actions();
 		negative_log_likelihood_layer_updater_plain upd;
+		double s = timed(1, [&]() {
+			upd.run_backward_data_propagation(0, in_err, plain_buffer::const_ptr(), ins, plain_buffer::const_ptr(), plain_buffer::ptr(), plain_buffer::ptr(),
+				plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(), layer_data_custom::const_ptr(), in_cfgs, out_cfg, add_to_destination != 0, actions, n);
+		});
+		memcpy(dpredicted, (const void *)(*in_err), in_bytes);
+		return s;
+		REF_GUARD_END
+	}
+	// nnforge/plain/cross_entropy_layer_tester_plain.cpp:32-98 (updater == 0) or cross_entropy_layer_updater_plain.cpp:32-101
+	// (updater != 0): err[n][1][h][w] from predicted and actual [n][c][h][w] and an optional scale mask [n][1][h][w].
+	double ref_cross_entropy_fwd(float * err, const float * predicted, const float * actual, const float * mask_or_null, float scale,
+		unsigned int n, unsigned int c, unsigned int h, unsigned int w, int updater, int threads, int reps)
+	{
+		REF_GUARD_BEGIN
+		layer::const_ptr schema(new cross_entropy_layer(scale));
+		const size_t in_bytes = (size_t)n * c * h * w * sizeof(float);
+		const size_t out_bytes = (size_t)n * h * w * sizeof(float);
+		plain_buffer::ptr out = make_buffer(0, out_bytes);
+		std::vector<plain_buffer::const_ptr> ins;
+		ins.push_back(make_buffer(predicted, in_bytes));
+		ins.push_back(make_buffer(actual, in_bytes));
+		std::vector<layer_configuration_specific> in_cfgs(2, make_config(c, h, w));
+		if (mask_or_null)
+		{
+			ins.push_back(make_buffer(mask_or_null, out_bytes));
+			in_cfgs.push_back(make_config(1, h, w));
+		}
+		layer_configuration_specific out_cfg = make_config(1, h, w);
+		plain_running_configuration::const_ptr cfg = make_running_config(threads);
+		std::set<layer_action> actions = all_actions();
+		cross_entropy_layer_tester_plain tester;
+		cross_entropy_layer_updater_plain upd;
+		double s = timed(reps, [&]() {
+			if (updater)
+				upd.run_forward_propagation(out, ins, plain_buffer::ptr(), plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, actions, n);
+			else
+				tester.run_forward_propagation(out, ins, plain_buffer::ptr(), plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(),
+					layer_data_custom::const_ptr(), in_cfgs, out_cfg, n);
+		});
+		memcpy(err, (const void *)(*out), out_bytes);
+		return s;
+		REF_GUARD_END
+	}
+
+	// nnforge/plain/cross_entropy_layer_updater_plain.cpp:103-175: the plain backend's backward action as it is (it stores
+	// zeros: the gradient is computed into a variable that shadows the one that is stored, :150-168).
+	double ref_cross_entropy_bwd(float * dpredicted, const float * predicted, const float * actual, const float * mask_or_null, float scale,
+		unsigned int n, unsigned int c, unsigned int h, unsigned int w, int add_to_destination, int threads)
+	{
+		REF_GUARD_BEGIN
+		layer::const_ptr schema(new cross_entropy_layer(scale));
+		const size_t in_bytes = (size_t)n * c * h * w * sizeof(float);
+		const size_t out_bytes = (size_t)n * h * w * sizeof(float);
+		plain_buffer::ptr in_err = make_buffer(dpredicted, in_bytes);
+		std::vector<plain_buffer::const_ptr> ins;
+		ins.push_back(make_buffer(predicted, in_bytes));
+		ins.push_back(make_buffer(actual, in_bytes));
+		std::vector<layer_configuration_specific> in_cfgs(2, make_config(c, h, w));
+		if (mask_or_null)
+		{
+			ins.push_back(make_buffer(mask_or_null, out_bytes));
+			in_cfgs.push_back(make_config(1, h, w));
+		}
+		layer_configuration_specific out_cfg = make_config(1, h, w);
+		plain_running_configuration::const_ptr cfg = make_running_config(threads);
+		std::set<layer_action> actions = all_actions();
+		cross_entropy_layer_updater_plain upd;
 		double s = timed(1, [&]() {
 			upd.run_backward_data_propagation(0, in_err, plain_buffer::const_ptr(), ins, plain_buffer::const_ptr(), plain_buffer::ptr(), plain_buffer::ptr(),
 				plain_buffer::ptr(), cfg, schema, layer_data::const_ptr(), layer_data_custom::const_ptr(), in_cfgs, out_cfg, add_to_destination != 0, actions, n);

@@ -1,5 +1,5 @@
 // Stand-in for the protobuf-generated accessors that the nnForge layer classes of this path touch in their
-// read_proto / write_proto members (BatchNorm, ReLU, PReLU, TanH, Add, MaxSubsampling, NegativeLogLikelihood, Accuracy, AverageSubsampling;
+// read_proto / write_proto members (BatchNorm, ReLU, PReLU, TanH, Add, MaxSubsampling, NegativeLogLikelihood, CrossEntropy, Accuracy, AverageSubsampling;
 // the other hot-path layers have no parameters). protoc is not available where the oracle is built and
 // the oracle never (de)serialises a schema, so these are plain structs with the same accessor names.
 // Test infrastructure only.
@@ -29,6 +29,7 @@ namespace nnforge
 		class TanHParam { NNF_SHIM_FIELD(float, scale) NNF_SHIM_FIELD(float, steepness) };
 		class PReLUParam { NNF_SHIM_FIELD(unsigned int, feature_map_count) };
 		class NegativeLogLikelihoodParam { NNF_SHIM_FIELD(float, scale) };
+		class CrossEntropyParam { NNF_SHIM_FIELD(float, scale) };
 		class AccuracyParam { NNF_SHIM_FIELD(unsigned int, top_n) };
 
 		enum MaxSubsamplingParam_MaxFunction { MaxSubsamplingParam_MaxFunction_MAX = 0, MaxSubsamplingParam_MaxFunction_MIN = 1 };
@@ -82,6 +83,7 @@ namespace nnforge
 			NNF_SHIM_MESSAGE(TanHParam, tanh_param)
 			NNF_SHIM_MESSAGE(PReLUParam, prelu_param)
 			NNF_SHIM_MESSAGE(NegativeLogLikelihoodParam, negative_log_likelihood_param)
+			NNF_SHIM_MESSAGE(CrossEntropyParam, cross_entropy_param)
 			NNF_SHIM_MESSAGE(AccuracyParam, accuracy_param)
 			NNF_SHIM_MESSAGE(AverageSubsamplingParam, average_subsampling_param)
 			NNF_SHIM_MESSAGE(MaxSubsamplingParam, max_subsampling_param)

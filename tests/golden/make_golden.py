@@ -109,6 +109,20 @@ def main():
     sy = synth.normal(g, (6, 5, 7, 3), 100.0, 3.0)
     out["stat_y"] = sy
     out["stat_minmaxavgstd"] = ref.feature_map_stats(sy)
+    # cross entropy on sigmoid-like predictions with hard and soft targets (appended last: the vectors before it keep their draws).
+    # The tester takes the mask instead of the scale, the updater multiplies the two; the plain backward action stores zeros
+    # (a shadowed variable), so no gradient vector can come from the reference.
+    for name, shape in (("ce", (3, 6, 4, 5)), ("ce_row", (5, 40, 1, 1))):
+        cp = (1.0 / (1.0 + np.exp(-synth.normal(g, shape, 0.0, 2.0).astype(np.float64)))).astype(np.float32)
+        ct = synth.targets(g, shape)
+        cp.flat[0], ct.flat[0] = 0.0, 1.0     # log of a clamped prediction
+        cp.flat[1], ct.flat[1] = 1.0, 0.0     # log of a clamped 1 - prediction
+        cmask = (synth.uniform(g, (shape[0], 1) + shape[2:], 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (shape[0], 1) + shape[2:], 0.5, 2.0)
+        out[name + "_p"], out[name + "_t"], out[name + "_mask"] = cp, ct, cmask
+        out[name + "_err_tester"] = ref.cross_entropy_fwd(cp, ct, cmask, 0.7)[0]
+        out[name + "_err_updater"] = ref.cross_entropy_fwd(cp, ct, cmask, 0.7, updater=True)[0]
+        out[name + "_err_nomask"] = ref.cross_entropy_fwd(cp, ct, None, 1.3)[0]
+        out[name + "_plain_backward"] = ref.cross_entropy_bwd(cp, ct, cmask, 0.7)[0]
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_backend.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -161,6 +161,27 @@ def test_negative_log_likelihood_objects(host, oracle):
     assert_bits_equal(out(acc), oracle.accuracy_fwd(p, t, mask, 3), "accuracy tester")
 
 
+def test_cross_entropy_objects(host, oracle):
+    g = synth.rng(3, salt=906)
+    n, c, h, w = SHAPE
+    p = (1.0 / (1.0 + np.exp(-synth.normal(g, SHAPE, 0.0, 2.0).astype(np.float64)))).astype(np.float32)
+    t = synth.targets(g, SHAPE)
+    mask = (synth.uniform(g, (n, 1, h, w), 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (n, 1, h, w), 0.5, 2.0)
+    err = torch.empty((n, 1, h, w), device="cuda")
+    # the tester reproduces the reference tester: with a mask, the mask alone is the total scale
+    host.Tester("CrossEntropy", c, w, h, params=[0.5], input_count=3).enqueue_forward_propagation(err, [], [dev(p), dev(t), dev(mask)], n)
+    assert_close(out(err), oracle.cross_entropy_fwd(p, t, mask, 0.5, mask_replaces_scale=True), "cross entropy tester, masked", atol=2e-5)
+    host.Tester("CrossEntropy", c, w, h, params=[0.5], input_count=2).enqueue_forward_propagation(err, [], [dev(p), dev(t)], n)
+    assert_close(out(err), oracle.cross_entropy_fwd(p, t, None, 0.5), "cross entropy tester", atol=2e-5)
+    u = host.Updater("CrossEntropy", c, w, h, params=[0.5], input_count=3)
+    u.enqueue_forward_propagation(err, [], [dev(p), dev(t), dev(mask)], n)
+    assert_close(out(err), oracle.cross_entropy_fwd(p, t, mask, 0.5), "cross entropy updater forward", atol=2e-5)
+    dp = torch.empty(SHAPE, device="cuda")
+    u.enqueue_backward_data_propagation_inputs(dp, None, [dev(p), dev(t), dev(mask)], None, n)
+    assert_bits_equal(out(dp), oracle.cross_entropy_bwd(p, t, mask, 0.5), "cross entropy updater backward")
+    assert u.is_backward_data_dependent_on_input_buffer() and not u.is_backward_data_dependent_on_output_buffer()
+
+
 def test_average_subsampling_objects(host, oracle):
     g = synth.rng(3, salt=904)
     shape = (4, 6, 8, 12)

@@ -817,6 +817,42 @@ def test_negative_log_likelihood(capi, oracle, shape, masked):
 
 @pytest.mark.parametrize("shape", LOSS_SHAPES)
 @pytest.mark.parametrize("masked", [False, True])
+def test_cross_entropy(capi, oracle, shape, masked):
+    """The loss behind sigmoid outputs: forward in tolerance (device logarithm; for rows a different order of the channel sum),
+    gradient bit-exact (IEEE divisions and one subtraction), accumulation included."""
+    g = synth.rng(1, salt=7300 + sum(shape))
+    p = (1.0 / (1.0 + np.exp(-synth.normal(g, shape, 0.0, 2.0).astype(np.float64)))).astype(np.float32)
+    t = synth.targets(g, shape)
+    p.flat[0], t.flat[0] = 0.0, 1.0      # clamped prediction under a positive target
+    if p.size > 1:
+        p.flat[1], t.flat[1] = 1.0, 0.0  # clamped 1 - prediction
+    mshape = (shape[0], 1) + shape[2:]
+    mask = (synth.uniform(g, mshape, 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, mshape, 0.5, 2.0) if masked else None
+    scale = 0.7
+    pd, td, md = dev(p), dev(t), dev(mask) if masked else None
+    err = torch.empty(mshape, device="cuda")
+    capi.cross_entropy_fwd(err, pd, td, md, scale)
+    want = oracle.cross_entropy_fwd(p, t, mask, scale)
+    # every channel contributes two logarithms of magnitude up to 46 (the clamp): the sum's absolute error grows with the terms
+    terms = np.abs(np.where(t > 0, t * np.log(np.maximum(p.astype(np.float64), 1e-20)), 0.0)) + np.abs(np.where(t < 1, (1 - t) * np.log(np.maximum(1 - p.astype(np.float64), 1e-20)), 0.0))
+    budget = 2e-6 + 3e-7 * terms.sum(axis=1, keepdims=True) * scale * (mask if masked else 1.0)
+    assert np.all(np.abs(host(err).astype(np.float64) - want) <= budget + 1e-5 * np.abs(want)), "cross entropy forward"
+    # the tester's form of the reference (the mask replaces the scale) is the same call with scale 1
+    if masked:
+        capi.cross_entropy_fwd(err, pd, td, md, 1.0)
+        want_t = oracle.cross_entropy_fwd(p, t, mask, scale, mask_replaces_scale=True)
+        assert np.all(np.abs(host(err).astype(np.float64) - want_t) <= budget / scale + 1e-5 * np.abs(want_t)), "cross entropy forward, tester form"
+    dp = torch.empty_like(pd)
+    capi.cross_entropy_bwd(dp, pd, td, md, scale)
+    assert_bits_equal(host(dp), oracle.cross_entropy_bwd(p, t, mask, scale), "cross entropy gradient")
+    seed = synth.normal(g, shape)
+    acc = dev(seed)
+    capi.cross_entropy_bwd(acc, pd, td, md, scale, add_to_destination=True)
+    assert_bits_equal(host(acc), oracle.cross_entropy_bwd(p, t, mask, scale, dx=seed), "cross entropy gradient, accumulated")
+
+
+@pytest.mark.parametrize("shape", LOSS_SHAPES)
+@pytest.mark.parametrize("masked", [False, True])
 def test_softmax_with_loss(capi, oracle, shape, masked):
     """Softmax and the loss in one pass: forward against softmax then loss of the plain restatement; backward
     against loss gradient then softmax backward, on the device's own probabilities."""

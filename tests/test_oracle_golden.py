@@ -52,6 +52,16 @@ def test_softmax(oracle):
     assert_bits_equal(oracle.softmax_fwd(G["row"]), G["softmax_row"], "softmax rows")
 
 
+@pytest.mark.parametrize("name", ["ce", "ce_row"])
+def test_cross_entropy_golden(oracle, name):
+    p, t, mask = G[name + "_p"], G[name + "_t"], G[name + "_mask"]
+    assert_bits_equal(oracle.cross_entropy_fwd(p, t, mask, 0.7, mask_replaces_scale=True), G[name + "_err_tester"], name + " forward, tester")
+    assert_bits_equal(oracle.cross_entropy_fwd(p, t, mask, 0.7), G[name + "_err_updater"], name + " forward, updater")
+    assert_bits_equal(oracle.cross_entropy_fwd(p, t, None, 1.3), G[name + "_err_nomask"], name + " forward, no mask")
+    assert not G[name + "_plain_backward"].any()      # what the plain backend's backward action stores
+    assert oracle.cross_entropy_bwd(p, t, mask, 0.7).any()
+
+
 @pytest.mark.parametrize("name", ["nll", "nll_row"])
 def test_negative_log_likelihood(oracle, name):
     p, t, mask = G[name + "_p"], G[name + "_t"], G[name + "_mask"]

@@ -76,6 +76,32 @@ def test_negative_log_likelihood(oracle, reference, shape):
 
 
 @pytest.mark.parametrize("shape", [(2, 1, 1, 1), (3, 21, 4, 5), (4, 1000, 1, 1), (2, 5, 1, 9)])
+def test_cross_entropy(oracle, reference, shape):
+    """Forward against the reference's tester (the mask REPLACES the scale) and updater (scale * mask). The reference's plain backward
+    action stores zeros - its gradient goes into a variable that shadows the stored one - so the restated gradient has no reference
+    twin here; it is the expression that file computes, checked against a float64 evaluation."""
+    g = synth.rng(55, salt=sum(shape))
+    p = (1.0 / (1.0 + np.exp(-synth.normal(g, shape, 0.0, 2.0).astype(np.float64)))).astype(np.float32)
+    t = synth.targets(g, shape)
+    p.flat[0], t.flat[0] = 0.0, 1.0
+    if p.size > 1:
+        p.flat[1], t.flat[1] = 1.0, 0.0
+    mask = (synth.uniform(g, (shape[0], 1) + shape[2:], 0.0, 1.0) > 0.3).astype(np.float32) * synth.uniform(g, (shape[0], 1) + shape[2:], 0.5, 2.0)
+    for m, scale in ((None, 1.0), (None, 0.7), (mask, 0.7), (mask, 0.0)):
+        assert_bits_equal(oracle.cross_entropy_fwd(p, t, m, scale, mask_replaces_scale=True), reference.cross_entropy_fwd(p, t, m, scale)[0], "cross entropy tester")
+        assert_bits_equal(oracle.cross_entropy_fwd(p, t, m, scale), reference.cross_entropy_fwd(p, t, m, scale, updater=True)[0], "cross entropy updater")
+        assert not reference.cross_entropy_bwd(p, t, m, scale)[0].any()   # the plain backend's own backward action: zeros
+        total = np.float64(np.float32(scale)) * (m.astype(np.float64) if m is not None else 1.0)
+        pd, td = p.astype(np.float64), t.astype(np.float64)
+        pos, neg = np.where(td > 0, td / np.maximum(pd, 1e-20), 0.0), np.where(td < 1, (1 - td) / np.maximum(1 - pd, 1e-20), 0.0)
+        want = (pos - neg) * total
+        got = oracle.cross_entropy_bwd(p, t, m, scale)
+        assert np.all(np.abs(got - want) <= 1e-6 * (pos + neg) * np.abs(total) + 1e-30)   # the two terms cancel for soft targets
+        seed = synth.normal(g, shape)
+        assert_bits_equal(oracle.cross_entropy_bwd(p, t, m, scale, dx=seed), (seed + got).astype(np.float32), "cross entropy bwd add")
+
+
+@pytest.mark.parametrize("shape", [(2, 1, 1, 1), (3, 21, 4, 5), (4, 1000, 1, 1), (2, 5, 1, 9)])
 def test_accuracy(oracle, reference, shape):
     g = synth.rng(54, salt=sum(shape))
     p = oracle.softmax_fwd(synth.normal(g, shape, 0.0, 3.0))
