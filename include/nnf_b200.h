@@ -313,6 +313,16 @@ NNF_API int nnf_bn_train_read_report(nnf_stream_t stream, nnf_launch_report * ho
  * tests and diagnosis; nnf_bn_train_read_report is the per-launch, asynchronous way. */
 NNF_API int nnf_fused_error_check(void);
 
+/* Where the launches raise the process-wide error word. By default a device variable inside the library, which the host
+ * can only read with a synchronising copy (nnf_fused_error_check). A host that wants to look at it after every step hands
+ * over ONE 32-bit word of pinned host memory here (cudaHostAlloc / cudaHostRegister; under unified addressing the device
+ * reaches it at the same address): a kernel whose bounded wait runs out then stores its code (2 or 4, as in
+ * nnf_launch_report.status) straight into that word, and the host reads it as ordinary memory once the stream has passed
+ * the launch - no copy, no event, nothing added to the stream. The host clears it (or calls nnf_fused_error_check) after it has
+ * dealt with the failure, e.g. by reading the launch reports to find the launch. NULL restores the default. The word must
+ * outlive every launch enqueued while it is set. No counterpart in the reference. */
+NNF_API int nnf_set_error_sink(int32_t * host_visible_word);
+
 NNF_API int nnf_bn_train_bwd_stats(nnf_stream_t stream, float * bsums, float * gsums, const float * dy, const float * x,
 	const float * gamma, const float * beta, const float * saved,
 	const nnf_act * acts, int n_acts, int64_t n, int64_t c, int64_t hw,

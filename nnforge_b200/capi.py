@@ -99,6 +99,7 @@ _SIGNATURES = {
     "nnf_bn_add_relu_avgpool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I64, _I, _I, _F]),
     "nnf_nll_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_nll_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
+    "nnf_set_error_sink": (_I, [_P]),
     "nnf_cross_entropy_fwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
     "nnf_cross_entropy_bwd": (_I, [_P, _P, _P, _P, _P, _F, _I64, _I64, _I64, _I]),
     "nnf_softmax_nll_fwd": (_I, [_P, _P, _P, _P, _P, _P, _F, _I64, _I64, _I64]),
@@ -343,6 +344,14 @@ def running_configuration():
     cfg = RunningConfiguration()
     _check(lib.nnf_get_running_configuration(ct.byref(cfg)))
     return {name: int(getattr(cfg, name)) for name, _ in RunningConfiguration._fields_}
+
+
+def set_error_sink(word):
+    """`word`: a pinned int32 CPU tensor of one element (or None to restore the device-side word): launches whose bounded wait runs
+    out store their code there, and the host reads it as ordinary memory (see nnf_set_error_sink)."""
+    if word is not None:
+        assert word.dtype == torch.int32 and word.numel() >= 1 and not word.is_cuda and word.is_pinned()
+    _check(lib.nnf_set_error_sink(None if word is None else word.data_ptr()))
 
 
 def set_tuning(name, value):

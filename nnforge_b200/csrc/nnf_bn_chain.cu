@@ -1728,14 +1728,18 @@ extern "C" int nnf_bn_train_bwd_sharded(nnf_stream_t stream, float * dx, float *
 }
 
 // The library's process-wide error word: a device variable inside the library, so that reaching it needs no
-// allocation. Kernels raise it next to their launch's own status word; no kernel reads it, so an old failure
-// cannot make a later launch give up its waits.
+// allocation - or, once the host has handed one over with nnf_set_error_sink, a word in host memory that the device can
+// address (pinned memory), which the host then reads without a copy, an event or a synchronisation. Kernels raise it next
+// to their launch's own status word; no kernel reads it, so an old failure cannot make a later launch give up its waits.
 static __device__ int nnf_error_word_storage;
+static std::atomic<int *> nnf_error_sink{nullptr};
 
 namespace nnf
 {
 	int * device_error_word()
 	{
+		if (int * sink = nnf_error_sink.load(std::memory_order_acquire))
+			return sink;
 		static std::mutex mu;
 		static int * words[64] = {};
 		int dev = 0;
@@ -1756,11 +1760,35 @@ namespace nnf
 	}
 }
 
-// Reads and clears the process-wide error word. Synchronises the device; meant for tests and diagnosis, not
-// for the enqueue path (nnf_bn_train_read_report is the asynchronous, per-launch way).
+extern "C" int nnf_set_error_sink(int32_t * host_visible_word)
+{
+	if (host_visible_word)
+	{
+		cudaPointerAttributes attr;
+		if (cudaPointerGetAttributes(&attr, host_visible_word) != cudaSuccess || attr.type != cudaMemoryTypeHost || !attr.devicePointer)
+		{
+			cudaGetLastError();
+			return nnf::set_error(NNF_ERR_INVALID_ARGUMENT, "nnf_set_error_sink: the word must be in pinned host memory that the device can address");
+		}
+		if (attr.devicePointer != static_cast<void *>(host_visible_word))
+			return nnf::set_error(NNF_ERR_UNSUPPORTED, "nnf_set_error_sink: host and device addresses of the word differ (no unified addressing)");
+	}
+	nnf_error_sink.store(host_visible_word, std::memory_order_release);
+	return NNF_OK;
+}
+
+// Reads and clears the process-wide error word. With a host-visible sink this is a plain read; otherwise it synchronises the
+// device and is meant for tests and diagnosis, not for the enqueue path.
 extern "C" int nnf_fused_error_check(void)
 {
-	int * w = device_error_word();
+	if (int * sink = nnf_error_sink.load(std::memory_order_acquire))
+	{
+		const int v = *static_cast<volatile int *>(sink);
+		if (v)
+			*static_cast<volatile int *>(sink) = 0;
+		return v;
+	}
+	int * w = nnf::device_error_word();
 	if (!w)
 		return 0;
 	int v = 0;

@@ -114,8 +114,22 @@ class ExchangeTimeout(RuntimeError):
 
 
 class ShardedBatchNormAct:
+    # A backend with nnf_set_error_sink raises one word of pinned host memory when a bounded wait runs out; the layers of a
+    # process share it, so the one that finds it raised counts a failure for all of them.
+    _process_sink = None
+    _process_failures = 0
+
     def __init__(self, kernels, channels, eps, acts, device, group=None, on_phase=None, exchange=None):
         self.k = kernels
+        self._sink = None
+        if hasattr(kernels, "set_error_sink") and torch.cuda.is_available():
+            if ShardedBatchNormAct._process_sink is None:
+                word = torch.zeros(1, dtype=torch.int32).pin_memory()
+                kernels.set_error_sink(word)
+                ShardedBatchNormAct._process_sink = word
+            self._sink = ShardedBatchNormAct._process_sink
+        self._seen_failures = ShardedBatchNormAct._process_failures
+        self._launched = {}       # direction -> workspace of this layer's most recent single launch
         self._pending = []        # (event, pinned report words, what) of single-launch steps not yet looked at
         self._free_reports = []
         self.degraded = False     # after a timed-out step: the NCCL sequence until reset_exchange()
@@ -159,9 +173,14 @@ class ShardedBatchNormAct:
 
     # ---- what the single-launch steps report ------------------------------------------------------------------
     def _note_launch(self, what, workspace):
-        """Enqueues the copy of the launch's report behind the launch; looked at by check()."""
+        """With a host-visible error word: nothing is added to the stream, the launch's workspace is remembered so that its report
+        can be fetched if the word is ever raised. Otherwise enqueues the copy of the launch's report behind the launch; looked at
+        by check()."""
         read = getattr(self.k, "read_report", None)
         if read is None:
+            return
+        if self._sink is not None:
+            self._launched[what] = workspace
             return
         words = self._free_reports.pop() if self._free_reports else self._new_report()
         if hasattr(self.k, "make_event"):      # a backend without streams (the CPU tests)
@@ -193,6 +212,21 @@ class ShardedBatchNormAct:
         GPU has already finished). A step whose wait ran out raises ExchangeTimeout; from then on the layer runs the
         statistics kernel / NCCL all-reduce / apply kernel sequence, which cannot time out silently, until
         reset_exchange() is called. Call it at a step boundary, before the outputs of the step are trusted."""
+        if self._sink is not None:
+            if block:
+                torch.cuda.current_stream().synchronize()
+            if int(self._sink[0]) != 0:
+                # some launch of this process gave up a wait: find out whether it was one of this layer's, tell every layer
+                torch.cuda.synchronize()
+                code = int(self._sink[0])
+                self._sink[0] = 0
+                ShardedBatchNormAct._process_failures += 1
+                self._last_failure = [(what, r) for what, r in self._fetch_reports() if r["status"] != 0] or [("a launch of this process", {"status": code})]
+            if self._seen_failures != ShardedBatchNormAct._process_failures:
+                self._seen_failures = ShardedBatchNormAct._process_failures
+                self.degraded = True
+                raise ExchangeTimeout(getattr(self, "_last_failure", [("a launch of this process", {"status": -1})]))
+            return
         bad, still = [], []
         for event, words, what in self._pending:
             if not block and not event.query():
@@ -211,9 +245,23 @@ class ShardedBatchNormAct:
     def reset_exchange(self):
         self.degraded = False
 
+    def _fetch_reports(self):
+        """The reports of this layer's most recent launch in each direction, read now (synchronises the device)."""
+        out = []
+        for what, workspace in self._launched.items():
+            words = self._new_report()
+            self.k.read_report(words, workspace)
+            torch.cuda.synchronize()
+            out.append((what, self.k.parse_report(words)))
+        return out
+
     def last_wait_ns(self):
         """(sum, max) of the waits inside the most recent single-launch step whose report has arrived; (0, 0) if none."""
         total = longest = 0
+        if self._sink is not None:
+            for what, r in self._fetch_reports():
+                total, longest = total + r["wait_ns_total"], max(longest, r["wait_ns_max"])
+            return total, longest
         for event, words, what in self._pending:
             if event.query():
                 r = self.k.parse_report(words)
@@ -233,7 +281,7 @@ class ShardedBatchNormAct:
         self.on_phase("start")
         ex = self.exchange
         hw = x.numel() // max(x.shape[0] * x.shape[1], 1)
-        if self._pending:
+        if self._pending or self._sink is not None:
             self.check(block=False)
         if self.world > 1 and getattr(ex, "in_launch", False) and not self.degraded and self._in_launch_ok(x, hw) and x.shape[1] == ex.channels:
             ws = self._ws(x, "forward")

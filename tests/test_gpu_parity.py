@@ -701,6 +701,22 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape, tuning):
     assert_bits_equal(host(y), y_ok, "the step after a failed one")
     assert capi.fused_error_check() == 2   # the process-wide word remembers that something failed ...
     assert capi.fused_error_check() == 0   # ... until it is read
+    # the same word in pinned host memory: the failed launch raises it there, the host reads it without a copy or an event
+    sink = torch.zeros(1, dtype=torch.int32).pin_memory()
+    capi.set_error_sink(sink)
+    try:
+        capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, x.size // c, ws, [mine.data_ptr()], 0, 1, 5)
+        torch.cuda.synchronize()
+        assert int(sink[0]) == 0
+        capi.bn_train_fwd_sharded(y, saved, sums, xd, gd, bd, 1e-5, acts, 2 * x.size // c, ws, [mine.data_ptr(), absent.data_ptr()], 0, 2, 6)
+        torch.cuda.synchronize()
+        assert int(sink[0]) == 2
+        assert capi.fused_error_check() == 2 and int(sink[0]) == 0
+        with pytest.raises(capi.NnfError):
+            capi.lib.nnf_set_error_sink.restype   # (binding present)
+            capi._check(capi.lib.nnf_set_error_sink(mine.data_ptr()))   # device memory is refused: the host could not read it
+    finally:
+        capi.set_error_sink(None)
 
 
 @pytest.mark.parametrize("shape", [(4, 6, 8, 8), (3, 5, 7, 7), (2, 3, 5, 3), (64, 64, 32, 32), (16, 24, 7, 7), (9, 40, 5, 5)])
