@@ -643,6 +643,49 @@ NNFH_API int nnfh_net_describe(void * n, char * out, size_t out_size)
 	}
 }
 
+// The buffer plan of an inference net (plan_forward_buffers with the objects' own get_input_index_layer_can_write answers):
+// first line "buffers=<count> total_bytes_per_entry=<n>", then one line per layer, "node=<name> buffer=<index|-> in_place=<input|->
+// bytes_per_entry=<n>".
+NNFH_API int nnfh_net_buffer_plan(void * n, char * out, size_t out_size)
+{
+	try
+	{
+		net& nt = *static_cast<net *>(n);
+		const int count = (int)nt.nodes.size();
+		std::vector<int> can_write(count, -1);
+		std::vector<size_t> bytes(count, 0);
+		for (const auto& o : nt.objects)
+		{
+			if (!o->handle.tester)
+				throw neural_network_exception("nnfh_net_buffer_plan: the plan covers inference nets (testers)");
+			can_write[o->node] = o->handle.tester->get_input_index_layer_can_write();
+		}
+		for (int i = 0; i < count; ++i)
+			bytes[i] = size_t(nt.shapes[nt.nodes[i].name].get_neuron_count()) * sizeof(float);
+		const buffer_plan bp = plan_forward_buffers(nt.nodes, nt.plan, can_write, bytes);
+		std::stringstream res;
+		res << "buffers=" << bp.buffer_bytes_per_entry.size() << " total_bytes_per_entry=" << bp.total_bytes_per_entry << "\n";
+		for (int i = 0; i < count; ++i)
+		{
+			res << "node=" << nt.nodes[i].name << " buffer=";
+			if (bp.buffer_of_node[i] < 0) res << "-"; else res << bp.buffer_of_node[i];
+			res << " in_place=";
+			if (bp.written_in_place[i] < 0) res << "-"; else res << bp.written_in_place[i];
+			res << " bytes_per_entry=" << bytes[i] << "\n";
+		}
+		const std::string text = res.str();
+		if (text.size() + 1 > out_size)
+			throw neural_network_exception("Result buffer too small");
+		memcpy(out, text.c_str(), text.size() + 1);
+		return 0;
+	}
+	catch (const std::exception& e)
+	{
+		g_net_error = e.what();
+		return -1;
+	}
+}
+
 // Lets `device` address the memory of `peer` (both directions are needed for a mailbox exchange: call it twice).
 // Returns 0 when access is, or already was, enabled.
 NNFH_API int nnfh_enable_peer_access(int device, int peer)

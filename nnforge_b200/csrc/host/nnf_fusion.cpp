@@ -1,5 +1,6 @@
 #include "nnf_fusion.h"
 
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <sstream>
@@ -220,6 +221,105 @@ namespace nnf_b200
 			}
 			plan.push_back(grp);
 		}
+		return plan;
+	}
+}
+
+namespace nnf_b200
+{
+	buffer_plan plan_forward_buffers(const std::vector<schema_node>& nodes, const std::vector<fused_group>& groups,
+		const std::vector<int>& can_write, const std::vector<size_t>& bytes)
+	{
+		const int n = (int)nodes.size();
+		if ((int)can_write.size() != n || (int)bytes.size() != n)
+			throw neural_network_exception("plan_forward_buffers: one answer and one size per node expected");
+		std::map<std::string, int> index;
+		for (int i = 0; i < n; ++i)
+			index[nodes[i].name] = i;
+		// per node: the action (position) that writes its output, the action that runs it, whether its output exists, and which
+		// inputs the RUNNING object of its group reads from outside the group
+		std::vector<int> written_at(n), runs_at(n), head_of(n);
+		std::vector<bool> exists(n, true), is_head(n, false);
+		for (const fused_group& g : groups)
+		{
+			const int head = g.members.at(0);
+			is_head[head] = true;
+			for (int m : g.members)
+			{
+				written_at[m] = head;
+				runs_at[m] = head;
+				head_of[m] = head;
+			}
+			for (int e : g.elided)
+				exists[e] = false;
+		}
+		// last action that reads each output
+		std::vector<int> last_read(n, -1);
+		for (int i = 0; i < n; ++i)
+			for (const std::string& in : nodes[i].inputs)
+			{
+				auto it = index.find(in);
+				if (it == index.end())
+					continue;                               // a data layer: not planned here
+				if (head_of[it->second] == head_of[i] && !is_head[i] && !exists[it->second])
+					continue;                               // a link inside a fused group: never materialised, never read
+				last_read[it->second] = std::max(last_read[it->second], runs_at[i]);
+			}
+		for (int i = 0; i < n; ++i)
+			if (nodes[i].output_needed)
+				last_read[i] = n;                           // a network output stays to the end
+		buffer_plan plan;
+		plan.buffer_of_node.assign(n, -1);
+		plan.written_in_place.assign(n, -1);
+		std::vector<int> free_at;                          // per buffer: the first action at which it is free again
+		for (int a = 0; a < n; ++a)                        // actions in order; a group's outputs are all written at its head
+		{
+			if (!is_head[a])
+				continue;
+			const fused_group * grp = nullptr;
+			for (const fused_group& g : groups)
+				if (g.members.at(0) == a)
+					grp = &g;
+			std::vector<int> outputs;
+			for (int m : grp->members)
+				if (exists[m])
+					outputs.push_back(m);
+			bool first_output = true;
+			for (int o : outputs)
+			{
+				int chosen = -1;
+				// in place over an input of the running object: the group's own input for a head
+				if (first_output && can_write[a] >= 0 && can_write[a] < (int)nodes[a].inputs.size())
+				{
+					auto it = index.find(nodes[a].inputs[can_write[a]]);
+					if (it != index.end() && exists[it->second] && last_read[it->second] == a && plan.buffer_of_node[it->second] >= 0
+						&& plan.buffer_bytes_per_entry[plan.buffer_of_node[it->second]] >= bytes[o])
+					{
+						chosen = plan.buffer_of_node[it->second];
+						plan.written_in_place[o] = can_write[a];
+					}
+				}
+				first_output = false;
+				if (chosen < 0)
+				{
+					for (size_t b = 0; b < free_at.size(); ++b)
+						if (free_at[b] <= a && plan.buffer_bytes_per_entry[b] >= bytes[o]
+							&& (chosen < 0 || plan.buffer_bytes_per_entry[b] < plan.buffer_bytes_per_entry[chosen]))
+							chosen = (int)b;
+				}
+				if (chosen < 0)
+				{
+					chosen = (int)free_at.size();
+					free_at.push_back(0);
+					plan.buffer_bytes_per_entry.push_back(bytes[o]);
+				}
+				plan.buffer_of_node[o] = chosen;
+				// an output nobody reads is still written: it keeps its buffer through its own action
+				free_at[chosen] = std::max(last_read[o], a) + 1;
+			}
+		}
+		for (size_t b : plan.buffer_bytes_per_entry)
+			plan.total_bytes_per_entry += b;
 		return plan;
 	}
 }

@@ -55,6 +55,25 @@ namespace nnf_b200
 
 	// The objects that run the plan are made by layer_factory_b200::create_testers / create_updaters (nnf_layers.h).
 
+	// Which layer outputs of an inference schedule share storage: the part of network_action_schema::get_buffer_set
+	// (nnforge/network_action_schema.h:106-109, driven from forward_propagation_cuda::setup_layer_buffer_sizes,
+	// nnforge/cuda/forward_propagation_cuda.cpp:771-832) that a scheduler needs once groups are fused. Actions run in the order of
+	// the node list, a fused group at the position of its first member. A materialised output lives from the action that writes it
+	// to the last action that reads it (to the end when output_needed); outputs in fused_group::elided get no buffer; an object whose
+	// get_input_index_layer_can_write() names an input writes its (first) output over that input's buffer when nobody reads the
+	// input afterwards; otherwise an output takes the smallest free buffer that is large enough, or a new one.
+	struct buffer_plan
+	{
+		std::vector<int> buffer_of_node;              // per node: index of its output's buffer, -1 for an elided output
+		std::vector<size_t> buffer_bytes_per_entry;   // per buffer
+		std::vector<int> written_in_place;            // per node: the input index whose buffer the output took over, or -1
+		size_t total_bytes_per_entry = 0;
+	};
+	// can_write[i]: what the object that runs node i answers (the head's answer for the first member of a group; ignored for the other
+	// members). output_bytes_per_entry[i]: size of node i's output.
+	buffer_plan plan_forward_buffers(const std::vector<schema_node>& nodes, const std::vector<fused_group>& groups,
+		const std::vector<int>& can_write, const std::vector<size_t>& output_bytes_per_entry);
+
 	// A schema in text form, one layer per line: "name type inputs [needed] [key=value ...]" with inputs a
 	// comma-separated list of layer names or "-" for none. Keys: alpha (Add, AverageSubsampling), slope (ReLU),
 	// scale and steepness (TanH; scale also NegativeLogLikelihood), eps (BatchNorm), topn (Accuracy),

@@ -55,6 +55,7 @@ lib.nnfh_net_object.restype = _P
 lib.nnfh_net_object.argtypes = [_P, ct.c_int]
 lib.nnfh_net_describe.argtypes = [_P, ct.c_char_p, ct.c_size_t]
 lib.nnfh_enable_peer_access.argtypes = [ct.c_int, ct.c_int]
+lib.nnfh_net_buffer_plan.argtypes = [_P, ct.c_char_p, ct.c_size_t]
 
 FORWARD, BACKWARD_DATA, BACKWARD_WEIGHTS, BACKWARD_DATA_AND_WEIGHTS = 0, 1, 2, 3
 
@@ -365,6 +366,21 @@ class Net:
                     "entry": None if d["entry"] == "-" else d["entry"], "shape": tuple(int(v) for v in d["shape"].split(",")),
                     "inputs": lst(d["inputs"]), "data": lst(d["data"]), "outputs": lst(d["outputs"]), "elided": lst(d["elided"])}
             self.objects.append(LayerObject(lib.nnfh_net_object(self.h, k), desc))
+
+    def buffer_plan(self):
+        """Which layer outputs of this inference net share storage (plan_forward_buffers): {"buffers": count, "total_bytes_per_entry": n,
+        "nodes": {layer: {"buffer": index or None, "in_place": input index or None, "bytes_per_entry": n}}}."""
+        buf = ct.create_string_buffer(1 << 16)
+        if lib.nnfh_net_buffer_plan(self.h, buf, len(buf)) != 0:
+            raise HostLayerError(lib.nnfh_net_last_error().decode())
+        lines = buf.value.decode().splitlines()
+        head = dict(tok.split("=") for tok in lines[0].split(" "))
+        nodes = {}
+        for line in lines[1:]:
+            d = dict(tok.split("=", 1) for tok in line.split(" "))
+            nodes[d["node"]] = {"buffer": None if d["buffer"] == "-" else int(d["buffer"]), "in_place": None if d["in_place"] == "-" else int(d["in_place"]),
+                                "bytes_per_entry": int(d["bytes_per_entry"])}
+        return {"buffers": int(head["buffers"]), "total_bytes_per_entry": int(head["total_bytes_per_entry"]), "nodes": nodes}
 
     def __del__(self):
         if getattr(self, "h", None) and lib is not None:

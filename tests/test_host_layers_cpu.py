@@ -175,3 +175,29 @@ def test_running_configuration_has_the_reference_fields():
     rc = host.running_configuration()
     assert rc["multiprocessor_count"] > 0 and rc["smem_per_block"] > 48 * 1024 and rc["l2_cache_size"] > 0
     assert rc["compute_capability_major"] >= 1 and (rc["device_pos"], rc["device_count"]) == (0, 1)
+
+
+def test_buffer_plan_of_a_fused_inference_net():
+    """plan_forward_buffers: elided outputs get no buffer, a head writes over its input when nobody else reads it, freed buffers are
+    taken again, network outputs stay to the end - with the objects' own get_input_index_layer_can_write answers."""
+    from nnforge_b200 import host
+    spec = ("bn1 BatchNorm c1\nadd1 Add bn1,skip\nrelu1 ReLU add1\npool1 MaxSubsampling relu1 win=3x3 stride=2x2\n"
+            "bn2 BatchNorm pool1\ntanh2 TanH bn2\nout Sigmoid tanh2 needed\n")
+    plan = host.Net(spec, {"c1": (8, 14, 14), "skip": (8, 14, 14)}).buffer_plan()
+    nodes = plan["nodes"]
+    assert [nodes[k]["buffer"] for k in ("bn1", "add1", "bn2", "tanh2")] == [None] * 4          # inside the fused launches
+    assert nodes["relu1"]["buffer"] is not None and nodes["pool1"]["buffer"] not in (None, nodes["relu1"]["buffer"])
+    assert nodes["out"]["buffer"] == nodes["pool1"]["buffer"] and nodes["out"]["in_place"] == 0  # the second group runs in place
+    assert plan["buffers"] == 2 and plan["total_bytes_per_entry"] == 4 * (8 * 14 * 14 + 8 * 6 * 6)
+    # the same layers with a second reader of every intermediate output: nothing fuses, nothing may be overwritten early
+    unfused = ("bn1 BatchNorm c1\nadd1 Add bn1,skip\nrelu1 ReLU add1\npool1 MaxSubsampling relu1 win=3x3 stride=2x2\n"
+               "tap Add bn1,add1,relu1 needed\nbn2 BatchNorm pool1\ntanh2 TanH bn2\nout Sigmoid tanh2 needed\n")
+    net = host.Net(unfused, {"c1": (8, 14, 14), "skip": (8, 14, 14)})
+    assert [o.role for o in net.objects[:3]] == ["single"] * 3
+    plan2 = net.buffer_plan()
+    n2 = plan2["nodes"]
+    assert len({n2[k]["buffer"] for k in ("bn1", "add1", "relu1")}) == 3 and n2["add1"]["in_place"] is None   # bn1 is read again by the tap
+    assert n2["tap"]["in_place"] == 0 and n2["tap"]["buffer"] == n2["bn1"]["buffer"]                        # the Add may write over its input 0
+    assert plan2["total_bytes_per_entry"] > plan["total_bytes_per_entry"]
+    with pytest.raises(host.HostLayerError):
+        host.Net("bn BatchNorm x\n", {"x": (8, 4, 4)}, training=True).buffer_plan()   # the plan covers inference nets
