@@ -393,6 +393,14 @@ def collect_sweep(args, quick):
         report(3, "bn_train+relu bwd N=%d C=%d %dx%d, one launch (channel-group items)" % (n, c, hw, hw),
                timeit(lambda i: capi.bn_train_bwd(dx, bsums, dy, x, gamma, beta, saved, acts, workspace=ws), 1), 12 * e)
         del x, dy, y, dx
+    # beyond the five configurations: inference BN + ReLU on planes that are not whole float4s (the channel-group kernel)
+    for n, c, hw in ([] if quick else [(1024, 512, 7), (1024, 2048, 7)]):
+        e = n * c * hw * hw
+        x = torch.randn((n, c, hw, hw), device="cuda")
+        y = torch.empty_like(x)
+        bn = bnp(c)
+        report(3, "bn_infer+relu N=%d C=%d %dx%d (channel groups)" % (n, c, hw, hw), timeit(lambda i: capi.bn_infer_act(y, x, bn=bn, acts=[capi.relu(0.0)]), 1), 8 * e)
+        del x, y
     # config 4: inference BN + TanH / Sigmoid bandwidth sweep
     sizes = [128, 1024] if quick else [128, 1024, 4096] + ([8192] if args.sweep_full else [])
     for n in sizes:
