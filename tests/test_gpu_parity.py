@@ -713,7 +713,6 @@ def test_bn_train_sharded_single_launch_wait_is_bounded(capi, shape, tuning):
         assert int(sink[0]) == 2
         assert capi.fused_error_check() == 2 and int(sink[0]) == 0
         with pytest.raises(capi.NnfError):
-            capi.lib.nnf_set_error_sink.restype   # (binding present)
             capi._check(capi.lib.nnf_set_error_sink(mine.data_ptr()))   # device memory is refused: the host could not read it
     finally:
         capi.set_error_sink(None)
