@@ -84,7 +84,8 @@ namespace nnf
 			uint32_t seq;
 			double count_total;          // elements per channel over all ranks
 			double * partial;            // [c][split_s][3]
-			uint32_t * done;             // [c] finished S items per channel; zero at kernel start
+			float * fin;                 // [c][8] one GPU: the constants a group's last S item leaves for its A items
+			uint32_t * done;             // [groups] finished S items per group, then [groups] flags "constants written"; zero at kernel start
 			uint32_t * ticket;           // zero at kernel start
 			int * error;                 // the launch's status word (in the workspace head; zero at kernel start)
 			int * error_word;            // the library's process-wide word: raised too, never consulted
@@ -974,27 +975,26 @@ namespace nnf
 						#pragma unroll
 						for (int k = 0; k < K; ++k)
 							out[k] = t[k];
-						__threadfence(); // the partial sums are visible before the count
 					}
 				}
 				__syncthreads();
 				if (threadIdx.x == 0)
 				{
-					__threadfence(); // every partial sum of this item, whichever thread wrote it, comes before the count
+					// the barrier orders every partial sum of this item, whichever thread wrote it, before this fence, and
+					// the fence before the count
+					__threadfence();
 					const uint32_t before = atomicAdd(p.done + grp, 1u);
-					if (PEER)
-					{
-						__threadfence(); // and the other items' partial sums are visible to this one if it is the last
-						s_item[3] = before == p.split_s - 1 ? 1u : 0u;
-					}
+					const bool last = before == p.split_s - 1;
+					if (last)
+						__threadfence(); // the other items' partial sums are visible to the group's last item
+					s_item[3] = last ? 1u : 0u;
 				}
-				if (!PEER)
-					return;
 				__syncthreads();
 				if (s_item[3] == 0)
 					return;
 				// last S item of this group on this rank: fold the partial sums of every channel of the group (slice
-				// order, eight lanes per channel), write the local per-channel outputs, publish the messages to every rank
+				// order, eight lanes per channel) and write the local per-channel outputs. One GPU: derive the constants
+				// the group's A items apply and raise the group's flag. Several: publish the messages to every rank.
 				for (uint32_t first = 0; first < channels; first += kChainThreads / kLanes)
 				{
 					const uint32_t lc = first + threadIdx.x / kLanes;
@@ -1004,12 +1004,15 @@ namespace nnf
 					for (int k = 0; k < K; ++k)
 						t[k] = 0.0;
 					if (lc < channels)
+					{
+						#pragma unroll 4
 						for (uint32_t q = lane; q < p.split_s; q += kLanes)
 						{
 							#pragma unroll
 							for (int k = 0; k < K; ++k)
 								t[k] += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
 						}
+					}
 					#pragma unroll
 					for (int k = 0; k < K; ++k)
 					{
@@ -1017,7 +1020,55 @@ namespace nnf
 						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 2);
 						t[k] += __shfl_xor_sync(0xffffffffu, t[k], 1);
 					}
-					if (lc < channels)
+					if constexpr (!PEER)
+					{
+						if (lc < channels && lane == 0)
+						{
+							float * fin = p.fin + size_t(ch) * 8;
+							if constexpr (!BWD)
+							{
+								const double sh = double(__ldg(p.x + size_t(ch) * p.hw));
+								const double ms = t[0] / p.count;       // mean of x - shift
+								double var = t[1] / p.count - ms * ms;
+								var = var < 0.0 ? 0.0 : var;
+								const float fmean = float(sh + ms);
+								t[1] = t[1] + 2.0 * sh * t[0] + p.count * sh * sh;   // {sum x, sum x^2} as the other entry points define them
+								t[0] = t[0] + p.count * sh;
+								const float finv = float(1.0 / sqrt(var + double(p.eps)));
+								const float mult = __fmul_rn(__ldg(p.gamma + ch), finv);
+								__stcg(reinterpret_cast<float2 *>(fin), make_float2(mult, __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, fmean))));
+								p.saved[ch] = fmean;
+								p.saved[p.c + ch] = finv;
+								if (p.sums)
+								{
+									p.sums[ch] = float(t[0]);
+									p.sums[p.c + ch] = float(t[1]);
+								}
+							}
+							else
+							{
+								const float fb = float(t[0]), fg = float(t[1]), fs = float(t[K - 1]);
+								const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
+								const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
+								// the same float-rounded sums the two-kernel form passes between its kernels
+								__stcg(reinterpret_cast<float4 *>(fin), make_float4(mult, __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean)), mean, invstd));
+								__stcg(reinterpret_cast<float2 *>(fin + 4), make_float2(float(double(fb) / p.count), float(double(fg) / p.count)));
+								if (p.sums)
+								{
+									p.sums[ch] = fb;
+									p.sums[p.c + ch] = fg;
+									p.sums[2 * p.c + ch] = fs;
+								}
+								// per-channel gradients accumulate (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
+								if (p.grad_beta) p.grad_beta[ch] += fb;
+								if (p.grad_gamma) p.grad_gamma[ch] += fg;
+								if (p.grad_slope) p.grad_slope[ch] += fs;
+								if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
+								if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
+							}
+						}
+					}
+					else if (lc < channels)
 					{
 						if constexpr (!BWD)
 						{
@@ -1053,6 +1104,13 @@ namespace nnf
 							st_sys_u64(p.mail[lane] + mail_index(p, p.rank, ch) + 1, (static_cast<unsigned long long>(p.seq) << 32) | __float_as_uint(m1));
 						}
 					}
+				}
+				if constexpr (!PEER)
+				{
+					// the barrier orders the constants, whichever thread wrote them, before the release that raises the flag
+					__syncthreads();
+					if (threadIdx.x == 0)
+						st_release_u32(p.done + p.groups + grp, 1u);
 				}
 				return;
 			}
@@ -1168,10 +1226,11 @@ namespace nnf
 			}
 			if (!PEER && threadIdx.x == 0)
 			{
+				// the flag the group's last S item raises behind the constants
 				bool ready = false;
 				for (uint32_t round = 0; round < kChainPollLimit; ++round)
 				{
-					if (ld_acquire(p.done + grp) >= p.split_s)
+					if (ld_acquire(p.done + p.groups + grp) != 0)
 					{
 						ready = true;
 						break;
@@ -1184,83 +1243,28 @@ namespace nnf
 					if (p.error_word) *p.error_word = 4;
 				}
 			}
-			__syncthreads();
-			// the S items' partial sums of every channel of the group, in slice order: eight lanes per channel
-			for (uint32_t first = 0; !PEER && first < channels; first += kChainThreads / kLanes)
+			if constexpr (!PEER)
 			{
-				const uint32_t lc = first + threadIdx.x / kLanes;
-				const uint32_t ch = ch0 + lc;
-				double t[K];
-				#pragma unroll
-				for (int k = 0; k < K; ++k)
-					t[k] = 0.0;
-				if (lc < channels)
-					for (uint32_t q = lane; q < p.split_s; q += kLanes)
-					{
-						#pragma unroll
-						for (int k = 0; k < K; ++k)
-							t[k] += __ldcg(p.partial + (size_t(ch) * p.split_s + q) * 3 + k);
-					}
-				#pragma unroll
-				for (int k = 0; k < K; ++k)
+				__syncthreads();
+				for (uint32_t lc = threadIdx.x; lc < channels; lc += kChainThreads)
 				{
-					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 4);
-					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 2);
-					t[k] += __shfl_xor_sync(0xffffffffu, t[k], 1);
-				}
-				if (lc < channels && lane == 0)
-				{
+					const float * fin = p.fin + size_t(ch0 + lc) * 8;
 					if constexpr (!BWD)
 					{
-						const double sh = double(__ldg(p.x + size_t(ch) * p.hw));
-						const double ms = t[0] / p.count;       // mean of x - shift
-						double var = t[1] / p.count - ms * ms;
-						var = var < 0.0 ? 0.0 : var;
-						const float fmean = float(sh + ms);
-						t[1] = t[1] + 2.0 * sh * t[0] + p.count * sh * sh;   // {sum x, sum x^2} as the other entry points define them
-						t[0] = t[0] + p.count * sh;
-						const float finv = float(1.0 / sqrt(var + double(p.eps)));
-						const float mult = __fmul_rn(__ldg(p.gamma + ch), finv);
-						s_const[0][lc] = mult;
-						s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, fmean));
-						if (sp == 0)
-						{
-							p.saved[ch] = fmean;
-							p.saved[p.c + ch] = finv;
-							if (p.sums)
-							{
-								p.sums[ch] = float(t[0]);
-								p.sums[p.c + ch] = float(t[1]);
-							}
-						}
+						const float2 q = __ldcg(reinterpret_cast<const float2 *>(fin));
+						s_const[0][lc] = q.x;
+						s_const[1][lc] = q.y;
 					}
 					else
 					{
-						const float fb = float(t[0]), fg = float(t[1]), fs = float(t[K - 1]);
-						const float mean = __ldg(p.saved + ch), invstd = __ldg(p.saved + p.c + ch);
-						const float mult = __fmul_rn(__ldg(p.gamma + ch), invstd);
-						s_const[0][lc] = mult;
-						s_const[1][lc] = __fsub_rn(__ldg(p.beta + ch), __fmul_rn(mult, mean));
-						s_const[NC - 4][lc] = mean;
-						s_const[NC - 3][lc] = invstd;
-						// the same float-rounded sums the two-kernel form passes between its kernels
-						s_const[NC - 2][lc] = float(double(fb) / p.count);
-						s_const[NC - 1][lc] = float(double(fg) / p.count);
-						if (sp == 0)
-						{
-							if (p.sums)
-							{
-								p.sums[ch] = fb;
-								p.sums[p.c + ch] = fg;
-								p.sums[2 * p.c + ch] = fs;
-							}
-							// per-channel gradients accumulate (batch_norm_layer_updater_cuda.cu:138-139, 167-182)
-							if (p.grad_beta) p.grad_beta[ch] += fb;
-							if (p.grad_gamma) p.grad_gamma[ch] += fg;
-							if (p.grad_slope) p.grad_slope[ch] += fs;
-							if (p.grad_mean) p.grad_mean[ch] += p.entry_count * (mean - p.mean[ch]);
-							if (p.grad_invsigma) p.grad_invsigma[ch] += p.entry_count * (invstd - p.invsigma[ch]);
-						}
+						const float4 q = __ldcg(reinterpret_cast<const float4 *>(fin));
+						const float2 r = __ldcg(reinterpret_cast<const float2 *>(fin + 4));
+						s_const[0][lc] = q.x;
+						s_const[1][lc] = q.y;
+						s_const[NC - 4][lc] = q.z;
+						s_const[NC - 3][lc] = q.w;
+						s_const[NC - 2][lc] = r.x;
+						s_const[NC - 1][lc] = r.y;
 					}
 				}
 			}
@@ -1395,7 +1399,7 @@ namespace nnf
 
 		// The grouped kernel's plan: items are channel groups. Returns false where the shape does not suit it (planes
 		// of whole float4s take the kernel above; runs shorter than 16 vectors or longer than 256 the separate kernels).
-		bool plan_chain_grouped(chain_params& p, int64_t n, int64_t c, int64_t hw)
+		bool plan_chain_grouped(chain_params& p, int64_t n, int64_t c, int64_t hw, bool backward = false)
 		{
 			if (hw % 4 == 0 || n < 1 || c < 1 || n >= (int64_t(1) << 31) || c >= (int64_t(1) << 24) || tune().no_grouped == 1)
 				return false;
@@ -1432,7 +1436,9 @@ namespace nnf
 			if (chunk > groups) chunk = groups;
 			p.chunk = (uint32_t)chunk;
 			p.nchunks = (uint32_t)div_up(groups, chunk);
-			int lag = tune().chain_lag > 0 ? tune().chain_lag - 1 : 1;   // the knob is lag + 1, so that 0 keeps the default
+			// the knob is lag + 1, so that 0 keeps the default: two chunks forward, one backward (x[1024,512,7,7] with ReLU on
+			// B200: forward 62 us at one chunk, 58 us at two; backward 90 us and 91 us)
+			int lag = tune().chain_lag > 0 ? tune().chain_lag - 1 : (backward ? 1 : 2);
 			p.lag = (uint32_t)(lag < 0 ? 0 : lag);
 			const int64_t items = groups * (int64_t(p.split_s) + int64_t(p.split_a));
 			if (items >= (int64_t(1) << 31))
@@ -1449,10 +1455,11 @@ namespace nnf
 			return true;
 		}
 
-		// Workspace of the channel-group kernel: the report, the counters (one per channel + padding), the partial sums.
+		// Workspace of the channel-group kernel: the report, the counters (one per channel + padding), the partial sums,
+		// eight floats of constants per channel (16-byte aligned).
 		size_t chain_workspace_needed(const chain_params& p)
 		{
-			return sizeof(launch_report) + (size_t(p.c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(p.c) * p.split_s * 3 * sizeof(double);
+			return sizeof(launch_report) + (size_t(p.c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(p.c) * p.split_s * 3 * sizeof(double) + 16 + size_t(p.c) * 8 * sizeof(float);
 		}
 
 		unsigned long long peer_wait_limit()
@@ -1467,6 +1474,7 @@ namespace nnf
 			launch_report * report = static_cast<launch_report *>(workspace);
 			p.done = reinterpret_cast<uint32_t *>(report + 1);
 			p.partial = reinterpret_cast<double *>(p.done + (size_t(p.c) + 2) / 2 * 2);
+			p.fin = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(p.partial + size_t(p.c) * p.split_s * 3) + 15) & ~uintptr_t(15));
 			p.ticket = &report->ticket;
 			p.error = &report->status;
 			p.wait_ns = &report->wait_ns_total;
@@ -1513,7 +1521,8 @@ namespace nnf
 		// the larger of what the two kernels plan for this shape, forward or backward (the plans share their item counts)
 		// the knobs may change between the size query and the launch: sized for the most items a plan can make
 		(void)n; (void)hw;
-		const size_t grouped = sizeof(launch_report) + (size_t(c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(c) * kChainMaxSplit * 3 * sizeof(double);
+		const size_t grouped = sizeof(launch_report) + (size_t(c) + 2) / 2 * 2 * sizeof(uint32_t) + size_t(c) * kChainMaxSplit * 3 * sizeof(double)
+			+ 16 + size_t(c) * 8 * sizeof(float);
 		const size_t stream = sizeof(launch_report) + size_t(c) * sizeof(uint32_t) + 16 + size_t(c) * 2 * sizeof(float4)
 			+ size_t(c) * kChainMaxSplit * 4 * sizeof(unsigned long long);
 		return grouped > stream ? grouped : stream;
@@ -1613,7 +1622,7 @@ namespace nnf
 			if (!aligned16(x) || !aligned16(dy) || !aligned16(dx))
 				return 1;
 			chain_params gp = {};
-			if (plan_chain_grouped(gp, n, c, hw))
+			if (plan_chain_grouped(gp, n, c, hw, true))
 			{
 				if (!workspace_ok(workspace, workspace_bytes, chain_workspace_needed(gp)))
 					return 2;
