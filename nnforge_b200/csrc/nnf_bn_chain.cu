@@ -807,7 +807,8 @@ namespace nnf
 		// whole vectors, a group is as many of those as fill the CTA's 256 vector lanes (20 channels for 7x7). A thread
 		// owns one vector position of the group's run in every entry of its item, so the channels of its four
 		// elements and their constants are loop invariants; an S item sums per position and folds the positions per
-		// channel through shared memory, an A item folds the S items' partial sums of all the group's channels.
+		// channel through shared memory; the S item that finishes a group last folds the items' partial sums of all the
+		// group's channels and leaves the constants for the group's A items.
 		constexpr int kChainGroupRun = 1024;       // floats of a group's run in one entry (one vector per thread)
 		constexpr int kChainGroupChannels = 256;
 
@@ -1375,7 +1376,8 @@ namespace nnf
 			p.es = (uint32_t)es; p.ea = (uint32_t)ea;
 			p.ss = (uint32_t)div_up(n, es); p.sa = (uint32_t)div_up(n, ea);
 			// batch-sharded launches: a channel's constants also wait for the other ranks' sums (an NVLink round trip and whatever
-			// the ranks are apart), so the forward launch keeps a longer distance (two GPUs: 119 us at 48 against 127-130 at 32)
+			// the ranks are apart), so the forward launch keeps a longer distance (two GPUs, before the staging ring: 119 us at
+			// 48 against 127-130 at 32; with it 88 us at either)
 			int64_t dist = t.chain_dist >= 0 ? t.chain_dist : (backward ? 24 : (sharded ? 48 : 32));
 			if (dist > c) dist = c;
 			p.dist = (uint32_t)dist;
