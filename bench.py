@@ -401,6 +401,70 @@ def collect_sweep(args, quick):
         bn = bnp(c)
         report(3, "bn_infer+relu N=%d C=%d %dx%d (channel groups)" % (n, c, hw, hw), timeit(lambda i: capi.bn_infer_act(y, x, bn=bn, acts=[capi.relu(0.0)]), 1), 8 * e)
         del x, y
+    if not quick:
+        # the layers either side of the path, each at a size well above L2 (rows "n": neighbours, not one of the five configurations)
+        shape = (256, 256, 28, 28)
+        e = 256 * 256 * 28 * 28
+        x, dy = torch.randn(shape, device="cuda"), torch.randn(shape, device="cuda")
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        slope = torch.rand(256, device="cuda") * 0.3
+        capi.act_fwd(y, x, capi.elu())
+        report("n", "ELU backward (dy, y -> dx) x[256,256,28,28]", timeit(lambda i: capi.act_bwd(dx, dy, y, capi.elu()), 1), 12 * e)
+        report("n", "PReLU backward, data (dy, x -> dx) x[256,256,28,28]", timeit(lambda i: capi.act_bwd(dx, dy, x, capi.prelu(slope)), 1), 12 * e)
+        dslope = torch.empty(256, device="cuda")
+        wsp = torch.empty(capi.lib.nnf_prelu_bwd_weights_workspace_bytes(256, 256, 784), dtype=torch.uint8, device="cuda")
+        report("n", "PReLU backward, slopes (dy, x -> dslope) x[256,256,28,28]", timeit(lambda i: capi.prelu_bwd_weights(dslope, dy, x, workspace=wsp), 1), 8 * e)
+        report("n", "add forward, two inputs x[256,256,28,28]", timeit(lambda i: capi.add_fwd(y, [x, dy]), 1), 12 * e)
+        report("n", "add backward (dy * alpha -> dx) x[256,256,28,28]", timeit(lambda i: capi.add_bwd(dx, dy, alpha=0.5), 1), 8 * e)
+        del x, dy, y, dx
+        # channel softmax outside the shapes of configuration 1: many channels per pixel (tile kernel), rows that are not whole
+        # float4s (scalar warp kernel), rows longer than a warp holds (CTA per row)
+        for shape in [(16, 150, 128, 128), (65536, 1001, 1, 1), (8192, 32000, 1, 1)]:
+            e = shape[0] * shape[1] * shape[2] * shape[3]
+            x = torch.randn(shape, device="cuda")
+            y, dy, dx = torch.empty_like(x), torch.randn(shape, device="cuda"), torch.empty_like(x)
+            report("n", "softmax fwd %s" % (list(shape),), timeit(lambda i: capi.softmax_fwd(y, x), 1), 8 * e)
+            report("n", "softmax bwd %s" % (list(shape),), timeit(lambda i: capi.softmax_bwd(dx, dy, y), 1), 12 * e)
+            del x, y, dy, dx
+        # top-n accuracy beside the loss (predictions and targets in, top_n + 1 values per row or pixel out)
+        for shape in [(65536, 1000, 1, 1), (512, 21, 128, 128)]:
+            e = shape[0] * shape[1] * shape[2] * shape[3]
+            pr = torch.softmax(torch.randn(shape, device="cuda"), dim=1)
+            tg = torch.zeros(shape, device="cuda")
+            tg.scatter_(1, torch.randint(0, shape[1], (shape[0], 1) + shape[2:], device="cuda"), 1.0)
+            out = torch.empty((shape[0], 2) + shape[2:], device="cuda")
+            report("n", "top-1 accuracy %s" % (list(shape),), timeit(lambda i: capi.accuracy_fwd(out, pr, tg, None, 1), 1), 8 * e + 8 * (e // shape[1]))
+            del pr, tg, out
+        # training statistics and apply through the separate channel-group kernels (what the single launch replaces at 7x7)
+        n, c, hw = 1024, 512, 7
+        shape = (n, c, hw, hw)
+        e = n * c * hw * hw
+        x, dy = torch.randn(shape, device="cuda"), torch.randn(shape, device="cuda")
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        gamma, beta = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda") * 0.1
+        saved, sums, bsums = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda"), torch.empty(3 * c, device="cuda")
+        ws = torch.empty(capi.bn_train_workspace_bytes(n, c, hw * hw), dtype=torch.uint8, device="cuda")
+        acts = [capi.relu(0.0)]
+        report("n", "bn_train stats, channel groups N=1024 C=512 7x7", timeit(lambda i: capi.bn_train_stats(sums, x, ws), 1), 4 * e)
+        report("n", "bn_train apply+relu, channel groups N=1024 C=512 7x7", timeit(lambda i: capi.bn_train_apply_act(y, saved, x, gamma, beta, sums, n * hw * hw, 1e-5, acts), 1), 8 * e)
+        report("n", "bn_train bwd stats, channel groups N=1024 C=512 7x7", timeit(lambda i: capi.bn_train_bwd_stats(bsums, dy, x, gamma, beta, saved, acts, ws), 1), 8 * e)
+        report("n", "bn_train bwd apply, channel groups N=1024 C=512 7x7", timeit(lambda i: capi.bn_train_bwd_apply(dx, dy, x, gamma, beta, saved, bsums, bsums, n * hw * hw, acts), 1), 12 * e)
+        # running-statistics calibration pass over the same tensor (one read)
+        acc = capi.bn_calibrate_accumulator(c)
+        mean, invsigma = torch.randn(c, device="cuda") * 0.1, torch.rand(c, device="cuda") + 0.5
+        cws = torch.empty(capi.lib.nnf_bn_calibrate_workspace_bytes(c), dtype=torch.uint8, device="cuda")
+        report("n", "bn calibration statistics N=1024 C=512 7x7", timeit(lambda i: capi.bn_calibrate_accumulate(acc, x, mean, invsigma, workspace=cws), 1), 4 * e)
+        del x, dy, y, dx
+        # optimiser step: one launch over a table of weight chunks (vanilla momentum: data, gradient, previous update in; data, previous
+        # update and the cleared gradient out)
+        parts = []
+        for k in range(16):
+            m = 4 * 1024 * 1024
+            parts.append({"data": torch.randn(m, device="cuda"), "gradient": torch.randn(m, device="cuda"), "prev_upd": torch.zeros(m, device="cuda"),
+                          "update_accum": torch.zeros(1, dtype=torch.float64, device="cuda"), "learning_rate": 0.01, "weight_decay": 1e-4})
+        w = 16 * 4 * 1024 * 1024
+        report("n", "optimiser step, vanilla momentum, 16 chunks of 4 M weights", timeit(lambda i: capi.apply_gradient(parts, momentum_type=capi.MOMENTUM_VANILLA, normalizer=256.0), 1), 24 * w)
+        del parts
     # config 4: inference BN + TanH / Sigmoid bandwidth sweep
     sizes = [128, 1024] if quick else [128, 1024, 4096] + ([8192] if args.sweep_full else [])
     for n in sizes:

@@ -211,19 +211,92 @@ namespace nnf
 		}
 
 		// ---- hw == 1, CTA per row; the row lives in shared memory when it fits, else it is re-read ----
-		template <bool BACKWARD, bool IN_SMEM>
-		__global__ void __launch_bounds__(256) softmax_rows_block_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
+		// THREADS: 256, or 1024 for rows of thousands of logits (one such row fills an SM's shared memory, so the CTA's
+		// own warps are all the parallelism the SM has). VEC: 128-bit accesses (c % 4 == 0, 16-byte aligned rows).
+		template <bool BACKWARD, bool IN_SMEM, int THREADS, bool VEC>
+		__global__ void __launch_bounds__(THREADS) softmax_rows_block_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
 		{
 			extern __shared__ float s_row[];
-			__shared__ float s_red[8];
+			__shared__ float s_red[THREADS / 32];
 			for (int64_t row = blockIdx.x; row < rows; row += gridDim.x)
 			{
 				const float * a = in0 + row * c;
 				float * o = out + row * c;
-				if (!BACKWARD)
+				if (VEC)
+				{
+					const int c4 = c >> 2;
+					const float4 * a4 = reinterpret_cast<const float4 *>(a);
+					float4 * o4 = reinterpret_cast<float4 *>(o);
+					float4 * s4 = reinterpret_cast<float4 *>(s_row);
+					if (!BACKWARD)
+					{
+						float m = kMaxSeed;
+						for (int i = threadIdx.x; i < c4; i += THREADS)
+						{
+							const float4 v = ld_stream(a4 + i);
+							if (IN_SMEM)
+								s4[i] = v;
+							m = ref_max(ref_max(ref_max(ref_max(m, v.x), v.y), v.z), v.w);
+						}
+						m = block_reduce(m, s_red, true);
+						float s = 0.0F;
+						for (int i = threadIdx.x; i < c4; i += THREADS)
+						{
+							const float4 v = IN_SMEM ? s4[i] : a4[i];
+							const float4 e = make_float4(fast_exp(__fsub_rn(v.x, m)), fast_exp(__fsub_rn(v.y, m)), fast_exp(__fsub_rn(v.z, m)), fast_exp(__fsub_rn(v.w, m)));
+							if (IN_SMEM)
+								s4[i] = e;
+							s = __fadd_rn(s, __fadd_rn(__fadd_rn(e.x, e.y), __fadd_rn(e.z, e.w)));
+						}
+						s = block_reduce(s, s_red, false);
+						const float mult = __fdiv_rn(1.0F, s);
+						for (int i = threadIdx.x; i < c4; i += THREADS)
+						{
+							float4 e;
+							if (IN_SMEM)
+								e = s4[i];
+							else
+							{
+								const float4 v = a4[i];
+								e = make_float4(fast_exp(__fsub_rn(v.x, m)), fast_exp(__fsub_rn(v.y, m)), fast_exp(__fsub_rn(v.z, m)), fast_exp(__fsub_rn(v.w, m)));
+							}
+							st_stream(o4 + i, make_float4(__fmul_rn(e.x, mult), __fmul_rn(e.y, mult), __fmul_rn(e.z, mult), __fmul_rn(e.w, mult)));
+						}
+					}
+					else
+					{
+						// in0 = dy, in1 = y; both stay in shared memory for the second pass when they fit
+						const float4 * y4 = reinterpret_cast<const float4 *>(in1 + row * c);
+						float4 * sy4 = s4 + c4;
+						float s = 0.0F;
+						for (int i = threadIdx.x; i < c4; i += THREADS)
+						{
+							const float4 g = ld_stream(a4 + i), y = ld_stream(y4 + i);
+							if (IN_SMEM)
+							{
+								s4[i] = g;
+								sy4[i] = y;
+							}
+							s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fmul_rn(g.x, y.x), __fmul_rn(g.y, y.y)), __fadd_rn(__fmul_rn(g.z, y.z), __fmul_rn(g.w, y.w))));
+						}
+						s = block_reduce(s, s_red, false);
+						for (int i = threadIdx.x; i < c4; i += THREADS)
+						{
+							const float4 g = IN_SMEM ? s4[i] : a4[i], y = IN_SMEM ? sy4[i] : y4[i];
+							float4 r = make_float4(__fmul_rn(y.x, __fsub_rn(g.x, s)), __fmul_rn(y.y, __fsub_rn(g.y, s)), __fmul_rn(y.z, __fsub_rn(g.z, s)), __fmul_rn(y.w, __fsub_rn(g.w, s)));
+							if (add)
+							{
+								const float4 old = o4[i];
+								r = make_float4(__fadd_rn(old.x, r.x), __fadd_rn(old.y, r.y), __fadd_rn(old.z, r.z), __fadd_rn(old.w, r.w));
+							}
+							st_stream(o4 + i, r);
+						}
+					}
+				}
+				else if (!BACKWARD)
 				{
 					float m = kMaxSeed;
-					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					for (int i = threadIdx.x; i < c; i += THREADS)
 					{
 						const float v = a[i];
 						if (IN_SMEM)
@@ -232,7 +305,7 @@ namespace nnf
 					}
 					m = block_reduce(m, s_red, true);
 					float s = 0.0F;
-					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					for (int i = threadIdx.x; i < c; i += THREADS)
 					{
 						const float e = fast_exp(__fsub_rn(IN_SMEM ? s_row[i] : a[i], m));
 						if (IN_SMEM)
@@ -241,7 +314,7 @@ namespace nnf
 					}
 					s = block_reduce(s, s_red, false);
 					const float mult = __fdiv_rn(1.0F, s);
-					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					for (int i = threadIdx.x; i < c; i += THREADS)
 					{
 						const float e = IN_SMEM ? s_row[i] : fast_exp(__fsub_rn(a[i], m));
 						o[i] = __fmul_rn(e, mult);
@@ -250,13 +323,23 @@ namespace nnf
 				else
 				{
 					const float * y = in1 + row * c;
+					float * s_y = s_row + c;
 					float s = 0.0F;
-					for (int i = threadIdx.x; i < c; i += blockDim.x)
-						s = __fadd_rn(s, __fmul_rn(a[i], y[i]));
-					s = block_reduce(s, s_red, false);
-					for (int i = threadIdx.x; i < c; i += blockDim.x)
+					for (int i = threadIdx.x; i < c; i += THREADS)
 					{
-						const float r = __fmul_rn(y[i], __fsub_rn(a[i], s));
+						const float g = a[i], yv = y[i];
+						if (IN_SMEM)
+						{
+							s_row[i] = g;
+							s_y[i] = yv;
+						}
+						s = __fadd_rn(s, __fmul_rn(g, yv));
+					}
+					s = block_reduce(s, s_red, false);
+					for (int i = threadIdx.x; i < c; i += THREADS)
+					{
+						const float g = IN_SMEM ? s_row[i] : a[i], yv = IN_SMEM ? s_y[i] : y[i];
+						const float r = __fmul_rn(yv, __fsub_rn(g, s));
 						o[i] = add ? __fadd_rn(o[i], r) : r;
 					}
 				}
@@ -353,12 +436,27 @@ namespace nnf
 				if (!BACKWARD)
 				{
 					float m = kMaxSeed;
-					for (int f = grp; f < c; f += 8)
+					// four channels of this warp's share at a time: their loads are in flight together (ascending channel order kept)
+					for (int f0 = grp; f0 < c; f0 += 32)
 					{
-						const float v = valid ? in0[base + int64_t(f) * hw] : 0.0F;
-						if (IN_SMEM)
-							s_tile[f * 32 + lane] = v;
-						m = ref_max(m, v);
+						float v[4];
+						#pragma unroll
+						for (int u = 0; u < 4; ++u)
+						{
+							const int f = f0 + 8 * u;
+							v[u] = (valid && f < c) ? ld_stream(in0 + base + int64_t(f) * hw) : 0.0F;
+						}
+						#pragma unroll
+						for (int u = 0; u < 4; ++u)
+						{
+							const int f = f0 + 8 * u;
+							if (f < c)
+							{
+								if (IN_SMEM)
+									s_tile[f * 32 + lane] = v[u];
+								m = ref_max(m, v[u]);
+							}
+						}
 					}
 					s_red[grp][lane] = m;
 					__syncthreads();
@@ -387,7 +485,7 @@ namespace nnf
 						for (int f = grp; f < c; f += 8)
 						{
 							const float e = IN_SMEM ? s_tile[f * 32 + lane] : fast_exp(__fsub_rn(in0[base + int64_t(f) * hw], m));
-							out[base + int64_t(f) * hw] = __fmul_rn(e, mult);
+							st_stream(out + base + int64_t(f) * hw, __fmul_rn(e, mult));
 						}
 					__syncthreads();
 				}
@@ -396,16 +494,30 @@ namespace nnf
 					float * s_dy = s_tile;
 					float * s_y = s_tile + size_t(c) * 32;
 					float s = 0.0F;
-					for (int f = grp; f < c; f += 8)
+					for (int f0 = grp; f0 < c; f0 += 32)
 					{
-						const float g = valid ? in0[base + int64_t(f) * hw] : 0.0F;
-						const float y = valid ? in1[base + int64_t(f) * hw] : 0.0F;
-						if (IN_SMEM)
+						float g[4], y[4];
+						#pragma unroll
+						for (int u = 0; u < 4; ++u)
 						{
-							s_dy[f * 32 + lane] = g;
-							s_y[f * 32 + lane] = y;
+							const int f = f0 + 8 * u;
+							g[u] = (valid && f < c) ? ld_stream(in0 + base + int64_t(f) * hw) : 0.0F;
+							y[u] = (valid && f < c) ? ld_stream(in1 + base + int64_t(f) * hw) : 0.0F;
 						}
-						s = __fadd_rn(s, __fmul_rn(g, y));
+						#pragma unroll
+						for (int u = 0; u < 4; ++u)
+						{
+							const int f = f0 + 8 * u;
+							if (f < c)
+							{
+								if (IN_SMEM)
+								{
+									s_dy[f * 32 + lane] = g[u];
+									s_y[f * 32 + lane] = y[u];
+								}
+								s = __fadd_rn(s, __fmul_rn(g[u], y[u]));
+							}
+						}
 					}
 					s_red[grp][lane] = s;
 					__syncthreads();
@@ -463,17 +575,35 @@ namespace nnf
 #undef NNF_ROWS
 					return check_launch("softmax_rows_warp_kernel");
 				}
-				const int grid = (int)(rows < int64_t(sm_count()) * 4 ? rows : int64_t(sm_count()) * 4);
-				const size_t smem = size_t(c) * sizeof(float);
-				if (!BACKWARD && smem <= staging_smem_limit())
+				// rows of thousands of logits: 1024 threads per CTA; the row (backward: dy and y) stays in shared memory when it fits
+				const bool big = c >= 4096;
+				const bool vec = (c & 3) == 0 && aligned16(out) && aligned16(in0) && (!in1 || aligned16(in1));
+				const size_t smem = size_t(c) * sizeof(float) * (BACKWARD ? 2 : 1);
+				const bool in_smem = smem <= staging_smem_limit();
+				const int per_sm = in_smem ? (int)(staging_smem_limit() / (smem < 1024 ? 1024 : smem)) : (big ? 2 : 8);
+				const int64_t cap = int64_t(sm_count()) * (per_sm < 1 ? 1 : (per_sm > (big ? 2 : 8) ? (big ? 2 : 8) : per_sm));
+				const int grid = (int)(rows < cap ? rows : cap);
+#define NNF_BLOCK(IN, TH, VE) \
+				do { \
+					if (IN) \
+					{ \
+						cudaError_t e = cudaFuncSetAttribute(softmax_rows_block_kernel<BACKWARD, IN, TH, VE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit()); \
+						if (e != cudaSuccess) \
+							return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+					} \
+					softmax_rows_block_kernel<BACKWARD, IN, TH, VE><<<grid, TH, IN ? smem : 0, s>>>(out, in0, in1, rows, (int)c, add); \
+				} while (0)
+				if (in_smem)
 				{
-					cudaError_t e = cudaFuncSetAttribute(softmax_rows_block_kernel<BACKWARD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staging_smem_limit());
-					if (e != cudaSuccess)
-						return set_error(NNF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-					softmax_rows_block_kernel<BACKWARD, true><<<grid, 256, smem, s>>>(out, in0, in1, rows, (int)c, add);
+					if (big) { if (vec) NNF_BLOCK(true, 1024, true); else NNF_BLOCK(true, 1024, false); }
+					else { if (vec) NNF_BLOCK(true, 256, true); else NNF_BLOCK(true, 256, false); }
 				}
 				else
-					softmax_rows_block_kernel<BACKWARD, false><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add);
+				{
+					if (big) { if (vec) NNF_BLOCK(false, 1024, true); else NNF_BLOCK(false, 1024, false); }
+					else { if (vec) NNF_BLOCK(false, 256, true); else NNF_BLOCK(false, 256, false); }
+				}
+#undef NNF_BLOCK
 				return check_launch("softmax_rows_block_kernel");
 			}
 
