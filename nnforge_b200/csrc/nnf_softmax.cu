@@ -417,6 +417,133 @@ namespace nnf
 			}
 		}
 
+		// ---- hw > 1, 33 to 160 channels, planes of whole float4s: a CTA takes 128 neighbouring pixels (a float4 per lane), its
+		// WARPS warps share the channels (warp w: channels w, w + WARPS, ...), every value stays in registers between the load
+		// and the store; maxima and sums cross the warps through shared memory. One pass over the data, 512-byte rows ----
+		template <int CPW, int WARPS, bool BACKWARD>
+		__global__ void __launch_bounds__(WARPS * 32, BACKWARD ? 1 : 2) softmax_pixels_wide_kernel(float * out, const float * in0, const float * in1, int64_t quads, uint32_t hw4, fastdiv hw4div, int c, int add)
+		{
+			__shared__ float4 s_red[WARPS][32];
+			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+			const int64_t ntiles = (quads + 31) / 32;
+			const float4 * in4 = reinterpret_cast<const float4 *>(in0);
+			const float4 * y4 = reinterpret_cast<const float4 *>(in1);
+			float4 * out4 = reinterpret_cast<float4 *>(out);
+			for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x)
+			{
+				const int64_t q = t * 32 + lane;
+				const bool valid = q < quads;
+				const uint32_t entry = valid ? hw4div.div((uint32_t)q) : 0;
+				const uint32_t pq = valid ? (uint32_t)q - entry * hw4 : 0;
+				const int64_t base = int64_t(entry) * c * hw4 + pq;   // in float4s; one channel further = hw4
+				if (!BACKWARD)
+				{
+					float4 v[CPW];
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						const int f = w + k * WARPS;
+						v[k] = (valid && f < c) ? ld_stream(in4 + base + int64_t(f) * hw4) : make_float4(kMaxSeed, kMaxSeed, kMaxSeed, kMaxSeed);
+					}
+					float4 m = make_float4(kMaxSeed, kMaxSeed, kMaxSeed, kMaxSeed);
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						m.x = ref_max(m.x, v[k].x); m.y = ref_max(m.y, v[k].y);
+						m.z = ref_max(m.z, v[k].z); m.w = ref_max(m.w, v[k].w);
+					}
+					s_red[w][lane] = m;
+					__syncthreads();
+					m = make_float4(kMaxSeed, kMaxSeed, kMaxSeed, kMaxSeed);
+					#pragma unroll
+					for (int i = 0; i < WARPS; ++i)
+					{
+						const float4 r = s_red[i][lane];
+						m.x = fmaxf(m.x, r.x); m.y = fmaxf(m.y, r.y); m.z = fmaxf(m.z, r.z); m.w = fmaxf(m.w, r.w);
+					}
+					__syncthreads();
+					float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						const int f = w + k * WARPS;
+						if (f < c)
+						{
+							v[k].x = fast_exp(__fsub_rn(v[k].x, m.x)); v[k].y = fast_exp(__fsub_rn(v[k].y, m.y));
+							v[k].z = fast_exp(__fsub_rn(v[k].z, m.z)); v[k].w = fast_exp(__fsub_rn(v[k].w, m.w));
+							sum.x = __fadd_rn(sum.x, v[k].x); sum.y = __fadd_rn(sum.y, v[k].y);
+							sum.z = __fadd_rn(sum.z, v[k].z); sum.w = __fadd_rn(sum.w, v[k].w);
+						}
+					}
+					s_red[w][lane] = sum;
+					__syncthreads();
+					sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					#pragma unroll
+					for (int i = 0; i < WARPS; ++i)
+					{
+						const float4 r = s_red[i][lane];
+						sum.x = __fadd_rn(sum.x, r.x); sum.y = __fadd_rn(sum.y, r.y); sum.z = __fadd_rn(sum.z, r.z); sum.w = __fadd_rn(sum.w, r.w);
+					}
+					const float4 mult = make_float4(__fdiv_rn(1.0F, sum.x), __fdiv_rn(1.0F, sum.y), __fdiv_rn(1.0F, sum.z), __fdiv_rn(1.0F, sum.w));
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						const int f = w + k * WARPS;
+						if (valid && f < c)
+							st_stream(out4 + base + int64_t(f) * hw4, make_float4(__fmul_rn(v[k].x, mult.x), __fmul_rn(v[k].y, mult.y), __fmul_rn(v[k].z, mult.z), __fmul_rn(v[k].w, mult.w)));
+					}
+					__syncthreads();
+				}
+				else
+				{
+					// in0 = dy, in1 = y
+					float4 g[CPW], y[CPW];
+					float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						const int f = w + k * WARPS;
+						const bool on = valid && f < c;
+						g[k] = on ? ld_stream(in4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						y[k] = on ? ld_stream(y4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					}
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						sum.x = __fadd_rn(sum.x, __fmul_rn(g[k].x, y[k].x)); sum.y = __fadd_rn(sum.y, __fmul_rn(g[k].y, y[k].y));
+						sum.z = __fadd_rn(sum.z, __fmul_rn(g[k].z, y[k].z)); sum.w = __fadd_rn(sum.w, __fmul_rn(g[k].w, y[k].w));
+					}
+					s_red[w][lane] = sum;
+					__syncthreads();
+					sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+					#pragma unroll
+					for (int i = 0; i < WARPS; ++i)
+					{
+						const float4 r = s_red[i][lane];
+						sum.x = __fadd_rn(sum.x, r.x); sum.y = __fadd_rn(sum.y, r.y); sum.z = __fadd_rn(sum.z, r.z); sum.w = __fadd_rn(sum.w, r.w);
+					}
+					#pragma unroll
+					for (int k = 0; k < CPW; ++k)
+					{
+						const int f = w + k * WARPS;
+						if (valid && f < c)
+						{
+							float4 r = make_float4(__fmul_rn(y[k].x, __fsub_rn(g[k].x, sum.x)), __fmul_rn(y[k].y, __fsub_rn(g[k].y, sum.y)),
+								__fmul_rn(y[k].z, __fsub_rn(g[k].z, sum.z)), __fmul_rn(y[k].w, __fsub_rn(g[k].w, sum.w)));
+							float4 * o = out4 + base + int64_t(f) * hw4;
+							if (add)
+							{
+								const float4 old = *o;
+								r = make_float4(__fadd_rn(old.x, r.x), __fadd_rn(old.y, r.y), __fadd_rn(old.z, r.z), __fadd_rn(old.w, r.w));
+							}
+							st_stream(o, r);
+						}
+					}
+					__syncthreads();
+				}
+			}
+		}
+
 		// ---- hw > 1, any C: CTA = 32 pixels x 8 channel groups, column tile staged in shared memory
 		// when it fits (single HBM pass), else re-read from global/L2 --------------------------------
 		template <bool BACKWARD, bool IN_SMEM>
@@ -638,6 +765,35 @@ namespace nnf
 					}
 #undef NNF_EXACT
 					int st = check_launch("softmax_pixels_reg_kernel");
+					if (st != NNF_OK)
+						return st;
+				}
+				else if (c <= 160 && hw % 4 == 0 && aligned16(o) && aligned16(a) && (!b || aligned16(b)))
+				{
+					// values in registers: 16 warps of up to 10 channels forward, 32 warps of up to 5 (two tensors) backward
+					constexpr int kWarps = BACKWARD ? 32 : 16;
+					const int cpw = (int)div_up(c, kWarps);
+					const int64_t quads = pixels / 4;
+					const int64_t ntiles = div_up(quads, 32);
+					const int64_t cap = int64_t(sm_count()) * (BACKWARD ? 2 : 4);
+					const int grid = (int)(ntiles < cap ? ntiles : cap);
+#define NNF_WIDE(CPW) case CPW: softmax_pixels_wide_kernel<CPW, kWarps, BACKWARD><<<grid, kWarps * 32, 0, s>>>(o, a, b, quads, (uint32_t)(hw / 4), fastdiv((uint32_t)(hw / 4)), (int)c, add); break;
+					switch (cpw)
+					{
+					NNF_WIDE(2) NNF_WIDE(3) NNF_WIDE(4) NNF_WIDE(5)   // more than 32 channels: at least two (32 warps) or three (16 warps) per warp
+					default:
+						if constexpr (!BACKWARD)
+						{
+							switch (cpw)
+							{
+							NNF_WIDE(6) NNF_WIDE(7) NNF_WIDE(8) NNF_WIDE(9) NNF_WIDE(10)
+							default: break;
+							}
+						}
+						break;
+					}
+#undef NNF_WIDE
+					int st = check_launch("softmax_pixels_wide_kernel");
 					if (st != NNF_OK)
 						return st;
 				}

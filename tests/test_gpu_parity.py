@@ -205,7 +205,8 @@ def test_add(capi, oracle, count):
 
 
 SOFTMAX_SHAPES = [(256, 1000, 1, 1), (32, 21, 128, 128), (4, 21, 32, 32), (3, 1, 1, 1), (5, 33, 3, 3), (2, 2000, 1, 1), (2, 5000, 1, 3),
-                  (7, 8, 5, 1), (3, 100, 2, 2), (6, 1500, 1, 1), (2, 3, 1, 1), (1, 1700, 2, 2)]
+                  (7, 8, 5, 1), (3, 100, 2, 2), (6, 1500, 1, 1), (2, 3, 1, 1), (1, 1700, 2, 2),
+                  (2, 150, 16, 16), (3, 33, 4, 5), (2, 160, 6, 2), (1, 65, 12, 1), (2, 161, 4, 4), (3, 4100, 1, 1), (2, 8192, 1, 1)]
 
 
 @pytest.mark.parametrize("shape", SOFTMAX_SHAPES)
