@@ -39,6 +39,7 @@ namespace nnf
 		__device__ __forceinline__ float ref_max(float a, float b) { return (a < b) ? b : a; }
 
 		// ---- hw == 1, warp per row ---------------------------------------------------------------
+		// PER_LANE = ceil(c / 32) exactly: only a lane's last slot can lie past the row's end, every other guard folds away
 		template <int PER_LANE, bool BACKWARD>
 		__global__ void __launch_bounds__(256) softmax_rows_warp_kernel(float * out, const float * in0, const float * in1, int64_t rows, int c, int add)
 		{
@@ -57,7 +58,7 @@ namespace nnf
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						v[j] = idx < c ? ld_stream(a + idx) : kMaxSeed;
+						v[j] = (j + 1 < PER_LANE || idx < c) ? ld_stream(a + idx) : kMaxSeed;
 					}
 					float m = kMaxSeed;
 					#pragma unroll
@@ -69,7 +70,7 @@ namespace nnf
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						v[j] = idx < c ? fast_exp(__fsub_rn(v[j], m)) : 0.0F;
+						v[j] = (j + 1 < PER_LANE || idx < c) ? fast_exp(__fsub_rn(v[j], m)) : 0.0F;
 						s = __fadd_rn(s, v[j]);
 					}
 					s = warp_sum(s);
@@ -78,7 +79,7 @@ namespace nnf
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						if (idx < c)
+						if ((j + 1 < PER_LANE || idx < c))
 							st_stream(o + idx, __fmul_rn(v[j], mult));
 					}
 				}
@@ -92,8 +93,8 @@ namespace nnf
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						g[j] = idx < c ? ld_stream(a + idx) : 0.0F;
-						v[j] = idx < c ? ld_stream(y + idx) : 0.0F;
+						g[j] = (j + 1 < PER_LANE || idx < c) ? ld_stream(a + idx) : 0.0F;
+						v[j] = (j + 1 < PER_LANE || idx < c) ? ld_stream(y + idx) : 0.0F;
 						s = __fadd_rn(s, __fmul_rn(g[j], v[j]));
 					}
 					s = warp_sum(s);
@@ -101,7 +102,7 @@ namespace nnf
 					for (int j = 0; j < PER_LANE; ++j)
 					{
 						const int idx = j * 32 + lane;
-						if (idx < c)
+						if ((j + 1 < PER_LANE || idx < c))
 						{
 							const float r = __fmul_rn(v[j], __fsub_rn(g[j], s));
 							o[idx] = add ? __fadd_rn(o[idx], r) : r;
@@ -692,21 +693,25 @@ namespace nnf
 #undef NNF_ROWS4
 						return check_launch("softmax_rows_warp4_kernel");
 					}
-#define NNF_ROWS(PL) softmax_rows_warp_kernel<PL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add)
-					if (c <= 32) NNF_ROWS(1);
-					else if (c <= 64) NNF_ROWS(2);
-					else if (c <= 128) NNF_ROWS(4);
-					else if (c <= 256) NNF_ROWS(8);
-					else if (c <= 512) NNF_ROWS(16);
-					else NNF_ROWS(32);
+#define NNF_ROWS(PL) case PL: softmax_rows_warp_kernel<PL, BACKWARD><<<grid, 256, 0, s>>>(out, in0, in1, rows, (int)c, add); break;
+					switch ((int)div_up(c, 32))
+					{
+					NNF_ROWS(1) NNF_ROWS(2) NNF_ROWS(3) NNF_ROWS(4) NNF_ROWS(5) NNF_ROWS(6) NNF_ROWS(7) NNF_ROWS(8)
+					NNF_ROWS(9) NNF_ROWS(10) NNF_ROWS(11) NNF_ROWS(12) NNF_ROWS(13) NNF_ROWS(14) NNF_ROWS(15) NNF_ROWS(16)
+					NNF_ROWS(17) NNF_ROWS(18) NNF_ROWS(19) NNF_ROWS(20) NNF_ROWS(21) NNF_ROWS(22) NNF_ROWS(23) NNF_ROWS(24)
+					NNF_ROWS(25) NNF_ROWS(26) NNF_ROWS(27) NNF_ROWS(28) NNF_ROWS(29) NNF_ROWS(30) NNF_ROWS(31) NNF_ROWS(32)
+					default: break;
+					}
 #undef NNF_ROWS
 					return check_launch("softmax_rows_warp_kernel");
 				}
-				// rows of thousands of logits: 1024 threads per CTA; the row (backward: dy and y) stays in shared memory when it fits
+				// rows of thousands of logits: 1024 threads per CTA, two CTAs per SM, second and third pass from L2 ([8192,32000] forward:
+				// 531 us with the row staged in shared memory and one CTA per SM, 471 us without); shorter rows (backward: dy and y)
+				// stay in shared memory when they fit
 				const bool big = c >= 4096;
 				const bool vec = (c & 3) == 0 && aligned16(out) && aligned16(in0) && (!in1 || aligned16(in1));
 				const size_t smem = size_t(c) * sizeof(float) * (BACKWARD ? 2 : 1);
-				const bool in_smem = smem <= staging_smem_limit();
+				const bool in_smem = smem <= staging_smem_limit() && !big;
 				const int per_sm = in_smem ? (int)(staging_smem_limit() / (smem < 1024 ? 1024 : smem)) : (big ? 2 : 8);
 				const int64_t cap = int64_t(sm_count()) * (per_sm < 1 ? 1 : (per_sm > (big ? 2 : 8) ? (big ? 2 : 8) : per_sm));
 				const int grid = (int)(rows < cap ? rows : cap);
