@@ -419,10 +419,10 @@ namespace nnf
 		}
 
 		// ---- hw > 1, 33 to 160 channels, planes of whole float4s: a CTA takes 128 neighbouring pixels (a float4 per lane), its
-		// WARPS warps share the channels (warp w: channels w, w + WARPS, ...), every value stays in registers between the load
-		// and the store; maxima and sums cross the warps through shared memory. One pass over the data, 512-byte rows ----
+		// WARPS warps share the channels (warp w: channels w, w + WARPS, ...); forward every value stays in registers between the
+		// load and the store; maxima and sums cross the warps through shared memory. One pass over DRAM, 512-byte rows ----
 		template <int CPW, int WARPS, bool BACKWARD>
-		__global__ void __launch_bounds__(WARPS * 32, BACKWARD ? 1 : 2) softmax_pixels_wide_kernel(float * out, const float * in0, const float * in1, int64_t quads, uint32_t hw4, fastdiv hw4div, int c, int add)
+		__global__ void __launch_bounds__(WARPS * 32, 2) softmax_pixels_wide_kernel(float * out, const float * in0, const float * in1, int64_t quads, uint32_t hw4, fastdiv hw4div, int c, int add)
 		{
 			__shared__ float4 s_red[WARPS][32];
 			const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -497,22 +497,18 @@ namespace nnf
 				}
 				else
 				{
-					// in0 = dy, in1 = y
-					float4 g[CPW], y[CPW];
+					// in0 = dy, in1 = y: not held between the sum and the result but read again (the second time from L2), which
+					// leaves registers for two CTAs per SM ([16,150,128,128]: 87 us; 118 us with both tensors held by one 1024-thread CTA)
 					float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
 					#pragma unroll
 					for (int k = 0; k < CPW; ++k)
 					{
 						const int f = w + k * WARPS;
 						const bool on = valid && f < c;
-						g[k] = on ? ld_stream(in4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-						y[k] = on ? ld_stream(y4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-					}
-					#pragma unroll
-					for (int k = 0; k < CPW; ++k)
-					{
-						sum.x = __fadd_rn(sum.x, __fmul_rn(g[k].x, y[k].x)); sum.y = __fadd_rn(sum.y, __fmul_rn(g[k].y, y[k].y));
-						sum.z = __fadd_rn(sum.z, __fmul_rn(g[k].z, y[k].z)); sum.w = __fadd_rn(sum.w, __fmul_rn(g[k].w, y[k].w));
+						const float4 g = on ? __ldg(in4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						const float4 y = on ? __ldg(y4 + base + int64_t(f) * hw4) : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+						sum.x = __fadd_rn(sum.x, __fmul_rn(g.x, y.x)); sum.y = __fadd_rn(sum.y, __fmul_rn(g.y, y.y));
+						sum.z = __fadd_rn(sum.z, __fmul_rn(g.z, y.z)); sum.w = __fadd_rn(sum.w, __fmul_rn(g.w, y.w));
 					}
 					s_red[w][lane] = sum;
 					__syncthreads();
@@ -529,8 +525,9 @@ namespace nnf
 						const int f = w + k * WARPS;
 						if (valid && f < c)
 						{
-							float4 r = make_float4(__fmul_rn(y[k].x, __fsub_rn(g[k].x, sum.x)), __fmul_rn(y[k].y, __fsub_rn(g[k].y, sum.y)),
-								__fmul_rn(y[k].z, __fsub_rn(g[k].z, sum.z)), __fmul_rn(y[k].w, __fsub_rn(g[k].w, sum.w)));
+							const float4 g = ld_stream(in4 + base + int64_t(f) * hw4), y = ld_stream(y4 + base + int64_t(f) * hw4);
+							float4 r = make_float4(__fmul_rn(y.x, __fsub_rn(g.x, sum.x)), __fmul_rn(y.y, __fsub_rn(g.y, sum.y)),
+								__fmul_rn(y.z, __fsub_rn(g.z, sum.z)), __fmul_rn(y.w, __fsub_rn(g.w, sum.w)));
 							float4 * o = out4 + base + int64_t(f) * hw4;
 							if (add)
 							{
@@ -775,27 +772,18 @@ namespace nnf
 				}
 				else if (c <= 160 && hw % 4 == 0 && aligned16(o) && aligned16(a) && (!b || aligned16(b)))
 				{
-					// values in registers: 16 warps of up to 10 channels forward, 32 warps of up to 5 (two tensors) backward
-					constexpr int kWarps = BACKWARD ? 32 : 16;
+					// 16 warps of up to 10 channels each; forward the values stay in registers, backward dy and y are read twice
+					constexpr int kWarps = 16;
 					const int cpw = (int)div_up(c, kWarps);
 					const int64_t quads = pixels / 4;
 					const int64_t ntiles = div_up(quads, 32);
-					const int64_t cap = int64_t(sm_count()) * (BACKWARD ? 2 : 4);
+					const int64_t cap = int64_t(sm_count()) * 4;
 					const int grid = (int)(ntiles < cap ? ntiles : cap);
 #define NNF_WIDE(CPW) case CPW: softmax_pixels_wide_kernel<CPW, kWarps, BACKWARD><<<grid, kWarps * 32, 0, s>>>(o, a, b, quads, (uint32_t)(hw / 4), fastdiv((uint32_t)(hw / 4)), (int)c, add); break;
-					switch (cpw)
+					switch (cpw)   // more than 32 channels: at least three per warp
 					{
-					NNF_WIDE(2) NNF_WIDE(3) NNF_WIDE(4) NNF_WIDE(5)   // more than 32 channels: at least two (32 warps) or three (16 warps) per warp
-					default:
-						if constexpr (!BACKWARD)
-						{
-							switch (cpw)
-							{
-							NNF_WIDE(6) NNF_WIDE(7) NNF_WIDE(8) NNF_WIDE(9) NNF_WIDE(10)
-							default: break;
-							}
-						}
-						break;
+					NNF_WIDE(3) NNF_WIDE(4) NNF_WIDE(5) NNF_WIDE(6) NNF_WIDE(7) NNF_WIDE(8) NNF_WIDE(9) NNF_WIDE(10)
+					default: break;
 					}
 #undef NNF_WIDE
 					int st = check_launch("softmax_pixels_wide_kernel");
