@@ -37,3 +37,20 @@ def test_argument_errors_without_a_gpu():
     assert capi.lib.nnf_pool_out_size(56, 3, 2, 0) == 27
     assert capi.lib.nnf_pool_out_size(56, 3, 2, 1) == 28
     assert capi.lib.nnf_bn_train_workspace_bytes(256, 256, 784) > 0
+
+
+def test_profile_summaries_name_their_command():
+    """Every ncu summary under profiles/ gives the command that made it, and every ncu command line leaves the clocks alone."""
+    import glob
+    import os
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "profiles")
+    files = sorted(glob.glob(os.path.join(root, "*.md")))
+    assert files, "no profile summaries"
+    for path in files:
+        text = open(path).read()
+        assert "python bench.py" in text, "%s does not name the command that made it" % os.path.basename(path)
+        # a command may be wrapped over several lines with backslashes
+        joined = text.replace("\\\n", " ")
+        for line in joined.splitlines():
+            if line.strip().startswith("ncu "):
+                assert "--clock-control none" in line, "%s: an ncu command without --clock-control none" % os.path.basename(path)
